@@ -1,0 +1,271 @@
+"""Python face of the CUDA library: loads it (building it on first use) and wraps each
+exported C function in a call that takes torch tensors.
+
+There is no fallback: if the library cannot be built or loaded, or no CUDA device is
+present, :func:`lib` raises :class:`ExtensionError`.  Wrappers check devices, element
+types and contiguity, pass raw pointers and the current torch stream, and turn a
+non-zero return code into an exception that names the refused argument.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_long, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+ACT_CODES = {None: 0, "none": 0, "gelu_new": 1, "gelu_pytorch_tanh": 1, "gelu": 2, "relu": 3}
+
+_ERRORS = {
+    -2: "unknown element type",
+    -3: "a size this kernel does not take",
+    -4: "a pointer or stride that is not aligned as the kernel requires",
+    -5: "bad argument",
+    -6: "the device or driver lacks a feature the kernel needs",
+}
+STATUS_TEXT = {
+    1: "token id outside the vocabulary (token index, id, vocabulary size)",
+    2: "position outside the position table or the cache (token index, position, limit)",
+    3: "cache slot outside the pool (token index, slot, pages)",
+    4: "block-table entry missing or outside the pool (token index, position, page)",
+    5: "a bounded wait inside a kernel gave up (kernel id, block, stage)",
+    6: "row index outside its tensor (row, index, rows)",
+}
+
+
+class ExtensionError(RuntimeError):
+    pass
+
+
+class KernelArgumentError(ValueError):
+    pass
+
+
+_LIB = None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; builds it at the first call."""
+    global _LIB
+    if _LIB is None:
+        try:
+            path = _build.build()
+            handle = ctypes.CDLL(path)
+        except (OSError, _build.BuildError) as exc:
+            raise ExtensionError(
+                f"the CUDA extension of pretrained_rstr_b200 is not available: {exc}") from exc
+        _declare(handle)
+        _LIB = handle
+    return _LIB
+
+
+def library_path() -> str:
+    return _build.build()
+
+
+def require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise ExtensionError("pretrained_rstr_b200 runs on a CUDA device only (sm_100a); "
+                             "torch.cuda.is_available() is False and there is no CPU path")
+
+
+def _declare(h: ctypes.CDLL) -> None:
+    P, I, L, F = c_void_p, c_int, c_long, c_float
+    h.prb_embed.argtypes = [P, P, P, P, P, I, I, I, I, I, P, P]
+    h.prb_layernorm.argtypes = [P, P, P, P, P, I, I, I, F, I, P, P]
+    h.prb_bias_act.argtypes = [P, P, P, P, I, I, I, I, I, P]
+    h.prb_kv_append.argtypes = [P, P, P, P, L, P, I, I, I, I, I, I, P, P]
+    h.prb_copy_pages.argtypes = [P, P, I, L, I, I, P, P]
+    h.prb_gemm_f32.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, P]
+    h.prb_attention_generic.argtypes = [P, L, P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I,
+                                        I, P, P]
+    h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
+    h.prb_sample_max_top_k.argtypes = []
+    for name in ("prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
+                 "prb_gemm_f32", "prb_attention_generic", "prb_sample", "prb_sample_max_top_k"):
+        getattr(h, name).restype = c_int
+
+
+# ------------------------------------------------------------------------- helpers
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelArgumentError(f"element type {dtype} is not supported (float32 or bfloat16)")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelArgumentError(f"{what}: {_ERRORS.get(code, 'error')} (code {code})")
+    raise ExtensionError(f"{what}: CUDA error {code} at launch")
+
+
+def _need(t: torch.Tensor, dtype, name: str, what: str) -> None:
+    if not t.is_cuda:
+        raise KernelArgumentError(f"{what}: {name} is not on a CUDA device")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelArgumentError(f"{what}: {name} must be {dtype}, is {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelArgumentError(f"{what}: {name} must be contiguous")
+
+
+# ------------------------------------------------------------------------ kernels
+def embed(out, tokens, positions, wte, wpe, status) -> None:
+    """out[t,:] = wte[tokens[t],:] (+ wpe[positions[t],:]); out float32 [T, width]."""
+    what = "embed"
+    _need(out, torch.float32, "out", what)
+    _need(tokens, torch.int32, "tokens", what)
+    _need(positions, torch.int32, "positions", what)
+    _need(wte, None, "wte", what)
+    n, width = out.shape
+    if wte.shape[1] != width or (wpe is not None and (wpe.shape[1] != width or wpe.dtype != wte.dtype)):
+        raise KernelArgumentError(f"{what}: table widths or types differ from the output's")
+    if tokens.numel() < n or positions.numel() < n:
+        raise KernelArgumentError(f"{what}: fewer token ids or positions than output rows")
+    _check(lib().prb_embed(_p(out), _p(tokens), _p(positions), _p(wte), _p(wpe), n, width,
+                           wte.shape[0], 0 if wpe is None else wpe.shape[0],
+                           dtype_code(wte.dtype), _p(status), _stream()), what)
+
+
+def layernorm(out, x, gamma, beta, eps: float, rows=None, status=None) -> None:
+    """out[r,:] = LayerNorm(x[rows[r],:] or x[r,:]); x float32, out float32 or bfloat16."""
+    what = "layernorm"
+    _need(x, torch.float32, "x", what)
+    _need(out, None, "out", what)
+    _need(gamma, torch.float32, "gamma", what)
+    if beta is not None:
+        _need(beta, torch.float32, "beta", what)
+    n_rows, width = out.shape
+    if x.shape[1] != width or gamma.numel() != width:
+        raise KernelArgumentError(f"{what}: widths differ")
+    if rows is None and x.shape[0] < n_rows:
+        raise KernelArgumentError(f"{what}: fewer input rows than output rows")
+    if rows is not None:
+        _need(rows, torch.int32, "rows", what)
+    _check(lib().prb_layernorm(_p(out), _p(x), _p(gamma), _p(beta), _p(rows), n_rows, x.shape[0],
+                               width, float(eps), dtype_code(out.dtype), _p(status), _stream()),
+           what)
+
+
+def bias_act(out, inp, bias, resid, act) -> None:
+    """out = act(inp + bias) (+ resid), sums in float32."""
+    what = "bias_act"
+    _need(out, None, "out", what)
+    _need(inp, None, "inp", what)
+    m, n = inp.shape
+    if out.shape != inp.shape:
+        raise KernelArgumentError(f"{what}: shapes differ")
+    if bias is not None:
+        _need(bias, torch.float32, "bias", what)
+    if resid is not None:
+        _need(resid, torch.float32, "resid", what)
+    _check(lib().prb_bias_act(_p(out), _p(inp), _p(bias), _p(resid), m, n, ACT_CODES[act],
+                              dtype_code(inp.dtype), dtype_code(out.dtype), _stream()), what)
+
+
+def kv_append(k_pages, v_pages, k_src, v_src, slots, n_tokens, status) -> None:
+    """Write the step's keys and values to their cache slots.  k_pages/v_pages:
+    [pages, kv_heads, page_size, head_dim]; k_src/v_src: [T, kv_heads*head_dim] views that
+    may be column slices of one wider row-major tensor."""
+    what = "kv_append"
+    num_pages, kv_heads, page_size, head_dim = k_pages.shape
+    _need(k_pages, None, "k_pages", what)
+    _need(v_pages, k_pages.dtype, "v_pages", what)
+    _need(slots, torch.int32, "slots", what)
+    for name, s in (("k_src", k_src), ("v_src", v_src)):
+        if s.dtype != k_pages.dtype or s.stride(1) != 1 or s.shape[1] != kv_heads * head_dim:
+            raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
+    if k_src.stride(0) != v_src.stride(0):
+        raise KernelArgumentError(f"{what}: k_src and v_src row strides differ")
+    _check(lib().prb_kv_append(_p(k_pages), _p(v_pages), _p(k_src), _p(v_src), k_src.stride(0),
+                               _p(slots), n_tokens, kv_heads, head_dim, page_size, num_pages,
+                               dtype_code(k_pages.dtype), _p(status), _stream()), what)
+
+
+def copy_pages(storage, pairs, n_pairs, status) -> None:
+    """storage: [pools, pages, ...] contiguous; pairs int32 [n, 2] (source, destination)."""
+    what = "copy_pages"
+    _need(storage, None, "storage", what)
+    _need(pairs, torch.int32, "pairs", what)
+    pools, pages = storage.shape[0], storage.shape[1]
+    page_bytes = storage[0, 0].numel() * storage.element_size()
+    _check(lib().prb_copy_pages(_p(storage), _p(pairs), n_pairs, page_bytes, pools, pages,
+                                _p(status), _stream()), what)
+
+
+def gemm_f32(out, a, w, bias=None, resid=None, act=None) -> None:
+    """out[M,N] = act(a[M,K] . w[N,K]^T + bias) (+ resid): true 32-bit FMA."""
+    what = "gemm_f32"
+    for name, t in (("out", out), ("a", a), ("w", w)):
+        if not t.is_cuda or t.dtype != torch.float32 or t.stride(1) != 1:
+            raise KernelArgumentError(f"{what}: {name} must be float32 on CUDA with unit inner stride")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
+        raise KernelArgumentError(f"{what}: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias", what)
+    if resid is not None:
+        _need(resid, torch.float32, "resid", what)
+        if resid.shape != out.shape or resid.stride(0) != out.stride(0):
+            raise KernelArgumentError(f"{what}: resid must have the output's shape and stride")
+    _check(lib().prb_gemm_f32(_p(out), _p(a), _p(w), _p(bias), _p(resid), m, n, k, a.stride(0),
+                              w.stride(0), out.stride(0), ACT_CODES[act], _stream()), what)
+
+
+def attention_generic(out, q, k_pages, v_pages, block_table, seq_of_token, positions, n_tokens,
+                      n_heads, scale, window, max_context, status) -> None:
+    """Attention of every token of the step over its request's cached keys; 32-bit
+    arithmetic.  q: [T, n_heads*head_dim] (may be a column slice), out likewise."""
+    what = "attention_generic"
+    num_pages, kv_heads, page_size, head_dim = k_pages.shape
+    for name, t in (("out", out), ("q", q)):
+        if t.dtype != k_pages.dtype or t.stride(1) != 1 or t.shape[1] != n_heads * head_dim:
+            raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
+    _need(block_table, torch.int32, "block_table", what)
+    _need(seq_of_token, torch.int32, "seq_of_token", what)
+    _need(positions, torch.int32, "positions", what)
+    _check(lib().prb_attention_generic(
+        _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(block_table),
+        _p(seq_of_token), _p(positions), n_tokens, n_heads, kv_heads, head_dim, page_size,
+        block_table.shape[1], num_pages, max_context, float(scale), int(window or 0),
+        dtype_code(k_pages.dtype), _p(status), _stream()), what)
+
+
+def max_top_k() -> int:
+    return lib().prb_sample_max_top_k()
+
+
+def sample(out, logits, n_rows, temperature=None, top_k=None, top_p=None, seeds=None, fresh=None,
+           slots=None, rng_states=None) -> None:
+    """out[r] = chosen token of logits[r,:] (float32).  Without ``temperature`` every row
+    is greedy; otherwise rows with temperature <= 0 are greedy and the rest sample."""
+    what = "sample"
+    _need(out, torch.int32, "out", what)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: logits must be float32 with unit inner stride")
+    if temperature is not None:
+        _need(temperature, torch.float32, "temperature", what)
+        _need(top_k, torch.int32, "top_k", what)
+        _need(top_p, torch.float32, "top_p", what)
+        _need(seeds, torch.int64, "seeds", what)
+        _need(fresh, torch.int32, "fresh", what)
+        _need(slots, torch.int32, "slots", what)
+        _need(rng_states, torch.int64, "rng_states", what)
+    _check(lib().prb_sample(_p(out), _p(logits), logits.stride(0), logits.shape[1],
+                            _p(temperature), _p(top_k), _p(top_p), _p(seeds), _p(fresh), _p(slots),
+                            _p(rng_states), n_rows, _stream()), what)

@@ -1,0 +1,221 @@
+"""The batch of one step as the kernels see it.
+
+The reference already describes a ragged batch at its attention interface: packed
+queries with ``row_offsets int32[B+1]`` and ``positions int32[tokens]``, a dense
+``page_table`` padded with -1, ``lengths`` and a ``slot_mapping``
+(``src/pretrained/continuation/paged_attention.clj:196-205``,
+``paged_decoder.clj:562-573``).  The same arrays are used here for the whole step, for
+any mix of prompt portions and single decoded tokens.
+
+All integer arrays of a step live in ONE int32 buffer: it is filled on the host in
+pinned memory and reaches the device in a single copy.  The offsets inside the buffer
+depend only on the capacities (tokens, requests) the layout was made for, so a layout's
+device addresses do not change from step to step; unused token rows carry request -1
+and slot -1 and are skipped by every kernel that touches the cache.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+
+@dataclass
+class Entry:
+    """One request's share of a step: its next tokens and the places (indices into
+    ``tokens``) whose logits are wanted."""
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass(frozen=True)
+class Runtime:
+    """How a model is instantiated on the device."""
+    device: torch.device
+    dtype: torch.dtype                 # weights, activations between products, cache
+    page_size: int = 64
+    max_batched_tokens: int = 2048
+    max_requests: int = 64
+
+    @property
+    def serving(self) -> bool:
+        return self.dtype == torch.bfloat16
+
+
+class BatchLayout:
+    """Offsets (in int32 words) of every array for given capacities."""
+
+    def __init__(self, t_cap: int, b_cap: int, n_groups: int, max_pages: int):
+        self.t_cap, self.b_cap, self.n_groups, self.max_pages = t_cap, b_cap, n_groups, max_pages
+        off = 0
+
+        def take(n: int) -> int:
+            nonlocal off
+            start = off
+            off += (n + 3) // 4 * 4          # keep every array 16-byte aligned
+            return start
+
+        self.tokens = take(t_cap)
+        self.positions = take(t_cap)
+        self.seq_of_token = take(t_cap)
+        self.logit_rows = take(t_cap)
+        self.q_start = take(b_cap + 1)
+        self.kv_len = take(b_cap)
+        self.state_slot = take(b_cap)
+        self.fresh = take(b_cap)
+        self.slots = [take(t_cap) for _ in range(n_groups)]
+        self.first_pos = [take(b_cap) for _ in range(n_groups)]
+        self.block_table = [take(b_cap * max_pages) for _ in range(n_groups)]
+        self.size = off
+
+
+@dataclass
+class GroupView:
+    """A cache group's arrays for this step (device int32 views)."""
+    slots: torch.Tensor            # [t_cap]   slot of each new token, -1 = none
+    block_table: torch.Tensor      # [b_cap, max_pages], -1 = no page
+    first_pos: torch.Tensor        # [b_cap]   lowest position still held (windows)
+    window: Optional[int]
+    page_size: int
+    num_pages: int
+
+
+@dataclass
+class HostBatch:
+    """The same step in plain Python, for parts written with array-library calls
+    (tests' toy parts) and for the engine's own book-keeping."""
+    rids: List[Hashable]
+    q_start: List[int]             # B+1 offsets into the token rows
+    start_pos: List[int]           # position of each request's first token in this step
+    state_slot: List[int]
+    fresh: List[bool]
+    tokens: List[int]
+
+
+class StepContext:
+    """Everything a part may ask about the step."""
+
+    def __init__(self, runtime: Runtime, layout: BatchLayout, device_buf: torch.Tensor,
+                 n_tokens: int, n_requests: int, n_rows: int, host: HostBatch,
+                 groups: List[GroupView], status: torch.Tensor, scratch_pool: "ScratchPool",
+                 max_context: int, max_q_len: int, launch_tokens: int, launch_rows: int):
+        self.runtime = runtime
+        self.layout = layout
+        self.n_tokens = n_tokens            # real tokens of the step
+        self.n_requests = n_requests
+        self.n_rows = n_rows                # logits rows wanted
+        self.launch_tokens = launch_tokens  # rows the kernels run (>= n_tokens when padded)
+        self.launch_rows = launch_rows      # logits rows computed (>= n_rows when padded)
+        self.host = host
+        self.groups = groups
+        self.status = status
+        self.max_context = max_context      # upper bound of any request's length after the step
+        self.max_q_len = max_q_len
+        self._scratch = scratch_pool
+        lay, buf = layout, device_buf
+        self.tokens = buf[lay.tokens:lay.tokens + lay.t_cap]
+        self.positions = buf[lay.positions:lay.positions + lay.t_cap]
+        self.seq_of_token = buf[lay.seq_of_token:lay.seq_of_token + lay.t_cap]
+        self.logit_rows = buf[lay.logit_rows:lay.logit_rows + lay.t_cap]
+        self.q_start = buf[lay.q_start:lay.q_start + lay.b_cap + 1]
+        self.kv_len = buf[lay.kv_len:lay.kv_len + lay.b_cap]
+        self.state_slot = buf[lay.state_slot:lay.state_slot + lay.b_cap]
+        self.fresh = buf[lay.fresh:lay.fresh + lay.b_cap]
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.runtime.dtype
+
+    @property
+    def token_capacity(self) -> int:
+        """Rows to give scratch tensors that hold one row per token."""
+        return self.runtime.max_batched_tokens
+
+    @staticmethod
+    def row_capacity(rows: int) -> int:
+        """Rows to give scratch tensors that hold one row per wanted logits row."""
+        cap = 8
+        while cap < rows:
+            cap *= 2
+        return cap
+
+    def scratch(self, key: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """Scratch memory with a stable address for (key, shape, dtype).  Contents do not
+        survive the step; two parts that use the same key share the memory."""
+        return self._scratch.get(key, shape, dtype)
+
+
+class ScratchPool:
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._bufs: Dict[Tuple, torch.Tensor] = {}
+
+    def get(self, key: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        k = (key, tuple(shape), dtype)
+        buf = self._bufs.get(k)
+        if buf is None:
+            buf = torch.empty(tuple(shape), dtype=dtype, device=self.device)
+            self._bufs[k] = buf
+        return buf
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: List[List[int]],
+                     start_pos: List[int], state_slots: List[int], fresh: List[bool],
+                     group_slots: List[List[List[int]]], group_tables: List[List[List[int]]],
+                     group_first: List[List[int]], logit_rows: List[int]) -> Tuple[int, int]:
+    """Write one step into the pinned host buffer.  Returns (tokens, requests)."""
+    lay = layout
+    n_req = len(entries_tokens)
+    t = 0
+    tok = host_np[lay.tokens:lay.tokens + lay.t_cap]
+    pos = host_np[lay.positions:lay.positions + lay.t_cap]
+    seq = host_np[lay.seq_of_token:lay.seq_of_token + lay.t_cap]
+    rows = host_np[lay.logit_rows:lay.logit_rows + lay.t_cap]
+    qs = host_np[lay.q_start:lay.q_start + lay.b_cap + 1]
+    kv = host_np[lay.kv_len:lay.kv_len + lay.b_cap]
+    ss = host_np[lay.state_slot:lay.state_slot + lay.b_cap]
+    fr = host_np[lay.fresh:lay.fresh + lay.b_cap]
+    for b, toks in enumerate(entries_tokens):
+        n = len(toks)
+        tok[t:t + n] = toks
+        pos[t:t + n] = np.arange(start_pos[b], start_pos[b] + n, dtype=np.int32)
+        seq[t:t + n] = b
+        qs[b] = t
+        kv[b] = start_pos[b] + n
+        ss[b] = state_slots[b]
+        fr[b] = 1 if fresh[b] else 0
+        t += n
+    n_tok = t
+    tok[n_tok:] = 0
+    pos[n_tok:] = 0
+    seq[n_tok:] = -1
+    qs[n_req:] = n_tok
+    kv[n_req:] = 0
+    ss[n_req:] = 0
+    fr[n_req:] = 0
+    rows[:len(logit_rows)] = logit_rows
+    rows[len(logit_rows):] = 0
+    for g in range(lay.n_groups):
+        sl = host_np[lay.slots[g]:lay.slots[g] + lay.t_cap]
+        t = 0
+        for b in range(n_req):
+            n = len(group_slots[g][b])
+            sl[t:t + n] = group_slots[g][b]
+            t += n
+        sl[n_tok:] = -1
+        fp = host_np[lay.first_pos[g]:lay.first_pos[g] + lay.b_cap]
+        fp[:n_req] = group_first[g]
+        fp[n_req:] = 0
+        bt = host_np[lay.block_table[g]:lay.block_table[g] + lay.b_cap * lay.max_pages]
+        bt[:] = -1
+        bt2 = bt.reshape(lay.b_cap, lay.max_pages)
+        for b in range(n_req):
+            table = group_tables[g][b]
+            bt2[b, :len(table)] = table
+    return n_tok, n_req

@@ -1,0 +1,209 @@
+"""The step function.
+
+``ModelRunner.step(entries)`` takes a batch of (request, its next tokens, wanted
+places): portions of prompts beside single decoded tokens, cut anywhere.  It runs only
+the tokens it is given, as one batch, from the cache earlier steps left, and returns the
+logits at the wanted places.  It is the reference's ``step-lanes!`` and
+``prefill-range!`` (``src/pretrained/continuation/paged_decoder.clj:512-583, 638-711``)
+made one: reserve slots -> describe the batch -> run -> commit, and abort the
+reservation if anything fails (``:580-583``).
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+from ..csrc import ops
+from .batch import (BatchLayout, Entry, GroupView, HostBatch, Runtime, ScratchPool, StepContext,
+                    fill_host_buffer)
+
+
+class StepError(RuntimeError):
+    pass
+
+
+def _bucket(n: int, floor: int, cap: int) -> int:
+    b = floor
+    while b < n:
+        b *= 2
+    return min(b, cap) if cap >= n else n
+
+
+class ModelRunner:
+    def __init__(self, model, runtime: Runtime, cache: CacheManager, storage: CacheStorage):
+        self.model, self.runtime, self.cache, self.storage = model, runtime, cache, storage
+        self.device = runtime.device
+        model.attach_storage(storage)
+        self.n_groups = len(cache.groups)
+        self.max_pages = cache.max_pages_per_request
+        self._layouts: Dict[tuple, BatchLayout] = {}
+        biggest = BatchLayout(runtime.max_batched_tokens, runtime.max_requests, self.n_groups,
+                              self.max_pages)
+        # two pinned staging buffers, used in turn, each guarded by an event
+        self._hosts = [torch.empty(biggest.size, dtype=torch.int32, pin_memory=True)
+                       for _ in range(2)]
+        self._host_events = [torch.cuda.Event() for _ in range(2)]
+        self._host_turn = 0
+        self._dev = torch.zeros(biggest.size, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
+        self._pairs_host = torch.empty((runtime.max_requests, 2), dtype=torch.int32,
+                                       pin_memory=True)
+        self._pairs_dev = torch.zeros((runtime.max_requests, 2), dtype=torch.int32,
+                                      device=self.device)
+        self.scratch = ScratchPool(self.device)
+        self.fail_next_step: Optional[Exception] = None      # host-side fault injection (tests)
+        self.counters = {"steps": 0, "tokens": 0, "cow_copies": 0}
+
+    # ------------------------------------------------------------------ layout
+    def layout_for(self, n_tokens: int, n_requests: int) -> BatchLayout:
+        key = (_bucket(n_tokens, 8, self.runtime.max_batched_tokens),
+               _bucket(n_requests, 1, self.runtime.max_requests))
+        lay = self._layouts.get(key)
+        if lay is None:
+            lay = BatchLayout(key[0], key[1], self.n_groups, self.max_pages)
+            self._layouts[key] = lay
+        return lay
+
+    # -------------------------------------------------------------------- step
+    def step(self, entries: Sequence[Entry]) -> torch.Tensor:
+        """Run one batch; returns float32 logits ``[wanted, vocab]`` in the order of the
+        entries and of each entry's ``want`` (a view of scratch memory, valid until the
+        next step).  New requests must have been opened in the cache manager."""
+        ctx = self.prepare(entries)
+        try:
+            if self.fail_next_step is not None:
+                exc, self.fail_next_step = self.fail_next_step, None
+                raise exc
+            logits = self.model.forward(ctx)
+        except Exception:
+            self.abort(entries)
+            raise
+        self.commit(entries)
+        return logits[:ctx.n_rows]
+
+    def prepare(self, entries: Sequence[Entry]) -> StepContext:
+        """Validate the batch, reserve cache slots, and put the step's arrays on the device."""
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        rids = [e.rid for e in entries]
+        if len(set(rids)) != len(rids):
+            raise StepError("a request appears twice in one step")
+        if len(entries) > self.runtime.max_requests:
+            raise StepError(f"{len(entries)} requests in one step; the runtime takes "
+                            f"{self.runtime.max_requests}")
+        total = sum(len(e.tokens) for e in entries)
+        if total > self.runtime.max_batched_tokens:
+            raise StepError(f"{total} tokens in one step; the runtime takes "
+                            f"{self.runtime.max_batched_tokens}")
+        vocab = self.model.vocab
+        for e in entries:
+            if len(e.tokens) == 0:
+                raise StepError(f"request {e.rid!r}: no tokens in this step")
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise StepError(f"request {e.rid!r}: wanted place {w} outside its "
+                                    f"{len(e.tokens)} tokens")
+            for tkn in e.tokens:
+                if not 0 <= tkn < vocab:
+                    raise StepError(f"request {e.rid!r}: token id {tkn} outside the vocabulary "
+                                    f"of {vocab}")
+            if self.cache.length(e.rid) + len(e.tokens) > self.model.max_positions:
+                raise StepError(f"request {e.rid!r}: {self.cache.length(e.rid)}+{len(e.tokens)} "
+                                f"tokens exceed the model's {self.model.max_positions} positions")
+        reserved: List[Hashable] = []
+        try:
+            reservations = []
+            for e in entries:
+                reservations.append(self.cache.reserve(e.rid, len(e.tokens)))
+                reserved.append(e.rid)
+        except Exception:
+            for rid in reserved:
+                self.cache.abort(rid)
+            raise
+        try:
+            return self._describe(entries, reservations)
+        except Exception:
+            self.abort(entries)
+            raise
+
+    def _describe(self, entries, reservations) -> StepContext:
+        n_req = len(entries)
+        total = sum(len(e.tokens) for e in entries)
+        layout = self.layout_for(total, n_req)
+        start_pos = [r.start for r in reservations]
+        state_slots = [self.cache.slot(e.rid) for e in entries]
+        fresh = [self.cache.is_fresh(e.rid) for e in entries]
+        group_slots = [[r.slots[g] for r in reservations] for g in range(self.n_groups)]
+        group_tables = [[self.cache.block_table(e.rid, g) for e in entries]
+                        for g in range(self.n_groups)]
+        group_first = [[self.cache.first_visible(e.rid, g) for e in entries]
+                       for g in range(self.n_groups)]
+        logit_rows: List[int] = []
+        q_start = [0]
+        for e in entries:
+            logit_rows.extend(q_start[-1] + w for w in e.want)
+            q_start.append(q_start[-1] + len(e.tokens))
+        turn = self._host_turn
+        self._host_turn ^= 1
+        self._host_events[turn].synchronize()        # the copy that last used this buffer is done
+        staging = self._hosts[turn]
+        fill_host_buffer(staging.numpy(), layout, [list(e.tokens) for e in entries], start_pos,
+                         state_slots, fresh, group_slots, group_tables, group_first, logit_rows)
+        self._dev[:layout.size].copy_(staging[:layout.size], non_blocking=True)
+        self._host_events[turn].record()
+        # copy-on-write page copies come before anything reads or writes the new pages
+        for g in range(self.n_groups):
+            pairs = [(src, dst) for r in reservations for (gg, src, dst) in r.copies if gg == g]
+            for i in range(0, len(pairs), self._pairs_host.shape[0]):
+                chunk = pairs[i:i + self._pairs_host.shape[0]]
+                self._pairs_host[:len(chunk)] = torch.tensor(chunk, dtype=torch.int32)
+                self._pairs_dev[:len(chunk)].copy_(self._pairs_host[:len(chunk)], non_blocking=True)
+                self.storage.copy_pages(g, self._pairs_dev, len(chunk), self.status)
+                torch.cuda.current_stream().synchronize()      # pinned pairs buffer is reused
+                self.counters["cow_copies"] += len(chunk)
+        groups = []
+        for g, spec in enumerate(self.cache.groups):
+            lay = layout
+            groups.append(GroupView(
+                slots=self._dev[lay.slots[g]:lay.slots[g] + lay.t_cap],
+                block_table=self._dev[lay.block_table[g]:lay.block_table[g]
+                                      + lay.b_cap * lay.max_pages].view(lay.b_cap, lay.max_pages),
+                first_pos=self._dev[lay.first_pos[g]:lay.first_pos[g] + lay.b_cap],
+                window=spec.window, page_size=self.cache.page_size,
+                num_pages=self.cache.allocators[g].num_pages))
+        host = HostBatch(rids=[e.rid for e in entries], q_start=q_start, start_pos=start_pos,
+                         state_slot=state_slots, fresh=fresh,
+                         tokens=[t for e in entries for t in e.tokens])
+        max_len = max(s + len(e.tokens) for s, e in zip(start_pos, entries))
+        max_context = min(self.model.max_positions, -(-max_len // 256) * 256)
+        max_q = max(len(e.tokens) for e in entries)
+        self.counters["steps"] += 1
+        self.counters["tokens"] += total
+        return StepContext(self.runtime, layout, self._dev, total, n_req, len(logit_rows), host,
+                           groups, self.status, self.scratch, max_context, max_q,
+                           launch_tokens=total, launch_rows=len(logit_rows))
+
+    def commit(self, entries: Sequence[Entry]) -> None:
+        for e in entries:
+            self.cache.commit(e.rid, list(e.tokens))
+
+    def abort(self, entries: Sequence[Entry]) -> None:
+        for e in entries:
+            self.cache.abort(e.rid)
+
+    # ------------------------------------------------------------------ status
+    def check_status(self) -> None:
+        """Read the device status word (synchronises); raises if a kernel recorded an
+        index out of range.  The word is cleared afterwards."""
+        self._status_host.copy_(self.status, non_blocking=False)
+        code = int(self._status_host[0])
+        if code != 0:
+            detail = [int(v) for v in self._status_host[1:]]
+            self.status.zero_()
+            raise StepError(f"device status {code}: {ops.STATUS_TEXT.get(code, 'unknown')} "
+                            f"{detail}")

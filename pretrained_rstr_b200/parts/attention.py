@@ -1,0 +1,84 @@
+"""Causal attention over the paged cache as a mixer.
+
+Order inside a layer follows the reference's paged decoder
+(``src/pretrained/continuation/paged_decoder.clj:266-278``): project Q, K, V; write the
+new keys and values to their slots; attend over the block table, the step's own
+tokens included; project the result and add it to the residual stream.
+
+Sizes and constants are parameters: width, number of query heads and of key/value
+heads (groups), head size, score scale, window, whether the projections have biases,
+and the checkpoint's weight layout.  The fused QKV matrix has columns [Q | K | V]
+(``dev/examples/gpt2.clj:186-194``); head h owns columns h*head_dim..(h+1)*head_dim of
+its part.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..csrc import ops
+from .interfaces import KVSpec, LayerCache, Mixer
+from .linear import Linear
+from .registry import register_part
+
+
+class CausalAttention(Mixer):
+    def __init__(self, qkv: Linear, out: Linear, width: int, n_head: int, n_kv_head: int,
+                 head_dim: int, scale: float, window: Optional[int], runtime,
+                 position=None):
+        if n_head % n_kv_head != 0:
+            raise ValueError(f"causal_attention: {n_head} query heads are not a multiple of "
+                             f"{n_kv_head} key/value heads")
+        self.q_width = n_head * head_dim
+        self.kv_width = n_kv_head * head_dim
+        if qkv.n_out != self.q_width + 2 * self.kv_width or qkv.n_in != width:
+            raise ValueError("causal_attention: fused QKV matrix has the wrong shape")
+        if out.n_in != self.q_width or out.n_out != width:
+            raise ValueError("causal_attention: output projection has the wrong shape")
+        self.qkv, self.out = qkv, out
+        self.width, self.n_head, self.n_kv_head, self.head_dim = width, n_head, n_kv_head, head_dim
+        self.scale, self.window = float(scale), window
+        self.runtime = runtime
+        self.position = position
+
+    def kv_spec(self) -> KVSpec:
+        return KVSpec(self.n_kv_head, self.head_dim, self.window)
+
+    def forward(self, ctx, h, x, cache: LayerCache) -> None:
+        t = h.shape[0]
+        dtype = self.runtime.dtype
+        qkv = ctx.scratch("attn_qkv", (ctx.token_capacity, self.qkv.n_out), dtype)[:t]
+        self.qkv.forward(ctx, h, qkv)
+        q = qkv[:, :self.q_width]
+        k = qkv[:, self.q_width:self.q_width + self.kv_width]
+        v = qkv[:, self.q_width + self.kv_width:]
+        if self.position is not None:
+            self.position.rotate(ctx, q, k)
+        group = ctx.groups[cache.group]
+        if cache.writes:
+            ops.kv_append(cache.k, cache.v, k, v, group.slots, t, ctx.status)
+        o = ctx.scratch("attn_out", (ctx.token_capacity, self.q_width), dtype)[:t]
+        attend(ctx, o, q, cache, group, self.n_head, self.scale, self.window)
+        self.out.forward(ctx, o, x, resid=x)
+
+
+def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
+           window: Optional[int]) -> None:
+    """Attention of the step's tokens over their requests' cached keys and values."""
+    ops.attention_generic(out, q, cache.k, cache.v, group.block_table, ctx.seq_of_token,
+                          ctx.positions, out.shape[0], n_head, scale, window,
+                          ctx.max_context, ctx.status)
+
+
+def _causal_attention(p, store, rt) -> CausalAttention:
+    width, nh, nkv, dh = p["width"], p["n_head"], p["n_kv_head"], p["head_dim"]
+    layout = p.get("weight_layout", "out_in")
+    qkv = Linear.from_store(store, p["weights"]["qkv"], layout, width, (nh + 2 * nkv) * dh,
+                            p.get("bias", False), rt)
+    out = Linear.from_store(store, p["weights"]["out"], layout, nh * dh, width,
+                            p.get("bias", False), rt)
+    return CausalAttention(qkv, out, width, nh, nkv, dh, p["scale"], p.get("window"), rt)
+
+
+register_part("mixer", "causal_attention", _causal_attention)
