@@ -1,0 +1,172 @@
+"""The generation engine: scheduler above the step function, sampling below it.
+
+One iteration (the reference's ``execute-lanes!``,
+``src/pretrained/continuation/paged_runtime.clj:214-286``): plan the iteration, build
+the batch from the plan, run one step, choose a token for every request that asked for
+logits, report the tokens to the scheduler, which advances, finishes and frees.
+Only token ids cross the host/device boundary: ids in, one int32 per sampled row out
+(``paged_decoder.clj:562-579``).
+"""
+from __future__ import annotations
+
+import os
+from typing import Callable, Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from ..csrc import ops
+from .batch import Entry
+from .loading import LoadedModel
+from .scheduler import Plan, Request, SamplingParams, Scheduler, SchedulerOptions
+
+
+class Engine:
+    def __init__(self, lm: LoadedModel, opts: Optional[SchedulerOptions] = None):
+        self.lm = lm
+        rt = lm.runtime
+        self.opts = opts or SchedulerOptions(max_batched_tokens=rt.max_batched_tokens,
+                                             max_lanes=rt.max_requests)
+        if self.opts.max_batched_tokens > rt.max_batched_tokens or \
+                self.opts.max_lanes > rt.max_requests:
+            raise ValueError("scheduler capacities exceed what the runtime was loaded with")
+        self.scheduler = Scheduler(self.opts, lm.cache)
+        self.runner = lm.runner
+        dev, n = rt.device, rt.max_requests
+        # per-request sampler state lives in the request's state slot
+        self.rng_states = torch.zeros(n, dtype=torch.int64, device=dev)
+        self._rng_started: Dict[Hashable, bool] = {}
+        self._tokens_dev = torch.zeros(n, dtype=torch.int32, device=dev)
+        self._tokens_host = torch.zeros(n, dtype=torch.int32, pin_memory=True)
+        self._p = {  # pinned staging and device copies of the sampler's per-row options
+            "temperature": (torch.zeros(n, dtype=torch.float32, pin_memory=True),
+                            torch.zeros(n, dtype=torch.float32, device=dev)),
+            "top_p": (torch.zeros(n, dtype=torch.float32, pin_memory=True),
+                      torch.zeros(n, dtype=torch.float32, device=dev)),
+            "top_k": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
+                      torch.zeros(n, dtype=torch.int32, device=dev)),
+            "fresh": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
+                      torch.zeros(n, dtype=torch.int32, device=dev)),
+            "slots": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
+                      torch.zeros(n, dtype=torch.int32, device=dev)),
+            "seeds": (torch.zeros(n, dtype=torch.int64, pin_memory=True),
+                      torch.zeros(n, dtype=torch.int64, device=dev)),
+        }
+        self.max_top_k = ops.max_top_k()
+
+    # ------------------------------------------------------------------ requests
+    def submit(self, rid: Hashable, prompt: Sequence[int], max_new_tokens: int,
+               sampling: Optional[SamplingParams] = None, eos_ids: Sequence[int] = (),
+               on_token: Optional[Callable[[Hashable, int], None]] = None) -> Request:
+        sampling = sampling or SamplingParams()
+        if not sampling.greedy:
+            k = 40 if sampling.top_k is None else int(sampling.top_k)
+            if k < 1:
+                raise ValueError("top_k must be >= 1")
+            if min(k, self.lm.model.vocab) > self.max_top_k:
+                raise ValueError(f"top_k={k} exceeds the sampling kernel's limit of {self.max_top_k}")
+            p = 1.0 if sampling.top_p is None else float(sampling.top_p)
+            if not 0.0 < p <= 1.0:
+                raise ValueError("top_p must be in (0, 1]")
+        vocab = self.lm.model.vocab
+        for t in prompt:
+            if not 0 <= int(t) < vocab:
+                raise ValueError(f"prompt token id {t} outside the vocabulary of {vocab}")
+        req = Request(rid=rid, prompt=[int(t) for t in prompt], max_new_tokens=int(max_new_tokens),
+                      sampling=sampling, eos_ids=tuple(int(e) for e in eos_ids), on_token=on_token)
+        self.scheduler.submit(req)
+        return req
+
+    def cancel(self, rid: Hashable) -> None:
+        self.scheduler.cancel(rid)
+
+    # ---------------------------------------------------------------------- step
+    def step(self) -> List[Request]:
+        """One iteration; returns the requests that finished in it."""
+        plan = self.scheduler.next_plan()
+        if not plan.scheduled:
+            return []
+        entries: List[Entry] = []
+        samplers: List[Request] = []
+        for item in plan.scheduled:
+            tokens = self.scheduler.step_tokens(item)
+            wants = self.scheduler.wants_logits(item)
+            entries.append(Entry(item.rid, tokens, [len(tokens) - 1] if wants else []))
+            if wants:
+                samplers.append(self.scheduler.running[item.rid])
+        logits = self.runner.step(entries)
+        new_tokens: Dict[Hashable, int] = {}
+        if samplers:
+            chosen = self._choose(logits, samplers)
+            new_tokens = {r.rid: t for r, t in zip(samplers, chosen)}
+        done = self.scheduler.complete(plan, new_tokens)
+        for r in done:
+            self._rng_started.pop(r.rid, None)
+        return done
+
+    def _choose(self, logits: torch.Tensor, requests: List[Request]) -> List[int]:
+        n = len(requests)
+        out = self._tokens_dev
+        if all(r.sampling.greedy for r in requests):
+            ops.sample(out, logits, n)
+        else:
+            for i, r in enumerate(requests):
+                sp = r.sampling
+                self._p["temperature"][0][i] = 0.0 if sp.greedy else float(sp.temperature)
+                self._p["top_p"][0][i] = 1.0 if sp.top_p is None else float(sp.top_p)
+                self._p["top_k"][0][i] = 40 if sp.top_k is None else int(sp.top_k)
+                started = self._rng_started.get(r.rid, False)
+                self._p["fresh"][0][i] = 0 if started else 1
+                if not started and not sp.greedy:
+                    self._rng_started[r.rid] = True
+                self._p["slots"][0][i] = self.lm.cache.slot(r.rid)
+                if sp.seed is None:           # unseeded, like java.util.Random() without a seed
+                    seed = int.from_bytes(os.urandom(6), "little")
+                else:
+                    seed = int(sp.seed)
+                self._p["seeds"][0][i] = seed
+            for host, dev in self._p.values():
+                dev[:n].copy_(host[:n], non_blocking=True)
+            ops.sample(out, logits, n, temperature=self._p["temperature"][1],
+                       top_k=self._p["top_k"][1], top_p=self._p["top_p"][1],
+                       seeds=self._p["seeds"][1], fresh=self._p["fresh"][1],
+                       slots=self._p["slots"][1], rng_states=self.rng_states)
+        self._tokens_host[:n].copy_(out[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.runner.check_status()
+        return [int(t) for t in self._tokens_host[:n].tolist()]
+
+    # ------------------------------------------------------------------ generate
+    def run(self) -> None:
+        """Iterate until every submitted request has finished."""
+        while not self.scheduler.idle:
+            before = (len(self.scheduler.waiting), len(self.scheduler.running))
+            done = self.step()
+            if not done and not self.scheduler.running and self.scheduler.waiting and \
+                    before == (len(self.scheduler.waiting), 0):
+                raise RuntimeError("scheduler made no progress: a waiting request cannot be admitted")
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int,
+                 sampling: Optional[SamplingParams] = None,
+                 eos_ids: Sequence[int] = ()) -> List[List[int]]:
+        """Generate for several prompts at once (continuous batching); returns the new
+        tokens of each."""
+        base = len(self.scheduler.finished)
+        rids = [("gen", base, i) for i in range(len(prompts))]
+        for rid, p in zip(rids, prompts):
+            self.submit(rid, p, max_new_tokens, sampling, eos_ids)
+        self.run()
+        return [self.scheduler.finished.pop(rid).output for rid in rids]
+
+    def stats(self) -> Dict[str, object]:
+        """Counters in the manner of the reference's runtime and pool statistics
+        (``paged_runtime.clj:434-440``, ``page_pool.clj:423-435``)."""
+        cache = self.lm.cache
+        return {
+            "scheduler": dict(self.scheduler.stats),
+            "runner": dict(self.runner.counters),
+            "cache": dict(cache.stats),
+            "free_pages": [a.free_count for a in cache.allocators],
+            "pages": [a.num_pages for a in cache.allocators],
+            "running": len(self.scheduler.running),
+            "waiting": len(self.scheduler.waiting),
+        }

@@ -3,7 +3,8 @@
 File layout (``src/pretrained/safetensors.clj:24-37, 88-107``): an unsigned 64-bit
 little-endian header length, a JSON header ``{name: {dtype, shape, data_offsets}}``
 (the ``__metadata__`` entry is skipped), and the raw little-endian tensor bytes.
-The file is memory-mapped; each tensor is a view into the map until it is copied.
+The file is memory-mapped (privately, so views are writable without touching the
+file); each tensor is a view into the map until it is copied.
 Unlike the reference, which widens every dtype to 32-bit floats
 (``safetensors.clj:47-78``), tensors keep the dtype they are stored in.
 """
@@ -48,7 +49,7 @@ class SafetensorsFile:
         self.metadata = header.pop("__metadata__", {})
         self.entries: Dict[str, dict] = header
         self._data_start = 8 + header_len
-        self._map = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ)
+        self._map = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_COPY)
         for name, entry in self.entries.items():
             if entry.get("dtype") not in _DTYPES:
                 raise SafetensorsError(

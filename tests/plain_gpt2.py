@@ -194,7 +194,7 @@ def greedy_generate(model: PlainGPT2, ids: Sequence[int], n: int) -> List[int]:
     ids = list(ids)
     out: List[int] = []
     for _ in range(n):
-        if len(ids) >= model.n_positions:
+        if len(ids) > model.n_positions:      # a step runs while its position < n_positions (decoder_gpu.clj:1302)
             break
         row = all_logits(model, ids)[-1]
         tok = int(torch.argmax(row))          # torch.argmax returns the first maximum
@@ -282,7 +282,7 @@ def sample_generate(model: PlainGPT2, ids: Sequence[int], n: int, temperature: f
     ids = list(ids)
     out: List[int] = []
     for _ in range(n):
-        if len(ids) >= model.n_positions:
+        if len(ids) > model.n_positions:      # a step runs while its position < n_positions (decoder_gpu.clj:1302)
             break
         tok = sample(all_logits(model, ids)[-1], temperature, top_k, top_p, rng)
         ids.append(tok)

@@ -1,0 +1,91 @@
+"""Generation through the Python entry point against the plain implementation:
+greedy and seeded temperature sampling, one request and several at once."""
+import pytest
+import torch
+
+import plain_gpt2
+from helpers import TINY, make_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {(name, dtype): make_folder(str(tmp_path_factory.mktemp(f"g{name}{dtype}")), raw, seed,
+                                       dtype)
+            for name, (raw, seed) in TINY.items() for dtype in ("float32", "bfloat16")}
+
+
+def _agree(plain, prompt, got, want, dtype, what):
+    """Token lists must be equal; in bfloat16 the first difference may only be a near-tie
+    of the plain logits (after it the sequences legitimately diverge)."""
+    if got == want:
+        return
+    assert dtype == "bfloat16", f"{what}: {got} != {want}"
+    for i, (a, b) in enumerate(zip(got, want)):
+        if a != b:
+            row = plain_gpt2.all_logits(plain, list(prompt) + want[:i])[-1]
+            gap = abs(float(row[a] - row[b]))
+            assert gap < 3e-2, f"{what}: token {i} is {a}, plain says {b}, logit gap {gap:.3g}"
+            return
+    assert len(got) == len(want), f"{what}: lengths differ"
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_entry_point(folders, name, dtype):
+    from pretrained_rstr_b200 import generate_batch, generate_ids, load_lm
+    raw, seed = TINY[name]
+    folder = folders[(name, dtype)]
+    plain = plain_gpt2.PlainGPT2(folder)
+    m = load_lm(folder, gpu=True, dtype=dtype, max_lanes=4, max_batched_tokens=128,
+                prefill_chunk=32)
+    lengths = [5, 17, 40] if name == "A" else [1, 9, 33, 64, 130]
+    prompts = [random_tokens(n, raw["vocab_size"], 31 * seed + i) for i, n in enumerate(lengths)]
+    n_new = 16 if name == "A" else 24
+    for p in prompts[:2]:
+        _agree(plain, p, generate_ids(m, p, n_new), plain_gpt2.greedy_generate(plain, p, n_new),
+               dtype, f"alone len {len(p)}")
+    outs = generate_batch(m, prompts, n_new)          # more prompts than lanes: queueing too
+    for p, got in zip(prompts, outs):
+        _agree(plain, p, got, plain_gpt2.greedy_generate(plain, p, n_new), dtype,
+               f"batched len {len(p)}")
+    assert m.engine.lm.cache.free_pages(0) + len(m.engine.lm.cache._index) >= \
+        m.engine.lm.cache.allocators[0].num_pages - len(m.engine.lm.cache._index)
+    m.engine.lm.cache.check()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_temperature_sampling_matches_plain(folders, name):
+    """float32 logits, same top-k / softmax / nucleus / generator: same tokens."""
+    from pretrained_rstr_b200 import generate_batch, generate_ids, load_lm
+    raw, seed = TINY[name]
+    folder = folders[(name, "float32")]
+    plain = plain_gpt2.PlainGPT2(folder)
+    m = load_lm(folder, gpu=True, dtype="float32", max_lanes=4, max_batched_tokens=128,
+                prefill_chunk=32)
+    prompts = [random_tokens(n, raw["vocab_size"], 7 * seed + i) for i, n in enumerate([9, 33, 3])]
+    for opts in ({"temperature": 0.8, "seed": 7}, {"temperature": 1.3, "top_k": 5, "seed": 1},
+                 {"temperature": 0.7, "top_k": 50, "top_p": 0.6, "seed": 123456789}):
+        want = [plain_gpt2.sample_generate(plain, p, 12, opts["temperature"], opts.get("top_k"),
+                                           opts.get("top_p"), opts["seed"]) for p in prompts]
+        assert generate_ids(m, prompts[0], 12, opts) == want[0]
+        assert generate_batch(m, prompts, 12, opts) == want
+
+
+def test_stop_token_and_capacity(folders):
+    from pretrained_rstr_b200 import generate_ids, load_lm
+    raw, seed = TINY["A"]
+    folder = folders[("A", "float32")]
+    plain = plain_gpt2.PlainGPT2(folder)
+    m = load_lm(folder, gpu=True, dtype="float32", max_lanes=2, max_batched_tokens=128)
+    p = random_tokens(6, raw["vocab_size"], 3)
+    free = plain_gpt2.greedy_generate(plain, p, 10)
+    m.eos_ids = (free[3],)
+    stop_at = free.index(free[3])
+    assert generate_ids(m, p, 10) == free[:stop_at + 1]       # the stop token is kept
+    m.eos_ids = ()
+    long_prompt = random_tokens(raw["n_positions"] - 3, raw["vocab_size"], 4)
+    out = generate_ids(m, long_prompt, 10)
+    assert len(out) == 4                                       # positions are used up
+    assert out == plain_gpt2.greedy_generate(plain, long_prompt, 10)[:4]
