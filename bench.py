@@ -1,0 +1,268 @@
+#!/usr/bin/env python3
+"""Benchmark: decode tokens/s (batch 8 by default) and prefill tokens/s at 2,048 tokens
+for GPT-2 small with random weights, each with its fraction of the roofline.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+Prints ONE JSON line.  A "step" is one decode step of the whole batch.  ``value`` is
+decoded tokens per second from device time (CUDA events around each step's kernels);
+``e2e`` is the same through the engine's public step (token ids from pinned host memory
+in, sampled ids read back to the host, every step).  ``prefill`` is one step of 2,048
+prompt tokens (2 prompts x 1,024).  ``roofline`` divides the bytes a decode step has to
+read (every weight once, and the cache of the live requests) by its time and by the
+measured copy bandwidth.  Weights (247 MB) plus cache are larger than the 126 MB L2, so
+no flush is needed between timed steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SMALL = dict(n_layer=12, n_embd=768, n_head=12, n_inner=3072, vocab_size=50257, n_positions=1024)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as fh:
+                raw = json.load(fh)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(raw.get(k), (int, float)):
+                    out[k] = float(raw[k])
+            out["source"] = "measured"
+            return out
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self.index = index
+
+    def _run(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                     "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(float(parts[0]))
+                    self.max_mhz = float(parts[1])
+                    for name, val in zip(names, parts[2:6]):
+                        if val.lower().startswith("active"):
+                            self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def model_bytes(cfg, dtype_bytes=2):
+    d, f, L, V = cfg["n_embd"], cfg["n_inner"], cfg["n_layer"], cfg["vocab_size"]
+    per_layer = (d * 3 * d + d * d + d * f + f * d) * dtype_bytes + (3 * d + d + f + d + 4 * d) * 4
+    return L * per_layer + V * d * dtype_bytes + 2 * d * 4
+
+
+def kv_bytes_per_token(cfg, dtype_bytes=2):
+    return 2 * cfg["n_layer"] * cfg["n_embd"] * dtype_bytes
+
+
+def prefill_flops(cfg, n_prompts, prompt_len):
+    d, f, L, V = cfg["n_embd"], cfg["n_inner"], cfg["n_layer"], cfg["vocab_size"]
+    t = n_prompts * prompt_len
+    gemm = 2 * t * (d * 3 * d + d * d + 2 * d * f) * L
+    attn = L * n_prompts * 4 * d * (prompt_len * (prompt_len + 1) // 2)
+    head = 2 * n_prompts * d * V
+    return gemm + attn + head
+
+
+def run_reference(args) -> int:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "replikativ/pretrained-rstr is Clojure on the JVM computing through the "
+                       "external Raster library; pip reports \"Directory '/root/reference' is not "
+                       "installable. Neither 'setup.py' nor 'pyproject.toml' found\", and no JVM, "
+                       "Clojure or Raster exists offline"}))
+    return 0
+
+
+def timed_decode(engine, lm, batch, ctx_len, steps, warmup, vocab, seed):
+    """Prefill ``batch`` requests so that the timed decode steps end at ``ctx_len``
+    tokens; returns per-step device milliseconds, wall seconds and launch count."""
+    import random
+    import torch
+    from pretrained_rstr_b200.csrc import ops
+    rng = random.Random(seed)
+    prompt_len = ctx_len - (steps + warmup) - 1
+    for i in range(batch):
+        engine.submit(("bench", batch, i), [rng.randrange(vocab) for _ in range(prompt_len)],
+                      steps + warmup + 1)
+    while any(r.phase != "decode" for r in engine.scheduler.running.values()) or \
+            engine.scheduler.waiting:
+        engine.step()
+    assert len(engine.scheduler.running) == batch
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    launches0 = ops.launch_count()
+    engine.timing_events = (starts, ends)
+    t0 = time.perf_counter()
+    for k in range(steps):
+        engine.step_index = k
+        engine.step()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    engine.timing_events = None
+    launches = ops.launch_count() - launches0
+    ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    mean_ctx = ctx_len - 1 - steps / 2.0
+    while engine.scheduler.running:
+        engine.step()
+    h2d = engine.runner.last_h2d_bytes
+    return ms, wall, launches, mean_ctx, h2d
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=1024)
+    ap.add_argument("--layers", type=int, default=None,
+                    help="fewer layers than GPT-2 small's 12 (named in the record)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from pretrained_rstr_b200 import load_lm
+    from pretrained_rstr_b200.config import GPT2Config
+    from pretrained_rstr_b200.engine.batch import Entry
+    from pretrained_rstr_b200.weights import make_random_model
+
+    raw = dict(SMALL)
+    if args.layers:
+        raw["n_layer"] = args.layers
+    cfg = GPT2Config.from_dict(raw)
+    pk = peaks()
+    vocab = raw["vocab_size"]
+    steps, warmup, ctx_len = args.steps, args.warmup, min(args.context, raw["n_positions"])
+    tmp = tempfile.mkdtemp(prefix="prb200_bench_")
+    try:
+        make_random_model(tmp, cfg, seed=2, dtype=torch.bfloat16)
+        m = load_lm(tmp, gpu=True, dtype="bfloat16", max_lanes=64, max_batched_tokens=2048,
+                    prefill_chunk=1024, share_prefixes=False)
+    finally:
+        import shutil
+        shutil.rmtree(tmp, ignore_errors=True)
+    engine = m.engine
+
+    # ---- prefill: one step of 2 x 1024 prompt tokens
+    import random
+    rng = random.Random(11)
+    pre_ms = []
+    for it in range(3 + 5):
+        entries = []
+        for i in range(2):
+            rid = ("prefill", it, i)
+            m.loaded.cache.open(rid)
+            entries.append(Entry(rid, [rng.randrange(vocab) for _ in range(1024)], [1023]))
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        m.loaded.runner.step(entries)
+        e.record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            pre_ms.append(s.elapsed_time(e))
+        for en in entries:
+            m.loaded.cache.close(en.rid)
+    pre = statistics.median(pre_ms)
+    flops = prefill_flops(raw, 2, 1024)
+    prefill = {"value": 2048 / (pre / 1e3), "tokens": 2048, "ms": pre,
+               "frac": flops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
+    # ---- decode
+    points = {}
+    for b in (1, 64):
+        ms, wall, _l, _c, _h = timed_decode(engine, m.loaded, b, ctx_len, steps, warmup, vocab, b)
+        points[f"decode_b{b}"] = b / (statistics.mean(ms) / 1e3)
+    with ClockSampler() as clocks:
+        ms, wall, launches, mean_ctx, h2d = timed_decode(engine, m.loaded, args.batch, ctx_len,
+                                                        steps, warmup, vocab, 5)
+    step_ms = statistics.mean(ms)
+    value = args.batch / (step_ms / 1e3)
+    bytes_step = model_bytes(raw) + args.batch * mean_ctx * kv_bytes_per_token(raw)
+    achieved = bytes_step / (step_ms / 1e3) / 1e9
+    record = {
+        "metric": "decode tok/s (GPT-2 small, random weights)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "gpt2-small-random", "global_batch": args.batch, "seq_len": ctx_len,
+                   "parallelism": "single-gpu", "n_layer": raw["n_layer"], "n_layer_full": 12,
+                   "n_embd": raw["n_embd"], "n_head": raw["n_head"], "n_inner": raw["n_inner"],
+                   "vocab_size": vocab, "n_positions": raw["n_positions"], "page_size": 64,
+                   "mean_context": mean_ctx, "l2": "inputs_exceed_l2",
+                   "peaks": pk["source"]},
+        "e2e": {"value": args.batch * steps / wall, "unit": "tokens/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch + 16},
+        "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"]},
+        "points": points,
+        "clocks": clocks.summary(),
+    }
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -106,8 +106,18 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far through these wrappers."""
+    return _LAUNCHES
+
+
 def _check(code: int, what: str) -> None:
+    global _LAUNCHES
     if code == 0:
+        _LAUNCHES += 1
         return
     if code < 0:
         raise KernelArgumentError(f"{what}: {_ERRORS.get(code, 'error')} (code {code})")

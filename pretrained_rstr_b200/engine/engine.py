@@ -52,6 +52,10 @@ class Engine:
                       torch.zeros(n, dtype=torch.int64, device=dev)),
         }
         self.max_top_k = ops.max_top_k()
+        # optional (start events, end events) lists: step ``step_index`` records its pair
+        # around the device work of the step (measurement only)
+        self.timing_events = None
+        self.step_index = 0
 
     # ------------------------------------------------------------------ requests
     def submit(self, rid: Hashable, prompt: Sequence[int], max_new_tokens: int,
@@ -93,6 +97,8 @@ class Engine:
             entries.append(Entry(item.rid, tokens, [len(tokens) - 1] if wants else []))
             if wants:
                 samplers.append(self.scheduler.running[item.rid])
+        if self.timing_events is not None:
+            self.timing_events[0][self.step_index].record()
         logits = self.runner.step(entries)
         new_tokens: Dict[Hashable, int] = {}
         if samplers:
@@ -130,6 +136,8 @@ class Engine:
                        top_k=self._p["top_k"][1], top_p=self._p["top_p"][1],
                        seeds=self._p["seeds"][1], fresh=self._p["fresh"][1],
                        slots=self._p["slots"][1], rng_states=self.rng_states)
+        if self.timing_events is not None:
+            self.timing_events[1][self.step_index].record()
         self._tokens_host[:n].copy_(out[:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         self.runner.check_status()

@@ -58,6 +58,7 @@ class ModelRunner:
         self.scratch = ScratchPool(self.device)
         self.fail_next_step: Optional[Exception] = None      # host-side fault injection (tests)
         self.counters = {"steps": 0, "tokens": 0, "cow_copies": 0}
+        self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------ layout
     def layout_for(self, n_tokens: int, n_requests: int) -> BatchLayout:
@@ -156,6 +157,7 @@ class ModelRunner:
                          state_slots, fresh, group_slots, group_tables, group_first, logit_rows)
         self._dev[:layout.size].copy_(staging[:layout.size], non_blocking=True)
         self._host_events[turn].record()
+        self.last_h2d_bytes = layout.size * 4
         # copy-on-write page copies come before anything reads or writes the new pages
         for g in range(self.n_groups):
             pairs = [(src, dst) for r in reservations for (gg, src, dst) in r.copies if gg == g]
