@@ -1,0 +1,455 @@
+// bfloat16 matrix product on the 5th-generation tensor cores with a fused epilogue:
+//
+//     C[M,N] = act(A[M,K] . W[N,K]^T + bias[N]) (+ resid[M,N])
+//
+// A and W are bfloat16 with K contiguous ("K-major"), accumulation is float32 in tensor
+// memory (TMEM), C is bfloat16 or float32, bias and resid are float32.
+//
+// One CTA computes one 128 x BN tile of C.  Warp roles:
+//   warp 0  producer: one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
+//           of a 128 x 64 tile of A and a BN x 64 tile of W per pipeline stage;
+//   warp 1  allocates TMEM; one thread issues tcgen05.mma (M=128, N=BN, K=16, four per
+//           stage) and commits each stage back to the producer through an mbarrier;
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (one row per thread), add bias,
+//           apply the activation, add the residual, store.
+// Rows of A beyond M, rows of W beyond N and the K tail are zero-filled by TMA; stores
+// are masked.  K and the row pitches must be multiples of 8 elements (TMA needs 16-byte
+// strides); other sizes are refused with PRB_E_ALIGN, never computed wrongly.
+// No TMA load uses cluster multicast.  Every mbarrier wait is bounded: on a timeout the
+// kernel records PRB_S_WAIT_TIMEOUT in the status word, skips the remaining work,
+// waits (bounded) for its loads in flight, frees its TMEM and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;             // 64 bf16 = 128 bytes = one swizzle atom row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up or another role already failed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* failed) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *failed) return false;
+    }
+    *failed = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+        : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane (base + i).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 bytes
+// apart, 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+    d |= (uint64_t)1 << 46;                 // version
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M x N tile.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN> struct TileCfg {
+    static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 4 : 4);
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256;
+};
+
+template <typename O>
+__device__ __forceinline__ void store_chunk(O* __restrict__ crow, const float* v, int n_valid,
+                                            bool vec_ok);
+template <>
+__device__ __forceinline__ void store_chunk<float>(float* __restrict__ crow, const float* v,
+                                                   int n_valid, bool vec_ok) {
+    if (vec_ok && n_valid == 32) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(crow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+        for (int j = 0; j < n_valid; ++j) crow[j] = v[j];
+    }
+}
+template <>
+__device__ __forceinline__ void store_chunk<__nv_bfloat16>(__nv_bfloat16* __restrict__ crow,
+                                                           const float* v, int n_valid,
+                                                           bool vec_ok) {
+    if (vec_ok && n_valid == 32) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+            uint4 u;
+            u.x = *reinterpret_cast<uint32_t*>(&p0);
+            u.y = *reinterpret_cast<uint32_t*>(&p1);
+            u.z = *reinterpret_cast<uint32_t*>(&p2);
+            u.w = *reinterpret_cast<uint32_t*>(&p3);
+            *reinterpret_cast<uint4*>(crow + j) = u;
+        }
+    } else {
+        for (int j = 0; j < n_valid; ++j) crow[j] = __float2bfloat16_rn(v[j]);
+    }
+}
+
+template <int BN, typename O>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                 O* __restrict__ c, const float* __restrict__ bias,
+                 const float* __restrict__ resid, int m, int n, int k, long ldc, int act,
+                 int* status) {
+    using Cfg = TileCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* tiles = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full_bar = bars;                       // [STAGES]
+    uint64_t* empty_bar = bars + Cfg::STAGES;        // [STAGES]
+    uint64_t* tmem_full_bar = bars + 2 * Cfg::STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::STAGES + 1);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int k_blocks = (k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(tmem_full_bar), 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"((uint32_t)Cfg::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            int armed = 0;
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % Cfg::STAGES;
+                const uint32_t parity = ((kb / Cfg::STAGES) & 1) ^ 1;
+                ok = mbar_wait(smem_u32(&empty_bar[s]), parity, failed);
+                if (!ok) {
+                    prb_set_status(status, PRB_S_WAIT_TIMEOUT, 1, blockIdx.x, kb);
+                    break;
+                }
+                const uint32_t fb = smem_u32(&full_bar[s]);
+                mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+                uint8_t* stage = tiles + (size_t)s * Cfg::STAGE_BYTES;
+                tma_load_2d(smem_u32(stage), &map_a, fb, kb * BK, m0);
+                tma_load_2d(smem_u32(stage + Cfg::A_BYTES), &map_w, fb, kb * BK, n0);
+                armed = kb + 1;
+            }
+            if (!ok) {
+                // wait (bounded) for loads still in flight before the CTA may exit
+                const int first = armed > Cfg::STAGES ? armed - Cfg::STAGES : 0;
+                for (int kb = first; kb < armed; ++kb) {
+                    const uint32_t fb = smem_u32(&full_bar[kb % Cfg::STAGES]);
+                    for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+                        if (mbar_try_wait(fb, (kb / Cfg::STAGES) & 1)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % Cfg::STAGES;
+                ok = mbar_wait(smem_u32(&full_bar[s]), (kb / Cfg::STAGES) & 1, failed);
+                if (!ok) {
+                    prb_set_status(status, PRB_S_WAIT_TIMEOUT, 2, blockIdx.x, kb);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t a_addr = smem_u32(tiles + (size_t)s * Cfg::STAGE_BYTES);
+                const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+                const uint64_t a_desc = make_smem_desc(a_addr);
+                const uint64_t b_desc = make_smem_desc(b_addr);
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                    // advance 16 elements = 32 bytes inside the swizzle atom: +2 in 16-byte units
+                    umma_bf16(tmem_base, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2),
+                              idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&empty_bar[s]));      // frees the stage when the MMAs retire
+            }
+            if (ok) umma_commit(smem_u32(tmem_full_bar));  // accumulator complete
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;                       // TMEM lanes this warp may read
+        const int row = m0 + quarter * 32 + lane;
+        bool ok = mbar_wait(smem_u32(tmem_full_bar), 0, failed);
+        if (!ok && lane == 0) prb_set_status(status, PRB_S_WAIT_TIMEOUT, 3, blockIdx.x, warp);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (ok) {
+            tcgen05_fence_after();
+            const bool vec_ok = ((ldc * (long)sizeof(O)) % 16 == 0) &&
+                                (((uintptr_t)c) % 16 == 0) &&
+                                (resid == nullptr ||
+                                 (((ldc * 4) % 16 == 0) && (((uintptr_t)resid) % 16 == 0)));
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= n) break;                    // uniform across the warp
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+                if (row < m) {
+                    const int ncol = n0 + c0;
+                    const int n_valid = (n - ncol) < 32 ? (n - ncol) : 32;
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float x = __uint_as_float(r[j]);
+                        if (j < n_valid) {
+                            if (bias) x += __ldg(bias + ncol + j);
+                            x = prb_activate(x, act);
+                        }
+                        v[j] = x;
+                    }
+                    if (resid) {
+                        const float* rr = resid + (size_t)row * ldc + ncol;
+                        if (vec_ok && n_valid == 32) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 q = *reinterpret_cast<const float4*>(rr + j);
+                                v[j] += q.x; v[j + 1] += q.y; v[j + 2] += q.z; v[j + 3] += q.w;
+                            }
+                        } else {
+                            for (int j = 0; j < n_valid; ++j) v[j] += rr[j];
+                        }
+                    }
+                    store_chunk<O>(c + (size_t)row * ldc + ncol, v, n_valid, vec_ok);
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"((uint32_t)Cfg::TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    long rows, cols, pitch;
+    int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && pitch == o.pitch &&
+               box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows;
+        h = h * 1000003u ^ (size_t)k.cols;
+        h = h * 1000003u ^ (size_t)k.pitch;
+        h = h * 1000003u ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+
+// Tensor map of a row-major bf16 matrix [rows, cols] with `pitch` elements between rows;
+// box = 64 columns x box_rows rows, 128-byte swizzle, out-of-range elements read as zero.
+int get_map(const void* ptr, long rows, long cols, long pitch, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, pitch, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return 0;
+    }
+    auto fn = encode_fn();
+    if (!fn) return -6;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap map;
+    CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return PRB_E_ARG;
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, map);
+    *out = map;
+    return 0;
+}
+
+template <int BN, typename O>
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, O* c, const float* bias,
+           const float* resid, int m, int n, int k, long ldc, int act, int* status,
+           cudaStream_t stream) {
+    using Cfg = TileCfg<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, O>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)Cfg::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
+    gemm_bf16_kernel<BN, O><<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(ma, mw, c, bias, resid, m,
+                                                                       n, k, ldc, act, status);
+    PRB_LAUNCH_CHECK();
+    return 0;
+}
+
+}  // namespace
+
+// tile_n: 0 = choose (by M and N), or one of 32, 64, 128, 256.
+PRB_API int prb_gemm_bf16(void* c, const void* a, const void* w, const float* bias,
+                          const float* resid, int m, int n, int k, long lda, long ldw, long ldc,
+                          int act, int out_dtype, int tile_n, int* status, cudaStream_t stream) {
+    if (m <= 0 || n <= 0) return 0;
+    if (k <= 0) return PRB_E_SIZE;
+    if (k % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)a) % 16 != 0 ||
+        ((uintptr_t)w) % 16 != 0)
+        return PRB_E_ALIGN;
+    if ((m + BM - 1) / BM > 65535) return PRB_E_SIZE;
+    if (tile_n == 0) {
+        // enough CTAs to fill 148 SMs where the problem allows it
+        const long mt = (m + BM - 1) / BM;
+        if (mt * ((n + 255) / 256) >= 148) tile_n = 256;
+        else if (mt * ((n + 127) / 128) >= 120) tile_n = 128;
+        else if (mt * ((n + 63) / 64) >= 100) tile_n = 64;
+        else tile_n = 32;
+    }
+    if (tile_n != 32 && tile_n != 64 && tile_n != 128 && tile_n != 256) return PRB_E_ARG;
+    CUtensorMap ma, mw;
+    int r = get_map(a, m, k, lda, BM, &ma);
+    if (r) return r;
+    r = get_map(w, n, k, ldw, tile_n, &mw);
+    if (r) return r;
+#define PRB_GO(BN_)                                                                              \
+    (out_dtype == PRB_F32                                                                        \
+         ? launch<BN_, float>(ma, mw, (float*)c, bias, resid, m, n, k, ldc, act, status, stream) \
+         : launch<BN_, __nv_bfloat16>(ma, mw, (__nv_bfloat16*)c, bias, resid, m, n, k, ldc, act, \
+                                      status, stream))
+    if (out_dtype != PRB_F32 && out_dtype != PRB_BF16) return PRB_E_DTYPE;
+    switch (tile_n) {
+        case 32: return PRB_GO(32);
+        case 64: return PRB_GO(64);
+        case 128: return PRB_GO(128);
+        default: return PRB_GO(256);
+    }
+#undef PRB_GO
+}

@@ -80,12 +80,13 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_kv_append.argtypes = [P, P, P, P, L, P, I, I, I, I, I, I, P, P]
     h.prb_copy_pages.argtypes = [P, P, I, L, I, I, P, P]
     h.prb_gemm_f32.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, P]
+    h.prb_gemm_bf16.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, I, P, P]
     h.prb_attention_generic.argtypes = [P, L, P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I,
                                         I, P, P]
     h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
     h.prb_sample_max_top_k.argtypes = []
     for name in ("prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
-                 "prb_gemm_f32", "prb_attention_generic", "prb_sample", "prb_sample_max_top_k"):
+                 "prb_gemm_f32", "prb_gemm_bf16", "prb_attention_generic", "prb_sample", "prb_sample_max_top_k"):
         getattr(h, name).restype = c_int
 
 
@@ -235,6 +236,31 @@ def gemm_f32(out, a, w, bias=None, resid=None, act=None) -> None:
             raise KernelArgumentError(f"{what}: resid must have the output's shape and stride")
     _check(lib().prb_gemm_f32(_p(out), _p(a), _p(w), _p(bias), _p(resid), m, n, k, a.stride(0),
                               w.stride(0), out.stride(0), ACT_CODES[act], _stream()), what)
+
+
+def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, status=None) -> None:
+    """out[M,N] = act(a[M,K] . w[N,K]^T + bias) (+ resid) on the tcgen05 tensor cores:
+    bfloat16 operands, float32 accumulation in tensor memory, epilogue in float32; out is
+    bfloat16 or float32.  K and the row pitches of a and w must be multiples of 8."""
+    what = "gemm_bf16"
+    for name, t in (("a", a), ("w", w)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(1) != 1:
+            raise KernelArgumentError(f"{what}: {name} must be bfloat16 on CUDA with unit inner stride")
+    if not out.is_cuda or out.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: out must be on CUDA with unit inner stride")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n:
+        raise KernelArgumentError(f"{what}: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias", what)
+    if resid is not None:
+        _need(resid, torch.float32, "resid", what)
+        if resid.shape != out.shape or resid.stride(0) != out.stride(0):
+            raise KernelArgumentError(f"{what}: resid must have the output's shape and stride")
+    _check(lib().prb_gemm_bf16(_p(out), _p(a), _p(w), _p(bias), _p(resid), m, n, k, a.stride(0),
+                               w.stride(0), out.stride(0), ACT_CODES[act], dtype_code(out.dtype),
+                               tile_n, _p(status), _stream()), what)
 
 
 def attention_generic(out, q, k_pages, v_pages, block_table, seq_of_token, positions, n_tokens,
