@@ -83,10 +83,18 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_gemm_bf16.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, I, P, P]
     h.prb_attention_generic.argtypes = [P, L, P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I,
                                         I, P, P]
+    h.prb_attention_decode.argtypes = [P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I,
+                                       P, P, I, P, P]
+    h.prb_attention_prefill.argtypes = [P, L, P, L, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F,
+                                        I, P, P]
+    h.prb_attention_prefill_supports.argtypes = [I]
+    h.prb_attention_decode_split.argtypes = []
     h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
     h.prb_sample_max_top_k.argtypes = []
     for name in ("prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
-                 "prb_gemm_f32", "prb_gemm_bf16", "prb_attention_generic", "prb_sample", "prb_sample_max_top_k"):
+                 "prb_gemm_f32", "prb_gemm_bf16", "prb_attention_generic", "prb_attention_decode",
+                 "prb_attention_prefill", "prb_attention_prefill_supports",
+                 "prb_attention_decode_split", "prb_sample", "prb_sample_max_top_k"):
         getattr(h, name).restype = c_int
 
 
@@ -280,6 +288,57 @@ def attention_generic(out, q, k_pages, v_pages, block_table, seq_of_token, posit
         _p(seq_of_token), _p(positions), n_tokens, n_heads, kv_heads, head_dim, page_size,
         block_table.shape[1], num_pages, max_context, float(scale), int(window or 0),
         dtype_code(k_pages.dtype), _p(status), _stream()), what)
+
+
+def decode_split() -> int:
+    """Keys per split of the decode attention kernel."""
+    return lib().prb_attention_decode_split()
+
+
+def prefill_supports(head_dim: int) -> bool:
+    return bool(lib().prb_attention_prefill_supports(int(head_dim)))
+
+
+def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positions, token_list,
+                     token_count, n_list, n_heads, scale, window, workspace, counters, max_splits,
+                     status) -> None:
+    """bfloat16 attention of single tokens (those in ``token_list``, or all of the first
+    ``n_list`` when it is None) over their requests' pages, keys split in ranges of
+    ``decode_split()`` positions.  ``workspace`` float32 [n_list, heads, max_splits,
+    head_dim + 2] and ``counters`` int32 [n_list * heads] (zero) are scratch."""
+    what = "attention_decode"
+    num_pages, kv_heads, page_size, head_dim = k_pages.shape
+    for name, t in (("out", out), ("q", q)):
+        if t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != n_heads * head_dim:
+            raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
+    if k_pages.dtype != torch.bfloat16:
+        raise KernelArgumentError(f"{what}: the cache must be bfloat16")
+    need = n_list * n_heads * max_splits * (head_dim + 2)
+    if workspace.dtype != torch.float32 or workspace.numel() < need or \
+            counters.dtype != torch.int32 or counters.numel() < n_list * n_heads:
+        raise KernelArgumentError(f"{what}: scratch too small or of the wrong type")
+    _check(lib().prb_attention_decode(
+        _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(block_table),
+        _p(seq_of_token), _p(positions), _p(token_list), _p(token_count), n_list, n_heads,
+        kv_heads, head_dim, page_size, block_table.shape[1], num_pages, float(scale),
+        int(window or 0), _p(workspace), _p(counters), max_splits, _p(status), _stream()), what)
+
+
+def attention_prefill(out, q, k_pages, v_pages, block_table, positions, tile_req, tile_row0,
+                      tile_rows, tile_count, n_tiles, n_heads, scale, window, status) -> None:
+    """bfloat16 causal attention of prompt portions, 64 queries per tile, on tensor cores."""
+    what = "attention_prefill"
+    num_pages, kv_heads, page_size, head_dim = k_pages.shape
+    for name, t in (("out", out), ("q", q)):
+        if t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != n_heads * head_dim:
+            raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
+    if k_pages.dtype != torch.bfloat16:
+        raise KernelArgumentError(f"{what}: the cache must be bfloat16")
+    _check(lib().prb_attention_prefill(
+        _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(block_table),
+        _p(positions), _p(tile_req), _p(tile_row0), _p(tile_rows), _p(tile_count), n_tiles,
+        n_heads, kv_heads, head_dim, page_size, block_table.shape[1], num_pages, float(scale),
+        int(window or 0), _p(status), _stream()), what)
 
 
 def max_top_k() -> int:

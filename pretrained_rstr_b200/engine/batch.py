@@ -22,6 +22,10 @@ import numpy as np
 import torch
 
 
+ATTENTION_TILE = 64      # queries per tile of the prompt attention kernel
+SINGLE_MAX_Q = 4         # portions up to this many tokens are attended token by token
+
+
 @dataclass
 class Entry:
     """One request's share of a step: its next tokens and the places (indices into
@@ -69,6 +73,15 @@ class BatchLayout:
         self.slots = [take(t_cap) for _ in range(n_groups)]
         self.first_pos = [take(b_cap) for _ in range(n_groups)]
         self.block_table = [take(b_cap * max_pages) for _ in range(n_groups)]
+        # work lists of the attention kernels: 64-query tiles of prompt portions, and single
+        # tokens (decoded tokens and very short portions); counts live on the device too
+        self.tile_cap = t_cap // ATTENTION_TILE + b_cap
+        self.tile_req = take(self.tile_cap)
+        self.tile_row0 = take(self.tile_cap)
+        self.tile_rows = take(self.tile_cap)
+        self.single_cap = min(t_cap, b_cap * SINGLE_MAX_Q)
+        self.single_tokens = take(self.single_cap)
+        self.counts = take(4)                 # [tiles, singles, tokens, requests]
         self.size = off
 
 
@@ -101,7 +114,8 @@ class StepContext:
     def __init__(self, runtime: Runtime, layout: BatchLayout, device_buf: torch.Tensor,
                  n_tokens: int, n_requests: int, n_rows: int, host: HostBatch,
                  groups: List[GroupView], status: torch.Tensor, scratch_pool: "ScratchPool",
-                 max_context: int, max_q_len: int, launch_tokens: int, launch_rows: int):
+                 max_context: int, max_q_len: int, launch_tokens: int, launch_rows: int,
+                 max_positions: int = 0):
         self.runtime = runtime
         self.layout = layout
         self.n_tokens = n_tokens            # real tokens of the step
@@ -114,6 +128,7 @@ class StepContext:
         self.status = status
         self.max_context = max_context      # upper bound of any request's length after the step
         self.max_q_len = max_q_len
+        self.max_positions = max_positions or max_context
         self._scratch = scratch_pool
         lay, buf = layout, device_buf
         self.tokens = buf[lay.tokens:lay.tokens + lay.t_cap]
@@ -124,6 +139,15 @@ class StepContext:
         self.kv_len = buf[lay.kv_len:lay.kv_len + lay.b_cap]
         self.state_slot = buf[lay.state_slot:lay.state_slot + lay.b_cap]
         self.fresh = buf[lay.fresh:lay.fresh + lay.b_cap]
+        self.tile_req = buf[lay.tile_req:lay.tile_req + lay.tile_cap]
+        self.tile_row0 = buf[lay.tile_row0:lay.tile_row0 + lay.tile_cap]
+        self.tile_rows = buf[lay.tile_rows:lay.tile_rows + lay.tile_cap]
+        self.single_tokens = buf[lay.single_tokens:lay.single_tokens + lay.single_cap]
+        self.counts = buf[lay.counts:lay.counts + 4]
+        # host-side counts of the work lists (None when the step is replayed from a graph
+        # and only the device-side counts are valid)
+        self.n_tiles: Optional[int] = None
+        self.n_singles: Optional[int] = None
 
     @property
     def dtype(self) -> torch.dtype:
@@ -147,17 +171,30 @@ class StepContext:
         survive the step; two parts that use the same key share the memory."""
         return self._scratch.get(key, shape, dtype)
 
+    def scratch_zero(self, key: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """Scratch that is zero when first handed out; whoever uses it leaves it zero
+        (counters that their kernel resets)."""
+        return self._scratch.get(key, shape, dtype, zero=True)
+
+    @property
+    def max_splits_cap(self) -> int:
+        """Upper bound of the decode attention kernel's key splits for any request."""
+        from ..csrc import ops
+        return -(-self.max_positions // ops.decode_split())
+
 
 class ScratchPool:
     def __init__(self, device: torch.device):
         self.device = device
         self._bufs: Dict[Tuple, torch.Tensor] = {}
 
-    def get(self, key: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+    def get(self, key: str, shape: Tuple[int, ...], dtype: torch.dtype,
+            zero: bool = False) -> torch.Tensor:
         k = (key, tuple(shape), dtype)
         buf = self._bufs.get(k)
         if buf is None:
-            buf = torch.empty(tuple(shape), dtype=dtype, device=self.device)
+            make = torch.zeros if zero else torch.empty
+            buf = make(tuple(shape), dtype=dtype, device=self.device)
             self._bufs[k] = buf
         return buf
 
@@ -169,7 +206,8 @@ def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: L
                      start_pos: List[int], state_slots: List[int], fresh: List[bool],
                      group_slots: List[List[List[int]]], group_tables: List[List[List[int]]],
                      group_first: List[List[int]], logit_rows: List[int]) -> Tuple[int, int]:
-    """Write one step into the pinned host buffer.  Returns (tokens, requests)."""
+    """Write one step into the pinned host buffer.  Returns the lengths of the attention
+    work lists (tiles, single tokens)."""
     lay = layout
     n_req = len(entries_tokens)
     t = 0
@@ -218,4 +256,28 @@ def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: L
         for b in range(n_req):
             table = group_tables[g][b]
             bt2[b, :len(table)] = table
-    return n_tok, n_req
+    # attention work lists
+    treq = host_np[lay.tile_req:lay.tile_req + lay.tile_cap]
+    trow = host_np[lay.tile_row0:lay.tile_row0 + lay.tile_cap]
+    tnum = host_np[lay.tile_rows:lay.tile_rows + lay.tile_cap]
+    sing = host_np[lay.single_tokens:lay.single_tokens + lay.single_cap]
+    n_tiles = n_sing = 0
+    t = 0
+    for b, toks in enumerate(entries_tokens):
+        n = len(toks)
+        if n <= SINGLE_MAX_Q:
+            sing[n_sing:n_sing + n] = np.arange(t, t + n, dtype=np.int32)
+            n_sing += n
+        else:
+            for r0 in range(0, n, ATTENTION_TILE):
+                treq[n_tiles] = b
+                trow[n_tiles] = t + r0
+                tnum[n_tiles] = min(ATTENTION_TILE, n - r0)
+                n_tiles += 1
+        t += n
+    treq[n_tiles:] = -1
+    trow[n_tiles:] = 0
+    tnum[n_tiles:] = 0
+    sing[n_sing:] = 0
+    host_np[lay.counts:lay.counts + 4] = (n_tiles, n_sing, n_tok, n_req)
+    return n_tiles, n_sing

@@ -153,7 +153,7 @@ class ModelRunner:
         self._host_turn ^= 1
         self._host_events[turn].synchronize()        # the copy that last used this buffer is done
         staging = self._hosts[turn]
-        fill_host_buffer(staging.numpy(), layout, [list(e.tokens) for e in entries], start_pos,
+        n_tiles, n_singles = fill_host_buffer(staging.numpy(), layout, [list(e.tokens) for e in entries], start_pos,
                          state_slots, fresh, group_slots, group_tables, group_first, logit_rows)
         self._dev[:layout.size].copy_(staging[:layout.size], non_blocking=True)
         self._host_events[turn].record()
@@ -186,9 +186,12 @@ class ModelRunner:
         max_q = max(len(e.tokens) for e in entries)
         self.counters["steps"] += 1
         self.counters["tokens"] += total
-        return StepContext(self.runtime, layout, self._dev, total, n_req, len(logit_rows), host,
-                           groups, self.status, self.scratch, max_context, max_q,
-                           launch_tokens=total, launch_rows=len(logit_rows))
+        ctx = StepContext(self.runtime, layout, self._dev, total, n_req, len(logit_rows), host,
+                          groups, self.status, self.scratch, max_context, max_q,
+                          launch_tokens=total, launch_rows=len(logit_rows),
+                          max_positions=self.model.max_positions)
+        ctx.n_tiles, ctx.n_singles = n_tiles, n_singles
+        return ctx
 
     def commit(self, entries: Sequence[Entry]) -> None:
         for e in entries:

@@ -18,6 +18,7 @@ from typing import Optional
 import torch
 
 from ..csrc import ops
+from ..engine.batch import SINGLE_MAX_Q
 from .interfaces import KVSpec, LayerCache, Mixer
 from .linear import Linear
 from .registry import register_part
@@ -65,10 +66,36 @@ class CausalAttention(Mixer):
 
 def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
            window: Optional[int]) -> None:
-    """Attention of the step's tokens over their requests' cached keys and values."""
-    ops.attention_generic(out, q, cache.k, cache.v, group.block_table, ctx.seq_of_token,
-                          ctx.positions, out.shape[0], n_head, scale, window,
-                          ctx.max_context, ctx.status)
+    """Attention of the step's tokens over their requests' cached keys and values.
+
+    float32 runtime: the 32-bit kernel for every token.  bfloat16 runtime: prompt
+    portions go in 64-query tiles to the tensor-core kernel, single tokens (decoded
+    tokens, portions of a few tokens) to the split-key decode kernel; head sizes or page
+    sizes those kernels do not take fall back to the 32-bit-arithmetic kernel."""
+    t = out.shape[0]
+    head_dim = cache.k.shape[3]
+    fast = ctx.dtype == torch.bfloat16 and head_dim % 8 == 0 and head_dim <= 256 and \
+        ops.decode_split() % group.page_size == 0 and ops.prefill_supports(head_dim)
+    if not fast:
+        ops.attention_generic(out, q, cache.k, cache.v, group.block_table, ctx.seq_of_token,
+                              ctx.positions, t, n_head, scale, window, ctx.max_context, ctx.status)
+        return
+    lay = ctx.layout
+    if ctx.n_tiles is None or ctx.n_tiles > 0:
+        n_tiles = lay.tile_cap if ctx.n_tiles is None else ctx.n_tiles
+        ops.attention_prefill(out, q, cache.k, cache.v, group.block_table, ctx.positions,
+                              ctx.tile_req, ctx.tile_row0, ctx.tile_rows, ctx.counts[0:1], n_tiles,
+                              n_head, scale, window, ctx.status)
+    if ctx.n_singles is None or ctx.n_singles > 0:
+        n_list = lay.single_cap if ctx.n_singles is None else ctx.n_singles
+        max_splits = -(-ctx.max_context // ops.decode_split())
+        cap = ctx.runtime.max_requests * SINGLE_MAX_Q
+        ws = ctx.scratch("attn_decode_ws", (cap * n_head * ctx.max_splits_cap * (head_dim + 2),),
+                         torch.float32)
+        counters = ctx.scratch_zero("attn_decode_counters", (cap * n_head,), torch.int32)
+        ops.attention_decode(out, q, cache.k, cache.v, group.block_table, ctx.seq_of_token,
+                             ctx.positions, ctx.single_tokens, ctx.counts[1:2], n_list, n_head,
+                             scale, window, ws, counters, max_splits, ctx.status)
 
 
 def _causal_attention(p, store, rt) -> CausalAttention:

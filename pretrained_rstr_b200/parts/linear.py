@@ -54,12 +54,5 @@ class Linear:
 
 
 def gemm_bf16(ctx, out, a, weight, bias, resid, act) -> None:
-    """bfloat16 operands, float32 accumulation, epilogue in float32."""
-    m, n = a.shape[0], weight.shape[0]
-    if out.dtype == torch.float32 and bias is None and resid is None and act is None \
-            and out.is_contiguous():
-        torch.mm(a, weight.t(), out_dtype=torch.float32, out=out)
-        return
-    acc = ctx.scratch("gemm_acc", (ctx.token_capacity, n), torch.float32)[:m]
-    torch.mm(a, weight.t(), out_dtype=torch.float32, out=acc)
-    ops.bias_act(out, acc, bias, resid, act)
+    """bfloat16 operands, float32 accumulation in tensor memory, epilogue in float32."""
+    ops.gemm_bf16(out, a, weight, bias, resid, act, status=ctx.status)

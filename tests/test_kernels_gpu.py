@@ -100,3 +100,146 @@ def test_gemm_f32_is_true_32_bit(m, n, k):
     alone = torch.zeros(1, n, device="cuda")
     ops.gemm_f32(alone, a[m - 1:m].contiguous(), w, bias=bias, act="gelu")
     assert torch.equal(alone[0], out[m - 1])
+
+
+# ------------------------------------------------------------------------ attention
+def _paged_case(seed, n_heads, kv_heads, dh, page_size, lengths, portions, dtype, num_pages=64):
+    """Random paged cache with shuffled pages.  ``lengths[b]``: tokens request b holds after
+    the step; ``portions[b]``: how many of them are the step's queries."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    max_pages = max(-(-n // page_size) for n in lengths) + 1
+    k = (torch.randn(num_pages, kv_heads, page_size, dh, generator=g)).to(dtype).cuda()
+    v = (torch.randn(num_pages, kv_heads, page_size, dh, generator=g)).to(dtype).cuda()
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    table = torch.full((len(lengths), max_pages), -1, dtype=torch.int32)
+    for b, n in enumerate(lengths):
+        for i in range(-(-n // page_size)):
+            table[b, i] = perm.pop()
+    seq, pos = [], []
+    for b, (n, p) in enumerate(zip(lengths, portions)):
+        seq += [b] * p
+        pos += list(range(n - p, n))
+    t = len(seq)
+    q = (torch.randn(t, n_heads * dh, generator=g)).to(dtype).cuda()
+    return q, k, v, table.cuda(), torch.tensor(seq, dtype=torch.int32).cuda(), \
+        torch.tensor(pos, dtype=torch.int32).cuda()
+
+
+def _ref_attention(q, k, v, table, seq, pos, n_heads, scale, window):
+    t = q.shape[0]
+    num_pages, kv_heads, page_size, dh = k.shape
+    out = torch.zeros(t, n_heads * dh, dtype=torch.float32, device="cuda")
+    kf, vf, qf = k.float(), v.float(), q.float()
+    for i in range(t):
+        b, p = int(seq[i]), int(pos[i])
+        lo = max(0, p - window + 1) if window else 0
+        js = torch.arange(lo, p + 1, device="cuda")
+        pages = table[b, (js // page_size).long()].long()
+        for h in range(n_heads):
+            hk = h // (n_heads // kv_heads)
+            kk = kf[pages, hk, (js % page_size).long()]          # [n, dh]
+            vv = vf[pages, hk, (js % page_size).long()]
+            s = (kk @ qf[i, h * dh:(h + 1) * dh]) * scale
+            out[i, h * dh:(h + 1) * dh] = torch.softmax(s, 0) @ vv
+    return out
+
+
+ATTN_CASES = [
+    # heads, kv heads, head size, page size, window
+    (4, 4, 16, 16, None), (3, 3, 32, 64, None), (6, 2, 64, 64, None), (5, 1, 48, 32, 40),
+    (2, 2, 128, 128, None), (8, 4, 80, 64, 100), (2, 1, 256, 64, None),
+]
+
+
+@pytest.mark.parametrize("nh,nkv,dh,ps,window", ATTN_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_generic(nh, nkv, dh, ps, window, dtype):
+    ops = _ops()
+    lengths, portions = [1, 70, 300, 129], [1, 5, 1, 129]
+    q, k, v, table, seq, pos = _paged_case(1, nh, nkv, dh, ps, lengths, portions, dtype)
+    out = torch.zeros_like(q)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ops.attention_generic(out, q, k, v, table, seq, pos, q.shape[0], nh, 0.3, window, 512, status)
+    ref = _ref_attention(q, k, v, table, seq, pos, nh, 0.3, window)
+    assert status.tolist() == [0, 0, 0, 0]
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert float((out.float() - ref).abs().max()) <= tol
+
+
+@pytest.mark.parametrize("nh,nkv,dh,ps,window", ATTN_CASES)
+def test_attention_decode(nh, nkv, dh, ps, window):
+    ops = _ops()
+    lengths, portions = [1, 70, 300, 257, 1000, 256], [1, 2, 1, 3, 1, 1]
+    q, k, v, table, seq, pos = _paged_case(2, nh, nkv, dh, ps, lengths, portions, torch.bfloat16)
+    t = q.shape[0]
+    splits = -(-1024 // ops.decode_split())
+    ws = torch.full((t * nh * splits * (dh + 2),), float("nan"), device="cuda")
+    counters = torch.zeros(t * nh, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ref = _ref_attention(q, k, v, table, seq, pos, nh, 0.2, window)
+    for _ in range(2):                      # twice: the counters must be left at zero
+        out = torch.full_like(q, float("nan"))
+        ops.attention_decode(out, q, k, v, table, seq, pos, None, None, t, nh, 0.2, window, ws,
+                             counters, splits, status)
+        assert status.tolist() == [0, 0, 0, 0]
+        assert float((out.float() - ref).abs().max()) <= 2e-2
+        assert int(counters.abs().sum()) == 0
+    # a token list picks tokens; the others are not touched
+    order = torch.tensor([t - 1, 0, 3], dtype=torch.int32, device="cuda")
+    count = torch.tensor([2], dtype=torch.int32, device="cuda")
+    out = torch.zeros_like(q)
+    ops.attention_decode(out, q, k, v, table, seq, pos, order, count, 3, nh, 0.2, window, ws,
+                         counters, splits, status)
+    assert float((out[t - 1].float() - ref[t - 1]).abs().max()) <= 2e-2
+    assert float((out[0].float() - ref[0]).abs().max()) <= 2e-2
+    assert float(out[3].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("nh,nkv,dh,ps,window", ATTN_CASES)
+def test_attention_prefill(nh, nkv, dh, ps, window):
+    ops = _ops()
+    assert ops.prefill_supports(dh)
+    lengths, portions = [5, 70, 300, 200, 64], [5, 70, 130, 9, 64]
+    q, k, v, table, seq, pos = _paged_case(3, nh, nkv, dh, ps, lengths, portions, torch.bfloat16)
+    tiles, row = [], 0
+    for b, p in enumerate(portions):
+        for r0 in range(0, p, 64):
+            tiles.append((b, row + r0, min(64, p - r0)))
+        row += p
+    tr = torch.tensor([x[0] for x in tiles], dtype=torch.int32, device="cuda")
+    t0 = torch.tensor([x[1] for x in tiles], dtype=torch.int32, device="cuda")
+    tn = torch.tensor([x[2] for x in tiles], dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = torch.full_like(q, float("nan"))
+    ops.attention_prefill(out, q, k, v, table, pos, tr, t0, tn, None, len(tiles), nh, 0.2, window,
+                          status)
+    ref = _ref_attention(q, k, v, table, seq, pos, nh, 0.2, window)
+    assert status.tolist() == [0, 0, 0, 0]
+    err = (out.float() - ref).abs()
+    assert float(err.max()) <= 2e-2, f"worst row {int(err.max(dim=1).values.argmax())}"
+
+
+def test_attention_far_key_stands_out():
+    """One early key among a thousand is made to dominate: every kernel must find it."""
+    ops = _ops()
+    nh, dh, ps, n = 2, 64, 64, 1000
+    q, k, v, table, seq, pos = _paged_case(4, nh, nh, dh, ps, [n], [66], torch.bfloat16)
+    far = 3
+    page, off = int(table[0, far // ps]), far % ps
+    k[page, :, off, :] = q[-1].view(nh, dh) * 4.0      # aligned with the last query: huge score
+    ref = _ref_attention(q, k, v, table, seq, pos, nh, 0.125, None)
+    assert float((ref[-1].view(nh, dh) - v[page, :, off].float()).abs().max()) < 0.05
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = torch.zeros_like(q)
+    tr = torch.zeros(2, dtype=torch.int32, device="cuda")
+    t0 = torch.tensor([0, 64], dtype=torch.int32, device="cuda")
+    tn = torch.tensor([64, 2], dtype=torch.int32, device="cuda")
+    ops.attention_prefill(out, q, k, v, table, pos, tr, t0, tn, None, 2, nh, 0.125, None, status)
+    assert float((out.float() - ref).abs().max()) <= 2e-2
+    t = q.shape[0]
+    ws = torch.zeros(t * nh * 4 * (dh + 2), device="cuda")
+    counters = torch.zeros(t * nh, dtype=torch.int32, device="cuda")
+    out2 = torch.zeros_like(q)
+    ops.attention_decode(out2, q, k, v, table, seq, pos, None, None, t, nh, 0.125, None, ws,
+                         counters, 4, status)
+    assert float((out2.float() - ref).abs().max()) <= 2e-2
