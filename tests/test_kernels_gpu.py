@@ -108,6 +108,7 @@ def _paged_case(seed, n_heads, kv_heads, dh, page_size, lengths, portions, dtype
     the step; ``portions[b]``: how many of them are the step's queries."""
     g = torch.Generator(device="cpu").manual_seed(seed)
     max_pages = max(-(-n // page_size) for n in lengths) + 1
+    num_pages = max(num_pages, sum(-(-n // page_size) for n in lengths) + 5)
     k = (torch.randn(num_pages, kv_heads, page_size, dh, generator=g)).to(dtype).cuda()
     v = (torch.randn(num_pages, kv_heads, page_size, dh, generator=g)).to(dtype).cuda()
     perm = torch.randperm(num_pages, generator=g).tolist()
