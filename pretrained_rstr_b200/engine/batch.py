@@ -43,6 +43,7 @@ class Runtime:
     page_size: int = 64
     max_batched_tokens: int = 2048
     max_requests: int = 64
+    use_graphs: bool = True            # replay small steps as CUDA graphs
 
     @property
     def serving(self) -> bool:

@@ -35,8 +35,7 @@ class Engine:
         # per-request sampler state lives in the request's state slot
         self.rng_states = torch.zeros(n, dtype=torch.int64, device=dev)
         self._rng_started: Dict[Hashable, bool] = {}
-        self._tokens_dev = torch.zeros(n, dtype=torch.int32, device=dev)
-        self._tokens_host = torch.zeros(n, dtype=torch.int32, pin_memory=True)
+        self._tokens_dev = self.runner.tokens_out
         self._p = {  # pinned staging and device copies of the sampler's per-row options
             "temperature": (torch.zeros(n, dtype=torch.float32, pin_memory=True),
                             torch.zeros(n, dtype=torch.float32, device=dev)),
@@ -138,10 +137,8 @@ class Engine:
                        slots=self._p["slots"][1], rng_states=self.rng_states)
         if self.timing_events is not None:
             self.timing_events[1][self.step_index].record()
-        self._tokens_host[:n].copy_(out[:n], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        self.runner.check_status()
-        return [int(t) for t in self._tokens_host[:n].tolist()]
+        host = self.runner.fetch_result()
+        return host[:n].tolist()
 
     # ------------------------------------------------------------------ generate
     def run(self) -> None:

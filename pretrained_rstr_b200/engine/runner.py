@@ -49,8 +49,19 @@ class ModelRunner:
         self._host_events = [torch.cuda.Event() for _ in range(2)]
         self._host_turn = 0
         self._dev = torch.zeros(biggest.size, dtype=torch.int32, device=self.device)
-        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # sampled tokens and the device status word share one buffer, so that one copy
+        # brings both to the host
+        self.result = torch.zeros(runtime.max_requests + 4, dtype=torch.int32, device=self.device)
+        self.result_host = torch.zeros(runtime.max_requests + 4, dtype=torch.int32,
+                                       pin_memory=True)
+        self.tokens_out = self.result[:runtime.max_requests]
+        self.status = self.result[runtime.max_requests:]
         self._status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
+        # CUDA graphs of whole steps, by (token capacity, request capacity, logits rows)
+        self.use_graphs = bool(runtime.use_graphs) and getattr(model, "graph_safe", False)
+        self.graph_max_tokens = 256
+        self._graphs: Dict[tuple, tuple] = {}
+        self._seen: Dict[tuple, int] = {}
         self._pairs_host = torch.empty((runtime.max_requests, 2), dtype=torch.int32,
                                        pin_memory=True)
         self._pairs_dev = torch.zeros((runtime.max_requests, 2), dtype=torch.int32,
@@ -80,12 +91,41 @@ class ModelRunner:
             if self.fail_next_step is not None:
                 exc, self.fail_next_step = self.fail_next_step, None
                 raise exc
-            logits = self.model.forward(ctx)
+            logits = self._run(ctx)
         except Exception:
             self.abort(entries)
             raise
         self.commit(entries)
         return logits[:ctx.n_rows]
+
+    def _run(self, ctx: StepContext) -> torch.Tensor:
+        """Run the model for a prepared step: directly, or, for small steps when graphs are
+        on, as a CUDA graph of the whole step.  A graph is captured for fixed capacities
+        (tokens, requests, logits rows); rows beyond the real ones are padding that no
+        kernel lets touch the cache.  The first step of a shape runs directly with the
+        padded sizes (which also sizes all scratch memory), the second is captured."""
+        lay = ctx.layout
+        if not self.use_graphs or lay.t_cap > self.graph_max_tokens:
+            return self.model.forward(ctx)
+        rows_cap = StepContext.row_capacity(max(ctx.n_rows, 1)) if ctx.n_rows else 0
+        key = (lay.t_cap, lay.b_cap, rows_cap)
+        ctx.launch_tokens, ctx.launch_rows = lay.t_cap, rows_cap
+        ctx.n_tiles = ctx.n_singles = None          # kernels read the device-side counts
+        ctx.max_context = self.model.max_positions
+        hit = self._graphs.get(key)
+        if hit is not None:
+            hit[0].replay()
+            return hit[1]
+        seen = self._seen.get(key, 0)
+        self._seen[key] = seen + 1
+        if seen == 0:
+            return self.model.forward(ctx)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx)
+        self._graphs[key] = (graph, logits)
+        graph.replay()
+        return logits
 
     def prepare(self, entries: Sequence[Entry]) -> StepContext:
         """Validate the batch, reserve cache slots, and put the step's arrays on the device."""
@@ -202,6 +242,20 @@ class ModelRunner:
             self.cache.abort(e.rid)
 
     # ------------------------------------------------------------------ status
+    def fetch_result(self) -> torch.Tensor:
+        """One device-to-host copy of the sampled tokens and the status word
+        (synchronises); raises if a kernel recorded an index out of range."""
+        self.result_host.copy_(self.result, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        n = self.runtime.max_requests
+        code = int(self.result_host[n])
+        if code != 0:
+            detail = [int(v) for v in self.result_host[n + 1:]]
+            self.status.zero_()
+            raise StepError(f"device status {code}: {ops.STATUS_TEXT.get(code, 'unknown')} "
+                            f"{detail}")
+        return self.result_host
+
     def check_status(self) -> None:
         """Read the device status word (synchronises); raises if a kernel recorded an
         index out of range.  The word is cleared afterwards."""

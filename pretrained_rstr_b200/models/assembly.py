@@ -38,6 +38,12 @@ class Model:
         self.state_specs: Dict[Tuple[int, str], StateSpec] = {}
         self._derive_cache_layout()
         self._caches: List[LayerCache] = []
+        # a step can be replayed as a CUDA graph only if every part launches the same
+        # kernels whatever the step holds (parts say so with ``graph_safe = True``)
+        parts = [embedding, position, final_norm, head]
+        for blk in blocks:
+            parts += [blk, blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm]
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
 
     # ---------------------------------------------------------------- cache layout
     def _derive_cache_layout(self) -> None:

@@ -25,6 +25,7 @@ from .registry import register_part
 
 
 class CausalAttention(Mixer):
+    graph_safe = True
     def __init__(self, qkv: Linear, out: Linear, width: int, n_head: int, n_kv_head: int,
                  head_dim: int, scale: float, window: Optional[int], runtime,
                  position=None):

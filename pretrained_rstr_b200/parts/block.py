@@ -8,6 +8,7 @@ from .registry import register_part
 
 
 class PreNormBlock(Block):
+    graph_safe = True
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
                  feed_forward_norm: Norm, width: int, runtime):
         self.mixer, self.feed_forward = mixer, feed_forward

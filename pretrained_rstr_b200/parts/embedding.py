@@ -11,6 +11,7 @@ from .registry import register_part
 
 
 class TokenEmbedding(Embedding):
+    graph_safe = True
     def __init__(self, table: torch.Tensor, vocab: int, width: int, runtime):
         if tuple(table.shape) != (vocab, width):
             raise ValueError(f"token_embedding: table is {list(table.shape)}, "

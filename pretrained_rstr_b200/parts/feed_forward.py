@@ -10,6 +10,7 @@ from .registry import register_part
 
 
 class DenseMLP(FeedForward):
+    graph_safe = True
     def __init__(self, up: Linear, down: Linear, width: int, inner: int, activation: str, runtime):
         if activation not in ops.ACT_CODES:
             raise ValueError(f"dense_mlp: unknown activation {activation!r}")

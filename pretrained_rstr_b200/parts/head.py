@@ -10,6 +10,7 @@ from .registry import register_part
 
 
 class TiedHead(Head):
+    graph_safe = True
     def __init__(self, table: torch.Tensor, vocab: int, width: int, runtime):
         if tuple(table.shape) != (vocab, width):
             raise ValueError(f"tied_head: table is {list(table.shape)}, expected [{vocab}, {width}]")

@@ -9,6 +9,7 @@ from .registry import register_part
 
 
 class LearnedAbsolute(PositionEncoding):
+    graph_safe = True
     def __init__(self, table: torch.Tensor, positions: int, width: int, runtime):
         if tuple(table.shape) != (positions, width):
             raise ValueError(f"learned_absolute: table is {list(table.shape)}, "
@@ -21,6 +22,7 @@ class LearnedAbsolute(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
+    graph_safe = True
     pass
 
 
