@@ -50,6 +50,7 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
     __shared__ float sh_m[DEC_WARPS], sh_l[DEC_WARPS];
     __shared__ float sh_o[DEC_WARPS][MAX_DH];
     __shared__ int sh_last;
+    __shared__ int sh_pages[SPLIT / 8];          // pages of this split (page_size >= 8)
 
     const int idx = blockIdx.x;
     if (token_count != nullptr && idx >= *token_count) return;
@@ -87,46 +88,62 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
 
-    // keys k_begin + warp*KPW + kslot, stepping DEC_WARPS*KPW
-    for (int base = k_begin + warp * KPW; base < k_end; base += DEC_WARPS * KPW) {
-        const int j = base + kslot;
-        float part = 0.0f;
-        bool ok = false;
-        uint4 vraw = make_uint4(0, 0, 0, 0);
-        if (j < k_end) {
-            const int page = table[j / page_size];
-            if (page < 0 || page >= num_pages) {
-                prb_set_status(status, PRB_S_PAGE_RANGE, t, j, page);
-            } else {
-                ok = true;
-                if (piece_ok) {
-                    const size_t row =
-                        (((size_t)page * kv_heads + hk) * page_size + (j % page_size)) * head_dim +
-                        sub * 8;
-                    const uint4 kraw = *reinterpret_cast<const uint4*>(k_pages + row);
-                    vraw = *reinterpret_cast<const uint4*>(v_pages + row);
-                    part = dot8(kraw, qf);
+    // page ids of this split, once
+    const int first_page = (s * SPLIT) / page_size;
+    for (int i = threadIdx.x; i < SPLIT / page_size; i += DEC_THREADS)
+        sh_pages[i] = (first_page + i < max_pages) ? table[first_page + i] : -1;
+    __syncthreads();
+
+    // keys k_begin + warp*KPW + kslot, stepping DEC_WARPS*KPW; UNROLL steps' loads are
+    // issued before any of them is used
+    constexpr int UNROLL = 4;
+    for (int base = k_begin + warp * KPW; base < k_end; base += DEC_WARPS * KPW * UNROLL) {
+        uint4 kraw[UNROLL], vraw[UNROLL];
+        bool ok[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int j = base + u * DEC_WARPS * KPW + kslot;
+            ok[u] = false;
+            kraw[u] = make_uint4(0, 0, 0, 0);
+            vraw[u] = make_uint4(0, 0, 0, 0);
+            if (j < k_end) {
+                const int page = sh_pages[j / page_size - first_page];
+                if (page < 0 || page >= num_pages) {
+                    prb_set_status(status, PRB_S_PAGE_RANGE, t, j, page);
+                } else {
+                    ok[u] = true;
+                    if (piece_ok) {
+                        const size_t row =
+                            (((size_t)page * kv_heads + hk) * page_size + (j % page_size)) *
+                                head_dim + sub * 8;
+                        kraw[u] = *reinterpret_cast<const uint4*>(k_pages + row);
+                        vraw[u] = *reinterpret_cast<const uint4*>(v_pages + row);
+                    }
                 }
             }
         }
-        // every lane takes part in the reduction over the LPK pieces of a key row
 #pragma unroll
-        for (int o = LPK / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-        const float sc = ok ? part * scale : -INFINITY;
-        // online softmax per key slot (each group of LPK lanes has its own running state)
-        const float m_new = fmaxf(m, sc);
-        if (m_new > -INFINITY) {
-            const float corr = (m == -INFINITY) ? 0.0f : __expf(m - m_new);
-            const float p = (sc == -INFINITY) ? 0.0f : __expf(sc - m_new);
-            l = l * corr + p;
-            const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vraw);
+        for (int u = 0; u < UNROLL; ++u) {
+            float part = dot8(kraw[u], qf);
+            // every lane takes part in the reduction over the LPK pieces of a key row
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(vp[i]);
-                acc[2 * i] = fmaf(p, f.x, acc[2 * i] * corr);
-                acc[2 * i + 1] = fmaf(p, f.y, acc[2 * i + 1] * corr);
+            for (int o = LPK / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            const float sc = ok[u] ? part * scale : -INFINITY;
+            // online softmax per key slot (each group of LPK lanes has its own running state)
+            const float m_new = fmaxf(m, sc);
+            if (m_new > -INFINITY) {
+                const float corr = (m == -INFINITY) ? 0.0f : __expf(m - m_new);
+                const float p = (sc == -INFINITY) ? 0.0f : __expf(sc - m_new);
+                l = l * corr + p;
+                const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vraw[u]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(vp[i]);
+                    acc[2 * i] = fmaf(p, f.x, acc[2 * i] * corr);
+                    acc[2 * i + 1] = fmaf(p, f.y, acc[2 * i + 1] * corr);
+                }
+                m = m_new;
             }
-            m = m_new;
         }
     }
     // merge the KPW key slots of the warp (fixed butterfly order)
@@ -223,7 +240,7 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
                                  cudaStream_t stream) {
     if (n_list <= 0) return 0;
     if (n_heads <= 0 || kv_heads <= 0 || n_heads % kv_heads != 0 || head_dim <= 0 ||
-        head_dim % 8 != 0 || head_dim > MAX_DH || page_size <= 0 || SPLIT % page_size != 0 ||
+        head_dim % 8 != 0 || head_dim > MAX_DH || page_size < 8 || SPLIT % page_size != 0 ||
         max_splits <= 0 || max_splits > 65535 || n_heads > 65535)
         return PRB_E_SIZE;
     if (q_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 || ((uintptr_t)k_pages) % 16 != 0 ||

@@ -81,6 +81,9 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_copy_pages.argtypes = [P, P, I, L, I, I, P, P]
     h.prb_gemm_f32.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, P]
     h.prb_gemm_bf16.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, I, P, P]
+    h.prb_gemm_smallm.argtypes = [P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I, P]
+    h.prb_gemm_smallm_max_rows.argtypes = []
+    h.prb_gemm_smallm_max_norm_width.argtypes = []
     h.prb_attention_generic.argtypes = [P, L, P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I,
                                         I, P, P]
     h.prb_attention_decode.argtypes = [P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I,
@@ -92,7 +95,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
     h.prb_sample_max_top_k.argtypes = []
     for name in ("prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
-                 "prb_gemm_f32", "prb_gemm_bf16", "prb_attention_generic", "prb_attention_decode",
+                 "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_smallm", "prb_gemm_smallm_max_rows",
+                 "prb_gemm_smallm_max_norm_width", "prb_attention_generic", "prb_attention_decode",
                  "prb_attention_prefill", "prb_attention_prefill_supports",
                  "prb_attention_decode_split", "prb_sample", "prb_sample_max_top_k"):
         getattr(h, name).restype = c_int
@@ -269,6 +273,52 @@ def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, statu
     _check(lib().prb_gemm_bf16(_p(out), _p(a), _p(w), _p(bias), _p(resid), m, n, k, a.stride(0),
                                w.stride(0), out.stride(0), ACT_CODES[act], dtype_code(out.dtype),
                                tile_n, _p(status), _stream()), what)
+
+
+_SMALLM = None
+
+
+def smallm_limits():
+    """(most rows, widest fused norm) of the decode-time product kernel."""
+    global _SMALLM
+    if _SMALLM is None:
+        _SMALLM = (lib().prb_gemm_smallm_max_rows(), lib().prb_gemm_smallm_max_norm_width())
+    return _SMALLM
+
+
+def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0, bias=None,
+                resid=None, act=None) -> None:
+    """out[M,N] = act(X . w[N,K]^T + bias) (+ resid) for M <= 64 rows, weights streamed once.
+    X is ``a`` (bfloat16 [M,K]) or LayerNorm(``norm_input``) (float32 [M,K]) with ``gamma``,
+    ``beta`` and ``eps``, the norm fused into the kernel."""
+    what = "gemm_smallm"
+    if not w.is_cuda or w.dtype != torch.bfloat16 or w.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: w must be bfloat16 on CUDA with unit inner stride")
+    n, k = w.shape
+    if norm_input is not None:
+        x = norm_input
+        if x.dtype != torch.float32 or x.stride(1) != 1:
+            raise KernelArgumentError(f"{what}: norm_input must be float32 with unit inner stride")
+        _need(gamma, torch.float32, "gamma", what)
+        if beta is not None:
+            _need(beta, torch.float32, "beta", what)
+    else:
+        x = a
+        if x is None or x.dtype != torch.bfloat16 or x.stride(1) != 1:
+            raise KernelArgumentError(f"{what}: a must be bfloat16 with unit inner stride")
+    m = out.shape[0]
+    if x.shape[0] < m or x.shape[1] != k or out.shape[1] != n or out.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias", what)
+    if resid is not None:
+        if resid.dtype != torch.float32 or resid.shape != out.shape or resid.stride(0) != out.stride(0):
+            raise KernelArgumentError(f"{what}: resid must be float32 with the output's shape and stride")
+    _check(lib().prb_gemm_smallm(
+        _p(out), None if norm_input is not None else _p(x),
+        _p(x) if norm_input is not None else None, _p(gamma), _p(beta), float(eps), _p(w),
+        _p(bias), _p(resid), m, n, k, x.stride(0), w.stride(0), out.stride(0), ACT_CODES[act],
+        dtype_code(out.dtype), _stream()), what)
 
 
 def attention_generic(out, q, k_pages, v_pages, block_table, seq_of_token, positions, n_tokens,

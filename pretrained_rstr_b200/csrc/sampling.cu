@@ -14,7 +14,7 @@
 #include "common.cuh"
 
 namespace {
-constexpr int SAMPLE_THREADS = 512;
+constexpr int SAMPLE_THREADS = 1024;
 constexpr int MAX_TOP_K = 1024;
 
 struct Best {
@@ -72,9 +72,17 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
 
     if (!(temp > 0.0f)) {
         Best b{0.0f, -1};
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            const float v = row[i];
-            if (better(v, i, b.v, b.i)) { b.v = v; b.i = i; }
+        const int bd = blockDim.x;
+        for (int i = threadIdx.x; i < vocab; i += 4 * bd) {        // four loads in flight
+            const int i1 = i + bd, i2 = i + 2 * bd, i3 = i + 3 * bd;
+            const float v0 = row[i];
+            const float v1 = i1 < vocab ? row[i1] : 0.0f;
+            const float v2 = i2 < vocab ? row[i2] : 0.0f;
+            const float v3 = i3 < vocab ? row[i3] : 0.0f;
+            if (better(v0, i, b.v, b.i)) { b.v = v0; b.i = i; }
+            if (i1 < vocab && better(v1, i1, b.v, b.i)) { b.v = v1; b.i = i1; }
+            if (i2 < vocab && better(v2, i2, b.v, b.i)) { b.v = v2; b.i = i2; }
+            if (i3 < vocab && better(v3, i3, b.v, b.i)) { b.v = v3; b.i = i3; }
         }
         b = block_best(b, sh);
         if (threadIdx.x == 0) out[r] = b.i;

@@ -26,6 +26,7 @@ from .registry import register_part
 
 class CausalAttention(Mixer):
     graph_safe = True
+    accepts_lazy_norm = True      # the first matrix product may compute the norm itself
     def __init__(self, qkv: Linear, out: Linear, width: int, n_head: int, n_kv_head: int,
                  head_dim: int, scale: float, window: Optional[int], runtime,
                  position=None):
@@ -48,7 +49,7 @@ class CausalAttention(Mixer):
         return KVSpec(self.n_kv_head, self.head_dim, self.window)
 
     def forward(self, ctx, h, x, cache: LayerCache) -> None:
-        t = h.shape[0]
+        t = x.shape[0]
         dtype = self.runtime.dtype
         qkv = ctx.scratch("attn_qkv", (ctx.token_capacity, self.qkv.n_out), dtype)[:t]
         self.qkv.forward(ctx, h, qkv)

@@ -4,6 +4,7 @@ The block knows its parts only through their interfaces."""
 from __future__ import annotations
 
 from .interfaces import Block, FeedForward, LayerCache, Mixer, Norm
+from .linear import LazyNorm
 from .registry import register_part
 
 
@@ -18,10 +19,17 @@ class PreNormBlock(Block):
     def forward(self, ctx, x, cache: LayerCache) -> None:
         t = x.shape[0]
         h = ctx.scratch("block_normed", (ctx.token_capacity, self.width), self.runtime.dtype)[:t]
-        self.mixer_norm.forward(ctx, x, h)
-        self.mixer.forward(ctx, h, x, cache)
-        self.feed_forward_norm.forward(ctx, x, h)
-        self.feed_forward.forward(ctx, h, x)
+        self.mixer.forward(ctx, self._normed(ctx, self.mixer, self.mixer_norm, x, h), x, cache)
+        self.feed_forward.forward(
+            ctx, self._normed(ctx, self.feed_forward, self.feed_forward_norm, x, h), x)
+
+    @staticmethod
+    def _normed(ctx, consumer, norm, x, out):
+        """The consumer's input: a norm that has run, or, for consumers that say they take
+        one (``accepts_lazy_norm``), a :class:`LazyNorm` they may fuse into their first
+        matrix product."""
+        lazy = LazyNorm(ctx, norm, x, out)
+        return lazy if getattr(consumer, "accepts_lazy_norm", False) else lazy.tensor()
 
 
 register_part("arrangement", "pre_norm", PreNormBlock)

@@ -11,6 +11,7 @@ from .registry import register_part
 
 class DenseMLP(FeedForward):
     graph_safe = True
+    accepts_lazy_norm = True      # the first matrix product may compute the norm itself
     def __init__(self, up: Linear, down: Linear, width: int, inner: int, activation: str, runtime):
         if activation not in ops.ACT_CODES:
             raise ValueError(f"dense_mlp: unknown activation {activation!r}")
@@ -21,7 +22,7 @@ class DenseMLP(FeedForward):
         self.runtime = runtime
 
     def forward(self, ctx, h, x) -> None:
-        t = h.shape[0]
+        t = x.shape[0]
         u = ctx.scratch("mlp_inner", (ctx.token_capacity, self.inner), self.runtime.dtype)[:t]
         self.up.forward(ctx, h, u, act=self.activation)
         self.down.forward(ctx, u, x, resid=x)

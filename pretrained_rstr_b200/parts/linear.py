@@ -43,16 +43,46 @@ class Linear:
         b = store.get(name + ".bias") if bias else None
         return cls(w, b, runtime)
 
-    def forward(self, ctx, a: torch.Tensor, out: torch.Tensor, act: Optional[str] = None,
+    def forward(self, ctx, a, out: torch.Tensor, act: Optional[str] = None,
                 resid: Optional[torch.Tensor] = None) -> None:
         """out = act(a . W^T + bias) (+ resid).  ``out`` may be float32 (then ``resid`` may
-        alias it) or the activation type."""
+        alias it) or the activation type.  ``a`` is a tensor, or a :class:`LazyNorm`: a
+        norm that has not run yet, which the decode-time kernel computes in its prologue
+        and every other kernel asks to run first."""
+        m = out.shape[0]
         if self.runtime.dtype == torch.float32:
-            ops.gemm_f32(out, a, self.weight, self.bias, resid, act)
+            ops.gemm_f32(out, _tensor(a), self.weight, self.bias, resid, act)
             return
-        gemm_bf16(ctx, out, a, self.weight, self.bias, resid, act)
+        max_rows, max_norm = ops.smallm_limits()
+        if m <= max_rows and self.n_in % 8 == 0:
+            if isinstance(a, LazyNorm) and a.fusable and self.n_in <= max_norm:
+                ops.gemm_smallm(out, self.weight, norm_input=a.x, gamma=a.norm.gamma,
+                                beta=a.norm.beta, eps=a.norm.eps, bias=self.bias, resid=resid,
+                                act=act)
+            else:
+                ops.gemm_smallm(out, self.weight, a=_tensor(a), bias=self.bias, resid=resid, act=act)
+            return
+        ops.gemm_bf16(out, _tensor(a), self.weight, self.bias, resid, act, status=ctx.status)
 
 
-def gemm_bf16(ctx, out, a, weight, bias, resid, act) -> None:
-    """bfloat16 operands, float32 accumulation in tensor memory, epilogue in float32."""
-    ops.gemm_bf16(out, a, weight, bias, resid, act, status=ctx.status)
+class LazyNorm:
+    """A norm of ``x`` that runs when its result is first needed.  A consumer that can
+    compute the norm itself (``fusable``: a plain layer norm) reads ``x`` and ``norm``
+    instead and the norm never runs as a kernel of its own."""
+
+    def __init__(self, ctx, norm, x: torch.Tensor, out: torch.Tensor):
+        self.ctx, self.norm, self.x, self._out = ctx, norm, x, out
+        self._done = False
+        self.fusable = all(hasattr(norm, f) for f in ("gamma", "beta", "eps")) and \
+            getattr(norm, "kind", "") == "layer_norm"
+        self.shape = out.shape
+
+    def tensor(self) -> torch.Tensor:
+        if not self._done:
+            self.norm.forward(self.ctx, self.x, self._out)
+            self._done = True
+        return self._out
+
+
+def _tensor(a) -> torch.Tensor:
+    return a.tensor() if isinstance(a, LazyNorm) else a

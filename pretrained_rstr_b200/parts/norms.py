@@ -12,6 +12,7 @@ from .registry import register_part
 
 class LayerNorm(Norm):
     graph_safe = True
+    kind = "layer_norm"
     def __init__(self, gamma: torch.Tensor, beta, eps: float, size: int):
         if gamma.numel() != size or (beta is not None and beta.numel() != size):
             raise ValueError(f"layer_norm: gain/bias size differs from {size}")

@@ -244,3 +244,131 @@ def test_attention_far_key_stands_out():
     ops.attention_decode(out2, q, k, v, table, seq, pos, None, None, t, nh, 0.125, None, ws,
                          counters, 4, status)
     assert float((out2.float() - ref).abs().max()) <= 2e-2
+
+
+# ------------------------------------------------------------------ decode-time product
+@pytest.mark.parametrize("m,n,k", [(1, 192, 64), (8, 2304, 768), (5, 1000, 96), (16, 320, 96),
+                                   (33, 768, 3072), (64, 50257, 768), (3, 24, 1608)])
+@pytest.mark.parametrize("variant", ["plain_f32", "bias_gelu_bf16", "bias_resid_f32", "norm_bf16"])
+def test_gemm_smallm(m, n, k, variant):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = (torch.randn(m, k, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda", generator=g) * 0.2
+    resid = torch.randn(m, n, device="cuda", generator=g)
+    ref = a.float() @ w.float().t()
+    if variant == "plain_f32":
+        out = torch.full((m, n), float("nan"), device="cuda")
+        ops.gemm_smallm(out, w, a=a)
+        tol = 2e-4
+    elif variant == "bias_gelu_bf16":
+        out = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+        ops.gemm_smallm(out, w, a=a, bias=bias, act="gelu_new")
+        ref = _act("gelu_new", ref + bias)
+        tol = 2e-2
+    elif variant == "bias_resid_f32":
+        out = resid.clone()
+        ops.gemm_smallm(out, w, a=a, bias=bias, resid=out)
+        ref = ref + bias + resid
+        tol = 2e-4
+    else:
+        xf = torch.randn(m, k, device="cuda", generator=g) * 3.0 + 0.5
+        gamma = torch.randn(k, device="cuda", generator=g)
+        beta = torch.randn(k, device="cuda", generator=g)
+        out = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+        ops.gemm_smallm(out, w, norm_input=xf, gamma=gamma, beta=beta, eps=1e-6, bias=bias)
+        normed = torch.nn.functional.layer_norm(xf, (k,), gamma, beta, 1e-6).to(torch.bfloat16)
+        ref = normed.float() @ w.float().t() + bias
+        tol = 3e-2
+    scale = float(ref.abs().max())
+    err = float((out.float() - ref).abs().max())
+    assert err <= tol * max(1.0, scale), f"max |difference| {err:.3e} (scale {scale:.3g})"
+
+
+def test_gemm_smallm_rows_do_not_depend_on_the_batch():
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(9)
+    a = torch.randn(40, 768, device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.randn(256, 768, device="cuda", generator=g).to(torch.bfloat16)
+    big = torch.zeros(40, 256, device="cuda")
+    ops.gemm_smallm(big, w, a=a)
+    one = torch.zeros(1, 256, device="cuda")
+    ops.gemm_smallm(one, w, a=a[17:18].contiguous())
+    assert torch.equal(one[0], big[17])
+
+
+# ------------------------------------------------------------------------ small kernels
+@pytest.mark.parametrize("rows,width", [(1, 64), (7, 96), (33, 1608), (5, 50000)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_layernorm(rows, width, out_dtype):
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    x = torch.randn(rows + 3, width, device="cuda", generator=g) * 2 + 1
+    gamma = torch.randn(width, device="cuda", generator=g)
+    beta = torch.randn(width, device="cuda", generator=g)
+    idx = torch.randperm(rows + 3, device="cuda", generator=g)[:rows].to(torch.int32)
+    out = torch.zeros(rows, width, device="cuda", dtype=out_dtype)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ops.layernorm(out, x, gamma, beta, 1e-6, rows=idx, status=status)
+    ref = torch.nn.functional.layer_norm(x[idx.long()].double(), (width,), gamma.double(),
+                                         beta.double(), 1e-6).float()
+    tol = 2e-5 if out_dtype == torch.float32 else 4e-2
+    assert float((out.float() - ref).abs().max()) <= tol * max(1.0, float(ref.abs().max()))
+    bad = torch.tensor([rows + 10], dtype=torch.int32, device="cuda")
+    ops.layernorm(out[:1], x, gamma, beta, 1e-6, rows=bad, status=status)
+    assert status.tolist()[0] == 6                      # refused, recorded, nothing read
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_and_range_check(dtype):
+    ops = _ops()
+    wte = torch.randn(1000, 96, device="cuda").to(dtype)
+    wpe = torch.randn(256, 96, device="cuda").to(dtype)
+    tok = torch.tensor([5, 999, 0, 17], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([0, 255, 3, 9], dtype=torch.int32, device="cuda")
+    out = torch.zeros(4, 96, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ops.embed(out, tok, pos, wte, wpe, status)
+    assert torch.equal(out, wte[tok.long()].float() + wpe[pos.long()].float())
+    assert status.tolist() == [0, 0, 0, 0]
+    ops.embed(out, torch.tensor([1, 1000, 2, 3], dtype=torch.int32, device="cuda"), pos, wte, wpe,
+              status)
+    assert status.tolist() == [1, 1, 1000, 1000] and float(out[1].abs().max()) == 0.0
+
+
+def test_kv_append_and_copy_pages():
+    ops = _ops()
+    pages, heads, ps, dh = 6, 3, 16, 32
+    store = torch.zeros(4, pages, heads, ps, dh, device="cuda", dtype=torch.bfloat16)
+    k, v = store[2], store[3]
+    qkv = torch.randn(5, 3 * heads * dh, device="cuda").to(torch.bfloat16)
+    slots = torch.tensor([3 * ps + 15, -1, 0, 5 * ps + 1, 2 * ps + 7], dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ops.kv_append(k, v, qkv[:, heads * dh:2 * heads * dh], qkv[:, 2 * heads * dh:], slots, 5, status)
+    for t, s in enumerate(slots.tolist()):
+        if s < 0:
+            continue
+        assert torch.equal(k[s // ps, :, s % ps, :].reshape(-1), qkv[t, heads * dh:2 * heads * dh])
+        assert torch.equal(v[s // ps, :, s % ps, :].reshape(-1), qkv[t, 2 * heads * dh:])
+    assert int((k != 0).any(dim=-1).sum()) <= 4 * heads      # the skipped token wrote nothing
+    pairs = torch.tensor([[3, 1], [5, 4]], dtype=torch.int32, device="cuda")
+    ops.copy_pages(store, pairs, 2, status)
+    assert torch.equal(store[:, 1], store[:, 3]) and torch.equal(store[:, 4], store[:, 5])
+    assert status.tolist() == [0, 0, 0, 0]
+    ops.kv_append(k, v, qkv[:, :heads * dh], qkv[:, :heads * dh],
+                  torch.tensor([pages * ps], dtype=torch.int32, device="cuda"), 1, status)
+    assert status.tolist()[0] == 3
+
+
+def test_sample_kernel_greedy_ties_and_nan():
+    ops = _ops()
+    logits = torch.randn(6, 50257, device="cuda")
+    logits[1, 77] = logits[1, 40000] = 99.0            # tie: lowest id
+    logits[2, 123] = float("nan")                       # NaN wins
+    logits[3, 50256] = 50.0                             # last column
+    out = torch.zeros(6, dtype=torch.int32, device="cuda")
+    ops.sample(out, logits, 6)
+    want = logits.argmax(dim=1).tolist()
+    want[1], want[2], want[3] = 77, 123, 50256
+    assert out.tolist() == want
