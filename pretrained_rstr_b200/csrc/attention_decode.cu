@@ -19,7 +19,7 @@
 namespace {
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
-constexpr int SPLIT = 256;          // keys per split
+constexpr int SPLIT = 128;          // keys per split
 constexpr int MAX_DH = 256;
 
 __device__ __forceinline__ float dot8(const uint4& a, const float* q) {
@@ -96,7 +96,7 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
 
     // keys k_begin + warp*KPW + kslot, stepping DEC_WARPS*KPW; UNROLL steps' loads are
     // issued before any of them is used
-    constexpr int UNROLL = 4;
+    constexpr int UNROLL = 8;
     for (int base = k_begin + warp * KPW; base < k_end; base += DEC_WARPS * KPW * UNROLL) {
         uint4 kraw[UNROLL], vraw[UNROLL];
         bool ok[UNROLL];

@@ -57,6 +57,26 @@ gemm_smallm_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ x,
     const int g = lane >> 2, q = lane & 3;        // MMA group (row / token) and quad index
     const int n0 = blockIdx.x * ROWS;
 
+    // ---- stream the 16 weight rows; this warp takes k-steps warp, warp+8, ...
+    // (the first loads are issued before the norm so that they overlap it)
+    float acc[MT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+    const int steps = (k + KSTEP - 1) / KSTEP;
+    const int r0 = n0 + g, r1 = n0 + g + 8;
+    const bool row0_ok = r0 < n, row1_ok = r1 < n;
+    const __nv_bfloat16* w0 = w + (size_t)(row0_ok ? r0 : 0) * ldw;
+    const __nv_bfloat16* w1 = w + (size_t)(row1_ok ? r1 : 0) * ldw;
+
+    constexpr int PF = 4;                          // steps of weights in flight per warp
+    uint4 wa[PF], wb[PF];
+#pragma unroll
+    for (int p = 0; p < PF; ++p) {
+        const int kk = (warp + p * SM_WARPS) * KSTEP + q * 8;
+        const bool ok = kk < k;
+        wa[p] = (ok && row0_ok) ? ldg_stream(w0 + kk) : make_uint4(0, 0, 0, 0);
+        wb[p] = (ok && row1_ok) ? ldg_stream(w1 + kk) : make_uint4(0, 0, 0, 0);
+    }
     if constexpr (LN) {
         // ---- fused LayerNorm of the M rows into shared memory (bfloat16)
         const int nvec = k / 4;                   // float4 per row
@@ -108,25 +128,6 @@ gemm_smallm_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ x,
         __syncthreads();
     }
 
-    // ---- stream the 16 weight rows; this warp takes k-steps warp, warp+8, ...
-    float acc[MT][4];
-#pragma unroll
-    for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
-    const int steps = (k + KSTEP - 1) / KSTEP;
-    const int r0 = n0 + g, r1 = n0 + g + 8;
-    const bool row0_ok = r0 < n, row1_ok = r1 < n;
-    const __nv_bfloat16* w0 = w + (size_t)(row0_ok ? r0 : 0) * ldw;
-    const __nv_bfloat16* w1 = w + (size_t)(row1_ok ? r1 : 0) * ldw;
-
-    constexpr int PF = 4;                          // steps of weights in flight per warp
-    uint4 wa[PF], wb[PF];
-#pragma unroll
-    for (int p = 0; p < PF; ++p) {
-        const int kk = (warp + p * SM_WARPS) * KSTEP + q * 8;
-        const bool ok = kk < k;
-        wa[p] = (ok && row0_ok) ? ldg_stream(w0 + kk) : make_uint4(0, 0, 0, 0);
-        wb[p] = (ok && row1_ok) ? ldg_stream(w1 + kk) : make_uint4(0, 0, 0, 0);
-    }
     for (int s0 = warp; s0 < steps; s0 += SM_WARPS * PF) {
 #pragma unroll
         for (int p = 0; p < PF; ++p) {
