@@ -65,6 +65,10 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
     }
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int s_first = lo / SPLIT, s_last = pos / SPLIT;
+    if (s_last >= max_splits) {                   // the launch does not cover this context
+        if (threadIdx.x == 0 && s == 0) prb_set_status(status, PRB_S_POSITION_RANGE, t, pos, max_splits);
+        return;
+    }
     if (s < s_first || s > s_last) return;
     const int n_splits = s_last - s_first + 1;
     const int k_begin = max(lo, s * SPLIT), k_end = min(pos + 1, (s + 1) * SPLIT);

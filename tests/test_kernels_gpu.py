@@ -238,12 +238,17 @@ def test_attention_far_key_stands_out():
     ops.attention_prefill(out, q, k, v, table, pos, tr, t0, tn, None, 2, nh, 0.125, None, status)
     assert float((out.float() - ref).abs().max()) <= 2e-2
     t = q.shape[0]
-    ws = torch.zeros(t * nh * 4 * (dh + 2), device="cuda")
+    splits = -(-1024 // ops.decode_split())
+    ws = torch.zeros(t * nh * splits * (dh + 2), device="cuda")
     counters = torch.zeros(t * nh, dtype=torch.int32, device="cuda")
     out2 = torch.zeros_like(q)
     ops.attention_decode(out2, q, k, v, table, seq, pos, None, None, t, nh, 0.125, None, ws,
-                         counters, 4, status)
+                         counters, splits, status)
     assert float((out2.float() - ref).abs().max()) <= 2e-2
+    # a launch with too few splits for the context is recorded, not computed wrongly
+    ops.attention_decode(out2, q, k, v, table, seq, pos, None, None, t, nh, 0.125, None, ws,
+                         counters, 2, status)
+    assert status.tolist()[0] == 2
 
 
 # ------------------------------------------------------------------ decode-time product
