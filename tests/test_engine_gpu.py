@@ -176,7 +176,7 @@ def test_step_refuses_bad_batches(folders):
     from pretrained_rstr_b200.engine.batch import Entry
     from pretrained_rstr_b200.engine.runner import StepError
     raw, seed = TINY["A"]
-    rp = Replayer(folders[("A", "float32")], "float32", max_tokens=128)
+    rp = Replayer(folders[("A", "float32")], "float32", max_tokens=256)
     rp.lm.cache.open("a")
     run = rp.lm.runner.step
     with pytest.raises(StepError, match="twice"):
@@ -187,6 +187,8 @@ def test_step_refuses_bad_batches(folders):
         run([Entry("a", [1, 2], [2])])
     with pytest.raises(StepError, match="positions"):
         run([Entry("a", [1] * (raw["n_positions"] + 1), [])])
+    with pytest.raises(StepError, match="the runtime takes"):
+        run([Entry("a", [1] * 100, []), Entry("b", [1] * 100, []), Entry("c", [1] * 100, [])])
     with pytest.raises(StepError, match="no tokens"):
         run([Entry("a", [], [])])
     assert rp.lm.cache.length("a") == 0
