@@ -211,7 +211,7 @@ def test_trace_run_program(tmp_path, dtype):
     out = tmp_path / "out"
     proc = subprocess.run(
         [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
-         "--out", str(out), "--max-tokens", "128"],
+         "--out", str(out), "--max-tokens", "192"],
         input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
         timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
