@@ -1,0 +1,339 @@
+"""Each part alone against the plain implementation's function for that part, and the
+generality of the assembly: a toy architecture defined here (a mixer with state of its
+own in one layer, attention in another, a layer that runs twice and reads a cache
+another run wrote) is registered, built and stepped without touching the framework."""
+import math
+import os
+from dataclasses import dataclass
+from typing import Dict
+
+import pytest
+import torch
+
+import plain_gpt2
+from helpers import ATOL, TINY, make_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.fixture(scope="module")
+def loaded(tmp_path_factory):
+    from pretrained_rstr_b200.engine.loading import load_model
+    out = {}
+    for name, (raw, seed) in TINY.items():
+        for dtype in DTYPES:
+            folder = make_folder(str(tmp_path_factory.mktemp(f"p{name}{dtype}")), raw, seed, dtype)
+            out[(name, dtype)] = (load_model(folder, dtype=dtype, max_batched_tokens=256,
+                                             max_requests=4, max_tokens=1024),
+                                  plain_gpt2.PlainGPT2(folder))
+    return out
+
+
+def _ctx(lm, lengths, rid0=0):
+    """A prepared step of whole prompts of the given lengths (reservation left pending)."""
+    from pretrained_rstr_b200.engine.batch import Entry
+    entries = []
+    for i, n in enumerate(lengths):
+        rid = f"part{rid0}_{i}"
+        lm.cache.open(rid)
+        entries.append(Entry(rid, random_tokens(n, lm.model.vocab, i), [n - 1]))
+    return lm.runner.prepare(entries), entries
+
+
+def _done(lm, entries):
+    lm.runner.abort(entries)
+    for e in entries:
+        lm.cache.close(e.rid)
+
+
+def _tol(dtype, scale=1.0):
+    return (2e-5 if dtype == "float32" else 2e-2) * max(1.0, scale)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_embedding_head_parts(loaded, name, dtype):
+    lm, plain = loaded[(name, dtype)]
+    ctx, entries = _ctx(lm, [7, 33])
+    t, d = 40, lm.model.width
+    act = lm.runtime.dtype
+    x = torch.randn(t, d, device="cuda") * 2 + 0.3
+    # norm
+    out = torch.zeros(t, d, device="cuda", dtype=act)
+    lm.model.blocks[1].mixer_norm.forward(ctx, x, out)
+    ref = plain_gpt2.layer_norm(x.cpu(), plain.w["h.1.ln_1.weight"], plain.w["h.1.ln_1.bias"], plain.eps)
+    assert float((out.float().cpu() - ref).abs().max()) <= _tol(dtype, float(ref.abs().max()))
+    # embedding + learned positions
+    emb = torch.zeros(t, d, device="cuda")
+    lm.model.embedding.forward(ctx, lm.model.position, emb)
+    toks = [tk for e in entries for tk in e.tokens]
+    ref = torch.cat([plain_gpt2.embeddings(plain.w["wte.weight"], plain.w["wpe.weight"], e.tokens)
+                     for e in entries])
+    assert float((emb.cpu() - ref).abs().max()) <= 1e-6
+    # tied head
+    h = (torch.randn(5, d, device="cuda")).to(act)
+    logits = torch.zeros(5, lm.model.vocab, device="cuda")
+    lm.model.head.forward(ctx, h, logits)
+    ref = h.float().cpu() @ plain.w["wte.weight"].T
+    assert float((logits.cpu() - ref).abs().max()) <= _tol(dtype) * 0.5
+    _done(lm, entries)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens", [5, 100])        # decode-time and prompt-time products
+def test_feed_forward_part(loaded, name, dtype, tokens):
+    lm, plain = loaded[(name, dtype)]
+    ctx, entries = _ctx(lm, [tokens], rid0=1)
+    d = lm.model.width
+    h = torch.randn(tokens, d, device="cuda").to(lm.runtime.dtype)
+    x0 = torch.randn(tokens, d, device="cuda")
+    x = x0.clone()
+    lm.model.blocks[0].feed_forward.forward(ctx, h, x)
+    w = plain.w
+    ref = x0.cpu() + plain_gpt2.mlp(h.float().cpu(), w["h.0.mlp.c_fc.weight"], w["h.0.mlp.c_fc.bias"],
+                                    w["h.0.mlp.c_proj.weight"], w["h.0.mlp.c_proj.bias"],
+                                    plain.activation)
+    assert float((x.cpu() - ref).abs().max()) <= _tol(dtype)
+    _done(lm, entries)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_mixer_part(loaded, name, dtype):
+    """Whole prompts of two requests through the mixer alone: projections, cache append,
+    attention over the pages, output projection, residual."""
+    lm, plain = loaded[(name, dtype)]
+    lengths = [70, 3]
+    ctx, entries = _ctx(lm, lengths, rid0=2)
+    d = lm.model.width
+    layer = lm.model.config.n_layer - 1
+    h = torch.randn(sum(lengths), d, device="cuda").to(lm.runtime.dtype)
+    x = torch.zeros(sum(lengths), d, device="cuda")
+    lm.model.blocks[layer].mixer.forward(ctx, h, x, lm.model._caches[layer])
+    w, p = plain.w, f"h.{layer}."
+    at = 0
+    for n in lengths:
+        ref = plain_gpt2.causal_attention(
+            h[at:at + n].float().cpu(), w[p + "attn.c_attn.weight"], w[p + "attn.c_attn.bias"],
+            w[p + "attn.c_proj.weight"], w[p + "attn.c_proj.bias"], plain.n_head,
+            plain_gpt2.attention_scale(plain, layer))
+        assert float((x[at:at + n].cpu() - ref).abs().max()) <= _tol(dtype)
+        at += n
+    _done(lm, entries)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_block_part(loaded, dtype):
+    lm, plain = loaded[("B", dtype)]
+    ctx, entries = _ctx(lm, [50], rid0=3)
+    x0 = torch.randn(50, lm.model.width, device="cuda")
+    x = x0.clone()
+    lm.model.blocks[1].forward(ctx, x, lm.model._caches[1])
+    ref = plain_gpt2.block(plain, 1, x0.cpu())
+    assert float((x.cpu() - ref).abs().max()) <= _tol(dtype, 2.0)
+    _done(lm, entries)
+
+
+# --------------------------------------------------------------------------- toy parts
+def _register_toy():
+    """A mixer that keeps a running state per request, and an architecture that uses it."""
+    from pretrained_rstr_b200.config import (Architecture, ConfigError, LayerSpec, ModelConfig,
+                                             PartSpec, RunEntry, register_architecture)
+    from pretrained_rstr_b200.models.assembly import build_model
+    from pretrained_rstr_b200.parts import Mixer, StateSpec, register_part
+    from pretrained_rstr_b200.weights import TensorExpectation, normal
+
+    class RunningStateMixer(Mixer):
+        """s_t = decay * s_{t-1} + h_t (per request, kept in its state slot between steps);
+        x_t += W s_t.  Written with array-library calls: toy parts need no kernels."""
+
+        def __init__(self, params, store, runtime):
+            self.w = store.get(params["weights"] + ".weight", torch.float32)
+            self.decay = float(params["decay"])
+            self.width = params["width"]
+
+        def state_specs(self):
+            return [StateSpec("running", (self.width,), torch.float32)]
+
+        def forward(self, ctx, h, x, cache):
+            state = cache.state["running"]
+            host = ctx.host
+            for b in range(len(host.rids)):
+                slot = host.state_slot[b]
+                s = torch.zeros(self.width, device=h.device) if host.fresh[b] else state[slot].clone()
+                for t in range(host.q_start[b], host.q_start[b + 1]):
+                    s = self.decay * s + h[t].float()
+                    x[t] += self.w @ s
+                state[slot] = s
+
+    register_part("mixer", "toy_running_state", RunningStateMixer)
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        width: int
+        heads: int
+        inner: int
+        vocab: int
+        positions: int
+        decay: float
+        identifiers = ("ToyForTests",)
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["width"], raw["heads"], raw["inner"], raw["vocab"], raw["positions"],
+                       raw["decay"])
+
+        def to_dict(self):
+            return {"architectures": ["ToyForTests"], "width": self.width, "heads": self.heads,
+                    "inner": self.inner, "vocab": self.vocab, "positions": self.positions,
+                    "decay": self.decay}
+
+        def _mlp(self, p):
+            return PartSpec("dense_mlp", {"weights": {"up": p + "up", "down": p + "down"},
+                                          "width": self.width, "inner": self.inner,
+                                          "activation": "relu", "bias": True,
+                                          "weight_layout": "out_in"})
+
+        def _norm(self, name):
+            return PartSpec("layer_norm", {"weights": name, "size": self.width, "eps": 1e-5})
+
+        def layer_specs(self):
+            toy = PartSpec("toy_running_state", {"weights": "l0.mix", "decay": self.decay,
+                                                 "width": self.width})
+            attn = PartSpec("causal_attention", {
+                "weights": {"qkv": "l1.qkv", "out": "l1.out"}, "width": self.width,
+                "n_head": self.heads, "n_kv_head": self.heads, "head_dim": self.width // self.heads,
+                "scale": 1.0 / math.sqrt(self.width // self.heads), "window": None, "bias": False,
+                "weight_layout": "out_in"})
+            return [LayerSpec("l0.", "pre_norm", toy, self._mlp("l0."), self._norm("l0.n1"),
+                              self._norm("l0.n2")),
+                    LayerSpec("l1.", "pre_norm", attn, self._mlp("l1."), self._norm("l1.n1"),
+                              self._norm("l1.n2"))]
+
+        def run_order(self):
+            # layer 1 runs twice; its second run reads the cache its first run wrote
+            return [RunEntry(0, 0, True), RunEntry(1, 1, True), RunEntry(1, 1, False)]
+
+        def embedding_spec(self):
+            return PartSpec("token_embedding", {"weights": "emb", "vocab": self.vocab,
+                                                "width": self.width})
+
+        def position_spec(self):
+            return PartSpec("learned_absolute", {"weights": "pos", "positions": self.positions,
+                                                 "width": self.width})
+
+        def final_norm_spec(self):
+            return self._norm("nf")
+
+        def head_spec(self):
+            return PartSpec("tied_head", {"weights": "emb", "vocab": self.vocab, "width": self.width})
+
+        @property
+        def max_positions(self):
+            return self.positions
+
+    def expected(cfg):
+        d, f = cfg.width, cfg.inner
+        e = {"emb.weight": (cfg.vocab, d), "pos.weight": (cfg.positions, d),
+             "nf.weight": (d,), "nf.bias": (d,), "l0.mix.weight": (d, d),
+             "l1.qkv.weight": (3 * d, d), "l1.out.weight": (d, d)}
+        for l in ("l0.", "l1."):
+            e.update({l + "n1.weight": (d,), l + "n1.bias": (d,), l + "n2.weight": (d,),
+                      l + "n2.bias": (d,), l + "up.weight": (f, d), l + "up.bias": (f,),
+                      l + "down.weight": (d, f), l + "down.bias": (d,)})
+        return {k: TensorExpectation(v) for k, v in e.items()}
+
+    def random_tensors(cfg, seed):
+        out = {}
+        for name, exp in expected(cfg).items():
+            is_gain = name.split(".")[-2] in ("n1", "n2", "nf") and name.endswith("weight")
+            out[name] = normal(seed, name, exp.shape, 0.05, mean=1.0 if is_gain else 0.0)
+        return out
+
+    register_architecture(ToyConfig.identifiers, Architecture(
+        "toy", ToyConfig, lambda cfg, store, rt: build_model(cfg, store, rt), expected,
+        random_tensors))
+    return ToyConfig
+
+
+def _toy_plain(w: Dict[str, torch.Tensor], cfg, ids):
+    """The toy model, whole sequence, plain."""
+    d, nh = cfg.width, cfg.heads
+    dh = d // nh
+    ln = lambda x, n: plain_gpt2.layer_norm(x, w[n + ".weight"], w[n + ".bias"], 1e-5)
+    mlp = lambda x, l: torch.relu(x @ w[l + "up.weight"].T + w[l + "up.bias"]) @ w[l + "down.weight"].T \
+        + w[l + "down.bias"]
+    x = w["emb.weight"][torch.tensor(ids)] + w["pos.weight"][:len(ids)]
+    h = ln(x, "l0.n1")
+    s = torch.zeros(d)
+    mixed = []
+    for t in range(len(ids)):
+        s = cfg.decay * s + h[t]
+        mixed.append(w["l0.mix.weight"] @ s)
+    x = x + torch.stack(mixed)
+    x = x + mlp(ln(x, "l0.n2"), "l0.")
+    kv = None
+    for run in range(2):
+        qkv = ln(x, "l1.n1") @ w["l1.qkv.weight"].T
+        q = qkv[:, :d]
+        if run == 0:
+            kv = (qkv[:, d:2 * d], qkv[:, 2 * d:])         # the second run reads these again
+        k, v = kv
+        mask = torch.tril(torch.ones(len(ids), len(ids), dtype=torch.bool))
+        o = torch.zeros_like(x)
+        for hh in range(nh):
+            c = slice(hh * dh, (hh + 1) * dh)
+            sc = (q[:, c] @ k[:, c].T) / math.sqrt(dh)
+            o[:, c] = torch.softmax(sc.masked_fill(~mask, -math.inf), 1) @ v[:, c]
+        x = x + o @ w["l1.out.weight"].T
+        x = x + mlp(ln(x, "l1.n2"), "l1.")
+    return ln(x, "nf") @ w["emb.weight"].T
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_toy_architecture_with_state_and_repeated_layer(tmp_path, dtype):
+    from pretrained_rstr_b200.engine.batch import Entry
+    from pretrained_rstr_b200.engine.loading import load_model
+    from pretrained_rstr_b200.weights import load_file, make_random_model
+    ToyConfig = _register_toy()
+    cfg = ToyConfig(width=48, heads=3, inner=80, vocab=200, positions=160, decay=0.7)
+    folder = str(tmp_path / "toy")
+    make_random_model(folder, cfg, seed=5,
+                      dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    lm = load_model(folder, dtype=dtype, max_batched_tokens=256, max_requests=2, max_tokens=512)
+    assert lm.model.graph_safe is False                       # toy parts are not replayed as graphs
+    assert (0, "running") in lm.model.state_specs and len(lm.model.group_specs) == 1
+    assert lm.model.group_specs[0].layers == (1,)
+    w = {k: v.float() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    prompts = {r: random_tokens(n, 200, i) for i, (r, n) in enumerate([("a", 90), ("b", 41), ("c", 70)])}
+    oracle = {r: _toy_plain(w, cfg, ids) for r, ids in prompts.items()}
+    got = {}
+
+    def run(batch, end=()):
+        entries = []
+        for rid, lo, hi in batch:
+            if rid not in lm.cache.requests:
+                lm.cache.open(rid)
+            entries.append(Entry(rid, prompts[rid][lo:hi], list(range(hi - lo))))
+        logits = lm.runner.step(entries).cpu()
+        lm.runner.check_status()
+        r = 0
+        for rid, lo, hi in batch:
+            for p in range(lo, hi):
+                got[(rid, p)] = logits[r].clone()
+                r += 1
+        for rid in end:
+            lm.cache.close(rid)
+
+    run([("a", 0, 30)])
+    run([("a", 30, 31), ("b", 0, 41)])                        # decode beside a whole prompt
+    run([("a", 31, 90), ("b", 41, 41)][:1], end=["a"])
+    run([("c", 0, 2)], end=[])                                # c takes the slot a gave back:
+    run([("c", 2, 70)], end=["c", "b"])                       # its state must start from zero
+    tol = ATOL[dtype]
+    for (rid, p), row in got.items():
+        err = float((row - oracle[rid][p]).abs().max())
+        assert err <= tol, f"request {rid} position {p}: {err:.3e}"
+    assert lm.cache.slots.free_count == 2
