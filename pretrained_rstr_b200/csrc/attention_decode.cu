@@ -267,3 +267,90 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
     PRB_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------------------------
+// Entry point that allocates nothing (declared in attention_decode_noalloc.h).
+//
+// Some programs that load this library may not allocate device memory at all: a host
+// whose allocator owns the whole GPU and hands nothing to third parties, a plugin that
+// runs inside someone else's process under a fixed memory budget, or a caller in a
+// context where an allocation would synchronise the device or fail.  For them the split
+// workspace and the per-(token, head) counters of the decode attention kernel live in
+// two file-scope device arrays of fixed size instead of caller-provided buffers.  Every
+// GPU that loads the library holds these arrays (a little over 4 MiB) until the process
+// exits, whether or not the entry point is ever called.
+//
+// In host code `noalloc_workspace` and `noalloc_counters` are only stand-ins for the
+// device arrays, not device addresses; the addresses are asked for with
+// cudaGetSymbolAddress once per device, with that device current, by the first call on
+// that device.  That first call should therefore come before any stream capture.
+//
+// All calls share the two arrays and the arrays keep what the last call left in them.
+// The counters have to be zero when the kernel starts, so every call clears the part it
+// is going to use (an asynchronous memset on the caller's stream, ordered before the
+// kernel).  Two calls whose kernels overlap on the GPU (different streams, or graph
+// branches that run side by side) race on the arrays and give wrong results: keep calls
+// to this entry point ordered one after the other.
+constexpr long NOALLOC_WS_FLOATS = 1L << 20;     // 4 MiB of float32 partial results
+constexpr int NOALLOC_COUNTERS = 1 << 14;        // 64 KiB of int32 counters
+constexpr int NOALLOC_MAX_DEVICES = 64;
+
+static __device__ __align__(256) float noalloc_workspace[NOALLOC_WS_FLOATS];
+static __device__ __align__(256) int noalloc_counters[NOALLOC_COUNTERS];
+
+namespace {
+struct NoAllocDevice {
+    bool ready = false;
+    float* workspace = nullptr;
+    int* counters = nullptr;
+};
+NoAllocDevice noalloc_devices[NOALLOC_MAX_DEVICES];
+}  // namespace
+
+// Largest sizes the entry point takes: floats of workspace (n_list * n_heads * max_splits
+// * (head_dim + 2) must not exceed it) and counters (n_list * n_heads).
+PRB_API void prb_attention_decode_noalloc_limits(long* workspace_floats, int* counters) {
+    if (workspace_floats) *workspace_floats = NOALLOC_WS_FLOATS;
+    if (counters) *counters = NOALLOC_COUNTERS;
+}
+
+// Same computation and arguments as prb_attention_decode, without the scratch pointers.
+// Returns PRB_E_SIZE (-3) when the launch would need more scratch than the fixed arrays
+// hold, a positive cudaError_t if the set-up or the launch failed, 0 otherwise.
+PRB_API int prb_attention_decode_noalloc(void* out, long out_stride, const void* q, long q_stride,
+                                         const void* k_pages, const void* v_pages,
+                                         const int* block_table, const int* seq_of_token,
+                                         const int* positions, const int* token_list,
+                                         const int* token_count, int n_list, int n_heads,
+                                         int kv_heads, int head_dim, int page_size, int max_pages,
+                                         int num_pages, float scale, int window, int max_splits,
+                                         int* status, cudaStream_t stream) {
+    if (n_list <= 0) return 0;
+    if (n_heads <= 0 || head_dim <= 0 || max_splits <= 0) return PRB_E_SIZE;
+    const long need_ws = (long)n_list * n_heads * max_splits * (head_dim + 2);
+    const long need_counters = (long)n_list * n_heads;
+    if (need_ws > NOALLOC_WS_FLOATS || need_counters > NOALLOC_COUNTERS) return PRB_E_SIZE;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return PRB_E_ARG;
+    NoAllocDevice& d = noalloc_devices[dev];
+    if (!d.ready) {
+        // once per device, with that device current: the device addresses of the arrays
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, noalloc_workspace);
+        if (e != cudaSuccess) return (int)e;
+        d.workspace = static_cast<float*>(p);
+        e = cudaGetSymbolAddress(&p, noalloc_counters);
+        if (e != cudaSuccess) return (int)e;
+        d.counters = static_cast<int*>(p);
+        d.ready = true;
+    }
+    // the counters must start at zero, whatever an earlier call left behind
+    e = cudaMemsetAsync(d.counters, 0, (size_t)need_counters * sizeof(int), stream);
+    if (e != cudaSuccess) return (int)e;
+    return prb_attention_decode(out, out_stride, q, q_stride, k_pages, v_pages, block_table,
+                                seq_of_token, positions, token_list, token_count, n_list, n_heads,
+                                kv_heads, head_dim, page_size, max_pages, num_pages, scale, window,
+                                d.workspace, d.counters, max_splits, status, stream);
+}
