@@ -161,8 +161,81 @@ def timed_decode(engine, lm, batch, ctx_len, steps, warmup, vocab, seed):
     return ms, wall, launches, mean_ctx, h2d
 
 
+def profile_gemm(shape: str) -> int:
+    """Small workload for ncu: the prompt-time GEMM at one shape, every tile width, timed as
+    a CUDA graph of 20 launches, with cuBLAS (torch.mm) beside it."""
+    import torch
+    from pretrained_rstr_b200.csrc import ops
+    m, n, k = (int(x) for x in shape.split(","))
+
+    def timeit(f, reps=20):
+        f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / reps * 1e3
+
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    w = torch.randn(n, k, device="cuda").bfloat16()
+    outb = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    outf = torch.zeros(m, n, device="cuda")
+    bias = torch.randn(n, device="cuda")
+    res = {}
+    for tn in (0, 32, 64, 128, 256):
+        res[f"tile{tn}"] = {
+            "bf16_plain_us": timeit(lambda: ops.gemm_bf16(outb, a, w, tile_n=tn)),
+            "bf16_bias_gelu_us": timeit(lambda: ops.gemm_bf16(outb, a, w, bias=bias, act="gelu_new", tile_n=tn)),
+            "f32_bias_resid_us": timeit(lambda: ops.gemm_bf16(outf, a, w, bias=bias, resid=outf, tile_n=tn)),
+        }
+    res["cublas_us"] = timeit(lambda: torch.mm(a, w.t(), out=outb))
+    res["gflop"] = 2 * m * n * k / 1e9
+    print(json.dumps({"profile_gemm": shape, **res}))
+    return 0
+
+
+def profile_decode(batch: int) -> int:
+    """Small workload for ncu: the benchmark model, ``batch`` requests of 900 prompt tokens,
+    then four decode steps launched kernel by kernel (no CUDA graph)."""
+    import random
+    import torch
+    from pretrained_rstr_b200 import load_lm
+    from pretrained_rstr_b200.config import GPT2Config
+    from pretrained_rstr_b200.weights import make_random_model
+    tmp = tempfile.mkdtemp(prefix="prb200_prof_")
+    try:
+        make_random_model(tmp, GPT2Config.from_dict(dict(SMALL)), seed=2, dtype=torch.bfloat16)
+        m = load_lm(tmp, gpu=True, dtype="bfloat16", max_lanes=64, max_batched_tokens=2048,
+                    prefill_chunk=1024, share_prefixes=False)
+    finally:
+        import shutil
+        shutil.rmtree(tmp, ignore_errors=True)
+    e = m.engine
+    e.runner.use_graphs = False
+    rng = random.Random(0)
+    for i in range(batch):
+        e.submit(i, [rng.randrange(SMALL["vocab_size"]) for _ in range(900)], 100)
+    while any(r.phase != "decode" for r in e.scheduler.running.values()) or e.scheduler.waiting:
+        e.step()
+    for _ in range(4):
+        e.step()
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_decode": batch, "ok": True}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--profile-gemm", default=None, metavar="M,N,K")
+    ap.add_argument("--profile-decode", type=int, default=None, metavar="BATCH")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
@@ -174,6 +247,10 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.profile_gemm:
+        return profile_gemm(args.profile_gemm)
+    if args.profile_decode:
+        return profile_decode(args.profile_decode)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -108,6 +108,11 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&p);
+}
+
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 bytes
 // apart, 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
@@ -126,51 +131,34 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
 }
 
 template <int BN> struct TileCfg {
-    static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 4 : 4);
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int STAGES = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256;
 };
 
-template <typename O>
-__device__ __forceinline__ void store_chunk(O* __restrict__ crow, const float* v, int n_valid,
-                                            bool vec_ok);
-template <>
-__device__ __forceinline__ void store_chunk<float>(float* __restrict__ crow, const float* v,
-                                                   int n_valid, bool vec_ok) {
-    if (vec_ok && n_valid == 32) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<float4*>(crow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-    } else {
-        for (int j = 0; j < n_valid; ++j) crow[j] = v[j];
-    }
-}
-template <>
-__device__ __forceinline__ void store_chunk<__nv_bfloat16>(__nv_bfloat16* __restrict__ crow,
-                                                           const float* v, int n_valid,
-                                                           bool vec_ok) {
-    if (vec_ok && n_valid == 32) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-            __nv_bfloat162 p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-            __nv_bfloat162 p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-            uint4 u;
-            u.x = *reinterpret_cast<uint32_t*>(&p0);
-            u.y = *reinterpret_cast<uint32_t*>(&p1);
-            u.z = *reinterpret_cast<uint32_t*>(&p2);
-            u.w = *reinterpret_cast<uint32_t*>(&p3);
-            *reinterpret_cast<uint4*>(crow + j) = u;
-        }
-    } else {
-        for (int j = 0; j < n_valid; ++j) crow[j] = __float2bfloat16_rn(v[j]);
-    }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// tanh-form GELU as u * sigmoid(2z), z = sqrt(2/pi) (u + 0.044715 u^3): no cancellation in
+// the negative tail, relative error of the fast exp and divide about 1e-6.
+__device__ __forceinline__ float gelu_tanh_fast(float u) {
+    const float z2 = 1.5957691216057308f * (u + 0.044715f * u * u * u);   // 2z
+    return __fdividef(u, 1.0f + __expf(-z2));
+}
+__device__ __forceinline__ float epilogue_act(float x, int act) {
+    if (act == PRB_ACT_GELU_TANH) return gelu_tanh_fast(x);
+    if (act == PRB_ACT_NONE) return x;
+    return prb_activate(x, act);
+}
+
+// Persistent kernel: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (tiles
+// that share a W tile are neighbours, so they run at the same time and share it in L2).
+// The producer runs ahead across tile borders; the accumulator alternates between two
+// TMEM buffers, so the epilogue of one tile overlaps the main loop of the next.
 template <int BN, typename O>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -183,14 +171,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles = smem;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
-    uint64_t* full_bar = bars;                       // [STAGES]
-    uint64_t* empty_bar = bars + Cfg::STAGES;        // [STAGES]
-    uint64_t* tmem_full_bar = bars + 2 * Cfg::STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::STAGES + 1);
+    uint64_t* full_bar = bars;                       // [STAGES]  TMA -> MMA
+    uint64_t* empty_bar = bars + Cfg::STAGES;        // [STAGES]  MMA -> TMA
+    uint64_t* tfull_bar = bars + 2 * Cfg::STAGES;    // [2]       MMA -> epilogue
+    uint64_t* tempty_bar = tfull_bar + 2;            // [2]       epilogue -> MMA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int m_tiles = (m + BM - 1) / BM, n_tiles = (n + BN - 1) / BN;
+    const int total_tiles = m_tiles * n_tiles;
     const int k_blocks = (k + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -198,7 +188,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
-        mbar_init(smem_u32(tmem_full_bar), 1);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&tfull_bar[a]), 1);
+            mbar_init(smem_u32(&tempty_bar[a]), 4);      // one arrival per epilogue warp
+        }
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -218,30 +211,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            int armed = 0;
+            int it = 0;                               // k-blocks issued so far, over all tiles
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % Cfg::STAGES;
-                const uint32_t parity = ((kb / Cfg::STAGES) & 1) ^ 1;
-                ok = mbar_wait(smem_u32(&empty_bar[s]), parity, failed);
-                if (!ok) {
-                    prb_set_status(status, PRB_S_WAIT_TIMEOUT, 1, blockIdx.x, kb);
-                    break;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % Cfg::STAGES;
+                    ok = mbar_wait(smem_u32(&empty_bar[s]), ((it / Cfg::STAGES) & 1) ^ 1, failed);
+                    if (!ok) {
+                        prb_set_status(status, PRB_S_WAIT_TIMEOUT, 1, blockIdx.x, it);
+                        break;
+                    }
+                    const uint32_t fb = smem_u32(&full_bar[s]);
+                    mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+                    uint8_t* stage = tiles + (size_t)s * Cfg::STAGE_BYTES;
+                    tma_load_2d(smem_u32(stage), &map_a, fb, kb * BK, m0);
+                    tma_load_2d(smem_u32(stage + Cfg::A_BYTES), &map_w, fb, kb * BK, n0);
                 }
-                const uint32_t fb = smem_u32(&full_bar[s]);
-                mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-                uint8_t* stage = tiles + (size_t)s * Cfg::STAGE_BYTES;
-                tma_load_2d(smem_u32(stage), &map_a, fb, kb * BK, m0);
-                tma_load_2d(smem_u32(stage + Cfg::A_BYTES), &map_w, fb, kb * BK, n0);
-                armed = kb + 1;
             }
             if (!ok) {
                 // wait (bounded) for loads still in flight before the CTA may exit
-                const int first = armed > Cfg::STAGES ? armed - Cfg::STAGES : 0;
-                for (int kb = first; kb < armed; ++kb) {
-                    const uint32_t fb = smem_u32(&full_bar[kb % Cfg::STAGES]);
+                const int first = it > Cfg::STAGES ? it - Cfg::STAGES : 0;
+                for (int j = first; j < it; ++j) {
+                    const uint32_t fb = smem_u32(&full_bar[j % Cfg::STAGES]);
                     for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-                        if (mbar_try_wait(fb, (kb / Cfg::STAGES) & 1)) break;
+                        if (mbar_try_wait(fb, (j / Cfg::STAGES) & 1)) break;
                 }
             }
         }
@@ -249,73 +243,116 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ---------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(BM, BN);
+            int it = 0, local = 0;
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % Cfg::STAGES;
-                ok = mbar_wait(smem_u32(&full_bar[s]), (kb / Cfg::STAGES) & 1, failed);
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+                const int acc = local & 1;
+                // the epilogue must have drained this accumulator (two tiles ago)
+                ok = mbar_wait(smem_u32(&tempty_bar[acc]), ((local >> 1) & 1) ^ 1, failed);
                 if (!ok) {
-                    prb_set_status(status, PRB_S_WAIT_TIMEOUT, 2, blockIdx.x, kb);
+                    prb_set_status(status, PRB_S_WAIT_TIMEOUT, 4, blockIdx.x, local);
                     break;
                 }
                 tcgen05_fence_after();
-                const uint32_t a_addr = smem_u32(tiles + (size_t)s * Cfg::STAGE_BYTES);
-                const uint32_t b_addr = a_addr + Cfg::A_BYTES;
-                const uint64_t a_desc = make_smem_desc(a_addr);
-                const uint64_t b_desc = make_smem_desc(b_addr);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % Cfg::STAGES;
+                    ok = mbar_wait(smem_u32(&full_bar[s]), (it / Cfg::STAGES) & 1, failed);
+                    if (!ok) {
+                        prb_set_status(status, PRB_S_WAIT_TIMEOUT, 2, blockIdx.x, it);
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * Cfg::STAGE_BYTES);
+                    const uint64_t a_desc = make_smem_desc(a_addr);
+                    const uint64_t b_desc = make_smem_desc(a_addr + Cfg::A_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                    // advance 16 elements = 32 bytes inside the swizzle atom: +2 in 16-byte units
-                    umma_bf16(tmem_base, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2),
-                              idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        // 16 elements = 32 bytes further inside the swizzle atom: +2 (16-byte units)
+                        umma_bf16(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2),
+                                  idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&empty_bar[s]));   // frees the stage when the MMAs retire
                 }
-                umma_commit(smem_u32(&empty_bar[s]));      // frees the stage when the MMAs retire
+                if (ok) umma_commit(smem_u32(&tfull_bar[acc]));   // accumulator complete
             }
-            if (ok) umma_commit(smem_u32(tmem_full_bar));  // accumulator complete
         }
     } else {
         // ------------------------------------------------------------ epilogue
         const int quarter = warp & 3;                       // TMEM lanes this warp may read
-        const int row = m0 + quarter * 32 + lane;
-        bool ok = mbar_wait(smem_u32(tmem_full_bar), 0, failed);
-        if (!ok && lane == 0) prb_set_status(status, PRB_S_WAIT_TIMEOUT, 3, blockIdx.x, warp);
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (ok) {
+        const bool vec_ok = ((ldc * (long)sizeof(O)) % 16 == 0) && (((uintptr_t)c) % 16 == 0) &&
+                            (resid == nullptr ||
+                             (((ldc * 4) % 16 == 0) && (((uintptr_t)resid) % 16 == 0)));
+        int local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            const int acc = local & 1;
+            const int row = m0 + quarter * 32 + lane;
+            ok = mbar_wait(smem_u32(&tfull_bar[acc]), (local >> 1) & 1, failed);
+            if (!ok && lane == 0) prb_set_status(status, PRB_S_WAIT_TIMEOUT, 3, blockIdx.x, local);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
             tcgen05_fence_after();
-            const bool vec_ok = ((ldc * (long)sizeof(O)) % 16 == 0) &&
-                                (((uintptr_t)c) % 16 == 0) &&
-                                (resid == nullptr ||
-                                 (((ldc * 4) % 16 == 0) && (((uintptr_t)resid) % 16 == 0)));
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 if (n0 + c0 >= n) break;                    // uniform across the warp
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
-                if (row < m) {
-                    const int ncol = n0 + c0;
-                    const int n_valid = (n - ncol) < 32 ? (n - ncol) : 32;
-                    float v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                                  (uint32_t)(acc * BN + c0), r);
+                if (c0 + 32 >= BN || n0 + c0 + 32 >= n) {
+                    // last read of this accumulator: hand it back before the stores
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+                }
+                if (row >= m) continue;
+                const int ncol = n0 + c0;
+                const int n_valid = (n - ncol) < 32 ? (n - ncol) : 32;
+                O* crow = c + (size_t)row * ldc + ncol;
+                const float* rrow = resid ? resid + (size_t)row * ldc + ncol : nullptr;
+                if (vec_ok && n_valid == 32) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                        if (bias) {
+                            const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + ncol + j));
+                            const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + ncol + j + 4));
+                            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                        }
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[e] = epilogue_act(v[e], act);
+                        if (rrow) {
+                            const float4 q0 = *reinterpret_cast<const float4*>(rrow + j);
+                            const float4 q1 = *reinterpret_cast<const float4*>(rrow + j + 4);
+                            v[0] += q0.x; v[1] += q0.y; v[2] += q0.z; v[3] += q0.w;
+                            v[4] += q1.x; v[5] += q1.y; v[6] += q1.z; v[7] += q1.w;
+                        }
+                        if constexpr (sizeof(O) == 4) {
+                            *reinterpret_cast<float4*>(crow + j) = make_float4(v[0], v[1], v[2], v[3]);
+                            *reinterpret_cast<float4*>(crow + j + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                        } else {
+                            uint4 u;
+                            u.x = pack2(v[0], v[1]); u.y = pack2(v[2], v[3]);
+                            u.z = pack2(v[4], v[5]); u.w = pack2(v[6], v[7]);
+                            *reinterpret_cast<uint4*>(crow + j) = u;
+                        }
+                    }
+                } else {
+                    // tail columns or unaligned rows (e.g. a vocabulary that is odd): one by one
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        float x = __uint_as_float(r[j]);
                         if (j < n_valid) {
+                            float x = __uint_as_float(r[j]);
                             if (bias) x += __ldg(bias + ncol + j);
-                            x = prb_activate(x, act);
-                        }
-                        v[j] = x;
-                    }
-                    if (resid) {
-                        const float* rr = resid + (size_t)row * ldc + ncol;
-                        if (vec_ok && n_valid == 32) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                const float4 q = *reinterpret_cast<const float4*>(rr + j);
-                                v[j] += q.x; v[j + 1] += q.y; v[j + 2] += q.z; v[j + 3] += q.w;
-                            }
-                        } else {
-                            for (int j = 0; j < n_valid; ++j) v[j] += rr[j];
+                            x = epilogue_act(x, act);
+                            if (rrow) x += rrow[j];
+                            crow[j] = prb_from_float<O>(x);
                         }
                     }
-                    store_chunk<O>(c + (size_t)row * ldc + ncol, v, n_valid, vec_ok);
                 }
             }
         }
@@ -406,7 +443,16 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, O* c, const float* bias
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            sm_count <= 0)
+            sm_count = 148;
+    }
+    const long tiles = (long)((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+    const int grid = (int)(tiles < sm_count ? tiles : sm_count);
     gemm_bf16_kernel<BN, O><<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(ma, mw, c, bias, resid, m,
                                                                        n, k, ldc, act, status);
     PRB_LAUNCH_CHECK();
@@ -424,14 +470,16 @@ PRB_API int prb_gemm_bf16(void* c, const void* a, const void* w, const float* bi
     if (k % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)a) % 16 != 0 ||
         ((uintptr_t)w) % 16 != 0)
         return PRB_E_ALIGN;
-    if ((m + BM - 1) / BM > 65535) return PRB_E_SIZE;
     if (tile_n == 0) {
-        // enough CTAs to fill 148 SMs where the problem allows it
+        // fewest rounds of tiles over the SMs, weighted by tile width plus a fixed cost
         const long mt = (m + BM - 1) / BM;
-        if (mt * ((n + 255) / 256) >= 148) tile_n = 256;
-        else if (mt * ((n + 127) / 128) >= 120) tile_n = 128;
-        else if (mt * ((n + 63) / 64) >= 100) tile_n = 64;
-        else tile_n = 32;
+        long best = -1;
+        for (int bn = 256; bn >= 32; bn /= 2) {
+            const long tiles = mt * ((n + bn - 1) / bn);
+            const long rounds = (tiles + 147) / 148;
+            const long cost = rounds * (bn + 64);
+            if (best < 0 || cost < best) { best = cost; tile_n = bn; }
+        }
     }
     if (tile_n != 32 && tile_n != 64 && tile_n != 128 && tile_n != 256) return PRB_E_ARG;
     CUtensorMap ma, mw;
