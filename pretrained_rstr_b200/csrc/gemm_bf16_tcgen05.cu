@@ -5,13 +5,16 @@
 // A and W are bfloat16 with K contiguous ("K-major"), accumulation is float32 in tensor
 // memory (TMEM), C is bfloat16 or float32, bias and resid are float32.
 //
-// One CTA computes one 128 x BN tile of C.  Warp roles:
+// Persistent CTAs (one per SM) walk 128 x BN tiles of C; the accumulator alternates
+// between two TMEM buffers so that a tile's epilogue overlaps the next tile's main loop.
+// Warp roles:
 //   warp 0  producer: one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
 //           of a 128 x 64 tile of A and a BN x 64 tile of W per pipeline stage;
 //   warp 1  allocates TMEM; one thread issues tcgen05.mma (M=128, N=BN, K=16, four per
 //           stage) and commits each stage back to the producer through an mbarrier;
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (one row per thread), add bias,
-//           apply the activation, add the residual, store.
+//   warps 2-9  epilogue: tcgen05.ld the accumulator (one row per thread, two warps per
+//           32-lane quarter taking alternate 32-column chunks), add bias, apply the
+//           activation, add the residual, store.
 // Rows of A beyond M, rows of W beyond N and the K tail are zero-filled by TMA; stores
 // are masked.  K and the row pitches must be multiples of 8 elements (TMA needs 16-byte
 // strides); other sizes are refused with PRB_E_ALIGN, never computed wrongly.
@@ -31,7 +34,7 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;             // 64 bf16 = 128 bytes = one swizzle atom row
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;     // producer warp, MMA warp, 8 epilogue warps
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -190,7 +193,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&tfull_bar[a]), 1);
-            mbar_init(smem_u32(&tempty_bar[a]), 4);      // one arrival per epilogue warp
+            mbar_init(smem_u32(&tempty_bar[a]), 8);      // one arrival per epilogue warp
         }
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -280,6 +283,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else {
         // ------------------------------------------------------------ epilogue
         const int quarter = warp & 3;                       // TMEM lanes this warp may read
+        const int half = (warp - 2) >> 2;                   // two warps share a quarter: even / odd chunks
         const bool vec_ok = ((ldc * (long)sizeof(O)) % 16 == 0) && (((uintptr_t)c) % 16 == 0) &&
                             (resid == nullptr ||
                              (((ldc * 4) % 16 == 0) && (((uintptr_t)resid) % 16 == 0)));
@@ -294,14 +298,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             tcgen05_fence_after();
+            if (half * 32 >= BN || n0 + half * 32 >= n) {      // nothing to read for this warp
+                if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+                continue;
+            }
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = half * 32; c0 < BN; c0 += 64) {
                 if (n0 + c0 >= n) break;                    // uniform across the warp
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) +
                                   (uint32_t)(acc * BN + c0), r);
-                if (c0 + 32 >= BN || n0 + c0 + 32 >= n) {
-                    // last read of this accumulator: hand it back before the stores
+                if (c0 + 64 >= BN || n0 + c0 + 64 >= n) {
+                    // this warp's last read of the accumulator: hand it back before the stores
                     tcgen05_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
