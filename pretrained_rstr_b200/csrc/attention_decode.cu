@@ -52,6 +52,8 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
     __shared__ int sh_last;
     __shared__ int sh_pages[SPLIT / 8];          // pages of this split (page_size >= 8)
 
+    prb_grid_launch_dependents();
+    prb_grid_wait();
     const int idx = blockIdx.x;
     if (token_count != nullptr && idx >= *token_count) return;
     const int t = token_list ? token_list[idx] : idx;
@@ -253,18 +255,19 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
     dim3 grid(n_list, n_heads, max_splits);
     const int pieces = head_dim / 8;
 #define PRB_DEC(L)                                                                             \
-    attention_decode_kernel<L><<<grid, DEC_THREADS, 0, stream>>>(                              \
+    e = prb_launch_dependent(attention_decode_kernel<L>, grid, dim3(DEC_THREADS), 0, stream,   \
         (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,                    \
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,             \
         seq_of_token, positions, token_list, token_count, n_heads, kv_heads, head_dim,         \
         page_size, max_pages, num_pages, scale, window, workspace, counters, max_splits, status)
+    cudaError_t e;
     if (pieces <= 2) PRB_DEC(2);
     else if (pieces <= 4) PRB_DEC(4);
     else if (pieces <= 8) PRB_DEC(8);
     else if (pieces <= 16) PRB_DEC(16);
     else PRB_DEC(32);
 #undef PRB_DEC
-    PRB_LAUNCH_CHECK();
+    if (e != cudaSuccess) return (int)e;
     return 0;
 }
 

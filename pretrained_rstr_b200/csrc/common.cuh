@@ -108,6 +108,36 @@ __device__ __forceinline__ float prb_activate(float u, int act) {
     }
 }
 
+// Programmatic dependent launch.  A kernel launched with prb_launch_dependent may start
+// while its predecessor in the stream is still running; everything it does before
+// prb_grid_wait() must not depend on the predecessor (prefetching weights, reading the
+// step's metadata).  Every thread calls prb_grid_wait() before it reads or writes
+// anything another kernel of the step produces or consumes, and before it exits, so
+// that completion of a kernel implies completion of all kernels before it.
+__device__ __forceinline__ void prb_grid_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void prb_grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+int prb_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t prb_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                        size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = prb_pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 #define PRB_LAUNCH_CHECK()                               \
     do {                                                 \
         cudaError_t e__ = cudaGetLastError();            \

@@ -3,6 +3,11 @@
 // 32-bit; element types of tables, activations and the cache are template parameters.
 #include "common.cuh"
 
+// Programmatic dependent launch is on unless switched off (for measurements).
+static int g_pdl = 1;
+int prb_pdl_enabled() { return g_pdl; }
+PRB_API void prb_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+
 // ------------------------------------------------------------------ embedding
 // x[t,:] = wte[token[t],:] (+ wpe[position[t],:])          (gpt2.clj:49-62)
 template <typename W>
@@ -170,6 +175,8 @@ __global__ void kv_append_kernel(T* __restrict__ k_pages, T* __restrict__ v_page
                                  long src_stride, const int* __restrict__ slots, int n_tokens,
                                  int kv_heads, int head_dim, int page_size, int num_pages,
                                  int* status) {
+    prb_grid_launch_dependents();
+    prb_grid_wait();
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
     const int slot = slots[t];
@@ -196,18 +203,21 @@ PRB_API int prb_kv_append(void* k_pages, void* v_pages, const void* k_src, const
     if (kv_heads <= 0 || head_dim <= 0 || page_size <= 0) return PRB_E_SIZE;
     const int row = kv_heads * head_dim;
     const int threads = row >= 256 ? 256 : ((row + 31) / 32) * 32;
+    cudaError_t e;
     if (dtype == PRB_F32)
-        kv_append_kernel<float><<<n_tokens, threads, 0, stream>>>(
-            (float*)k_pages, (float*)v_pages, (const float*)k_src, (const float*)v_src, src_stride,
-            slots, n_tokens, kv_heads, head_dim, page_size, num_pages, status);
+        e = prb_launch_dependent(kv_append_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream,
+                                 (float*)k_pages, (float*)v_pages, (const float*)k_src,
+                                 (const float*)v_src, src_stride, slots, n_tokens, kv_heads,
+                                 head_dim, page_size, num_pages, status);
     else if (dtype == PRB_BF16)
-        kv_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, (const __nv_bfloat16*)k_src,
-            (const __nv_bfloat16*)v_src, src_stride, slots, n_tokens, kv_heads, head_dim,
-            page_size, num_pages, status);
+        e = prb_launch_dependent(kv_append_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0,
+                                 stream, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
+                                 (const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src,
+                                 src_stride, slots, n_tokens, kv_heads, head_dim, page_size,
+                                 num_pages, status);
     else
         return PRB_E_DTYPE;
-    PRB_LAUNCH_CHECK();
+    if (e != cudaSuccess) return (int)e;
     return 0;
 }
 

@@ -56,6 +56,7 @@ gemm_smallm_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ x,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;        // MMA group (row / token) and quad index
     const int n0 = blockIdx.x * ROWS;
+    prb_grid_launch_dependents();                  // the next kernel may start its own prefetch
 
     // ---- stream the 16 weight rows; this warp takes k-steps warp, warp+8, ...
     // (the first loads are issued before the norm so that they overlap it)
@@ -77,6 +78,8 @@ gemm_smallm_kernel(O* __restrict__ out, const __nv_bfloat16* __restrict__ x,
         wa[p] = (ok && row0_ok) ? ldg_stream(w0 + kk) : make_uint4(0, 0, 0, 0);
         wb[p] = (ok && row1_ok) ? ldg_stream(w1 + kk) : make_uint4(0, 0, 0, 0);
     }
+    // The weights above do not depend on the previous kernel; everything below does.
+    prb_grid_wait();
     if constexpr (LN) {
         // ---- fused LayerNorm of the M rows into shared memory (bfloat16)
         const int nvec = k / 4;                   // float4 per row
@@ -205,9 +208,10 @@ int launch_smallm(O* out, const __nv_bfloat16* x, const float* xf, const float* 
         configured = smem;
     }
     const int grid = (n + ROWS - 1) / ROWS;
-    gemm_smallm_kernel<MT, LN, O><<<grid, SM_THREADS, smem, stream>>>(
-        out, x, xf, gamma, beta, eps, w, bias, resid, m, n, k, ldx, ldw, ldc, act, pitch);
-    PRB_LAUNCH_CHECK();
+    cudaError_t e = prb_launch_dependent(gemm_smallm_kernel<MT, LN, O>, dim3(grid),
+                                         dim3(SM_THREADS), smem, stream, out, x, xf, gamma, beta,
+                                         eps, w, bias, resid, m, n, k, ldx, ldw, ldc, act, pitch);
+    if (e != cudaSuccess) return (int)e;
     return 0;
 }
 
