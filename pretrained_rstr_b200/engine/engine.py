@@ -97,8 +97,9 @@ class Engine:
             if wants:
                 samplers.append(self.scheduler.running[item.rid])
         if self.timing_events is not None:
-            self.timing_events[0][self.step_index].record()
+            self.runner.start_event = self.timing_events[0][self.step_index]
         logits = self.runner.step(entries)
+        self.runner.start_event = None
         new_tokens: Dict[Hashable, int] = {}
         if samplers:
             chosen = self._choose(logits, samplers)

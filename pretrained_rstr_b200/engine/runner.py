@@ -70,6 +70,7 @@ class ModelRunner:
         self.fail_next_step: Optional[Exception] = None      # host-side fault injection (tests)
         self.counters = {"steps": 0, "tokens": 0, "cow_copies": 0}
         self.last_h2d_bytes = 0
+        self.start_event = None                       # optional CUDA event recorded before the copy
 
     # ------------------------------------------------------------------ layout
     def layout_for(self, n_tokens: int, n_requests: int) -> BatchLayout:
@@ -195,6 +196,8 @@ class ModelRunner:
         staging = self._hosts[turn]
         n_tiles, n_singles = fill_host_buffer(staging.numpy(), layout, [list(e.tokens) for e in entries], start_pos,
                          state_slots, fresh, group_slots, group_tables, group_first, logit_rows)
+        if self.start_event is not None:             # measurement: device work of the step begins
+            self.start_event.record()
         self._dev[:layout.size].copy_(staging[:layout.size], non_blocking=True)
         self._host_events[turn].record()
         self.last_h2d_bytes = layout.size * 4
