@@ -14,220 +14,20 @@
 //
 // Scratch: workspace [tokens, heads, max_splits, head_dim + 2] float32 and counters
 // [tokens * heads] int32 (zero before the first launch; the kernel leaves them zero).
-#include "common.cuh"
+#include "attention_decode.cuh"
 
 namespace {
+using namespace decode_attn;
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
-constexpr int SPLIT = 128;          // keys per split
-constexpr int MAX_DH = 256;
-
-__device__ __forceinline__ float dot8(const uint4& a, const float* q) {
-    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&a);
-    float s = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(p[i]);
-        s = fmaf(f.x, q[2 * i], s);
-        s = fmaf(f.y, q[2 * i + 1], s);
-    }
-    return s;
-}
 
 template <int LPK>   // lanes per key row: 2, 4, 8, 16 or 32 (head_dim <= 8 * LPK)
 __global__ void __launch_bounds__(DEC_THREADS)
-attention_decode_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
-                        const __nv_bfloat16* __restrict__ q, long q_stride,
-                        const __nv_bfloat16* __restrict__ k_pages,
-                        const __nv_bfloat16* __restrict__ v_pages,
-                        const int* __restrict__ block_table, const int* __restrict__ seq_of_token,
-                        const int* __restrict__ positions, const int* __restrict__ token_list,
-                        const int* __restrict__ token_count, int n_heads, int kv_heads,
-                        int head_dim, int page_size, int max_pages, int num_pages, float scale,
-                        int window, float* __restrict__ workspace, int* __restrict__ counters,
-                        int max_splits, int* status) {
-    constexpr int KPW = 32 / LPK;                 // keys per warp per load
-    __shared__ float sh_m[DEC_WARPS], sh_l[DEC_WARPS];
-    __shared__ float sh_o[DEC_WARPS][MAX_DH];
-    __shared__ int sh_last;
-    __shared__ int sh_pages[SPLIT / 8];          // pages of this split (page_size >= 8)
-
+attention_decode_kernel(Args a) {
+    __shared__ Shared<DEC_WARPS> sh;
     prb_grid_launch_dependents();
     prb_grid_wait();
-    const int idx = blockIdx.x;
-    if (token_count != nullptr && idx >= *token_count) return;
-    const int t = token_list ? token_list[idx] : idx;
-    const int h = blockIdx.y, s = blockIdx.z;
-    const int b = seq_of_token[t];
-    if (b < 0) return;
-    const int pos = positions[t];
-    if (pos < 0 || pos >= max_pages * page_size) {
-        if (threadIdx.x == 0 && s == 0) prb_set_status(status, PRB_S_POSITION_RANGE, t, pos, 0);
-        return;
-    }
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int s_first = lo / SPLIT, s_last = pos / SPLIT;
-    if (s_last >= max_splits) {                   // the launch does not cover this context
-        if (threadIdx.x == 0 && s == 0) prb_set_status(status, PRB_S_POSITION_RANGE, t, pos, max_splits);
-        return;
-    }
-    if (s < s_first || s > s_last) return;
-    const int n_splits = s_last - s_first + 1;
-    const int k_begin = max(lo, s * SPLIT), k_end = min(pos + 1, (s + 1) * SPLIT);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int sub = lane % LPK;                   // which 16-byte piece of the row
-    const int kslot = lane / LPK;                 // which key of the warp's load
-    const int hk = h / (n_heads / kv_heads);
-    const int* table = block_table + (size_t)b * max_pages;
-    const bool piece_ok = sub * 8 < head_dim;
-
-    // this lane's 8 query dims; scores are (q . k) * scale as in the formula
-    float qf[8];
-    {
-        const __nv_bfloat16* qp = q + (size_t)t * q_stride + (size_t)h * head_dim + sub * 8;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) qf[i] = piece_ok ? __bfloat162float(qp[i]) : 0.0f;
-    }
-    float m = -INFINITY, l = 0.0f;
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-
-    // page ids of this split, once
-    const int first_page = (s * SPLIT) / page_size;
-    for (int i = threadIdx.x; i < SPLIT / page_size; i += DEC_THREADS)
-        sh_pages[i] = (first_page + i < max_pages) ? table[first_page + i] : -1;
-    __syncthreads();
-
-    // keys k_begin + warp*KPW + kslot, stepping DEC_WARPS*KPW; UNROLL steps' loads are
-    // issued before any of them is used
-    constexpr int UNROLL = 8;
-    for (int base = k_begin + warp * KPW; base < k_end; base += DEC_WARPS * KPW * UNROLL) {
-        uint4 kraw[UNROLL], vraw[UNROLL];
-        bool ok[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int j = base + u * DEC_WARPS * KPW + kslot;
-            ok[u] = false;
-            kraw[u] = make_uint4(0, 0, 0, 0);
-            vraw[u] = make_uint4(0, 0, 0, 0);
-            if (j < k_end) {
-                const int page = sh_pages[j / page_size - first_page];
-                if (page < 0 || page >= num_pages) {
-                    prb_set_status(status, PRB_S_PAGE_RANGE, t, j, page);
-                } else {
-                    ok[u] = true;
-                    if (piece_ok) {
-                        const size_t row =
-                            (((size_t)page * kv_heads + hk) * page_size + (j % page_size)) *
-                                head_dim + sub * 8;
-                        kraw[u] = *reinterpret_cast<const uint4*>(k_pages + row);
-                        vraw[u] = *reinterpret_cast<const uint4*>(v_pages + row);
-                    }
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            float part = dot8(kraw[u], qf);
-            // every lane takes part in the reduction over the LPK pieces of a key row
-#pragma unroll
-            for (int o = LPK / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            const float sc = ok[u] ? part * scale : -INFINITY;
-            // online softmax per key slot (each group of LPK lanes has its own running state)
-            const float m_new = fmaxf(m, sc);
-            if (m_new > -INFINITY) {
-                const float corr = (m == -INFINITY) ? 0.0f : __expf(m - m_new);
-                const float p = (sc == -INFINITY) ? 0.0f : __expf(sc - m_new);
-                l = l * corr + p;
-                const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vraw[u]);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(vp[i]);
-                    acc[2 * i] = fmaf(p, f.x, acc[2 * i] * corr);
-                    acc[2 * i + 1] = fmaf(p, f.y, acc[2 * i + 1] * corr);
-                }
-                m = m_new;
-            }
-        }
-    }
-    // merge the KPW key slots of the warp (fixed butterfly order)
-#pragma unroll
-    for (int o = LPK; o < 32; o <<= 1) {
-        const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
-        const float l2 = __shfl_xor_sync(0xffffffffu, l, o);
-        const float mn = fmaxf(m, m2);
-        const float c1 = (m == -INFINITY) ? 0.0f : __expf(m - mn);
-        const float c2 = (m2 == -INFINITY) ? 0.0f : __expf(m2 - mn);
-        l = l * c1 + l2 * c2;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float a2 = __shfl_xor_sync(0xffffffffu, acc[i], o);
-            acc[i] = acc[i] * c1 + a2 * c2;
-        }
-        m = mn;
-    }
-    if (kslot == 0 && piece_ok) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sh_o[warp][sub * 8 + i] = acc[i];
-    }
-    if (lane == 0) { sh_m[warp] = m; sh_l[warp] = l; }
-    __syncthreads();
-
-    // merge warps in order 0..3; thread d owns output dimension d (and d + 128)
-    float mt = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) mt = fmaxf(mt, sh_m[w]);
-    float lt = 0.0f;
-    float cw[DEC_WARPS];
-#pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) {
-        cw[w] = (sh_m[w] == -INFINITY) ? 0.0f : __expf(sh_m[w] - mt);
-        lt += sh_l[w] * cw[w];
-    }
-    const size_t pair = (size_t)idx * n_heads + h;       // scratch is indexed by list place
-    float* ws = workspace + (pair * max_splits + s) * (size_t)(head_dim + 2);
-    __nv_bfloat16* o = out + (size_t)t * out_stride + (size_t)h * head_dim;
-    for (int d = threadIdx.x; d < head_dim; d += DEC_THREADS) {
-        float od = 0.0f;
-#pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) od += sh_o[w][d] * cw[w];
-        if (n_splits == 1) o[d] = __float2bfloat16_rn(lt > 0.0f ? od / lt : 0.0f);
-        else ws[d] = od;
-    }
-    if (n_splits == 1) return;
-    if (threadIdx.x == 0) { ws[head_dim] = mt; ws[head_dim + 1] = lt; }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int done = atomicAdd(&counters[pair], 1);
-        sh_last = (done == n_splits - 1) ? 1 : 0;
-    }
-    __syncthreads();
-    if (!sh_last) return;
-    __threadfence();
-    // last CTA of this (token, head): merge the splits in order
-    const float* wbase = workspace + pair * max_splits * (size_t)(head_dim + 2);
-    float mg = -INFINITY;
-    for (int ss = s_first; ss <= s_last; ++ss)
-        mg = fmaxf(mg, __ldcg(wbase + (size_t)ss * (head_dim + 2) + head_dim));
-    float lg = 0.0f;
-    for (int ss = s_first; ss <= s_last; ++ss) {
-        const float* w = wbase + (size_t)ss * (head_dim + 2);
-        const float ms = __ldcg(w + head_dim);
-        lg += __ldcg(w + head_dim + 1) * ((ms == -INFINITY) ? 0.0f : __expf(ms - mg));
-    }
-    for (int d = threadIdx.x; d < head_dim; d += DEC_THREADS) {
-        float od = 0.0f;
-        for (int ss = s_first; ss <= s_last; ++ss) {
-            const float* w = wbase + (size_t)ss * (head_dim + 2);
-            const float ms = __ldcg(w + head_dim);
-            od += __ldcg(w + d) * ((ms == -INFINITY) ? 0.0f : __expf(ms - mg));
-        }
-        o[d] = __float2bfloat16_rn(lg > 0.0f ? od / lg : 0.0f);
-    }
-    if (threadIdx.x == 0) counters[pair] = 0;
+    unit<LPK, DEC_WARPS>(a, blockIdx.x, blockIdx.y, blockIdx.z, sh);
 }
 }  // namespace
 
@@ -254,12 +54,17 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
         return PRB_E_ALIGN;
     dim3 grid(n_list, n_heads, max_splits);
     const int pieces = head_dim / 8;
-#define PRB_DEC(L)                                                                             \
-    e = prb_launch_dependent(attention_decode_kernel<L>, grid, dim3(DEC_THREADS), 0, stream,   \
-        (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,                    \
-        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,             \
-        seq_of_token, positions, token_list, token_count, n_heads, kv_heads, head_dim,         \
-        page_size, max_pages, num_pages, scale, window, workspace, counters, max_splits, status)
+    Args a;
+    a.out = (__nv_bfloat16*)out; a.out_stride = out_stride;
+    a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride;
+    a.k_pages = (const __nv_bfloat16*)k_pages; a.v_pages = (const __nv_bfloat16*)v_pages;
+    a.block_table = block_table; a.seq_of_token = seq_of_token; a.positions = positions;
+    a.token_list = token_list; a.token_count = token_count;
+    a.n_heads = n_heads; a.kv_heads = kv_heads; a.head_dim = head_dim; a.page_size = page_size;
+    a.max_pages = max_pages; a.num_pages = num_pages; a.scale = scale; a.window = window;
+    a.workspace = workspace; a.counters = counters; a.max_splits = max_splits; a.status = status;
+#define PRB_DEC(L) \
+    e = prb_launch_dependent(attention_decode_kernel<L>, grid, dim3(DEC_THREADS), 0, stream, a)
     cudaError_t e;
     if (pieces <= 2) PRB_DEC(2);
     else if (pieces <= 4) PRB_DEC(4);

@@ -92,13 +92,32 @@ def _declare(h: ctypes.CDLL) -> None:
                                         I, P, P]
     h.prb_attention_prefill_supports.argtypes = [I]
     h.prb_attention_decode_split.argtypes = []
+    h.prb_program_new.argtypes = [I]
+    h.prb_program_new.restype = P
+    h.prb_program_free.argtypes = [P]
+    h.prb_program_free.restype = None
+    h.prb_program_length.argtypes = [P]
+    h.prb_program_bytes.argtypes = [P]
+    h.prb_program_bytes.restype = L
+    h.prb_program_add_embed.argtypes = [P, P, P, P, P, P, I, I, I, I, I, P]
+    h.prb_program_add_norm.argtypes = [P, P, P, P, P, P, I, I, I, F, I, P]
+    h.prb_program_add_gemm.argtypes = [P, P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I]
+    h.prb_program_add_append.argtypes = [P, P, P, P, P, L, P, I, I, I, I, I, I, P]
+    h.prb_program_add_attention.argtypes = [P, P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I,
+                                            I, F, I, P, P, I, P]
+    h.prb_program_upload.argtypes = [P, P, P]
+    h.prb_program_run.argtypes = [P, P, P, P, P]
+    h.prb_set_pdl.argtypes = [I]
+    h.prb_set_pdl.restype = None
     h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
     h.prb_sample_max_top_k.argtypes = []
     for name in ("prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
                  "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_smallm", "prb_gemm_smallm_max_rows",
                  "prb_gemm_smallm_max_norm_width", "prb_attention_generic", "prb_attention_decode",
                  "prb_attention_prefill", "prb_attention_prefill_supports",
-                 "prb_attention_decode_split", "prb_sample", "prb_sample_max_top_k"):
+                 "prb_attention_decode_split", "prb_program_length", "prb_program_add_embed",
+                 "prb_program_add_norm", "prb_program_add_gemm", "prb_program_add_append",
+                 "prb_program_add_attention", "prb_program_upload", "prb_program_run", "prb_sample", "prb_sample_max_top_k"):
         getattr(h, name).restype = c_int
 
 
@@ -146,6 +165,69 @@ def _need(t: torch.Tensor, dtype, name: str, what: str) -> None:
         raise KernelArgumentError(f"{what}: {name} must be contiguous")
 
 
+# ---------------------------------------------------------------------- programs
+class NotRecordable(RuntimeError):
+    """An operation that a decode program cannot hold was called while recording."""
+
+
+_RECORDER = None
+
+
+class Program:
+    """The operations of one decode step, recorded once and run as a single persistent
+    kernel (``csrc/decode_program.cu``).  While a program records (``with program:``) the
+    wrappers below that it can hold (embed, layernorm, gemm_smallm, kv_append,
+    attention_decode) append an operation instead of launching; any other wrapper raises
+    :class:`NotRecordable`."""
+
+    def __init__(self, max_rows: int, device):
+        self.handle = lib().prb_program_new(int(max_rows))
+        self.device = device
+        self.ops = None                    # device copy of the operation list
+        self.barrier = torch.zeros(2, dtype=torch.int32, device=device)
+        self.length = 0
+
+    def __enter__(self):
+        global _RECORDER
+        if _RECORDER is not None:
+            raise RuntimeError("a program is already recording")
+        _RECORDER = self
+        return self
+
+    def __exit__(self, *exc):
+        global _RECORDER
+        _RECORDER = None
+        return False
+
+    def finish(self) -> None:
+        self.length = lib().prb_program_length(self.handle)
+        nbytes = lib().prb_program_bytes(self.handle)
+        self.ops = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=self.device)
+        _check(lib().prb_program_upload(self.handle, _p(self.ops), _stream()), "program upload")
+
+    def run(self, status) -> None:
+        _check(lib().prb_program_run(self.handle, _p(self.ops), _p(self.barrier), _p(status),
+                                     _stream()), "program run")
+
+    def __del__(self):
+        try:
+            if self.handle:
+                lib().prb_program_free(self.handle)
+                self.handle = None
+        except Exception:
+            pass
+
+
+def _no_record(what: str) -> None:
+    if _RECORDER is not None:
+        raise NotRecordable(what)
+
+
+def set_pdl(on: bool) -> None:
+    """Switch programmatic dependent launch of the decode-chain kernels on or off."""
+    lib().prb_set_pdl(1 if on else 0)
+
+
 # ------------------------------------------------------------------------ kernels
 def embed(out, tokens, positions, wte, wpe, status) -> None:
     """out[t,:] = wte[tokens[t],:] (+ wpe[positions[t],:]); out float32 [T, width]."""
@@ -159,6 +241,12 @@ def embed(out, tokens, positions, wte, wpe, status) -> None:
         raise KernelArgumentError(f"{what}: table widths or types differ from the output's")
     if tokens.numel() < n or positions.numel() < n:
         raise KernelArgumentError(f"{what}: fewer token ids or positions than output rows")
+    if _RECORDER is not None:
+        _check(lib().prb_program_add_embed(_RECORDER.handle, _p(out), _p(tokens), _p(positions),
+                                           _p(wte), _p(wpe), n, width, wte.shape[0],
+                                           0 if wpe is None else wpe.shape[0],
+                                           dtype_code(wte.dtype), _p(status)), what)
+        return
     _check(lib().prb_embed(_p(out), _p(tokens), _p(positions), _p(wte), _p(wpe), n, width,
                            wte.shape[0], 0 if wpe is None else wpe.shape[0],
                            dtype_code(wte.dtype), _p(status), _stream()), what)
@@ -179,6 +267,11 @@ def layernorm(out, x, gamma, beta, eps: float, rows=None, status=None) -> None:
         raise KernelArgumentError(f"{what}: fewer input rows than output rows")
     if rows is not None:
         _need(rows, torch.int32, "rows", what)
+    if _RECORDER is not None:
+        _check(lib().prb_program_add_norm(_RECORDER.handle, _p(out), _p(x), _p(gamma), _p(beta),
+                                          _p(rows), n_rows, x.shape[0], width, float(eps),
+                                          dtype_code(out.dtype), _p(status)), what)
+        return
     _check(lib().prb_layernorm(_p(out), _p(x), _p(gamma), _p(beta), _p(rows), n_rows, x.shape[0],
                                width, float(eps), dtype_code(out.dtype), _p(status), _stream()),
            what)
@@ -187,6 +280,7 @@ def layernorm(out, x, gamma, beta, eps: float, rows=None, status=None) -> None:
 def bias_act(out, inp, bias, resid, act) -> None:
     """out = act(inp + bias) (+ resid), sums in float32."""
     what = "bias_act"
+    _no_record(what)
     _need(out, None, "out", what)
     _need(inp, None, "inp", what)
     m, n = inp.shape
@@ -214,6 +308,12 @@ def kv_append(k_pages, v_pages, k_src, v_src, slots, n_tokens, status) -> None:
             raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
     if k_src.stride(0) != v_src.stride(0):
         raise KernelArgumentError(f"{what}: k_src and v_src row strides differ")
+    if _RECORDER is not None:
+        _check(lib().prb_program_add_append(_RECORDER.handle, _p(k_pages), _p(v_pages), _p(k_src),
+                                            _p(v_src), k_src.stride(0), _p(slots), n_tokens,
+                                            kv_heads, head_dim, page_size, num_pages,
+                                            dtype_code(k_pages.dtype), _p(status)), what)
+        return
     _check(lib().prb_kv_append(_p(k_pages), _p(v_pages), _p(k_src), _p(v_src), k_src.stride(0),
                                _p(slots), n_tokens, kv_heads, head_dim, page_size, num_pages,
                                dtype_code(k_pages.dtype), _p(status), _stream()), what)
@@ -222,6 +322,7 @@ def kv_append(k_pages, v_pages, k_src, v_src, slots, n_tokens, status) -> None:
 def copy_pages(storage, pairs, n_pairs, status) -> None:
     """storage: [pools, pages, ...] contiguous; pairs int32 [n, 2] (source, destination)."""
     what = "copy_pages"
+    _no_record(what)
     _need(storage, None, "storage", what)
     _need(pairs, torch.int32, "pairs", what)
     pools, pages = storage.shape[0], storage.shape[1]
@@ -233,6 +334,7 @@ def copy_pages(storage, pairs, n_pairs, status) -> None:
 def gemm_f32(out, a, w, bias=None, resid=None, act=None) -> None:
     """out[M,N] = act(a[M,K] . w[N,K]^T + bias) (+ resid): true 32-bit FMA."""
     what = "gemm_f32"
+    _no_record(what)
     for name, t in (("out", out), ("a", a), ("w", w)):
         if not t.is_cuda or t.dtype != torch.float32 or t.stride(1) != 1:
             raise KernelArgumentError(f"{what}: {name} must be float32 on CUDA with unit inner stride")
@@ -255,6 +357,7 @@ def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, statu
     bfloat16 operands, float32 accumulation in tensor memory, epilogue in float32; out is
     bfloat16 or float32.  K and the row pitches of a and w must be multiples of 8."""
     what = "gemm_bf16"
+    _no_record(what)
     for name, t in (("a", a), ("w", w)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(1) != 1:
             raise KernelArgumentError(f"{what}: {name} must be bfloat16 on CUDA with unit inner stride")
@@ -314,6 +417,13 @@ def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0,
     if resid is not None:
         if resid.dtype != torch.float32 or resid.shape != out.shape or resid.stride(0) != out.stride(0):
             raise KernelArgumentError(f"{what}: resid must be float32 with the output's shape and stride")
+    if _RECORDER is not None:
+        _check(lib().prb_program_add_gemm(
+            _RECORDER.handle, _p(out), None if norm_input is not None else _p(x),
+            _p(x) if norm_input is not None else None, _p(gamma), _p(beta), float(eps), _p(w),
+            _p(bias), _p(resid), m, n, k, x.stride(0), w.stride(0), out.stride(0), ACT_CODES[act],
+            dtype_code(out.dtype)), what)
+        return
     _check(lib().prb_gemm_smallm(
         _p(out), None if norm_input is not None else _p(x),
         _p(x) if norm_input is not None else None, _p(gamma), _p(beta), float(eps), _p(w),
@@ -326,6 +436,7 @@ def attention_generic(out, q, k_pages, v_pages, block_table, seq_of_token, posit
     """Attention of every token of the step over its request's cached keys; 32-bit
     arithmetic.  q: [T, n_heads*head_dim] (may be a column slice), out likewise."""
     what = "attention_generic"
+    _no_record(what)
     num_pages, kv_heads, page_size, head_dim = k_pages.shape
     for name, t in (("out", out), ("q", q)):
         if t.dtype != k_pages.dtype or t.stride(1) != 1 or t.shape[1] != n_heads * head_dim:
@@ -367,6 +478,14 @@ def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positi
     if workspace.dtype != torch.float32 or workspace.numel() < need or \
             counters.dtype != torch.int32 or counters.numel() < n_list * n_heads:
         raise KernelArgumentError(f"{what}: scratch too small or of the wrong type")
+    if _RECORDER is not None:
+        _check(lib().prb_program_add_attention(
+            _RECORDER.handle, _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages),
+            _p(v_pages), _p(block_table), _p(seq_of_token), _p(positions), _p(token_list),
+            _p(token_count), n_list, n_heads, kv_heads, head_dim, page_size, block_table.shape[1],
+            num_pages, float(scale), int(window or 0), _p(workspace), _p(counters), max_splits,
+            _p(status)), what)
+        return
     _check(lib().prb_attention_decode(
         _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(block_table),
         _p(seq_of_token), _p(positions), _p(token_list), _p(token_count), n_list, n_heads,
@@ -378,6 +497,7 @@ def attention_prefill(out, q, k_pages, v_pages, block_table, positions, tile_req
                       tile_rows, tile_count, n_tiles, n_heads, scale, window, status) -> None:
     """bfloat16 causal attention of prompt portions, 64 queries per tile, on tensor cores."""
     what = "attention_prefill"
+    _no_record(what)
     num_pages, kv_heads, page_size, head_dim = k_pages.shape
     for name, t in (("out", out), ("q", q)):
         if t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != n_heads * head_dim:
@@ -400,6 +520,7 @@ def sample(out, logits, n_rows, temperature=None, top_k=None, top_p=None, seeds=
     """out[r] = chosen token of logits[r,:] (float32).  Without ``temperature`` every row
     is greedy; otherwise rows with temperature <= 0 are greedy and the rest sample."""
     what = "sample"
+    _no_record(what)
     _need(out, torch.int32, "out", what)
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelArgumentError(f"{what}: logits must be float32 with unit inner stride")

@@ -62,6 +62,10 @@ class ModelRunner:
         self.graph_max_tokens = 256
         self._graphs: Dict[tuple, tuple] = {}
         self._seen: Dict[tuple, int] = {}
+        # decode programs (whole steps of single tokens as one persistent kernel), same keys
+        self.use_programs = bool(runtime.use_programs) and runtime.dtype == torch.bfloat16 and \
+            getattr(model, "graph_safe", False)
+        self._programs: Dict[tuple, object] = {}
         self._pairs_host = torch.empty((runtime.max_requests, 2), dtype=torch.int32,
                                        pin_memory=True)
         self._pairs_dev = torch.zeros((runtime.max_requests, 2), dtype=torch.int32,
@@ -106,6 +110,10 @@ class ModelRunner:
         kernel lets touch the cache.  The first step of a shape runs directly with the
         padded sizes (which also sizes all scratch memory), the second is captured."""
         lay = ctx.layout
+        if self.use_programs and ctx.n_tiles == 0 and lay.t_cap <= ops.smallm_limits()[0]:
+            logits = self._run_program(ctx)
+            if logits is not None:
+                return logits
         if not self.use_graphs or lay.t_cap > self.graph_max_tokens:
             return self.model.forward(ctx)
         rows_cap = StepContext.row_capacity(max(ctx.n_rows, 1)) if ctx.n_rows else 0
@@ -235,6 +243,34 @@ class ModelRunner:
                           max_positions=self.model.max_positions)
         ctx.n_tiles, ctx.n_singles = n_tiles, n_singles
         return ctx
+
+    def _run_program(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        """A step of single tokens only (decoding) as ONE persistent kernel: the model's
+        forward pass is recorded once per shape as a list of operations and from then on a
+        cooperative kernel interprets the list (``csrc/decode_program.cu``).  Returns None
+        when the model uses an operation a program cannot hold."""
+        lay = ctx.layout
+        rows_cap = StepContext.row_capacity(max(ctx.n_rows, 1)) if ctx.n_rows else 0
+        key = (lay.t_cap, lay.b_cap, rows_cap)
+        hit = self._programs.get(key)
+        if hit is False:
+            return None
+        ctx.launch_tokens, ctx.launch_rows = lay.t_cap, rows_cap
+        ctx.n_tiles, ctx.n_singles = 0, None        # no prompt tiles; single tokens by device count
+        ctx.max_context = self.model.max_positions
+        if hit is None:
+            program = ops.Program(lay.t_cap, self.device)
+            try:
+                with program:
+                    logits = self.model.forward(ctx)
+            except ops.NotRecordable:
+                self._programs[key] = False
+                return None
+            program.finish()
+            hit = (program, logits)
+            self._programs[key] = hit
+        hit[0].run(self.status)
+        return hit[1]
 
     def commit(self, entries: Sequence[Entry]) -> None:
         for e in entries:

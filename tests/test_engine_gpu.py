@@ -230,3 +230,31 @@ def test_trace_run_program(tmp_path, dtype):
     assert float((got1 - oracle["b"][[1]]).abs().max()) <= tol
     assert float((got2 - oracle["b"][[8]]).abs().max()) <= tol
     assert float((got7 - oracle["a"][66:70]).abs().max()) <= tol
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_decode_program_equals_kernel_by_kernel(folders, name):
+    """Decode-only steps run as one persistent kernel that interprets the recorded step;
+    the same steps launched kernel by kernel give the same logits (to rounding: the two
+    differ only in how many warps merge an attention unit), and both match the oracle."""
+    raw, seed = TINY[name]
+    folder = folders[(name, "bfloat16")]
+    prompts = {f"d{i}": random_tokens(n, raw["vocab_size"], 50 + i)
+               for i, n in enumerate([raw["n_positions"] - 5, 70, 9])}
+    oracle = oracle_logits(folder, prompts)
+    results = {}
+    for programs in (True, False):
+        rp = Replayer(folder, "bfloat16", max_tokens=512)
+        rp.lm.runner.use_programs = programs
+        rp.lm.runner.use_graphs = False
+        rp.step([(r, ids[:len(ids) - 4], [len(ids) - 5]) for r, ids in prompts.items()])
+        for k in range(4, 0, -1):
+            rp.step([(r, ids[len(ids) - k:len(ids) - k + 1], [0]) for r, ids in prompts.items()])
+        used = [v for v in rp.lm.runner._programs.values() if v]
+        assert bool(used) == programs
+        if programs:
+            assert used[0][0].length > 5 * raw["n_layer"]
+        compare(rp.rows, oracle, ATOL["bfloat16"])
+        results[programs] = rp.rows
+    for key, row in results[True].items():
+        assert float((row - results[False][key]).abs().max()) <= 2e-3
