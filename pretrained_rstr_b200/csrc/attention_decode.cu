@@ -1,19 +1,6 @@
-// Decode attention over the paged bfloat16 cache: one query row per (token, head), keys
-// split into fixed ranges of absolute positions so that a single token still fills the
-// GPU, partial results merged in split order.
-//
-// Grid (token list, head, split).  Split s owns positions [s*SPLIT, (s+1)*SPLIT), a
-// multiple of the page size, so what a split sums and in which order depends only on
-// the token's own visible range [lo, pos], never on the batch.  Each warp takes the
-// keys of the split in turn, 32/LPK keys per load (LPK lanes share one key row, 16 bytes
-// each), keeps a running maximum and sum (online softmax, float32) and accumulates
-// weighted values; warps are merged through shared memory, splits through a float32
-// workspace: the last CTA of a (token, head) to finish merges all of its splits in
-// order s = first..last (a counter in scratch memory tells which CTA is last, and is
-// reset by it).  Softmax statistics and all sums are float32.
-//
-// Scratch: workspace [tokens, heads, max_splits, head_dim + 2] float32 and counters
-// [tokens * heads] int32 (zero before the first launch; the kernel leaves them zero).
+// Decode attention over the paged bfloat16 cache: the stand-alone kernel.  The work is
+// described in attention_decode.cuh; here four warps per CTA each take their own
+// (token, head, split) unit.
 #include "attention_decode.cuh"
 
 namespace {
@@ -23,17 +10,17 @@ constexpr int DEC_WARPS = DEC_THREADS / 32;
 
 template <int LPK>   // lanes per key row: 2, 4, 8, 16 or 32 (head_dim <= 8 * LPK)
 __global__ void __launch_bounds__(DEC_THREADS)
-attention_decode_kernel(Args a) {
-    __shared__ Shared<DEC_WARPS> sh;
+attention_decode_kernel(Args a, int n_units) {
     prb_grid_launch_dependents();
     prb_grid_wait();
-    unit<LPK, DEC_WARPS>(a, blockIdx.x, blockIdx.y, blockIdx.z, sh);
+    const int unit = blockIdx.x * DEC_WARPS + (threadIdx.x >> 5);
+    if (unit < n_units) warp_unit_flat<LPK>(a, unit);
 }
 }  // namespace
 
 PRB_API int prb_attention_decode_split() { return SPLIT; }
 
-// workspace: float32 [n_list, n_heads, max_splits, head_dim + 2]; counters: int32
+// workspace: float32 [n_list, n_heads, max_splits, head_dim + 4]; counters: int32
 // [n_list * n_heads], zero; both indexed by the place in the token list.  token_list/token_count may be null (all
 // tokens 0..n_list-1).  max_splits >= ceil(max context / SPLIT).
 PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long q_stride,
@@ -47,12 +34,16 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
     if (n_list <= 0) return 0;
     if (n_heads <= 0 || kv_heads <= 0 || n_heads % kv_heads != 0 || head_dim <= 0 ||
         head_dim % 8 != 0 || head_dim > MAX_DH || page_size < 8 || SPLIT % page_size != 0 ||
-        max_splits <= 0 || max_splits > 65535 || n_heads > 65535)
+        max_splits <= 0)
         return PRB_E_SIZE;
-    if (q_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 || ((uintptr_t)k_pages) % 16 != 0 ||
-        ((uintptr_t)v_pages) % 16 != 0)
+    if (q_stride % 8 != 0 || out_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 ||
+        ((uintptr_t)out) % 16 != 0 || ((uintptr_t)k_pages) % 16 != 0 ||
+        ((uintptr_t)v_pages) % 16 != 0 || ((uintptr_t)workspace) % 16 != 0)
         return PRB_E_ALIGN;
-    dim3 grid(n_list, n_heads, max_splits);
+    const long n_units_l = (long)n_list * n_heads * max_splits;
+    if (n_units_l > 0x7fffffffL) return PRB_E_SIZE;
+    const int n_units = (int)n_units_l;
+    dim3 grid((n_units + DEC_WARPS - 1) / DEC_WARPS);
     const int pieces = head_dim / 8;
     Args a;
     a.out = (__nv_bfloat16*)out; a.out_stride = out_stride;
@@ -64,7 +55,7 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
     a.max_pages = max_pages; a.num_pages = num_pages; a.scale = scale; a.window = window;
     a.workspace = workspace; a.counters = counters; a.max_splits = max_splits; a.status = status;
 #define PRB_DEC(L) \
-    e = prb_launch_dependent(attention_decode_kernel<L>, grid, dim3(DEC_THREADS), 0, stream, a)
+    e = prb_launch_dependent(attention_decode_kernel<L>, grid, dim3(DEC_THREADS), 0, stream, a, n_units)
     cudaError_t e;
     if (pieces <= 2) PRB_DEC(2);
     else if (pieces <= 4) PRB_DEC(4);
@@ -116,7 +107,7 @@ NoAllocDevice noalloc_devices[NOALLOC_MAX_DEVICES];
 }  // namespace
 
 // Largest sizes the entry point takes: floats of workspace (n_list * n_heads * max_splits
-// * (head_dim + 2) must not exceed it) and counters (n_list * n_heads).
+// * (head_dim + 4) must not exceed it) and counters (n_list * n_heads).
 PRB_API void prb_attention_decode_noalloc_limits(long* workspace_floats, int* counters) {
     if (workspace_floats) *workspace_floats = NOALLOC_WS_FLOATS;
     if (counters) *counters = NOALLOC_COUNTERS;
@@ -135,7 +126,7 @@ PRB_API int prb_attention_decode_noalloc(void* out, long out_stride, const void*
                                          int* status, cudaStream_t stream) {
     if (n_list <= 0) return 0;
     if (n_heads <= 0 || head_dim <= 0 || max_splits <= 0) return PRB_E_SIZE;
-    const long need_ws = (long)n_list * n_heads * max_splits * (head_dim + 2);
+    const long need_ws = (long)n_list * n_heads * max_splits * (head_dim + 4);
     const long need_counters = (long)n_list * n_heads;
     if (need_ws > NOALLOC_WS_FLOATS || need_counters > NOALLOC_COUNTERS) return PRB_E_SIZE;
     int dev = 0;

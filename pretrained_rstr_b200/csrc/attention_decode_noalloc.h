@@ -8,7 +8,7 @@
 // results of the key splits and one counter per (token, head)) is held in fixed-size
 // device arrays inside the library instead of being passed in.
 //
-// Limits: n_list * n_heads * max_splits * (head_dim + 2) <= 1,048,576 floats and
+// Limits: n_list * n_heads * max_splits * (head_dim + 4) <= 1,048,576 floats and
 // n_list * n_heads <= 16,384 (see prb_attention_decode_noalloc_limits); larger launches
 // are refused with -3 and nothing runs.  Every GPU that loads the library holds about
 // 4.1 MiB for these arrays until the process exits.

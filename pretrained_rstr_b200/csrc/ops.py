@@ -466,7 +466,7 @@ def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positi
     """bfloat16 attention of single tokens (those in ``token_list``, or all of the first
     ``n_list`` when it is None) over their requests' pages, keys split in ranges of
     ``decode_split()`` positions.  ``workspace`` float32 [n_list, heads, max_splits,
-    head_dim + 2] and ``counters`` int32 [n_list * heads] (zero) are scratch."""
+    head_dim + 4] and ``counters`` int32 [n_list * heads] (zero) are scratch."""
     what = "attention_decode"
     num_pages, kv_heads, page_size, head_dim = k_pages.shape
     for name, t in (("out", out), ("q", q)):
@@ -474,7 +474,7 @@ def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positi
             raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
     if k_pages.dtype != torch.bfloat16:
         raise KernelArgumentError(f"{what}: the cache must be bfloat16")
-    need = n_list * n_heads * max_splits * (head_dim + 2)
+    need = n_list * n_heads * max_splits * (head_dim + 4)
     if workspace.dtype != torch.float32 or workspace.numel() < need or \
             counters.dtype != torch.int32 or counters.numel() < n_list * n_heads:
         raise KernelArgumentError(f"{what}: scratch too small or of the wrong type")

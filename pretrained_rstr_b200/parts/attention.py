@@ -92,7 +92,7 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
         n_list = lay.single_cap if ctx.n_singles is None else ctx.n_singles
         max_splits = -(-ctx.max_context // ops.decode_split())
         cap = ctx.runtime.max_requests * SINGLE_MAX_Q
-        ws = ctx.scratch("attn_decode_ws", (cap * n_head * ctx.max_splits_cap * (head_dim + 2),),
+        ws = ctx.scratch("attn_decode_ws", (cap * n_head * ctx.max_splits_cap * (head_dim + 4),),
                          torch.float32)
         counters = ctx.scratch_zero("attn_decode_counters", (cap * n_head,), torch.int32)
         ops.attention_decode(out, q, cache.k, cache.v, group.block_table, ctx.seq_of_token,

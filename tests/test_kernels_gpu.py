@@ -174,7 +174,7 @@ def test_attention_decode(nh, nkv, dh, ps, window):
     q, k, v, table, seq, pos = _paged_case(2, nh, nkv, dh, ps, lengths, portions, torch.bfloat16)
     t = q.shape[0]
     splits = -(-1024 // ops.decode_split())
-    ws = torch.full((t * nh * splits * (dh + 2),), float("nan"), device="cuda")
+    ws = torch.full((t * nh * splits * (dh + 4),), float("nan"), device="cuda")
     counters = torch.zeros(t * nh, dtype=torch.int32, device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     ref = _ref_attention(q, k, v, table, seq, pos, nh, 0.2, window)
@@ -239,7 +239,7 @@ def test_attention_far_key_stands_out():
     assert float((out.float() - ref).abs().max()) <= 2e-2
     t = q.shape[0]
     splits = -(-1024 // ops.decode_split())
-    ws = torch.zeros(t * nh * splits * (dh + 2), device="cuda")
+    ws = torch.zeros(t * nh * splits * (dh + 4), device="cuda")
     counters = torch.zeros(t * nh, dtype=torch.int32, device="cuda")
     out2 = torch.zeros_like(q)
     ops.attention_decode(out2, q, k, v, table, seq, pos, None, None, t, nh, 0.125, None, ws,

@@ -53,7 +53,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one():
         t = q.shape[0]
         status = torch.zeros(4, dtype=torch.int32, device="cuda")
         want = torch.zeros_like(q)
-        ws = torch.zeros(t * n_heads * splits * (dh + 2), device="cuda")
+        ws = torch.zeros(t * n_heads * splits * (dh + 4), device="cuda")
         counters = torch.zeros(t * n_heads, dtype=torch.int32, device="cuda")
         ops.attention_decode(want, q, k, v, table, seq, pos, None, None, t, n_heads, 0.125, None,
                              ws, counters, splits, status)
