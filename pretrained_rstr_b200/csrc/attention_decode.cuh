@@ -213,7 +213,7 @@ __device__ __forceinline__ void warp_unit(const Args& a, int idx, int h, int s) 
     }
     // several splits: park this one in the workspace, the last warp to arrive merges them
     const size_t pair = (size_t)idx * a.n_heads + h;       // scratch is indexed by list place
-    const size_t stride = (size_t)(a.head_dim + 2);
+    const size_t stride = (size_t)(a.head_dim + 4);      // keeps every split 16-byte aligned
     float* ws = a.workspace + (pair * a.max_splits + s) * stride;
     if (kslot == 0 && piece_ok) {
         *reinterpret_cast<float4*>(ws + sub * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
