@@ -20,6 +20,16 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
            "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
 
 
+def _env_flag(name: str, default: bool) -> bool:
+    """Measurement switches: PRB200_GRAPHS=0 launches small steps kernel by kernel,
+    PRB200_PROGRAMS=0 does not run decode steps as one persistent kernel."""
+    import os
+    value = os.environ.get(name)
+    if value is None:
+        return default
+    return value.strip().lower() not in ("0", "false", "no", "off", "")
+
+
 def parse_dtype(dtype) -> torch.dtype:
     if isinstance(dtype, torch.dtype):
         if dtype not in (torch.bfloat16, torch.float32):
@@ -57,7 +67,9 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0", page_size: int = 
     torch.cuda.set_device(device)
     arch, config = read_config(folder)
     runtime = Runtime(device=device, dtype=dtype, page_size=page_size,
-                      max_batched_tokens=max_batched_tokens, max_requests=max_requests)
+                      max_batched_tokens=max_batched_tokens, max_requests=max_requests,
+                      use_graphs=_env_flag("PRB200_GRAPHS", True),
+                      use_programs=_env_flag("PRB200_PROGRAMS", True))
     store = load_weights(folder, arch.expected_tensors(config), device,
                          strip_prefixes=arch.strip_prefixes, ignorable=arch.ignorable)
     model = arch.build(config, store, runtime)
