@@ -33,7 +33,7 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
                                  cudaStream_t stream) {
     if (n_list <= 0) return 0;
     if (n_heads <= 0 || kv_heads <= 0 || n_heads % kv_heads != 0 || head_dim <= 0 ||
-        head_dim % 8 != 0 || head_dim > MAX_DH || page_size < 8 || SPLIT % page_size != 0 ||
+        head_dim % 8 != 0 || head_dim > MAX_DH || page_size < 8 || SPLIT / 8 + 1 > 32 ||
         max_splits <= 0)
         return PRB_E_SIZE;
     if (q_stride % 8 != 0 || out_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 ||

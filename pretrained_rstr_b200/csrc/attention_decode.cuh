@@ -5,7 +5,7 @@
 // The unit of work is one (token, head, split) and is done by ONE WARP, with no shared
 // memory and no block-wide barrier: warps of a CTA work on different units at the same
 // time, which is what hides the latency of these short dependent chains.  Split s owns
-// positions [s*SPLIT, (s+1)*SPLIT), a multiple of the page size, so what a split sums and
+// positions [s*SPLIT, (s+1)*SPLIT), so what a split sums and
 // in which order depends only on the token's own visible range [lo, pos], never on the
 // batch.  LPK lanes share a key row (16 bytes each), so a warp reads 32/LPK keys per load;
 // eight loads of keys and of values are in flight before the first is used.  Each group
@@ -25,7 +25,7 @@
 #include "common.cuh"
 
 namespace decode_attn {
-constexpr int SPLIT = 128;          // keys per split
+constexpr int SPLIT = 32;           // keys per split: one round of loads per warp
 constexpr int MAX_DH = 256;
 constexpr int UNROLL = 8;           // loads in flight per lane (keys and values each)
 
@@ -93,9 +93,10 @@ __device__ __forceinline__ void warp_unit(const Args& a, int idx, int h, int s) 
     const int hk = h / (a.n_heads / a.kv_heads);
     const bool piece_ok = sub * 8 < a.head_dim;
 
-    // page ids of this split: lane i holds page i of the split (page_size >= 8: <= 16 pages)
+    // page ids of this split: lane i holds the i-th page the split touches (page_size >= 8,
+    // so at most SPLIT / 8 + 1 pages)
     const int first_page = (s * SPLIT) / a.page_size;
-    const int pages_in_split = SPLIT / a.page_size;
+    const int pages_in_split = (s * SPLIT + SPLIT - 1) / a.page_size - first_page + 1;
     int my_page = -1;
     if (lane < pages_in_split && first_page + lane < a.max_pages)
         my_page = a.block_table[(size_t)b * a.max_pages + first_page + lane];

@@ -307,8 +307,7 @@ PRB_API int prb_program_add_attention(void* handle, void* out, long out_stride, 
                                       int* counters, int max_splits, int* status) {
     Program* p = static_cast<Program*>(handle);
     if (n_heads <= 0 || kv_heads <= 0 || n_heads % kv_heads != 0 || head_dim <= 0 ||
-        head_dim % 8 != 0 || head_dim > decode_attn::MAX_DH || page_size < 8 ||
-        decode_attn::SPLIT % page_size != 0 || max_splits <= 0)
+        head_dim % 8 != 0 || head_dim > decode_attn::MAX_DH || page_size < 8 || max_splits <= 0)
         return PRB_E_SIZE;
     if (q_stride % 8 != 0 || out_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 ||
         ((uintptr_t)out) % 16 != 0 || ((uintptr_t)k_pages) % 16 != 0 ||
