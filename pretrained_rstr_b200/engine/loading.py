@@ -22,7 +22,8 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
 
 def _env_flag(name: str, default: bool) -> bool:
     """Measurement switches: PRB200_GRAPHS=0 launches small steps kernel by kernel,
-    PRB200_PROGRAMS=0 does not run decode steps as one persistent kernel."""
+    PRB200_PROGRAMS=0 does not run decode steps as one persistent kernel, PRB200_PDL=0
+    switches programmatic dependent launch off."""
     import os
     value = os.environ.get(name)
     if value is None:
@@ -62,6 +63,7 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0", page_size: int = 
     ``max_requests`` requests of full length."""
     ops.require_cuda()
     ops.lib()                                   # build / load now, fail loudly here
+    ops.set_pdl(_env_flag("PRB200_PDL", True))
     dtype = parse_dtype(dtype)
     device = torch.device(device)
     torch.cuda.set_device(device)
