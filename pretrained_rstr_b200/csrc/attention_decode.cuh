@@ -231,25 +231,50 @@ __device__ __forceinline__ void warp_unit(const Args& a, int idx, int h, int s) 
     last = __shfl_sync(FULL, last, 0);
     if (!last) return;
     __threadfence();
+    // Merge: rounds of up to 32 splits, one split per lane for the statistics, then every
+    // lane sums its dimensions over the round's splits (weights passed by shuffle).
     const float* wbase = a.workspace + pair * a.max_splits * stride;
-    float mg = -INFINITY;
-    for (int ss = s_first; ss <= s_last; ++ss)
-        mg = fmaxf(mg, __ldcg(wbase + (size_t)ss * stride + a.head_dim));
-    float lg = 0.0f;
-    for (int ss = s_first; ss <= s_last; ++ss) {
-        const float* w = wbase + (size_t)ss * stride;
-        const float ms = __ldcg(w + a.head_dim);
-        lg += __ldcg(w + a.head_dim + 1) * ((ms == -INFINITY) ? 0.0f : __expf(ms - mg));
+    float mg = -INFINITY, lg = 0.0f;
+    float od[MAX_DH / 32];
+#pragma unroll
+    for (int i = 0; i < MAX_DH / 32; ++i) od[i] = 0.0f;
+    for (int r0 = s_first; r0 <= s_last; r0 += 32) {
+        const int ss = r0 + lane;
+        const bool have = ss <= s_last;
+        const float* w = wbase + (size_t)(have ? ss : s_last) * stride;
+        const float ms = have ? __ldcg(w + a.head_dim) : -INFINITY;
+        const float ls = have ? __ldcg(w + a.head_dim + 1) : 0.0f;
+        float mr = ms;
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) mr = fmaxf(mr, __shfl_xor_sync(FULL, mr, o2));
+        const float mn = fmaxf(mg, mr);
+        const float keep = (mg == -INFINITY) ? 0.0f : __expf(mg - mn);
+        const float cs = (ms == -INFINITY) ? 0.0f : __expf(ms - mn);     // this lane's split
+        float lsum = ls * cs;
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) lsum += __shfl_xor_sync(FULL, lsum, o2);
+        lg = lg * keep + lsum;
+        const int in_round = min(32, s_last - r0 + 1);
+#pragma unroll
+        for (int i = 0; i < MAX_DH / 32; ++i) {
+            const int d = lane + 32 * i;
+            float sum = od[i] * keep;
+            const bool mine = d < a.head_dim;        // the shuffles below are done by every lane
+#pragma unroll 8
+            for (int j = 0; j < in_round; ++j) {
+                const float cj = __shfl_sync(FULL, cs, j);
+                const float wv = mine ? __ldcg(wbase + (size_t)(r0 + j) * stride + d) : 0.0f;
+                sum = fmaf(cj, wv, sum);
+            }
+            od[i] = sum;
+        }
+        mg = mn;
     }
     const float inv = lg > 0.0f ? 1.0f / lg : 0.0f;
-    for (int d = lane; d < a.head_dim; d += 32) {
-        float od = 0.0f;
-        for (int ss = s_first; ss <= s_last; ++ss) {
-            const float* w = wbase + (size_t)ss * stride;
-            const float ms = __ldcg(w + a.head_dim);
-            od += __ldcg(w + d) * ((ms == -INFINITY) ? 0.0f : __expf(ms - mg));
-        }
-        o[d] = __float2bfloat16_rn(od * inv);
+#pragma unroll
+    for (int i = 0; i < MAX_DH / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < a.head_dim) o[d] = __float2bfloat16_rn(od[i] * inv);
     }
     if (lane == 0) a.counters[pair] = 0;
 }
