@@ -292,8 +292,9 @@ def main() -> int:
             entries.append(Entry(rid, [rng.randrange(vocab) for _ in range(1024)], [1023]))
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
+        m.loaded.runner.start_event = s          # recorded where the step's device work begins
         m.loaded.runner.step(entries)
+        m.loaded.runner.start_event = None
         e.record()
         torch.cuda.synchronize()
         if it >= 3:

@@ -1,6 +1,19 @@
-// Decode attention over the paged bfloat16 cache: the stand-alone kernel.  The work is
-// described in attention_decode.cuh; here four warps per CTA each take their own
-// (token, head, split) unit.
+// Decode attention over the paged bfloat16 cache: one query row per (token, head), keys
+// split into fixed ranges of absolute positions so that a single token still fills the
+// GPU, partial results merged in split order.
+//
+// Grid (token list, head, split).  Split s owns positions [s*SPLIT, (s+1)*SPLIT), a
+// multiple of the page size, so what a split sums and in which order depends only on
+// the token's own visible range [lo, pos], never on the batch.  Each warp takes the
+// keys of the split in turn, 32/LPK keys per load (LPK lanes share one key row, 16 bytes
+// each), keeps a running maximum and sum (online softmax, float32) and accumulates
+// weighted values; warps are merged through shared memory, splits through a float32
+// workspace: the last CTA of a (token, head) to finish merges all of its splits in
+// order s = first..last (a counter in scratch memory tells which CTA is last, and is
+// reset by it).  Softmax statistics and all sums are float32.
+//
+// Scratch: workspace [tokens, heads, max_splits, head_dim + 4] float32 and counters
+// [tokens * heads] int32 (zero before the first launch; the kernel leaves them zero).
 #include "attention_decode.cuh"
 
 namespace {
@@ -10,11 +23,11 @@ constexpr int DEC_WARPS = DEC_THREADS / 32;
 
 template <int LPK>   // lanes per key row: 2, 4, 8, 16 or 32 (head_dim <= 8 * LPK)
 __global__ void __launch_bounds__(DEC_THREADS)
-attention_decode_kernel(Args a, int n_units) {
+attention_decode_kernel(Args a) {
+    __shared__ Shared<DEC_WARPS> sh;
     prb_grid_launch_dependents();
     prb_grid_wait();
-    const int unit = blockIdx.x * DEC_WARPS + (threadIdx.x >> 5);
-    if (unit < n_units) warp_unit_flat<LPK>(a, unit);
+    unit<LPK, DEC_WARPS>(a, blockIdx.x, blockIdx.y, blockIdx.z, sh);
 }
 }  // namespace
 
@@ -33,17 +46,13 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
                                  cudaStream_t stream) {
     if (n_list <= 0) return 0;
     if (n_heads <= 0 || kv_heads <= 0 || n_heads % kv_heads != 0 || head_dim <= 0 ||
-        head_dim % 8 != 0 || head_dim > MAX_DH || page_size < 8 || SPLIT / 8 + 1 > 32 ||
-        max_splits <= 0)
+        head_dim % 8 != 0 || head_dim > MAX_DH || page_size < 8 || SPLIT % page_size != 0 ||
+        max_splits <= 0 || max_splits > 65535 || n_heads > 65535)
         return PRB_E_SIZE;
-    if (q_stride % 8 != 0 || out_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 ||
-        ((uintptr_t)out) % 16 != 0 || ((uintptr_t)k_pages) % 16 != 0 ||
+    if (q_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 || ((uintptr_t)k_pages) % 16 != 0 ||
         ((uintptr_t)v_pages) % 16 != 0 || ((uintptr_t)workspace) % 16 != 0)
         return PRB_E_ALIGN;
-    const long n_units_l = (long)n_list * n_heads * max_splits;
-    if (n_units_l > 0x7fffffffL) return PRB_E_SIZE;
-    const int n_units = (int)n_units_l;
-    dim3 grid((n_units + DEC_WARPS - 1) / DEC_WARPS);
+    dim3 grid(n_list, n_heads, max_splits);
     const int pieces = head_dim / 8;
     Args a;
     a.out = (__nv_bfloat16*)out; a.out_stride = out_stride;
@@ -55,7 +64,7 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
     a.max_pages = max_pages; a.num_pages = num_pages; a.scale = scale; a.window = window;
     a.workspace = workspace; a.counters = counters; a.max_splits = max_splits; a.status = status;
 #define PRB_DEC(L) \
-    e = prb_launch_dependent(attention_decode_kernel<L>, grid, dim3(DEC_THREADS), 0, stream, a, n_units)
+    e = prb_launch_dependent(attention_decode_kernel<L>, grid, dim3(DEC_THREADS), 0, stream, a)
     cudaError_t e;
     if (pieces <= 2) PRB_DEC(2);
     else if (pieces <= 4) PRB_DEC(4);

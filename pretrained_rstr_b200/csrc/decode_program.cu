@@ -97,18 +97,22 @@ __device__ __forceinline__ void run_gemm(const smallm::Args& a, int units, float
     }
 }
 
-// attention units are per warp: the warps of all CTAs share the list of units
 template <int LPK>
-__device__ __forceinline__ void run_attn(const decode_attn::Args& a, int units) {
-    const int warp = threadIdx.x >> 5;
-    for (int u = blockIdx.x * PROG_WARPS + warp; u < units; u += gridDim.x * PROG_WARPS)
-        decode_attn::warp_unit_flat<LPK>(a, u);
+__device__ __forceinline__ void run_attn(const decode_attn::Args& a, int units, int per_place,
+                                         decode_attn::Shared<PROG_WARPS>& sh) {
+    for (int vb = blockIdx.x; vb < units; vb += gridDim.x) {
+        const int idx = vb / per_place, rem = vb - idx * per_place;
+        const int h = rem / a.max_splits, s = rem - h * a.max_splits;
+        decode_attn::unit<LPK, PROG_WARPS>(a, idx, h, s, sh);
+        __syncthreads();
+    }
 }
 
 template <int MT>
 __global__ void __launch_bounds__(PROG_THREADS, 1)
 decode_program_kernel(const Op* __restrict__ ops, int n_ops, unsigned* bar, int* status) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    __shared__ decode_attn::Shared<PROG_WARPS> attn_sh;
     __shared__ float scratch[32];
     __shared__ int sh_flag;
     float* red = reinterpret_cast<float*>(smem_raw);                       // [8][16][8*MT]
@@ -152,11 +156,11 @@ decode_program_kernel(const Op* __restrict__ ops, int n_ops, unsigned* bar, int*
                 break;
             case OP_ATTN:
                 switch (flags) {
-                    case 2: run_attn<2>(op.attn, units); break;
-                    case 4: run_attn<4>(op.attn, units); break;
-                    case 8: run_attn<8>(op.attn, units); break;
-                    case 16: run_attn<16>(op.attn, units); break;
-                    default: run_attn<32>(op.attn, units); break;
+                    case 2: run_attn<2>(op.attn, units, op.aux, attn_sh); break;
+                    case 4: run_attn<4>(op.attn, units, op.aux, attn_sh); break;
+                    case 8: run_attn<8>(op.attn, units, op.aux, attn_sh); break;
+                    case 16: run_attn<16>(op.attn, units, op.aux, attn_sh); break;
+                    default: run_attn<32>(op.attn, units, op.aux, attn_sh); break;
                 }
                 break;
             default:
@@ -307,11 +311,12 @@ PRB_API int prb_program_add_attention(void* handle, void* out, long out_stride, 
                                       int* counters, int max_splits, int* status) {
     Program* p = static_cast<Program*>(handle);
     if (n_heads <= 0 || kv_heads <= 0 || n_heads % kv_heads != 0 || head_dim <= 0 ||
-        head_dim % 8 != 0 || head_dim > decode_attn::MAX_DH || page_size < 8 || max_splits <= 0)
+        head_dim % 8 != 0 || head_dim > decode_attn::MAX_DH || page_size < 8 ||
+        decode_attn::SPLIT % page_size != 0 || max_splits <= 0)
         return PRB_E_SIZE;
-    if (q_stride % 8 != 0 || out_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 ||
-        ((uintptr_t)out) % 16 != 0 || ((uintptr_t)k_pages) % 16 != 0 ||
-        ((uintptr_t)v_pages) % 16 != 0 || ((uintptr_t)workspace) % 16 != 0)
+    if (q_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 ||
+        ((uintptr_t)out) % 4 != 0 || ((uintptr_t)k_pages) % 16 != 0 ||
+        ((uintptr_t)v_pages) % 16 != 0)
         return PRB_E_ALIGN;
     Op op{};
     op.type = OP_ATTN;

@@ -22,7 +22,7 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
 
 def _env_flag(name: str, default: bool) -> bool:
     """Measurement switches: PRB200_GRAPHS=0 launches small steps kernel by kernel,
-    PRB200_PROGRAMS=0 does not run decode steps as one persistent kernel, PRB200_PDL=0
+    PRB200_PROGRAMS=1 runs decode-only steps as one persistent kernel, PRB200_PDL=0
     switches programmatic dependent launch off."""
     import os
     value = os.environ.get(name)
@@ -71,7 +71,7 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0", page_size: int = 
     runtime = Runtime(device=device, dtype=dtype, page_size=page_size,
                       max_batched_tokens=max_batched_tokens, max_requests=max_requests,
                       use_graphs=_env_flag("PRB200_GRAPHS", True),
-                      use_programs=_env_flag("PRB200_PROGRAMS", True))
+                      use_programs=_env_flag("PRB200_PROGRAMS", False))
     store = load_weights(folder, arch.expected_tensors(config), device,
                          strip_prefixes=arch.strip_prefixes, ignorable=arch.ignorable)
     model = arch.build(config, store, runtime)

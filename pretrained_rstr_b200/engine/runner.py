@@ -27,9 +27,16 @@ class StepError(RuntimeError):
 
 
 def _bucket(n: int, floor: int, cap: int) -> int:
-    b = floor
-    while b < n:
-        b *= 2
+    """Capacity a count is rounded up to: powers of two up to 64, multiples of 64 up to 512,
+    multiples of 256 beyond (few shapes, little padding)."""
+    if n <= 64:
+        b = floor
+        while b < n:
+            b *= 2
+    elif n <= 512:
+        b = -(-n // 64) * 64
+    else:
+        b = -(-n // 256) * 256
     return min(b, cap) if cap >= n else n
 
 
@@ -59,7 +66,7 @@ class ModelRunner:
         self._status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
         # CUDA graphs of whole steps, by (token capacity, request capacity, logits rows)
         self.use_graphs = bool(runtime.use_graphs) and getattr(model, "graph_safe", False)
-        self.graph_max_tokens = 256
+        self.graph_max_tokens = runtime.max_batched_tokens
         self._graphs: Dict[tuple, tuple] = {}
         self._seen: Dict[tuple, int] = {}
         # decode programs (whole steps of single tokens as one persistent kernel), same keys
@@ -158,10 +165,11 @@ class ModelRunner:
                 if not 0 <= w < len(e.tokens):
                     raise StepError(f"request {e.rid!r}: wanted place {w} outside its "
                                     f"{len(e.tokens)} tokens")
-            for tkn in e.tokens:
-                if not 0 <= tkn < vocab:
-                    raise StepError(f"request {e.rid!r}: token id {tkn} outside the vocabulary "
-                                    f"of {vocab}")
+            toks = np.asarray(e.tokens)
+            if toks.dtype.kind not in "iu" or int(toks.min()) < 0 or int(toks.max()) >= vocab:
+                bad = [t for t in e.tokens if not (isinstance(t, (int, np.integer)) and 0 <= t < vocab)]
+                raise StepError(f"request {e.rid!r}: token id {bad[0] if bad else '?'} outside the "
+                                f"vocabulary of {vocab}")
             if self.cache.length(e.rid) + len(e.tokens) > self.model.max_positions:
                 raise StepError(f"request {e.rid!r}: {self.cache.length(e.rid)}+{len(e.tokens)} "
                                 f"tokens exceed the model's {self.model.max_positions} positions")

@@ -77,7 +77,8 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
     t = out.shape[0]
     head_dim = cache.k.shape[3]
     fast = ctx.dtype == torch.bfloat16 and head_dim % 8 == 0 and head_dim <= 256 and \
-        group.page_size >= 8 and ops.prefill_supports(head_dim)
+        group.page_size >= 8 and ops.decode_split() % group.page_size == 0 and \
+        ops.prefill_supports(head_dim)
     if not fast:
         ops.attention_generic(out, q, cache.k, cache.v, group.block_table, ctx.seq_of_token,
                               ctx.positions, t, n_head, scale, window, ctx.max_context, ctx.status)
