@@ -35,18 +35,20 @@ PRB_API int prb_attention_decode_split() { return SPLIT; }
 
 // workspace: float32 [n_list, n_heads, max_splits, head_dim + 4]; counters: int32
 // [n_list * n_heads], zero; both indexed by the place in the token list.  token_list/token_count may be null (all
-// tokens 0..n_list-1).  max_splits >= ceil(max context / SPLIT).
+// tokens 0..n_list-1).  split_keys: keys per split (a multiple of 128 and of the page size);
+// max_splits >= ceil(max context / split_keys).
 PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long q_stride,
                                  const void* k_pages, const void* v_pages, const int* block_table,
                                  const int* seq_of_token, const int* positions,
                                  const int* token_list, const int* token_count, int n_list,
                                  int n_heads, int kv_heads, int head_dim, int page_size,
                                  int max_pages, int num_pages, float scale, int window,
-                                 float* workspace, int* counters, int max_splits, int* status,
-                                 cudaStream_t stream) {
+                                 float* workspace, int* counters, int max_splits,
+                                 int split_keys, int* status, cudaStream_t stream) {
     if (n_list <= 0) return 0;
     if (n_heads <= 0 || kv_heads <= 0 || n_heads % kv_heads != 0 || head_dim <= 0 ||
         head_dim % 8 != 0 || head_dim > MAX_DH || page_size < 8 || SPLIT % page_size != 0 ||
+        split_keys < SPLIT || split_keys % SPLIT != 0 || split_keys / page_size > MAX_SPLIT_PAGES ||
         max_splits <= 0 || max_splits > 65535 || n_heads > 65535)
         return PRB_E_SIZE;
     if (q_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 || ((uintptr_t)k_pages) % 16 != 0 ||
@@ -62,7 +64,8 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
     a.token_list = token_list; a.token_count = token_count;
     a.n_heads = n_heads; a.kv_heads = kv_heads; a.head_dim = head_dim; a.page_size = page_size;
     a.max_pages = max_pages; a.num_pages = num_pages; a.scale = scale; a.window = window;
-    a.workspace = workspace; a.counters = counters; a.max_splits = max_splits; a.status = status;
+    a.workspace = workspace; a.counters = counters; a.max_splits = max_splits;
+    a.split = split_keys; a.status = status;
 #define PRB_DEC(L) \
     e = prb_launch_dependent(attention_decode_kernel<L>, grid, dim3(DEC_THREADS), 0, stream, a)
     cudaError_t e;
@@ -132,7 +135,7 @@ PRB_API int prb_attention_decode_noalloc(void* out, long out_stride, const void*
                                          const int* token_count, int n_list, int n_heads,
                                          int kv_heads, int head_dim, int page_size, int max_pages,
                                          int num_pages, float scale, int window, int max_splits,
-                                         int* status, cudaStream_t stream) {
+                                         int split_keys, int* status, cudaStream_t stream) {
     if (n_list <= 0) return 0;
     if (n_heads <= 0 || head_dim <= 0 || max_splits <= 0) return PRB_E_SIZE;
     const long need_ws = (long)n_list * n_heads * max_splits * (head_dim + 4);
@@ -160,5 +163,5 @@ PRB_API int prb_attention_decode_noalloc(void* out, long out_stride, const void*
     return prb_attention_decode(out, out_stride, q, q_stride, k_pages, v_pages, block_table,
                                 seq_of_token, positions, token_list, token_count, n_list, n_heads,
                                 kv_heads, head_dim, page_size, max_pages, num_pages, scale, window,
-                                d.workspace, d.counters, max_splits, status, stream);
+                                d.workspace, d.counters, max_splits, split_keys, status, stream);
 }

@@ -2,8 +2,9 @@
 // split into fixed ranges of absolute positions so that a single token still fills the
 // GPU, partial results merged in split order.
 //
-// Grid (token list, head, split).  Split s owns positions [s*SPLIT, (s+1)*SPLIT), a
-// multiple of the page size, so what a split sums and in which order depends only on
+// Grid (token list, head, split).  Split s owns positions [s*split, (s+1)*split), split a
+// multiple of 128 keys and of the page size chosen per launch (fewer, longer splits when
+// there are many (token, head) pairs), so what a split sums and in which order depends only on
 // the token's own visible range [lo, pos], never on the batch.  Each warp takes the
 // keys of the split in turn, 32/LPK keys per load (LPK lanes share one key row, 16 bytes
 // each), keeps a running maximum and sum (online softmax, float32) and accumulates
@@ -22,7 +23,8 @@
 #include "common.cuh"
 
 namespace decode_attn {
-constexpr int SPLIT = 128;          // keys per split (a multiple of the page size)
+constexpr int SPLIT = 128;          // granule of the split size (keys); a multiple of the page size
+constexpr int MAX_SPLIT_PAGES = 128; // most pages one split may span
 constexpr int MAX_DH = 256;
 
 struct Args {
@@ -43,6 +45,7 @@ struct Args {
     float* workspace;
     int* counters;
     int max_splits;
+    int split;                      // keys per split: a multiple of SPLIT
     int* status;
 };
 
@@ -64,7 +67,7 @@ template <int NW> struct Shared {
     float m[NW], l[NW];
     float o[NW][MAX_DH];
     int last;
-    int pages[SPLIT / 8];           // pages of this split (page_size >= 8)
+    int pages[MAX_SPLIT_PAGES];     // pages of this split
 };
 
 // One (token list place idx, head h, split s).  LPK lanes share a key row (head_dim <= 8 *
@@ -88,14 +91,14 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
         return;
     }
     const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
-    const int s_first = lo / SPLIT, s_last = pos / SPLIT;
+    const int s_first = lo / a.split, s_last = pos / a.split;
     if (s_last >= a.max_splits) {                   // the launch does not cover this context
         if (threadIdx.x == 0 && s == 0) prb_set_status(a.status, PRB_S_POSITION_RANGE, t, pos, a.max_splits);
         return;
     }
     if (s < s_first || s > s_last) return;
     const int n_splits = s_last - s_first + 1;
-    const int k_begin = max(lo, s * SPLIT), k_end = min(pos + 1, (s + 1) * SPLIT);
+    const int k_begin = max(lo, s * a.split), k_end = min(pos + 1, (s + 1) * a.split);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPK;                   // which 16-byte piece of the row
@@ -117,8 +120,8 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
     for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
 
     // page ids of this split, once
-    const int first_page = (s * SPLIT) / a.page_size;
-    for (int i = threadIdx.x; i < SPLIT / a.page_size; i += (NW * 32))
+    const int first_page = (s * a.split) / a.page_size;
+    for (int i = threadIdx.x; i < a.split / a.page_size; i += (NW * 32))
         sh_pages[i] = (first_page + i < a.max_pages) ? table[first_page + i] : -1;
     __syncthreads();
 

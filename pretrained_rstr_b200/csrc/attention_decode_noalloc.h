@@ -31,7 +31,7 @@ int prb_attention_decode_noalloc(void* out, long out_stride, const void* q, long
                                  const int* token_list, const int* token_count, int n_list,
                                  int n_heads, int kv_heads, int head_dim, int page_size,
                                  int max_pages, int num_pages, float scale, int window,
-                                 int max_splits, int* status, cudaStream_t stream);
+                                 int max_splits, int split_keys, int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

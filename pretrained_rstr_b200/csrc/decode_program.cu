@@ -308,11 +308,14 @@ PRB_API int prb_program_add_attention(void* handle, void* out, long out_stride, 
                                       const int* token_count, int n_list, int n_heads,
                                       int kv_heads, int head_dim, int page_size, int max_pages,
                                       int num_pages, float scale, int window, float* workspace,
-                                      int* counters, int max_splits, int* status) {
+                                      int* counters, int max_splits, int split_keys,
+                                      int* status) {
     Program* p = static_cast<Program*>(handle);
     if (n_heads <= 0 || kv_heads <= 0 || n_heads % kv_heads != 0 || head_dim <= 0 ||
         head_dim % 8 != 0 || head_dim > decode_attn::MAX_DH || page_size < 8 ||
-        decode_attn::SPLIT % page_size != 0 || max_splits <= 0)
+        decode_attn::SPLIT % page_size != 0 || max_splits <= 0 || split_keys < decode_attn::SPLIT ||
+        split_keys % decode_attn::SPLIT != 0 ||
+        split_keys / page_size > decode_attn::MAX_SPLIT_PAGES)
         return PRB_E_SIZE;
     if (q_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 ||
         ((uintptr_t)out) % 4 != 0 || ((uintptr_t)k_pages) % 16 != 0 ||
@@ -332,7 +335,8 @@ PRB_API int prb_program_add_attention(void* handle, void* out, long out_stride, 
     a.token_list = token_list; a.token_count = token_count;
     a.n_heads = n_heads; a.kv_heads = kv_heads; a.head_dim = head_dim; a.page_size = page_size;
     a.max_pages = max_pages; a.num_pages = num_pages; a.scale = scale; a.window = window;
-    a.workspace = workspace; a.counters = counters; a.max_splits = max_splits; a.status = status;
+    a.workspace = workspace; a.counters = counters; a.max_splits = max_splits;
+    a.split = split_keys; a.status = status;
     op.attn = a;
     p->ops.push_back(op);
     return 0;

@@ -87,7 +87,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_attention_generic.argtypes = [P, L, P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I,
                                         I, P, P]
     h.prb_attention_decode.argtypes = [P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I,
-                                       P, P, I, P, P]
+                                       P, P, I, I, P, P]
     h.prb_attention_prefill.argtypes = [P, L, P, L, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F,
                                         I, P, P]
     h.prb_attention_prefill_supports.argtypes = [I]
@@ -104,7 +104,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_program_add_gemm.argtypes = [P, P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I]
     h.prb_program_add_append.argtypes = [P, P, P, P, P, L, P, I, I, I, I, I, I, P]
     h.prb_program_add_attention.argtypes = [P, P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I,
-                                            I, F, I, P, P, I, P]
+                                            I, F, I, P, P, I, I, P]
     h.prb_program_upload.argtypes = [P, P, P]
     h.prb_program_run.argtypes = [P, P, P, P, P]
     h.prb_set_pdl.argtypes = [I]
@@ -462,10 +462,10 @@ def prefill_supports(head_dim: int) -> bool:
 
 def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positions, token_list,
                      token_count, n_list, n_heads, scale, window, workspace, counters, max_splits,
-                     status) -> None:
+                     status, split_keys: Optional[int] = None) -> None:
     """bfloat16 attention of single tokens (those in ``token_list``, or all of the first
     ``n_list`` when it is None) over their requests' pages, keys split in ranges of
-    ``decode_split()`` positions.  ``workspace`` float32 [n_list, heads, max_splits,
+    ``split_keys`` positions (a multiple of ``decode_split()``, the default).  ``workspace`` float32 [n_list, heads, max_splits,
     head_dim + 4] and ``counters`` int32 [n_list * heads] (zero) are scratch."""
     what = "attention_decode"
     num_pages, kv_heads, page_size, head_dim = k_pages.shape
@@ -474,6 +474,7 @@ def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positi
             raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
     if k_pages.dtype != torch.bfloat16:
         raise KernelArgumentError(f"{what}: the cache must be bfloat16")
+    split_keys = decode_split() if split_keys is None else int(split_keys)
     need = n_list * n_heads * max_splits * (head_dim + 4)
     if workspace.dtype != torch.float32 or workspace.numel() < need or \
             counters.dtype != torch.int32 or counters.numel() < n_list * n_heads:
@@ -484,13 +485,14 @@ def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positi
             _p(v_pages), _p(block_table), _p(seq_of_token), _p(positions), _p(token_list),
             _p(token_count), n_list, n_heads, kv_heads, head_dim, page_size, block_table.shape[1],
             num_pages, float(scale), int(window or 0), _p(workspace), _p(counters), max_splits,
-            _p(status)), what)
+            split_keys, _p(status)), what)
         return
     _check(lib().prb_attention_decode(
         _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(block_table),
         _p(seq_of_token), _p(positions), _p(token_list), _p(token_count), n_list, n_heads,
         kv_heads, head_dim, page_size, block_table.shape[1], num_pages, float(scale),
-        int(window or 0), _p(workspace), _p(counters), max_splits, _p(status), _stream()), what)
+        int(window or 0), _p(workspace), _p(counters), max_splits, split_keys, _p(status),
+        _stream()), what)
 
 
 def attention_prefill(out, q, k_pages, v_pages, block_table, positions, tile_req, tile_row0,

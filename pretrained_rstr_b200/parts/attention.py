@@ -91,14 +91,20 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
                               n_head, scale, window, ctx.status)
     if ctx.n_singles is None or ctx.n_singles > 0:
         n_list = lay.single_cap if ctx.n_singles is None else ctx.n_singles
-        max_splits = -(-ctx.max_context // ops.decode_split())
+        # about four CTAs per SM: many (token, head) pairs get fewer, longer splits
+        granule = ops.decode_split()
+        most = -(-ctx.max_context // granule)
+        wanted = max(1, min(most, -(-600 // max(1, n_list * n_head))))
+        split_keys = -(-ctx.max_context // wanted // granule) * granule
+        max_splits = -(-ctx.max_context // split_keys)
         cap = ctx.runtime.max_requests * SINGLE_MAX_Q
         ws = ctx.scratch("attn_decode_ws", (cap * n_head * ctx.max_splits_cap * (head_dim + 4),),
                          torch.float32)
         counters = ctx.scratch_zero("attn_decode_counters", (cap * n_head,), torch.int32)
         ops.attention_decode(out, q, cache.k, cache.v, group.block_table, ctx.seq_of_token,
                              ctx.positions, ctx.single_tokens, ctx.counts[1:2], n_list, n_head,
-                             scale, window, ws, counters, max_splits, ctx.status)
+                             scale, window, ws, counters, max_splits, ctx.status,
+                             split_keys=split_keys)
 
 
 def _causal_attention(p, store, rt) -> CausalAttention:

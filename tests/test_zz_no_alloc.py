@@ -37,7 +37,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one():
     lib = ops.lib()
     fn = lib.prb_attention_decode_noalloc
     P, I, L, F = c_void_p, c_int, c_long, c_float
-    fn.argtypes = [P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P]
+    fn.argtypes = [P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P]
     fn.restype = c_int
     lib.prb_attention_decode_noalloc_limits.argtypes = [ctypes.POINTER(c_long), ctypes.POINTER(c_int)]
     lib.prb_attention_decode_noalloc_limits.restype = None
@@ -61,7 +61,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one():
         rc = fn(got.data_ptr(), got.stride(0), q.data_ptr(), q.stride(0), k.data_ptr(),
                 v.data_ptr(), table.data_ptr(), seq.data_ptr(), pos.data_ptr(), None, None, t,
                 n_heads, n_heads, dh, ps, table.shape[1], k.shape[0], 0.125, 0, splits,
-                status.data_ptr(), stream)
+                ops.decode_split(), status.data_ptr(), stream)
         assert rc == 0
         torch.cuda.synchronize()
         assert status.tolist() == [0, 0, 0, 0]
@@ -69,5 +69,6 @@ def test_no_alloc_entry_point_matches_the_ordinary_one():
     # a launch that needs more scratch than the fixed arrays hold is refused, nothing runs
     rc = fn(got.data_ptr(), got.stride(0), q.data_ptr(), q.stride(0), k.data_ptr(), v.data_ptr(),
             table.data_ptr(), seq.data_ptr(), pos.data_ptr(), None, None, 4096, n_heads, n_heads,
-            dh, ps, table.shape[1], k.shape[0], 0.125, 0, splits, status.data_ptr(), stream)
+            dh, ps, table.shape[1], k.shape[0], 0.125, 0, splits, ops.decode_split(),
+            status.data_ptr(), stream)
     assert rc == -3
