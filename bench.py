@@ -124,16 +124,22 @@ def run_reference(args) -> int:
 
 
 def timed_decode(engine, lm, batch, ctx_len, steps, warmup, vocab, seed):
-    """Prefill ``batch`` requests so that the timed decode steps end at ``ctx_len``
-    tokens; returns per-step device milliseconds, wall seconds and launch count."""
+    """Prefill ``batch`` requests and time ``steps`` decode steps of all of them together,
+    ending near ``ctx_len`` tokens of context.  Requests whose prompts finish early decode
+    while the others still prefill, so every request gets enough tokens to generate that
+    none finishes inside the timed region; the mean context actually decoded at is
+    measured.  Returns per-step device milliseconds, wall seconds, launches, mean context,
+    bytes copied to the device per step."""
     import random
     import torch
     from pretrained_rstr_b200.csrc import ops
     rng = random.Random(seed)
-    prompt_len = ctx_len - (steps + warmup) - 1
-    for i in range(batch):
-        engine.submit(("bench", batch, i), [rng.randrange(vocab) for _ in range(prompt_len)],
-                      steps + warmup + 1)
+    extra = batch + 2                      # steps the first request may decode before the last one starts
+    max_new = steps + warmup + extra + 1
+    prompt_len = max(16, ctx_len - max_new)
+    rids = [("bench", batch, i) for i in range(batch)]
+    for rid in rids:
+        engine.submit(rid, [rng.randrange(vocab) for _ in range(prompt_len)], max_new)
     while any(r.phase != "decode" for r in engine.scheduler.running.values()) or \
             engine.scheduler.waiting:
         engine.step()
@@ -141,6 +147,8 @@ def timed_decode(engine, lm, batch, ctx_len, steps, warmup, vocab, seed):
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
+    assert len(engine.scheduler.running) == batch
+    ctx_before = sum(len(r.prompt) + len(r.output) for r in engine.scheduler.running.values()) / batch
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
     launches0 = ops.launch_count()
@@ -153,8 +161,11 @@ def timed_decode(engine, lm, batch, ctx_len, steps, warmup, vocab, seed):
     wall = time.perf_counter() - t0
     engine.timing_events = None
     launches = ops.launch_count() - launches0
+    assert len(engine.scheduler.running) == batch, "a request finished inside the timed region"
     ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
-    mean_ctx = ctx_len - 1 - steps / 2.0
+    mean_ctx = ctx_before + steps / 2.0
+    for rid in rids:
+        engine.cancel(rid)
     while engine.scheduler.running:
         engine.step()
     h2d = engine.runner.last_h2d_bytes
@@ -311,6 +322,8 @@ def main() -> int:
     for b in (1, 64):
         ms, wall, _l, _c, _h = timed_decode(engine, m.loaded, b, ctx_len, steps, warmup, vocab, b)
         points[f"decode_b{b}"] = b / (statistics.mean(ms) / 1e3)
+        points[f"decode_b{b}_ms"] = [round(min(ms), 4), round(statistics.median(ms), 4),
+                                     round(max(ms), 4)]
     with ClockSampler() as clocks:
         ms, wall, launches, mean_ctx, h2d = timed_decode(engine, m.loaded, args.batch, ctx_len,
                                                         steps, warmup, vocab, 5)
