@@ -53,9 +53,13 @@ class Linear:
         if self.runtime.dtype == torch.float32:
             ops.gemm_f32(out, _tensor(a), self.weight, self.bias, resid, act)
             return
+        # Which kernel (measured on GPT-2-small shapes, see profiles/): up to 16 rows the
+        # weight-streaming kernel with the norm fused into it; up to 64 rows the same kernel
+        # without the fused norm (every CTA would repeat it) for narrow outputs, the
+        # tensor-memory kernel for wide ones; beyond 64 rows the tensor-memory kernel.
         max_rows, max_norm = ops.smallm_limits()
-        if m <= max_rows and self.n_in % 8 == 0:
-            if isinstance(a, LazyNorm) and a.fusable and self.n_in <= max_norm:
+        if m <= max_rows and self.n_in % 8 == 0 and (m <= 16 or self.n_out <= 1024):
+            if m <= 16 and isinstance(a, LazyNorm) and a.fusable and self.n_in <= max_norm:
                 ops.gemm_smallm(out, self.weight, norm_input=a.x, gamma=a.norm.gamma,
                                 beta=a.norm.beta, eps=a.norm.eps, bias=self.bias, resid=resid,
                                 act=act)
