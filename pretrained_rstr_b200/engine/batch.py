@@ -85,6 +85,26 @@ class BatchLayout:
         self.single_tokens = take(self.single_cap)
         self.counts = take(4)                 # [tiles, singles, tokens, requests]
         self.size = off
+        self._views = None
+
+    def device_views(self, buf: torch.Tensor):
+        if self._views is None:
+            lay = self
+            self._views = (
+                buf[lay.tokens:lay.tokens + lay.t_cap],
+                buf[lay.positions:lay.positions + lay.t_cap],
+                buf[lay.seq_of_token:lay.seq_of_token + lay.t_cap],
+                buf[lay.logit_rows:lay.logit_rows + lay.t_cap],
+                buf[lay.q_start:lay.q_start + lay.b_cap + 1],
+                buf[lay.kv_len:lay.kv_len + lay.b_cap],
+                buf[lay.state_slot:lay.state_slot + lay.b_cap],
+                buf[lay.fresh:lay.fresh + lay.b_cap],
+                buf[lay.tile_req:lay.tile_req + lay.tile_cap],
+                buf[lay.tile_row0:lay.tile_row0 + lay.tile_cap],
+                buf[lay.tile_rows:lay.tile_rows + lay.tile_cap],
+                buf[lay.single_tokens:lay.single_tokens + lay.single_cap],
+                buf[lay.counts:lay.counts + 4])
+        return self._views
 
 
 @dataclass
@@ -132,20 +152,11 @@ class StepContext:
         self.max_q_len = max_q_len
         self.max_positions = max_positions or max_context
         self._scratch = scratch_pool
-        lay, buf = layout, device_buf
-        self.tokens = buf[lay.tokens:lay.tokens + lay.t_cap]
-        self.positions = buf[lay.positions:lay.positions + lay.t_cap]
-        self.seq_of_token = buf[lay.seq_of_token:lay.seq_of_token + lay.t_cap]
-        self.logit_rows = buf[lay.logit_rows:lay.logit_rows + lay.t_cap]
-        self.q_start = buf[lay.q_start:lay.q_start + lay.b_cap + 1]
-        self.kv_len = buf[lay.kv_len:lay.kv_len + lay.b_cap]
-        self.state_slot = buf[lay.state_slot:lay.state_slot + lay.b_cap]
-        self.fresh = buf[lay.fresh:lay.fresh + lay.b_cap]
-        self.tile_req = buf[lay.tile_req:lay.tile_req + lay.tile_cap]
-        self.tile_row0 = buf[lay.tile_row0:lay.tile_row0 + lay.tile_cap]
-        self.tile_rows = buf[lay.tile_rows:lay.tile_rows + lay.tile_cap]
-        self.single_tokens = buf[lay.single_tokens:lay.single_tokens + lay.single_cap]
-        self.counts = buf[lay.counts:lay.counts + 4]
+        # device views of the step's arrays: made once per layout, their addresses never change
+        views = layout.device_views(device_buf)
+        (self.tokens, self.positions, self.seq_of_token, self.logit_rows, self.q_start,
+         self.kv_len, self.state_slot, self.fresh, self.tile_req, self.tile_row0, self.tile_rows,
+         self.single_tokens, self.counts) = views
         # host-side counts of the work lists (None when the step is replayed from a graph
         # and only the device-side counts are valid)
         self.n_tiles: Optional[int] = None

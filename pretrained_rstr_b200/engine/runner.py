@@ -48,6 +48,7 @@ class ModelRunner:
         self.n_groups = len(cache.groups)
         self.max_pages = cache.max_pages_per_request
         self._layouts: Dict[tuple, BatchLayout] = {}
+        self._group_views: Dict[int, list] = {}
         biggest = BatchLayout(runtime.max_batched_tokens, runtime.max_requests, self.n_groups,
                               self.max_pages)
         # two pinned staging buffers, used in turn, each guarded by an event
@@ -227,16 +228,19 @@ class ModelRunner:
                 self.storage.copy_pages(g, self._pairs_dev, len(chunk), self.status)
                 torch.cuda.current_stream().synchronize()      # pinned pairs buffer is reused
                 self.counters["cow_copies"] += len(chunk)
-        groups = []
-        for g, spec in enumerate(self.cache.groups):
-            lay = layout
-            groups.append(GroupView(
-                slots=self._dev[lay.slots[g]:lay.slots[g] + lay.t_cap],
-                block_table=self._dev[lay.block_table[g]:lay.block_table[g]
-                                      + lay.b_cap * lay.max_pages].view(lay.b_cap, lay.max_pages),
-                first_pos=self._dev[lay.first_pos[g]:lay.first_pos[g] + lay.b_cap],
-                window=spec.window, page_size=self.cache.page_size,
-                num_pages=self.cache.allocators[g].num_pages))
+        groups = self._group_views.get(id(layout))
+        if groups is None:
+            groups = []
+            for g, spec in enumerate(self.cache.groups):
+                lay = layout
+                groups.append(GroupView(
+                    slots=self._dev[lay.slots[g]:lay.slots[g] + lay.t_cap],
+                    block_table=self._dev[lay.block_table[g]:lay.block_table[g]
+                                          + lay.b_cap * lay.max_pages].view(lay.b_cap, lay.max_pages),
+                    first_pos=self._dev[lay.first_pos[g]:lay.first_pos[g] + lay.b_cap],
+                    window=spec.window, page_size=self.cache.page_size,
+                    num_pages=self.cache.allocators[g].num_pages))
+            self._group_views[id(layout)] = groups
         host = HostBatch(rids=[e.rid for e in entries], q_start=q_start, start_pos=start_pos,
                          state_slot=state_slots, fresh=fresh,
                          tokens=[t for e in entries for t in e.tokens])
