@@ -260,7 +260,10 @@ PRB_API int prb_program_add_norm(void* handle, void* out, const float* x, const 
 PRB_API int prb_program_add_gemm(void* handle, void* out, const void* x, const float* xf,
                                  const float* gamma, const float* beta, float eps, const void* w,
                                  const float* bias, const float* resid, int m, int n, int k,
-                                 long ldx, long ldw, long ldc, int act, int out_dtype) {
+                                 long ldx, long ldw, long ldc, int act, int out_dtype,
+                                 void* k_pages, void* v_pages, const int* slots, int q_width,
+                                 int kv_width, int head_dim, int page_size, int num_pages,
+                                 int* status) {
     Program* p = static_cast<Program*>(handle);
     if (out_dtype != PRB_F32 && out_dtype != PRB_BF16) return PRB_E_DTYPE;
     if (m > 8 * p->mt) return PRB_E_SIZE;
@@ -278,6 +281,12 @@ PRB_API int prb_program_add_gemm(void* handle, void* out, const void* x, const f
     a.eps = eps; a.w = (const __nv_bfloat16*)w; a.bias = bias; a.resid = resid;
     a.m = m; a.n = n; a.k = k; a.ldx = ldx; a.ldw = ldw; a.ldc = ldc; a.act = act;
     a.xs_pitch = ln ? smallm::norm_pitch(k) : k;
+    if (kv_width > 0 && (head_dim <= 0 || kv_width % head_dim != 0 || page_size <= 0 ||
+                         q_width + 2 * kv_width != n || !k_pages || !v_pages || !slots))
+        return PRB_E_ARG;
+    a.k_pages = k_pages; a.v_pages = v_pages; a.slots = slots;
+    a.q_width = q_width; a.kv_width = kv_width; a.head_dim = head_dim;
+    a.page_size = page_size; a.num_pages = num_pages; a.status = status;
     op.gemm = a;
     p->smem = max_size(p->smem, smem);
     p->ops.push_back(op);

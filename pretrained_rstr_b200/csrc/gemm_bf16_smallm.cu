@@ -85,10 +85,14 @@ int prb_gemm_smallm_check(const void* x, const float* xf, const float* gamma, co
 
 // x: bfloat16 [M,K] (xf null), or xf: float32 [M,K] to be LayerNorm-ed first with gamma, beta
 // (may be null) and eps.  m <= 64, k % 8 == 0, pitches multiples of 8 (4 for xf).
+// kv_width > 0: the product is a fused QKV projection and its key and value columns are
+// also written to the paged cache at slots[token] (the cache has the output's element type).
 PRB_API int prb_gemm_smallm(void* out, const void* x, const float* xf, const float* gamma,
                             const float* beta, float eps, const void* w, const float* bias,
                             const float* resid, int m, int n, int k, long ldx, long ldw, long ldc,
-                            int act, int out_dtype, cudaStream_t stream) {
+                            int act, int out_dtype, void* k_pages, void* v_pages,
+                            const int* slots, int q_width, int kv_width, int head_dim,
+                            int page_size, int num_pages, int* status, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     const int bad = prb_gemm_smallm_check(x, xf, gamma, beta, w, m, n, k, ldx, ldw);
     if (bad) return bad;
@@ -106,6 +110,15 @@ PRB_API int prb_gemm_smallm(void* out, const void* x, const float* xf, const flo
     a.ldx = ldx; a.ldw = ldw; a.ldc = ldc;
     a.act = act;
     a.xs_pitch = k;
+    if (kv_width > 0) {
+        if (head_dim <= 0 || kv_width % head_dim != 0 || page_size <= 0 || q_width < 0 ||
+            q_width + 2 * kv_width != n || k_pages == nullptr || v_pages == nullptr ||
+            slots == nullptr)
+            return PRB_E_ARG;
+    }
+    a.k_pages = k_pages; a.v_pages = v_pages; a.slots = slots;
+    a.q_width = q_width; a.kv_width = kv_width; a.head_dim = head_dim;
+    a.page_size = page_size; a.num_pages = num_pages; a.status = status;
     const bool ln = xf != nullptr;
     if (out_dtype == PRB_F32)
         return ln ? dispatch_mt<true, float>(a, stream) : dispatch_mt<false, float>(a, stream);

@@ -43,6 +43,13 @@ struct Args {
     long ldx, ldw, ldc;
     int act;
     int xs_pitch;                   // row pitch (elements) of the normalised rows in shared memory
+    // Optional scatter of output columns into the paged cache (a fused QKV product: columns
+    // [q_width, q_width + kv_width) are keys, the next kv_width are values).  kv_width == 0: off.
+    void* k_pages;                  // [pages][kv heads][page_size][head_dim], element type of out
+    void* v_pages;
+    const int* slots;               // cache slot of each token, -1 = none
+    int q_width, kv_width, head_dim, page_size, num_pages;
+    int* status;
 };
 
 struct Prefetch {
@@ -218,7 +225,25 @@ __device__ __forceinline__ void strip(const Args& a, int strip_index, float* red
         if (a.bias) v += a.bias[col];
         v = prb_activate(v, a.act);
         if (a.resid) v += a.resid[(size_t)tok * a.ldc + col];
-        out[(size_t)tok * a.ldc + col] = prb_from_float<O>(v);
+        const O o = prb_from_float<O>(v);
+        out[(size_t)tok * a.ldc + col] = o;
+        if (a.kv_width > 0 && col >= a.q_width) {
+            // this column is a key or value element of token `tok`: also to its cache slot
+            const int slot = a.slots[tok];
+            if (slot >= 0) {
+                const int page = slot / a.page_size, off = slot - page * a.page_size;
+                if (page >= a.num_pages) {
+                    prb_set_status(a.status, PRB_S_SLOT_RANGE, tok, slot, a.num_pages);
+                } else {
+                    int c = col - a.q_width;
+                    O* pages = reinterpret_cast<O*>(c < a.kv_width ? a.k_pages : a.v_pages);
+                    if (c >= a.kv_width) c -= a.kv_width;
+                    const int h = c / a.head_dim, d = c - h * a.head_dim;
+                    const int kv_heads = a.kv_width / a.head_dim;
+                    pages[(((size_t)page * kv_heads + h) * a.page_size + off) * a.head_dim + d] = o;
+                }
+            }
+        }
     }
     __syncthreads();
 }

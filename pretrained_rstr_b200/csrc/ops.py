@@ -81,7 +81,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_copy_pages.argtypes = [P, P, I, L, I, I, P, P]
     h.prb_gemm_f32.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, P]
     h.prb_gemm_bf16.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, I, P, P]
-    h.prb_gemm_smallm.argtypes = [P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I, P]
+    h.prb_gemm_smallm.argtypes = [P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
+                                  P, P, P, I, I, I, I, I, P, P]
     h.prb_gemm_smallm_max_rows.argtypes = []
     h.prb_gemm_smallm_max_norm_width.argtypes = []
     h.prb_attention_generic.argtypes = [P, L, P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I,
@@ -101,7 +102,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_program_bytes.restype = L
     h.prb_program_add_embed.argtypes = [P, P, P, P, P, P, I, I, I, I, I, P]
     h.prb_program_add_norm.argtypes = [P, P, P, P, P, P, I, I, I, F, I, P]
-    h.prb_program_add_gemm.argtypes = [P, P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I]
+    h.prb_program_add_gemm.argtypes = [P, P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
+                                       P, P, P, I, I, I, I, I, P]
     h.prb_program_add_append.argtypes = [P, P, P, P, P, L, P, I, I, I, I, I, I, P]
     h.prb_program_add_attention.argtypes = [P, P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I,
                                             I, F, I, P, P, I, I, P]
@@ -390,10 +392,12 @@ def smallm_limits():
 
 
 def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0, bias=None,
-                resid=None, act=None) -> None:
+                resid=None, act=None, kv_scatter=None, status=None) -> None:
     """out[M,N] = act(X . w[N,K]^T + bias) (+ resid) for M <= 64 rows, weights streamed once.
     X is ``a`` (bfloat16 [M,K]) or LayerNorm(``norm_input``) (float32 [M,K]) with ``gamma``,
-    ``beta`` and ``eps``, the norm fused into the kernel."""
+    ``beta`` and ``eps``, the norm fused into the kernel.  ``kv_scatter`` = (k_pages, v_pages,
+    slots, q_width): the product is a fused QKV projection; its key and value columns are also
+    written to the paged cache (same element type as ``out``) at each token's slot."""
     what = "gemm_smallm"
     if not w.is_cuda or w.dtype != torch.bfloat16 or w.stride(1) != 1:
         raise KernelArgumentError(f"{what}: w must be bfloat16 on CUDA with unit inner stride")
@@ -417,18 +421,27 @@ def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0,
     if resid is not None:
         if resid.dtype != torch.float32 or resid.shape != out.shape or resid.stride(0) != out.stride(0):
             raise KernelArgumentError(f"{what}: resid must be float32 with the output's shape and stride")
+    kv = (None, None, None, 0, 0, 0, 0, 0)
+    if kv_scatter is not None:
+        k_pages, v_pages, slots, q_width = kv_scatter
+        num_pages, kv_heads, page_size, head_dim = k_pages.shape
+        if k_pages.dtype != out.dtype or v_pages.dtype != out.dtype or slots.dtype != torch.int32 \
+                or q_width + 2 * kv_heads * head_dim != n:
+            raise KernelArgumentError(f"{what}: cache type or widths do not fit the product")
+        kv = (_p(k_pages), _p(v_pages), _p(slots), q_width, kv_heads * head_dim, head_dim,
+              page_size, num_pages)
     if _RECORDER is not None:
         _check(lib().prb_program_add_gemm(
             _RECORDER.handle, _p(out), None if norm_input is not None else _p(x),
             _p(x) if norm_input is not None else None, _p(gamma), _p(beta), float(eps), _p(w),
             _p(bias), _p(resid), m, n, k, x.stride(0), w.stride(0), out.stride(0), ACT_CODES[act],
-            dtype_code(out.dtype)), what)
+            dtype_code(out.dtype), *kv, _p(status)), what)
         return
     _check(lib().prb_gemm_smallm(
         _p(out), None if norm_input is not None else _p(x),
         _p(x) if norm_input is not None else None, _p(gamma), _p(beta), float(eps), _p(w),
         _p(bias), _p(resid), m, n, k, x.stride(0), w.stride(0), out.stride(0), ACT_CODES[act],
-        dtype_code(out.dtype), _stream()), what)
+        dtype_code(out.dtype), *kv, _p(status), _stream()), what)
 
 
 def attention_generic(out, q, k_pages, v_pages, block_table, seq_of_token, positions, n_tokens,

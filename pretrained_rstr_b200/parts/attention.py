@@ -19,7 +19,7 @@ import torch
 
 from ..csrc import ops
 from ..engine.batch import SINGLE_MAX_Q
-from .interfaces import KVSpec, LayerCache, Mixer
+from .interfaces import KVSpec, LayerCache, Mixer, PositionEncoding
 from .linear import Linear
 from .registry import register_part
 
@@ -52,14 +52,20 @@ class CausalAttention(Mixer):
         t = x.shape[0]
         dtype = self.runtime.dtype
         qkv = ctx.scratch("attn_qkv", (ctx.token_capacity, self.qkv.n_out), dtype)[:t]
-        self.qkv.forward(ctx, h, qkv)
+        group = ctx.groups[cache.group]
+        # With no rotation of keys to wait for, the decode-time product may write the new
+        # keys and values to their cache slots itself.
+        rotates = self.position is not None and \
+            type(self.position).rotate is not PositionEncoding.rotate
+        scatter = (cache.k, cache.v, group.slots, self.q_width) \
+            if cache.writes and not rotates else None
+        appended = self.qkv.forward(ctx, h, qkv, kv_scatter=scatter)
         q = qkv[:, :self.q_width]
         k = qkv[:, self.q_width:self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:]
-        if self.position is not None:
+        if rotates:
             self.position.rotate(ctx, q, k)
-        group = ctx.groups[cache.group]
-        if cache.writes:
+        if cache.writes and not appended:
             ops.kv_append(cache.k, cache.v, k, v, group.slots, t, ctx.status)
         o = ctx.scratch("attn_out", (ctx.token_capacity, self.q_width), dtype)[:t]
         attend(ctx, o, q, cache, group, self.n_head, self.scale, self.window)

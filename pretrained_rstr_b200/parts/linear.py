@@ -44,29 +44,35 @@ class Linear:
         return cls(w, b, runtime)
 
     def forward(self, ctx, a, out: torch.Tensor, act: Optional[str] = None,
-                resid: Optional[torch.Tensor] = None) -> None:
+                resid: Optional[torch.Tensor] = None, kv_scatter=None) -> bool:
         """out = act(a . W^T + bias) (+ resid).  ``out`` may be float32 (then ``resid`` may
         alias it) or the activation type.  ``a`` is a tensor, or a :class:`LazyNorm`: a
         norm that has not run yet, which the decode-time kernel computes in its prologue
-        and every other kernel asks to run first."""
+        and every other kernel asks to run first.  ``kv_scatter`` = (k_pages, v_pages, slots,
+        q_width) offers the kernel the chance to write the key and value columns of a fused
+        QKV product straight to the cache; returns True when it did."""
         m = out.shape[0]
         if self.runtime.dtype == torch.float32:
             ops.gemm_f32(out, _tensor(a), self.weight, self.bias, resid, act)
-            return
+            return False
         # Which kernel (measured on GPT-2-small shapes, see profiles/): up to 16 rows the
         # weight-streaming kernel with the norm fused into it; up to 64 rows the same kernel
         # without the fused norm (every CTA would repeat it) for narrow outputs, the
         # tensor-memory kernel for wide ones; beyond 64 rows the tensor-memory kernel.
         max_rows, max_norm = ops.smallm_limits()
         if m <= max_rows and self.n_in % 8 == 0 and (m <= 16 or self.n_out <= 1024):
+            if kv_scatter is not None and kv_scatter[0].dtype != out.dtype:
+                kv_scatter = None
             if m <= 16 and isinstance(a, LazyNorm) and a.fusable and self.n_in <= max_norm:
                 ops.gemm_smallm(out, self.weight, norm_input=a.x, gamma=a.norm.gamma,
                                 beta=a.norm.beta, eps=a.norm.eps, bias=self.bias, resid=resid,
-                                act=act)
+                                act=act, kv_scatter=kv_scatter, status=ctx.status)
             else:
-                ops.gemm_smallm(out, self.weight, a=_tensor(a), bias=self.bias, resid=resid, act=act)
-            return
+                ops.gemm_smallm(out, self.weight, a=_tensor(a), bias=self.bias, resid=resid,
+                                act=act, kv_scatter=kv_scatter, status=ctx.status)
+            return kv_scatter is not None
         ops.gemm_bf16(out, _tensor(a), self.weight, self.bias, resid, act, status=ctx.status)
+        return False
 
 
 class LazyNorm:

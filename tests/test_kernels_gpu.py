@@ -381,3 +381,30 @@ def test_sample_kernel_greedy_ties_and_nan():
     want = logits.argmax(dim=1).tolist()
     want[1], want[2], want[3] = 77, 123, 50256
     assert out.tolist() == want
+
+
+def test_gemm_smallm_scatters_keys_and_values_to_the_cache():
+    """The decode-time QKV product writes its key and value columns to the cache slots
+    itself; the result equals the product followed by the append kernel."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    m, heads, kv_heads, dh, ps, pages, k = 7, 6, 3, 32, 16, 9, 96
+    q_width, kv_width = heads * dh, kv_heads * dh
+    n = q_width + 2 * kv_width
+    a = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.2).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda", generator=g)
+    slots = torch.tensor([5, ps * 3 + 15, -1, ps * 8, 0, ps * 2 + 1, ps * 8 + 7], dtype=torch.int32,
+                         device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    k1 = torch.zeros(pages, kv_heads, ps, dh, device="cuda", dtype=torch.bfloat16)
+    v1, k2, v2 = torch.zeros_like(k1), torch.zeros_like(k1), torch.zeros_like(k1)
+    out1 = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    out2 = torch.zeros_like(out1)
+    ops.gemm_smallm(out1, w, a=a, bias=bias, kv_scatter=(k1, v1, slots, q_width), status=status)
+    ops.gemm_smallm(out2, w, a=a, bias=bias)
+    ops.kv_append(k2, v2, out2[:, q_width:q_width + kv_width], out2[:, q_width + kv_width:], slots, m,
+                  status)
+    torch.cuda.synchronize()
+    assert torch.equal(out1, out2) and torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert int((k1 != 0).any(dim=-1).sum()) == 6 * kv_heads and status.tolist() == [0, 0, 0, 0]
