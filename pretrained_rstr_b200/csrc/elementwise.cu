@@ -41,26 +41,93 @@ __global__ void layernorm_kernel(elementwise::NormArgs a) {
     elementwise::layernorm_row<O>(a, blockIdx.x, row, scratch);
 }
 
+// Rows that fit a warp's registers (width <= 1024, a multiple of 4): one warp per row, four
+// rows per CTA, 16-byte loads, statistics by shuffles only.  Same two-pass formula.
+template <typename O>
+__global__ void __launch_bounds__(128)
+layernorm_warp_kernel(elementwise::NormArgs a) {
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (r >= a.n_rows) return;
+    O* out = reinterpret_cast<O*>(a.out) + (size_t)r * a.width;
+    const int src = a.rows ? a.rows[r] : r;
+    if (src < 0 || src >= a.n_rows_in) {
+        if (lane == 0) prb_set_status(a.status, PRB_S_ROW_RANGE, r, src, a.n_rows_in);
+        for (int i = lane; i < a.width; i += 32) out[i] = prb_from_float<O>(0.0f);
+        return;
+    }
+    const int nvec = a.width / 4;
+    const float4* x4 = reinterpret_cast<const float4*>(a.x + (size_t)src * a.width);
+    float4 v[8];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = lane + 32 * i;
+        v[i] = idx < nvec ? x4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    const float mean = prb_warp_sum(s) / (float)a.width;
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (lane + 32 * i < nvec) {
+            const float c0 = v[i].x - mean, c1 = v[i].y - mean, c2 = v[i].z - mean,
+                        c3 = v[i].w - mean;
+            q += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+        }
+    }
+    const float inv = 1.0f / sqrtf(prb_warp_sum(q) / (float)a.width + a.eps);
+    const float4* g4 = reinterpret_cast<const float4*>(a.gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(a.beta);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = lane + 32 * i;
+        if (idx < nvec) {
+            const float4 g = g4[idx];
+            const float4 b = a.beta ? b4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float y0 = (v[i].x - mean) * inv * g.x + b.x, y1 = (v[i].y - mean) * inv * g.y + b.y;
+            const float y2 = (v[i].z - mean) * inv * g.z + b.z, y3 = (v[i].w - mean) * inv * g.w + b.w;
+            if constexpr (sizeof(O) == 4) {
+                *reinterpret_cast<float4*>(out + idx * 4) = make_float4(y0, y1, y2, y3);
+            } else {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+                uint2 pk;
+                pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(out + idx * 4) = pk;
+            }
+        }
+    }
+}
+
 PRB_API int prb_layernorm(void* out, const float* x, const float* gamma, const float* beta,
                           const int* rows, int n_rows, int n_rows_in, int width, float eps,
                           int out_dtype, int* status, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width <= 0 || (size_t)width * 4 > 200 * 1024) return PRB_E_SIZE;
+    if (out_dtype != PRB_F32 && out_dtype != PRB_BF16) return PRB_E_DTYPE;
+    elementwise::NormArgs a{out, x, gamma, beta, rows, n_rows, n_rows_in, width, eps, status};
+    const bool aligned = ((uintptr_t)x) % 16 == 0 && ((uintptr_t)out) % 16 == 0 &&
+                         ((uintptr_t)gamma) % 16 == 0 && (!beta || ((uintptr_t)beta) % 16 == 0);
+    if (width % 4 == 0 && width <= 1024 && aligned && n_rows >= 16) {
+        const int blocks = (n_rows + 3) / 4;
+        if (out_dtype == PRB_F32) layernorm_warp_kernel<float><<<blocks, 128, 0, stream>>>(a);
+        else layernorm_warp_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(a);
+        PRB_LAUNCH_CHECK();
+        return 0;
+    }
     const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
     const size_t smem = (size_t)width * sizeof(float);
-    elementwise::NormArgs a{out, x, gamma, beta, rows, n_rows, n_rows_in, width, eps, status};
     if (out_dtype == PRB_F32) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(layernorm_kernel<float>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         layernorm_kernel<float><<<n_rows, threads, smem, stream>>>(a);
-    } else if (out_dtype == PRB_BF16) {
+    } else {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(a);
-    } else {
-        return PRB_E_DTYPE;
     }
     PRB_LAUNCH_CHECK();
     return 0;

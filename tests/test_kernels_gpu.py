@@ -308,7 +308,7 @@ def test_gemm_smallm_rows_do_not_depend_on_the_batch():
 
 
 # ------------------------------------------------------------------------ small kernels
-@pytest.mark.parametrize("rows,width", [(1, 64), (7, 96), (33, 1608), (5, 50000)])
+@pytest.mark.parametrize("rows,width", [(1, 64), (7, 96), (33, 1608), (5, 50000), (40, 768), (17, 64), (300, 1000)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_layernorm(rows, width, out_dtype):
     ops = _ops()
