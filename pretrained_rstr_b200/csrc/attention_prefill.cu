@@ -1,6 +1,6 @@
 // Causal attention for prompt portions over the paged bfloat16 cache, flash style:
 // scores are never written to memory.  One CTA takes 64 consecutive query tokens of one
-// request for one head (4 warps x 16 rows) and walks the keys in tiles of 64 absolute
+// request for one head (two warps x 32 rows, or four x 16 for very large heads) and walks the keys in tiles of 64 absolute
 // positions (tile boundaries at multiples of 64, independent of where the portion
 // starts, so a row's summation order depends on its own position only).  Per tile:
 // S = Q K^T on tensor cores (bf16 inputs, float32 accumulate), scale, mask (causal,
@@ -15,7 +15,6 @@
 namespace {
 constexpr int QT = 64;              // queries per CTA
 constexpr int KT = 64;              // keys per tile
-constexpr int PF_THREADS = 128;
 constexpr int PADE = 8;             // row padding in elements (16 bytes): conflict-free ldmatrix
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -53,8 +52,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&p);
 }
 
-template <int DH>
-__global__ void __launch_bounds__(PF_THREADS)
+// MT: 16-row MMA tiles per warp.  A warp with two tiles (32 query rows) reuses every key
+// and value fragment it reads from shared memory twice, and keeps its query fragments in
+// registers when the head is small; 64 query rows then need only two warps.  Heads too
+// large for that register budget use one tile per warp and four warps.
+template <int DH, int MT>
+__global__ void __launch_bounds__(128 / MT)
 attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
                          const __nv_bfloat16* __restrict__ q, long q_stride,
                          const __nv_bfloat16* __restrict__ k_pages,
@@ -64,8 +67,10 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
                          const int* __restrict__ tile_rows, const int* __restrict__ tile_count,
                          int n_heads, int kv_heads, int page_size, int max_pages, int num_pages,
                          float scale, int window, int* status) {
+    constexpr int THREADS = 128 / MT;
     constexpr int PITCH = DH + PADE;
     constexpr int CHUNKS = DH / 8;                 // 16-byte pieces per row
+    constexpr bool Q_IN_REGS = DH <= 64;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [QT][PITCH]
     __nv_bfloat16* ks = qs + QT * PITCH;                                     // [2][KT][PITCH]
@@ -90,7 +95,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
     const int tile_first = lo_all / KT, tile_last = pos_last / KT;
 
     // ---- Q tile -> shared memory (rows beyond `rows` are zero)
-    for (int c = threadIdx.x; c < QT * CHUNKS; c += PF_THREADS) {
+    for (int c = threadIdx.x; c < QT * CHUNKS; c += THREADS) {
         const int r = c / CHUNKS, piece = c % CHUNKS;
         const bool valid = r < rows;
         const __nv_bfloat16* src = q + (size_t)(row0 + (valid ? r : 0)) * q_stride +
@@ -100,7 +105,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
     auto load_kv = [&](int tile, int buf) {
         __nv_bfloat16* kd = ks + buf * KT * PITCH;
         __nv_bfloat16* vd = vs + buf * KT * PITCH;
-        for (int c = threadIdx.x; c < KT * CHUNKS; c += PF_THREADS) {
+        for (int c = threadIdx.x; c < KT * CHUNKS; c += THREADS) {
             const int r = c / CHUNKS, piece = c % CHUNKS;
             const int j = tile * KT + r;
             bool valid = j >= lo_all && j <= pos_last;
@@ -122,14 +127,28 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
     load_kv(tile_first, 0);
     cp_async_commit();
 
-    float o[DH / 8][4];
+    float o[MT][DH / 8][4];
 #pragma unroll
-    for (int i = 0; i < DH / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-    const int qr = warp * 16 + (lane >> 2);        // this thread's first query row in the tile
-    const int qpos[2] = {pos0 + qr, pos0 + qr + 8};
-    const bool qvalid[2] = {qr < rows, qr + 8 < rows};
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < DH / 8; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.0f;
+    float m_run[MT][2], l_run[MT][2];
+    int qpos[MT][2];
+    bool qvalid[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int qr = warp * (16 * MT) + mt * 16 + (lane >> 2) + rr * 8;
+            m_run[mt][rr] = -INFINITY;
+            l_run[mt][rr] = 0.0f;
+            qpos[mt][rr] = pos0 + qr;
+            qvalid[mt][rr] = qr < rows;
+        }
     const float sl2 = scale * 1.4426950408889634f;  // scores are handled in log2 units
+    const int warp_pos_min = pos0 + warp * (16 * MT);          // lowest query position of this warp
+    uint32_t qf[Q_IN_REGS ? MT : 1][Q_IN_REGS ? DH / 16 : 1][4];
+    bool q_loaded = false;
 
     for (int tile = tile_first; tile <= tile_last; ++tile) {
         const int buf = (tile - tile_first) & 1;
@@ -141,103 +160,146 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
             cp_async_wait<0>();
         }
         __syncthreads();
+        if (Q_IN_REGS && !q_loaded) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int kk = 0; kk < DH / 16; ++kk)
+                    ldmatrix_x4(qf[Q_IN_REGS ? mt : 0][Q_IN_REGS ? kk : 0],
+                                qs + (warp * (16 * MT) + mt * 16 + (lane & 15)) * PITCH + kk * 16 +
+                                    (lane >> 4) * 8);
+            q_loaded = true;
+        }
         const __nv_bfloat16* kb = ks + buf * KT * PITCH;
         const __nv_bfloat16* vb = vs + buf * KT * PITCH;
 
-        // ---- S = Q K^T for this warp's 16 rows x 64 keys
-        float s[KT / 8][4];
+        // ---- S = Q K^T for this warp's rows x 64 keys
+        float s[MT][KT / 8][4];
 #pragma unroll
-        for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < KT / 8; ++i) s[mt][i][0] = s[mt][i][1] = s[mt][i][2] = s[mt][i][3] = 0.0f;
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
-            uint32_t a[4];
-            ldmatrix_x4(a, qs + (warp * 16 + (lane & 15)) * PITCH + kk * 16 + (lane >> 4) * 8);
+            uint32_t a[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                if constexpr (Q_IN_REGS) {
+                    a[mt][0] = qf[mt][kk][0]; a[mt][1] = qf[mt][kk][1];
+                    a[mt][2] = qf[mt][kk][2]; a[mt][3] = qf[mt][kk][3];
+                } else {
+                    ldmatrix_x4(a[mt], qs + (warp * (16 * MT) + mt * 16 + (lane & 15)) * PITCH +
+                                           kk * 16 + (lane >> 4) * 8);
+                }
+            }
 #pragma unroll
             for (int nt = 0; nt < KT / 16; ++nt) {
                 uint32_t bfr[4];
                 const int mi = lane >> 3, r = lane & 7;
                 ldmatrix_x4(bfr, kb + (nt * 16 + (mi >> 1) * 8 + r) * PITCH + kk * 16 + (mi & 1) * 8);
-                mma_bf16(s[2 * nt], a, bfr[0], bfr[1]);
-                mma_bf16(s[2 * nt + 1], a, bfr[2], bfr[3]);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma_bf16(s[mt][2 * nt], a[mt], bfr[0], bfr[1]);
+                    mma_bf16(s[mt][2 * nt + 1], a[mt], bfr[2], bfr[3]);
+                }
             }
         }
-        // ---- scale, mask, online softmax (two rows per thread)
-        float mx[2] = {-INFINITY, -INFINITY};
+        // ---- scale, mask, online softmax (two rows per thread and tile)
+        // a tile whose keys all lie at or before the warp's first query needs no mask
+        const bool need_mask = window > 0 || tile * KT + KT - 1 > warp_pos_min ||
+                               rows < QT;
 #pragma unroll
-        for (int nt = 0; nt < KT / 8; ++nt) {
+        for (int mt = 0; mt < MT; ++mt) {
+            float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int rr = e >> 1;
-                const int j = tile * KT + nt * 8 + (lane & 3) * 2 + (e & 1);
-                const bool vis = qvalid[rr] && j <= qpos[rr] &&
-                                 (window <= 0 || j > qpos[rr] - window);
-                const float v = vis ? s[nt][e] * sl2 : -INFINITY;
-                s[nt][e] = v;
-                mx[rr] = fmaxf(mx[rr], v);
+            for (int nt = 0; nt < KT / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int rr = e >> 1;
+                    float v = s[mt][nt][e] * sl2;
+                    if (need_mask) {
+                        const int j = tile * KT + nt * 8 + (lane & 3) * 2 + (e & 1);
+                        const bool vis = qvalid[mt][rr] && j <= qpos[mt][rr] &&
+                                         (window <= 0 || j > qpos[mt][rr] - window);
+                        v = vis ? v : -INFINITY;
+                    }
+                    s[mt][nt][e] = v;
+                    mx[rr] = fmaxf(mx[rr], v);
+                }
             }
-        }
-        float corr[2];
+            float corr[2];
 #pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-            mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
-            mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
-            const float m_new = fmaxf(m_run[rr], mx[rr]);
-            corr[rr] = (m_run[rr] == -INFINITY) ? 0.0f : exp2f(m_run[rr] - m_new);
-            m_run[rr] = m_new;
-        }
-        float rs[2] = {0.0f, 0.0f};
-#pragma unroll
-        for (int nt = 0; nt < KT / 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int rr = e >> 1;
-                const float p = (s[nt][e] == -INFINITY) ? 0.0f : exp2f(s[nt][e] - m_run[rr]);
-                s[nt][e] = p;
-                rs[rr] += p;
+            for (int rr = 0; rr < 2; ++rr) {
+                mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+                mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+                const float m_new = fmaxf(m_run[mt][rr], mx[rr]);
+                corr[rr] = (m_run[mt][rr] == -INFINITY) ? 0.0f : exp2f(m_run[mt][rr] - m_new);
+                m_run[mt][rr] = m_new;
             }
-        }
+            float rs[2] = {0.0f, 0.0f};
 #pragma unroll
-        for (int rr = 0; rr < 2; ++rr) l_run[rr] = l_run[rr] * corr[rr] + rs[rr];
+            for (int nt = 0; nt < KT / 8; ++nt) {
 #pragma unroll
-        for (int i = 0; i < DH / 8; ++i) {
-            o[i][0] *= corr[0]; o[i][1] *= corr[0];
-            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+                for (int e = 0; e < 4; ++e) {
+                    const int rr = e >> 1;
+                    const float p = (s[mt][nt][e] == -INFINITY) ? 0.0f
+                                                                 : exp2f(s[mt][nt][e] - m_run[mt][rr]);
+                    s[mt][nt][e] = p;
+                    rs[rr] += p;
+                }
+            }
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) l_run[mt][rr] = l_run[mt][rr] * corr[rr] + rs[rr];
+#pragma unroll
+            for (int i = 0; i < DH / 8; ++i) {
+                o[mt][i][0] *= corr[0]; o[mt][i][1] *= corr[0];
+                o[mt][i][2] *= corr[1]; o[mt][i][3] *= corr[1];
+            }
         }
         // ---- O += P V
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
-            uint32_t a[4];
-            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            uint32_t a[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                a[mt][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+                a[mt][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+                a[mt][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+                a[mt][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+            }
 #pragma unroll
             for (int dt = 0; dt < DH / 16; ++dt) {
                 uint32_t bfr[4];
                 const int mi = lane >> 3, r = lane & 7;
                 ldmatrix_x4_trans(bfr, vb + (kk * 16 + (mi & 1) * 8 + r) * PITCH + dt * 16 +
                                             (mi >> 1) * 8);
-                mma_bf16(o[2 * dt], a, bfr[0], bfr[1]);
-                mma_bf16(o[2 * dt + 1], a, bfr[2], bfr[3]);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma_bf16(o[mt][2 * dt], a[mt], bfr[0], bfr[1]);
+                    mma_bf16(o[mt][2 * dt + 1], a[mt], bfr[2], bfr[3]);
+                }
             }
         }
         __syncthreads();      // everyone is done with this buffer before it is refilled
     }
     // ---- normalise and store
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-        l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 1);
-        l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 2);
-    }
+    for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-        if (!qvalid[rr]) continue;
-        const float inv = l_run[rr] > 0.0f ? 1.0f / l_run[rr] : 0.0f;
-        __nv_bfloat16* dst = out + (size_t)(row0 + qr + rr * 8) * out_stride + (size_t)h * DH;
+        for (int rr = 0; rr < 2; ++rr) {
+            float l = l_run[mt][rr];
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            if (!qvalid[mt][rr]) continue;
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            const int qr = warp * (16 * MT) + mt * 16 + (lane >> 2) + rr * 8;
+            __nv_bfloat16* dst = out + (size_t)(row0 + qr) * out_stride + (size_t)h * DH;
 #pragma unroll
-        for (int i = 0; i < DH / 8; ++i) {
-            const __nv_bfloat162 p = __floats2bfloat162_rn(o[i][2 * rr] * inv, o[i][2 * rr + 1] * inv);
-            *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + (lane & 3) * 2) = p;
+            for (int i = 0; i < DH / 8; ++i) {
+                const __nv_bfloat162 p =
+                    __floats2bfloat162_rn(o[mt][i][2 * rr] * inv, o[mt][i][2 * rr + 1] * inv);
+                *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + (lane & 3) * 2) = p;
+            }
         }
     }
 }
@@ -249,16 +311,17 @@ int launch_prefill(void* out, long out_stride, const void* q, long q_stride, con
                    const int* tile_count, int n_tiles, int n_heads, int kv_heads, int page_size,
                    int max_pages, int num_pages, float scale, int window, int* status,
                    cudaStream_t stream) {
+    constexpr int MT = DH <= 128 ? 2 : 1;
     constexpr size_t smem = (size_t)(QT + 4 * KT) * (DH + PADE) * 2;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DH>,
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DH, MT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
     configured = true;
     dim3 grid(n_tiles, n_heads);
-    attention_prefill_kernel<DH><<<grid, PF_THREADS, smem, stream>>>(
+    attention_prefill_kernel<DH, MT><<<grid, 128 / MT, smem, stream>>>(
         (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, positions,
         tile_req, tile_row0, tile_rows, tile_count, n_heads, kv_heads, page_size, max_pages,
