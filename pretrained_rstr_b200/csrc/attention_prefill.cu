@@ -311,7 +311,7 @@ int launch_prefill(void* out, long out_stride, const void* q, long q_stride, con
                    const int* tile_count, int n_tiles, int n_heads, int kv_heads, int page_size,
                    int max_pages, int num_pages, float scale, int window, int* status,
                    cudaStream_t stream) {
-    constexpr int MT = DH <= 128 ? 2 : 1;
+    constexpr int MT = 1;      // two tiles per warp measured slower (too few warps per SM)
     constexpr size_t smem = (size_t)(QT + 4 * KT) * (DH + PADE) * 2;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
