@@ -243,8 +243,50 @@ def profile_decode(batch: int) -> int:
     return 0
 
 
+def profile_prefill() -> int:
+    """Small workload for a profiler: one step of 2 x 1,000 prompt tokens, launched kernel
+    by kernel, with the torch profiler's kernel table printed."""
+    import random
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from pretrained_rstr_b200 import load_lm
+    from pretrained_rstr_b200.config import GPT2Config
+    from pretrained_rstr_b200.engine.batch import Entry
+    from pretrained_rstr_b200.weights import make_random_model
+    tmp = tempfile.mkdtemp(prefix="prb200_prof_")
+    try:
+        make_random_model(tmp, GPT2Config.from_dict(dict(SMALL)), seed=2, dtype=torch.bfloat16)
+        m = load_lm(tmp, gpu=True, dtype="bfloat16", max_lanes=8, max_batched_tokens=2048,
+                    prefill_chunk=1024, share_prefixes=False)
+    finally:
+        import shutil
+        shutil.rmtree(tmp, ignore_errors=True)
+    runner, cache = m.loaded.runner, m.loaded.cache
+    runner.use_graphs = False
+    rng = random.Random(0)
+
+    def one_step(tag):
+        entries = []
+        for i in range(2):
+            cache.open((tag, i))
+            entries.append(Entry((tag, i), [rng.randrange(SMALL["vocab_size"]) for _ in range(1000)],
+                                 [999]))
+        runner.step(entries)
+        torch.cuda.synchronize()
+        for e in entries:
+            cache.close(e.rid)
+
+    one_step("warm")
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        one_step("timed")
+    print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=12,
+                                    max_name_column_width=70))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--profile-prefill", action="store_true")
     ap.add_argument("--profile-gemm", default=None, metavar="M,N,K")
     ap.add_argument("--profile-decode", type=int, default=None, metavar="BATCH")
     ap.add_argument("--gpus", type=int, default=1)
@@ -262,6 +304,8 @@ def main() -> int:
         return profile_gemm(args.profile_gemm)
     if args.profile_decode:
         return profile_decode(args.profile_decode)
+    if args.profile_prefill:
+        return profile_prefill()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -281,6 +325,7 @@ def main() -> int:
     pk = peaks()
     vocab = raw["vocab_size"]
     steps, warmup, ctx_len = args.steps, args.warmup, min(args.context, raw["n_positions"])
+    steps = max(1, min(steps, ctx_len - warmup - 64 - 3 - 16))     # every request must fit its context
     tmp = tempfile.mkdtemp(prefix="prb200_bench_")
     try:
         make_random_model(tmp, cfg, seed=2, dtype=torch.bfloat16)
