@@ -364,14 +364,16 @@ def main() -> int:
 
     # ---- decode
     points = {}
+    clocks = ClockSampler()
+    clocks.__enter__()
     for b in (1, 64):
         ms, wall, _l, _c, _h = timed_decode(engine, m.loaded, b, ctx_len, steps, warmup, vocab, b)
         points[f"decode_b{b}"] = b / (statistics.mean(ms) / 1e3)
         points[f"decode_b{b}_ms"] = [round(min(ms), 4), round(statistics.median(ms), 4),
                                      round(max(ms), 4)]
-    with ClockSampler() as clocks:
-        ms, wall, launches, mean_ctx, h2d = timed_decode(engine, m.loaded, args.batch, ctx_len,
-                                                        steps, warmup, vocab, 5)
+    ms, wall, launches, mean_ctx, h2d = timed_decode(engine, m.loaded, args.batch, ctx_len,
+                                                    steps, warmup, vocab, 5)
+    clocks.__exit__(None, None, None)
     step_ms = statistics.mean(ms)
     value = args.batch / (step_ms / 1e3)
     bytes_step = model_bytes(raw) + args.batch * mean_ctx * kv_bytes_per_token(raw)

@@ -148,6 +148,12 @@ def launch_count() -> int:
     return _LAUNCHES
 
 
+def add_launches(n: int) -> None:
+    """Account for kernels launched by replaying a CUDA graph that holds ``n`` of them."""
+    global _LAUNCHES
+    _LAUNCHES += int(n)
+
+
 def _check(code: int, what: str) -> None:
     global _LAUNCHES
     if code == 0:

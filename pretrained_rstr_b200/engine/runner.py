@@ -132,16 +132,21 @@ class ModelRunner:
         hit = self._graphs.get(key)
         if hit is not None:
             hit[0].replay()
+            ops.add_launches(hit[2])
             return hit[1]
         seen = self._seen.get(key, 0)
         self._seen[key] = seen + 1
         if seen == 0:
             return self.model.forward(ctx)
         graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
         with torch.cuda.graph(graph):
             logits = self.model.forward(ctx)
-        self._graphs[key] = (graph, logits)
+        kernels = ops.launch_count() - before      # recorded, not run: counted at each replay
+        ops.add_launches(-kernels)
+        self._graphs[key] = (graph, logits, kernels)
         graph.replay()
+        ops.add_launches(kernels)
         return logits
 
     def prepare(self, entries: Sequence[Entry]) -> StepContext:
