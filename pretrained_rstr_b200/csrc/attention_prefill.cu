@@ -1,6 +1,6 @@
 // Causal attention for prompt portions over the paged bfloat16 cache, flash style:
 // scores are never written to memory.  One CTA takes 64 consecutive query tokens of one
-// request for one head (two warps x 32 rows, or four x 16 for very large heads) and walks the keys in tiles of 64 absolute
+// request for one head (warp groups of 4 warps x 16 rows) and walks the keys in tiles of 64 absolute
 // positions (tile boundaries at multiples of 64, independent of where the portion
 // starts, so a row's summation order depends on its own position only).  Per tile:
 // S = Q K^T on tensor cores (bf16 inputs, float32 accumulate), scale, mask (causal,
@@ -52,12 +52,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&p);
 }
 
-// MT: 16-row MMA tiles per warp.  A warp with two tiles (32 query rows) reuses every key
-// and value fragment it reads from shared memory twice, and keeps its query fragments in
-// registers when the head is small; 64 query rows then need only two warps.  Heads too
-// large for that register budget use one tile per warp and four warps.
-template <int DH, int MT>
-__global__ void __launch_bounds__(128 / MT)
+__device__ __forceinline__ void group_sync(int group) {
+    // barrier of the 128 threads of one warp group (ids 1.. leave 0 to __syncthreads)
+    asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
+}
+
+// G warp groups of four warps share the key tiles of one 64-query tile: group g takes
+// tiles first+g, first+g+G, ... with its own running softmax state and its own buffers,
+// and the groups' results are merged (in group order) at the end.  The kernel lasts as
+// long as its longest chain of key tiles, and this divides that chain by G.
+template <int DH, int G>
+__global__ void __launch_bounds__(128 * G)
 attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
                          const __nv_bfloat16* __restrict__ q, long q_stride,
                          const __nv_bfloat16* __restrict__ k_pages,
@@ -67,17 +72,20 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
                          const int* __restrict__ tile_rows, const int* __restrict__ tile_count,
                          int n_heads, int kv_heads, int page_size, int max_pages, int num_pages,
                          float scale, int window, int* status) {
-    constexpr int THREADS = 128 / MT;
     constexpr int PITCH = DH + PADE;
     constexpr int CHUNKS = DH / 8;                 // 16-byte pieces per row
-    constexpr bool Q_IN_REGS = DH <= 64;
+    constexpr int GROUP_ELEMS = (QT + 4 * KT) * PITCH;
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [QT][PITCH]
-    __nv_bfloat16* ks = qs + QT * PITCH;                                     // [2][KT][PITCH]
-    __nv_bfloat16* vs = ks + 2 * KT * PITCH;                                 // [2][KT][PITCH]
+    const int group = threadIdx.x >> 7, tid = threadIdx.x & 127;
+    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(smem_raw) + (size_t)group * GROUP_ELEMS;
+    __nv_bfloat16* qs = base;                      // [QT][PITCH]       (a copy per group)
+    __nv_bfloat16* ks = qs + QT * PITCH;           // [2][KT][PITCH]
+    __nv_bfloat16* vs = ks + 2 * KT * PITCH;       // [2][KT][PITCH]
 
-    const int item = blockIdx.x;
-    if (tile_count != nullptr && item >= *tile_count) return;
+    // the longest tiles (late query positions) first
+    const int n_items = tile_count != nullptr ? *tile_count : (int)gridDim.x;
+    if ((int)blockIdx.x >= n_items) return;
+    const int item = n_items - 1 - blockIdx.x;
     const int h = blockIdx.y;
     const int b = tile_req[item];
     const int row0 = tile_row0[item];              // first token row of this tile
@@ -90,12 +98,12 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
     }
     const int hk = h / (n_heads / kv_heads);
     const int* table = block_table + (size_t)b * max_pages;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = tid >> 5, lane = tid & 31;    // warp within the group
     const int lo_all = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
     const int tile_first = lo_all / KT, tile_last = pos_last / KT;
 
-    // ---- Q tile -> shared memory (rows beyond `rows` are zero)
-    for (int c = threadIdx.x; c < QT * CHUNKS; c += THREADS) {
+    // ---- Q tile -> this group's shared memory (rows beyond `rows` are zero)
+    for (int c = tid; c < QT * CHUNKS; c += 128) {
         const int r = c / CHUNKS, piece = c % CHUNKS;
         const bool valid = r < rows;
         const __nv_bfloat16* src = q + (size_t)(row0 + (valid ? r : 0)) * q_stride +
@@ -105,7 +113,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
     auto load_kv = [&](int tile, int buf) {
         __nv_bfloat16* kd = ks + buf * KT * PITCH;
         __nv_bfloat16* vd = vs + buf * KT * PITCH;
-        for (int c = threadIdx.x; c < KT * CHUNKS; c += THREADS) {
+        for (int c = tid; c < KT * CHUNKS; c += 128) {
             const int r = c / CHUNKS, piece = c % CHUNKS;
             const int j = tile * KT + r;
             bool valid = j >= lo_all && j <= pos_last;
@@ -124,182 +132,175 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
             cp_async16(vd + r * PITCH + piece * 8, v_pages + off, valid);
         }
     };
-    load_kv(tile_first, 0);
+    const int my_first = tile_first + group;
+    if (my_first <= tile_last) load_kv(my_first, 0);
     cp_async_commit();
 
-    float o[MT][DH / 8][4];
+    float o[DH / 8][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int i = 0; i < DH / 8; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.0f;
-    float m_run[MT][2], l_run[MT][2];
-    int qpos[MT][2];
-    bool qvalid[MT][2];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-            const int qr = warp * (16 * MT) + mt * 16 + (lane >> 2) + rr * 8;
-            m_run[mt][rr] = -INFINITY;
-            l_run[mt][rr] = 0.0f;
-            qpos[mt][rr] = pos0 + qr;
-            qvalid[mt][rr] = qr < rows;
-        }
+    for (int i = 0; i < DH / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    const int qr = warp * 16 + (lane >> 2);        // this thread's first query row in the tile
+    const int qpos[2] = {pos0 + qr, pos0 + qr + 8};
+    const bool qvalid[2] = {qr < rows, qr + 8 < rows};
     const float sl2 = scale * 1.4426950408889634f;  // scores are handled in log2 units
-    const int warp_pos_min = pos0 + warp * (16 * MT);          // lowest query position of this warp
-    uint32_t qf[Q_IN_REGS ? MT : 1][Q_IN_REGS ? DH / 16 : 1][4];
-    bool q_loaded = false;
+    const int warp_pos_min = pos0 + warp * 16;
 
-    for (int tile = tile_first; tile <= tile_last; ++tile) {
-        const int buf = (tile - tile_first) & 1;
-        if (tile < tile_last) {
-            load_kv(tile + 1, buf ^ 1);
+    int it = 0;
+    for (int tile = my_first; tile <= tile_last; tile += G, ++it) {
+        const int buf = it & 1;
+        if (tile + G <= tile_last) {
+            load_kv(tile + G, buf ^ 1);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
         }
-        __syncthreads();
-        if (Q_IN_REGS && !q_loaded) {
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                for (int kk = 0; kk < DH / 16; ++kk)
-                    ldmatrix_x4(qf[Q_IN_REGS ? mt : 0][Q_IN_REGS ? kk : 0],
-                                qs + (warp * (16 * MT) + mt * 16 + (lane & 15)) * PITCH + kk * 16 +
-                                    (lane >> 4) * 8);
-            q_loaded = true;
-        }
+        group_sync(group);
         const __nv_bfloat16* kb = ks + buf * KT * PITCH;
         const __nv_bfloat16* vb = vs + buf * KT * PITCH;
 
-        // ---- S = Q K^T for this warp's rows x 64 keys
-        float s[MT][KT / 8][4];
+        // ---- S = Q K^T for this warp's 16 rows x 64 keys
+        float s[KT / 8][4];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int i = 0; i < KT / 8; ++i) s[mt][i][0] = s[mt][i][1] = s[mt][i][2] = s[mt][i][3] = 0.0f;
+        for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
-            uint32_t a[MT][4];
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                if constexpr (Q_IN_REGS) {
-                    a[mt][0] = qf[mt][kk][0]; a[mt][1] = qf[mt][kk][1];
-                    a[mt][2] = qf[mt][kk][2]; a[mt][3] = qf[mt][kk][3];
-                } else {
-                    ldmatrix_x4(a[mt], qs + (warp * (16 * MT) + mt * 16 + (lane & 15)) * PITCH +
-                                           kk * 16 + (lane >> 4) * 8);
-                }
-            }
+            uint32_t a[4];
+            ldmatrix_x4(a, qs + (warp * 16 + (lane & 15)) * PITCH + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
             for (int nt = 0; nt < KT / 16; ++nt) {
                 uint32_t bfr[4];
                 const int mi = lane >> 3, r = lane & 7;
                 ldmatrix_x4(bfr, kb + (nt * 16 + (mi >> 1) * 8 + r) * PITCH + kk * 16 + (mi & 1) * 8);
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    mma_bf16(s[mt][2 * nt], a[mt], bfr[0], bfr[1]);
-                    mma_bf16(s[mt][2 * nt + 1], a[mt], bfr[2], bfr[3]);
-                }
+                mma_bf16(s[2 * nt], a, bfr[0], bfr[1]);
+                mma_bf16(s[2 * nt + 1], a, bfr[2], bfr[3]);
             }
         }
-        // ---- scale, mask, online softmax (two rows per thread and tile)
-        // a tile whose keys all lie at or before the warp's first query needs no mask
-        const bool need_mask = window > 0 || tile * KT + KT - 1 > warp_pos_min ||
-                               rows < QT;
+        // ---- scale, mask, online softmax (two rows per thread); a tile whose keys all lie
+        // at or before the warp's first query needs no mask
+        const bool need_mask = window > 0 || tile * KT + KT - 1 > warp_pos_min || rows < QT;
+        float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            float mx[2] = {-INFINITY, -INFINITY};
+        for (int nt = 0; nt < KT / 8; ++nt) {
 #pragma unroll
-            for (int nt = 0; nt < KT / 8; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int rr = e >> 1;
-                    float v = s[mt][nt][e] * sl2;
-                    if (need_mask) {
-                        const int j = tile * KT + nt * 8 + (lane & 3) * 2 + (e & 1);
-                        const bool vis = qvalid[mt][rr] && j <= qpos[mt][rr] &&
-                                         (window <= 0 || j > qpos[mt][rr] - window);
-                        v = vis ? v : -INFINITY;
-                    }
-                    s[mt][nt][e] = v;
-                    mx[rr] = fmaxf(mx[rr], v);
+            for (int e = 0; e < 4; ++e) {
+                const int rr = e >> 1;
+                float v = s[nt][e] * sl2;
+                if (need_mask) {
+                    const int j = tile * KT + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const bool vis = qvalid[rr] && j <= qpos[rr] &&
+                                     (window <= 0 || j > qpos[rr] - window);
+                    v = vis ? v : -INFINITY;
                 }
+                s[nt][e] = v;
+                mx[rr] = fmaxf(mx[rr], v);
             }
-            float corr[2];
+        }
+        float corr[2];
 #pragma unroll
-            for (int rr = 0; rr < 2; ++rr) {
-                mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
-                mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
-                const float m_new = fmaxf(m_run[mt][rr], mx[rr]);
-                corr[rr] = (m_run[mt][rr] == -INFINITY) ? 0.0f : exp2f(m_run[mt][rr] - m_new);
-                m_run[mt][rr] = m_new;
+        for (int rr = 0; rr < 2; ++rr) {
+            mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+            mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+            const float m_new = fmaxf(m_run[rr], mx[rr]);
+            corr[rr] = (m_run[rr] == -INFINITY) ? 0.0f : exp2f(m_run[rr] - m_new);
+            m_run[rr] = m_new;
+        }
+        float rs[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int rr = e >> 1;
+                const float p = (s[nt][e] == -INFINITY) ? 0.0f : exp2f(s[nt][e] - m_run[rr]);
+                s[nt][e] = p;
+                rs[rr] += p;
             }
-            float rs[2] = {0.0f, 0.0f};
+        }
 #pragma unroll
-            for (int nt = 0; nt < KT / 8; ++nt) {
+        for (int rr = 0; rr < 2; ++rr) l_run[rr] = l_run[rr] * corr[rr] + rs[rr];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int rr = e >> 1;
-                    const float p = (s[mt][nt][e] == -INFINITY) ? 0.0f
-                                                                 : exp2f(s[mt][nt][e] - m_run[mt][rr]);
-                    s[mt][nt][e] = p;
-                    rs[rr] += p;
-                }
-            }
-#pragma unroll
-            for (int rr = 0; rr < 2; ++rr) l_run[mt][rr] = l_run[mt][rr] * corr[rr] + rs[rr];
-#pragma unroll
-            for (int i = 0; i < DH / 8; ++i) {
-                o[mt][i][0] *= corr[0]; o[mt][i][1] *= corr[0];
-                o[mt][i][2] *= corr[1]; o[mt][i][3] *= corr[1];
-            }
+        for (int i = 0; i < DH / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
         }
         // ---- O += P V
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk) {
-            uint32_t a[MT][4];
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                a[mt][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
-                a[mt][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
-                a[mt][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
-                a[mt][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
-            }
+            uint32_t a[4];
+            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
             for (int dt = 0; dt < DH / 16; ++dt) {
                 uint32_t bfr[4];
                 const int mi = lane >> 3, r = lane & 7;
                 ldmatrix_x4_trans(bfr, vb + (kk * 16 + (mi & 1) * 8 + r) * PITCH + dt * 16 +
                                             (mi >> 1) * 8);
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    mma_bf16(o[mt][2 * dt], a[mt], bfr[0], bfr[1]);
-                    mma_bf16(o[mt][2 * dt + 1], a[mt], bfr[2], bfr[3]);
-                }
+                mma_bf16(o[2 * dt], a, bfr[0], bfr[1]);
+                mma_bf16(o[2 * dt + 1], a, bfr[2], bfr[3]);
             }
         }
-        __syncthreads();      // everyone is done with this buffer before it is refilled
+        group_sync(group);    // the group is done with this buffer before it is refilled
+    }
+    cp_async_wait<0>();       // a group without tiles still has its Q copies in flight
+
+    // ---- merge the groups (in order 1, 2, ...) into group 0, through shared memory
+    if constexpr (G > 1) {
+        constexpr int PER_THREAD = DH / 2 + 4;     // o values, then m and l of two rows
+        float* mine = reinterpret_cast<float*>(base) + (size_t)tid * PER_THREAD;
+        group_sync(group);
+        if (group > 0) {
+#pragma unroll
+            for (int i = 0; i < DH / 8; ++i) {
+                mine[4 * i] = o[i][0]; mine[4 * i + 1] = o[i][1];
+                mine[4 * i + 2] = o[i][2]; mine[4 * i + 3] = o[i][3];
+            }
+            mine[DH / 2] = m_run[0]; mine[DH / 2 + 1] = m_run[1];
+            mine[DH / 2 + 2] = l_run[0]; mine[DH / 2 + 3] = l_run[1];
+        }
+        __syncthreads();
+        if (group > 0) return;
+#pragma unroll
+        for (int g = 1; g < G; ++g) {
+            const float* other = reinterpret_cast<const float*>(
+                                     reinterpret_cast<__nv_bfloat16*>(smem_raw) + (size_t)g * GROUP_ELEMS) +
+                                 (size_t)tid * PER_THREAD;
+            float c_me[2], c_ot[2];
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const float mo = other[DH / 2 + rr];
+                const float mn = fmaxf(m_run[rr], mo);
+                c_me[rr] = (m_run[rr] == -INFINITY) ? 0.0f : exp2f(m_run[rr] - mn);
+                c_ot[rr] = (mo == -INFINITY) ? 0.0f : exp2f(mo - mn);
+                l_run[rr] = l_run[rr] * c_me[rr] + other[DH / 2 + 2 + rr] * c_ot[rr];
+                m_run[rr] = mn;
+            }
+#pragma unroll
+            for (int i = 0; i < DH / 8; ++i) {
+                o[i][0] = o[i][0] * c_me[0] + other[4 * i] * c_ot[0];
+                o[i][1] = o[i][1] * c_me[0] + other[4 * i + 1] * c_ot[0];
+                o[i][2] = o[i][2] * c_me[1] + other[4 * i + 2] * c_ot[1];
+                o[i][3] = o[i][3] * c_me[1] + other[4 * i + 3] * c_ot[1];
+            }
+        }
     }
     // ---- normalise and store
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
+    for (int rr = 0; rr < 2; ++rr) {
+        l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 1);
+        l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 2);
+    }
 #pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-            float l = l_run[mt][rr];
-            l += __shfl_xor_sync(0xffffffffu, l, 1);
-            l += __shfl_xor_sync(0xffffffffu, l, 2);
-            if (!qvalid[mt][rr]) continue;
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            const int qr = warp * (16 * MT) + mt * 16 + (lane >> 2) + rr * 8;
-            __nv_bfloat16* dst = out + (size_t)(row0 + qr) * out_stride + (size_t)h * DH;
+    for (int rr = 0; rr < 2; ++rr) {
+        if (!qvalid[rr]) continue;
+        const float inv = l_run[rr] > 0.0f ? 1.0f / l_run[rr] : 0.0f;
+        __nv_bfloat16* dst = out + (size_t)(row0 + qr + rr * 8) * out_stride + (size_t)h * DH;
 #pragma unroll
-            for (int i = 0; i < DH / 8; ++i) {
-                const __nv_bfloat162 p =
-                    __floats2bfloat162_rn(o[mt][i][2 * rr] * inv, o[mt][i][2 * rr + 1] * inv);
-                *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + (lane & 3) * 2) = p;
-            }
+        for (int i = 0; i < DH / 8; ++i) {
+            const __nv_bfloat162 p = __floats2bfloat162_rn(o[i][2 * rr] * inv, o[i][2 * rr + 1] * inv);
+            *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + (lane & 3) * 2) = p;
         }
     }
 }
@@ -311,17 +312,17 @@ int launch_prefill(void* out, long out_stride, const void* q, long q_stride, con
                    const int* tile_count, int n_tiles, int n_heads, int kv_heads, int page_size,
                    int max_pages, int num_pages, float scale, int window, int* status,
                    cudaStream_t stream) {
-    constexpr int MT = 1;      // two tiles per warp measured slower (too few warps per SM)
-    constexpr size_t smem = (size_t)(QT + 4 * KT) * (DH + PADE) * 2;
+    constexpr int G = DH <= 128 ? 2 : 1;           // warp groups (shared memory allows two)
+    constexpr size_t smem = (size_t)G * (QT + 4 * KT) * (DH + PADE) * 2;
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DH, MT>,
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DH, G>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
     configured = true;
     dim3 grid(n_tiles, n_heads);
-    attention_prefill_kernel<DH, MT><<<grid, 128 / MT, smem, stream>>>(
+    attention_prefill_kernel<DH, G><<<grid, 128 * G, smem, stream>>>(
         (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, positions,
         tile_req, tile_row0, tile_rows, tile_count, n_heads, kv_heads, page_size, max_pages,
