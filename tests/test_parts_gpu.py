@@ -337,3 +337,184 @@ def test_toy_architecture_with_state_and_repeated_layer(tmp_path, dtype):
         err = float((row - oracle[rid][p]).abs().max())
         assert err <= tol, f"request {rid} position {p}: {err:.3e}"
     assert lm.cache.slots.free_count == 2
+
+
+# ------------------------------------------------- groups: a windowed layer, grouped heads
+def _register_windowed():
+    """A second toy architecture out of the framework's own parts: layer 0 attends over all
+    keys with grouped key/value heads, layer 1 over a window of 40 keys.  The two layers
+    need different caches, so they get page pools and block tables of their own, and the
+    windowed one gives pages back while a request is still running."""
+    from pretrained_rstr_b200.config import (Architecture, LayerSpec, ModelConfig, PartSpec,
+                                             register_architecture)
+    from pretrained_rstr_b200.models.assembly import build_model
+    from pretrained_rstr_b200.weights import TensorExpectation, normal
+
+    @dataclass(frozen=True)
+    class WindowedConfig(ModelConfig):
+        width: int
+        heads: int
+        kv_heads: int
+        inner: int
+        vocab: int
+        positions: int
+        window: int
+        identifiers = ("WindowedToyForTests",)
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(*(raw[k] for k in ("width", "heads", "kv_heads", "inner", "vocab",
+                                          "positions", "window")))
+
+        def to_dict(self):
+            return {"architectures": ["WindowedToyForTests"], "width": self.width,
+                    "heads": self.heads, "kv_heads": self.kv_heads, "inner": self.inner,
+                    "vocab": self.vocab, "positions": self.positions, "window": self.window}
+
+        def _norm(self, name):
+            return PartSpec("layer_norm", {"weights": name, "size": self.width, "eps": 1e-5})
+
+        def layer_specs(self):
+            dh = self.width // self.heads
+            specs = []
+            for i, (kv, window) in enumerate([(self.kv_heads, None), (self.heads, self.window)]):
+                p = f"l{i}."
+                specs.append(LayerSpec(
+                    p, "pre_norm",
+                    PartSpec("causal_attention", {
+                        "weights": {"qkv": p + "qkv", "out": p + "out"}, "width": self.width,
+                        "n_head": self.heads, "n_kv_head": kv, "head_dim": dh,
+                        "scale": 1.0 / math.sqrt(dh), "window": window, "bias": True,
+                        "weight_layout": "out_in"}),
+                    PartSpec("dense_mlp", {"weights": {"up": p + "up", "down": p + "down"},
+                                           "width": self.width, "inner": self.inner,
+                                           "activation": "gelu_new", "bias": True,
+                                           "weight_layout": "out_in"}),
+                    self._norm(p + "n1"), self._norm(p + "n2")))
+            return specs
+
+        def embedding_spec(self):
+            return PartSpec("token_embedding", {"weights": "emb", "vocab": self.vocab,
+                                                "width": self.width})
+
+        def position_spec(self):
+            return PartSpec("learned_absolute", {"weights": "pos", "positions": self.positions,
+                                                 "width": self.width})
+
+        def final_norm_spec(self):
+            return self._norm("nf")
+
+        def head_spec(self):
+            return PartSpec("tied_head", {"weights": "emb", "vocab": self.vocab, "width": self.width})
+
+        @property
+        def max_positions(self):
+            return self.positions
+
+    def expected(cfg):
+        d, f, dh = cfg.width, cfg.inner, cfg.width // cfg.heads
+        e = {"emb.weight": (cfg.vocab, d), "pos.weight": (cfg.positions, d),
+             "nf.weight": (d,), "nf.bias": (d,)}
+        for i, kv in enumerate([cfg.kv_heads, cfg.heads]):
+            l = f"l{i}."
+            n_qkv = (cfg.heads + 2 * kv) * dh
+            e.update({l + "qkv.weight": (n_qkv, d), l + "qkv.bias": (n_qkv,),
+                      l + "out.weight": (d, d), l + "out.bias": (d,),
+                      l + "n1.weight": (d,), l + "n1.bias": (d,), l + "n2.weight": (d,),
+                      l + "n2.bias": (d,), l + "up.weight": (f, d), l + "up.bias": (f,),
+                      l + "down.weight": (d, f), l + "down.bias": (d,)})
+        return {k: TensorExpectation(v) for k, v in e.items()}
+
+    def random_tensors(cfg, seed):
+        out = {}
+        for name, exp in expected(cfg).items():
+            gain = name.split(".")[-2] in ("n1", "n2", "nf") and name.endswith("weight")
+            std = 0.3 if "qkv.weight" in name else 0.05        # peaked attention: edges matter
+            out[name] = normal(seed, name, exp.shape, std, mean=1.0 if gain else 0.0)
+        return out
+
+    register_architecture(WindowedConfig.identifiers, Architecture(
+        "windowed-toy", WindowedConfig, lambda cfg, store, rt: build_model(cfg, store, rt),
+        expected, random_tensors))
+    return WindowedConfig
+
+
+def _windowed_plain(w, cfg, ids):
+    d, nh, dh = cfg.width, cfg.heads, cfg.width // cfg.heads
+    ln = lambda x, n: plain_gpt2.layer_norm(x, w[n + ".weight"], w[n + ".bias"], 1e-5)
+    x = w["emb.weight"][torch.tensor(ids)] + w["pos.weight"][:len(ids)]
+    t = len(ids)
+    i, j = torch.arange(t).unsqueeze(1), torch.arange(t).unsqueeze(0)
+    for li, (kv, window) in enumerate([(cfg.kv_heads, None), (cfg.heads, cfg.window)]):
+        l = f"l{li}."
+        qkv = ln(x, l + "n1") @ w[l + "qkv.weight"].T + w[l + "qkv.bias"]
+        q, k, v = qkv[:, :nh * dh], qkv[:, nh * dh:(nh + kv) * dh], qkv[:, (nh + kv) * dh:]
+        vis = j <= i
+        if window is not None:
+            vis = vis & (j > i - window)
+        o = torch.zeros(t, d)
+        for h in range(nh):
+            hk = h // (nh // kv)
+            sc = (q[:, h * dh:(h + 1) * dh] @ k[:, hk * dh:(hk + 1) * dh].T) / math.sqrt(dh)
+            o[:, h * dh:(h + 1) * dh] = torch.softmax(sc.masked_fill(~vis, -math.inf), 1) @ \
+                v[:, hk * dh:(hk + 1) * dh]
+        x = x + o @ w[l + "out.weight"].T + w[l + "out.bias"]
+        hmid = plain_gpt2.gelu_new(ln(x, l + "n2") @ w[l + "up.weight"].T + w[l + "up.bias"])
+        x = x + hmid @ w[l + "down.weight"].T + w[l + "down.bias"]
+    return ln(x, "nf") @ w["emb.weight"].T
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_windowed_and_grouped_layers_have_pools_of_their_own(tmp_path, dtype):
+    from pretrained_rstr_b200.engine.batch import Entry
+    from pretrained_rstr_b200.engine.loading import load_model
+    from pretrained_rstr_b200.weights import load_file, make_random_model
+    Cfg = _register_windowed()
+    cfg = Cfg(width=64, heads=4, kv_heads=2, inner=96, vocab=300, positions=200, window=40)
+    folder = str(tmp_path / "win")
+    make_random_model(folder, cfg, seed=9,
+                      dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    lm = load_model(folder, dtype=dtype, page_size=16, max_batched_tokens=256, max_requests=3,
+                    max_tokens=3 * 208)
+    groups = lm.model.group_specs
+    assert len(groups) == 2 and {g.window for g in groups} == {None, 40}
+    assert {g.kv_heads for g in groups} == {2, 4}
+    win = [i for i, g in enumerate(groups) if g.window == 40][0]
+    w = {k: v.float() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    prompts = {"a": random_tokens(190, 300, 1), "b": random_tokens(75, 300, 2)}
+    oracle = {r: _windowed_plain(w, cfg, ids) for r, ids in prompts.items()}
+    got, at = {}, {"a": 0, "b": 0}
+    for r in prompts:
+        lm.cache.open(r)
+    cuts = {"a": [50, 1, 1, 30, 2, 64, 1, 41], "b": [3, 40, 1, 1, 30]}
+    k = 0
+    most_window_pages = 0
+    while any(at[r] < len(prompts[r]) for r in prompts):
+        entries = []
+        for r in prompts:
+            if at[r] < len(prompts[r]):
+                n = min(cuts[r][k % len(cuts[r])], len(prompts[r]) - at[r])
+                entries.append(Entry(r, prompts[r][at[r]:at[r] + n], list(range(n))))
+        logits = lm.runner.step(entries).cpu()
+        lm.runner.check_status()
+        row = 0
+        for e in entries:
+            for p in range(len(e.tokens)):
+                got[(e.rid, at[e.rid] + p)] = logits[row].clone()
+                row += 1
+            at[e.rid] += len(e.tokens)
+        k += 1
+        lm.cache.check()
+        held = sum(1 for p in lm.cache.block_table("a", win) if p >= 0)
+        most_window_pages = max(most_window_pages, held)
+    # the windowed group never held more than the window plus the longest portion needs
+    assert most_window_pages <= -(-(40 + 64) // 16) + 1
+    assert lm.cache.stats["window_released"] > 0
+    assert sum(1 for p in lm.cache.block_table("a", 1 - win) if p >= 0) == -(-190 // 16)
+    tol = ATOL[dtype] * (3.0 if dtype == "bfloat16" else 2.0)      # peaked attention
+    for (rid, p), rowv in sorted(got.items()):
+        err = float((rowv - oracle[rid][p]).abs().max())
+        assert err <= tol, f"request {rid} position {p}: {err:.3e}"
+    for r in prompts:
+        lm.cache.close(r)
+    assert all(a.free_count == a.num_pages for a in lm.cache.allocators)
