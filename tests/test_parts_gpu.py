@@ -429,7 +429,7 @@ def _register_windowed():
         out = {}
         for name, exp in expected(cfg).items():
             gain = name.split(".")[-2] in ("n1", "n2", "nf") and name.endswith("weight")
-            std = 0.3 if "qkv.weight" in name else 0.05        # peaked attention: edges matter
+            std = 0.12 if "qkv.weight" in name else 0.05       # fairly peaked attention: edges matter
             out[name] = normal(seed, name, exp.shape, std, mean=1.0 if gain else 0.0)
         return out
 
