@@ -55,6 +55,8 @@ class Engine:
         # around the device work of the step (measurement only)
         self.timing_events = None
         self.step_index = 0
+        self._prepared = None              # (entries, context) of a step described ahead of time
+        self.ahead = {"used": 0, "dropped": 0}
 
     # ------------------------------------------------------------------ requests
     def submit(self, rid: Hashable, prompt: Sequence[int], max_new_tokens: int,
@@ -84,9 +86,15 @@ class Engine:
 
     # ---------------------------------------------------------------------- step
     def step(self) -> List[Request]:
-        """One iteration; returns the requests that finished in it."""
+        """One iteration; returns the requests that finished in it.
+
+        While the GPU runs the step, the host already describes the next one (who decodes
+        at which position into which slot) on the assumption that nobody stops on a stop
+        token; only the token ids are filled in when they arrive.  If the assumption was
+        wrong the prepared step is dropped and described again."""
         plan = self.scheduler.next_plan()
         if not plan.scheduled:
+            self._drop_prepared()
             return []
         entries: List[Entry] = []
         samplers: List[Request] = []
@@ -96,20 +104,82 @@ class Engine:
             entries.append(Entry(item.rid, tokens, [len(tokens) - 1] if wants else []))
             if wants:
                 samplers.append(self.scheduler.running[item.rid])
+        ctx = self._take_prepared(entries)
         if self.timing_events is not None:
             self.runner.start_event = self.timing_events[0][self.step_index]
-        logits = self.runner.step(entries)
+        if ctx is None:
+            ctx = self.runner.prepare(entries)
+        logits = self.runner.launch(ctx, entries)
         self.runner.start_event = None
         new_tokens: Dict[Hashable, int] = {}
         if samplers:
-            chosen = self._choose(logits, samplers)
+            self._launch_choice(logits, samplers)
+            self._prepare_ahead(plan)                  # overlaps the GPU's work
+            chosen = self._fetch_choice(len(samplers))
             new_tokens = {r.rid: t for r, t in zip(samplers, chosen)}
         done = self.scheduler.complete(plan, new_tokens)
         for r in done:
             self._rng_started.pop(r.rid, None)
         return done
 
-    def _choose(self, logits: torch.Tensor, requests: List[Request]) -> List[int]:
+    # ------------------------------------------------------------- preparing ahead
+    def _prepare_ahead(self, plan: Plan) -> None:
+        """Describe the next step before this one's tokens are known.  Only in the steady
+        state: nothing waiting or deferred, and every scheduled request will be decoding."""
+        self._prepared = None
+        sched = self.scheduler
+        if sched.waiting or plan.deferred or len(plan.scheduled) != len(sched.running):
+            return
+        ahead = []
+        for item in plan.scheduled:
+            r = sched.running[item.rid]
+            if item.phase == "prefill" and r.computed + item.tokens < len(r.prompt):
+                return                                  # still in its prompt: not predicted
+            n_out = len(r.output) + 1
+            if r.cancelled or n_out >= r.max_new_tokens or \
+                    len(r.prompt) + n_out > self.lm.cache.max_positions:
+                continue                                # finishes with this step
+            ahead.append(r)
+        if not ahead:
+            return
+        ahead.sort(key=lambda r: (r.arrival, str(r.rid)))
+        entries = [Entry(r.rid, [0], [0]) for r in ahead]          # placeholder token ids
+        try:
+            ctx = self.runner.prepare(entries)
+        except Exception:
+            return
+        self._prepared = (entries, ctx)
+
+    def _take_prepared(self, entries: List[Entry]):
+        """The step prepared ahead, if it is exactly the step that is now due."""
+        prepared, self._prepared = self._prepared, None
+        if prepared is None:
+            return None
+        ahead, ctx = prepared
+        same = len(ahead) == len(entries) and all(
+            a.rid == e.rid and len(e.tokens) == 1 and list(e.want) == [0]
+            for a, e in zip(ahead, entries))
+        if not same:
+            self._abort_entries(ahead)
+            self.ahead["dropped"] += 1
+            return None
+        self.runner.patch_tokens(ctx, entries)
+        self.ahead["used"] += 1
+        return ctx
+
+    def _drop_prepared(self) -> None:
+        prepared, self._prepared = self._prepared, None
+        if prepared is not None:
+            self._abort_entries(prepared[0])
+            self.ahead["dropped"] += 1
+
+    def _abort_entries(self, entries: List[Entry]) -> None:
+        for e in entries:                               # requests that ended are closed already
+            if e.rid in self.lm.cache.requests:
+                self.lm.cache.abort(e.rid)
+
+    def _launch_choice(self, logits: torch.Tensor, requests: List[Request]) -> None:
+        """Launch the kernel that chooses a token for every row (no synchronisation)."""
         n = len(requests)
         out = self._tokens_dev
         if all(r.sampling.greedy for r in requests):
@@ -138,6 +208,9 @@ class Engine:
                        slots=self._p["slots"][1], rng_states=self.rng_states)
         if self.timing_events is not None:
             self.timing_events[1][self.step_index].record()
+
+    def _fetch_choice(self, n: int) -> List[int]:
+        """Wait for the step and read the chosen tokens (and the device status word)."""
         host = self.runner.fetch_result()
         return host[:n].tolist()
 
@@ -170,6 +243,7 @@ class Engine:
         return {
             "scheduler": dict(self.scheduler.stats),
             "runner": dict(self.runner.counters),
+            "prepared_ahead": dict(self.ahead),
             "cache": dict(cache.stats),
             "free_pages": [a.free_count for a in cache.allocators],
             "pages": [a.num_pages for a in cache.allocators],

@@ -99,17 +99,34 @@ class ModelRunner:
         """Run one batch; returns float32 logits ``[wanted, vocab]`` in the order of the
         entries and of each entry's ``want`` (a view of scratch memory, valid until the
         next step).  New requests must have been opened in the cache manager."""
-        ctx = self.prepare(entries)
+        return self.launch(self.prepare(entries), entries)
+
+    def launch(self, ctx: StepContext, entries: Sequence[Entry]) -> torch.Tensor:
+        """Second half of a step: copy the prepared arrays to the device, run, commit."""
         try:
             if self.fail_next_step is not None:
                 exc, self.fail_next_step = self.fail_next_step, None
                 raise exc
+            self.upload(ctx)
             logits = self._run(ctx)
         except Exception:
             self.abort(entries)
             raise
         self.commit(entries)
         return logits[:ctx.n_rows]
+
+    def patch_tokens(self, ctx: StepContext, entries: Sequence[Entry]) -> None:
+        """Put the real token ids into a step that was prepared ahead of time with
+        placeholders (same requests, same token counts)."""
+        lay = ctx.layout
+        flat = [int(t) for e in entries for t in e.tokens]
+        if len(flat) != ctx.n_tokens:
+            raise StepError("patch_tokens: token count differs from the prepared step")
+        vocab = self.model.vocab
+        if flat and (min(flat) < 0 or max(flat) >= vocab):
+            raise StepError(f"token id outside the vocabulary of {vocab}")
+        ctx.staging.numpy()[lay.tokens:lay.tokens + len(flat)] = flat
+        ctx.host.tokens = flat
 
     def _run(self, ctx: StepContext) -> torch.Tensor:
         """Run the model for a prepared step: directly, or, for small steps when graphs are
@@ -150,7 +167,8 @@ class ModelRunner:
         return logits
 
     def prepare(self, entries: Sequence[Entry]) -> StepContext:
-        """Validate the batch, reserve cache slots, and put the step's arrays on the device."""
+        """First half of a step: validate the batch, reserve cache slots, and describe the
+        step in pinned host memory (nothing touches the device yet)."""
         if not entries:
             raise StepError("a step needs at least one entry")
         rids = [e.rid for e in entries]
@@ -218,21 +236,6 @@ class ModelRunner:
         staging = self._hosts[turn]
         n_tiles, n_singles = fill_host_buffer(staging.numpy(), layout, [list(e.tokens) for e in entries], start_pos,
                          state_slots, fresh, group_slots, group_tables, group_first, logit_rows)
-        if self.start_event is not None:             # measurement: device work of the step begins
-            self.start_event.record()
-        self._dev[:layout.size].copy_(staging[:layout.size], non_blocking=True)
-        self._host_events[turn].record()
-        self.last_h2d_bytes = layout.size * 4
-        # copy-on-write page copies come before anything reads or writes the new pages
-        for g in range(self.n_groups):
-            pairs = [(src, dst) for r in reservations for (gg, src, dst) in r.copies if gg == g]
-            for i in range(0, len(pairs), self._pairs_host.shape[0]):
-                chunk = pairs[i:i + self._pairs_host.shape[0]]
-                self._pairs_host[:len(chunk)] = torch.tensor(chunk, dtype=torch.int32)
-                self._pairs_dev[:len(chunk)].copy_(self._pairs_host[:len(chunk)], non_blocking=True)
-                self.storage.copy_pages(g, self._pairs_dev, len(chunk), self.status)
-                torch.cuda.current_stream().synchronize()      # pinned pairs buffer is reused
-                self.counters["cow_copies"] += len(chunk)
         groups = self._group_views.get(id(layout))
         if groups is None:
             groups = []
@@ -259,7 +262,28 @@ class ModelRunner:
                           launch_tokens=total, launch_rows=len(logit_rows),
                           max_positions=self.model.max_positions)
         ctx.n_tiles, ctx.n_singles = n_tiles, n_singles
+        ctx.staging, ctx.staging_turn = staging, turn
+        ctx.copies = [c for r in reservations for c in r.copies]
         return ctx
+
+    def upload(self, ctx: StepContext) -> None:
+        """The step's arrays go to the device in one copy; copy-on-write page copies come
+        before anything reads or writes the new pages."""
+        layout = ctx.layout
+        if self.start_event is not None:             # measurement: device work of the step begins
+            self.start_event.record()
+        self._dev[:layout.size].copy_(ctx.staging[:layout.size], non_blocking=True)
+        self._host_events[ctx.staging_turn].record()
+        self.last_h2d_bytes = layout.size * 4
+        for g in range(self.n_groups):
+            pairs = [(src, dst) for (gg, src, dst) in ctx.copies if gg == g]
+            for i in range(0, len(pairs), self._pairs_host.shape[0]):
+                chunk = pairs[i:i + self._pairs_host.shape[0]]
+                self._pairs_host[:len(chunk)] = torch.tensor(chunk, dtype=torch.int32)
+                self._pairs_dev[:len(chunk)].copy_(self._pairs_host[:len(chunk)], non_blocking=True)
+                self.storage.copy_pages(g, self._pairs_dev, len(chunk), self.status)
+                torch.cuda.current_stream().synchronize()      # pinned pairs buffer is reused
+                self.counters["cow_copies"] += len(chunk)
 
     def _run_program(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """A step of single tokens only (decoding) as ONE persistent kernel: the model's

@@ -89,3 +89,27 @@ def test_stop_token_and_capacity(folders):
     out = generate_ids(m, long_prompt, 10)
     assert len(out) == 4                                       # positions are used up
     assert out == plain_gpt2.greedy_generate(plain, long_prompt, 10)[:4]
+
+
+def test_stop_token_inside_a_batch(folders):
+    """The engine describes the next step while the GPU runs this one, assuming nobody
+    stops on a stop token.  One of three requests does stop: the prepared step is dropped,
+    the others go on unchanged, and no page is lost."""
+    from pretrained_rstr_b200 import generate_batch, load_lm
+    raw, seed = TINY["B"]
+    folder = folders[("B", "float32")]
+    plain = plain_gpt2.PlainGPT2(folder)
+    m = load_lm(folder, gpu=True, dtype="float32", max_lanes=4, max_batched_tokens=128)
+    prompts = [random_tokens(n, raw["vocab_size"], 50 + i) for i, n in enumerate([7, 12, 3])]
+    opts = {"temperature": 1.2, "seed": 11}           # greedy output of random weights repeats
+    free = [plain_gpt2.sample_generate(plain, p, 20, 1.2, None, None, 11) for p in prompts]
+    stop = next(t for t in free[1][4:]
+                if t not in free[0] and t not in free[2] and t not in free[1][:4])
+    want = [free[0], free[1][:free[1].index(stop) + 1], free[2]]
+    assert 4 < len(want[1]) < 20
+    m.eos_ids = (stop,)
+    assert generate_batch(m, prompts, 20, opts) == want
+    ahead = m.engine.stats()["prepared_ahead"]
+    assert ahead["used"] > 10 and ahead["dropped"] >= 1
+    m.engine.lm.cache.check()
+    assert not m.engine.lm.cache.requests

@@ -38,7 +38,9 @@ def _ctx(lm, lengths, rid0=0):
         rid = f"part{rid0}_{i}"
         lm.cache.open(rid)
         entries.append(Entry(rid, random_tokens(n, lm.model.vocab, i), [n - 1]))
-    return lm.runner.prepare(entries), entries
+    ctx = lm.runner.prepare(entries)
+    lm.runner.upload(ctx)                       # the step's arrays go to the device
+    return ctx, entries
 
 
 def _done(lm, entries):
