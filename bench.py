@@ -29,6 +29,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 SMALL = dict(n_layer=12, n_embd=768, n_head=12, n_inner=3072, vocab_size=50257, n_positions=1024)
+SIZES = {
+    "small": SMALL,
+    "medium": dict(n_layer=24, n_embd=1024, n_head=16, n_inner=4096, vocab_size=50257, n_positions=1024),
+    "xl": dict(n_layer=48, n_embd=1600, n_head=25, n_inner=6400, vocab_size=50257, n_positions=1024),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -296,7 +301,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=None,
-                    help="fewer layers than GPT-2 small's 12 (named in the record)")
+                    help="fewer layers than the size has (named in the record)")
+    ap.add_argument("--size", default="small", choices=sorted(SIZES),
+                    help="layer sizes: GPT-2 small (the default record), medium or xl")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -318,7 +325,8 @@ def main() -> int:
     from pretrained_rstr_b200.engine.batch import Entry
     from pretrained_rstr_b200.weights import make_random_model
 
-    raw = dict(SMALL)
+    raw = dict(SIZES[args.size])
+    full_layers = raw["n_layer"]
     if args.layers:
         raw["n_layer"] = args.layers
     cfg = GPT2Config.from_dict(raw)
@@ -379,12 +387,12 @@ def main() -> int:
     bytes_step = model_bytes(raw) + args.batch * mean_ctx * kv_bytes_per_token(raw)
     achieved = bytes_step / (step_ms / 1e3) / 1e9
     record = {
-        "metric": "decode tok/s (GPT-2 small, random weights)",
+        "metric": f"decode tok/s (GPT-2 {args.size}, random weights)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": "gpt2-small-random", "global_batch": args.batch, "seq_len": ctx_len,
-                   "parallelism": "single-gpu", "n_layer": raw["n_layer"], "n_layer_full": 12,
+        "config": {"model": f"gpt2-{args.size}-random", "global_batch": args.batch, "seq_len": ctx_len,
+                   "parallelism": "single-gpu", "n_layer": raw["n_layer"], "n_layer_full": full_layers,
                    "n_embd": raw["n_embd"], "n_head": raw["n_head"], "n_inner": raw["n_inner"],
                    "vocab_size": vocab, "n_positions": raw["n_positions"], "page_size": 64,
                    "mean_context": mean_ctx, "l2": "inputs_exceed_l2",

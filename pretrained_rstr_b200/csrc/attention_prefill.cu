@@ -315,10 +315,15 @@ int launch_prefill(void* out, long out_stride, const void* q, long q_stride, con
     constexpr int G = DH <= 128 ? 2 : 1;           // warp groups (shared memory allows two)
     constexpr size_t smem = (size_t)G * (QT + 4 * KT) * (DH + PADE) * 2;
     static bool configured = false;
-    if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DH, G>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
+    if (!configured) {      // several CTAs per SM need the large shared-memory carve-out
+        cudaFuncSetAttribute(attention_prefill_kernel<DH, G>,
+                             cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DH, G>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
     }
     configured = true;
     dim3 grid(n_tiles, n_heads);

@@ -28,6 +28,8 @@ NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math=fa
                            "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 # --use_fast_math is deliberately off: expf/tanhf/erff/division stay IEEE-accurate.
 NVCC_FLAGS = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+# extra flags for experiments (part of the stamp, so changing them rebuilds)
+NVCC_FLAGS += os.environ.get("PRB200_NVCC_FLAGS", "").split()
 
 
 class BuildError(RuntimeError):

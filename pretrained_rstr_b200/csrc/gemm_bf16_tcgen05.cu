@@ -28,6 +28,7 @@
 #include <unordered_map>
 
 #include "common.cuh"
+#include "tensor_map.cuh"
 
 namespace {
 
@@ -376,18 +377,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }
 
 // ------------------------------------------------------------------ host side
-PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
-    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
-                cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
-    });
-    return fn;
-}
+using tmap::encode_fn;
 
 struct MapKey {
     const void* ptr;

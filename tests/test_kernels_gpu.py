@@ -253,7 +253,8 @@ def test_attention_far_key_stands_out():
 
 # ------------------------------------------------------------------ decode-time product
 @pytest.mark.parametrize("m,n,k", [(1, 192, 64), (8, 2304, 768), (5, 1000, 96), (16, 320, 96),
-                                   (33, 768, 3072), (64, 50257, 768), (3, 24, 1608)])
+                                   (33, 768, 3072), (64, 50257, 768), (3, 24, 1608),
+                                   (8, 100, 6400), (12, 200, 1000), (2, 50, 1600), (16, 72, 3072)])
 @pytest.mark.parametrize("variant", ["plain_f32", "bias_gelu_bf16", "bias_resid_f32", "norm_bf16"])
 def test_gemm_smallm(m, n, k, variant):
     ops = _ops()
@@ -295,16 +296,23 @@ def test_gemm_smallm(m, n, k, variant):
     assert err <= tol * max(1.0, scale), f"max |difference| {err:.3e} (scale {scale:.3g})"
 
 
-def test_gemm_smallm_rows_do_not_depend_on_the_batch():
+@pytest.mark.parametrize("k", [768, 3072, 1000])
+def test_gemm_smallm_rows_do_not_depend_on_the_batch(k):
+    """One row alone and among 12: the same bits, the weights chunked or not; among 40
+    (another kernel): the same up to rounding."""
     ops = _ops()
     g = torch.Generator(device="cuda").manual_seed(9)
-    a = torch.randn(40, 768, device="cuda", generator=g).to(torch.bfloat16)
-    w = torch.randn(256, 768, device="cuda", generator=g).to(torch.bfloat16)
+    a = torch.randn(40, k, device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.randn(256, k, device="cuda", generator=g).to(torch.bfloat16)
     big = torch.zeros(40, 256, device="cuda")
     ops.gemm_smallm(big, w, a=a)
+    mid = torch.zeros(12, 256, device="cuda")
+    ops.gemm_smallm(mid, w, a=a[10:22].contiguous())
     one = torch.zeros(1, 256, device="cuda")
     ops.gemm_smallm(one, w, a=a[17:18].contiguous())
-    assert torch.equal(one[0], big[17])
+    assert torch.equal(one[0], mid[7])             # the same kernel: the same bits
+    # 40 rows go to another kernel, which adds the same products in another order
+    assert float((big[17] - one[0]).abs().max()) <= 2e-4 * float(big[17].abs().max())
 
 
 # ------------------------------------------------------------------------ small kernels
