@@ -117,14 +117,15 @@ inline Plan make_plan(int mt, bool ln, int n, int k) {
     const int mp = 8 * mt;
     const size_t fixed = (size_t)WARPS * ROWS * mp * sizeof(float) + 256 + 1024 +
                          (ln ? (size_t)mp * norm_pitch(k) * 2 + (size_t)2 * k * sizeof(float) : 0);
+    const size_t sm_bytes = 224 * 1024;                // shared memory of an SM that CTAs can share
     Plan p;
     Geometry& g = p.geo;
     const int strips = (n + ROWS - 1) / ROWS;
-    const int max_ctas = sm_count() * (g_tune[1] > 0 ? g_tune[1] : MAX_CTAS_PER_SM);
-    const int per = (strips + max_ctas - 1) / max_ctas;
-    p.grid = (strips + per - 1) / per;
-    const size_t budget = (size_t)(g_tune[3] > 0 ? g_tune[3] : 110) * 1024;   // two CTAs per SM
+    const int sms = sm_count();
     const int max_stages = g_tune[2] > 0 && g_tune[2] < MAX_STAGES ? g_tune[2] : MAX_STAGES;
+    // Pieces as large as possible (a whole strip when a copy can hold it); as many CTAs per
+    // SM as still leaves each a ring of two pieces (or all its work), because what limits a
+    // short streaming kernel is the bytes in flight; the strips are then dealt out evenly.
     const int cand[] = {k, 2048, 1024, 512, 256, 128, 64};
     for (int c = 0; c < 7; ++c) {
         g.kc = cand[c];
@@ -133,16 +134,30 @@ inline Plan make_plan(int mt, bool ln, int n, int k) {
         if (g.kc > 64 * 256) continue;                 // a copy takes at most 256 slabs
         g.chunks = (k + g.kc - 1) / g.kc;
         const size_t stage = stage_size(mp, ln, g.kc);
-        const int items = g.chunks * per;
-        int fit = fixed + stage <= budget ? (int)((budget - fixed) / stage) : 0;
-        if (fit > max_stages) fit = max_stages;
-        g.stages = fit < items ? fit : items;
-        p.smem = fixed + (size_t)g.stages * stage;
-        // a strip whole if that leaves the ring deep enough, else finer pieces
-        if (g.stages >= items || g.stages >= 3 || (g_tune[0] > 0 && g.stages >= 1)) return p;
+        for (int per_sm = (g_tune[1] > 0 ? g_tune[1] : MAX_CTAS_PER_SM); per_sm >= 1; --per_sm) {
+            size_t budget = g_tune[3] > 0 ? (size_t)g_tune[3] * 1024 : sm_bytes / per_sm - 1024;
+            if (budget > 216 * 1024) budget = 216 * 1024;    // a CTA's own limit
+            if (fixed + stage > budget) continue;
+            const int slots = sms * per_sm;
+            const int per = (strips + slots - 1) / slots;
+            const int items = g.chunks * per;
+            int fit = (int)((budget - fixed) / stage);
+            if (fit > max_stages) fit = max_stages;
+            g.stages = fit < items ? fit : items;
+            if (g.stages < items && g.stages < 2 && !(g_tune[0] > 0 && per_sm == 1)) continue;
+            p.grid = (strips + per - 1) / per;
+            p.smem = fixed + (size_t)g.stages * stage;
+            return p;
+        }
+        if (g_tune[0] > 0) break;
     }
-    if (g.stages < 1) g.stages = 1;
-    p.smem = fixed + (size_t)g.stages * stage_size(mp, ln, g.kc);
+    // nothing fits (a very wide K with many rows): smallest pieces, one CTA per SM
+    g.kc = 64;
+    g.chunks = k / 64;
+    g.stages = 1;
+    const int per = (strips + sms - 1) / sms;
+    p.grid = (strips + per - 1) / per;
+    p.smem = fixed + stage_size(mp, ln, 64);
     return p;
 }
 inline Plan finish_plan(Plan p) {
@@ -236,20 +251,23 @@ __device__ __forceinline__ void norm_rows_staged(const Args& a, __nv_bfloat16* x
         }
         const float4* src = reinterpret_cast<const float4*>(a.xf + (size_t)t * a.ldx);
         float4 v[LN_MAX_K / 128];
-        float s = 0.0f;
+        const int iters = (nvec + 31) / 32;       // the same for the whole warp
 #pragma unroll
         for (int i = 0; i < LN_MAX_K / 128; ++i) {
-            const int idx = lane + 32 * i;
-            v[i] = idx < nvec ? src[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < iters) {
+                const int idx = lane + 32 * i;
+                v[i] = idx < nvec ? src[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
+        float s = 0.0f;
 #pragma unroll
-        for (int i = 0; i < LN_MAX_K / 128; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        for (int i = 0; i < LN_MAX_K / 128; ++i)
+            if (i < iters) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         const float mean = prb_warp_sum(s) / (float)k;
-        if (mean != 12345.678f) { TRACE(3); }
         float sq = 0.0f;
 #pragma unroll
         for (int i = 0; i < LN_MAX_K / 128; ++i) {
-            if (lane + 32 * i < nvec) {
+            if (i < iters && lane + 32 * i < nvec) {
                 const float c0 = v[i].x - mean, c1 = v[i].y - mean, c2 = v[i].z - mean,
                             c3 = v[i].w - mean;
                 sq += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
@@ -259,7 +277,7 @@ __device__ __forceinline__ void norm_rows_staged(const Args& a, __nv_bfloat16* x
 #pragma unroll
         for (int i = 0; i < LN_MAX_K / 128; ++i) {
             const int idx = lane + 32 * i;
-            if (idx < nvec) {
+            if (i < iters && idx < nvec) {
                 const float4 gm = reinterpret_cast<const float4*>(gb)[idx];
                 float4 bt = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (a.beta) bt = reinterpret_cast<const float4*>(gb + k)[idx];
