@@ -125,48 +125,54 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
         sh_pages[i] = (first_page + i < a.max_pages) ? table[first_page + i] : -1;
     __syncthreads();
 
-    // keys k_begin + warp*KPW + kslot, stepping NW*KPW; UNROLL steps' loads are
-    // issued before any of them is used
-    constexpr int UNROLL = 8;
-    for (int base = k_begin + warp * KPW; base < k_end; base += NW * KPW * UNROLL) {
-        uint4 kraw[UNROLL], vraw[UNROLL];
-        bool ok[UNROLL];
+    // Keys k_begin + warp*KPW + kslot, stepping NW*KPW, in batches of UB per thread.  Two
+    // batches of registers take turns: the loads of the next batch are issued before the
+    // current one is scored, so some are always in flight.
+    constexpr int UB = 4;
+    constexpr int BATCH = NW * KPW * UB;
+    struct Batch {
+        uint4 k[UB], v[UB];
+        bool ok[UB];
+    };
+    auto load = [&](int base, Batch& bt) {
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
+        for (int u = 0; u < UB; ++u) {
             const int j = base + u * NW * KPW + kslot;
-            ok[u] = false;
-            kraw[u] = make_uint4(0, 0, 0, 0);
-            vraw[u] = make_uint4(0, 0, 0, 0);
+            bt.ok[u] = false;
+            bt.k[u] = make_uint4(0, 0, 0, 0);
+            bt.v[u] = make_uint4(0, 0, 0, 0);
             if (j < k_end) {
                 const int page = sh_pages[j / a.page_size - first_page];
                 if (page < 0 || page >= a.num_pages) {
                     prb_set_status(a.status, PRB_S_PAGE_RANGE, t, j, page);
                 } else {
-                    ok[u] = true;
+                    bt.ok[u] = true;
                     if (piece_ok) {
                         const size_t row =
                             (((size_t)page * a.kv_heads + hk) * a.page_size + (j % a.page_size)) *
                                 a.head_dim + sub * 8;
-                        kraw[u] = *reinterpret_cast<const uint4*>(a.k_pages + row);
-                        vraw[u] = *reinterpret_cast<const uint4*>(a.v_pages + row);
+                        bt.k[u] = *reinterpret_cast<const uint4*>(a.k_pages + row);
+                        bt.v[u] = *reinterpret_cast<const uint4*>(a.v_pages + row);
                     }
                 }
             }
         }
+    };
+    auto score = [&](const Batch& bt) {
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            float part = dot8(kraw[u], qf);
+        for (int u = 0; u < UB; ++u) {
+            float part = dot8(bt.k[u], qf);
             // every lane takes part in the reduction over the LPK pieces of a key row
 #pragma unroll
             for (int o = LPK / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            const float sc = ok[u] ? part * a.scale : -INFINITY;
+            const float sc = bt.ok[u] ? part * a.scale : -INFINITY;
             // online softmax per key slot (each group of LPK lanes has its own running state)
             const float m_new = fmaxf(m, sc);
             if (m_new > -INFINITY) {
                 const float corr = (m == -INFINITY) ? 0.0f : __expf(m - m_new);
                 const float p = (sc == -INFINITY) ? 0.0f : __expf(sc - m_new);
                 l = l * corr + p;
-                const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vraw[u]);
+                const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&bt.v[u]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float2 f = __bfloat1622float2(vp[i]);
@@ -175,6 +181,22 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
                 }
                 m = m_new;
             }
+        }
+    };
+    {
+        Batch b0, b1;
+        int base = k_begin + warp * KPW;           // the same for the whole warp
+        load(base, b0);
+        load(base + BATCH, b1);                    // keys beyond the split are not fetched
+        while (base < k_end) {
+            score(b0);
+            base += BATCH;
+            if (base >= k_end) break;
+            load(base + BATCH, b0);
+            score(b1);
+            base += BATCH;
+            if (base >= k_end) break;
+            load(base + BATCH, b1);
         }
     }
     // merge the KPW key slots of the warp (fixed butterfly order)

@@ -400,9 +400,13 @@ gemm_stream_kernel(Args a, Geometry geo, const __grid_constant__ CUtensorMap map
         const int c = i % geo.chunks;
         if (c == 0) {
             const int col = ((int)blockIdx.x + (i / geo.chunks) * (int)gridDim.x) * ROWS + e_r;
+            // plain loads from addresses that are always valid (a word of shared memory when
+            // there is nothing to fetch): nothing waits for them before the epilogue
             const bool mine_e = e_tok < m && col < n;
-            e_bias = (a.bias && mine_e) ? a.bias[col] : 0.0f;
-            e_resid = (a.resid && mine_e) ? a.resid[(size_t)e_tok * a.ldc + col] : 0.0f;
+            const float* bp = (a.bias && mine_e) ? a.bias + col : red;
+            const float* rp = (a.resid && mine_e) ? a.resid + (size_t)e_tok * a.ldc + col : red;
+            e_bias = *bp;
+            e_resid = *rp;
         }
         // refill the buffer of the item before, once every warp has released it
         if (alive && threadIdx.x == 0 && i >= 1 && i - 1 + geo.stages < items) {
@@ -415,6 +419,7 @@ gemm_stream_kernel(Args a, Geometry geo, const __grid_constant__ CUtensorMap map
         }
         // After a wait gave up nothing more is multiplied or stored, but every warp still
         // walks all items so that the CTA's barriers stay matched.
+        if (i == 0) TRACE(3);
         if (alive) alive = mbar_wait(full0 + 8 * st, (uint32_t)(i / geo.stages) & 1u, failed);
         if (i == 0) TRACE(5);
         const int k0 = c * geo.kc;
@@ -478,9 +483,9 @@ gemm_stream_kernel(Args a, Geometry geo, const __grid_constant__ CUtensorMap map
             float v = 0.0f;
 #pragma unroll
             for (int wv = 0; wv < WARPS; ++wv) v += red[((size_t)wv * ROWS + r) * MP + tok];
-            v += e_bias;
+            if (a.bias) v += e_bias;
             v = prb_activate(v, a.act);
-            v += e_resid;
+            if (a.resid) v += e_resid;
             const O o = prb_from_float<O>(v);
             out[(size_t)tok * a.ldc + col] = o;
             if (a.kv_width > 0 && col >= a.q_width) {

@@ -168,12 +168,15 @@ def test_attention_generic(nh, nkv, dh, ps, window, dtype):
 
 
 @pytest.mark.parametrize("nh,nkv,dh,ps,window", ATTN_CASES)
-def test_attention_decode(nh, nkv, dh, ps, window):
+@pytest.mark.parametrize("split_keys", [128, 384, 1024])
+def test_attention_decode(nh, nkv, dh, ps, window, split_keys):
+    """Short splits, splits of three stages, and one split that walks the whole context
+    (its ring of buffers is used again)."""
     ops = _ops()
     lengths, portions = [1, 70, 300, 257, 1000, 256], [1, 2, 1, 3, 1, 1]
     q, k, v, table, seq, pos = _paged_case(2, nh, nkv, dh, ps, lengths, portions, torch.bfloat16)
     t = q.shape[0]
-    splits = -(-1024 // ops.decode_split())
+    splits = -(-1024 // split_keys)
     ws = torch.full((t * nh * splits * (dh + 4),), float("nan"), device="cuda")
     counters = torch.zeros(t * nh, dtype=torch.int32, device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
@@ -181,7 +184,7 @@ def test_attention_decode(nh, nkv, dh, ps, window):
     for _ in range(2):                      # twice: the counters must be left at zero
         out = torch.full_like(q, float("nan"))
         ops.attention_decode(out, q, k, v, table, seq, pos, None, None, t, nh, 0.2, window, ws,
-                             counters, splits, status)
+                             counters, splits, status, split_keys=split_keys)
         assert status.tolist() == [0, 0, 0, 0]
         assert float((out.float() - ref).abs().max()) <= 2e-2
         assert int(counters.abs().sum()) == 0
@@ -190,7 +193,7 @@ def test_attention_decode(nh, nkv, dh, ps, window):
     count = torch.tensor([2], dtype=torch.int32, device="cuda")
     out = torch.zeros_like(q)
     ops.attention_decode(out, q, k, v, table, seq, pos, order, count, 3, nh, 0.2, window, ws,
-                         counters, splits, status)
+                         counters, splits, status, split_keys=split_keys)
     assert float((out[t - 1].float() - ref[t - 1]).abs().max()) <= 2e-2
     assert float((out[0].float() - ref[0]).abs().max()) <= 2e-2
     assert float(out[3].abs().max()) == 0.0
