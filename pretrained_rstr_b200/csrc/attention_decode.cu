@@ -14,6 +14,18 @@
 //
 // Scratch: workspace [tokens, heads, max_splits, head_dim + 4] float32 and counters
 // [tokens * heads] int32 (zero before the first launch; the kernel leaves them zero).
+#ifdef PRB_TRACE
+__device__ unsigned long long g_dec_trace[4096 * 8];
+#define DEC_TRACE(slot)                                                               \
+    do {                                                                              \
+        const int cta__ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x; \
+        if (threadIdx.x == 0 && cta__ < 4096) {                                       \
+            unsigned long long t__;                                                   \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                   \
+            g_dec_trace[cta__ * 8 + (slot)] = t__;                                    \
+        }                                                                             \
+    } while (0)
+#endif
 #include "attention_decode.cuh"
 
 namespace {
@@ -32,6 +44,11 @@ attention_decode_kernel(Args a) {
 }  // namespace
 
 PRB_API int prb_attention_decode_split() { return SPLIT; }
+#ifdef PRB_TRACE
+PRB_API int prb_attention_decode_trace(unsigned long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, g_dec_trace, sizeof(unsigned long long) * n);
+}
+#endif
 
 // workspace: float32 [n_list, n_heads, max_splits, head_dim + 4]; counters: int32
 // [n_list * n_heads], zero; both indexed by the place in the token list.  token_list/token_count may be null (all

@@ -22,6 +22,10 @@
 #pragma once
 #include "common.cuh"
 
+#ifndef DEC_TRACE
+#define DEC_TRACE(slot)
+#endif
+
 namespace decode_attn {
 constexpr int SPLIT = 128;          // granule of the split size (keys); a multiple of the page size
 constexpr int MAX_SPLIT_PAGES = 128; // most pages one split may span
@@ -81,6 +85,7 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
     int& sh_last = sh.last;
     constexpr int KPW = 32 / LPK;                 // keys per warp per load
 
+    DEC_TRACE(0);
     if (a.token_count != nullptr && idx >= *a.token_count) return;
     const int t = a.token_list ? a.token_list[idx] : idx;
     const int b = a.seq_of_token[t];
@@ -124,6 +129,7 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
     for (int i = threadIdx.x; i < a.split / a.page_size; i += (NW * 32))
         sh_pages[i] = (first_page + i < a.max_pages) ? table[first_page + i] : -1;
     __syncthreads();
+    DEC_TRACE(1);
 
     // Keys k_begin + warp*KPW + kslot, stepping NW*KPW, in batches of UB per thread.  Two
     // batches of registers take turns: the loads of the next batch are issued before the
@@ -188,8 +194,10 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
         int base = k_begin + warp * KPW;           // the same for the whole warp
         load(base, b0);
         load(base + BATCH, b1);                    // keys beyond the split are not fetched
+        bool first_batch = true;
         while (base < k_end) {
             score(b0);
+            if (first_batch && m != 1234.5f) { DEC_TRACE(2); first_batch = false; }
             base += BATCH;
             if (base >= k_end) break;
             load(base + BATCH, b0);
@@ -199,6 +207,7 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
             load(base + BATCH, b1);
         }
     }
+    if (m != 1234.5f) { DEC_TRACE(3); }
     // merge the KPW key slots of the warp (fixed butterfly order)
 #pragma unroll
     for (int o = LPK; o < 32; o <<= 1) {
@@ -243,6 +252,7 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
         if (n_splits == 1) o[d] = __float2bfloat16_rn(lt > 0.0f ? od / lt : 0.0f);
         else ws[d] = od;
     }
+    DEC_TRACE(4);
     if (n_splits == 1) return;
     if (threadIdx.x == 0) { ws[a.head_dim] = mt; ws[a.head_dim + 1] = lt; }
     __threadfence();
@@ -252,28 +262,60 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
         sh_last = (done == n_splits - 1) ? 1 : 0;
     }
     __syncthreads();
+    DEC_TRACE(5);
     if (!sh_last) return;
     __threadfence();
     // last CTA of this (token, head): merge the splits in order
     const float* wbase = a.workspace + pair * a.max_splits * (size_t)(a.head_dim + 4);
-    float mg = -INFINITY;
-    for (int ss = s_first; ss <= s_last; ++ss)
-        mg = fmaxf(mg, __ldcg(wbase + (size_t)ss * (a.head_dim + 4) + a.head_dim));
-    float lg = 0.0f;
-    for (int ss = s_first; ss <= s_last; ++ss) {
-        const float* w = wbase + (size_t)ss * (a.head_dim + 4);
-        const float ms = __ldcg(w + a.head_dim);
-        lg += __ldcg(w + a.head_dim + 1) * ((ms == -INFINITY) ? 0.0f : __expf(ms - mg));
-    }
-    for (int d = threadIdx.x; d < a.head_dim; d += (NW * 32)) {
-        float od = 0.0f;
+    constexpr int FAST = 8;                       // splits merged from registers
+    if (n_splits <= FAST && a.head_dim <= NW * 32) {
+        // everything a thread needs is fetched at once (one round trip to the L2), then
+        // combined in split order exactly as in the general loop below
+        const int d = threadIdx.x;
+        float ms[FAST], ls[FAST], os[FAST];
+#pragma unroll
+        for (int j = 0; j < FAST; ++j) {
+            const bool on = j < n_splits;
+            const float* w = wbase + (size_t)(s_first + (on ? j : 0)) * (a.head_dim + 4);
+            ms[j] = __ldcg(w + a.head_dim);
+            ls[j] = __ldcg(w + a.head_dim + 1);
+            os[j] = __ldcg(w + (d < a.head_dim ? d : 0));
+            if (!on) ms[j] = -INFINITY;
+        }
+        float mg = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < FAST; ++j) mg = fmaxf(mg, ms[j]);
+        float lg = 0.0f, od = 0.0f;
+#pragma unroll
+        for (int j = 0; j < FAST; ++j) {
+            if (j < n_splits) {
+                const float c = (ms[j] == -INFINITY) ? 0.0f : __expf(ms[j] - mg);
+                lg += ls[j] * c;
+                od += os[j] * c;
+            }
+        }
+        if (d < a.head_dim) o[d] = __float2bfloat16_rn(lg > 0.0f ? od / lg : 0.0f);
+    } else {
+        float mg = -INFINITY;
+        for (int ss = s_first; ss <= s_last; ++ss)
+            mg = fmaxf(mg, __ldcg(wbase + (size_t)ss * (a.head_dim + 4) + a.head_dim));
+        float lg = 0.0f;
         for (int ss = s_first; ss <= s_last; ++ss) {
             const float* w = wbase + (size_t)ss * (a.head_dim + 4);
             const float ms = __ldcg(w + a.head_dim);
-            od += __ldcg(w + d) * ((ms == -INFINITY) ? 0.0f : __expf(ms - mg));
+            lg += __ldcg(w + a.head_dim + 1) * ((ms == -INFINITY) ? 0.0f : __expf(ms - mg));
         }
-        o[d] = __float2bfloat16_rn(lg > 0.0f ? od / lg : 0.0f);
+        for (int d = threadIdx.x; d < a.head_dim; d += (NW * 32)) {
+            float od = 0.0f;
+            for (int ss = s_first; ss <= s_last; ++ss) {
+                const float* w = wbase + (size_t)ss * (a.head_dim + 4);
+                const float ms = __ldcg(w + a.head_dim);
+                od += __ldcg(w + d) * ((ms == -INFINITY) ? 0.0f : __expf(ms - mg));
+            }
+            o[d] = __float2bfloat16_rn(lg > 0.0f ? od / lg : 0.0f);
+        }
     }
     if (threadIdx.x == 0) a.counters[pair] = 0;
+    DEC_TRACE(6);
 }
 }  // namespace decode_attn
