@@ -14,6 +14,7 @@
 
 namespace {
 constexpr int QT = 64;              // queries per CTA
+constexpr int LIST_TILE = 128;      // queries per item of the work list
 constexpr int KT = 64;              // keys per tile
 constexpr int PADE = 8;             // row padding in elements (16 bytes): conflict-free ldmatrix
 
@@ -83,16 +84,21 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, long out_stride,
     __nv_bfloat16* vs = ks + 2 * KT * PITCH;       // [2][KT][PITCH]
 
     // the longest tiles (late query positions) first
-    const int n_items = tile_count != nullptr ? *tile_count : (int)gridDim.x;
-    if ((int)blockIdx.x >= n_items) return;
-    const int item = n_items - 1 - blockIdx.x;
+    // a work item is a tile of up to LIST_TILE rows; two CTAs take its halves
+    const int n_items = tile_count != nullptr ? *tile_count : (int)gridDim.x / (LIST_TILE / QT);
+    const int which = blockIdx.x / (LIST_TILE / QT), half = blockIdx.x % (LIST_TILE / QT);
+    if (which >= n_items) return;
+    const int item = n_items - 1 - which;
     const int h = blockIdx.y;
     const int b = tile_req[item];
-    const int row0 = tile_row0[item];              // first token row of this tile
-    const int rows = tile_rows[item];              // valid queries (1..64)
+    const int item_rows = tile_rows[item];         // valid queries of the item (1..LIST_TILE)
+    if (item_rows > 0 && item_rows <= half * QT) return;
+    const int row0 = tile_row0[item] + half * QT;  // first token row of this CTA
+    const int rows = min(QT, item_rows - half * QT);
     const int pos0 = positions[row0];
     const int pos_last = pos0 + rows - 1;
-    if (b < 0 || rows <= 0 || pos0 < 0 || pos_last >= max_pages * page_size) {
+    if (b < 0 || item_rows <= 0 || item_rows > LIST_TILE || pos0 < 0 ||
+        pos_last >= max_pages * page_size) {
         if (threadIdx.x == 0) prb_set_status(status, PRB_S_POSITION_RANGE, row0, pos0, rows);
         return;
     }
@@ -326,7 +332,7 @@ int launch_prefill(void* out, long out_stride, const void* q, long q_stride, con
         }
     }
     configured = true;
-    dim3 grid(n_tiles, n_heads);
+    dim3 grid(n_tiles * (LIST_TILE / QT), n_heads);
     attention_prefill_kernel<DH, G><<<grid, 128 * G, smem, stream>>>(
         (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, positions,
@@ -337,7 +343,7 @@ int launch_prefill(void* out, long out_stride, const void* q, long q_stride, con
 }
 }  // namespace
 
-PRB_API int prb_attention_prefill_tile() { return QT; }
+PRB_API int prb_attention_prefill_tile() { return LIST_TILE; }
 
 // 1 when this head size has a tensor-core instance, else 0.
 PRB_API int prb_attention_prefill_supports(int head_dim) {

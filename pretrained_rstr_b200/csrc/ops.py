@@ -92,6 +92,11 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_attention_prefill.argtypes = [P, L, P, L, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F,
                                         I, P, P]
     h.prb_attention_prefill_supports.argtypes = [I]
+    h.prb_attention_prefill_tile.argtypes = []
+    h.prb_attention_prefill_tc.argtypes = [P, L, P, L, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I,
+                                           I, F, I, P, P]
+    h.prb_attention_prefill_tc_supports.argtypes = [I, I]
+    h.prb_attention_prefill_tc_tile.argtypes = []
     h.prb_attention_decode_split.argtypes = []
     h.prb_program_new.argtypes = [I]
     h.prb_program_new.restype = P
@@ -117,6 +122,8 @@ def _declare(h: ctypes.CDLL) -> None:
                  "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_smallm", "prb_gemm_smallm_max_rows",
                  "prb_gemm_smallm_max_norm_width", "prb_attention_generic", "prb_attention_decode",
                  "prb_attention_prefill", "prb_attention_prefill_supports",
+                 "prb_attention_prefill_tile", "prb_attention_prefill_tc",
+                 "prb_attention_prefill_tc_supports", "prb_attention_prefill_tc_tile",
                  "prb_attention_decode_split", "prb_program_length", "prb_program_add_embed",
                  "prb_program_add_norm", "prb_program_add_gemm", "prb_program_add_append",
                  "prb_program_add_attention", "prb_program_upload", "prb_program_run", "prb_sample", "prb_sample_max_top_k"):
@@ -514,9 +521,38 @@ def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positi
         _stream()), what)
 
 
+def prefill_tile() -> int:
+    """Rows per item of the work list the prompt attention kernels take."""
+    return lib().prb_attention_prefill_tile()
+
+
+def prefill_tc_supports(head_dim: int, page_size: int) -> bool:
+    return bool(lib().prb_attention_prefill_tc_supports(int(head_dim), int(page_size)))
+
+
+def attention_prefill_tc(out, q, k_pages, v_pages, block_table, positions, tile_req, tile_row0,
+                         tile_rows, tile_count, n_tiles, n_heads, scale, window, status) -> None:
+    """bfloat16 causal attention of prompt portions on tcgen05 (head size 64, pages of a
+    multiple of 64 positions): one CTA per work item of up to 128 queries and head."""
+    what = "attention_prefill_tc"
+    _no_record(what)
+    num_pages, kv_heads, page_size, head_dim = k_pages.shape
+    for name, t in (("out", out), ("q", q)):
+        if t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != n_heads * head_dim:
+            raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
+    if k_pages.dtype != torch.bfloat16 or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise KernelArgumentError(f"{what}: the cache must be contiguous bfloat16")
+    _check(lib().prb_attention_prefill_tc(
+        _p(out), out.stride(0), _p(q), q.stride(0), q.shape[0], _p(k_pages), _p(v_pages),
+        _p(block_table), _p(positions), _p(tile_req), _p(tile_row0), _p(tile_rows), _p(tile_count),
+        n_tiles, n_heads, kv_heads, head_dim, page_size, block_table.shape[1], num_pages,
+        float(scale), int(window or 0), _p(status), _stream()), what)
+
+
 def attention_prefill(out, q, k_pages, v_pages, block_table, positions, tile_req, tile_row0,
                       tile_rows, tile_count, n_tiles, n_heads, scale, window, status) -> None:
-    """bfloat16 causal attention of prompt portions, 64 queries per tile, on tensor cores."""
+    """bfloat16 causal attention of prompt portions (work items of up to 128 queries, two
+    CTAs of 64 each) on mma.sync tensor-core instructions; any head size in steps of 16."""
     what = "attention_prefill"
     _no_record(what)
     num_pages, kv_heads, page_size, head_dim = k_pages.shape

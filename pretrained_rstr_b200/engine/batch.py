@@ -22,7 +22,7 @@ import numpy as np
 import torch
 
 
-ATTENTION_TILE = 64      # queries per tile of the prompt attention kernel
+ATTENTION_TILE = 128     # queries per work item of the prompt attention kernels
 SINGLE_MAX_Q = 4         # portions up to this many tokens are attended token by token
 
 

@@ -13,6 +13,8 @@ its part.
 """
 from __future__ import annotations
 
+import os
+
 from typing import Optional
 
 import torch
@@ -72,12 +74,16 @@ class CausalAttention(Mixer):
         self.out.forward(ctx, o, x, resid=x)
 
 
+USE_TC = os.environ.get("PRB200_ATTN_TC", "1") != "0"
+
+
 def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
            window: Optional[int]) -> None:
     """Attention of the step's tokens over their requests' cached keys and values.
 
     float32 runtime: the 32-bit kernel for every token.  bfloat16 runtime: prompt
-    portions go in 64-query tiles to the tensor-core kernel, single tokens (decoded
+    portions go in tiles of up to 128 queries to a tensor-core kernel (tcgen05 for head
+    size 64 and pages of a multiple of 64, else mma.sync), single tokens (decoded
     tokens, portions of a few tokens) to the split-key decode kernel; head sizes or page
     sizes those kernels do not take fall back to the 32-bit-arithmetic kernel."""
     t = out.shape[0]
@@ -92,9 +98,11 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
     lay = ctx.layout
     if ctx.n_tiles is None or ctx.n_tiles > 0:
         n_tiles = lay.tile_cap if ctx.n_tiles is None else ctx.n_tiles
-        ops.attention_prefill(out, q, cache.k, cache.v, group.block_table, ctx.positions,
-                              ctx.tile_req, ctx.tile_row0, ctx.tile_rows, ctx.counts[0:1], n_tiles,
-                              n_head, scale, window, ctx.status)
+        prefill = ops.attention_prefill_tc if USE_TC and ops.prefill_tc_supports(head_dim, group.page_size) \
+            else ops.attention_prefill
+        prefill(out, q, cache.k, cache.v, group.block_table, ctx.positions,
+                ctx.tile_req, ctx.tile_row0, ctx.tile_rows, ctx.counts[0:1], n_tiles,
+                n_head, scale, window, ctx.status)
     if ctx.n_singles is None or ctx.n_singles > 0:
         n_list = lay.single_cap if ctx.n_singles is None else ctx.n_singles
         # about four CTAs per SM: many (token, head) pairs get fewer, longer splits

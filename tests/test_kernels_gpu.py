@@ -199,28 +199,40 @@ def test_attention_decode(nh, nkv, dh, ps, window, split_keys):
     assert float(out[3].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("nh,nkv,dh,ps,window", ATTN_CASES)
-def test_attention_prefill(nh, nkv, dh, ps, window):
+PREFILL_CASES = ATTN_CASES + [(12, 12, 64, 64, None), (4, 2, 64, 128, 100), (3, 1, 64, 64, 70)]
+
+
+@pytest.mark.parametrize("nh,nkv,dh,ps,window", PREFILL_CASES)
+@pytest.mark.parametrize("tile", [64, 128])
+def test_attention_prefill(nh, nkv, dh, ps, window, tile):
+    """Both prompt kernels (mma.sync for every head size, tcgen05 where it applies) on work
+    items of up to 64 and up to 128 rows."""
     ops = _ops()
-    assert ops.prefill_supports(dh)
-    lengths, portions = [5, 70, 300, 200, 64], [5, 70, 130, 9, 64]
+    assert ops.prefill_supports(dh) and ops.prefill_tile() == 128
+    lengths, portions = [5, 70, 300, 200, 64, 500], [5, 70, 130, 9, 64, 300]
     q, k, v, table, seq, pos = _paged_case(3, nh, nkv, dh, ps, lengths, portions, torch.bfloat16)
     tiles, row = [], 0
     for b, p in enumerate(portions):
-        for r0 in range(0, p, 64):
-            tiles.append((b, row + r0, min(64, p - r0)))
+        for r0 in range(0, p, tile):
+            tiles.append((b, row + r0, min(tile, p - r0)))
         row += p
     tr = torch.tensor([x[0] for x in tiles], dtype=torch.int32, device="cuda")
     t0 = torch.tensor([x[1] for x in tiles], dtype=torch.int32, device="cuda")
     tn = torch.tensor([x[2] for x in tiles], dtype=torch.int32, device="cuda")
-    status = torch.zeros(4, dtype=torch.int32, device="cuda")
-    out = torch.full_like(q, float("nan"))
-    ops.attention_prefill(out, q, k, v, table, pos, tr, t0, tn, None, len(tiles), nh, 0.2, window,
-                          status)
     ref = _ref_attention(q, k, v, table, seq, pos, nh, 0.2, window)
-    assert status.tolist() == [0, 0, 0, 0]
-    err = (out.float() - ref).abs()
-    assert float(err.max()) <= 2e-2, f"worst row {int(err.max(dim=1).values.argmax())}"
+    kernels = [ops.attention_prefill]
+    if ops.prefill_tc_supports(dh, ps):
+        kernels.append(ops.attention_prefill_tc)
+    else:
+        assert not (dh == 64 and ps % 64 == 0)
+    for kernel in kernels:
+        status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        out = torch.full_like(q, float("nan"))
+        kernel(out, q, k, v, table, pos, tr, t0, tn, None, len(tiles), nh, 0.2, window, status)
+        assert status.tolist() == [0, 0, 0, 0], kernel.__name__
+        err = (out.float() - ref).abs()
+        assert float(err.max()) <= 2e-2, \
+            f"{kernel.__name__}: worst row {int(err.max(dim=1).values.argmax())}"
 
 
 def test_attention_far_key_stands_out():
@@ -240,6 +252,9 @@ def test_attention_far_key_stands_out():
     tn = torch.tensor([64, 2], dtype=torch.int32, device="cuda")
     ops.attention_prefill(out, q, k, v, table, pos, tr, t0, tn, None, 2, nh, 0.125, None, status)
     assert float((out.float() - ref).abs().max()) <= 2e-2
+    out_tc = torch.zeros_like(q)
+    ops.attention_prefill_tc(out_tc, q, k, v, table, pos, tr, t0, tn, None, 2, nh, 0.125, None, status)
+    assert float((out_tc.float() - ref).abs().max()) <= 2e-2
     t = q.shape[0]
     splits = -(-1024 // ops.decode_split())
     ws = torch.zeros(t * nh * splits * (dh + 4), device="cuda")
