@@ -218,7 +218,7 @@ def profile_gemm(shape: str) -> int:
     return 0
 
 
-def profile_decode(batch: int) -> int:
+def profile_decode(batch: int, table: bool = False) -> int:
     """Small workload for ncu: the benchmark model, ``batch`` requests of 900 prompt tokens,
     then four decode steps launched kernel by kernel (no CUDA graph)."""
     import random
@@ -241,16 +241,27 @@ def profile_decode(batch: int) -> int:
         e.submit(i, [rng.randrange(SMALL["vocab_size"]) for _ in range(900)], 100)
     while any(r.phase != "decode" for r in e.scheduler.running.values()) or e.scheduler.waiting:
         e.step()
-    for _ in range(4):
+    if table:
+        from torch.profiler import ProfilerActivity, profile
         e.step()
-    torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(4):
+                e.step()
+            torch.cuda.synchronize()
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=12,
+                                        max_name_column_width=70))
+    else:
+        for _ in range(4):
+            e.step()
+        torch.cuda.synchronize()
     print(json.dumps({"profile_decode": batch, "ok": True}))
     return 0
 
 
-def profile_prefill() -> int:
+def profile_prefill(table: bool = True) -> int:
     """Small workload for a profiler: one step of 2 x 1,000 prompt tokens, launched kernel
-    by kernel, with the torch profiler's kernel table printed."""
+    by kernel, with the torch profiler's kernel table printed (``table``; off under ncu)."""
     import random
     import torch
     from torch.profiler import ProfilerActivity, profile
@@ -282,6 +293,10 @@ def profile_prefill() -> int:
             cache.close(e.rid)
 
     one_step("warm")
+    if not table:
+        one_step("timed")
+        print(json.dumps({"profile_prefill": True, "ok": True}))
+        return 0
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         one_step("timed")
     print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=12,
@@ -294,6 +309,10 @@ def main() -> int:
     ap.add_argument("--profile-prefill", action="store_true")
     ap.add_argument("--profile-gemm", default=None, metavar="M,N,K")
     ap.add_argument("--profile-decode", type=int, default=None, metavar="BATCH")
+    ap.add_argument("--kernel-table", action="store_true",
+                    help="with --profile-decode: print the torch profiler's kernel table")
+    ap.add_argument("--no-table", action="store_true",
+                    help="with --profile-prefill: no torch profiler (for runs under ncu)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
@@ -310,9 +329,9 @@ def main() -> int:
     if args.profile_gemm:
         return profile_gemm(args.profile_gemm)
     if args.profile_decode:
-        return profile_decode(args.profile_decode)
+        return profile_decode(args.profile_decode, args.kernel_table)
     if args.profile_prefill:
-        return profile_prefill()
+        return profile_prefill(not args.no_table)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -74,6 +74,7 @@ class CausalAttention(Mixer):
         self.out.forward(ctx, o, x, resid=x)
 
 
+DECODE_CTAS = int(os.environ.get("PRB200_DECODE_CTAS", "600"))
 USE_TC = os.environ.get("PRB200_ATTN_TC", "1") != "0"
 
 
@@ -105,10 +106,12 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
                 n_head, scale, window, ctx.status)
     if ctx.n_singles is None or ctx.n_singles > 0:
         n_list = lay.single_cap if ctx.n_singles is None else ctx.n_singles
-        # about four CTAs per SM: many (token, head) pairs get fewer, longer splits
+        # about four CTAs per SM: many (token, head) pairs get fewer, longer splits (more pairs
+        # than CTAs fit at once still get two, which evens out the last round)
         granule = ops.decode_split()
         most = -(-ctx.max_context // granule)
-        wanted = max(1, min(most, -(-600 // max(1, n_list * n_head))))
+        pairs = max(1, n_list * n_head)
+        wanted = max(1, min(most, -(-DECODE_CTAS // pairs) if pairs < DECODE_CTAS else 2))
         split_keys = -(-ctx.max_context // wanted // granule) * granule
         max_splits = -(-ctx.max_context // split_keys)
         cap = ctx.runtime.max_requests * SINGLE_MAX_Q
