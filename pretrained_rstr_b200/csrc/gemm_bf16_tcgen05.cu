@@ -31,6 +31,23 @@
 #include "tcgen05.cuh"
 #include "tensor_map.cuh"
 
+#ifdef PRB_TRACE
+__device__ unsigned long long g_gemm_trace[256 * 8];
+#define GT(slot)                                                                      \
+    do {                                                                              \
+        if (lane == 0 && blockIdx.x < 256) {                                          \
+            unsigned long long t__;                                                   \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                   \
+            g_gemm_trace[blockIdx.x * 8 + (slot)] = t__;                              \
+        }                                                                             \
+    } while (0)
+PRB_API int prb_gemm_bf16_trace(unsigned long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, g_gemm_trace, sizeof(unsigned long long) * n);
+}
+#else
+#define GT(slot)
+#endif
+
 namespace {
 
 constexpr int BM = 128;
@@ -44,11 +61,44 @@ template <int BN> struct TileCfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = (160 * 1024) / STAGE_BYTES > 8 ? 8 : (160 * 1024) / STAGE_BYTES;
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256;
+    // per epilogue warp a 32 x 33 word staging tile (rows of the accumulator are turned into
+    // rows of the output so that global accesses are whole lines)
+    static constexpr int STG_WORDS = 32 * 33;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 +
+                                   (size_t)8 * STG_WORDS * 4;
 };
 
+
+// Optional scatter of output columns into the paged cache (a fused QKV product whose output
+// has the cache's element type: columns [q_width, q_width + kv_width) are keys, the next
+// kv_width are values; slots[row] is the token's cache slot, -1 = none).  kv_width == 0: off.
+struct Scatter {
+    void* k_pages;                  // [pages][kv heads][page_size][head_dim]
+    void* v_pages;
+    const int* slots;
+    int q_width, kv_width, head_dim, page_size, num_pages;
+};
+
+// Where `count` consecutive output columns starting at `col` (inside one head) of the token
+// with cache slot `slot` go; null when they are not key or value columns or there is no slot.
+template <typename O>
+__device__ __forceinline__ O* scatter_dst(const Scatter& sc, int col, int slot, int row,
+                                          int* status) {
+    if (sc.kv_width == 0 || col < sc.q_width || slot < 0) return nullptr;
+    const int page = slot / sc.page_size, off = slot - page * sc.page_size;
+    if (page >= sc.num_pages) {
+        prb_set_status(status, PRB_S_SLOT_RANGE, row, slot, sc.num_pages);
+        return nullptr;
+    }
+    int cc = col - sc.q_width;
+    O* pages = reinterpret_cast<O*>(cc < sc.kv_width ? sc.k_pages : sc.v_pages);
+    if (cc >= sc.kv_width) cc -= sc.kv_width;
+    const int h = cc / sc.head_dim, d = cc - h * sc.head_dim;
+    const int kv_heads = sc.kv_width / sc.head_dim;
+    return pages + (((size_t)page * kv_heads + h) * sc.page_size + off) * sc.head_dim + d;
+}
 
 // tanh-form GELU as u * sigmoid(2z), z = sqrt(2/pi) (u + 0.044715 u^3): no cancellation in
 // the negative tail, relative error of the fast exp and divide about 1e-6.
@@ -71,7 +121,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                  O* __restrict__ c, const float* __restrict__ bias,
                  const float* __restrict__ resid, int m, int n, int k, long ldc, int act,
-                 int* status) {
+                 int* status, Scatter sc) {
     using Cfg = TileCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
@@ -84,8 +134,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint64_t* tempty_bar = tfull_bar + 2;            // [2]       epilogue -> MMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint32_t* staging = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) GT(0);
     const int m_tiles = (m + BM - 1) / BM, n_tiles = (n + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
     const int k_blocks = (k + BK - 1) / BK;
@@ -114,6 +166,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (warp == 0) GT(1);
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
@@ -170,6 +223,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         break;
                     }
                     tcgen05_fence_after();
+                    if (it == 0) GT(2);
                     const uint32_t a_addr = smem_u32(tiles + (size_t)s * Cfg::STAGE_BYTES);
                     const uint64_t a_desc = make_smem_desc(a_addr);
                     const uint64_t b_desc = make_smem_desc(a_addr + Cfg::A_BYTES);
@@ -182,17 +236,55 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     umma_commit(smem_u32(&empty_bar[s]));   // frees the stage when the MMAs retire
                 }
                 if (ok) umma_commit(smem_u32(&tfull_bar[acc]));   // accumulator complete
+                if (local == 0) GT(3);
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue
+        // A warp reads 32 accumulator rows x 32 columns from tensor memory (one row per
+        // thread), turns them through its staging tile so that a quarter warp (float32
+        // output) or four lanes (bfloat16) own a contiguous piece of one output row, and
+        // there adds bias, applies the activation, adds the residual and stores whole lines.
+        // The bias and residual values of a chunk are requested before the chunk's
+        // accumulator is waited for, so their latency is off the path.
         const int quarter = warp & 3;                       // TMEM lanes this warp may read
         const int half = (warp - 2) >> 2;                   // two warps share a quarter: even / odd chunks
         const bool vec_ok = ((ldc * (long)sizeof(O)) % 16 == 0) && (((uintptr_t)c) % 16 == 0) &&
+                            (((uintptr_t)bias) % 16 == 0) &&
                             (resid == nullptr ||
                              (((ldc * 4) % 16 == 0) && (((uintptr_t)resid) % 16 == 0)));
+        constexpr bool F32 = sizeof(O) == 4;
+        constexpr int ITERS = F32 ? 8 : 4;                  // passes over the staging tile
+        constexpr int RPI = 32 / ITERS;                     // rows per pass
+        constexpr int CPL = 32 / (32 / RPI);                // columns per lane: 4 or 8
+        uint32_t* stg = staging + (size_t)(warp - 2) * Cfg::STG_WORDS;
+        const int t_row = lane / (32 / RPI);                // row within a pass
+        const int t_col = (lane % (32 / RPI)) * CPL;        // first column of this lane
+        float pb[CPL];                                      // prefetched bias of the lane's columns
+        float4 pr[F32 ? ITERS : 1];                         // prefetched residual (float32 output)
+        auto prefetch = [&](int m0, int ncol) {
+            // only chunks that take the vector path are prefetched
+            if (!(vec_ok && ncol + 32 <= n)) return;
+#pragma unroll
+            for (int e = 0; e < CPL; e += 4) {
+                float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (bias) b = __ldg(reinterpret_cast<const float4*>(bias + ncol + t_col + e));
+                pb[e] = b.x; pb[e + 1] = b.y; pb[e + 2] = b.z; pb[e + 3] = b.w;
+            }
+            if constexpr (F32) {
+#pragma unroll
+                for (int it = 0; it < ITERS; ++it) {
+                    const int rr = m0 + quarter * 32 + it * RPI + t_row;
+                    pr[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (resid && rr < m)
+                        pr[it] = *reinterpret_cast<const float4*>(resid + (size_t)rr * ldc + ncol + t_col);
+                }
+            }
+        };
         int local = 0;
         bool ok = true;
+        if ((int)blockIdx.x < total_tiles && half * 32 < BN)
+            prefetch((blockIdx.x % m_tiles) * BM, (blockIdx.x / m_tiles) * BN + half * 32);
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
             const int acc = local & 1;
@@ -202,8 +294,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             tcgen05_fence_after();
+            if (warp == 2 && local == 0) GT(4);
             if (half * 32 >= BN || n0 + half * 32 >= n) {      // nothing to read for this warp
                 if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+                const int nt = tile + gridDim.x;
+                if (nt < total_tiles && half * 32 < BN)
+                    prefetch((nt % m_tiles) * BM, (nt / m_tiles) * BN + half * 32);
                 continue;
             }
 #pragma unroll 1
@@ -212,65 +308,100 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) +
                                   (uint32_t)(acc * BN + c0), r);
-                if (c0 + 64 >= BN || n0 + c0 + 64 >= n) {
+                const bool last_chunk = c0 + 64 >= BN || n0 + c0 + 64 >= n;
+                if (last_chunk) {
                     // this warp's last read of the accumulator: hand it back before the stores
                     tcgen05_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
                 }
-                if (row >= m) continue;
                 const int ncol = n0 + c0;
                 const int n_valid = (n - ncol) < 32 ? (n - ncol) : 32;
-                O* crow = c + (size_t)row * ldc + ncol;
-                const float* rrow = resid ? resid + (size_t)row * ldc + ncol : nullptr;
                 if (vec_ok && n_valid == 32) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        float v[8];
+                    for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = r[j];
+                    __syncwarp();
+                    // what this chunk needs has been requested before; keep it and request the
+                    // next chunk's (of this tile, or the first of the CTA's next tile)
+                    float b_now[CPL];
+                    float4 r_now[F32 ? ITERS : 1];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-                        if (bias) {
-                            const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + ncol + j));
-                            const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + ncol + j + 4));
-                            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-                        }
+                    for (int e = 0; e < CPL; ++e) b_now[e] = pb[e];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) v[e] = epilogue_act(v[e], act);
-                        if (rrow) {
-                            const float4 q0 = *reinterpret_cast<const float4*>(rrow + j);
-                            const float4 q1 = *reinterpret_cast<const float4*>(rrow + j + 4);
-                            v[0] += q0.x; v[1] += q0.y; v[2] += q0.z; v[3] += q0.w;
-                            v[4] += q1.x; v[5] += q1.y; v[6] += q1.z; v[7] += q1.w;
-                        }
-                        if constexpr (sizeof(O) == 4) {
-                            *reinterpret_cast<float4*>(crow + j) = make_float4(v[0], v[1], v[2], v[3]);
-                            *reinterpret_cast<float4*>(crow + j + 4) = make_float4(v[4], v[5], v[6], v[7]);
-                        } else {
-                            uint4 u;
-                            u.x = pack2(v[0], v[1]); u.y = pack2(v[2], v[3]);
-                            u.z = pack2(v[4], v[5]); u.w = pack2(v[6], v[7]);
-                            *reinterpret_cast<uint4*>(crow + j) = u;
+                    for (int it = 0; it < (F32 ? ITERS : 1); ++it) r_now[it] = pr[it];
+                    if (!last_chunk) {
+                        prefetch(m0, ncol + 64);
+                    } else {
+                        const int nt = tile + gridDim.x;
+                        if (nt < total_tiles)
+                            prefetch((nt % m_tiles) * BM, (nt / m_tiles) * BN + half * 32);
+                    }
+                    const int row_base = m0 + quarter * 32;
+#pragma unroll
+                    for (int it = 0; it < ITERS; ++it) {
+                        const int rr = it * RPI + t_row;
+                        float v[CPL];
+#pragma unroll
+                        for (int e = 0; e < CPL; ++e)
+                            v[e] = epilogue_act(__uint_as_float(stg[rr * 33 + t_col + e]) + b_now[e], act);
+                        if (row_base + rr < m) {
+                            const size_t off = (size_t)(row_base + rr) * ldc + ncol + t_col;
+                            if constexpr (F32) {
+                                if (resid) {
+                                    v[0] += r_now[it].x; v[1] += r_now[it].y;
+                                    v[2] += r_now[it].z; v[3] += r_now[it].w;
+                                }
+                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(c) + off) =
+                                    make_float4(v[0], v[1], v[2], v[3]);
+                            } else {
+                                uint4 u;
+                                u.x = pack2(v[0], v[1]); u.y = pack2(v[2], v[3]);
+                                u.z = pack2(v[4], v[5]); u.w = pack2(v[6], v[7]);
+                                *reinterpret_cast<uint4*>(c + off) = u;
+                                if (sc.kv_width != 0 && ncol + t_col >= sc.q_width) {
+                                    // eight columns inside one head (head sizes are multiples of 8)
+                                    O* dst = scatter_dst<O>(sc, ncol + t_col, sc.slots[row_base + rr],
+                                                            row_base + rr, status);
+                                    if (dst) *reinterpret_cast<uint4*>(dst) = u;
+                                }
+                            }
                         }
                     }
+                    __syncwarp();                           // the tile is reused by the next chunk
                 } else {
                     // tail columns or unaligned rows (e.g. a vocabulary that is odd): one by one
+                    O* crow = c + (size_t)row * ldc + ncol;
+                    const float* rrow = resid ? resid + (size_t)row * ldc + ncol : nullptr;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        if (j < n_valid) {
+                        if (j < n_valid && row < m) {
                             float x = __uint_as_float(r[j]);
                             if (bias) x += __ldg(bias + ncol + j);
                             x = epilogue_act(x, act);
                             if (rrow) x += rrow[j];
                             crow[j] = prb_from_float<O>(x);
+                            if (sc.kv_width != 0 && ncol + j >= sc.q_width) {
+                                O* dst = scatter_dst<O>(sc, ncol + j, sc.slots[row], row, status);
+                                if (dst) *dst = prb_from_float<O>(x);
+                            }
                         }
+                    }
+                    if (last_chunk) {
+                        const int nt = tile + gridDim.x;
+                        if (nt < total_tiles)
+                            prefetch((nt % m_tiles) * BM, (nt / m_tiles) * BN + half * 32);
+                    } else {
+                        prefetch(m0, ncol + 64);
                     }
                 }
             }
+            if (warp == 2 && local == 0) GT(5);
         }
+        if (warp == 2) GT(6);
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (warp == 0) GT(7);
     if (warp == 1) {
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
@@ -285,7 +416,7 @@ using tmap::get_map;
 template <int BN, typename O>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, O* c, const float* bias,
            const float* resid, int m, int n, int k, long ldc, int act, int* status,
-           cudaStream_t stream) {
+           const Scatter& sc, cudaStream_t stream) {
     using Cfg = TileCfg<BN>;
     static bool configured = false;
     if (!configured) {
@@ -306,17 +437,17 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, O* c, const float* bias
     const long tiles = (long)((n + BN - 1) / BN) * ((m + BM - 1) / BM);
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
     gemm_bf16_kernel<BN, O><<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(ma, mw, c, bias, resid, m,
-                                                                       n, k, ldc, act, status);
+                                                                       n, k, ldc, act, status, sc);
     PRB_LAUNCH_CHECK();
     return 0;
 }
 
 }  // namespace
 
-// tile_n: 0 = choose (by M and N), or one of 32, 64, 128, 256.
-PRB_API int prb_gemm_bf16(void* c, const void* a, const void* w, const float* bias,
-                          const float* resid, int m, int n, int k, long lda, long ldw, long ldc,
-                          int act, int out_dtype, int tile_n, int* status, cudaStream_t stream) {
+namespace {
+int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, const float* resid,
+                    int m, int n, int k, long lda, long ldw, long ldc, int act, int out_dtype,
+                    int tile_n, int* status, const Scatter& sc, cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (k <= 0) return PRB_E_SIZE;
     if (k % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)a) % 16 != 0 ||
@@ -341,9 +472,10 @@ PRB_API int prb_gemm_bf16(void* c, const void* a, const void* w, const float* bi
     if (r) return r;
 #define PRB_GO(BN_)                                                                              \
     (out_dtype == PRB_F32                                                                        \
-         ? launch<BN_, float>(ma, mw, (float*)c, bias, resid, m, n, k, ldc, act, status, stream) \
+         ? launch<BN_, float>(ma, mw, (float*)c, bias, resid, m, n, k, ldc, act, status, sc,     \
+                              stream)                                                            \
          : launch<BN_, __nv_bfloat16>(ma, mw, (__nv_bfloat16*)c, bias, resid, m, n, k, ldc, act, \
-                                      status, stream))
+                                      status, sc, stream))
     if (out_dtype != PRB_F32 && out_dtype != PRB_BF16) return PRB_E_DTYPE;
     switch (tile_n) {
         case 32: return PRB_GO(32);
@@ -352,4 +484,32 @@ PRB_API int prb_gemm_bf16(void* c, const void* a, const void* w, const float* bi
         default: return PRB_GO(256);
     }
 #undef PRB_GO
+}
+}  // namespace
+
+// tile_n: 0 = choose (by M and N), or one of 32, 64, 128, 256.
+PRB_API int prb_gemm_bf16(void* c, const void* a, const void* w, const float* bias,
+                          const float* resid, int m, int n, int k, long lda, long ldw, long ldc,
+                          int act, int out_dtype, int tile_n, int* status, cudaStream_t stream) {
+    Scatter sc = {};
+    return gemm_bf16_entry(c, a, w, bias, resid, m, n, k, lda, ldw, ldc, act, out_dtype, tile_n,
+                           status, sc, stream);
+}
+
+// The same product whose key and value columns (a fused QKV projection: n = q_width + 2 *
+// kv_width) are also written to the paged cache at slots[row]; the cache has the output's
+// element type and head_dim is a multiple of 8.
+PRB_API int prb_gemm_bf16_scatter(void* c, const void* a, const void* w, const float* bias, int m,
+                                  int n, int k, long lda, long ldw, long ldc, int act,
+                                  int out_dtype, void* k_pages, void* v_pages, const int* slots,
+                                  int q_width, int kv_width, int head_dim, int page_size,
+                                  int num_pages, int* status, cudaStream_t stream) {
+    if (head_dim <= 0 || head_dim % 8 != 0 || kv_width <= 0 || kv_width % head_dim != 0 ||
+        page_size <= 0 || q_width < 0 || q_width % 8 != 0 || q_width + 2 * kv_width != n ||
+        k_pages == nullptr || v_pages == nullptr || slots == nullptr)
+        return PRB_E_ARG;
+    if (((uintptr_t)k_pages) % 16 != 0 || ((uintptr_t)v_pages) % 16 != 0) return PRB_E_ALIGN;
+    Scatter sc = {k_pages, v_pages, slots, q_width, kv_width, head_dim, page_size, num_pages};
+    return gemm_bf16_entry(c, a, w, bias, nullptr, m, n, k, lda, ldw, ldc, act, out_dtype, 0,
+                           status, sc, stream);
 }

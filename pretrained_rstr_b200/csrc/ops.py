@@ -81,6 +81,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_copy_pages.argtypes = [P, P, I, L, I, I, P, P]
     h.prb_gemm_f32.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, P]
     h.prb_gemm_bf16.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, I, P, P]
+    h.prb_gemm_bf16_scatter.argtypes = [P, P, P, P, I, I, I, L, L, L, I, I, P, P, P, I, I, I, I, I,
+                                        P, P]
     h.prb_gemm_smallm.argtypes = [P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
                                   P, P, P, I, I, I, I, I, P, P]
     h.prb_gemm_smallm_max_rows.argtypes = []
@@ -119,7 +121,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
     h.prb_sample_max_top_k.argtypes = []
     for name in ("prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
-                 "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_smallm", "prb_gemm_smallm_max_rows",
+                 "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_bf16_scatter", "prb_gemm_smallm", "prb_gemm_smallm_max_rows",
                  "prb_gemm_smallm_max_norm_width", "prb_attention_generic", "prb_attention_decode",
                  "prb_attention_prefill", "prb_attention_prefill_supports",
                  "prb_attention_prefill_tile", "prb_attention_prefill_tc",
@@ -367,10 +369,13 @@ def gemm_f32(out, a, w, bias=None, resid=None, act=None) -> None:
                               w.stride(0), out.stride(0), ACT_CODES[act], _stream()), what)
 
 
-def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, status=None) -> None:
+def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, status=None,
+              kv_scatter=None) -> None:
     """out[M,N] = act(a[M,K] . w[N,K]^T + bias) (+ resid) on the tcgen05 tensor cores:
     bfloat16 operands, float32 accumulation in tensor memory, epilogue in float32; out is
-    bfloat16 or float32.  K and the row pitches of a and w must be multiples of 8."""
+    bfloat16 or float32.  K and the row pitches of a and w must be multiples of 8.
+    ``kv_scatter`` = (k_pages, v_pages, slots, q_width): the key and value columns of a fused
+    QKV product also go to the paged cache (of the output's element type)."""
     what = "gemm_bf16"
     _no_record(what)
     for name, t in (("a", a), ("w", w)):
@@ -388,6 +393,20 @@ def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, statu
         _need(resid, torch.float32, "resid", what)
         if resid.shape != out.shape or resid.stride(0) != out.stride(0):
             raise KernelArgumentError(f"{what}: resid must have the output's shape and stride")
+    if kv_scatter is not None:
+        k_pages, v_pages, slots, q_width = kv_scatter
+        if resid is not None or tile_n:
+            raise KernelArgumentError(f"{what}: a product that scatters takes no residual or tile width")
+        if k_pages.dtype != out.dtype or v_pages.dtype != out.dtype or not k_pages.is_contiguous() \
+                or not v_pages.is_contiguous():
+            raise KernelArgumentError(f"{what}: the cache must be contiguous and of the output's type")
+        _need(slots, torch.int32, "slots", what)
+        num_pages, kv_heads, page_size, head_dim = k_pages.shape
+        _check(lib().prb_gemm_bf16_scatter(
+            _p(out), _p(a), _p(w), _p(bias), m, n, k, a.stride(0), w.stride(0), out.stride(0),
+            ACT_CODES[act], dtype_code(out.dtype), _p(k_pages), _p(v_pages), _p(slots), int(q_width),
+            kv_heads * head_dim, head_dim, page_size, num_pages, _p(status), _stream()), what)
+        return
     _check(lib().prb_gemm_bf16(_p(out), _p(a), _p(w), _p(bias), _p(resid), m, n, k, a.stride(0),
                                w.stride(0), out.stride(0), ACT_CODES[act], dtype_code(out.dtype),
                                tile_n, _p(status), _stream()), what)

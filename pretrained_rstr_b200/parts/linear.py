@@ -71,8 +71,12 @@ class Linear:
                 ops.gemm_smallm(out, self.weight, a=_tensor(a), bias=self.bias, resid=resid,
                                 act=act, kv_scatter=kv_scatter, status=ctx.status)
             return kv_scatter is not None
-        ops.gemm_bf16(out, _tensor(a), self.weight, self.bias, resid, act, status=ctx.status)
-        return False
+        if kv_scatter is not None and (kv_scatter[0].dtype != out.dtype or resid is not None or
+                                       kv_scatter[0].shape[3] % 8 != 0 or kv_scatter[3] % 8 != 0):
+            kv_scatter = None
+        ops.gemm_bf16(out, _tensor(a), self.weight, self.bias, resid, act, status=ctx.status,
+                      kv_scatter=kv_scatter)
+        return kv_scatter is not None
 
 
 class LazyNorm:

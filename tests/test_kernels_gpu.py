@@ -434,3 +434,33 @@ def test_gemm_smallm_scatters_keys_and_values_to_the_cache():
     torch.cuda.synchronize()
     assert torch.equal(out1, out2) and torch.equal(k1, k2) and torch.equal(v1, v2)
     assert int((k1 != 0).any(dim=-1).sum()) == 6 * kv_heads and status.tolist() == [0, 0, 0, 0]
+
+
+@pytest.mark.parametrize("m,heads,kv_heads,dh,ps", [(200, 6, 3, 32, 16), (130, 12, 12, 64, 64), (70, 5, 1, 24, 32)])
+def test_gemm_bf16_scatters_keys_and_values_to_the_cache(m, heads, kv_heads, dh, ps):
+    """The prompt-time QKV product writes its key and value columns to the cache slots itself
+    (whole 16-byte pieces, or element by element when the width is not a multiple of 32); the
+    result equals the product followed by the append kernel."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(m)
+    pages, k = (m + ps - 1) // ps + 3, 96
+    q_width, kv_width = heads * dh, kv_heads * dh
+    n = q_width + 2 * kv_width
+    a = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.2).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda", generator=g)
+    slots = torch.randperm(pages * ps, device="cuda", generator=g)[:m].to(torch.int32)
+    slots[3] = -1
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    k1 = torch.zeros(pages, kv_heads, ps, dh, device="cuda", dtype=torch.bfloat16)
+    v1, k2, v2 = torch.zeros_like(k1), torch.zeros_like(k1), torch.zeros_like(k1)
+    out1 = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    out2 = torch.zeros_like(out1)
+    ops.gemm_bf16(out1, a, w, bias=bias, kv_scatter=(k1, v1, slots, q_width), status=status)
+    ops.gemm_bf16(out2, a, w, bias=bias, status=status)
+    ops.kv_append(k2, v2, out2[:, q_width:q_width + kv_width], out2[:, q_width + kv_width:], slots, m,
+                  status)
+    torch.cuda.synchronize()
+    assert torch.equal(out1, out2) and torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert status.tolist() == [0, 0, 0, 0]
+    assert int((k1 != 0).any(dim=-1).sum()) == (m - 1) * kv_heads
