@@ -33,13 +33,16 @@ using namespace decode_attn;
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 
-template <int LPK>   // lanes per key row: 2, 4, 8, 16 or 32 (head_dim <= 8 * LPK)
-__global__ void __launch_bounds__(DEC_THREADS)
+// LPK: lanes per key row: 2, 4, 8, 16 or 32 (head_dim <= 8 * LPK).  Two instances per LPK:
+// batches of four keys per thread at four CTAs per SM, and batches of two at six CTAs per
+// SM for launches with more CTAs than four per SM hold at once.  Both sum in the same order.
+template <int LPK, int UB, int MIN_CTAS>
+__global__ void __launch_bounds__(DEC_THREADS, MIN_CTAS)
 attention_decode_kernel(Args a) {
     __shared__ Shared<DEC_WARPS> sh;
     prb_grid_launch_dependents();
     prb_grid_wait();
-    unit<LPK, DEC_WARPS>(a, blockIdx.x, blockIdx.y, blockIdx.z, sh);
+    unit<LPK, DEC_WARPS, UB>(a, blockIdx.x, blockIdx.y, blockIdx.z, sh);
 }
 }  // namespace
 
@@ -83,8 +86,13 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
     a.max_pages = max_pages; a.num_pages = num_pages; a.scale = scale; a.window = window;
     a.workspace = workspace; a.counters = counters; a.max_splits = max_splits;
     a.split = split_keys; a.status = status;
-#define PRB_DEC(L) \
-    e = prb_launch_dependent(attention_decode_kernel<L>, grid, dim3(DEC_THREADS), 0, stream, a)
+    // more CTAs than fit at four per SM: the leaner instance, six per SM
+    const bool many = (long)n_list * n_heads * max_splits > 4L * 148;
+#define PRB_DEC(L)                                                                               \
+    e = many ? prb_launch_dependent(attention_decode_kernel<L, 2, 6>, grid, dim3(DEC_THREADS), 0, \
+                                    stream, a)                                                   \
+             : prb_launch_dependent(attention_decode_kernel<L, 4, 4>, grid, dim3(DEC_THREADS), 0, \
+                                    stream, a)
     cudaError_t e;
     if (pieces <= 2) PRB_DEC(2);
     else if (pieces <= 4) PRB_DEC(4);

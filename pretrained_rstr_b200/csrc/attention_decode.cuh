@@ -76,7 +76,9 @@ template <int NW> struct Shared {
 
 // One (token list place idx, head h, split s).  LPK lanes share a key row (head_dim <= 8 *
 // LPK); NW warps of the CTA take part; barriers inside are reached by all of them or none.
-template <int LPK, int NW>
+// UB: keys per thread in a register batch (4: most bytes in flight per thread; 2: fewer
+// registers, so more CTAs per SM when there are many units).
+template <int LPK, int NW, int UB = 4>
 __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Shared<NW>& sh) {
     float* sh_m = sh.m;
     float* sh_l = sh.l;
@@ -134,7 +136,6 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
     // Keys k_begin + warp*KPW + kslot, stepping NW*KPW, in batches of UB per thread.  Two
     // batches of registers take turns: the loads of the next batch are issued before the
     // current one is scored, so some are always in flight.
-    constexpr int UB = 4;
     constexpr int BATCH = NW * KPW * UB;
     struct Batch {
         uint4 k[UB], v[UB];

@@ -106,12 +106,16 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
                 n_head, scale, window, ctx.status)
     if ctx.n_singles is None or ctx.n_singles > 0:
         n_list = lay.single_cap if ctx.n_singles is None else ctx.n_singles
-        # about four CTAs per SM: many (token, head) pairs get fewer, longer splits (more pairs
-        # than CTAs fit at once still get two, which evens out the last round)
+        # about four CTAs per SM: many (token, head) pairs get fewer, longer splits, and one
+        # each when there are more pairs than that (the kernel then runs its leaner instance)
         granule = ops.decode_split()
         most = -(-ctx.max_context // granule)
         pairs = max(1, n_list * n_head)
-        wanted = max(1, min(most, -(-DECODE_CTAS // pairs) if pairs < DECODE_CTAS else 2))
+        if pairs < DECODE_CTAS:
+            wanted = -(-DECODE_CTAS // pairs)
+        else:
+            wanted = 1
+        wanted = max(1, min(most, wanted))
         split_keys = -(-ctx.max_context // wanted // granule) * granule
         max_splits = -(-ctx.max_context // split_keys)
         cap = ctx.runtime.max_requests * SINGLE_MAX_Q
