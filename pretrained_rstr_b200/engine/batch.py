@@ -67,7 +67,9 @@ class BatchLayout:
         self.tokens = take(t_cap)
         self.positions = take(t_cap)
         self.seq_of_token = take(t_cap)
-        self.logit_rows = take(t_cap)
+        # rows of logits are padded to a power of two, which may exceed the token capacity
+        self.row_cap = 1 << max(3, (t_cap - 1).bit_length())
+        self.logit_rows = take(self.row_cap)
         self.q_start = take(b_cap + 1)
         self.kv_len = take(b_cap)
         self.state_slot = take(b_cap)
@@ -94,7 +96,7 @@ class BatchLayout:
                 buf[lay.tokens:lay.tokens + lay.t_cap],
                 buf[lay.positions:lay.positions + lay.t_cap],
                 buf[lay.seq_of_token:lay.seq_of_token + lay.t_cap],
-                buf[lay.logit_rows:lay.logit_rows + lay.t_cap],
+                buf[lay.logit_rows:lay.logit_rows + lay.row_cap],
                 buf[lay.q_start:lay.q_start + lay.b_cap + 1],
                 buf[lay.kv_len:lay.kv_len + lay.b_cap],
                 buf[lay.state_slot:lay.state_slot + lay.b_cap],
@@ -227,7 +229,7 @@ def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: L
     tok = host_np[lay.tokens:lay.tokens + lay.t_cap]
     pos = host_np[lay.positions:lay.positions + lay.t_cap]
     seq = host_np[lay.seq_of_token:lay.seq_of_token + lay.t_cap]
-    rows = host_np[lay.logit_rows:lay.logit_rows + lay.t_cap]
+    rows = host_np[lay.logit_rows:lay.logit_rows + lay.row_cap]
     qs = host_np[lay.q_start:lay.q_start + lay.b_cap + 1]
     kv = host_np[lay.kv_len:lay.kv_len + lay.b_cap]
     ss = host_np[lay.state_slot:lay.state_slot + lay.b_cap]

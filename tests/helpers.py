@@ -24,7 +24,15 @@ TINY_B = {
     "n_positions": 256, "layer_norm_epsilon": 1e-6, "activation_function": "gelu",
     "scale_attn_weights": True, "scale_attn_by_inverse_layer_idx": True,
 }
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1)}
+# A third one with the head size (64) and widths (multiples of 64) that the tcgen05 prompt
+# attention and the TMA decode product take, and contexts of several 128-query tiles.
+TINY_C = {
+    "architectures": ["GPT2LMHeadModel"], "model_type": "gpt2",
+    "n_layer": 2, "n_embd": 128, "n_head": 2, "n_inner": 448, "vocab_size": 700,
+    "n_positions": 512, "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new",
+    "scale_attn_weights": True, "scale_attn_by_inverse_layer_idx": False,
+}
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
 
 # Absolute tolerance on logits.  Random-weight logits are O(0.2); float32 differences
 # come from summation order only; bfloat16 ones from rounding activations to 8 bits

@@ -7,7 +7,7 @@ from helpers import ATOL, TINY, Replayer, compare, make_folder, oracle_logits, r
 
 pytestmark = pytest.mark.gpu
 
-CASES = [(name, dtype) for name in ("A", "B") for dtype in ("float32", "bfloat16")]
+CASES = [(name, dtype) for name in ("A", "B", "C") for dtype in ("float32", "bfloat16")]
 
 
 @pytest.fixture(scope="module")
@@ -22,7 +22,7 @@ def folders(tmp_path_factory):
 
 def _prompts(name):
     raw, seed = TINY[name]
-    lengths = [5, 17, 40, 100] if name == "A" else [1, 9, 33, 64, 130, 250]
+    lengths = {"A": [5, 17, 40, 100], "B": [1, 9, 33, 64, 130, 250], "C": [3, 64, 129, 300, 500]}[name]
     return {f"r{i}": random_tokens(n, raw["vocab_size"], 100 * seed + i)
             for i, n in enumerate(lengths)}
 
@@ -33,7 +33,7 @@ def test_whole(folders, name, dtype):
     folder = folders[(name, dtype)]
     prompts = _prompts(name)
     oracle = oracle_logits(folder, prompts)
-    rp = Replayer(folder, dtype, max_tokens=256)
+    rp = Replayer(folder, dtype, max_tokens=512)
     for rid, ids in prompts.items():
         rp.step([(rid, ids, list(range(len(ids))))], end=[rid])
     compare(rp.rows, oracle, ATOL[dtype])
@@ -45,7 +45,7 @@ def test_prefill_then_decode(folders, name, dtype):
     folder = folders[(name, dtype)]
     prompts = {k: v for k, v in _prompts(name).items() if len(v) > 33}
     oracle = oracle_logits(folder, prompts)
-    rp = Replayer(folder, dtype, max_tokens=256)
+    rp = Replayer(folder, dtype, max_tokens=512)
     for rid, ids in prompts.items():
         head = len(ids) - 32
         rp.step([(rid, ids[:head], [head - 1])])
@@ -60,8 +60,8 @@ def test_portions(folders, name, dtype):
     folder = folders[(name, dtype)]
     prompts = _prompts(name)
     oracle = oracle_logits(folder, prompts)
-    rp = Replayer(folder, dtype, max_tokens=256)
-    sizes = [7, 2, 19, 2, 5, 64, 3, 2, 31, 66]
+    rp = Replayer(folder, dtype, max_tokens=512)
+    sizes = [7, 2, 19, 2, 5, 64, 3, 2, 31, 66, 130]
     for rid, ids in prompts.items():
         at, k = 0, 0
         while at < len(ids):
@@ -80,7 +80,8 @@ def test_mixed_with_page_reuse(folders, name, dtype):
     folder = folders[(name, dtype)]
     raw, seed = TINY[name]
     n_pos = raw["n_positions"]
-    lengths = [40, 100, 17, 70, 128, 5, 90, 33] if name == "A" else [130, 64, 250, 9, 33, 200, 1, 120]
+    lengths = {"A": [40, 100, 17, 70, 128, 5, 90, 33], "B": [130, 64, 250, 9, 33, 200, 1, 120],
+               "C": [300, 130, 500, 64, 257, 9, 400, 128]}[name]
     prompts = {f"m{i}": random_tokens(n, raw["vocab_size"], 977 * seed + i)
                for i, n in enumerate(lengths)}
     oracle = oracle_logits(folder, prompts)
@@ -104,7 +105,7 @@ def test_mixed_with_page_reuse(folders, name, dtype):
             if at == 0 and rng.random() < 0.3 and len(live) > 1:
                 continue                                   # left out of this step
             if left > 34 and at < len(ids) - 16:
-                n = min(left - 16, rng.choice([2, 3, 8, 21, 64, 70]))
+                n = min(left - 16, rng.choice([2, 3, 8, 21, 64, 70, 140]))
             else:
                 n = 1                                      # decode the tail token by token
             entries.append((rid, ids[at:at + n], list(range(n))))
