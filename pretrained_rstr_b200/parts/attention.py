@@ -74,7 +74,7 @@ class CausalAttention(Mixer):
         self.out.forward(ctx, o, x, resid=x)
 
 
-DECODE_CTAS = int(os.environ.get("PRB200_DECODE_CTAS", "600"))
+DECODE_CTAS = int(os.environ.get("PRB200_DECODE_CTAS", "768"))
 USE_TC = os.environ.get("PRB200_ATTN_TC", "1") != "0"
 
 
@@ -106,8 +106,8 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
                 n_head, scale, window, ctx.status)
     if ctx.n_singles is None or ctx.n_singles > 0:
         n_list = lay.single_cap if ctx.n_singles is None else ctx.n_singles
-        # about four CTAs per SM: many (token, head) pairs get fewer, longer splits, and one
-        # each when there are more pairs than that (the kernel then runs its leaner instance)
+        # about five CTAs per SM (the kernel's leaner instance fits six): many (token, head)
+        # pairs get fewer, longer splits, and one each when there are more pairs than that
         granule = ops.decode_split()
         most = -(-ctx.max_context // granule)
         pairs = max(1, n_list * n_head)
