@@ -161,7 +161,8 @@ def timed_decode(engine, lm, batch, ctx_len, steps, warmup, vocab, seed):
     t0 = time.perf_counter()
     for k in range(steps):
         engine.step_index = k
-        engine.step()
+        engine.step(ahead=True)            # the host reads step k's tokens during step k + 1
+    engine.flush()
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
     engine.timing_events = None

@@ -226,3 +226,33 @@ PRB_API int prb_copy_pages(void* base, const int* pairs, int n_pairs, long page_
     PRB_LAUNCH_CHECK();
     return 0;
 }
+
+
+// ------------------------------------------------------------------ token feedback
+// A step that was launched before the step before it had reported its chosen tokens names
+// them by place: token id -(k + 1) stands for prev[k], the k-th token the sampling kernel
+// chose last.  This kernel puts the ids in (before the step's first kernel reads them).
+namespace {
+__global__ void resolve_tokens_kernel(int* __restrict__ tokens, int n, const int* __restrict__ prev,
+                                      int n_prev, int* status) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n) return;
+    const int v = tokens[t];
+    if (v >= 0) return;
+    const int k = -v - 1;
+    if (k >= n_prev) {
+        prb_set_status(status, PRB_S_ROW_RANGE, t, k, n_prev);
+        tokens[t] = 0;
+        return;
+    }
+    tokens[t] = prev[k];
+}
+}  // namespace
+
+PRB_API int prb_resolve_tokens(int* tokens, int n, const int* prev, int n_prev, int* status,
+                               cudaStream_t stream) {
+    if (n <= 0) return 0;
+    resolve_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, n, prev, n_prev, status);
+    PRB_LAUNCH_CHECK();
+    return 0;
+}

@@ -79,6 +79,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_bias_act.argtypes = [P, P, P, P, I, I, I, I, I, P]
     h.prb_kv_append.argtypes = [P, P, P, P, L, P, I, I, I, I, I, I, P, P]
     h.prb_copy_pages.argtypes = [P, P, I, L, I, I, P, P]
+    h.prb_resolve_tokens.argtypes = [P, I, P, I, P, P]
     h.prb_gemm_f32.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, P]
     h.prb_gemm_bf16.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, I, P, P]
     h.prb_gemm_bf16_scatter.argtypes = [P, P, P, P, I, I, I, L, L, L, I, I, P, P, P, I, I, I, I, I,
@@ -120,7 +121,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_set_pdl.restype = None
     h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
     h.prb_sample_max_top_k.argtypes = []
-    for name in ("prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
+    for name in ("prb_resolve_tokens", "prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
                  "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_bf16_scatter", "prb_gemm_smallm", "prb_gemm_smallm_max_rows",
                  "prb_gemm_smallm_max_norm_width", "prb_attention_generic", "prb_attention_decode",
                  "prb_attention_prefill", "prb_attention_prefill_supports",
@@ -585,6 +586,17 @@ def attention_prefill(out, q, k_pages, v_pages, block_table, positions, tile_req
         _p(positions), _p(tile_req), _p(tile_row0), _p(tile_rows), _p(tile_count), n_tiles,
         n_heads, kv_heads, head_dim, page_size, block_table.shape[1], num_pages, float(scale),
         int(window or 0), _p(status), _stream()), what)
+
+
+def resolve_tokens(tokens, n, prev, status) -> None:
+    """tokens[t] = prev[-tokens[t] - 1] wherever tokens[t] < 0 (t < n): ids that name a place
+    among the tokens the sampling kernel chose last."""
+    what = "resolve_tokens"
+    _no_record(what)
+    _need(tokens, torch.int32, "tokens", what)
+    _need(prev, torch.int32, "prev", what)
+    _check(lib().prb_resolve_tokens(_p(tokens), int(n), _p(prev), prev.numel(), _p(status),
+                                    _stream()), what)
 
 
 def max_top_k() -> int:

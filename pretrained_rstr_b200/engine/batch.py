@@ -163,6 +163,7 @@ class StepContext:
         # and only the device-side counts are valid)
         self.n_tiles: Optional[int] = None
         self.n_singles: Optional[int] = None
+        self.feedback = False               # token ids below zero name tokens chosen last
 
     @property
     def dtype(self) -> torch.dtype:

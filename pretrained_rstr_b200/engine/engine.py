@@ -17,7 +17,7 @@ import torch
 from ..csrc import ops
 from .batch import Entry
 from .loading import LoadedModel
-from .scheduler import Plan, Request, SamplingParams, Scheduler, SchedulerOptions
+from .scheduler import Plan, Request, SamplingParams, Scheduled, Scheduler, SchedulerOptions
 
 
 class Engine:
@@ -36,27 +36,34 @@ class Engine:
         self.rng_states = torch.zeros(n, dtype=torch.int64, device=dev)
         self._rng_started: Dict[Hashable, bool] = {}
         self._tokens_dev = self.runner.tokens_out
-        self._p = {  # pinned staging and device copies of the sampler's per-row options
-            "temperature": (torch.zeros(n, dtype=torch.float32, pin_memory=True),
-                            torch.zeros(n, dtype=torch.float32, device=dev)),
-            "top_p": (torch.zeros(n, dtype=torch.float32, pin_memory=True),
-                      torch.zeros(n, dtype=torch.float32, device=dev)),
-            "top_k": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
-                      torch.zeros(n, dtype=torch.int32, device=dev)),
-            "fresh": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
-                      torch.zeros(n, dtype=torch.int32, device=dev)),
-            "slots": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
-                      torch.zeros(n, dtype=torch.int32, device=dev)),
-            "seeds": (torch.zeros(n, dtype=torch.int64, pin_memory=True),
-                      torch.zeros(n, dtype=torch.int64, device=dev)),
-        }
+        def option_buffers():
+            # pinned staging and device copies of the sampler's per-row options
+            return {
+                "temperature": (torch.zeros(n, dtype=torch.float32, pin_memory=True),
+                                torch.zeros(n, dtype=torch.float32, device=dev)),
+                "top_p": (torch.zeros(n, dtype=torch.float32, pin_memory=True),
+                          torch.zeros(n, dtype=torch.float32, device=dev)),
+                "top_k": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
+                          torch.zeros(n, dtype=torch.int32, device=dev)),
+                "fresh": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
+                          torch.zeros(n, dtype=torch.int32, device=dev)),
+                "slots": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
+                          torch.zeros(n, dtype=torch.int32, device=dev)),
+                "seeds": (torch.zeros(n, dtype=torch.int64, pin_memory=True),
+                          torch.zeros(n, dtype=torch.int64, device=dev)),
+            }
+        # two sets take turns: with a step in flight the set of the step before is free
+        self._option_sets = [option_buffers(), option_buffers()]
+        self._option_turn = 0
+        self._p = self._option_sets[0]
         self.max_top_k = ops.max_top_k()
         # optional (start events, end events) lists: step ``step_index`` records its pair
         # around the device work of the step (measurement only)
         self.timing_events = None
         self.step_index = 0
-        self._prepared = None              # (entries, context) of a step described ahead of time
-        self.ahead = {"used": 0, "dropped": 0}
+        self._prepared = None              # (entries, context, requests) of a step described ahead
+        self._flight = None                # (plan, entries, samplers, ticket) of a launched step
+        self.ahead = {"used": 0, "dropped": 0, "dead_rows": 0}
 
     # ------------------------------------------------------------------ requests
     def submit(self, rid: Hashable, prompt: Sequence[int], max_new_tokens: int,
@@ -85,98 +92,149 @@ class Engine:
         self.scheduler.cancel(rid)
 
     # ---------------------------------------------------------------------- step
-    def step(self) -> List[Request]:
-        """One iteration; returns the requests that finished in it.
+    def step(self, ahead: bool = False) -> List[Request]:
+        """One iteration; returns the requests that finished.
 
-        While the GPU runs the step, the host already describes the next one (who decodes
-        at which position into which slot) on the assumption that nobody stops on a stop
-        token; only the token ids are filled in when they arrive.  If the assumption was
-        wrong the prepared step is dropped and described again."""
-        plan = self.scheduler.next_plan()
-        if not plan.scheduled:
-            self._drop_prepared()
-            return []
-        entries: List[Entry] = []
-        samplers: List[Request] = []
-        for item in plan.scheduled:
-            tokens = self.scheduler.step_tokens(item)
-            wants = self.scheduler.wants_logits(item)
-            entries.append(Entry(item.rid, tokens, [len(tokens) - 1] if wants else []))
-            if wants:
-                samplers.append(self.scheduler.running[item.rid])
-        ctx = self._take_prepared(entries)
+        While the GPU runs a step, the host already describes the next one (who decodes at
+        which position into which slot) on the assumption that nobody stops on a stop token
+        and nobody new arrives.  ``ahead=False``: the call waits for its step's tokens, and
+        the described step only needs its token ids patched in.  ``ahead=True``: the
+        described step is launched at the start of the next call, before the tokens of the
+        step in flight have reached the host (it names them by place and the device puts
+        them in); the call then returns what finished in the step launched by the call
+        before, so the host runs one step behind the GPU (:meth:`flush` catches up).  A
+        request that stops on a stop token has by then one token too many in flight: its
+        row is dropped, its pages are freed when it ends."""
+        flight, prepared = self._flight, self._prepared
+        self._flight = self._prepared = None
+        launched = None
+        if flight is not None and prepared is not None and self._still_steady(prepared[0]):
+            entries, ctx, samplers = prepared
+            launched = self._launch(Plan(tuple(Scheduled(e.rid, "decode", 1) for e in entries),
+                                         (), 0, 0), entries, ctx, samplers)
+            self.scheduler.stats["iterations"] += 1
+            self.scheduler.stats["scheduled_tokens"] += len(entries)
+            self.ahead["used"] += 1
+            prepared = None
+        done = self._finish(flight) if flight is not None else []
+        if launched is None:
+            plan = self.scheduler.next_plan()
+            if not plan.scheduled:
+                self._drop(prepared)
+                return done
+            entries: List[Entry] = []
+            samplers: List[Request] = []
+            for item in plan.scheduled:
+                tokens = self.scheduler.step_tokens(item)
+                wants = self.scheduler.wants_logits(item)
+                entries.append(Entry(item.rid, tokens, [len(tokens) - 1] if wants else []))
+                if wants:
+                    samplers.append(self.scheduler.running[item.rid])
+            ctx = self._take_prepared(prepared, entries)
+            if ctx is None:
+                ctx = self.runner.prepare(entries)
+            launched = self._launch(plan, entries, ctx, samplers)
+        self._prepared = self._prepare_ahead(launched)     # overlaps the GPU's work
+        if ahead:
+            self._flight = launched
+            return done
+        return done + self._finish(launched)
+
+    def flush(self) -> List[Request]:
+        """Catch up with the GPU: wait for the step in flight (``step(ahead=True)``) and
+        return the requests that finished in it."""
+        flight, self._flight = self._flight, None
+        done = self._finish(flight) if flight is not None else []
+        return done
+
+    # ------------------------------------------------------------- launch and finish
+    def _launch(self, plan: Plan, entries: List[Entry], ctx, samplers: List[Request]):
         if self.timing_events is not None:
             self.runner.start_event = self.timing_events[0][self.step_index]
-        if ctx is None:
-            ctx = self.runner.prepare(entries)
         logits = self.runner.launch(ctx, entries)
         self.runner.start_event = None
-        new_tokens: Dict[Hashable, int] = {}
+        ticket = None
         if samplers:
             self._launch_choice(logits, samplers)
-            self._prepare_ahead(plan)                  # overlaps the GPU's work
-            chosen = self._fetch_choice(len(samplers))
+            ticket = self.runner.queue_result()
+        return (plan, entries, samplers, ticket)
+
+    def _finish(self, flight) -> List[Request]:
+        """Wait for a launched step's tokens and report them to the scheduler."""
+        plan, _entries, samplers, ticket = flight
+        new_tokens: Dict[Hashable, int] = {}
+        if ticket is not None:
+            chosen = self.runner.wait_result(ticket)[:len(samplers)].tolist()
             new_tokens = {r.rid: t for r, t in zip(samplers, chosen)}
+            self.ahead["dead_rows"] += sum(1 for r in samplers if r.rid not in self.scheduler.running)
         done = self.scheduler.complete(plan, new_tokens)
         for r in done:
             self._rng_started.pop(r.rid, None)
         return done
 
     # ------------------------------------------------------------- preparing ahead
-    def _prepare_ahead(self, plan: Plan) -> None:
-        """Describe the next step before this one's tokens are known.  Only in the steady
-        state: nothing waiting or deferred, and every scheduled request will be decoding."""
-        self._prepared = None
+    def _prepare_ahead(self, launched):
+        """Describe the step after ``launched`` before its tokens are known.  Only in the
+        steady state: nothing waiting or deferred, and every scheduled request will be
+        decoding.  Token ids are given by place among the tokens ``launched`` chooses."""
+        plan, _entries, samplers, ticket = launched
         sched = self.scheduler
-        if sched.waiting or plan.deferred or len(plan.scheduled) != len(sched.running):
-            return
+        if ticket is None or sched.waiting or plan.deferred or \
+                len(plan.scheduled) != len(sched.running):
+            return None
+        row = {r.rid: i for i, r in enumerate(samplers)}
         ahead = []
         for item in plan.scheduled:
-            r = sched.running[item.rid]
+            r = sched.running.get(item.rid)
+            if r is None:
+                return None                             # ended while the step was in flight
             if item.phase == "prefill" and r.computed + item.tokens < len(r.prompt):
-                return                                  # still in its prompt: not predicted
+                return None                             # still in its prompt: not predicted
             n_out = len(r.output) + 1
             if r.cancelled or n_out >= r.max_new_tokens or \
                     len(r.prompt) + n_out > self.lm.cache.max_positions:
                 continue                                # finishes with this step
             ahead.append(r)
         if not ahead:
-            return
+            return None
         ahead.sort(key=lambda r: (r.arrival, str(r.rid)))
-        entries = [Entry(r.rid, [0], [0]) for r in ahead]          # placeholder token ids
+        entries = [Entry(r.rid, [-(row[r.rid] + 1)], [0]) for r in ahead]
         try:
-            ctx = self.runner.prepare(entries)
+            ctx = self.runner.prepare(entries, feedback=True)
         except Exception:
-            return
-        self._prepared = (entries, ctx)
+            return None
+        return (entries, ctx, ahead)
 
-    def _take_prepared(self, entries: List[Entry]):
-        """The step prepared ahead, if it is exactly the step that is now due."""
-        prepared, self._prepared = self._prepared, None
+    def _still_steady(self, entries: List[Entry]) -> bool:
+        """May the step described ahead be launched before the step in flight is known?"""
+        sched = self.scheduler
+        if sched.waiting or len(entries) > len(sched.running):
+            return False
+        return all(e.rid in sched.running and not sched.running[e.rid].cancelled for e in entries)
+
+    def _take_prepared(self, prepared, entries: List[Entry]):
+        """The step described ahead, with the real token ids, if it is exactly the step
+        that is now due."""
         if prepared is None:
             return None
-        ahead, ctx = prepared
+        ahead, ctx, _ = prepared
         same = len(ahead) == len(entries) and all(
             a.rid == e.rid and len(e.tokens) == 1 and list(e.want) == [0]
             for a, e in zip(ahead, entries))
         if not same:
-            self._abort_entries(ahead)
-            self.ahead["dropped"] += 1
+            self._drop(prepared)
             return None
         self.runner.patch_tokens(ctx, entries)
         self.ahead["used"] += 1
         return ctx
 
-    def _drop_prepared(self) -> None:
-        prepared, self._prepared = self._prepared, None
-        if prepared is not None:
-            self._abort_entries(prepared[0])
-            self.ahead["dropped"] += 1
-
-    def _abort_entries(self, entries: List[Entry]) -> None:
-        for e in entries:                               # requests that ended are closed already
+    def _drop(self, prepared) -> None:
+        if prepared is None:
+            return
+        for e in prepared[0]:                           # requests that ended are closed already
             if e.rid in self.lm.cache.requests:
                 self.lm.cache.abort(e.rid)
+        self.ahead["dropped"] += 1
 
     def _launch_choice(self, logits: torch.Tensor, requests: List[Request]) -> None:
         """Launch the kernel that chooses a token for every row (no synchronisation)."""
@@ -185,6 +243,8 @@ class Engine:
         if all(r.sampling.greedy for r in requests):
             ops.sample(out, logits, n)
         else:
+            self._option_turn ^= 1
+            self._p = self._option_sets[self._option_turn]
             for i, r in enumerate(requests):
                 sp = r.sampling
                 self._p["temperature"][0][i] = 0.0 if sp.greedy else float(sp.temperature)
@@ -209,20 +269,20 @@ class Engine:
         if self.timing_events is not None:
             self.timing_events[1][self.step_index].record()
 
-    def _fetch_choice(self, n: int) -> List[int]:
-        """Wait for the step and read the chosen tokens (and the device status word)."""
-        host = self.runner.fetch_result()
-        return host[:n].tolist()
-
     # ------------------------------------------------------------------ generate
     def run(self) -> None:
         """Iterate until every submitted request has finished."""
         while not self.scheduler.idle:
             before = (len(self.scheduler.waiting), len(self.scheduler.running))
-            done = self.step()
-            if not done and not self.scheduler.running and self.scheduler.waiting and \
+            in_flight = self._flight is not None
+            done = self.step(ahead=True)
+            if not done and not in_flight and self._flight is None and \
+                    not self.scheduler.running and self.scheduler.waiting and \
                     before == (len(self.scheduler.waiting), 0):
                 raise RuntimeError("scheduler made no progress: a waiting request cannot be admitted")
+        self.flush()
+        self._drop(self._prepared)
+        self._prepared = None
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int,
                  sampling: Optional[SamplingParams] = None,

@@ -62,6 +62,12 @@ class ModelRunner:
         self.result = torch.zeros(runtime.max_requests + 4, dtype=torch.int32, device=self.device)
         self.result_host = torch.zeros(runtime.max_requests + 4, dtype=torch.int32,
                                        pin_memory=True)
+        # two host copies take turns, so that a step's tokens can be read while the next
+        # step's copy is already queued
+        self._result_hosts = [self.result_host,
+                              torch.zeros_like(self.result_host).pin_memory()]
+        self._result_events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._result_turn = 0
         self.tokens_out = self.result[:runtime.max_requests]
         self.status = self.result[runtime.max_requests:]
         self._status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
@@ -102,12 +108,16 @@ class ModelRunner:
         return self.launch(self.prepare(entries), entries)
 
     def launch(self, ctx: StepContext, entries: Sequence[Entry]) -> torch.Tensor:
-        """Second half of a step: copy the prepared arrays to the device, run, commit."""
+        """Second half of a step: copy the prepared arrays to the device, run, commit.
+        Token ids below zero name places among the tokens chosen last (``prepare`` with
+        ``feedback``); they are put in on the device before the model runs."""
         try:
             if self.fail_next_step is not None:
                 exc, self.fail_next_step = self.fail_next_step, None
                 raise exc
             self.upload(ctx)
+            if ctx.feedback:
+                ops.resolve_tokens(ctx.tokens, ctx.n_tokens, self.tokens_out, self.status)
             logits = self._run(ctx)
         except Exception:
             self.abort(entries)
@@ -127,6 +137,7 @@ class ModelRunner:
             raise StepError(f"token id outside the vocabulary of {vocab}")
         ctx.staging.numpy()[lay.tokens:lay.tokens + len(flat)] = flat
         ctx.host.tokens = flat
+        ctx.feedback = False
 
     def _run(self, ctx: StepContext) -> torch.Tensor:
         """Run the model for a prepared step: directly, or, for small steps when graphs are
@@ -166,9 +177,10 @@ class ModelRunner:
         ops.add_launches(kernels)
         return logits
 
-    def prepare(self, entries: Sequence[Entry]) -> StepContext:
+    def prepare(self, entries: Sequence[Entry], feedback: bool = False) -> StepContext:
         """First half of a step: validate the batch, reserve cache slots, and describe the
-        step in pinned host memory (nothing touches the device yet)."""
+        step in pinned host memory (nothing touches the device yet).  With ``feedback`` a
+        token id -(k + 1) is allowed: the k-th token the sampling kernel chose last."""
         if not entries:
             raise StepError("a step needs at least one entry")
         rids = [e.rid for e in entries]
@@ -190,7 +202,8 @@ class ModelRunner:
                     raise StepError(f"request {e.rid!r}: wanted place {w} outside its "
                                     f"{len(e.tokens)} tokens")
             toks = np.asarray(e.tokens)
-            if toks.dtype.kind not in "iu" or int(toks.min()) < 0 or int(toks.max()) >= vocab:
+            lowest = -self.runtime.max_requests if feedback else 0
+            if toks.dtype.kind not in "iu" or int(toks.min()) < lowest or int(toks.max()) >= vocab:
                 bad = [t for t in e.tokens if not (isinstance(t, (int, np.integer)) and 0 <= t < vocab)]
                 raise StepError(f"request {e.rid!r}: token id {bad[0] if bad else '?'} outside the "
                                 f"vocabulary of {vocab}")
@@ -208,10 +221,12 @@ class ModelRunner:
                 self.cache.abort(rid)
             raise
         try:
-            return self._describe(entries, reservations)
+            ctx = self._describe(entries, reservations)
         except Exception:
             self.abort(entries)
             raise
+        ctx.feedback = feedback and any(t < 0 for e in entries for t in e.tokens)
+        return ctx
 
     def _describe(self, entries, reservations) -> StepContext:
         n_req = len(entries)
@@ -315,7 +330,10 @@ class ModelRunner:
 
     def commit(self, entries: Sequence[Entry]) -> None:
         for e in entries:
-            self.cache.commit(e.rid, list(e.tokens))
+            # ids that are not known on the host yet are not recorded (such pages are not
+            # offered for sharing)
+            known = all(t >= 0 for t in e.tokens)
+            self.cache.commit(e.rid, list(e.tokens) if known else None)
 
     def abort(self, entries: Sequence[Entry]) -> None:
         for e in entries:
@@ -325,16 +343,31 @@ class ModelRunner:
     def fetch_result(self) -> torch.Tensor:
         """One device-to-host copy of the sampled tokens and the status word
         (synchronises); raises if a kernel recorded an index out of range."""
-        self.result_host.copy_(self.result, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        return self.wait_result(self.queue_result())
+
+    def queue_result(self) -> int:
+        """Queue the copy of the sampled tokens and the status word to the host behind the
+        work launched so far; returns a ticket for :meth:`wait_result`.  Work launched
+        afterwards does not delay the ticket."""
+        turn = self._result_turn
+        self._result_turn ^= 1
+        self._result_hosts[turn].copy_(self.result, non_blocking=True)
+        self._result_events[turn].record()
+        return turn
+
+    def wait_result(self, ticket: int) -> torch.Tensor:
+        """Wait for a queued copy; raises if a kernel had recorded an index out of range."""
+        self._result_events[ticket].synchronize()
+        host = self._result_hosts[ticket]
         n = self.runtime.max_requests
-        code = int(self.result_host[n])
+        code = int(host[n])
         if code != 0:
-            detail = [int(v) for v in self.result_host[n + 1:]]
+            detail = [int(v) for v in host[n + 1:]]
+            torch.cuda.current_stream().synchronize()
             self.status.zero_()
             raise StepError(f"device status {code}: {ops.STATUS_TEXT.get(code, 'unknown')} "
                             f"{detail}")
-        return self.result_host
+        return host
 
     def check_status(self) -> None:
         """Read the device status word (synchronises); raises if a kernel recorded an

@@ -247,7 +247,9 @@ class Scheduler:
         requests that wanted logits.  Returns the requests that finished."""
         done: List[Request] = []
         for item in plan.scheduled:
-            r = self.running[item.rid]
+            r = self.running.get(item.rid)
+            if r is None:           # ended while this step was already in flight
+                continue
             r.computed += item.tokens
             if item.phase == "prefill" and r.computed < len(r.prompt):
                 continue

@@ -92,9 +92,9 @@ def test_stop_token_and_capacity(folders):
 
 
 def test_stop_token_inside_a_batch(folders):
-    """The engine describes the next step while the GPU runs this one, assuming nobody
-    stops on a stop token.  One of three requests does stop: the prepared step is dropped,
-    the others go on unchanged, and no page is lost."""
+    """The engine launches the next step before this one's tokens have reached the host,
+    assuming nobody stops on a stop token.  One of three requests does stop: its row in the
+    step already in flight is dropped, the others go on unchanged, and no page is lost."""
     from pretrained_rstr_b200 import generate_batch, load_lm
     raw, seed = TINY["B"]
     folder = folders[("B", "float32")]
@@ -110,6 +110,54 @@ def test_stop_token_inside_a_batch(folders):
     m.eos_ids = (stop,)
     assert generate_batch(m, prompts, 20, opts) == want
     ahead = m.engine.stats()["prepared_ahead"]
-    assert ahead["used"] > 10 and ahead["dropped"] >= 1
+    # the step after the stop token was already in flight: its row for that request is dropped
+    assert ahead["used"] > 10 and ahead["dead_rows"] >= 1
+    m.engine.lm.cache.check()
+    assert not m.engine.lm.cache.requests
+
+
+def test_arrivals_cancels_and_mixed_sampling_with_steps_in_flight(folders):
+    """The host runs one step behind the GPU (``step(ahead=True)``): requests with
+    different sampling options side by side, one arriving and one cancelled while steps
+    are in flight; every output equals the plain implementation's (a prefix of it for the
+    cancelled request)."""
+    from pretrained_rstr_b200 import load_lm
+    from pretrained_rstr_b200.engine.scheduler import SamplingParams
+    raw, seed = TINY["C"]
+    folder = folders[("C", "float32")]
+    plain = plain_gpt2.PlainGPT2(folder)
+    m = load_lm(folder, gpu=True, dtype="float32", max_lanes=4, max_batched_tokens=256)
+    eng = m.engine
+    prompts = [random_tokens(n, raw["vocab_size"], 900 + i) for i, n in enumerate([11, 70, 5, 33])]
+    opts = [SamplingParams(), SamplingParams(temperature=0.9, top_k=20, seed=5),
+            SamplingParams(temperature=1.4, top_k=7, top_p=0.8, seed=6), SamplingParams()]
+    n_new = [30, 25, 40, 12]
+    want = []
+    for p, o, n in zip(prompts, opts, n_new):
+        want.append(plain_gpt2.greedy_generate(plain, p, n) if o.greedy else
+                    plain_gpt2.sample_generate(plain, p, n, o.temperature, o.top_k, o.top_p, o.seed))
+    for i in (0, 1):
+        eng.submit(i, prompts[i], n_new[i], opts[i])
+    finished, calls = {}, 0
+    while not eng.scheduler.idle or calls < 8:
+        if calls == 6:
+            eng.submit(2, prompts[2], n_new[2], opts[2])      # arrives while steps are in flight
+            eng.submit(3, prompts[3], n_new[3], opts[3])
+        if calls == 14:
+            eng.cancel(0)
+        for r in eng.step(ahead=True):
+            finished[r.rid] = r
+        calls += 1
+        assert calls < 400
+    for r in eng.flush():
+        finished[r.rid] = r
+    assert sorted(finished) == [1, 2, 3]               # a cancelled request is not reported as done
+    finished[0] = eng.scheduler.finished[0]
+    assert finished[0].finish_reason == "cancelled"
+    assert 3 < len(finished[0].output) < n_new[0] and finished[0].output == want[0][:len(finished[0].output)]
+    for i in (1, 2, 3):
+        assert finished[i].output == want[i], f"request {i}"
+    stats = eng.stats()
+    assert stats["prepared_ahead"]["used"] > 20
     m.engine.lm.cache.check()
     assert not m.engine.lm.cache.requests
