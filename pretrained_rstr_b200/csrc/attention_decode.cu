@@ -36,17 +36,46 @@ constexpr int DEC_WARPS = DEC_THREADS / 32;
 // LPK: lanes per key row: 2, 4, 8, 16 or 32 (head_dim <= 8 * LPK).  Two instances per LPK:
 // batches of four keys per thread at four CTAs per SM, and batches of two at six CTAs per
 // SM for launches with more CTAs than four per SM hold at once.  Both sum in the same order.
-template <int LPK, int UB, int MIN_CTAS>
+template <int LPK, int UB, int MIN_CTAS, bool CLUSTER>
 __global__ void __launch_bounds__(DEC_THREADS, MIN_CTAS)
 attention_decode_kernel(Args a) {
     __shared__ Shared<DEC_WARPS> sh;
     prb_grid_launch_dependents();
     prb_grid_wait();
-    unit<LPK, DEC_WARPS, UB>(a, blockIdx.x, blockIdx.y, blockIdx.z, sh);
+    unit<LPK, DEC_WARPS, UB, CLUSTER>(a, blockIdx.x, blockIdx.y, blockIdx.z, sh);
+}
+
+// Launch with programmatic dependent launch and, for `cluster_z` > 1, the CTAs of a
+// (token, head) (grid z) as one thread-block cluster.
+template <typename K>
+cudaError_t launch_decode(K kernel, dim3 grid, int cluster_z, cudaStream_t stream, const Args& a) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DEC_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = prb_pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = 1;
+    if (cluster_z > 1) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 1;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = (unsigned)cluster_z;
+        cfg.numAttrs = 2;
+    }
+    cfg.attrs = attr;
+    return cudaLaunchKernelEx(&cfg, kernel, a);
 }
 }  // namespace
 
 PRB_API int prb_attention_decode_split() { return SPLIT; }
+
+// Switch (for measurements): 0 = splits always merge through the workspace.
+static int g_decode_clusters = 1;
+static int prb_decode_clusters() { return g_decode_clusters; }
+PRB_API void prb_attention_decode_set_clusters(int on) { g_decode_clusters = on ? 1 : 0; }
 #ifdef PRB_TRACE
 PRB_API int prb_attention_decode_trace(unsigned long long* host, int n) {
     return (int)cudaMemcpyFromSymbol(host, g_dec_trace, sizeof(unsigned long long) * n);
@@ -86,13 +115,22 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
     a.max_pages = max_pages; a.num_pages = num_pages; a.scale = scale; a.window = window;
     a.workspace = workspace; a.counters = counters; a.max_splits = max_splits;
     a.split = split_keys; a.status = status;
-    // more CTAs than fit at four per SM: the leaner instance, six per SM
+    // more CTAs than fit at four per SM: the leaner instance, six per SM; two to eight
+    // splits: the CTAs of a (token, head) form a cluster and merge through shared memory
     const bool many = (long)n_list * n_heads * max_splits > 4L * 148;
+    const bool cluster = max_splits >= 2 && max_splits <= 8 && prb_decode_clusters();
 #define PRB_DEC(L)                                                                               \
-    e = many ? prb_launch_dependent(attention_decode_kernel<L, 2, 6>, grid, dim3(DEC_THREADS), 0, \
-                                    stream, a)                                                   \
-             : prb_launch_dependent(attention_decode_kernel<L, 4, 4>, grid, dim3(DEC_THREADS), 0, \
-                                    stream, a)
+    do {                                                                                         \
+        if (cluster)                                                                             \
+            e = many ? launch_decode(attention_decode_kernel<L, 2, 6, true>, grid, max_splits,   \
+                                     stream, a)                                                  \
+                     : launch_decode(attention_decode_kernel<L, 4, 4, true>, grid, max_splits,   \
+                                     stream, a);                                                 \
+        else                                                                                     \
+            e = many ? launch_decode(attention_decode_kernel<L, 2, 6, false>, grid, 1, stream, a) \
+                     : launch_decode(attention_decode_kernel<L, 4, 4, false>, grid, 1, stream,   \
+                                     a);                                                         \
+    } while (0)
     cudaError_t e;
     if (pieces <= 2) PRB_DEC(2);
     else if (pieces <= 4) PRB_DEC(4);

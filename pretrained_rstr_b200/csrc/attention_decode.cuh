@@ -72,13 +72,58 @@ template <int NW> struct Shared {
     float o[NW][MAX_DH];
     int last;
     int pages[MAX_SPLIT_PAGES];     // pages of this split
+    float part_o[MAX_DH];           // this split's result, read by the cluster's first CTA
+    float part_ml[2];
 };
+
+// Thread-block cluster helpers (the splits of one (token, head) form a cluster).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local, int rank) {
+    const uint32_t laddr = (uint32_t)__cvta_generic_to_shared(local);
+    uint32_t raddr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(laddr), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
+    return v;
+}
+
+// The cluster's first CTA merges the splits s_first..s_last in split order, reading each
+// split's (maximum, sum, weighted values) from that CTA's shared memory; the arithmetic is
+// that of the workspace merge.
+template <int NW>
+__device__ __forceinline__ void merge_cluster(const Args& a, int t, int h, int s_first, int s_last,
+                                              Shared<NW>& sh) {
+    __nv_bfloat16* o = a.out + (size_t)t * a.out_stride + (size_t)h * a.head_dim;
+    float mg = -INFINITY;
+    for (int ss = s_first; ss <= s_last; ++ss) mg = fmaxf(mg, ld_cluster_f32(&sh.part_ml[0], ss));
+    float lg = 0.0f;
+    for (int ss = s_first; ss <= s_last; ++ss) {
+        const float ms = ld_cluster_f32(&sh.part_ml[0], ss);
+        lg += ld_cluster_f32(&sh.part_ml[1], ss) * ((ms == -INFINITY) ? 0.0f : __expf(ms - mg));
+    }
+    for (int d = threadIdx.x; d < a.head_dim; d += (NW * 32)) {
+        float od = 0.0f;
+        for (int ss = s_first; ss <= s_last; ++ss) {
+            const float ms = ld_cluster_f32(&sh.part_ml[0], ss);
+            od += ld_cluster_f32(&sh.part_o[d], ss) * ((ms == -INFINITY) ? 0.0f : __expf(ms - mg));
+        }
+        o[d] = __float2bfloat16_rn(lg > 0.0f ? od / lg : 0.0f);
+    }
+}
 
 // One (token list place idx, head h, split s).  LPK lanes share a key row (head_dim <= 8 *
 // LPK); NW warps of the CTA take part; barriers inside are reached by all of them or none.
 // UB: keys per thread in a register batch (4: most bytes in flight per thread; 2: fewer
 // registers, so more CTAs per SM when there are many units).
-template <int LPK, int NW, int UB = 4>
+// CLUSTER: the launch put the max_splits CTAs of a (token, head) into one thread-block
+// cluster (split s = rank s): partial results are exchanged through distributed shared
+// memory and merged by the cluster's first CTA instead of going through the workspace and
+// a counter.  Every CTA of the cluster then reaches the two cluster barriers, also those
+// whose split holds no visible key.
+template <int LPK, int NW, int UB = 4, bool CLUSTER = false>
 __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Shared<NW>& sh) {
     float* sh_m = sh.m;
     float* sh_l = sh.l;
@@ -103,8 +148,19 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
         if (threadIdx.x == 0 && s == 0) prb_set_status(a.status, PRB_S_POSITION_RANGE, t, pos, a.max_splits);
         return;
     }
-    if (s < s_first || s > s_last) return;
     const int n_splits = s_last - s_first + 1;
+    if (s < s_first || s > s_last) {
+        if constexpr (CLUSTER) {
+            if (n_splits > 1) {
+                cluster_sync_all();                  // the partial results are in place
+                if (s == 0) {                        // (a window has moved past split 0)
+                    merge_cluster<NW>(a, t, h, s_first, s_last, sh);
+                }
+                cluster_sync_all();                  // they have been read
+            }
+        }
+        return;
+    }
     const int k_begin = max(lo, s * a.split), k_end = min(pos + 1, (s + 1) * a.split);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -251,10 +307,20 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
 #pragma unroll
         for (int w = 0; w < NW; ++w) od += sh_o[w][d] * cw[w];
         if (n_splits == 1) o[d] = __float2bfloat16_rn(lt > 0.0f ? od / lt : 0.0f);
+        else if constexpr (CLUSTER) sh.part_o[d] = od;
         else ws[d] = od;
+    }
+    if constexpr (CLUSTER) {
+        if (threadIdx.x == 0) { sh.part_ml[0] = mt; sh.part_ml[1] = lt; }
     }
     DEC_TRACE(4);
     if (n_splits == 1) return;
+    if constexpr (CLUSTER) {
+        cluster_sync_all();                          // every split's partial result is in place
+        if (s == 0) merge_cluster<NW>(a, t, h, s_first, s_last, sh);
+        cluster_sync_all();                          // they have been read: CTAs may leave
+        return;
+    }
     if (threadIdx.x == 0) { ws[a.head_dim] = mt; ws[a.head_dim + 1] = lt; }
     __threadfence();
     __syncthreads();
