@@ -162,6 +162,7 @@ inline Plan make_plan(int mt, bool ln, int n, int k) {
 }
 inline Plan finish_plan(Plan p) {
     p.geo.early = g_tune[4] > 0 && g_tune[4] < p.geo.stages ? g_tune[4] : p.geo.stages;
+    if (g_tune[4] < 0) p.geo.early = 0;
     return p;
 }
 
@@ -259,32 +260,45 @@ __device__ __forceinline__ void norm_rows_staged(const Args& a, __nv_bfloat16* x
                 v[i] = idx < nvec ? src[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-        float s = 0.0f;
-#pragma unroll
-        for (int i = 0; i < LN_MAX_K / 128; ++i)
-            if (i < iters) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-        const float mean = prb_warp_sum(s) / (float)k;
-        float sq = 0.0f;
+        // One pass for both statistics, on data shifted by the row's first element so that
+        // the difference of squares does not cancel; one round of shuffles for both sums.
+        const float pivot = __shfl_sync(0xffffffffu, v[0].x, 0);
+        float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
         for (int i = 0; i < LN_MAX_K / 128; ++i) {
             if (i < iters && lane + 32 * i < nvec) {
-                const float c0 = v[i].x - mean, c1 = v[i].y - mean, c2 = v[i].z - mean,
-                            c3 = v[i].w - mean;
-                sq += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+                const float c0 = v[i].x - pivot, c1 = v[i].y - pivot, c2 = v[i].z - pivot,
+                            c3 = v[i].w - pivot;
+                s1 += (c0 + c1) + (c2 + c3);
+                s2 += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
             }
         }
-        const float inv = 1.0f / sqrtf(prb_warp_sum(sq) / (float)k + a.eps);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+            s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+        }
+        const float dm = s1 / (float)k;                        // mean - pivot
+        const float var = fmaxf(s2 / (float)k - dm * dm, 0.0f);
+        const float inv = rsqrtf(var + a.eps);
+        const float shift = -(pivot + dm) * inv;               // y = (x * inv + shift) * gamma + beta
+        const uint32_t gaddr = (uint32_t)__cvta_generic_to_shared(gb);
 #pragma unroll
         for (int i = 0; i < LN_MAX_K / 128; ++i) {
             const int idx = lane + 32 * i;
             if (i < iters && idx < nvec) {
-                const float4 gm = reinterpret_cast<const float4*>(gb)[idx];
-                float4 bt = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (a.beta) bt = reinterpret_cast<const float4*>(gb + k)[idx];
+                float4 gm, bt = make_float4(0.f, 0.f, 0.f, 0.f);
+                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                             : "=f"(gm.x), "=f"(gm.y), "=f"(gm.z), "=f"(gm.w)
+                             : "r"(gaddr + idx * 16));
+                if (a.beta)
+                    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                 : "=f"(bt.x), "=f"(bt.y), "=f"(bt.z), "=f"(bt.w)
+                                 : "r"(gaddr + (k + idx * 4) * 4));
                 const __nv_bfloat162 lo = __floats2bfloat162_rn(
-                    (v[i].x - mean) * inv * gm.x + bt.x, (v[i].y - mean) * inv * gm.y + bt.y);
+                    fmaf(fmaf(v[i].x, inv, shift), gm.x, bt.x), fmaf(fmaf(v[i].y, inv, shift), gm.y, bt.y));
                 const __nv_bfloat162 hi = __floats2bfloat162_rn(
-                    (v[i].z - mean) * inv * gm.z + bt.z, (v[i].w - mean) * inv * gm.w + bt.w);
+                    fmaf(fmaf(v[i].z, inv, shift), gm.z, bt.z), fmaf(fmaf(v[i].w, inv, shift), gm.w, bt.w));
                 uint2 pk;
                 pk.x = *reinterpret_cast<const uint32_t*>(&lo);
                 pk.y = *reinterpret_cast<const uint32_t*>(&hi);
