@@ -66,6 +66,51 @@ def library_path() -> str:
     return _build.build()
 
 
+_PROGRAM_LIB = None
+
+
+def program_lib() -> ctypes.CDLL:
+    """The library of the whole-step decode program; built and loaded when first asked for."""
+    global _PROGRAM_LIB
+    if _PROGRAM_LIB is None:
+        lib()                                   # the core comes first (and its objects are linked in)
+        try:
+            handle = ctypes.CDLL(_build.build(which="program"))
+        except (OSError, _build.BuildError) as exc:
+            raise ExtensionError(
+                f"the decode-program library of pretrained_rstr_b200 is not available: {exc}") from exc
+        _declare_program(handle)
+        handle.prb_set_pdl(1 if _PDL else 0)
+        _PROGRAM_LIB = handle
+    return _PROGRAM_LIB
+
+
+def _declare_program(h: ctypes.CDLL) -> None:
+    P, I, L, F = c_void_p, c_int, c_long, c_float
+    h.prb_program_new.argtypes = [I]
+    h.prb_program_new.restype = P
+    h.prb_program_free.argtypes = [P]
+    h.prb_program_free.restype = None
+    h.prb_program_length.argtypes = [P]
+    h.prb_program_bytes.argtypes = [P]
+    h.prb_program_bytes.restype = L
+    h.prb_program_add_embed.argtypes = [P, P, P, P, P, P, I, I, I, I, I, P]
+    h.prb_program_add_norm.argtypes = [P, P, P, P, P, P, I, I, I, F, I, P]
+    h.prb_program_add_gemm.argtypes = [P, P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
+                                       P, P, P, I, I, I, I, I, P]
+    h.prb_program_add_append.argtypes = [P, P, P, P, P, L, P, I, I, I, I, I, I, P]
+    h.prb_program_add_attention.argtypes = [P, P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I,
+                                            I, F, I, P, P, I, I, P]
+    h.prb_program_upload.argtypes = [P, P, P]
+    h.prb_program_run.argtypes = [P, P, P, P, P]
+    h.prb_set_pdl.argtypes = [I]
+    h.prb_set_pdl.restype = None
+    for name in ("prb_program_length", "prb_program_add_embed", "prb_program_add_norm",
+                 "prb_program_add_gemm", "prb_program_add_append", "prb_program_add_attention",
+                 "prb_program_upload", "prb_program_run"):
+        getattr(h, name).restype = c_int
+
+
 def require_cuda() -> None:
     if not torch.cuda.is_available():
         raise ExtensionError("pretrained_rstr_b200 runs on a CUDA device only (sm_100a); "
@@ -101,22 +146,6 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_attention_prefill_tc_supports.argtypes = [I, I]
     h.prb_attention_prefill_tc_tile.argtypes = []
     h.prb_attention_decode_split.argtypes = []
-    h.prb_program_new.argtypes = [I]
-    h.prb_program_new.restype = P
-    h.prb_program_free.argtypes = [P]
-    h.prb_program_free.restype = None
-    h.prb_program_length.argtypes = [P]
-    h.prb_program_bytes.argtypes = [P]
-    h.prb_program_bytes.restype = L
-    h.prb_program_add_embed.argtypes = [P, P, P, P, P, P, I, I, I, I, I, P]
-    h.prb_program_add_norm.argtypes = [P, P, P, P, P, P, I, I, I, F, I, P]
-    h.prb_program_add_gemm.argtypes = [P, P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
-                                       P, P, P, I, I, I, I, I, P]
-    h.prb_program_add_append.argtypes = [P, P, P, P, P, L, P, I, I, I, I, I, I, P]
-    h.prb_program_add_attention.argtypes = [P, P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I,
-                                            I, F, I, P, P, I, I, P]
-    h.prb_program_upload.argtypes = [P, P, P]
-    h.prb_program_run.argtypes = [P, P, P, P, P]
     h.prb_set_pdl.argtypes = [I]
     h.prb_set_pdl.restype = None
     h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
@@ -127,9 +156,7 @@ def _declare(h: ctypes.CDLL) -> None:
                  "prb_attention_prefill", "prb_attention_prefill_supports",
                  "prb_attention_prefill_tile", "prb_attention_prefill_tc",
                  "prb_attention_prefill_tc_supports", "prb_attention_prefill_tc_tile",
-                 "prb_attention_decode_split", "prb_program_length", "prb_program_add_embed",
-                 "prb_program_add_norm", "prb_program_add_gemm", "prb_program_add_append",
-                 "prb_program_add_attention", "prb_program_upload", "prb_program_run", "prb_sample", "prb_sample_max_top_k"):
+                 "prb_attention_decode_split", "prb_sample", "prb_sample_max_top_k"):
         getattr(h, name).restype = c_int
 
 
@@ -199,7 +226,7 @@ class Program:
     :class:`NotRecordable`."""
 
     def __init__(self, max_rows: int, device):
-        self.handle = lib().prb_program_new(int(max_rows))
+        self.handle = program_lib().prb_program_new(int(max_rows))
         self.device = device
         self.ops = None                    # device copy of the operation list
         self.barrier = torch.zeros(2, dtype=torch.int32, device=device)
@@ -218,19 +245,19 @@ class Program:
         return False
 
     def finish(self) -> None:
-        self.length = lib().prb_program_length(self.handle)
-        nbytes = lib().prb_program_bytes(self.handle)
+        self.length = program_lib().prb_program_length(self.handle)
+        nbytes = program_lib().prb_program_bytes(self.handle)
         self.ops = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=self.device)
-        _check(lib().prb_program_upload(self.handle, _p(self.ops), _stream()), "program upload")
+        _check(program_lib().prb_program_upload(self.handle, _p(self.ops), _stream()), "program upload")
 
     def run(self, status) -> None:
-        _check(lib().prb_program_run(self.handle, _p(self.ops), _p(self.barrier), _p(status),
+        _check(program_lib().prb_program_run(self.handle, _p(self.ops), _p(self.barrier), _p(status),
                                      _stream()), "program run")
 
     def __del__(self):
         try:
             if self.handle:
-                lib().prb_program_free(self.handle)
+                program_lib().prb_program_free(self.handle)
                 self.handle = None
         except Exception:
             pass
@@ -241,9 +268,16 @@ def _no_record(what: str) -> None:
         raise NotRecordable(what)
 
 
+_PDL = True
+
+
 def set_pdl(on: bool) -> None:
     """Switch programmatic dependent launch of the decode-chain kernels on or off."""
+    global _PDL
+    _PDL = bool(on)
     lib().prb_set_pdl(1 if on else 0)
+    if _PROGRAM_LIB is not None:
+        _PROGRAM_LIB.prb_set_pdl(1 if on else 0)
 
 
 # ------------------------------------------------------------------------ kernels
@@ -260,7 +294,7 @@ def embed(out, tokens, positions, wte, wpe, status) -> None:
     if tokens.numel() < n or positions.numel() < n:
         raise KernelArgumentError(f"{what}: fewer token ids or positions than output rows")
     if _RECORDER is not None:
-        _check(lib().prb_program_add_embed(_RECORDER.handle, _p(out), _p(tokens), _p(positions),
+        _check(program_lib().prb_program_add_embed(_RECORDER.handle, _p(out), _p(tokens), _p(positions),
                                            _p(wte), _p(wpe), n, width, wte.shape[0],
                                            0 if wpe is None else wpe.shape[0],
                                            dtype_code(wte.dtype), _p(status)), what)
@@ -286,7 +320,7 @@ def layernorm(out, x, gamma, beta, eps: float, rows=None, status=None) -> None:
     if rows is not None:
         _need(rows, torch.int32, "rows", what)
     if _RECORDER is not None:
-        _check(lib().prb_program_add_norm(_RECORDER.handle, _p(out), _p(x), _p(gamma), _p(beta),
+        _check(program_lib().prb_program_add_norm(_RECORDER.handle, _p(out), _p(x), _p(gamma), _p(beta),
                                           _p(rows), n_rows, x.shape[0], width, float(eps),
                                           dtype_code(out.dtype), _p(status)), what)
         return
@@ -327,7 +361,7 @@ def kv_append(k_pages, v_pages, k_src, v_src, slots, n_tokens, status) -> None:
     if k_src.stride(0) != v_src.stride(0):
         raise KernelArgumentError(f"{what}: k_src and v_src row strides differ")
     if _RECORDER is not None:
-        _check(lib().prb_program_add_append(_RECORDER.handle, _p(k_pages), _p(v_pages), _p(k_src),
+        _check(program_lib().prb_program_add_append(_RECORDER.handle, _p(k_pages), _p(v_pages), _p(k_src),
                                             _p(v_src), k_src.stride(0), _p(slots), n_tokens,
                                             kv_heads, head_dim, page_size, num_pages,
                                             dtype_code(k_pages.dtype), _p(status)), what)
@@ -464,7 +498,7 @@ def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0,
         kv = (_p(k_pages), _p(v_pages), _p(slots), q_width, kv_heads * head_dim, head_dim,
               page_size, num_pages)
     if _RECORDER is not None:
-        _check(lib().prb_program_add_gemm(
+        _check(program_lib().prb_program_add_gemm(
             _RECORDER.handle, _p(out), None if norm_input is not None else _p(x),
             _p(x) if norm_input is not None else None, _p(gamma), _p(beta), float(eps), _p(w),
             _p(bias), _p(resid), m, n, k, x.stride(0), w.stride(0), out.stride(0), ACT_CODES[act],
@@ -526,7 +560,7 @@ def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positi
             counters.dtype != torch.int32 or counters.numel() < n_list * n_heads:
         raise KernelArgumentError(f"{what}: scratch too small or of the wrong type")
     if _RECORDER is not None:
-        _check(lib().prb_program_add_attention(
+        _check(program_lib().prb_program_add_attention(
             _RECORDER.handle, _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages),
             _p(v_pages), _p(block_table), _p(seq_of_token), _p(positions), _p(token_list),
             _p(token_count), n_list, n_heads, kv_heads, head_dim, page_size, block_table.shape[1],
