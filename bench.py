@@ -122,9 +122,9 @@ def run_reference(args) -> int:
     print(json.dumps({
         "impl": "reference",
         "unavailable": "replikativ/pretrained-rstr is Clojure on the JVM computing through the "
-                       "external Raster library; pip reports \"Directory '/root/reference' is not "
-                       "installable. Neither 'setup.py' nor 'pyproject.toml' found\", and no JVM, "
-                       "Clojure or Raster exists offline"}))
+                       "external Raster library; pip reports that its folder is not installable "
+                       "(neither setup.py nor pyproject.toml found), and no JVM, Clojure or Raster "
+                       "exists offline"}))
     return 0
 
 
