@@ -129,6 +129,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_gemm_bf16.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, I, P, P]
     h.prb_gemm_bf16_scatter.argtypes = [P, P, P, P, I, I, I, L, L, L, I, I, P, P, P, I, I, I, I, I,
                                         P, P]
+    h.prb_gemm_midm.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, P, P]
+    h.prb_gemm_midm_supports.argtypes = [I, I, I]
     h.prb_gemm_smallm.argtypes = [P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
                                   P, P, P, I, I, I, I, I, P, P]
     h.prb_gemm_smallm_max_rows.argtypes = []
@@ -151,7 +153,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
     h.prb_sample_max_top_k.argtypes = []
     for name in ("prb_resolve_tokens", "prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
-                 "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_bf16_scatter", "prb_gemm_smallm", "prb_gemm_smallm_max_rows",
+                 "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_bf16_scatter", "prb_gemm_midm",
+                 "prb_gemm_midm_supports", "prb_gemm_smallm", "prb_gemm_smallm_max_rows",
                  "prb_gemm_smallm_max_norm_width", "prb_attention_generic", "prb_attention_decode",
                  "prb_attention_prefill", "prb_attention_prefill_supports",
                  "prb_attention_prefill_tile", "prb_attention_prefill_tc",
@@ -445,6 +448,33 @@ def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, statu
     _check(lib().prb_gemm_bf16(_p(out), _p(a), _p(w), _p(bias), _p(resid), m, n, k, a.stride(0),
                                w.stride(0), out.stride(0), ACT_CODES[act], dtype_code(out.dtype),
                                tile_n, _p(status), _stream()), what)
+
+
+def midm_supports(m: int, n: int, k: int) -> bool:
+    return bool(lib().prb_gemm_midm_supports(int(m), int(n), int(k)))
+
+
+def gemm_midm(out, a, w, bias=None, resid=None, act=None, status=None) -> None:
+    """out[M,N] = act(a[M,K] . w[N,K]^T + bias) (+ resid) for up to 64 rows, K a multiple of
+    64: the reduction is split over a thread-block cluster (``csrc/gemm_bf16_midm.cu``)."""
+    what = "gemm_midm"
+    _no_record(what)
+    for name, t in (("a", a), ("w", w)):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(1) != 1:
+            raise KernelArgumentError(f"{what}: {name} must be bfloat16 on CUDA with unit inner stride")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape[0] != m or out.shape[1] != n or out.stride(1) != 1:
+        raise KernelArgumentError(f"{what}: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, torch.float32, "bias", what)
+    if resid is not None:
+        _need(resid, torch.float32, "resid", what)
+        if resid.shape != out.shape or resid.stride(0) != out.stride(0):
+            raise KernelArgumentError(f"{what}: resid must have the output's shape and stride")
+    _check(lib().prb_gemm_midm(_p(out), _p(a), _p(w), _p(bias), _p(resid), m, n, k, a.stride(0),
+                               w.stride(0), out.stride(0), ACT_CODES[act], dtype_code(out.dtype),
+                               _p(status), _stream()), what)
 
 
 _SMALLM = None

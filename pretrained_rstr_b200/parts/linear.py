@@ -55,11 +55,18 @@ class Linear:
         if self.runtime.dtype == torch.float32:
             ops.gemm_f32(out, _tensor(a), self.weight, self.bias, resid, act)
             return False
-        # Which kernel (measured on GPT-2-small shapes, see profiles/): up to 16 rows the
-        # weight-streaming kernel with the norm fused into it; up to 64 rows the same kernel
-        # without the fused norm (every CTA would repeat it) for narrow outputs, the
-        # tensor-memory kernel for wide ones; beyond 64 rows the tensor-memory kernel.
+        # Which kernel (measured on GPT-2 small and XL shapes, see profiles/): up to 16 rows
+        # the weight-streaming kernel with the norm fused into it; 17 to 64 rows the cluster
+        # split-K kernel for narrow outputs and long reductions, the tensor-memory kernel for
+        # wide outputs (the register-streaming kernel where K is no multiple of 64); beyond
+        # 64 rows the tensor-memory kernel.
         max_rows, max_norm = ops.smallm_limits()
+        if 16 < m <= 64 and (self.n_out <= 1024 or self.n_in >= 4 * self.n_out) and \
+                ops.midm_supports(m, self.n_out, self.n_in):
+            # narrow outputs or long reductions at a few dozen rows: the reduction split over
+            # a thread-block cluster (measured against the other two kernels)
+            ops.gemm_midm(out, _tensor(a), self.weight, self.bias, resid, act, status=ctx.status)
+            return False
         if m <= max_rows and self.n_in % 8 == 0 and (m <= 16 or self.n_out <= 1024):
             if kv_scatter is not None and kv_scatter[0].dtype != out.dtype:
                 kv_scatter = None

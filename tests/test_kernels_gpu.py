@@ -464,3 +464,41 @@ def test_gemm_bf16_scatters_keys_and_values_to_the_cache(m, heads, kv_heads, dh,
     assert torch.equal(out1, out2) and torch.equal(k1, k2) and torch.equal(v1, v2)
     assert status.tolist() == [0, 0, 0, 0]
     assert int((k1 != 0).any(dim=-1).sum()) == (m - 1) * kv_heads
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 768, 768), (17, 768, 3072), (40, 1600, 6400), (33, 4800, 1600),
+                                   (64, 100, 64), (20, 50257, 128), (1, 40, 192), (64, 2304, 768)])
+@pytest.mark.parametrize("variant", ["plain_f32", "bias_gelu_bf16", "bias_resid_f32"])
+def test_gemm_midm(m, n, k, variant):
+    """The cluster split-K product for up to 64 rows against float32 arithmetic, and a row's
+    bits do not depend on the other rows."""
+    ops = _ops()
+    assert ops.midm_supports(m, n, k)
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = (torch.randn(m, k, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda", generator=g) * 0.2
+    resid = torch.randn(m, n, device="cuda", generator=g)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ref = a.float() @ w.float().t()
+    if variant == "plain_f32":
+        out = torch.full((m, n), float("nan"), device="cuda")
+        ops.gemm_midm(out, a, w, status=status)
+        tol = 3e-4
+        one = torch.zeros(1, n, device="cuda")
+        ops.gemm_midm(one, a[m // 2:m // 2 + 1].contiguous(), w, status=status)
+        assert torch.equal(one[0], out[m // 2])
+    elif variant == "bias_gelu_bf16":
+        out = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+        ops.gemm_midm(out, a, w, bias=bias, act="gelu_new", status=status)
+        ref = _act("gelu_new", ref + bias)
+        tol = 2e-2
+    else:
+        out = resid.clone()
+        ops.gemm_midm(out, a, w, bias=bias, resid=out, status=status)
+        ref = ref + bias + resid
+        tol = 3e-4
+    assert status.tolist() == [0, 0, 0, 0]
+    scale = float(ref.abs().max())
+    err = float((out.float() - ref).abs().max())
+    assert err <= tol * max(1.0, scale), f"max |difference| {err:.3e} (scale {scale:.3g})"
