@@ -18,6 +18,24 @@
 #include "common.cuh"
 #include "tensor_map.cuh"
 
+#ifdef PRB_TRACE
+__device__ unsigned long long g_midm_trace[512 * 8];
+#define MT_TRACE(slot)                                                                \
+    do {                                                                              \
+        const int cta__ = blockIdx.z * gridDim.x + blockIdx.x;                        \
+        if (threadIdx.x == 0 && cta__ < 512) {                                        \
+            unsigned long long t__;                                                   \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                   \
+            g_midm_trace[cta__ * 8 + (slot)] = t__;                                   \
+        }                                                                             \
+    } while (0)
+PRB_API int prb_gemm_midm_trace(unsigned long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, g_midm_trace, sizeof(unsigned long long) * n);
+}
+#else
+#define MT_TRACE(slot)
+#endif
+
 namespace {
 constexpr int THREADS = 256;
 constexpr int WARPS = 8;
@@ -134,6 +152,7 @@ gemm_midm_kernel(Args a, const __grid_constant__ CUtensorMap map_a,
     const int slab_lo = (int)((long)slabs * rank / S), slab_hi = (int)((long)slabs * (rank + 1) / S);
     const int items = (slab_hi - slab_lo + KC - 1) / KC;
 
+    MT_TRACE(0);
     prb_grid_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -180,6 +199,8 @@ gemm_midm_kernel(Args a, const __grid_constant__ CUtensorMap map_a,
             }
         }
         if (alive) alive = mbar_wait(full0 + 8 * st, (uint32_t)(i / STAGES) & 1u, failed);
+        if (i == 0) MT_TRACE(1);
+        if (i == items - 1) MT_TRACE(2);
         if (alive) {
             const uint32_t abase = ring + st * STAGE_BYTES, wbase = abase + A_BYTES;
             // slabs of this stage that lie inside this CTA's part of K (a copy may have run
@@ -207,6 +228,7 @@ gemm_midm_kernel(Args a, const __grid_constant__ CUtensorMap map_a,
             }
         }
     }
+    MT_TRACE(3);
     // ---- this CTA's partial tile -> shared memory
     {
         const int g = lane >> 2, q = lane & 3;
@@ -233,7 +255,9 @@ gemm_midm_kernel(Args a, const __grid_constant__ CUtensorMap map_a,
     } else if (threadIdx.x == 0) {
         part[MROWS * PP] = 0.0f;
     }
+    MT_TRACE(4);
     cluster_sync_all();                                   // every CTA's partial tile is in place
+    MT_TRACE(5);
     // ---- rows rank, rank + S, ...: sum over the cluster in rank order, epilogue, store
     bool any_bad = false;
     for (int r = 0; r < S; ++r) any_bad |= ld_cluster_f32(smem_u32(part + MROWS * PP), r) != 0.0f;
@@ -245,8 +269,12 @@ gemm_midm_kernel(Args a, const __grid_constant__ CUtensorMap map_a,
         const float bias = (a.bias && gcol < a.n) ? a.bias[gcol] : 0.0f;
         for (int row = rank + rsub * S; row < a.m && row < MROWS; row += RPP * S) {
             const uint32_t addr = smem_u32(part + (size_t)row * PP + col);
+            float pv[8];                                  // all requested before any is used
+#pragma unroll
+            for (int r = 0; r < 8; ++r) pv[r] = r < S ? ld_cluster_f32(addr, r) : 0.0f;
             float v = 0.0f;
-            for (int r = 0; r < S; ++r) v += ld_cluster_f32(addr, r);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) v += pv[r];
             if (gcol < a.n) {
                 v = prb_activate(v + bias, a.act);
                 if (a.resid) v += a.resid[(size_t)row * a.ldc + gcol];
@@ -254,7 +282,9 @@ gemm_midm_kernel(Args a, const __grid_constant__ CUtensorMap map_a,
             }
         }
     }
+    MT_TRACE(6);
     cluster_sync_all();                                   // the partial tiles have been read
+    MT_TRACE(7);
 }
 
 template <int NB, typename O>
@@ -305,15 +335,24 @@ PRB_API int prb_gemm_midm(void* c, const void* a, const void* w, const float* bi
     if (lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)a) % 16 != 0 || ((uintptr_t)w) % 16 != 0)
         return PRB_E_ALIGN;
     if (out_dtype != PRB_F32 && out_dtype != PRB_BF16) return PRB_E_DTYPE;
-    // Tile width and cluster size from N and K only: wide tiles when there are many, and as
-    // many CTAs over K as it takes to reach about two per SM (at most 8, at least 2 slabs each)
+    // Tile width and cluster size from N and K only.  All CTAs should run at once (one per
+    // SM with 64-column tiles, two with 32-column tiles); within that, the split that gives
+    // an SM the fewest bytes to take in (its CTAs' slices of A and W) wins.
     const int slabs = k / 64;
-    const int nb = (n + 63) / 64 >= 74 ? 64 : 32;
-    const int tiles = (n + nb - 1) / nb;
-    int splits = (296 + tiles - 1) / tiles;
-    if (splits > 8) splits = 8;
-    if (splits > slabs / 2) splits = slabs / 2;
-    if (splits < 1) splits = 1;
+    int nb = 32, splits = 1;
+    long best = -1;
+    for (int cand = 64; cand >= 32; cand /= 2) {
+        const int tiles = (n + cand - 1) / cand;
+        const int slots = 148 * (cand == 64 ? 1 : 2);
+        int s = slots / tiles;
+        if (s > 8) s = 8;
+        if (s > slabs / 2) s = slabs / 2;
+        if (s < 1) s = 1;
+        const long per_cta = (long)(MROWS + cand) * 2 * ((long)k / s);
+        const long ctas = (long)tiles * s;
+        const long per_sm = per_cta * ((ctas + 147) / 148);
+        if (best < 0 || per_sm < best) { best = per_sm; nb = cand; splits = s; }
+    }
     CUtensorMap ma, mw;
     int rc = tmap::slab_map(a, m, k, lda, MROWS, KC, &ma);
     if (rc) return rc;

@@ -61,7 +61,7 @@ class Linear:
         # wide outputs (the register-streaming kernel where K is no multiple of 64); beyond
         # 64 rows the tensor-memory kernel.
         max_rows, max_norm = ops.smallm_limits()
-        if 16 < m <= 64 and (self.n_out <= 1024 or self.n_in >= 4 * self.n_out) and \
+        if 16 < m <= 64 and (self.n_out <= 2048 or self.n_in >= 4 * self.n_out) and \
                 ops.midm_supports(m, self.n_out, self.n_in):
             # narrow outputs or long reductions at a few dozen rows: the reduction split over
             # a thread-block cluster (measured against the other two kernels)
