@@ -207,7 +207,7 @@ def profile_gemm(shape: str) -> int:
     outf = torch.zeros(m, n, device="cuda")
     bias = torch.randn(n, device="cuda")
     res = {}
-    for tn in (0, 32, 64, 128, 256):
+    for tn in (0, 32, 64, 96, 128, 160, 192, 224, 256):
         res[f"tile{tn}"] = {
             "bf16_plain_us": timeit(lambda: ops.gemm_bf16(outb, a, w, tile_n=tn)),
             "bf16_bias_gelu_us": timeit(lambda: ops.gemm_bf16(outb, a, w, bias=bias, act="gelu_new", tile_n=tn)),

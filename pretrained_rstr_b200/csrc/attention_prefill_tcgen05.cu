@@ -124,10 +124,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     float* xmax = reinterpret_cast<float*>(bars + 32);     // [2 blocks][2 halves][QT]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    prb_grid_launch_dependents();     // the next kernel may set itself up while this one runs
 
     // the longest tiles (late query positions) first
     const int n_items = p.tile_count != nullptr ? *p.tile_count : (int)gridDim.x;
-    if ((int)blockIdx.x >= n_items) return;
+    if ((int)blockIdx.x >= n_items) {
+        prb_grid_wait();              // a kernel is complete only when those before it are
+        return;
+    }
     const int item = n_items - 1 - blockIdx.x;
     const int h = blockIdx.y;
     const int b = p.tile_req[item];
@@ -137,6 +141,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int pos_last = pos0 + rows - 1;
     if (b < 0 || rows <= 0 || rows > QT || pos0 < 0 || pos_last >= p.max_pages * p.page_size) {
         if (threadIdx.x == 0) prb_set_status(p.status, PRB_S_POSITION_RANGE, row0, pos0, rows);
+        prb_grid_wait();
         return;
     }
     const int hk = h / (p.n_heads / p.kv_heads);
@@ -170,6 +175,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set up; the queries, keys and values below were written by the kernels before
+    prb_grid_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
@@ -461,7 +468,8 @@ PRB_API int prb_attention_prefill_tc(void* out, long out_stride, const void* q, 
     p.max_pages = max_pages; p.num_pages = num_pages; p.scale = scale; p.window = window;
     p.status = status;
     dim3 grid(n_tiles, n_heads);
-    attention_prefill_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
-    PRB_LAUNCH_CHECK();
+    cudaError_t le = prb_launch_dependent(attention_prefill_tc_kernel, grid, dim3(THREADS),
+                                          SMEM_BYTES, stream, map_q, map_k, map_v, p);
+    if (le != cudaSuccess) return (int)le;
     return 0;
 }

@@ -48,6 +48,8 @@ __global__ void __launch_bounds__(128)
 layernorm_warp_kernel(elementwise::NormArgs a) {
     const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    prb_grid_launch_dependents();
+    prb_grid_wait();
     if (r >= a.n_rows) return;
     O* out = reinterpret_cast<O*>(a.out) + (size_t)r * a.width;
     const int src = a.rows ? a.rows[r] : r;
@@ -111,13 +113,17 @@ PRB_API int prb_layernorm(void* out, const float* x, const float* gamma, const f
                          ((uintptr_t)gamma) % 16 == 0 && (!beta || ((uintptr_t)beta) % 16 == 0);
     if (width % 4 == 0 && width <= 1024 && aligned && n_rows >= 16) {
         const int blocks = (n_rows + 3) / 4;
-        if (out_dtype == PRB_F32) layernorm_warp_kernel<float><<<blocks, 128, 0, stream>>>(a);
-        else layernorm_warp_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(a);
-        PRB_LAUNCH_CHECK();
+        cudaError_t e = out_dtype == PRB_F32
+            ? prb_launch_dependent(layernorm_warp_kernel<float>, dim3(blocks), dim3(128), 0, stream, a)
+            : prb_launch_dependent(layernorm_warp_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0,
+                                   stream, a);
+        if (e != cudaSuccess) return (int)e;
         return 0;
     }
     const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
     const size_t smem = (size_t)width * sizeof(float);
+    // (few rows: the norm of the wanted rows before the head; launched the plain way, which
+    // keeps the head's product from starting its copies while the last layer still runs)
     if (out_dtype == PRB_F32) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(layernorm_kernel<float>,

@@ -58,11 +58,15 @@ constexpr int GEMM_THREADS = 320;     // producer warp, MMA warp, 8 epilogue war
 using namespace tc5;
 
 template <int BN> struct TileCfg {
+    static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile width: a multiple of 32 up to 256");
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (160 * 1024) / STAGE_BYTES > 8 ? 8 : (160 * 1024) / STAGE_BYTES;
-    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators
+    static constexpr int STAGES = (176 * 1024) / STAGE_BYTES > 8 ? 8 : (176 * 1024) / STAGE_BYTES;
+    // two accumulators, each at a power-of-two column offset (tensor memory is allocated in
+    // powers of two)
+    static constexpr int ACC_STRIDE = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
+    static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
     // per epilogue warp a 32 x 33 word staging tile (rows of the accumulator are turned into
     // rows of the output so that global accesses are whole lines)
     static constexpr int STG_WORDS = 32 * 33;
@@ -138,6 +142,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (warp == 0) GT(0);
+    prb_grid_launch_dependents();     // the next kernel may set itself up while this one runs
     const int m_tiles = (m + BM - 1) / BM, n_tiles = (n + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
     const int k_blocks = (k + BK - 1) / BK;
@@ -167,6 +172,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (warp == 0) GT(1);
+    // barriers and tensor memory are set up; everything below reads what earlier kernels wrote
+    prb_grid_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
@@ -214,7 +221,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     break;
                 }
                 tcgen05_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * Cfg::ACC_STRIDE);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % Cfg::STAGES;
                     ok = mbar_wait(smem_u32(&full_bar[s]), (it / Cfg::STAGES) & 1, failed);
@@ -307,7 +314,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (n0 + c0 >= n) break;                    // uniform across the warp
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) +
-                                  (uint32_t)(acc * BN + c0), r);
+                                  (uint32_t)(acc * Cfg::ACC_STRIDE + c0), r);
                 const bool last_chunk = c0 + 64 >= BN || n0 + c0 + 64 >= n;
                 if (last_chunk) {
                     // this warp's last read of the accumulator: hand it back before the stores
@@ -436,9 +443,10 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, O* c, const float* bias
     }
     const long tiles = (long)((n + BN - 1) / BN) * ((m + BM - 1) / BM);
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    gemm_bf16_kernel<BN, O><<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(ma, mw, c, bias, resid, m,
-                                                                       n, k, ldc, act, status, sc);
-    PRB_LAUNCH_CHECK();
+    cudaError_t le = prb_launch_dependent(gemm_bf16_kernel<BN, O>, dim3(grid), dim3(GEMM_THREADS),
+                                          Cfg::SMEM, stream, ma, mw, c, bias, resid, m, n, k, ldc,
+                                          act, status, sc);
+    if (le != cudaSuccess) return (int)le;
     return 0;
 }
 
@@ -454,17 +462,25 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
         ((uintptr_t)w) % 16 != 0)
         return PRB_E_ALIGN;
     if (tile_n == 0) {
-        // fewest rounds of tiles over the SMs, weighted by tile width plus a fixed cost
+        // The CTA with the most tiles sets the time.  A tile's main loop is bound by the
+        // bytes its SM takes in (128 + width rows of 128 bytes per block of 64 along K), its
+        // epilogue by the bytes it loads and stores (measured: a 128-column float32 tile with
+        // residual costs what 11 blocks of the main loop do, a bfloat16 tile half of that);
+        // all but a CTA's last epilogue hide behind the next tile's main loop.
         const long mt = (m + BM - 1) / BM;
+        const long kb = (k + BK - 1) / BK;
+        const long per_col = out_dtype == PRB_F32 ? 23 : 12;
         long best = -1;
-        for (int bn = 256; bn >= 32; bn /= 2) {
+        for (int bn = 256; bn >= 32; bn -= 32) {
             const long tiles = mt * ((n + bn - 1) / bn);
             const long rounds = (tiles + 147) / 148;
-            const long cost = rounds * (bn + 64);
+            const long main_loop = kb * (128 + bn) + 400, epilogue = per_col * bn;
+            const long cost = (rounds - 1) * (main_loop > epilogue ? main_loop : epilogue) +
+                              main_loop + epilogue;
             if (best < 0 || cost < best) { best = cost; tile_n = bn; }
         }
     }
-    if (tile_n != 32 && tile_n != 64 && tile_n != 128 && tile_n != 256) return PRB_E_ARG;
+    if (tile_n < 32 || tile_n > 256 || tile_n % 32 != 0) return PRB_E_ARG;
     CUtensorMap ma, mw;
     int r = get_map(a, m, k, lda, BM, &ma);
     if (r) return r;
@@ -480,14 +496,18 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
     switch (tile_n) {
         case 32: return PRB_GO(32);
         case 64: return PRB_GO(64);
+        case 96: return PRB_GO(96);
         case 128: return PRB_GO(128);
+        case 160: return PRB_GO(160);
+        case 192: return PRB_GO(192);
+        case 224: return PRB_GO(224);
         default: return PRB_GO(256);
     }
 #undef PRB_GO
 }
 }  // namespace
 
-// tile_n: 0 = choose (by M and N), or one of 32, 64, 128, 256.
+// tile_n: 0 = choose (by M, N, K and the output type), or a multiple of 32 up to 256.
 PRB_API int prb_gemm_bf16(void* c, const void* a, const void* w, const float* bias,
                           const float* resid, int m, int n, int k, long lda, long ldw, long ldc,
                           int act, int out_dtype, int tile_n, int* status, cudaStream_t stream) {

@@ -146,16 +146,22 @@ class ModelRunner:
         kernel lets touch the cache.  The first step of a shape runs directly with the
         padded sizes (which also sizes all scratch memory), the second is captured."""
         lay = ctx.layout
-        if self.use_programs and ctx.n_tiles == 0 and lay.t_cap <= ops.smallm_limits()[0]:
+        has_tiles, has_singles = bool(ctx.n_tiles), bool(ctx.n_singles)
+        if self.use_programs and not has_tiles and lay.t_cap <= ops.smallm_limits()[0]:
+            counts = (ctx.n_tiles, ctx.n_singles)
             logits = self._run_program(ctx)
             if logits is not None:
                 return logits
+            ctx.n_tiles, ctx.n_singles = counts
         if not self.use_graphs or lay.t_cap > self.graph_max_tokens:
             return self.model.forward(ctx)
         rows_cap = StepContext.row_capacity(max(ctx.n_rows, 1)) if ctx.n_rows else 0
-        key = (lay.t_cap, lay.b_cap, rows_cap)
+        # a step without prompt tiles (or without single tokens) gets a graph without that
+        # attention kernel: an idle launch per layer is a tenth of a small decode step
+        key = (lay.t_cap, lay.b_cap, rows_cap, has_tiles, has_singles)
         ctx.launch_tokens, ctx.launch_rows = lay.t_cap, rows_cap
-        ctx.n_tiles = ctx.n_singles = None          # kernels read the device-side counts
+        ctx.n_tiles = None if has_tiles else 0      # None: kernels read the device-side counts
+        ctx.n_singles = None if has_singles else 0
         ctx.max_context = self.model.max_positions
         hit = self._graphs.get(key)
         if hit is not None:

@@ -64,7 +64,7 @@ def test_gemm_bf16_tcgen05(m, n, k, variant):
     assert err <= tol * max(1.0, scale), f"max |difference| {err:.3e} (scale {scale:.3g})"
 
 
-@pytest.mark.parametrize("tile_n", [32, 64, 128, 256])
+@pytest.mark.parametrize("tile_n", [32, 64, 96, 128, 160, 192, 224, 256])
 def test_gemm_bf16_every_tile_width(tile_n):
     ops = _ops()
     g = torch.Generator(device="cuda").manual_seed(tile_n)
