@@ -26,6 +26,12 @@ class Linear:
         self.bias = None if bias is None else bias.to(torch.float32).contiguous()
         self.n_out, self.n_in = self.weight.shape
         self.runtime = runtime
+        if runtime.dtype != torch.float32 and self.n_in % 8 != 0:
+            # the tensor-core kernels read rows in 16-byte pieces; said here, when the model
+            # is built, rather than by the first step
+            raise ValueError(f"a {str(runtime.dtype).replace('torch.', '')} product needs an input "
+                             f"width that is a multiple of 8; this one has {self.n_in} "
+                             f"(float32 takes any width)")
 
     @classmethod
     def from_store(cls, store, name: str, layout: str, n_in: int, n_out: int, bias: bool,

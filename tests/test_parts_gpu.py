@@ -520,3 +520,241 @@ def test_windowed_and_grouped_layers_have_pools_of_their_own(tmp_path, dtype):
     for r in prompts:
         lm.cache.close(r)
     assert all(a.free_count == a.num_pages for a in lm.cache.allocators)
+
+
+# ------------------------- a position encoding and a routed feed-forward defined in the test
+def _register_routed():
+    """A third toy architecture: no position table but a rotation of queries and keys by
+    their position (a position encoding defined here), and in the last layer a feed-forward
+    that routes every token to two of three small experts (also defined here)."""
+    from pretrained_rstr_b200.config import (Architecture, LayerSpec, ModelConfig, PartSpec,
+                                             register_architecture)
+    from pretrained_rstr_b200.models.assembly import build_model
+    from pretrained_rstr_b200.parts import FeedForward, PositionEncoding, register_part
+    from pretrained_rstr_b200.weights import TensorExpectation, normal
+
+    class ToyRotation(PositionEncoding):
+        """Pairs (i, i + half) of every head turn by position * theta^(-i / half), in 32-bit."""
+
+        def __init__(self, params, store, runtime):
+            self.head_dim, self.theta = params["head_dim"], float(params["theta"])
+
+        def rotate(self, ctx, q, k):
+            t, half = q.shape[0], self.head_dim // 2
+            pos = ctx.positions[:t].float()
+            inv = self.theta ** (-torch.arange(half, device=q.device, dtype=torch.float32) / half)
+            ang = pos[:, None, None] * inv[None, None, :]
+            cos, sin = torch.cos(ang), torch.sin(ang)
+            for x in (q, k):
+                v = x.float().view(t, -1, self.head_dim)
+                a, b = v[..., :half], v[..., half:]
+                turned = torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+                x.copy_(turned.view(t, -1).to(x.dtype))
+
+    class ToyRoutedExperts(FeedForward):
+        """x += sum over the token's top two experts of softmax weight * expert(h); router
+        logits and weights in 32-bit.  Array-library calls: toy parts need no kernels."""
+
+        def __init__(self, params, store, runtime):
+            name = params["weights"]
+            self.router = store.get(name + ".router.weight", torch.float32)
+            self.up = store.get(name + ".experts.up", torch.float32)        # [E, inner, width]
+            self.down = store.get(name + ".experts.down", torch.float32)    # [E, width, inner]
+            self.top = int(params["top"])
+
+        def forward(self, ctx, h, x):
+            hf = h.tensor().float() if hasattr(h, "tensor") else h.float()
+            logits = hf @ self.router.T
+            top, which = torch.topk(logits, self.top, dim=1)
+            weight = torch.softmax(top, dim=1)
+            for e in range(self.router.shape[0]):
+                share = (weight * (which == e)).sum(1, keepdim=True)          # 0 where not routed
+                x += share * (torch.relu(hf @ self.up[e].T) @ self.down[e].T)
+
+    register_part("position", "toy_rotation", ToyRotation)
+    register_part("feed_forward", "toy_routed_experts", ToyRoutedExperts)
+
+    @dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        width: int
+        heads: int
+        inner: int
+        experts: int
+        vocab: int
+        positions: int
+        theta: float
+        identifiers = ("RoutedToyForTests",)
+        _keys = ("width", "heads", "inner", "experts", "vocab", "positions", "theta")
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(*(raw[k] for k in cls._keys))
+
+        def to_dict(self):
+            return {"architectures": ["RoutedToyForTests"], **{k: getattr(self, k) for k in self._keys}}
+
+        def _norm(self, name):
+            return PartSpec("layer_norm", {"weights": name, "size": self.width, "eps": 1e-5})
+
+        def layer_specs(self):
+            dh = self.width // self.heads
+            specs = []
+            for i in range(2):
+                p = f"l{i}."
+                attn = PartSpec("causal_attention", {
+                    "weights": {"qkv": p + "qkv", "out": p + "out"}, "width": self.width,
+                    "n_head": self.heads, "n_kv_head": self.heads, "head_dim": dh,
+                    "scale": 1.0 / math.sqrt(dh), "window": None, "bias": False,
+                    "weight_layout": "out_in"})
+                if i == 0:
+                    ff = PartSpec("dense_mlp", {"weights": {"up": p + "up", "down": p + "down"},
+                                                "width": self.width, "inner": self.inner,
+                                                "activation": "relu", "bias": False,
+                                                "weight_layout": "out_in"})
+                else:
+                    ff = PartSpec("toy_routed_experts", {"weights": p + "moe", "top": 2})
+                specs.append(LayerSpec(p, "pre_norm", attn, ff, self._norm(p + "n1"),
+                                       self._norm(p + "n2")))
+            return specs
+
+        def embedding_spec(self):
+            return PartSpec("token_embedding", {"weights": "emb", "vocab": self.vocab,
+                                                "width": self.width})
+
+        def position_spec(self):
+            return PartSpec("toy_rotation", {"head_dim": self.width // self.heads,
+                                             "theta": self.theta})
+
+        def final_norm_spec(self):
+            return self._norm("nf")
+
+        def head_spec(self):
+            return PartSpec("tied_head", {"weights": "emb", "vocab": self.vocab, "width": self.width})
+
+        @property
+        def max_positions(self):
+            return self.positions
+
+    def expected(cfg):
+        d, f, n = cfg.width, cfg.inner, cfg.experts
+        e = {"emb.weight": (cfg.vocab, d), "nf.weight": (d,), "nf.bias": (d,),
+             "l0.up.weight": (f, d), "l0.down.weight": (d, f),
+             "l1.moe.router.weight": (n, d), "l1.moe.experts.up": (n, f, d),
+             "l1.moe.experts.down": (n, d, f)}
+        for l in ("l0.", "l1."):
+            e.update({l + "qkv.weight": (3 * d, d), l + "out.weight": (d, d),
+                      l + "n1.weight": (d,), l + "n1.bias": (d,),
+                      l + "n2.weight": (d,), l + "n2.bias": (d,)})
+        return {k: TensorExpectation(v) for k, v in e.items()}
+
+    def random_tensors(cfg, seed):
+        out = {}
+        for name, exp in expected(cfg).items():
+            gain = name.split(".")[-2] in ("n1", "n2", "nf") and name.endswith("weight")
+            std = 0.5 if "router" in name else 0.15 if "qkv" in name else 0.05
+            out[name] = normal(seed, name, exp.shape, std, mean=1.0 if gain else 0.0)
+        return out
+
+    register_architecture(RoutedConfig.identifiers, Architecture(
+        "routed-toy", RoutedConfig, lambda cfg, store, rt: build_model(cfg, store, rt),
+        expected, random_tensors))
+    return RoutedConfig
+
+
+def _routed_plain(w, cfg, ids):
+    """The routed toy model, whole sequence, plain.  Also returns, per position, how far the
+    router's second choice is ahead of its third."""
+    d, nh, dh = cfg.width, cfg.heads, cfg.width // cfg.heads
+    half, t = dh // 2, len(ids)
+    ln = lambda x, n: plain_gpt2.layer_norm(x, w[n + ".weight"], w[n + ".bias"], 1e-5)
+    inv = cfg.theta ** (-torch.arange(half, dtype=torch.float32) / half)
+    ang = torch.arange(t, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang), torch.sin(ang)
+
+    def turn(m):                                   # [t, dh] of one head
+        a, b = m[:, :half], m[:, half:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=1)
+
+    mask = torch.tril(torch.ones(t, t, dtype=torch.bool))
+    x = w["emb.weight"][torch.tensor(ids)]
+    margin = None
+    for l in ("l0.", "l1."):
+        qkv = ln(x, l + "n1") @ w[l + "qkv.weight"].T
+        o = torch.zeros(t, d)
+        for h in range(nh):
+            c = slice(h * dh, (h + 1) * dh)
+            q, k, v = turn(qkv[:, c]), turn(qkv[:, d:2 * d][:, c]), qkv[:, 2 * d:][:, c]
+            sc = (q @ k.T) / math.sqrt(dh)
+            o[:, c] = torch.softmax(sc.masked_fill(~mask, -math.inf), 1) @ v
+        x = x + o @ w[l + "out.weight"].T
+        hn = ln(x, l + "n2")
+        if l == "l0.":
+            x = x + torch.relu(hn @ w["l0.up.weight"].T) @ w["l0.down.weight"].T
+        else:
+            logits = hn @ w["l1.moe.router.weight"].T
+            ranked, order = torch.sort(logits, dim=1, descending=True)
+            margin = ranked[:, 1] - ranked[:, 2]
+            weight = torch.softmax(ranked[:, :2], dim=1)
+            y = torch.zeros(t, d)
+            for pos in range(t):
+                for slot in range(2):
+                    e = int(order[pos, slot])
+                    y[pos] += weight[pos, slot] * (torch.relu(hn[pos] @ w["l1.moe.experts.up"][e].T)
+                                                   @ w["l1.moe.experts.down"][e].T)
+            x = x + y
+    return ln(x, "nf") @ w["emb.weight"].T, margin
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_position_encoding_and_routed_feed_forward_defined_in_the_test(tmp_path, dtype):
+    from pretrained_rstr_b200.engine.batch import Entry
+    from pretrained_rstr_b200.engine.loading import load_model
+    from pretrained_rstr_b200.weights import load_file, make_random_model
+    Cfg = _register_routed()
+    cfg = Cfg(width=64, heads=4, inner=40, experts=3, vocab=150, positions=200, theta=50.0)
+    folder = str(tmp_path / "routed")
+    make_random_model(folder, cfg, seed=11,
+                      dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    lm = load_model(folder, dtype=dtype, page_size=16, max_batched_tokens=256, max_requests=2,
+                    max_tokens=2 * 208)
+    assert lm.model.graph_safe is False
+    w = {k: v.float() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    prompts = {"a": random_tokens(150, 150, 3), "b": random_tokens(67, 150, 4)}
+    oracle = {r: _routed_plain(w, cfg, ids) for r, ids in prompts.items()}
+    got, at = {}, {"a": 0, "b": 0}
+    for r in prompts:
+        lm.cache.open(r)
+    cuts = {"a": [70, 1, 1, 2, 33, 1], "b": [5, 1, 40, 1, 1]}
+    k = 0
+    while any(at[r] < len(prompts[r]) for r in prompts):
+        entries = []
+        for r in prompts:
+            if at[r] < len(prompts[r]):
+                n = min(cuts[r][k % len(cuts[r])], len(prompts[r]) - at[r])
+                entries.append(Entry(r, prompts[r][at[r]:at[r] + n], list(range(n))))
+        logits = lm.runner.step(entries).cpu()
+        lm.runner.check_status()
+        row = 0
+        for e in entries:
+            for p in range(len(e.tokens)):
+                got[(e.rid, at[e.rid] + p)] = logits[row].clone()
+                row += 1
+            at[e.rid] += len(e.tokens)
+        k += 1
+    # where the router's second and third choices lie closer than rounding can move them the
+    # engine may rightly choose otherwise; the routed layer is the last, so only that
+    # position's logits would differ
+    near = 1e-4 if dtype == "float32" else 5e-2
+    # (bfloat16: the rotation defined above rounds queries and keys a second time)
+    tol, checked = ATOL[dtype] * (1.0 if dtype == "float32" else 2.0), 0
+    for (rid, p), rowv in sorted(got.items()):
+        ref, margin = oracle[rid]
+        if float(margin[p]) < near:
+            continue
+        checked += 1
+        err = float((rowv - ref[p]).abs().max())
+        assert err <= tol, f"request {rid} position {p}: {err:.3e}"
+    assert checked >= 0.8 * len(got)
+    for r in prompts:
+        lm.cache.close(r)
+    lm.cache.check()
