@@ -20,7 +20,15 @@
 //              accumulate in tensor memory over all blocks; a row's reference maximum moves
 //              only in large steps, and only then are its output values rescaled there.
 // The score MMA of block j+1 is issued before the softmax of block j is waited for, so the
-// tensor cores and the softmax warps overlap.  No TMA load uses cluster multicast.  Every
+// tensor cores and the softmax warps overlap.
+//
+// Key parts: a tile late in a long prompt walks many blocks one after the other while the
+// CTAs of early tiles have long finished.  With part_blocks > 0 a (tile, head) is taken by
+// as many CTAs (grid z) as its keys have chunks of part_blocks blocks (chunk borders at
+// absolute positions; a CTA whose z has no chunk leaves at once).  A tile with one chunk is
+// stored as before.  Otherwise every CTA writes its maximum, sum and output rows (float32)
+// to a workspace and counts itself in; the one that finds itself last merges all parts in
+// chunk order and stores the rows, so the result does not depend on who came last.  No TMA load uses cluster multicast.  Every
 // mbarrier wait is bounded: on a timeout the kernel records PRB_S_WAIT_TIMEOUT, stores
 // nothing more, waits (bounded) for its loads in flight, frees its tensor memory and
 // returns.
@@ -60,7 +68,13 @@ constexpr int TMEM_COLS = 256;      // two score buffers and the output rows, 64
 constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + 2 * P_BYTES + STAGES * STAGE_BYTES + 256 + 4 * QT * 4;
 constexpr float RESCALE_STEP = 8.0f;   // a row's reference maximum moves only by more than this (log2 units)
 
+constexpr int MAX_PARTS = 16;       // most chunks of keys one (tile, head) may have
+
 struct Params {
+    float* part_o;                  // [(tile * heads + head) * max_parts + part][DH][QT]
+    float* part_ml;                 // [...][QT][2]: maximum (log2 units) and sum of a row
+    int* part_count;                // [tile * heads + head], zero before and after
+    int part_blocks;                // blocks per chunk; 0: one CTA per (tile, head)
     __nv_bfloat16* out;
     long out_stride;
     const int* block_table;
@@ -121,6 +135,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     uint64_t* o_full = p_full + 1;             // O_blk ready
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* is_last = reinterpret_cast<volatile int*>(tmem_slot + 2);
     float* xmax = reinterpret_cast<float*>(bars + 32);     // [2 blocks][2 halves][QT]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -147,7 +162,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int hk = h / (p.n_heads / p.kv_heads);
     const int* table = p.block_table + (size_t)b * p.max_pages;
     const int lo_all = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
-    const int blk_first = lo_all / KB, blk_last = pos_last / KB;
+    int blk_first = lo_all / KB, blk_last = pos_last / KB;
+    int n_parts = 1;
+    if (p.part_blocks > 0) {
+        // chunk (first chunk + z) of the tile's keys
+        const int chunk0 = blk_first / p.part_blocks;
+        n_parts = blk_last / p.part_blocks - chunk0 + 1;
+        if (n_parts > (int)gridDim.z || n_parts > MAX_PARTS) {
+            if (threadIdx.x == 0 && blockIdx.z == 0)
+                prb_set_status(p.status, PRB_S_POSITION_RANGE, row0, pos_last, n_parts);
+            prb_grid_wait();
+            return;
+        }
+        if ((int)blockIdx.z >= n_parts) {
+            prb_grid_wait();
+            return;
+        }
+        const int lo = (chunk0 + (int)blockIdx.z) * p.part_blocks;
+        if (lo > blk_first) blk_first = lo;
+        if (lo + p.part_blocks - 1 < blk_last) blk_last = lo + p.part_blocks - 1;
+    }
     const int n_blocks = blk_last - blk_first + 1;
 
     if (threadIdx.x == 0) {
@@ -384,24 +418,71 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             ok = mbar_wait(smem_u32(o_full), (n_blocks - 1) & 1, failed);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         }
+        __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * p.out_stride + (size_t)h * DH + half * HD;
+        auto store_row = [&](const float (&o)[HD], float inv) {
+#pragma unroll
+            for (int c = 0; c < HD; c += 8) {
+                uint4 v;
+                v.x = pack2(o[c] * inv, o[c + 1] * inv);
+                v.y = pack2(o[c + 2] * inv, o[c + 3] * inv);
+                v.z = pack2(o[c + 4] * inv, o[c + 5] * inv);
+                v.w = pack2(o[c + 6] * inv, o[c + 7] * inv);
+                *reinterpret_cast<uint4*>(dst + c) = v;
+            }
+        };
+        float o_own[HD];
         if (ok) {
             tcgen05_fence_after();
             uint32_t ob[HD];
             tmem_ld_32x32(lane_addr + (uint32_t)(2 * KB + half * HD), ob);
-            if (row_ok) {
-                const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
-                __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * p.out_stride + (size_t)h * DH + half * HD;
-#pragma unroll
-                for (int c = 0; c < HD; c += 8) {
-                    uint4 v;
-                    v.x = pack2(__uint_as_float(ob[c]) * inv, __uint_as_float(ob[c + 1]) * inv);
-                    v.y = pack2(__uint_as_float(ob[c + 2]) * inv, __uint_as_float(ob[c + 3]) * inv);
-                    v.z = pack2(__uint_as_float(ob[c + 4]) * inv, __uint_as_float(ob[c + 5]) * inv);
-                    v.w = pack2(__uint_as_float(ob[c + 6]) * inv, __uint_as_float(ob[c + 7]) * inv);
-                    *reinterpret_cast<uint4*>(dst + c) = v;
-                }
-            }
             tcgen05_fence_before();
+#pragma unroll
+            for (int i = 0; i < HD; ++i) o_own[i] = __uint_as_float(ob[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < HD; ++i) o_own[i] = 0.0f;
+        }
+        if (n_parts == 1) {
+            if (ok && row_ok) store_row(o_own, l_all > 0.0f ? 1.0f / l_all : 0.0f);
+        } else {
+            // this CTA's part: rows as [dim][row], so that a warp's 32 rows are one line
+            const size_t unit = (size_t)item * p.n_heads + h;
+            const size_t slot = unit * gridDim.z + blockIdx.z;
+            float* po = p.part_o + slot * (size_t)(DH * QT) + (size_t)(half * HD) * QT + r;
+#pragma unroll
+            for (int i = 0; i < HD; ++i) __stcg(po + (size_t)i * QT, o_own[i]);
+            if (half == 0)
+                __stcg(reinterpret_cast<float2*>(p.part_ml + slot * (size_t)(2 * QT)) + r,
+                       make_float2(ok ? m_run : -INFINITY, ok ? l_all : 0.0f));
+            __threadfence();
+            asm volatile("bar.sync 5, 256;" ::: "memory");
+            if (warp == 2 && lane == 0) {
+                const int before = atomicAdd(p.part_count + unit, 1);
+                const int last = before == n_parts - 1 ? 1 : 0;
+                if (last) p.part_count[unit] = 0;              // left zero for the next launch
+                *is_last = last;
+            }
+            asm volatile("bar.sync 5, 256;" ::: "memory");
+            if (*is_last) {
+                __threadfence();
+                const size_t slot0 = unit * gridDim.z;
+                float ms[MAX_PARTS], m_all = -INFINITY;
+                for (int s = 0; s < n_parts; ++s) {
+                    ms[s] = __ldcg(p.part_ml + (slot0 + s) * (size_t)(2 * QT) + 2 * r);
+                    m_all = fmaxf(m_all, ms[s]);
+                }
+                float acc[HD], l_sum = 0.0f;
+#pragma unroll
+                for (int i = 0; i < HD; ++i) acc[i] = 0.0f;
+                for (int s = 0; s < n_parts; ++s) {          // in chunk order
+                    const float wgt = ms[s] == -INFINITY ? 0.0f : fast_exp2(ms[s] - m_all);
+                    l_sum = fmaf(wgt, __ldcg(p.part_ml + (slot0 + s) * (size_t)(2 * QT) + 2 * r + 1), l_sum);
+                    const float* src = p.part_o + (slot0 + s) * (size_t)(DH * QT) + (size_t)(half * HD) * QT + r;
+#pragma unroll
+                    for (int i = 0; i < HD; ++i) acc[i] = fmaf(wgt, __ldcg(src + (size_t)i * QT), acc[i]);
+                }
+                if (row_ok) store_row(acc, l_sum > 0.0f ? 1.0f / l_sum : 0.0f);
+            }
         }
         if (!ok && lane == 0) prb_set_status(p.status, PRB_S_WAIT_TIMEOUT, 13, blockIdx.x, warp);
     }
@@ -424,7 +505,10 @@ PRB_API int prb_attention_prefill_tc_supports(int head_dim, int page_size) {
     return head_dim == DH && page_size > 0 && page_size % KB == 0 ? 1 : 0;
 }
 
-// Work list as prb_attention_prefill, with tiles of up to 128 rows.  q: bfloat16 rows of
+// Work list as prb_attention_prefill, with tiles of up to 128 rows.  part_blocks > 0: the
+// keys of a tile in chunks of part_blocks * 64 positions, a CTA each, at most max_parts (up
+// to 16) per tile; part_o: float32 [n_tiles * n_heads * max_parts * 64 * 128], part_ml:
+// float32 [n_tiles * n_heads * max_parts * 256], part_count: int32 [n_tiles * n_heads], zero.  q: bfloat16 rows of
 // q_stride elements, q_rows of them (head h at columns [h*64, h*64+64)); out likewise.
 PRB_API int prb_attention_prefill_tc(void* out, long out_stride, const void* q, long q_stride,
                                      int q_rows, const void* k_pages, const void* v_pages,
@@ -433,8 +517,14 @@ PRB_API int prb_attention_prefill_tc(void* out, long out_stride, const void* q, 
                                      const int* tile_rows, const int* tile_count, int n_tiles,
                                      int n_heads, int kv_heads, int head_dim, int page_size,
                                      int max_pages, int num_pages, float scale, int window,
-                                     int* status, cudaStream_t stream) {
+                                     int part_blocks, int max_parts, float* part_o,
+                                     float* part_ml, int* part_count, int* status,
+                                     cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
+    if (part_blocks < 0 || (part_blocks > 0 && (max_parts < 1 || max_parts > MAX_PARTS ||
+                                                part_o == nullptr || part_ml == nullptr ||
+                                                part_count == nullptr)))
+        return PRB_E_ARG;
     if (!prb_attention_prefill_tc_supports(head_dim, page_size) || n_heads <= 0 || kv_heads <= 0 ||
         n_heads % kv_heads != 0 || n_heads > 65535 || q_rows <= 0)
         return PRB_E_SIZE;
@@ -460,6 +550,7 @@ PRB_API int prb_attention_prefill_tc(void* out, long out_stride, const void* q, 
         configured = true;
     }
     Params p;
+    p.part_o = part_o; p.part_ml = part_ml; p.part_count = part_count; p.part_blocks = part_blocks;
     p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
     p.block_table = block_table; p.positions = positions;
     p.tile_req = tile_req; p.tile_row0 = tile_row0; p.tile_rows = tile_rows;
@@ -467,9 +558,9 @@ PRB_API int prb_attention_prefill_tc(void* out, long out_stride, const void* q, 
     p.n_heads = n_heads; p.kv_heads = kv_heads; p.page_size = page_size;
     p.max_pages = max_pages; p.num_pages = num_pages; p.scale = scale; p.window = window;
     p.status = status;
-    dim3 grid(n_tiles, n_heads);
-    cudaError_t le = prb_launch_dependent(attention_prefill_tc_kernel, grid, dim3(THREADS),
-                                          SMEM_BYTES, stream, map_q, map_k, map_v, p);
+    dim3 grid(n_tiles, n_heads, part_blocks > 0 ? max_parts : 1);
+    cudaError_t le = prb_launch_maybe_early(prb_small_ctas_early(), attention_prefill_tc_kernel, grid,
+                                            dim3(THREADS), SMEM_BYTES, stream, map_q, map_k, map_v, p);
     if (le != cudaSuccess) return (int)le;
     return 0;
 }

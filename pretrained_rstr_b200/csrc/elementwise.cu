@@ -1,12 +1,17 @@
 // Memory-bound kernels of the step: embedding + position gather, LayerNorm, bias /
 // activation / residual epilogue, cache append, page copy.  All statistics and sums in
 // 32-bit; element types of tables, activations and the cache are template parameters.
+#include <cstdlib>
 #include "elementwise.cuh"
 
 // Programmatic dependent launch is on unless switched off (for measurements).
 static int g_pdl = 1;
 int prb_pdl_enabled() { return g_pdl; }
 PRB_API void prb_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+int prb_small_ctas_early() {
+    static const int on = [] { const char* e = getenv("PRB200_EARLY_SMALL"); return e ? atoi(e) : 0; }();
+    return on;
+}
 
 // ------------------------------------------------------------------ embedding
 template <typename W>
@@ -114,9 +119,10 @@ PRB_API int prb_layernorm(void* out, const float* x, const float* gamma, const f
     if (width % 4 == 0 && width <= 1024 && aligned && n_rows >= 16) {
         const int blocks = (n_rows + 3) / 4;
         cudaError_t e = out_dtype == PRB_F32
-            ? prb_launch_dependent(layernorm_warp_kernel<float>, dim3(blocks), dim3(128), 0, stream, a)
-            : prb_launch_dependent(layernorm_warp_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0,
-                                   stream, a);
+            ? prb_launch_maybe_early(prb_small_ctas_early(), layernorm_warp_kernel<float>,
+                                     dim3(blocks), dim3(128), 0, stream, a)
+            : prb_launch_maybe_early(prb_small_ctas_early(), layernorm_warp_kernel<__nv_bfloat16>,
+                                     dim3(blocks), dim3(128), 0, stream, a);
         if (e != cudaSuccess) return (int)e;
         return 0;
     }

@@ -144,7 +144,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_attention_prefill_supports.argtypes = [I]
     h.prb_attention_prefill_tile.argtypes = []
     h.prb_attention_prefill_tc.argtypes = [P, L, P, L, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I,
-                                           I, F, I, P, P]
+                                           I, F, I, I, I, P, P, P, P, P]
     h.prb_attention_prefill_tc_supports.argtypes = [I, I]
     h.prb_attention_prefill_tc_tile.argtypes = []
     h.prb_attention_decode_split.argtypes = []
@@ -614,10 +614,18 @@ def prefill_tc_supports(head_dim: int, page_size: int) -> bool:
     return bool(lib().prb_attention_prefill_tc_supports(int(head_dim), int(page_size)))
 
 
+PREFILL_MAX_PARTS = 16
+
+
 def attention_prefill_tc(out, q, k_pages, v_pages, block_table, positions, tile_req, tile_row0,
-                         tile_rows, tile_count, n_tiles, n_heads, scale, window, status) -> None:
+                         tile_rows, tile_count, n_tiles, n_heads, scale, window, status,
+                         part_blocks: int = 0, max_parts: int = 1, parts=None) -> None:
     """bfloat16 causal attention of prompt portions on tcgen05 (head size 64, pages of a
-    multiple of 64 positions): one CTA per work item of up to 128 queries and head."""
+    multiple of 64 positions): one CTA per work item of up to 128 queries and head, or, with
+    ``part_blocks`` > 0, one per chunk of ``part_blocks`` * 64 keys of the item (at most
+    ``max_parts`` chunks; ``parts`` = (float32 [n_tiles * n_heads * max_parts * 8192],
+    float32 [n_tiles * n_heads * max_parts * 256], zeroed int32 [n_tiles * n_heads]) is the
+    workspace through which the chunks of an item are merged)."""
     what = "attention_prefill_tc"
     _no_record(what)
     num_pages, kv_heads, page_size, head_dim = k_pages.shape
@@ -626,11 +634,25 @@ def attention_prefill_tc(out, q, k_pages, v_pages, block_table, positions, tile_
             raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
     if k_pages.dtype != torch.bfloat16 or not k_pages.is_contiguous() or not v_pages.is_contiguous():
         raise KernelArgumentError(f"{what}: the cache must be contiguous bfloat16")
+    part_o = part_ml = part_count = None
+    if part_blocks:
+        if parts is None or not 1 <= max_parts <= PREFILL_MAX_PARTS:
+            raise KernelArgumentError(f"{what}: key parts need a workspace and 1 to "
+                                      f"{PREFILL_MAX_PARTS} parts per item")
+        part_o, part_ml, part_count = parts
+        units = n_tiles * n_heads
+        _need(part_o, torch.float32, "parts[0]", what)
+        _need(part_ml, torch.float32, "parts[1]", what)
+        _need(part_count, torch.int32, "parts[2]", what)
+        if part_o.numel() < units * max_parts * 8192 or part_ml.numel() < units * max_parts * 256 \
+                or part_count.numel() < units:
+            raise KernelArgumentError(f"{what}: the workspace of the key parts is too small")
     _check(lib().prb_attention_prefill_tc(
         _p(out), out.stride(0), _p(q), q.stride(0), q.shape[0], _p(k_pages), _p(v_pages),
         _p(block_table), _p(positions), _p(tile_req), _p(tile_row0), _p(tile_rows), _p(tile_count),
         n_tiles, n_heads, kv_heads, head_dim, page_size, block_table.shape[1], num_pages,
-        float(scale), int(window or 0), _p(status), _stream()), what)
+        float(scale), int(window or 0), int(part_blocks), int(max_parts), _p(part_o), _p(part_ml),
+        _p(part_count), _p(status), _stream()), what)
 
 
 def attention_prefill(out, q, k_pages, v_pages, block_table, positions, tile_req, tile_row0,

@@ -78,6 +78,33 @@ DECODE_CTAS = int(os.environ.get("PRB200_DECODE_CTAS", "768"))
 USE_TC = os.environ.get("PRB200_ATTN_TC", "1") != "0"
 
 
+PREFILL_PART = int(os.environ.get("PRB200_PREFILL_PART", "-1"))     # blocks per key part; -1: choose
+
+
+def prefill_key_parts(items: int, max_context: int, window: Optional[int]):
+    """(blocks per part, most parts per item) for the tensor-memory prompt kernel; (0, 1):
+    one CTA per item.  Splitting an item's keys over several CTAs costs each of them a
+    part written and a merge (about 5 microseconds, as much as four blocks of keys), so it
+    pays only while the items alone leave most SMs empty.  Measured on a B200, kernel alone:
+    8 items of up to 16 blocks 17.4 -> 12.1 us in parts of 4, 128 items of up to 128 blocks
+    128 -> 70 us in parts of 32, 192 items of up to 16 blocks 23.0 -> 26.9 us; in a GPT-2
+    small step: 512 tokens at positions 512 to 1,023 (48 items) 0.991 -> 0.953 ms, a whole
+    prompt of 1,024 (96 items) 1.07 -> 1.11 ms.  Hence: only up to 74 items (half the SMs)."""
+    span = min(max_context, window + 128) if window else max_context
+    blocks = -(-span // 64) + (1 if window else 0)
+    if PREFILL_PART >= 0:
+        part = PREFILL_PART
+    elif items > 74 or blocks < 8:
+        part = 0
+    else:
+        # about as many CTAs as run at a time (two per SM), parts of at least four blocks
+        part = max(4, -(-items * blocks // (2 * 296)))
+    if part <= 0 or part >= blocks:
+        return 0, 1
+    part = max(part, -(-blocks // (ops.PREFILL_MAX_PARTS - 1)))
+    return part, -(-blocks // part) + (1 if window else 0)
+
+
 def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
            window: Optional[int]) -> None:
     """Attention of the step's tokens over their requests' cached keys and values.
@@ -99,11 +126,24 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
     lay = ctx.layout
     if ctx.n_tiles is None or ctx.n_tiles > 0:
         n_tiles = lay.tile_cap if ctx.n_tiles is None else ctx.n_tiles
-        prefill = ops.attention_prefill_tc if USE_TC and ops.prefill_tc_supports(head_dim, group.page_size) \
-            else ops.attention_prefill
-        prefill(out, q, cache.k, cache.v, group.block_table, ctx.positions,
-                ctx.tile_req, ctx.tile_row0, ctx.tile_rows, ctx.counts[0:1], n_tiles,
-                n_head, scale, window, ctx.status)
+        if USE_TC and ops.prefill_tc_supports(head_dim, group.page_size):
+            # (a step that runs as a graph is planned with its capacities: the most tiles and
+            # the longest context it may have)
+            parts = None
+            part_blocks, max_parts = prefill_key_parts(n_tiles * n_head, ctx.max_context, window)
+            if part_blocks:
+                units = 1 << max(6, (n_tiles * n_head - 1).bit_length())
+                parts = (ctx.scratch("attn_part_o", (units * max_parts * 8192,), torch.float32),
+                         ctx.scratch("attn_part_ml", (units * max_parts * 256,), torch.float32),
+                         ctx.scratch_zero("attn_part_count", (units,), torch.int32))
+            ops.attention_prefill_tc(out, q, cache.k, cache.v, group.block_table, ctx.positions,
+                                     ctx.tile_req, ctx.tile_row0, ctx.tile_rows, ctx.counts[0:1],
+                                     n_tiles, n_head, scale, window, ctx.status,
+                                     part_blocks=part_blocks, max_parts=max_parts, parts=parts)
+        else:
+            ops.attention_prefill(out, q, cache.k, cache.v, group.block_table, ctx.positions,
+                                  ctx.tile_req, ctx.tile_row0, ctx.tile_rows, ctx.counts[0:1],
+                                  n_tiles, n_head, scale, window, ctx.status)
     if ctx.n_singles is None or ctx.n_singles > 0:
         n_list = lay.single_cap if ctx.n_singles is None else ctx.n_singles
         # about five CTAs per SM (the kernel's leaner instance fits six): many (token, head)

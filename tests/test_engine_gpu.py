@@ -195,6 +195,23 @@ def test_step_refuses_bad_batches(folders):
     rp.lm.cache.check()
 
 
+def test_inner_width_that_is_no_multiple_of_8(tmp_path):
+    """float32 takes any width; the bfloat16 kernels read rows in 16-byte pieces and say so
+    when the model is built, not by a wrong result."""
+    raw = dict(TINY["A"][0], n_inner=100)
+    ids = random_tokens(70, raw["vocab_size"], 3)
+    folder = make_folder(str(tmp_path / "f32"), raw, 5, "float32")
+    oracle = oracle_logits(folder, {"a": ids})
+    rp = Replayer(folder, "float32", max_tokens=128)
+    rp.step([("a", ids[:40], list(range(40)))])
+    for i in range(40, len(ids)):
+        rp.step([("a", ids[i:i + 1], [0])])
+    compare(rp.rows, oracle, ATOL["float32"])
+    folder16 = make_folder(str(tmp_path / "bf16"), raw, 5, "bfloat16")
+    with pytest.raises(ValueError, match="multiple of 8"):
+        Replayer(folder16, "bfloat16", max_tokens=128)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_trace_run_program(tmp_path, dtype):
     """bin/trace_run as a user runs it: JSON lines in, <step>.f32 files and 'done' lines out."""

@@ -199,6 +199,13 @@ def test_attention_decode(nh, nkv, dh, ps, window, split_keys):
     assert float(out[3].abs().max()) == 0.0
 
 
+def _prefill_parts(units, most):
+    """Workspace of the tensor-memory prompt kernel's key parts."""
+    return (torch.empty(units * most * 8192, device="cuda"),
+            torch.empty(units * most * 256, device="cuda"),
+            torch.zeros(units, dtype=torch.int32, device="cuda"))
+
+
 PREFILL_CASES = ATTN_CASES + [(12, 12, 64, 64, None), (4, 2, 64, 128, 100), (3, 1, 64, 64, 70)]
 
 
@@ -220,19 +227,25 @@ def test_attention_prefill(nh, nkv, dh, ps, window, tile):
     t0 = torch.tensor([x[1] for x in tiles], dtype=torch.int32, device="cuda")
     tn = torch.tensor([x[2] for x in tiles], dtype=torch.int32, device="cuda")
     ref = _ref_attention(q, k, v, table, seq, pos, nh, 0.2, window)
-    kernels = [ops.attention_prefill]
+    kernels = [("mma.sync", ops.attention_prefill, {})]
     if ops.prefill_tc_supports(dh, ps):
-        kernels.append(ops.attention_prefill_tc)
+        # one CTA per tile, and the keys of a tile in chunks of 1, 2 and 4 blocks, a CTA each
+        kernels.append(("tcgen05", ops.attention_prefill_tc, {}))
+        for part in (1, 2, 4):
+            most = -(-(-(-max(lengths) // 64)) // part) + 1
+            kernels.append((f"tcgen05 / parts of {part}", ops.attention_prefill_tc,
+                            {"part_blocks": part, "max_parts": most,
+                             "parts": _prefill_parts(len(tiles) * nh, most)}))
     else:
         assert not (dh == 64 and ps % 64 == 0)
-    for kernel in kernels:
+    for name, kernel, kw in kernels:
         status = torch.zeros(4, dtype=torch.int32, device="cuda")
         out = torch.full_like(q, float("nan"))
-        kernel(out, q, k, v, table, pos, tr, t0, tn, None, len(tiles), nh, 0.2, window, status)
-        assert status.tolist() == [0, 0, 0, 0], kernel.__name__
+        kernel(out, q, k, v, table, pos, tr, t0, tn, None, len(tiles), nh, 0.2, window, status, **kw)
+        assert status.tolist() == [0, 0, 0, 0], name
         err = (out.float() - ref).abs()
         assert float(err.max()) <= 2e-2, \
-            f"{kernel.__name__}: worst row {int(err.max(dim=1).values.argmax())}"
+            f"{name}: worst row {int(err.max(dim=1).values.argmax())}"
 
 
 def test_attention_far_key_stands_out():
@@ -252,9 +265,14 @@ def test_attention_far_key_stands_out():
     tn = torch.tensor([64, 2], dtype=torch.int32, device="cuda")
     ops.attention_prefill(out, q, k, v, table, pos, tr, t0, tn, None, 2, nh, 0.125, None, status)
     assert float((out.float() - ref).abs().max()) <= 2e-2
-    out_tc = torch.zeros_like(q)
-    ops.attention_prefill_tc(out_tc, q, k, v, table, pos, tr, t0, tn, None, 2, nh, 0.125, None, status)
-    assert float((out_tc.float() - ref).abs().max()) <= 2e-2
+    for part in (0, 1, 3, 8):
+        out_tc = torch.zeros_like(q)
+        most = -(-16 // part) if part else 1
+        ops.attention_prefill_tc(out_tc, q, k, v, table, pos, tr, t0, tn, None, 2, nh, 0.125, None,
+                                 status, part_blocks=part, max_parts=most,
+                                 parts=_prefill_parts(2 * nh, most) if part else None)
+        assert float((out_tc.float() - ref).abs().max()) <= 2e-2, part
+        assert status.tolist() == [0, 0, 0, 0]
     t = q.shape[0]
     splits = -(-1024 // ops.decode_split())
     ws = torch.zeros(t * nh * splits * (dh + 4), device="cuda")
