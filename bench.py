@@ -179,8 +179,9 @@ def timed_decode(engine, lm, batch, ctx_len, steps, warmup, vocab, seed):
 
 
 def profile_gemm(shape: str) -> int:
-    """Small workload for ncu: the prompt-time GEMM at one shape, every tile width, timed as
-    a CUDA graph of 20 launches, with cuBLAS (torch.mm) beside it."""
+    """Small workload for ncu: the prompt-time GEMM at one shape, every tile width and every
+    split of the reduction over a cluster that fits, timed as a CUDA graph of 20 launches,
+    with cuBLAS (torch.mm) beside it."""
     import torch
     from pretrained_rstr_b200.csrc import ops
     m, n, k = (int(x) for x in shape.split(","))
@@ -213,6 +214,16 @@ def profile_gemm(shape: str) -> int:
             "bf16_bias_gelu_us": timeit(lambda: ops.gemm_bf16(outb, a, w, bias=bias, act="gelu_new", tile_n=tn)),
             "f32_bias_resid_us": timeit(lambda: ops.gemm_bf16(outf, a, w, bias=bias, resid=outf, tile_n=tn)),
         }
+    blocks = -(-k // 64)
+    for tn in (64, 128):
+        for sp in (2, 4, 8):
+            if -(-blocks // sp) * (sp - 1) >= blocks or -(-m // 128) * -(-n // tn) * sp > 148:
+                continue
+            res[f"tile{tn}_split{sp}"] = {
+                "bf16_plain_us": timeit(lambda: ops.gemm_bf16(outb, a, w, tile_n=tn, split_k=sp)),
+                "bf16_bias_gelu_us": timeit(lambda: ops.gemm_bf16(outb, a, w, bias=bias, act="gelu_new", tile_n=tn, split_k=sp)),
+                "f32_bias_resid_us": timeit(lambda: ops.gemm_bf16(outf, a, w, bias=bias, resid=outf, tile_n=tn, split_k=sp)),
+            }
     res["cublas_us"] = timeit(lambda: torch.mm(a, w.t(), out=outb))
     res["gflop"] = 2 * m * n * k / 1e9
     print(json.dumps({"profile_gemm": shape, **res}))

@@ -417,6 +417,213 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
 }
 
+// ---------------------------------------------------------------- split-K variant
+// For products with too few output tiles to fill the SMs (a few hundred rows into a narrow
+// output): the reduction dimension of a tile is split over the S CTAs of a thread-block
+// cluster.  CTA r multiplies k-blocks [r * per, (r + 1) * per) into tensor memory, copies its
+// 128 x BN float32 partial tile into its shared memory (over the stage ring, which is free by
+// then), and after a cluster barrier every CTA finishes 128 / S rows: it sums their partial
+// values over the cluster in rank order through distributed shared memory, adds bias, applies
+// the activation, adds the residual and stores.  A second cluster barrier keeps every CTA's
+// shared memory alive until its peers have read it.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, int rank) {
+    uint32_t raddr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(local_addr), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
+    return v;
+}
+
+template <int BN, int S, typename O>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_splitk_kernel(const __grid_constant__ CUtensorMap map_a,
+                        const __grid_constant__ CUtensorMap map_w, O* __restrict__ c,
+                        const float* __restrict__ bias, const float* __restrict__ resid, int m,
+                        int n, int k, long ldc, int act, int* status) {
+    using Cfg = TileCfg<BN>;
+    constexpr int PP = BN + 1;                       // pitch of the partial tile (words)
+    static_assert((size_t)BM * PP * 4 <= (size_t)Cfg::STAGES * Cfg::STAGE_BYTES,
+                  "the partial tile must fit over the stage ring");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* tiles = smem;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full_bar = bars;                       // [STAGES]  TMA -> MMA
+    uint64_t* empty_bar = bars + Cfg::STAGES;        // [STAGES]  MMA -> TMA
+    uint64_t* tfull_bar = bars + 2 * Cfg::STAGES;    // accumulator complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfull_bar + 1);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* part = reinterpret_cast<float*>(tiles);   // [BM][PP], after the main loop
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    prb_grid_launch_dependents();
+    const int rank = (int)(blockIdx.x % S);          // clusters are S consecutive CTAs of x
+    const int tile = (int)(blockIdx.x / S);
+    const int m_tiles = (m + BM - 1) / BM;
+    const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+    const int k_blocks = (k + BK - 1) / BK;
+    const int per = (k_blocks + S - 1) / S;
+    const int kb0 = rank * per;
+    const int kb1 = kb0 + per < k_blocks ? kb0 + per : k_blocks;
+    const int n_kb = kb1 > kb0 ? kb1 - kb0 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(tfull_bar), 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(tmem_slot)),
+                     "r"((uint32_t)Cfg::ACC_STRIDE)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    prb_grid_wait();
+
+    // Rows rank * RPC .. of the tile are finished here; a warp takes every eighth of them, a
+    // lane every 32nd column.  Their bias and residual values do not depend on the product:
+    // they are requested before the cluster barrier, so their latency is off the path.
+    constexpr int RPC = BM / S, CPL = BN / 32, RPW = (RPC + 7) / 8;
+    float pre_b[CPL], pre_r[RPW][CPL];
+    if (warp >= 2) {
+#pragma unroll
+        for (int j = 0; j < CPL; ++j) {
+            const int col = n0 + j * 32 + lane;
+            pre_b[j] = (bias && col < n) ? __ldg(bias + col) : 0.0f;
+#pragma unroll
+            for (int i = 0; i < RPW; ++i) {
+                const int row = m0 + rank * RPC + (warp - 2) + 8 * i;
+                pre_r[i][j] = (resid && col < n && row < m && (warp - 2) + 8 * i < RPC)
+                                  ? resid[(size_t)row * ldc + col] : 0.0f;
+            }
+        }
+    }
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            int it = 0;
+            for (; it < n_kb; ++it) {
+                const int s = it % Cfg::STAGES;
+                ok = mbar_wait(smem_u32(&empty_bar[s]), ((it / Cfg::STAGES) & 1) ^ 1, failed);
+                if (!ok) {
+                    prb_set_status(status, PRB_S_WAIT_TIMEOUT, 21, blockIdx.x, it);
+                    break;
+                }
+                const uint32_t fb = smem_u32(&full_bar[s]);
+                mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+                uint8_t* stage = tiles + (size_t)s * Cfg::STAGE_BYTES;
+                tma_load_2d(smem_u32(stage), &map_a, fb, (kb0 + it) * BK, m0);
+                tma_load_2d(smem_u32(stage + Cfg::A_BYTES), &map_w, fb, (kb0 + it) * BK, n0);
+            }
+            if (!ok) {
+                const int first = it > Cfg::STAGES ? it - Cfg::STAGES : 0;
+                for (int j = first; j < it; ++j) {
+                    const uint32_t fb = smem_u32(&full_bar[j % Cfg::STAGES]);
+                    for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+                        if (mbar_try_wait(fb, (j / Cfg::STAGES) & 1)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BM, BN);
+            bool ok = true;
+            for (int it = 0; it < n_kb; ++it) {
+                const int s = it % Cfg::STAGES;
+                ok = mbar_wait(smem_u32(&full_bar[s]), (it / Cfg::STAGES) & 1, failed);
+                if (!ok) {
+                    prb_set_status(status, PRB_S_WAIT_TIMEOUT, 22, blockIdx.x, it);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t a_addr = smem_u32(tiles + (size_t)s * Cfg::STAGE_BYTES);
+                const uint64_t a_desc = make_smem_desc(a_addr);
+                const uint64_t b_desc = make_smem_desc(a_addr + Cfg::A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                    umma_bf16(tmem_base, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2),
+                              idesc, (it > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&empty_bar[s]));
+            }
+            if (ok) {
+                if (n_kb > 0) umma_commit(smem_u32(tfull_bar));
+                else mbar_arrive(smem_u32(tfull_bar));       // nothing to wait for
+            }
+        }
+    } else {
+        // the accumulator, one row per thread, into the partial tile
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        bool ok = mbar_wait(smem_u32(tfull_bar), 0, failed);
+        if (!ok && lane == 0) prb_set_status(status, PRB_S_WAIT_TIMEOUT, 23, blockIdx.x, warp);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        tcgen05_fence_after();
+        float* prow = part + (size_t)(quarter * 32 + lane) * PP;
+        for (int c0 = half * 32; c0 < BN; c0 += 64) {
+            uint32_t r[32];
+            if (ok && n_kb > 0) {
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) prow[c0 + j] = __uint_as_float(r[j]);
+        }
+        tcgen05_fence_before();
+    }
+    __syncwarp();
+    cluster_sync_all();                               // every CTA's partial tile is in place
+    if (warp >= 2) {
+        const uint32_t part_addr = smem_u32(part);
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) {
+            const int rr = (warp - 2) + 8 * i;
+            const int trow = rank * RPC + rr, row = m0 + trow;
+            if (rr >= RPC || row >= m) break;         // uniform across the warp
+            float v[CPL][S];
+#pragma unroll
+            for (int j = 0; j < CPL; ++j)
+#pragma unroll
+                for (int s = 0; s < S; ++s)
+                    v[j][s] = ld_cluster_f32(part_addr + (uint32_t)(trow * PP + j * 32 + lane) * 4, s);
+#pragma unroll
+            for (int j = 0; j < CPL; ++j) {
+                const int col = n0 + j * 32 + lane;
+                if (col >= n) continue;
+                float x = v[j][0];
+#pragma unroll
+                for (int s = 1; s < S; ++s) x += v[j][s];           // in rank order
+                x = epilogue_act(x + pre_b[j], act) + pre_r[i][j];
+                c[(size_t)row * ldc + col] = prb_from_float<O>(x);
+            }
+        }
+    }
+    __syncwarp();
+    cluster_sync_all();                               // the partial tiles have been read
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"((uint32_t)Cfg::ACC_STRIDE)
+                     : "memory");
+    }
+}
+
 // ------------------------------------------------------------------ host side
 using tmap::get_map;
 
@@ -450,6 +657,39 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, O* c, const float* bias
     return 0;
 }
 
+template <int BN, int S, typename O>
+int launch_splitk(const CUtensorMap& ma, const CUtensorMap& mw, O* c, const float* bias,
+                  const float* resid, int m, int n, int k, long ldc, int act, int* status,
+                  cudaStream_t stream) {
+    using Cfg = TileCfg<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_splitk_kernel<BN, S, O>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)Cfg::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const long tiles = (long)((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles * S));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = prb_pdl_enabled() ? 1 : 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = S;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_bf16_splitk_kernel<BN, S, O>, ma, mw, c, bias,
+                                        resid, m, n, k, ldc, act, status);
+    if (le != cudaSuccess) return (int)le;
+    return 0;
+}
 }  // namespace
 
 namespace {
@@ -461,6 +701,8 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
     if (k % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)a) % 16 != 0 ||
         ((uintptr_t)w) % 16 != 0)
         return PRB_E_ALIGN;
+    int split = tile_n >> 16;          // forced: tile width in the low half, cluster size above
+    tile_n &= 0xffff;
     if (tile_n == 0) {
         // The CTA with the most tiles sets the time.  A tile's main loop is bound by the
         // bytes its SM takes in (128 + width rows of 128 bytes per block of 64 along K), its
@@ -477,9 +719,28 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
             const long main_loop = kb * (128 + bn) + 400, epilogue = per_col * bn;
             const long cost = (rounds - 1) * (main_loop > epilogue ? main_loop : epilogue) +
                               main_loop + epilogue;
-            if (best < 0 || cost < best) { best = cost; tile_n = bn; }
+            if (best < 0 || cost < best) { best = cost; tile_n = bn; split = 0; }
+        }
+        // Few tiles and a long reduction: the k-blocks of a tile over a cluster of CTAs, which
+        // costs the partial tiles' way through shared memory and two cluster barriers, while a
+        // CTA finishes only its share of the tile's rows (constants fitted to measurements at
+        // 128 to 1,024 rows, N = 768 and 1,600, K = 768 to 6,400).
+        if (sc.kv_width == 0) {
+            for (int bn = 128; bn >= 64; bn -= 64) {
+                const long tiles = mt * ((n + bn - 1) / bn);
+                for (int sp = 2; sp <= 8; sp *= 2) {
+                    const long per = (kb + sp - 1) / sp;
+                    if (tiles * sp > 148 || per * (sp - 1) >= kb || per < 2) continue;
+                    const long cost = per * (128 + bn) + 400 + 700 + per_col * bn / 2;
+                    if (cost < best) { best = cost; tile_n = bn; split = sp; }
+                }
+            }
         }
     }
+    if (split != 0 && (sc.kv_width != 0 || (split != 2 && split != 4 && split != 8) ||
+                       (tile_n != 64 && tile_n != 128) ||
+                       (((k + BK - 1) / BK + split - 1) / split) * (split - 1) >= (k + BK - 1) / BK))
+        return PRB_E_ARG;
     if (tile_n < 32 || tile_n > 256 || tile_n % 32 != 0) return PRB_E_ARG;
     CUtensorMap ma, mw;
     int r = get_map(a, m, k, lda, BM, &ma);
@@ -493,6 +754,18 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
          : launch<BN_, __nv_bfloat16>(ma, mw, (__nv_bfloat16*)c, bias, resid, m, n, k, ldc, act, \
                                       status, sc, stream))
     if (out_dtype != PRB_F32 && out_dtype != PRB_BF16) return PRB_E_DTYPE;
+#define PRB_GO_SPLIT(BN_, S_)                                                                    \
+    (out_dtype == PRB_F32                                                                        \
+         ? launch_splitk<BN_, S_, float>(ma, mw, (float*)c, bias, resid, m, n, k, ldc, act,      \
+                                         status, stream)                                         \
+         : launch_splitk<BN_, S_, __nv_bfloat16>(ma, mw, (__nv_bfloat16*)c, bias, resid, m, n, k, \
+                                                 ldc, act, status, stream))
+    if (split != 0) {
+        if (tile_n == 64)
+            return split == 2 ? PRB_GO_SPLIT(64, 2) : split == 4 ? PRB_GO_SPLIT(64, 4) : PRB_GO_SPLIT(64, 8);
+        return split == 2 ? PRB_GO_SPLIT(128, 2) : split == 4 ? PRB_GO_SPLIT(128, 4) : PRB_GO_SPLIT(128, 8);
+    }
+#undef PRB_GO_SPLIT
     switch (tile_n) {
         case 32: return PRB_GO(32);
         case 64: return PRB_GO(64);
@@ -507,7 +780,8 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
 }
 }  // namespace
 
-// tile_n: 0 = choose (by M, N, K and the output type), or a multiple of 32 up to 256.
+// tile_n: 0 = choose (by M, N, K and the output type), or a multiple of 32 up to 256; with a
+// cluster size of 2, 4 or 8 in bits 16 and up, the split-K variant at tile width 64 or 128.
 PRB_API int prb_gemm_bf16(void* c, const void* a, const void* w, const float* bias,
                           const float* resid, int m, int n, int k, long lda, long ldw, long ldc,
                           int act, int out_dtype, int tile_n, int* status, cudaStream_t stream) {

@@ -408,12 +408,14 @@ def gemm_f32(out, a, w, bias=None, resid=None, act=None) -> None:
 
 
 def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, status=None,
-              kv_scatter=None) -> None:
+              kv_scatter=None, split_k: int = 0) -> None:
     """out[M,N] = act(a[M,K] . w[N,K]^T + bias) (+ resid) on the tcgen05 tensor cores:
     bfloat16 operands, float32 accumulation in tensor memory, epilogue in float32; out is
     bfloat16 or float32.  K and the row pitches of a and w must be multiples of 8.
     ``kv_scatter`` = (k_pages, v_pages, slots, q_width): the key and value columns of a fused
-    QKV product also go to the paged cache (of the output's element type)."""
+    QKV product also go to the paged cache (of the output's element type).  ``tile_n`` and
+    ``split_k`` force a tile width and, for widths 64 and 128, a cluster of 2, 4 or 8 CTAs
+    that share a tile's reduction; left at 0 the kernel chooses."""
     what = "gemm_bf16"
     _no_record(what)
     for name, t in (("a", a), ("w", w)):
@@ -433,7 +435,7 @@ def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, statu
             raise KernelArgumentError(f"{what}: resid must have the output's shape and stride")
     if kv_scatter is not None:
         k_pages, v_pages, slots, q_width = kv_scatter
-        if resid is not None or tile_n:
+        if resid is not None or tile_n or split_k:
             raise KernelArgumentError(f"{what}: a product that scatters takes no residual or tile width")
         if k_pages.dtype != out.dtype or v_pages.dtype != out.dtype or not k_pages.is_contiguous() \
                 or not v_pages.is_contiguous():
@@ -447,7 +449,7 @@ def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, statu
         return
     _check(lib().prb_gemm_bf16(_p(out), _p(a), _p(w), _p(bias), _p(resid), m, n, k, a.stride(0),
                                w.stride(0), out.stride(0), ACT_CODES[act], dtype_code(out.dtype),
-                               tile_n, _p(status), _stream()), what)
+                               int(tile_n) | (int(split_k) << 16), _p(status), _stream()), what)
 
 
 def midm_supports(m: int, n: int, k: int) -> bool:

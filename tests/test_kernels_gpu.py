@@ -77,6 +77,38 @@ def test_gemm_bf16_every_tile_width(tile_n):
     assert float((out - ref).abs().max()) <= 1e-3
 
 
+@pytest.mark.parametrize("tile_n,split_k", [(64, 2), (64, 4), (64, 8), (128, 2), (128, 4), (128, 8)])
+@pytest.mark.parametrize("m,n,k", [(256, 768, 3072), (200, 600, 1000), (130, 72, 520)])
+def test_gemm_bf16_split_over_a_cluster(tile_n, split_k, m, n, k):
+    """The reduction of a tile split over a thread-block cluster: both output types, with
+    bias, activation and residual, at sizes that leave ragged tiles and a ragged last split."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(tile_n + split_k)
+    a = (torch.randn(m, k, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda", generator=g)
+    resid = torch.randn(m, n, device="cuda", generator=g)
+    blocks = -(-k // 64)
+    if -(-blocks // split_k) * (split_k - 1) >= blocks:
+        with pytest.raises(ops.KernelArgumentError):
+            ops.gemm_bf16(torch.zeros(m, n, device="cuda"), a, w, tile_n=tile_n, split_k=split_k)
+        return
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ref = a.float() @ w.float().t() + bias
+    out = resid.clone()
+    ops.gemm_bf16(out, a, w, bias=bias, resid=out, tile_n=tile_n, split_k=split_k, status=status)
+    assert float((out - (ref + resid)).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))
+    out16 = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(out16, a, w, bias=bias, act="gelu_new", tile_n=tile_n, split_k=split_k, status=status)
+    want = _act("gelu_new", ref)
+    assert float((out16.float() - want).abs().max()) <= 1e-2 * max(1.0, float(want.abs().max()))
+    assert status.tolist() == [0, 0, 0, 0]
+    # the choice left to the kernel gives the same values up to the order of summation
+    auto = resid.clone()
+    ops.gemm_bf16(auto, a, w, bias=bias, resid=auto, status=status)
+    assert float((auto - out).abs().max()) <= 1e-3 * max(1.0, float(ref.abs().max()))
+
+
 def test_gemm_bf16_refuses_unaligned_k():
     ops = _ops()
     a = torch.zeros(4, 20, device="cuda", dtype=torch.bfloat16)
