@@ -271,6 +271,127 @@ def profile_decode(batch: int, table: bool = False) -> int:
     return 0
 
 
+def profile_prompt(spec: str, table: bool = True) -> int:
+    """One prompt alone: a step of N tokens (after AT tokens already in the cache) as the
+    engine runs it (a CUDA graph from the third time on): device time of the step and the
+    torch profiler's kernel table.  ``spec`` is "N" or "N,AT"."""
+    import random
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from pretrained_rstr_b200 import load_lm
+    from pretrained_rstr_b200.config import GPT2Config
+    from pretrained_rstr_b200.engine.batch import Entry
+    from pretrained_rstr_b200.weights import make_random_model
+    parts = [int(x) for x in spec.split(",")]
+    n, at = parts[0], (parts[1] if len(parts) > 1 else 0)
+    tmp = tempfile.mkdtemp(prefix="prb200_prof_")
+    try:
+        make_random_model(tmp, GPT2Config.from_dict(dict(SMALL)), seed=2, dtype=torch.bfloat16)
+        m = load_lm(tmp, gpu=True, dtype="bfloat16", max_lanes=8, max_batched_tokens=2048,
+                    prefill_chunk=1024, share_prefixes=False)
+    finally:
+        import shutil
+        shutil.rmtree(tmp, ignore_errors=True)
+    runner, cache = m.loaded.runner, m.loaded.cache
+    rng = random.Random(0)
+    ids = [rng.randrange(SMALL["vocab_size"]) for _ in range(at + n)]
+
+    def one(tag):
+        cache.open(tag)
+        if at:
+            runner.step([Entry(tag, ids[:at], [])])
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        runner.start_event = start
+        runner.step([Entry(tag, ids[at:], [n - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        runner.start_event = None
+        cache.close(tag)
+        return start.elapsed_time(end)
+
+    for i in range(4):
+        one(("warm", i))
+    times = sorted(one(("timed", i)) for i in range(5))
+    if table:
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for i in range(3):
+                one(("table", i))
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=12,
+                                        max_name_column_width=70))
+    print(json.dumps({"profile_prompt": spec, "device_ms": [round(t, 4) for t in times]}))
+    return 0
+
+
+def profile_attention(spec: str) -> int:
+    """The prompt attention kernels alone: PROMPTS prompts of LENGTH tokens, HEADS heads of
+    64 ("HEADS,PROMPTS,LENGTH"), causal, over a paged cache, each timed as a CUDA graph of 10
+    launches: the mma.sync kernel, the tcgen05 kernel with one CTA per tile, and with a tile's
+    keys in parts of 1 to 32 blocks."""
+    import torch
+    from pretrained_rstr_b200.csrc import ops
+    nh, nseq, length = (int(x) for x in spec.split(","))
+    dh = ps = 64
+    g = torch.Generator(device="cpu").manual_seed(0)
+    pages_per = -(-length // ps)
+    num_pages = nseq * pages_per + 3
+    k = torch.randn(num_pages, nh, ps, dh, generator=g).bfloat16().cuda()
+    v = torch.randn(num_pages, nh, ps, dh, generator=g).bfloat16().cuda()
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    table = torch.full((nseq, pages_per + 1), -1, dtype=torch.int32)
+    for b in range(nseq):
+        for i in range(pages_per):
+            table[b, i] = perm.pop()
+    table = table.cuda()
+    pos = torch.cat([torch.arange(length) for _ in range(nseq)]).int().cuda()
+    q = torch.randn(nseq * length, nh * dh, generator=g).bfloat16().cuda()
+    tiles = [(b, b * length + r0, min(128, length - r0)) for b in range(nseq)
+             for r0 in range(0, length, 128)]
+    tr, t0, tn = (torch.tensor([x[i] for x in tiles], dtype=torch.int32, device="cuda")
+                  for i in range(3))
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+
+    def timeit(f, reps=10):
+        f()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                f()
+        graph.replay()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / reps * 1e3
+
+    blocks = -(-length // 64)
+    units = len(tiles) * nh
+    cases = [("mma_sync", ops.attention_prefill, {}), ("tcgen05", ops.attention_prefill_tc, {})]
+    for part in (1, 2, 4, 8, 16, 32):
+        most = -(-blocks // part)
+        if part < blocks and most <= ops.PREFILL_MAX_PARTS:
+            ws = (torch.empty(units * most * 8192, device="cuda"),
+                  torch.empty(units * most * 256, device="cuda"),
+                  torch.zeros(units, dtype=torch.int32, device="cuda"))
+            cases.append((f"tcgen05_parts_of_{part}", ops.attention_prefill_tc,
+                          {"part_blocks": part, "max_parts": most, "parts": ws}))
+    flops = 4 * nseq * nh * dh * length * (length + 1) / 2
+    res, ref = {}, None
+    for name, fn, kw in cases:
+        out = torch.zeros_like(q)
+        us = timeit(lambda: fn(out, q, k, v, table, pos, tr, t0, tn, None, len(tiles), nh, 0.125,
+                               None, status, **kw))
+        if ref is None:
+            ref = out.clone()
+        res[name] = {"us": round(us, 1), "tflops": round(flops / us / 1e6, 1),
+                     "max_diff": float((out.float() - ref.float()).abs().max())}
+    print(json.dumps({"profile_attention": spec, "status": status.tolist(), **res}))
+    return 0
+
+
 def profile_prefill(table: bool = True) -> int:
     """Small workload for a profiler: one step of 2 x 1,000 prompt tokens, launched kernel
     by kernel, with the torch profiler's kernel table printed (``table``; off under ncu)."""
@@ -320,6 +441,10 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--profile-prefill", action="store_true")
     ap.add_argument("--profile-gemm", default=None, metavar="M,N,K")
+    ap.add_argument("--profile-prompt", default=None, metavar="N[,AT]",
+                    help="one prompt step of N tokens after AT cached ones: device time, kernel table")
+    ap.add_argument("--profile-attention", default=None, metavar="HEADS,PROMPTS,LENGTH",
+                    help="the prompt attention kernels alone, every way of sharing a tile's keys")
     ap.add_argument("--profile-decode", type=int, default=None, metavar="BATCH")
     ap.add_argument("--kernel-table", action="store_true",
                     help="with --profile-decode: print the torch profiler's kernel table")
@@ -344,6 +469,10 @@ def main() -> int:
         return profile_decode(args.profile_decode, args.kernel_table)
     if args.profile_prefill:
         return profile_prefill(not args.no_table)
+    if args.profile_prompt:
+        return profile_prompt(args.profile_prompt, not args.no_table)
+    if args.profile_attention:
+        return profile_attention(args.profile_attention)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
