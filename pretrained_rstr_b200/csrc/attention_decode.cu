@@ -46,6 +46,21 @@ attention_decode_kernel(Args a) {
     unit<LPK, DEC_WARPS, UB, CLUSTER>(a, blockIdx.x, blockIdx.y, blockIdx.z, sh);
 }
 
+// The streaming variant: one more template of the same unit, with the ring in dynamic shared
+// memory (3 stages x (keys + values) x 64 positions x head_dim x 2 bytes: 48 KB at head size
+// 64, four CTAs per SM).
+template <int LPK, bool CLUSTER>
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+attention_decode_stream_kernel(Args a) {
+    extern __shared__ __align__(128) unsigned char stream_ring[];
+    __shared__ Shared<DEC_WARPS> sh;
+    __shared__ StreamState st;
+    prb_grid_launch_dependents();
+    prb_grid_wait();
+    if (threadIdx.x == 0) st.ring = stream_ring;
+    unit<LPK, DEC_WARPS, 2, CLUSTER, true>(a, blockIdx.x, blockIdx.y, blockIdx.z, sh, &st);
+}
+
 // Whether the kernel may be placed on the SMs before its predecessor has ended.  Off, by
 // measurement: GPT-2 small with 8 requests takes 0.467 ms a step with it and 0.430 ms
 // without.  The likely cause: CTAs that are placed one by one, as the CTAs of the QKV product
@@ -59,11 +74,12 @@ static int decode_early() {
 // Launch (the kernel itself lets its successor start early) and, for `cluster_z` > 1, the
 // CTAs of a (token, head) (grid z) as one thread-block cluster.
 template <typename K>
-cudaError_t launch_decode(K kernel, dim3 grid, int cluster_z, cudaStream_t stream, const Args& a) {
+cudaError_t launch_decode(K kernel, dim3 grid, int cluster_z, cudaStream_t stream, const Args& a,
+                          size_t dynamic_smem = 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(DEC_THREADS);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = dynamic_smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -84,6 +100,11 @@ cudaError_t launch_decode(K kernel, dim3 grid, int cluster_z, cudaStream_t strea
 PRB_API int prb_attention_decode_split() { return SPLIT; }
 
 // Switch (for measurements): 0 = splits always merge through the workspace.
+// Switch (for measurements): -1 = the streaming variant where it is chosen, 0 = never,
+// 1 = wherever it applies.
+static int g_decode_stream = -1;
+static int prb_decode_stream() { return g_decode_stream; }
+PRB_API void prb_attention_decode_set_stream(int mode) { g_decode_stream = mode; }
 static int g_decode_clusters = 1;
 static int prb_decode_clusters() { return g_decode_clusters; }
 PRB_API void prb_attention_decode_set_clusters(int on) { g_decode_clusters = on ? 1 : 0; }
@@ -143,6 +164,35 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
                                      a);                                                         \
     } while (0)
     cudaError_t e;
+    // Long splits and more units than run at once: the streaming variant.
+    const size_t ring_bytes = (size_t)STREAM_STAGES * 2 * STREAM_KEYS * head_dim * 2;
+    const int stream_mode = prb_decode_stream();
+    const bool use_stream = window <= 0 && head_dim <= 128 &&
+                            (stream_mode == 1 || (stream_mode < 0 && many && split_keys >= 512));
+    if (use_stream) {
+#define PRB_DEC_STREAM(L)                                                                        \
+    do {                                                                                         \
+        auto kern = cluster ? attention_decode_stream_kernel<L, true>                            \
+                            : attention_decode_stream_kernel<L, false>;                          \
+        static bool configured[2] = {false, false};                                              \
+        if (!configured[cluster ? 1 : 0]) {                                                      \
+            cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,           \
+                                 cudaSharedmemCarveoutMaxShared);                                \
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                                     (int)((size_t)STREAM_STAGES * 2 * STREAM_KEYS * (L * 8) * 2)); \
+            if (e != cudaSuccess) return (int)e;                                                 \
+            configured[cluster ? 1 : 0] = true;                                                  \
+        }                                                                                        \
+        e = launch_decode(kern, grid, cluster ? max_splits : 1, stream, a, ring_bytes);          \
+    } while (0)
+        if (pieces <= 2) PRB_DEC_STREAM(2);
+        else if (pieces <= 4) PRB_DEC_STREAM(4);
+        else if (pieces <= 8) PRB_DEC_STREAM(8);
+        else PRB_DEC_STREAM(16);
+#undef PRB_DEC_STREAM
+        if (e != cudaSuccess) return (int)e;
+        return 0;
+    }
     if (pieces <= 2) PRB_DEC(2);
     else if (pieces <= 4) PRB_DEC(4);
     else if (pieces <= 8) PRB_DEC(8);

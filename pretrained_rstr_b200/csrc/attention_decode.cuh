@@ -76,6 +76,68 @@ template <int NW> struct Shared {
     float part_ml[2];
 };
 
+// Streaming variant (long splits, many units): keys and values of a split come in blocks of
+// 64 positions by bulk copies (cp.async.bulk, whole runs of a page's rows; no multicast) into
+// a ring of shared-memory stages, signalled by mbarriers, so that two blocks are in flight
+// while the warps score a third; the register-batch variant has at most one batch in flight
+// while it scores.  The keys go to the same (warp, lane) in the same order, so both variants
+// give the same bits.
+constexpr int STREAM_KEYS = 64;     // keys per block
+constexpr int STREAM_STAGES = 3;
+constexpr uint32_t STREAM_WAIT_LIMIT = 1u << 22;
+struct StreamState {
+    unsigned long long full[STREAM_STAGES];       // mbarriers: a block has landed
+    unsigned long long empty[STREAM_STAGES];      //            all warps have read it
+    int bad[STREAM_STAGES];                       // the block names a page outside the pool
+    int failed;                                   // a wait gave up
+    unsigned char* ring;                          // [stages][K | V][64 keys * head_dim * 2 bytes]
+};
+__device__ __forceinline__ uint32_t st_smem(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void st_mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void st_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void st_mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool st_mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; false when it gave up or another thread of the CTA already had.
+__device__ __forceinline__ bool st_mbar_wait(uint32_t bar, uint32_t parity, volatile int* failed) {
+    for (uint32_t i = 0; i < STREAM_WAIT_LIMIT; ++i) {
+        if (st_mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *failed) return false;
+    }
+    *failed = 1;
+    return false;
+}
+__device__ __forceinline__ void st_bulk_copy(uint32_t dst, const void* src, uint32_t bytes,
+                                             uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ uint4 st_ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
 // Thread-block cluster helpers (the splits of one (token, head) form a cluster).
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -123,8 +185,11 @@ __device__ __forceinline__ void merge_cluster(const Args& a, int t, int h, int s
 // memory and merged by the cluster's first CTA instead of going through the workspace and
 // a counter.  Every CTA of the cluster then reaches the two cluster barriers, also those
 // whose split holds no visible key.
-template <int LPK, int NW, int UB = 4, bool CLUSTER = false>
-__device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Shared<NW>& sh) {
+// STREAM: the keys come through the shared-memory ring of `stream` (no window; head_dim up
+// to 128).
+template <int LPK, int NW, int UB = 4, bool CLUSTER = false, bool STREAM = false>
+__device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Shared<NW>& sh,
+                                     StreamState* stream = nullptr) {
     float* sh_m = sh.m;
     float* sh_l = sh.l;
     float (*sh_o)[MAX_DH] = sh.o;
@@ -186,6 +251,17 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
     const int first_page = (s * a.split) / a.page_size;
     for (int i = threadIdx.x; i < a.split / a.page_size; i += (NW * 32))
         sh_pages[i] = (first_page + i < a.max_pages) ? table[first_page + i] : -1;
+    if constexpr (STREAM) {
+        if (threadIdx.x == 0) {
+            for (int i = 0; i < STREAM_STAGES; ++i) {
+                st_mbar_init(st_smem(&stream->full[i]), 1);
+                st_mbar_init(st_smem(&stream->empty[i]), NW);
+            }
+            stream->failed = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+    }
     __syncthreads();
     DEC_TRACE(1);
 
@@ -221,21 +297,20 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
             }
         }
     };
-    auto score = [&](const Batch& bt) {
-#pragma unroll
-        for (int u = 0; u < UB; ++u) {
-            float part = dot8(bt.k[u], qf);
+    auto score_key = [&](const uint4& kk, const uint4& vv, bool ok) {
+        {
+            float part = dot8(kk, qf);
             // every lane takes part in the reduction over the LPK pieces of a key row
 #pragma unroll
             for (int o = LPK / 2; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            const float sc = bt.ok[u] ? part * a.scale : -INFINITY;
+            const float sc = ok ? part * a.scale : -INFINITY;
             // online softmax per key slot (each group of LPK lanes has its own running state)
             const float m_new = fmaxf(m, sc);
             if (m_new > -INFINITY) {
                 const float corr = (m == -INFINITY) ? 0.0f : __expf(m - m_new);
                 const float p = (sc == -INFINITY) ? 0.0f : __expf(sc - m_new);
                 l = l * corr + p;
-                const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&bt.v[u]);
+                const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vv);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float2 f = __bfloat1622float2(vp[i]);
@@ -246,7 +321,94 @@ __device__ __forceinline__ void unit(const Args& a, int idx, int h, int s, Share
             }
         }
     };
-    {
+    auto score = [&](const Batch& bt) {
+#pragma unroll
+        for (int u = 0; u < UB; ++u) score_key(bt.k[u], bt.v[u], bt.ok[u]);
+    };
+    if constexpr (STREAM) {
+        const int row_bytes = a.head_dim * 2;
+        const uint32_t ring = st_smem(stream->ring);
+        const uint32_t stage_bytes = 2u * STREAM_KEYS * row_bytes;
+        const int n_blk = (k_end - k_begin + STREAM_KEYS - 1) / STREAM_KEYS;
+        volatile int* failed = &stream->failed;
+        // thread 0: the copies of block `blk` (its stage is free)
+        auto issue = [&](int blk) {
+            const int st = blk % STREAM_STAGES;
+            const int j0 = k_begin + blk * STREAM_KEYS;
+            const int cnt = min(STREAM_KEYS, k_end - j0);
+            const uint32_t fb = st_smem(&stream->full[st]);
+            bool bad = false;
+            for (int j = j0; j < j0 + cnt; j += a.page_size - j % a.page_size) {
+                const int page = sh_pages[j / a.page_size - first_page];
+                if (page < 0 || page >= a.num_pages) {
+                    prb_set_status(a.status, PRB_S_PAGE_RANGE, t, j, page);
+                    bad = true;
+                }
+            }
+            stream->bad[st] = bad ? 1 : 0;
+            if (bad) {                             // nothing is copied; the block counts as masked
+                st_mbar_arrive(fb);
+                return;
+            }
+            st_mbar_expect_tx(fb, 2u * cnt * row_bytes);
+            const uint32_t kd = ring + st * stage_bytes, vd = kd + STREAM_KEYS * row_bytes;
+            for (int j = j0; j < j0 + cnt;) {
+                const int off = j % a.page_size;
+                const int n = min(a.page_size - off, j0 + cnt - j);
+                const int page = sh_pages[j / a.page_size - first_page];
+                const size_t row = (((size_t)page * a.kv_heads + hk) * a.page_size + off) * a.head_dim;
+                st_bulk_copy(kd + (j - j0) * row_bytes, a.k_pages + row, n * row_bytes, fb);
+                st_bulk_copy(vd + (j - j0) * row_bytes, a.v_pages + row, n * row_bytes, fb);
+                j += n;
+            }
+        };
+        int issued = 0;
+        if (threadIdx.x == 0)
+            for (; issued < STREAM_STAGES && issued < n_blk; ++issued) issue(issued);
+        bool ok = true;
+        int blk = 0;
+        for (; blk < n_blk && ok; ++blk) {
+            const int st = blk % STREAM_STAGES;
+            // the stage of the block before is free once all warps have passed it: refill it
+            if (threadIdx.x == 0 && blk >= 1 && issued < n_blk) {
+                const int prev = (blk - 1) % STREAM_STAGES;
+                if (st_mbar_wait(st_smem(&stream->empty[prev]), ((blk - 1) / STREAM_STAGES) & 1, failed)) {
+                    issue(issued);
+                    ++issued;
+                }
+            }
+            ok = st_mbar_wait(st_smem(&stream->full[st]), (blk / STREAM_STAGES) & 1, failed);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            const bool bad = stream->bad[st] != 0;
+            const int j0 = k_begin + blk * STREAM_KEYS;
+            const uint32_t kd = ring + st * stage_bytes, vd = kd + STREAM_KEYS * row_bytes;
+#pragma unroll
+            for (int u = 0; u < STREAM_KEYS / (NW * KPW); ++u) {
+                const int jj = u * NW * KPW + warp * KPW + kslot;      // key within the block
+                const bool key_ok = j0 + jj < k_end && !bad;
+                uint4 kk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+                if (key_ok && piece_ok) {
+                    kk = st_ld_shared_v4(kd + jj * row_bytes + sub * 16);
+                    vv = st_ld_shared_v4(vd + jj * row_bytes + sub * 16);
+                }
+                score_key(kk, vv, key_ok);
+            }
+            if (blk == 0 && m != 1234.5f) { DEC_TRACE(2); }
+            __syncwarp();
+            if (lane == 0) st_mbar_arrive(st_smem(&stream->empty[st]));
+        }
+        if (!ok && lane == 0) prb_set_status(a.status, PRB_S_WAIT_TIMEOUT, 31, idx, blk);
+        __syncthreads();
+        if (threadIdx.x == 0 && *failed) {
+            // wait (bounded) for the copies still in flight before the CTA may leave
+            for (int b2 = blk; b2 < issued; ++b2) {
+                const uint32_t fb = st_smem(&stream->full[b2 % STREAM_STAGES]);
+                for (uint32_t i = 0; i < STREAM_WAIT_LIMIT; ++i)
+                    if (st_mbar_try_wait(fb, (b2 / STREAM_STAGES) & 1)) break;
+            }
+        }
+    } else {
         Batch b0, b1;
         int base = k_begin + warp * KPW;           // the same for the whole warp
         load(base, b0);

@@ -148,6 +148,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_attention_prefill_tc_supports.argtypes = [I, I]
     h.prb_attention_prefill_tc_tile.argtypes = []
     h.prb_attention_decode_split.argtypes = []
+    h.prb_attention_decode_set_stream.argtypes = [I]
+    h.prb_attention_decode_set_stream.restype = None
     h.prb_set_pdl.argtypes = [I]
     h.prb_set_pdl.restype = None
     h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
@@ -566,6 +568,13 @@ def attention_generic(out, q, k_pages, v_pages, block_table, seq_of_token, posit
 def decode_split() -> int:
     """Keys per split of the decode attention kernel."""
     return lib().prb_attention_decode_split()
+
+
+def decode_stream(mode: int) -> None:
+    """Which key loop the decode attention kernel runs (for tests and measurements): -1 the
+    kernel's own choice, 0 register batches always, 1 the shared-memory ring wherever it
+    applies (no window, head size up to 128)."""
+    lib().prb_attention_decode_set_stream(int(mode))
 
 
 def prefill_supports(head_dim: int) -> bool:

@@ -231,6 +231,39 @@ def test_attention_decode(nh, nkv, dh, ps, window, split_keys):
     assert float(out[3].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("nh,nkv,dh,ps", [(12, 12, 64, 64), (3, 1, 48, 16), (4, 2, 128, 32),
+                                          (2, 2, 16, 128), (5, 5, 80, 8)])
+@pytest.mark.parametrize("split_keys", [128, 512, 1024])
+def test_attention_decode_streaming_variant_gives_the_same_bits(nh, nkv, dh, ps, split_keys):
+    """Keys through the shared-memory ring (bulk copies of page runs) or through register
+    batches: the same keys reach the same lanes in the same order, so the outputs are equal
+    bit for bit; both agree with the plain reference."""
+    ops = _ops()
+    lengths, portions = [1, 64, 65, 300, 1000, 1024, 513], [1, 1, 2, 1, 3, 1, 1]
+    q, k, v, table, seq, pos = _paged_case(6, nh, nkv, dh, ps, lengths, portions, torch.bfloat16)
+    t = q.shape[0]
+    splits = -(-1024 // split_keys)
+    ws = torch.full((t * nh * splits * (dh + 4),), float("nan"), device="cuda")
+    counters = torch.zeros(t * nh, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ref = _ref_attention(q, k, v, table, seq, pos, nh, 0.2, None)
+    outs = []
+    try:
+        for mode in (0, 1, 1):
+            ops.decode_stream(mode)
+            out = torch.full_like(q, float("nan"))
+            ops.attention_decode(out, q, k, v, table, seq, pos, None, None, t, nh, 0.2, None, ws,
+                                 counters, splits, status, split_keys=split_keys)
+            torch.cuda.synchronize()
+            assert status.tolist() == [0, 0, 0, 0]
+            assert int(counters.abs().sum()) == 0
+            outs.append(out)
+    finally:
+        ops.decode_stream(-1)
+    assert float((outs[0].float() - ref).abs().max()) <= 2e-2
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+
+
 def _prefill_parts(units, most):
     """Workspace of the tensor-memory prompt kernel's key parts."""
     return (torch.empty(units * most * 8192, device="cuda"),
