@@ -177,7 +177,8 @@ def chain_hash(parent: bytes, tokens: Sequence[int]) -> bytes:
 class CacheManager:
     def __init__(self, groups: Sequence[GroupSpec], page_size: int,
                  num_pages: Sequence[int] | int, num_slots: int,
-                 max_positions: int, share_prefixes: bool = False):
+                 max_positions: int, share_prefixes: bool = False, has_state: bool = False,
+                 copy_state=None):
         if page_size <= 0:
             raise CacheError("page_size must be positive")
         self.groups = list(groups)
@@ -189,8 +190,15 @@ class CacheManager:
         self.max_positions = max_positions
         self.max_pages_per_request = -(-max_positions // page_size)
         self.requests: Dict[Hashable, _Request] = {}
-        # Sharing full prompt pages needs every group to keep all its pages.
-        self.share_prefixes = share_prefixes and all(g.window is None for g in self.groups)
+        # Sharing full prompt pages needs every group to keep all its pages, and a model
+        # without fixed-size state per request: a request that takes over shared pages skips
+        # their tokens, so a part that keeps a state would never see them
+        # (``doc/serving-architecture.md:76-79``: per-request state is no reusable attention
+        # state).
+        self.has_state = bool(has_state)
+        self.copy_state = copy_state           # (source slot, destination slot) -> None
+        self.share_prefixes = share_prefixes and not self.has_state and \
+            all(g.window is None for g in self.groups)
         # chain hash -> (pages per group, tokens of that page); LRU order.
         self._index: "OrderedDict[bytes, Tuple[Tuple[int, ...], Tuple[int, ...]]]" = OrderedDict()
         self.stats = {"allocated": 0, "released": 0, "window_released": 0, "cow_copies": 0,
@@ -273,8 +281,19 @@ class CacheManager:
         for g in self.groups:
             if self._first_live_page(g, length) < self._first_live_page(g, src.length):
                 raise CacheError("fork point lies before a page the window already released")
+        if self.has_state and length > 0:
+            # the state slot holds the state after the source's last token and no other
+            if length != src.length:
+                raise CacheError(
+                    f"the model keeps per-request state: request {source!r} can be forked at its "
+                    f"present length {src.length} only, not at {length}")
+            if self.copy_state is None:
+                raise CacheError("the model keeps per-request state and no state copy was given: "
+                                 "it cannot be forked")
         slot = self.open(rid)
         req = self.requests[rid]
+        if self.has_state and length > 0:
+            self.copy_state(src.slot, slot)
         req.fresh = False if length > 0 else True
         n_pages = -(-length // self.page_size)
         for gi in range(len(self.groups)):

@@ -41,6 +41,12 @@ class CacheStorage:
         """Copy-on-write: page pairs[i,0] -> pairs[i,1] in every pool of the group."""
         ops.copy_pages(self.kv[group], pairs, n_pairs, status)
 
+    def copy_state(self, src_slot: int, dst_slot: int) -> None:
+        """Every state tensor's row of ``src_slot`` -> row of ``dst_slot`` (a fork takes the
+        source's state as it is now), on the current stream."""
+        for t in self.state.values():
+            t[dst_slot].copy_(t[src_slot])
+
     def bytes(self) -> int:
         total = sum(t.numel() * t.element_size() for t in self.kv)
         return total + sum(t.numel() * t.element_size() for t in self.state.values())

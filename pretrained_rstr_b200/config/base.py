@@ -43,14 +43,17 @@ class LayerSpec:
 
     ``prefix`` is the tensor-name prefix of the layer's weights (``"h.3."``).
     ``arrangement`` names a registered block arrangement (``"pre_norm"``).
+    ``norms`` are the layer's norms by the names its arrangement asks for: ``pre_norm``
+    wants ``"mixer"`` and ``"feed_forward"``; a block with sandwich norms would name four,
+    a parallel block one.  ``width`` is the width of the residual stream.
     """
 
     prefix: str
     arrangement: str
     mixer: PartSpec
     feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    norms: Dict[str, PartSpec]
+    width: int
 
 
 @dataclass(frozen=True)

@@ -135,8 +135,9 @@ class GPT2Config(ModelConfig):
                     "bias": True,
                     "weight_layout": "in_out",
                 }),
-                mixer_norm=PartSpec("layer_norm", {"weights": p + "ln_1", **norm}),
-                feed_forward_norm=PartSpec("layer_norm", {"weights": p + "ln_2", **norm}),
+                norms={"mixer": PartSpec("layer_norm", {"weights": p + "ln_1", **norm}),
+                       "feed_forward": PartSpec("layer_norm", {"weights": p + "ln_2", **norm})},
+                width=self.n_embd,
             ))
         return specs
 

@@ -32,6 +32,8 @@ class Architecture:
     strip_prefixes: Tuple[str, ...] = ()
     #: ``ignorable(name) -> bool``: tensors that may be present without being parameters
     ignorable: Callable[[str], bool] = lambda name: False
+    #: named sizes for random-weight models: name -> raw ``config.json`` dict
+    named_sizes: Dict[str, Dict[str, Any]] = None
 
 
 _REGISTRY: Dict[str, Architecture] = {}
@@ -83,6 +85,25 @@ def lookup(raw: Dict[str, Any]) -> Architecture:
     raise ConfigError(
         f"No architecture registered for {keys or '<no architectures/model_type key>'}; "
         f"known: {sorted(_REGISTRY)}")
+
+
+def named_sizes() -> Dict[str, Dict[str, Any]]:
+    """Every named size of every registered architecture: name -> raw ``config.json`` dict
+    (with its ``architectures`` key), for models made from a size's name and a seed."""
+    _ensure_bundled()
+    out: Dict[str, Dict[str, Any]] = {}
+    for arch in {id(a): a for a in _REGISTRY.values()}.values():
+        for name, raw in (arch.named_sizes or {}).items():
+            out[name] = dict(raw)
+    return out
+
+
+def named_size(name: str) -> Tuple[Architecture, ModelConfig]:
+    sizes = named_sizes()
+    if name not in sizes:
+        raise ConfigError(f"no size named {name!r}; known: {sorted(sizes)}")
+    arch = lookup(sizes[name])
+    return arch, arch.config_class.from_dict(sizes[name])
 
 
 def read_config(folder: str) -> Tuple[Architecture, ModelConfig]:

@@ -27,6 +27,7 @@ __device__ unsigned long long g_dec_trace[4096 * 8];
     } while (0)
 #endif
 #include <cstdlib>
+#include <mutex>
 #include "attention_decode.cuh"
 
 namespace {
@@ -98,6 +99,7 @@ cudaError_t launch_decode(K kernel, dim3 grid, int cluster_z, cudaStream_t strea
 }  // namespace
 
 PRB_API int prb_attention_decode_split() { return SPLIT; }
+PRB_API int prb_attention_decode_max_split_pages() { return MAX_SPLIT_PAGES; }
 
 // Switch (for measurements): 0 = splits always merge through the workspace.
 // Switch (for measurements): -1 = the streaming variant where it is chosen, 0 = never,
@@ -149,7 +151,7 @@ PRB_API int prb_attention_decode(void* out, long out_stride, const void* q, long
     a.split = split_keys; a.status = status;
     // more CTAs than fit at four per SM: the leaner instance, six per SM; two to eight
     // splits: the CTAs of a (token, head) form a cluster and merge through shared memory
-    const bool many = (long)n_list * n_heads * max_splits > 4L * 148;
+    const bool many = (long)n_list * n_heads * max_splits > 4L * prb_sm_count();
     const bool cluster = max_splits >= 2 && max_splits <= 8 && prb_decode_clusters();
 #define PRB_DEC(L)                                                                               \
     do {                                                                                         \
@@ -240,6 +242,7 @@ struct NoAllocDevice {
     int* counters = nullptr;
 };
 NoAllocDevice noalloc_devices[NOALLOC_MAX_DEVICES];
+std::mutex noalloc_setup_lock;          // two host threads may make the first call together
 }  // namespace
 
 // Largest sizes the entry point takes: floats of workspace (n_list * n_heads * max_splits
@@ -270,16 +273,19 @@ PRB_API int prb_attention_decode_noalloc(void* out, long out_stride, const void*
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return PRB_E_ARG;
     NoAllocDevice& d = noalloc_devices[dev];
-    if (!d.ready) {
-        // once per device, with that device current: the device addresses of the arrays
-        void* p = nullptr;
-        e = cudaGetSymbolAddress(&p, noalloc_workspace);
-        if (e != cudaSuccess) return (int)e;
-        d.workspace = static_cast<float*>(p);
-        e = cudaGetSymbolAddress(&p, noalloc_counters);
-        if (e != cudaSuccess) return (int)e;
-        d.counters = static_cast<int*>(p);
-        d.ready = true;
+    {
+        std::lock_guard<std::mutex> guard(noalloc_setup_lock);
+        if (!d.ready) {
+            // once per device, with that device current: the device addresses of the arrays
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, noalloc_workspace);
+            if (e != cudaSuccess) return (int)e;
+            d.workspace = static_cast<float*>(p);
+            e = cudaGetSymbolAddress(&p, noalloc_counters);
+            if (e != cudaSuccess) return (int)e;
+            d.counters = static_cast<int*>(p);
+            d.ready = true;
+        }
     }
     // the counters must start at zero, whatever an earlier call left behind
     e = cudaMemsetAsync(d.counters, 0, (size_t)need_counters * sizeof(int), stream);

@@ -122,6 +122,10 @@ __device__ __forceinline__ void prb_grid_launch_dependents() {
 }
 int prb_pdl_enabled();
 
+// Streaming multiprocessors of the current device (asked once per device); every heuristic
+// that sizes a grid or counts waves takes the number from here.
+int prb_sm_count();
+
 // Kernels of many small CTAs (norms, attention) are not placed early: their CTAs would fill
 // the few SMs that the predecessor leaves free, several to an SM, instead of spreading
 // over all of them when it has ended, and then run at the pace of those SMs (measured: a

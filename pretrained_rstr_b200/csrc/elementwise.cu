@@ -8,6 +8,19 @@
 static int g_pdl = 1;
 int prb_pdl_enabled() { return g_pdl; }
 PRB_API void prb_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+int prb_sm_count() {
+    static int counts[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+    if (counts[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 1;
+        counts[dev] = n;
+    }
+    return counts[dev];
+}
+PRB_API int prb_device_sm_count() { return prb_sm_count(); }
 int prb_small_ctas_early() {
     static const int on = [] { const char* e = getenv("PRB200_EARLY_SMALL"); return e ? atoi(e) : 0; }();
     return on;

@@ -339,18 +339,19 @@ PRB_API int prb_gemm_midm(void* c, const void* a, const void* w, const float* bi
     // SM with 64-column tiles, two with 32-column tiles); within that, the split that gives
     // an SM the fewest bytes to take in (its CTAs' slices of A and W) wins.
     const int slabs = k / 64;
+    const int sms = prb_sm_count();
     int nb = 32, splits = 1;
     long best = -1;
     for (int cand = 64; cand >= 32; cand /= 2) {
         const int tiles = (n + cand - 1) / cand;
-        const int slots = 148 * (cand == 64 ? 1 : 2);
+        const int slots = sms * (cand == 64 ? 1 : 2);
         int s = slots / tiles;
         if (s > 8) s = 8;
         if (s > slabs / 2) s = slabs / 2;
         if (s < 1) s = 1;
         const long per_cta = (long)(MROWS + cand) * 2 * ((long)k / s);
         const long ctas = (long)tiles * s;
-        const long per_sm = per_cta * ((ctas + 147) / 148);
+        const long per_sm = per_cta * ((ctas + sms - 1) / sms);
         if (best < 0 || per_sm < best) { best = per_sm; nb = cand; splits = s; }
     }
     CUtensorMap ma, mw;

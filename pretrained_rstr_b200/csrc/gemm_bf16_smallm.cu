@@ -98,16 +98,7 @@ struct Plan {
 // shared-memory budget of a CTA in KB.
 int g_tune[5] = {0, 0, 0, 0, 0};   // [4]: ring buffers filled before the wait on the previous kernel
 
-inline int sm_count() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
-    }
-    return sms;
-}
+inline int sm_count() { return prb_sm_count(); }
 
 __host__ __device__ inline size_t stage_size(int mp, bool ln, int kc) {
     return (size_t)(kc / 64) * (ROWS * 128 + (ln ? 0 : mp * 128));

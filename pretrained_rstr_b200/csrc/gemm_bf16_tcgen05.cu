@@ -640,14 +640,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, O* c, const float* bias
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-            sm_count <= 0)
-            sm_count = 148;
-    }
+    const int sm_count = prb_sm_count();
     const long tiles = (long)((n + BN - 1) / BN) * ((m + BM - 1) / BM);
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
     cudaError_t le = prb_launch_dependent(gemm_bf16_kernel<BN, O>, dim3(grid), dim3(GEMM_THREADS),
@@ -713,9 +706,10 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
         const long kb = (k + BK - 1) / BK;
         const long per_col = out_dtype == PRB_F32 ? 23 : 12;
         long best = -1;
+        const long sms = prb_sm_count();
         for (int bn = 256; bn >= 32; bn -= 32) {
             const long tiles = mt * ((n + bn - 1) / bn);
-            const long rounds = (tiles + 147) / 148;
+            const long rounds = (tiles + sms - 1) / sms;
             const long main_loop = kb * (128 + bn) + 400, epilogue = per_col * bn;
             const long cost = (rounds - 1) * (main_loop > epilogue ? main_loop : epilogue) +
                               main_loop + epilogue;
@@ -730,7 +724,7 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
                 const long tiles = mt * ((n + bn - 1) / bn);
                 for (int sp = 2; sp <= 8; sp *= 2) {
                     const long per = (kb + sp - 1) / sp;
-                    if (tiles * sp > 148 || per * (sp - 1) >= kb || per < 2) continue;
+                    if (tiles * sp > sms || per * (sp - 1) >= kb || per < 2) continue;
                     const long cost = per * (128 + bn) + 400 + 700 + per_col * bn / 2;
                     if (cost < best) { best = cost; tile_n = bn; split = sp; }
                 }

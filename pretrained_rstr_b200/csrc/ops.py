@@ -148,6 +148,10 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_attention_prefill_tc_supports.argtypes = [I, I]
     h.prb_attention_prefill_tc_tile.argtypes = []
     h.prb_attention_decode_split.argtypes = []
+    h.prb_attention_decode_max_split_pages.argtypes = []
+    h.prb_attention_decode_max_split_pages.restype = c_int
+    h.prb_device_sm_count.argtypes = []
+    h.prb_device_sm_count.restype = c_int
     h.prb_attention_decode_set_stream.argtypes = [I]
     h.prb_attention_decode_set_stream.restype = None
     h.prb_set_pdl.argtypes = [I]
@@ -563,6 +567,22 @@ def attention_generic(out, q, k_pages, v_pages, block_table, seq_of_token, posit
         _p(seq_of_token), _p(positions), n_tokens, n_heads, kv_heads, head_dim, page_size,
         block_table.shape[1], num_pages, max_context, float(scale), int(window or 0),
         dtype_code(k_pages.dtype), _p(status), _stream()), what)
+
+
+_SM_COUNT = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device."""
+    global _SM_COUNT
+    if _SM_COUNT is None:
+        _SM_COUNT = max(1, int(lib().prb_device_sm_count()))
+    return _SM_COUNT
+
+
+def decode_max_split_pages() -> int:
+    """Most pages one split of the decode attention kernel may span."""
+    return lib().prb_attention_decode_max_split_pages()
 
 
 def decode_split() -> int:

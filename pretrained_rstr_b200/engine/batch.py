@@ -22,8 +22,43 @@ import numpy as np
 import torch
 
 
-ATTENTION_TILE = 128     # queries per work item of the prompt attention kernels
-SINGLE_MAX_Q = 4         # portions up to this many tokens are attended token by token
+class WorkPlanner:
+    """Work lists a part wants in the description of every step.
+
+    The step's description knows requests, tokens, positions and cache slots; how a part's
+    kernels cut that into work items (tiles of queries, lists of single tokens, groups of
+    tokens per expert, ...) is the part's own business.  A part that needs such lists
+    returns planners from ``work_planners()``; the model gathers them (one per ``key``),
+    the layout gives their arrays room in the step's one int32 buffer, and
+    :func:`fill_host_buffer` lets them write their lists for every step.  Parts find the
+    device views in ``ctx.work[key]`` (a :class:`WorkView`).
+    """
+
+    #: name under which parts find the lists in ``ctx.work``
+    key: str = ""
+    #: names of the counters (one int32 each on the device, beside the arrays)
+    counters: Tuple[str, ...] = ()
+
+    def arrays(self, t_cap: int, b_cap: int) -> Dict[str, Tuple[int, int]]:
+        """array name -> (capacity in int32 words, value of unused entries) for a layout of
+        ``t_cap`` tokens and ``b_cap`` requests."""
+        raise NotImplementedError
+
+    def fill(self, arrays: Dict[str, np.ndarray], lengths: Sequence[int]) -> Dict[str, int]:
+        """Write the lists of a step whose requests bring ``lengths[b]`` tokens each (token
+        rows are concatenated in request order); returns the counters."""
+        raise NotImplementedError
+
+
+@dataclass
+class WorkView:
+    """One planner's lists as a part sees them in a step."""
+    arrays: Dict[str, torch.Tensor]            # device int32 views
+    counts: Dict[str, torch.Tensor]            # device views of one int32 each
+    caps: Dict[str, int]                       # capacity of every array
+    #: the counters as the host knows them; None while a step is replayed from a CUDA graph
+    #: (kernels then take the capacity as their grid and the device-side counter as the bound)
+    host_counts: Dict[str, Optional[int]]
 
 
 @dataclass
@@ -54,8 +89,10 @@ class Runtime:
 class BatchLayout:
     """Offsets (in int32 words) of every array for given capacities."""
 
-    def __init__(self, t_cap: int, b_cap: int, n_groups: int, max_pages: int):
+    def __init__(self, t_cap: int, b_cap: int, n_groups: int, max_pages: int,
+                 planners: Sequence[WorkPlanner] = ()):
         self.t_cap, self.b_cap, self.n_groups, self.max_pages = t_cap, b_cap, n_groups, max_pages
+        self.planners = tuple(planners)
         off = 0
 
         def take(n: int) -> int:
@@ -77,17 +114,25 @@ class BatchLayout:
         self.slots = [take(t_cap) for _ in range(n_groups)]
         self.first_pos = [take(b_cap) for _ in range(n_groups)]
         self.block_table = [take(b_cap * max_pages) for _ in range(n_groups)]
-        # work lists of the attention kernels: 64-query tiles of prompt portions, and single
-        # tokens (decoded tokens and very short portions); counts live on the device too
-        self.tile_cap = t_cap // ATTENTION_TILE + b_cap
-        self.tile_req = take(self.tile_cap)
-        self.tile_row0 = take(self.tile_cap)
-        self.tile_rows = take(self.tile_cap)
-        self.single_cap = min(t_cap, b_cap * SINGLE_MAX_Q)
-        self.single_tokens = take(self.single_cap)
-        self.counts = take(4)                 # [tiles, singles, tokens, requests]
+        # work lists of the parts that asked for some (see WorkPlanner): arrays, and counters
+        # that live on the device too
+        self.work_arrays: Dict[str, Dict[str, Tuple[int, int, int]]] = {}   # key -> name -> (offset, words, fill)
+        for planner in self.planners:
+            self.work_arrays[planner.key] = {
+                name: (take(words), words, fill)
+                for name, (words, fill) in planner.arrays(t_cap, b_cap).items()}
+        n_counters = sum(len(p.counters) for p in self.planners)
+        self.counts = take(2 + n_counters)    # [tokens, requests, planners' counters ...]
+        self.work_counts: Dict[str, Dict[str, int]] = {}
+        at = self.counts + 2
+        for planner in self.planners:
+            self.work_counts[planner.key] = {}
+            for name in planner.counters:
+                self.work_counts[planner.key][name] = at
+                at += 1
         self.size = off
         self._views = None
+        self._work_views = None
 
     def device_views(self, buf: torch.Tensor):
         if self._views is None:
@@ -101,12 +146,19 @@ class BatchLayout:
                 buf[lay.kv_len:lay.kv_len + lay.b_cap],
                 buf[lay.state_slot:lay.state_slot + lay.b_cap],
                 buf[lay.fresh:lay.fresh + lay.b_cap],
-                buf[lay.tile_req:lay.tile_req + lay.tile_cap],
-                buf[lay.tile_row0:lay.tile_row0 + lay.tile_cap],
-                buf[lay.tile_rows:lay.tile_rows + lay.tile_cap],
-                buf[lay.single_tokens:lay.single_tokens + lay.single_cap],
-                buf[lay.counts:lay.counts + 4])
+                buf[lay.counts:lay.counts + 2])
         return self._views
+
+    def work_views(self, buf: torch.Tensor):
+        """Per planner: (array views, counter views, capacities), made once per layout."""
+        if self._work_views is None:
+            out = {}
+            for key, arrays in self.work_arrays.items():
+                out[key] = ({name: buf[off:off + words] for name, (off, words, _f) in arrays.items()},
+                            {name: buf[off:off + 1] for name, off in self.work_counts[key].items()},
+                            {name: words for name, (_o, words, _f) in arrays.items()})
+            self._work_views = out
+        return self._work_views
 
 
 @dataclass
@@ -157,12 +209,11 @@ class StepContext:
         # device views of the step's arrays: made once per layout, their addresses never change
         views = layout.device_views(device_buf)
         (self.tokens, self.positions, self.seq_of_token, self.logit_rows, self.q_start,
-         self.kv_len, self.state_slot, self.fresh, self.tile_req, self.tile_row0, self.tile_rows,
-         self.single_tokens, self.counts) = views
-        # host-side counts of the work lists (None when the step is replayed from a graph
-        # and only the device-side counts are valid)
-        self.n_tiles: Optional[int] = None
-        self.n_singles: Optional[int] = None
+         self.kv_len, self.state_slot, self.fresh, self.counts) = views
+        # the parts' own work lists; the host-side counters are filled in by the runner
+        self.work: Dict[str, WorkView] = {
+            key: WorkView(arrays, counts, caps, {name: None for name in counts})
+            for key, (arrays, counts, caps) in layout.work_views(device_buf).items()}
         self.feedback = False               # token ids below zero name tokens chosen last
 
     @property
@@ -192,12 +243,6 @@ class StepContext:
         (counters that their kernel resets)."""
         return self._scratch.get(key, shape, dtype, zero=True)
 
-    @property
-    def max_splits_cap(self) -> int:
-        """Upper bound of the decode attention kernel's key splits for any request."""
-        from ..csrc import ops
-        return -(-self.max_positions // ops.decode_split())
-
 
 class ScratchPool:
     def __init__(self, device: torch.device):
@@ -221,9 +266,9 @@ class ScratchPool:
 def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: List[List[int]],
                      start_pos: List[int], state_slots: List[int], fresh: List[bool],
                      group_slots: List[List[List[int]]], group_tables: List[List[List[int]]],
-                     group_first: List[List[int]], logit_rows: List[int]) -> Tuple[int, int]:
-    """Write one step into the pinned host buffer.  Returns the lengths of the attention
-    work lists (tiles, single tokens)."""
+                     group_first: List[List[int]], logit_rows: List[int]) -> Dict[str, Dict[str, int]]:
+    """Write one step into the pinned host buffer.  Returns the counters of the parts' work
+    lists, by planner key and counter name."""
     lay = layout
     n_req = len(entries_tokens)
     t = 0
@@ -272,28 +317,19 @@ def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: L
         for b in range(n_req):
             table = group_tables[g][b]
             bt2[b, :len(table)] = table
-    # attention work lists
-    treq = host_np[lay.tile_req:lay.tile_req + lay.tile_cap]
-    trow = host_np[lay.tile_row0:lay.tile_row0 + lay.tile_cap]
-    tnum = host_np[lay.tile_rows:lay.tile_rows + lay.tile_cap]
-    sing = host_np[lay.single_tokens:lay.single_tokens + lay.single_cap]
-    n_tiles = n_sing = 0
-    t = 0
-    for b, toks in enumerate(entries_tokens):
-        n = len(toks)
-        if n <= SINGLE_MAX_Q:
-            sing[n_sing:n_sing + n] = np.arange(t, t + n, dtype=np.int32)
-            n_sing += n
-        else:
-            for r0 in range(0, n, ATTENTION_TILE):
-                treq[n_tiles] = b
-                trow[n_tiles] = t + r0
-                tnum[n_tiles] = min(ATTENTION_TILE, n - r0)
-                n_tiles += 1
-        t += n
-    treq[n_tiles:] = -1
-    trow[n_tiles:] = 0
-    tnum[n_tiles:] = 0
-    sing[n_sing:] = 0
-    host_np[lay.counts:lay.counts + 4] = (n_tiles, n_sing, n_tok, n_req)
-    return n_tiles, n_sing
+    # the parts' work lists
+    lengths = [len(toks) for toks in entries_tokens]
+    counts: Dict[str, Dict[str, int]] = {}
+    at = lay.counts + 2
+    for planner in lay.planners:
+        views = {}
+        for name, (off, words, fill) in lay.work_arrays[planner.key].items():
+            views[name] = host_np[off:off + words]
+            views[name][:] = fill              # entries the planner leaves unused
+        got = planner.fill(views, lengths)
+        counts[planner.key] = {name: int(got[name]) for name in planner.counters}
+        for name in planner.counters:
+            host_np[at] = counts[planner.key][name]
+            at += 1
+    host_np[lay.counts:lay.counts + 2] = (n_tok, n_req)
+    return counts

@@ -3,6 +3,9 @@ from ``config.json`` through the registry, weights by name, parts, cache, runner
 The path of the reference's ``from-pretrained`` (``src/pretrained/loader.clj:80-97``)."""
 from __future__ import annotations
 
+import contextlib
+import shutil
+import tempfile
 from dataclasses import dataclass
 from typing import Optional
 
@@ -12,23 +15,13 @@ from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage
 from ..config.registry import read_config
 from ..csrc import ops
+from ..settings import SETTINGS
 from ..weights.loader import load_weights
 from .batch import Runtime
 from .runner import ModelRunner
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
            "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
-
-
-def _env_flag(name: str, default: bool) -> bool:
-    """Measurement switches: PRB200_GRAPHS=0 launches small steps kernel by kernel,
-    PRB200_PROGRAMS=1 runs decode-only steps as one persistent kernel, PRB200_PDL=0
-    switches programmatic dependent launch off."""
-    import os
-    value = os.environ.get(name)
-    if value is None:
-        return default
-    return value.strip().lower() not in ("0", "false", "no", "off", "")
 
 
 def parse_dtype(dtype) -> torch.dtype:
@@ -40,6 +33,22 @@ def parse_dtype(dtype) -> torch.dtype:
         return _DTYPES[str(dtype)]
     except KeyError:
         raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, got {dtype!r}") from None
+
+
+@contextlib.contextmanager
+def random_model_folder(size: str, seed: int, dtype="bfloat16"):
+    """A temporary model folder of a named size with seeded random weights, stored in the
+    element type it will run in; removed when the block ends (the weights are on the device
+    by then)."""
+    from ..config.registry import named_size
+    from ..weights.loader import make_random_model
+    _arch, config = named_size(size)
+    folder = tempfile.mkdtemp(prefix="prb200_random_")
+    try:
+        make_random_model(folder, config, int(seed), parse_dtype(dtype))
+        yield folder
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
 
 
 @dataclass
@@ -63,15 +72,14 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0", page_size: int = 
     ``max_requests`` requests of full length."""
     ops.require_cuda()
     ops.lib()                                   # build / load now, fail loudly here
-    ops.set_pdl(_env_flag("PRB200_PDL", True))
+    ops.set_pdl(SETTINGS.pdl)
     dtype = parse_dtype(dtype)
     device = torch.device(device)
     torch.cuda.set_device(device)
     arch, config = read_config(folder)
     runtime = Runtime(device=device, dtype=dtype, page_size=page_size,
                       max_batched_tokens=max_batched_tokens, max_requests=max_requests,
-                      use_graphs=_env_flag("PRB200_GRAPHS", True),
-                      use_programs=_env_flag("PRB200_PROGRAMS", False))
+                      use_graphs=SETTINGS.graphs, use_programs=SETTINGS.programs)
     store = load_weights(folder, arch.expected_tensors(config), device,
                          strip_prefixes=arch.strip_prefixes, ignorable=arch.ignorable)
     model = arch.build(config, store, runtime)
@@ -81,9 +89,12 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0", page_size: int = 
             max_tokens = max_requests * (-(-config.max_positions // page_size) * page_size)
         num_pages = max(1, -(-max_tokens // page_size))
     pages = [num_pages] * len(model.group_specs)
-    cache = CacheManager(model.group_specs, page_size, pages if pages else 1, max_requests,
-                         config.max_positions, share_prefixes=share_prefixes)
     storage = CacheStorage(model.group_specs, pages, page_size, dtype, device,
                            model.state_specs, max_requests)
+    # A model whose parts keep state of fixed size per request cannot skip shared prompt
+    # tokens (their state updates would never run), and a fork has to copy the state rows.
+    cache = CacheManager(model.group_specs, page_size, pages if pages else 1, max_requests,
+                         config.max_positions, share_prefixes=share_prefixes,
+                         has_state=bool(model.state_specs), copy_state=storage.copy_state)
     runner = ModelRunner(model, runtime, cache, storage)
     return LoadedModel(folder, arch, config, runtime, model, cache, storage, runner)

@@ -49,8 +49,9 @@ class ModelRunner:
         self.max_pages = cache.max_pages_per_request
         self._layouts: Dict[tuple, BatchLayout] = {}
         self._group_views: Dict[int, list] = {}
+        self.planners = tuple(getattr(model, "planners", ()))
         biggest = BatchLayout(runtime.max_batched_tokens, runtime.max_requests, self.n_groups,
-                              self.max_pages)
+                              self.max_pages, self.planners)
         # two pinned staging buffers, used in turn, each guarded by an event
         self._hosts = [torch.empty(biggest.size, dtype=torch.int32, pin_memory=True)
                        for _ in range(2)]
@@ -96,7 +97,7 @@ class ModelRunner:
                _bucket(n_requests, 1, self.runtime.max_requests))
         lay = self._layouts.get(key)
         if lay is None:
-            lay = BatchLayout(key[0], key[1], self.n_groups, self.max_pages)
+            lay = BatchLayout(key[0], key[1], self.n_groups, self.max_pages, self.planners)
             self._layouts[key] = lay
         return lay
 
@@ -146,22 +147,23 @@ class ModelRunner:
         kernel lets touch the cache.  The first step of a shape runs directly with the
         padded sizes (which also sizes all scratch memory), the second is captured."""
         lay = ctx.layout
-        has_tiles, has_singles = bool(ctx.n_tiles), bool(ctx.n_singles)
-        if self.use_programs and not has_tiles and lay.t_cap <= ops.smallm_limits()[0]:
-            counts = (ctx.n_tiles, ctx.n_singles)
-            logits = self._run_program(ctx)
+        # which of the parts' work lists hold something: a step without prompt tiles (or
+        # without single tokens) gets a graph without the kernels of that list, since an idle
+        # launch per layer is a tenth of a small decode step
+        filled = tuple(bool(c) for view in ctx.work.values() for c in view.host_counts.values())
+        if self.use_programs and lay.t_cap <= ops.smallm_limits()[0]:
+            saved = [dict(view.host_counts) for view in ctx.work.values()]
+            logits = self._run_program(ctx, filled)
             if logits is not None:
                 return logits
-            ctx.n_tiles, ctx.n_singles = counts
+            for view, counts in zip(ctx.work.values(), saved):
+                view.host_counts = counts
         if not self.use_graphs or lay.t_cap > self.graph_max_tokens:
             return self.model.forward(ctx)
         rows_cap = StepContext.row_capacity(max(ctx.n_rows, 1)) if ctx.n_rows else 0
-        # a step without prompt tiles (or without single tokens) gets a graph without that
-        # attention kernel: an idle launch per layer is a tenth of a small decode step
-        key = (lay.t_cap, lay.b_cap, rows_cap, has_tiles, has_singles)
+        key = (lay.t_cap, lay.b_cap, rows_cap, filled)
         ctx.launch_tokens, ctx.launch_rows = lay.t_cap, rows_cap
-        ctx.n_tiles = None if has_tiles else 0      # None: kernels read the device-side counts
-        ctx.n_singles = None if has_singles else 0
+        self._counts_from_device(ctx)
         ctx.max_context = self.model.max_positions
         hit = self._graphs.get(key)
         if hit is not None:
@@ -182,6 +184,14 @@ class ModelRunner:
         graph.replay()
         ops.add_launches(kernels)
         return logits
+
+    @staticmethod
+    def _counts_from_device(ctx: StepContext) -> None:
+        """For a step that is recorded or replayed: a work list that holds something is run
+        at its capacity with the device-side counter as the bound (None), an empty one not
+        at all (0)."""
+        for view in ctx.work.values():
+            view.host_counts = {name: (None if c else 0) for name, c in view.host_counts.items()}
 
     def prepare(self, entries: Sequence[Entry], feedback: bool = False) -> StepContext:
         """First half of a step: validate the batch, reserve cache slots, and describe the
@@ -255,8 +265,9 @@ class ModelRunner:
         self._host_turn ^= 1
         self._host_events[turn].synchronize()        # the copy that last used this buffer is done
         staging = self._hosts[turn]
-        n_tiles, n_singles = fill_host_buffer(staging.numpy(), layout, [list(e.tokens) for e in entries], start_pos,
-                         state_slots, fresh, group_slots, group_tables, group_first, logit_rows)
+        work_counts = fill_host_buffer(staging.numpy(), layout, [list(e.tokens) for e in entries],
+                                       start_pos, state_slots, fresh, group_slots, group_tables,
+                                       group_first, logit_rows)
         groups = self._group_views.get(id(layout))
         if groups is None:
             groups = []
@@ -282,7 +293,8 @@ class ModelRunner:
                           groups, self.status, self.scratch, max_context, max_q,
                           launch_tokens=total, launch_rows=len(logit_rows),
                           max_positions=self.model.max_positions)
-        ctx.n_tiles, ctx.n_singles = n_tiles, n_singles
+        for key, counts in work_counts.items():
+            ctx.work[key].host_counts = dict(counts)
         ctx.staging, ctx.staging_turn = staging, turn
         ctx.copies = [c for r in reservations for c in r.copies]
         return ctx
@@ -306,19 +318,19 @@ class ModelRunner:
                 torch.cuda.current_stream().synchronize()      # pinned pairs buffer is reused
                 self.counters["cow_copies"] += len(chunk)
 
-    def _run_program(self, ctx: StepContext) -> Optional[torch.Tensor]:
+    def _run_program(self, ctx: StepContext, filled: tuple) -> Optional[torch.Tensor]:
         """A step of single tokens only (decoding) as ONE persistent kernel: the model's
         forward pass is recorded once per shape as a list of operations and from then on a
         cooperative kernel interprets the list (``csrc/decode_program.cu``).  Returns None
         when the model uses an operation a program cannot hold."""
         lay = ctx.layout
         rows_cap = StepContext.row_capacity(max(ctx.n_rows, 1)) if ctx.n_rows else 0
-        key = (lay.t_cap, lay.b_cap, rows_cap)
+        key = (lay.t_cap, lay.b_cap, rows_cap, filled)
         hit = self._programs.get(key)
         if hit is False:
             return None
         ctx.launch_tokens, ctx.launch_rows = lay.t_cap, rows_cap
-        ctx.n_tiles, ctx.n_singles = 0, None        # no prompt tiles; single tokens by device count
+        self._counts_from_device(ctx)
         ctx.max_context = self.model.max_positions
         if hit is None:
             program = ops.Program(lay.t_cap, self.device)

@@ -42,8 +42,14 @@ class Model:
         # kernels whatever the step holds (parts say so with ``graph_safe = True``)
         parts = [embedding, position, final_norm, head]
         for blk in blocks:
-            parts += [blk, blk.mixer, blk.feed_forward, blk.mixer_norm, blk.feed_forward_norm]
+            parts += [blk, blk.mixer, blk.feed_forward, *blk.norms.values()]
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
+        # work lists the parts want in every step's description, one planner per key
+        self.planners = []
+        for part in parts:
+            for planner in getattr(part, "work_planners", lambda: [])():
+                if all(planner.key != have.key for have in self.planners):
+                    self.planners.append(planner)
 
     # ---------------------------------------------------------------- cache layout
     def _derive_cache_layout(self) -> None:
@@ -114,10 +120,9 @@ def build_model(config, store, runtime) -> Model:
     for spec in specs:
         mixer = build_part("mixer", spec.mixer, store, runtime)
         ff = build_part("feed_forward", spec.feed_forward, store, runtime)
-        n1 = build_part("norm", spec.mixer_norm, store, runtime)
-        n2 = build_part("norm", spec.feed_forward_norm, store, runtime)
-        width = spec.mixer_norm.params["size"]
-        blocks.append(part_factory("arrangement", spec.arrangement)(mixer, ff, n1, n2, width, runtime))
+        norms = {name: build_part("norm", ns, store, runtime) for name, ns in spec.norms.items()}
+        blocks.append(part_factory("arrangement", spec.arrangement)(mixer, ff, norms, spec.width,
+                                                                    runtime))
     position = build_part("position", config.position_spec(), store, runtime)
     for block in blocks:                      # rotary-style encodings act inside the mixer
         if hasattr(block.mixer, "position") and block.mixer.position is None:

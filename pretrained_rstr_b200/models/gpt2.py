@@ -74,6 +74,24 @@ def random_tensors(cfg: GPT2Config, seed: int) -> Dict[str, torch.Tensor]:
     return out
 
 
+_IDS = {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2"}
+#: Sizes a random-weight model can be asked for by name: the two tiny test configurations
+#: and the layer sizes of GPT-2 small, medium and XL.
+NAMED_SIZES = {
+    "tiny-a": dict(_IDS, n_layer=2, n_embd=64, n_head=4, n_inner=256, vocab_size=512,
+                   n_positions=128),
+    "tiny-b": dict(_IDS, n_layer=3, n_embd=96, n_head=3, n_inner=320, vocab_size=1000,
+                   n_positions=256, layer_norm_epsilon=1e-6, activation_function="gelu",
+                   scale_attn_by_inverse_layer_idx=True),
+    "small": dict(_IDS, n_layer=12, n_embd=768, n_head=12, n_inner=3072, vocab_size=50257,
+                  n_positions=1024),
+    "medium": dict(_IDS, n_layer=24, n_embd=1024, n_head=16, n_inner=4096, vocab_size=50257,
+                   n_positions=1024),
+    "xl": dict(_IDS, n_layer=48, n_embd=1600, n_head=25, n_inner=6400, vocab_size=50257,
+               n_positions=1024),
+}
+
+
 def build(cfg: GPT2Config, store, runtime):
     from .assembly import build_model
     return build_model(cfg, store, runtime)
@@ -87,5 +105,6 @@ ARCHITECTURE = Architecture(
     random_tensors=random_tensors,
     strip_prefixes=STRIP_PREFIXES,
     ignorable=ignorable,
+    named_sizes=NAMED_SIZES,
 )
 register_architecture(GPT2Config.identifiers, ARCHITECTURE)

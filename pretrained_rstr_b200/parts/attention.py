@@ -13,17 +13,54 @@ its part.
 """
 from __future__ import annotations
 
-import os
+from typing import Dict, Optional, Sequence
 
-from typing import Optional
-
+import numpy as np
 import torch
 
 from ..csrc import ops
-from ..engine.batch import SINGLE_MAX_Q
+from ..engine.batch import WorkPlanner
+from ..settings import SETTINGS
 from .interfaces import KVSpec, LayerCache, Mixer, PositionEncoding
 from .linear import Linear
 from .registry import register_part
+
+
+class AttentionWork(WorkPlanner):
+    """How the attention kernels cut a step: portions of prompts go in tiles of up to
+    ``TILE`` queries of one request to the prompt kernels; decoded tokens and portions of
+    up to ``SINGLE_MAX_Q`` tokens go token by token to the split-key decode kernel."""
+
+    key = "causal_attention"
+    counters = ("tiles", "singles")
+    TILE = 128
+    SINGLE_MAX_Q = 4
+
+    def arrays(self, t_cap: int, b_cap: int):
+        tile_cap = t_cap // self.TILE + b_cap
+        return {"tile_req": (tile_cap, -1), "tile_row0": (tile_cap, 0), "tile_rows": (tile_cap, 0),
+                "single_tokens": (min(t_cap, b_cap * self.SINGLE_MAX_Q), 0)}
+
+    def fill(self, arrays: Dict[str, np.ndarray], lengths: Sequence[int]) -> Dict[str, int]:
+        treq, trow, tnum = arrays["tile_req"], arrays["tile_row0"], arrays["tile_rows"]
+        sing = arrays["single_tokens"]
+        n_tiles = n_sing = 0
+        t = 0
+        for b, n in enumerate(lengths):
+            if n <= self.SINGLE_MAX_Q:
+                sing[n_sing:n_sing + n] = np.arange(t, t + n, dtype=np.int32)
+                n_sing += n
+            else:
+                for r0 in range(0, n, self.TILE):
+                    treq[n_tiles] = b
+                    trow[n_tiles] = t + r0
+                    tnum[n_tiles] = min(self.TILE, n - r0)
+                    n_tiles += 1
+            t += n
+        return {"tiles": n_tiles, "singles": n_sing}
+
+
+ATTENTION_WORK = AttentionWork()
 
 
 class CausalAttention(Mixer):
@@ -50,6 +87,9 @@ class CausalAttention(Mixer):
     def kv_spec(self) -> KVSpec:
         return KVSpec(self.n_kv_head, self.head_dim, self.window)
 
+    def work_planners(self):
+        return [ATTENTION_WORK]
+
     def forward(self, ctx, h, x, cache: LayerCache) -> None:
         t = x.shape[0]
         dtype = self.runtime.dtype
@@ -74,13 +114,6 @@ class CausalAttention(Mixer):
         self.out.forward(ctx, o, x, resid=x)
 
 
-DECODE_CTAS = int(os.environ.get("PRB200_DECODE_CTAS", "768"))
-USE_TC = os.environ.get("PRB200_ATTN_TC", "1") != "0"
-
-
-PREFILL_PART = int(os.environ.get("PRB200_PREFILL_PART", "-1"))     # blocks per key part; -1: choose
-
-
 def prefill_key_parts(items: int, max_context: int, window: Optional[int]):
     """(blocks per part, most parts per item) for the tensor-memory prompt kernel; (0, 1):
     one CTA per item.  Splitting an item's keys over several CTAs costs each of them a
@@ -92,13 +125,14 @@ def prefill_key_parts(items: int, max_context: int, window: Optional[int]):
     prompt of 1,024 (96 items) 1.07 -> 1.11 ms.  Hence: only up to 74 items (half the SMs)."""
     span = min(max_context, window + 128) if window else max_context
     blocks = -(-span // 64) + (1 if window else 0)
-    if PREFILL_PART >= 0:
-        part = PREFILL_PART
-    elif items > 74 or blocks < 8:
+    sms = ops.sm_count()
+    if SETTINGS.prefill_part >= 0:
+        part = SETTINGS.prefill_part
+    elif items > sms // 2 or blocks < 8:
         part = 0
     else:
         # about as many CTAs as run at a time (two per SM), parts of at least four blocks
-        part = max(4, -(-items * blocks // (2 * 296)))
+        part = max(4, -(-items * blocks // (4 * sms)))
     if part <= 0 or part >= blocks:
         return 0, 1
     part = max(part, -(-blocks // (ops.PREFILL_MAX_PARTS - 1)))
@@ -123,10 +157,12 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
         ops.attention_generic(out, q, cache.k, cache.v, group.block_table, ctx.seq_of_token,
                               ctx.positions, t, n_head, scale, window, ctx.max_context, ctx.status)
         return
-    lay = ctx.layout
-    if ctx.n_tiles is None or ctx.n_tiles > 0:
-        n_tiles = lay.tile_cap if ctx.n_tiles is None else ctx.n_tiles
-        if USE_TC and ops.prefill_tc_supports(head_dim, group.page_size):
+    work = ctx.work[ATTENTION_WORK.key]
+    tiles, singles = work.host_counts["tiles"], work.host_counts["singles"]
+    tile_req, tile_row0, tile_rows = (work.arrays[n] for n in ("tile_req", "tile_row0", "tile_rows"))
+    if tiles is None or tiles > 0:
+        n_tiles = work.caps["tile_req"] if tiles is None else tiles
+        if SETTINGS.attention_tcgen05 and ops.prefill_tc_supports(head_dim, group.page_size):
             # (a step that runs as a graph is planned with its capacities: the most tiles and
             # the longest context it may have)
             parts = None
@@ -137,35 +173,44 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
                          ctx.scratch("attn_part_ml", (units * max_parts * 256,), torch.float32),
                          ctx.scratch_zero("attn_part_count", (units,), torch.int32))
             ops.attention_prefill_tc(out, q, cache.k, cache.v, group.block_table, ctx.positions,
-                                     ctx.tile_req, ctx.tile_row0, ctx.tile_rows, ctx.counts[0:1],
+                                     tile_req, tile_row0, tile_rows, work.counts["tiles"],
                                      n_tiles, n_head, scale, window, ctx.status,
                                      part_blocks=part_blocks, max_parts=max_parts, parts=parts)
         else:
             ops.attention_prefill(out, q, cache.k, cache.v, group.block_table, ctx.positions,
-                                  ctx.tile_req, ctx.tile_row0, ctx.tile_rows, ctx.counts[0:1],
+                                  tile_req, tile_row0, tile_rows, work.counts["tiles"],
                                   n_tiles, n_head, scale, window, ctx.status)
-    if ctx.n_singles is None or ctx.n_singles > 0:
-        n_list = lay.single_cap if ctx.n_singles is None else ctx.n_singles
-        # about five CTAs per SM (the kernel's leaner instance fits six): many (token, head)
-        # pairs get fewer, longer splits, and one each when there are more pairs than that
-        granule = ops.decode_split()
-        most = -(-ctx.max_context // granule)
-        pairs = max(1, n_list * n_head)
-        if pairs < DECODE_CTAS:
-            wanted = -(-DECODE_CTAS // pairs)
-        else:
-            wanted = 1
-        wanted = max(1, min(most, wanted))
-        split_keys = -(-ctx.max_context // wanted // granule) * granule
-        max_splits = -(-ctx.max_context // split_keys)
-        cap = ctx.runtime.max_requests * SINGLE_MAX_Q
-        ws = ctx.scratch("attn_decode_ws", (cap * n_head * ctx.max_splits_cap * (head_dim + 4),),
+    if singles is None or singles > 0:
+        n_list = work.caps["single_tokens"] if singles is None else singles
+        split_keys, max_splits = decode_splits(n_list * n_head, ctx.max_context, group.page_size)
+        cap = ctx.runtime.max_requests * AttentionWork.SINGLE_MAX_Q
+        # room for the shortest splits any step may choose
+        splits_cap = -(-ctx.max_positions // ops.decode_split())
+        ws = ctx.scratch("attn_decode_ws", (cap * n_head * splits_cap * (head_dim + 4),),
                          torch.float32)
         counters = ctx.scratch_zero("attn_decode_counters", (cap * n_head,), torch.int32)
         ops.attention_decode(out, q, cache.k, cache.v, group.block_table, ctx.seq_of_token,
-                             ctx.positions, ctx.single_tokens, ctx.counts[1:2], n_list, n_head,
-                             scale, window, ws, counters, max_splits, ctx.status,
+                             ctx.positions, work.arrays["single_tokens"], work.counts["singles"],
+                             n_list, n_head, scale, window, ws, counters, max_splits, ctx.status,
                              split_keys=split_keys)
+
+
+def decode_splits(pairs: int, max_context: int, page_size: int):
+    """(keys per split, most splits per (token, head)) of the decode kernel for a launch of
+    ``pairs`` (token, head) pairs over contexts of up to ``max_context`` keys.  The launch
+    should have about five CTAs per SM: many pairs get fewer, longer splits, and one each when
+    there are more pairs than that.  A split is a multiple of the kernel's granule and spans
+    no more pages than the kernel holds page ids for."""
+    granule = ops.decode_split()
+    target = SETTINGS.decode_ctas or 768 * ops.sm_count() // 148
+    most = -(-max_context // granule)
+    pairs = max(1, pairs)
+    wanted = -(-target // pairs) if pairs < target else 1
+    wanted = max(1, min(most, wanted))
+    split_keys = -(-max_context // wanted // granule) * granule
+    longest = ops.decode_max_split_pages() * page_size // granule * granule
+    split_keys = max(granule, min(split_keys, longest))
+    return split_keys, -(-max_context // split_keys)
 
 
 def _causal_attention(p, store, rt) -> CausalAttention:

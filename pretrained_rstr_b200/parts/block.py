@@ -3,6 +3,8 @@ x += mixer(norm_1(x)); x += feed_forward(norm_2(x))  (``dev/examples/gpt2.clj:14
 The block knows its parts only through their interfaces."""
 from __future__ import annotations
 
+from typing import Dict
+
 from .interfaces import Block, FeedForward, LayerCache, Mixer, Norm
 from .linear import LazyNorm
 from .registry import register_part
@@ -10,10 +12,14 @@ from .registry import register_part
 
 class PreNormBlock(Block):
     graph_safe = True
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
-                 feed_forward_norm: Norm, width: int, runtime):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Dict[str, Norm],
+                 width: int, runtime):
+        missing = {"mixer", "feed_forward"} - set(norms)
+        if missing or len(norms) != 2:
+            raise ValueError(f"pre_norm wants the norms 'mixer' and 'feed_forward', got {sorted(norms)}")
         self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.norms = dict(norms)
+        self.mixer_norm, self.feed_forward_norm = norms["mixer"], norms["feed_forward"]
         self.width, self.runtime = width, runtime
 
     def forward(self, ctx, x, cache: LayerCache) -> None:

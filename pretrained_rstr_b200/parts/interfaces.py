@@ -61,6 +61,11 @@ class Mixer:
     def state_specs(self) -> List[StateSpec]:
         return []
 
+    def work_planners(self) -> list:
+        """Planners (:class:`~pretrained_rstr_b200.engine.batch.WorkPlanner`) of the work lists
+        this mixer's kernels want in every step's description; see ``ctx.work``."""
+        return []
+
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor, cache: LayerCache) -> None:
         """x += mix(h) for the T tokens of the step, reading and (if ``cache.writes``)
         extending the cache."""
@@ -68,6 +73,9 @@ class Mixer:
 
 
 class FeedForward:
+    def work_planners(self) -> list:
+        return []
+
     def forward(self, ctx, h: torch.Tensor, x: torch.Tensor) -> None:
         """x += feed_forward(h)."""
         raise NotImplementedError
@@ -99,5 +107,8 @@ class Head:
 
 
 class Block:
+    """Keeps ``mixer``, ``feed_forward`` and ``norms`` (a dict) as attributes: the assembly
+    reads the cache needs of the mixer and the work lists of all of them."""
+
     def forward(self, ctx, x: torch.Tensor, cache: LayerCache) -> None:
         raise NotImplementedError

@@ -10,7 +10,8 @@ Categories and what a factory returns (interfaces in :mod:`.interfaces`):
 ``position``      :class:`PositionEncoding`  factory(params, store, runtime)
 ``embedding``     :class:`Embedding`    factory(params, store, runtime)
 ``head``          :class:`Head`         factory(params, store, runtime)
-``arrangement``   :class:`Block`        factory(mixer, feed_forward, mixer_norm, feed_forward_norm)
+``arrangement``   :class:`Block`        factory(mixer, feed_forward, norms by name, width, runtime);
+                                        the block keeps ``mixer``, ``feed_forward`` and ``norms``
 """
 from __future__ import annotations
 

@@ -47,10 +47,15 @@ class TensorExpectation:
 
 
 def _stored_dtype(dtype: torch.dtype, kind: str) -> torch.dtype:
+    """Element type a tensor is kept in until a part binds it: integer tables int32, 32-bit
+    (and wider) floats float32, bfloat16 bfloat16, and float16 as it is: the part converts it
+    to the runtime's type in one step, so a float32 runtime loses none of its bits."""
     if kind == "int":
         return torch.int32
     if dtype in (torch.float32, torch.float64):
         return torch.float32
+    if dtype == torch.float16:
+        return torch.float16
     return torch.bfloat16
 
 

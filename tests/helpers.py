@@ -34,6 +34,27 @@ TINY_C = {
 }
 TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
 
+
+def real_width(name: str) -> Dict:
+    """The layer sizes of GPT-2 small, medium and XL (width, heads, inner width, vocabulary,
+    positions) with two layers: fewer layers, not smaller ones, so that the engine runs the
+    very kernel instances, tile widths and splits it runs at those sizes."""
+    d, h = {"small": (768, 12), "medium": (1024, 16), "xl": (1600, 25)}[name]
+    return {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "n_layer": 2,
+            "n_embd": d, "n_head": h, "n_inner": 4 * d, "vocab_size": 50257, "n_positions": 1024,
+            "layer_norm_epsilon": 1e-5, "activation_function": "gelu_new",
+            "scale_attn_weights": True, "scale_attn_by_inverse_layer_idx": False}
+
+
+def bf16_atol(width: int) -> float:
+    """bfloat16 tolerance on logits for a model of this width.  Between two products the
+    activations are rounded to 8 bits of mantissa (relative error up to 2^-9); a logit is a sum
+    over ``width`` such terms against table entries of standard deviation 0.02, so its error
+    grows like sqrt(width), and the largest among ten thousands of logits is several standard
+    deviations out.  6e-4 * sqrt(width): 4.8e-3 at 64, 1.7e-2 at 768, 2.4e-2 at 1,600 (the
+    tiny configurations keep their fixed 1.5e-2)."""
+    return 6e-4 * width ** 0.5
+
 # Absolute tolerance on logits.  Random-weight logits are O(0.2); float32 differences
 # come from summation order only; bfloat16 ones from rounding activations to 8 bits
 # of mantissa between products.
@@ -103,6 +124,20 @@ def compare(rows: Dict[Tuple[str, int], torch.Tensor], oracle: Dict[str, torch.T
                              f"{int(ref.argmax())})")
         worst = max(worst, err)
     return worst
+
+
+def oracle_rows(folder: str, prompts: Dict[str, Sequence[int]],
+                wanted: Dict[str, Sequence[int]]) -> Dict[str, Dict[int, torch.Tensor]]:
+    """The plain implementation's logits at chosen positions only (large vocabularies): the
+    whole sequence runs, the head is applied to the wanted rows."""
+    model = plain_gpt2.PlainGPT2(folder)
+    out = {}
+    for rid, ids in prompts.items():
+        hidden = plain_gpt2.forward(model, ids)
+        pos = sorted(set(wanted[rid]))
+        rows = plain_gpt2.logits(model, hidden[pos]).to(torch.float32)
+        out[rid] = {p: rows[i] for i, p in enumerate(pos)}
+    return out
 
 
 def oracle_logits(folder: str, prompts: Dict[str, Sequence[int]]) -> Dict[str, torch.Tensor]:

@@ -198,7 +198,7 @@ def greedy_generate(model: PlainGPT2, ids: Sequence[int], n: int) -> List[int]:
             break
         row = all_logits(model, ids)[-1]
         tok = int(torch.argmax(row))          # torch.argmax returns the first maximum
-        assert tok == argmax(row) or True
+        assert tok == argmax(row), "the tie rule of the scalar argmax differs from torch.argmax"
         ids.append(tok)
         out.append(tok)
     return out

@@ -217,3 +217,33 @@ def test_random_orders_lose_nothing(seed):
     for gi, alloc in enumerate(cm.allocators):
         assert alloc.free_count == alloc.num_pages
     assert cm.slots.free_count == 5
+
+
+def test_state_keeping_models_share_no_prefix_and_fork_with_their_state():
+    """A model whose parts keep fixed-size state per request: a request that took over cached
+    pages would skip their tokens and never run their state updates, so sharing is off; a fork
+    copies the source's state row, and is refused at any length but the source's present one."""
+    copied = []
+    cm = CacheManager([FULL], 16, 8, 4, 128, share_prefixes=True, has_state=True,
+                      copy_state=lambda src, dst: copied.append((src, dst)))
+    assert cm.share_prefixes is False
+    cm.open("a")
+    cm.reserve("a", 40)
+    cm.commit("a", list(range(40)))
+    cm.open("b")
+    assert cm.match_prefix("b", list(range(40))) == 0 and cm.is_fresh("b")
+    cm.close("b")
+    with pytest.raises(CacheError, match="present length"):
+        cm.fork("a", "c", 32)
+    assert "c" not in cm.requests
+    slot = cm.fork("a", "c")
+    assert copied == [(cm.slot("a"), slot)] and cm.length("c") == 40 and not cm.is_fresh("c")
+    empty = cm.fork("a", "d", 0)                      # nothing to copy: it starts fresh
+    assert len(copied) == 1 and cm.is_fresh("d") and empty != slot
+    cm.check()
+    bare = CacheManager([FULL], 16, 8, 4, 128, has_state=True)
+    bare.open("a")
+    bare.reserve("a", 5)
+    bare.commit("a")
+    with pytest.raises(CacheError, match="no state copy"):
+        bare.fork("a", "b")

@@ -97,6 +97,16 @@ def test_random_model_is_seeded_and_storage_precision_kept(tmp_path):
     store = load_weights(fb, gpt2_arch.expected_tensors(cfg), "cpu")
     assert store.get("wte.weight").dtype == torch.bfloat16
     assert store.get("h.1.mlp.c_fc.weight").shape == (64, 256)
+    # a float16 checkpoint is kept as it is until a part converts it to the runtime's type:
+    # widened to float32 it loses no bits (it is not rounded to bfloat16 on the way)
+    from pretrained_rstr_b200.weights import save_file
+    half = {k: v.to(torch.float16) for k, v in a.items()}
+    os.makedirs(tmp_path / "h")
+    cfg.save(str(tmp_path / "h"))
+    save_file(half, str(tmp_path / "h" / "model.safetensors"))
+    store = load_weights(str(tmp_path / "h"), gpt2_arch.expected_tensors(cfg), "cpu")
+    assert store.get("wte.weight").dtype == torch.float16
+    assert torch.equal(store.get("wte.weight", torch.float32), half["wte.weight"].float())
 
 
 def test_weight_errors_list_everything_at_once(tmp_path):

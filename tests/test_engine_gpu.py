@@ -242,6 +242,11 @@ def test_trace_run_program(tmp_path, dtype):
     got2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(-1, vocab))
     got7 = torch.from_numpy(np.fromfile(out / "7.f32", dtype="<f4").reshape(-1, vocab))
     assert got0.shape[0] == 2 and got1.shape[0] == 1 and got2.shape[0] == 1 and got7.shape[0] == 4
+    # beside every file of logits, an index of its rows by (request, position)
+    index = {s: json.loads((out / f"{s}.json").read_text()) for s in (0, 1, 2, 7)}
+    assert index[0] == {"step": 0, "vocab": vocab, "rows": [["a", 0], ["a", 39]]}
+    assert index[1]["rows"] == [["b", 1]] and index[2]["rows"] == [["b", 8]]
+    assert index[7]["rows"] == [["a", 66], ["a", 67], ["a", 68], ["a", 69]]
     tol = ATOL[dtype]
     assert float((got0 - oracle["a"][[0, 39]]).abs().max()) <= tol
     assert float((got1 - oracle["b"][[1]]).abs().max()) <= tol
@@ -275,3 +280,65 @@ def test_decode_program_equals_kernel_by_kernel(folders, name):
         results[programs] = rp.rows
     for key, row in results[True].items():
         assert float((row - results[False][key]).abs().max()) <= 2e-3
+
+
+def _run_cli(*args, stdin=None):
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    proc = subprocess.run([sys.executable, "-m", "pretrained_rstr_b200", *args], input=stdin,
+                          capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    return proc.stdout
+
+
+@pytest.mark.parametrize("size,seed", [("tiny-a", 0), ("tiny-b", 1)])
+def test_command_line_random_then_generate(tmp_path, size, seed):
+    """``python -m pretrained_rstr_b200 random`` writes a model folder, ``generate`` prints one
+    JSON object with the generated ids: greedy in float32 they are the plain implementation's;
+    ``generate --random SIZE`` makes the same weights itself and gives the same ids."""
+    folder = str(tmp_path / "model")
+    made = json.loads(_run_cli("random", "--out", folder, "--size", size, "--seed", str(seed)))
+    assert made["out"] == folder and made["config"]["architectures"] == ["GPT2LMHeadModel"]
+    prompt = random_tokens(11, made["config"]["vocab_size"], 21)
+    ids = ",".join(str(t) for t in prompt)
+    out = json.loads(_run_cli("generate", "--model", folder, "--ids", ids, "--n", "9",
+                              "--dtype", "float32").strip().splitlines()[-1])
+    want = plain_gpt2.greedy_generate(plain_gpt2.PlainGPT2(folder), prompt, 9)
+    assert out["prompt"] == prompt and out["generated"] == want
+    again = json.loads(_run_cli("generate", "--random", size, "--weights-seed", str(seed), "--ids", ids,
+                                "--n", "9", "--dtype", "float32").strip().splitlines()[-1])
+    assert again["generated"] == want
+    sampled = json.loads(_run_cli("generate", "--model", folder, "--ids", ids, "--n", "9", "--dtype",
+                                  "float32", "--temperature", "0.8", "--seed", "7")
+                         .strip().splitlines()[-1])
+    assert sampled["generated"] == plain_gpt2.sample_generate(plain_gpt2.PlainGPT2(folder), prompt, 9,
+                                                              0.8, None, None, 7)
+
+
+def test_replay_with_random_weights_and_six_live_requests(tmp_path):
+    """``replay --random SIZE --seed S`` makes its own model; ``--max-requests`` lifts the
+    default of four live requests."""
+    raw, seed = TINY["A"]
+    folder = make_folder(str(tmp_path / "same"), raw, seed, "float32")     # what --random tiny-a --seed 0 makes
+    prompts = {f"r{i}": random_tokens(7 + 3 * i, raw["vocab_size"], 60 + i) for i in range(6)}
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": ids[:-1], "want": []} for r, ids in prompts.items()],
+              "end": []},
+             {"step": 1, "entries": [{"id": r, "tokens": ids[-1:], "want": [0]} for r, ids in prompts.items()],
+              "end": list(prompts)}]
+    out = tmp_path / "out"
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    done = _run_cli("replay", "--random", "tiny-a", "--seed", "0", "--dtype", "float32", "--out", str(out),
+                    "--max-tokens", str(6 * 64), "--max-requests", "6", stdin=text)
+    assert [l for l in done.splitlines() if l.startswith("done")] == ["done 0", "done 1"]
+    import numpy as np
+    got = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(6, raw["vocab_size"]))
+    index = json.loads((out / "1.json").read_text())
+    oracle = oracle_logits(folder, prompts)
+    for row, (rid, pos) in zip(got, index["rows"]):
+        assert pos == len(prompts[rid]) - 1
+        assert float((row - oracle[rid][pos]).abs().max()) <= ATOL["float32"]
+    # with the default of four, the fifth live request is refused
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder,
+                           "--dtype", "float32", "--out", str(tmp_path / "o2"), "--max-tokens", "384"],
+                          input=text, capture_output=True, text=True, timeout=600, env=env)
+    assert proc.returncode != 0 and "requests" in proc.stderr

@@ -50,8 +50,10 @@ def test_greedy_entry_point(folders, name, dtype):
     for p, got in zip(prompts, outs):
         _agree(plain, p, got, plain_gpt2.greedy_generate(plain, p, n_new), dtype,
                f"batched len {len(p)}")
-    assert m.engine.lm.cache.free_pages(0) + len(m.engine.lm.cache._index) >= \
-        m.engine.lm.cache.allocators[0].num_pages - len(m.engine.lm.cache._index)
+    cache = m.engine.lm.cache
+    assert not cache.requests
+    # every page is either free or held by the prefix index alone: none is lost
+    assert cache.free_pages(0) + len(cache._index) == cache.allocators[0].num_pages
     m.engine.lm.cache.check()
 
 

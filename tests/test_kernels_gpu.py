@@ -220,6 +220,24 @@ def test_attention_decode(nh, nkv, dh, ps, window, split_keys):
         assert status.tolist() == [0, 0, 0, 0]
         assert float((out.float() - ref).abs().max()) <= 2e-2
         assert int(counters.abs().sum()) == 0
+    if split_keys == 128:
+        # contexts of up to 2,000 keys: 16 splits, more than a cluster takes, so the partial
+        # results go through the workspace (filled with NaN here) and the last CTA merges
+        lengths2, portions2 = [2000, 5, 1300, 1025], [1, 1, 2, 1]
+        q2, k2, v2, table2, seq2, pos2 = _paged_case(8, nh, nkv, dh, ps, lengths2, portions2,
+                                                     torch.bfloat16)
+        t2, splits2 = q2.shape[0], 16
+        ws2 = torch.full((t2 * nh * splits2 * (dh + 4),), float("nan"), device="cuda")
+        counters2 = torch.zeros(t2 * nh, dtype=torch.int32, device="cuda")
+        ref2 = _ref_attention(q2, k2, v2, table2, seq2, pos2, nh, 0.2, window)
+        for _ in range(2):
+            out2 = torch.full_like(q2, float("nan"))
+            ops.attention_decode(out2, q2, k2, v2, table2, seq2, pos2, None, None, t2, nh, 0.2,
+                                 window, ws2, counters2, splits2, status, split_keys=128)
+            assert status.tolist() == [0, 0, 0, 0]
+            assert float((out2.float() - ref2).abs().max()) <= 2e-2
+            assert int(counters2.abs().sum()) == 0
+        assert window is not None or bool(torch.isfinite(ws2).any())
     # a token list picks tokens; the others are not touched
     order = torch.tensor([t - 1, 0, 3], dtype=torch.int32, device="cuda")
     count = torch.tensor([2], dtype=torch.int32, device="cuda")

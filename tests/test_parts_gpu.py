@@ -209,10 +209,12 @@ def _register_toy():
                 "n_head": self.heads, "n_kv_head": self.heads, "head_dim": self.width // self.heads,
                 "scale": 1.0 / math.sqrt(self.width // self.heads), "window": None, "bias": False,
                 "weight_layout": "out_in"})
-            return [LayerSpec("l0.", "pre_norm", toy, self._mlp("l0."), self._norm("l0.n1"),
-                              self._norm("l0.n2")),
-                    LayerSpec("l1.", "pre_norm", attn, self._mlp("l1."), self._norm("l1.n1"),
-                              self._norm("l1.n2"))]
+            return [LayerSpec("l0.", "pre_norm", toy, self._mlp("l0."),
+                              {"mixer": self._norm("l0.n1"), "feed_forward": self._norm("l0.n2")},
+                              self.width),
+                    LayerSpec("l1.", "pre_norm", attn, self._mlp("l1."),
+                              {"mixer": self._norm("l1.n1"), "feed_forward": self._norm("l1.n2")},
+                              self.width)]
 
         def run_order(self):
             # layer 1 runs twice; its second run reads the cache its first run wrote
@@ -341,6 +343,60 @@ def test_toy_architecture_with_state_and_repeated_layer(tmp_path, dtype):
     assert lm.cache.slots.free_count == 2
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_state_keeping_toy_through_the_entry_point_and_forked(tmp_path, dtype):
+    """The same toy model through ``load_lm``, whose default shares prompt prefixes: for a
+    model that keeps per-request state the sharing is switched off (a request that took over
+    cached pages would never run the state updates of their tokens), so two requests with a
+    common 64-token prefix both give the plain tokens.  A fork copies the state row."""
+    from pretrained_rstr_b200 import generate_batch, load_lm
+    from pretrained_rstr_b200.cache import CacheError
+    from pretrained_rstr_b200.engine.batch import Entry
+    from pretrained_rstr_b200.weights import load_file, make_random_model
+    ToyConfig = _register_toy()
+    cfg = ToyConfig(width=48, heads=3, inner=80, vocab=200, positions=160, decay=0.7)
+    folder = str(tmp_path / "toy")
+    make_random_model(folder, cfg, seed=5,
+                      dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    w = {k: v.float() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    m = load_lm(folder, gpu=True, dtype=dtype, max_lanes=3, max_batched_tokens=128,
+                prefill_chunk=32, page_size=16)
+    cache = m.loaded.cache
+    assert cache.has_state and cache.share_prefixes is False
+    prefix = random_tokens(64, 200, 1)
+    prompts = [prefix + random_tokens(n, 200, 2 + n) for n in (5, 9)]
+    first = generate_batch(m, prompts[:1], 5)[0]
+    outs = generate_batch(m, prompts, 5)                  # the prefix is in the cache by now
+    assert m.stats()["cache"]["prefix_hits"] == 0 and outs[0] == first
+    for p, got in zip(prompts, outs):
+        ids = list(p)
+        for i, tok in enumerate(got):
+            row = _toy_plain(w, cfg, ids)[-1]
+            want = int(row.argmax())
+            if tok != want:
+                assert dtype == "bfloat16" and abs(float(row[tok] - row[want])) < 3e-2, \
+                    f"token {i}: {tok}, plain says {want}"
+            ids.append(tok)
+    # fork at a page edge: the child goes on from the parent's pages AND the parent's state
+    runner = m.loaded.runner
+    base, tails = random_tokens(32, 200, 30), {"root": random_tokens(9, 200, 31),
+                                               "kid": random_tokens(12, 200, 32)}
+    cache.open("root")
+    runner.step([Entry("root", base, [])])
+    with pytest.raises(CacheError, match="present length"):
+        cache.fork("root", "kid", 16)
+    cache.fork("root", "kid")
+    logits = runner.step([Entry("root", tails["root"], list(range(9))),
+                          Entry("kid", tails["kid"], list(range(12)))]).cpu()
+    runner.check_status()
+    want = torch.cat([_toy_plain(w, cfg, base + tails["root"])[32:],
+                      _toy_plain(w, cfg, base + tails["kid"])[32:]])
+    assert float((logits - want).abs().max()) <= ATOL[dtype]
+    cache.close("root")
+    cache.close("kid")
+    cache.check()
+
+
 # ------------------------------------------------- groups: a windowed layer, grouped heads
 def _register_windowed():
     """A second toy architecture out of the framework's own parts: layer 0 attends over all
@@ -392,7 +448,8 @@ def _register_windowed():
                                            "width": self.width, "inner": self.inner,
                                            "activation": "gelu_new", "bias": True,
                                            "weight_layout": "out_in"}),
-                    self._norm(p + "n1"), self._norm(p + "n2")))
+                    {"mixer": self._norm(p + "n1"), "feed_forward": self._norm(p + "n2")},
+                    self.width))
             return specs
 
         def embedding_spec(self):
@@ -526,11 +583,12 @@ def test_windowed_and_grouped_layers_have_pools_of_their_own(tmp_path, dtype):
 def _register_routed():
     """A third toy architecture: no position table but a rotation of queries and keys by
     their position (a position encoding defined here), and in the last layer a feed-forward
-    that routes every token to two of three small experts (also defined here)."""
+    that routes every token to two of three small experts (also defined here), in a block
+    arrangement of its own: mixer and feed-forward side by side behind ONE norm."""
     from pretrained_rstr_b200.config import (Architecture, LayerSpec, ModelConfig, PartSpec,
                                              register_architecture)
     from pretrained_rstr_b200.models.assembly import build_model
-    from pretrained_rstr_b200.parts import FeedForward, PositionEncoding, register_part
+    from pretrained_rstr_b200.parts import Block, FeedForward, PositionEncoding, register_part
     from pretrained_rstr_b200.weights import TensorExpectation, normal
 
     class ToyRotation(PositionEncoding):
@@ -571,6 +629,22 @@ def _register_routed():
                 share = (weight * (which == e)).sum(1, keepdim=True)          # 0 where not routed
                 x += share * (torch.relu(hf @ self.up[e].T) @ self.down[e].T)
 
+    class ToyParallelBlock(Block):
+        """x += mixer(n(x)) + feed_forward(n(x)): both branches read the same normed input."""
+
+        def __init__(self, mixer, feed_forward, norms, width, runtime):
+            assert sorted(norms) == ["shared"]
+            self.mixer, self.feed_forward, self.norms = mixer, feed_forward, dict(norms)
+            self.width, self.runtime = width, runtime
+
+        def forward(self, ctx, x, cache):
+            h = ctx.scratch("toy_parallel_normed", (ctx.token_capacity, self.width),
+                            self.runtime.dtype)[:x.shape[0]]
+            self.norms["shared"].forward(ctx, x, h)
+            self.mixer.forward(ctx, h, x, cache)        # x changes, h does not
+            self.feed_forward.forward(ctx, h, x)
+
+    register_part("arrangement", "toy_parallel", ToyParallelBlock)
     register_part("position", "toy_rotation", ToyRotation)
     register_part("feed_forward", "toy_routed_experts", ToyRoutedExperts)
 
@@ -613,8 +687,13 @@ def _register_routed():
                                                 "weight_layout": "out_in"})
                 else:
                     ff = PartSpec("toy_routed_experts", {"weights": p + "moe", "top": 2})
-                specs.append(LayerSpec(p, "pre_norm", attn, ff, self._norm(p + "n1"),
-                                       self._norm(p + "n2")))
+                if i == 0:
+                    specs.append(LayerSpec(p, "pre_norm", attn, ff,
+                                           {"mixer": self._norm(p + "n1"),
+                                            "feed_forward": self._norm(p + "n2")}, self.width))
+                else:
+                    specs.append(LayerSpec(p, "toy_parallel", attn, ff,
+                                           {"shared": self._norm(p + "n1")}, self.width))
             return specs
 
         def embedding_spec(self):
@@ -643,8 +722,8 @@ def _register_routed():
              "l1.moe.experts.down": (n, d, f)}
         for l in ("l0.", "l1."):
             e.update({l + "qkv.weight": (3 * d, d), l + "out.weight": (d, d),
-                      l + "n1.weight": (d,), l + "n1.bias": (d,),
-                      l + "n2.weight": (d,), l + "n2.bias": (d,)})
+                      l + "n1.weight": (d,), l + "n1.bias": (d,)})
+        e.update({"l0.n2.weight": (d,), "l0.n2.bias": (d,)})      # the parallel block has one norm
         return {k: TensorExpectation(v) for k, v in e.items()}
 
     def random_tensors(cfg, seed):
@@ -686,11 +765,13 @@ def _routed_plain(w, cfg, ids):
             q, k, v = turn(qkv[:, c]), turn(qkv[:, d:2 * d][:, c]), qkv[:, 2 * d:][:, c]
             sc = (q @ k.T) / math.sqrt(dh)
             o[:, c] = torch.softmax(sc.masked_fill(~mask, -math.inf), 1) @ v
-        x = x + o @ w[l + "out.weight"].T
-        hn = ln(x, l + "n2")
         if l == "l0.":
+            x = x + o @ w[l + "out.weight"].T
+            hn = ln(x, l + "n2")
             x = x + torch.relu(hn @ w["l0.up.weight"].T) @ w["l0.down.weight"].T
         else:
+            hn = ln(x, l + "n1")                   # the parallel block: one norm feeds both branches
+            x = x + o @ w[l + "out.weight"].T
             logits = hn @ w["l1.moe.router.weight"].T
             ranked, order = torch.sort(logits, dim=1, descending=True)
             margin = ranked[:, 1] - ranked[:, 2]
