@@ -61,6 +61,7 @@ class Engine:
         # around the device work of the step (measurement only)
         self.timing_events = None
         self.step_index = 0
+        self.launched_entries = None       # the entries of the step launched last
         self._prepared = None              # (entries, context, requests) of a step described ahead
         self._flight = None                # (plan, entries, samplers, ticket) of a launched step
         self.ahead = {"used": 0, "dropped": 0, "dead_rows": 0}
@@ -151,11 +152,15 @@ class Engine:
     def _launch(self, plan: Plan, entries: List[Entry], ctx, samplers: List[Request]):
         if self.timing_events is not None:
             self.runner.start_event = self.timing_events[0][self.step_index]
+        self.launched_entries = entries
         logits = self.runner.launch(ctx, entries)
         self.runner.start_event = None
         ticket = None
         if samplers:
             self._launch_choice(logits, samplers)
+        if self.timing_events is not None:             # the step's device work ends here
+            self.timing_events[1][self.step_index].record()
+        if samplers:
             ticket = self.runner.queue_result()
         return (plan, entries, samplers, ticket)
 
@@ -266,8 +271,6 @@ class Engine:
                        top_k=self._p["top_k"][1], top_p=self._p["top_p"][1],
                        seeds=self._p["seeds"][1], fresh=self._p["fresh"][1],
                        slots=self._p["slots"][1], rng_states=self.rng_states)
-        if self.timing_events is not None:
-            self.timing_events[1][self.step_index].record()
 
     # ------------------------------------------------------------------ generate
     def run(self) -> None:

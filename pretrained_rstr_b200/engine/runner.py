@@ -87,7 +87,7 @@ class ModelRunner:
                                       device=self.device)
         self.scratch = ScratchPool(self.device)
         self.fail_next_step: Optional[Exception] = None      # host-side fault injection (tests)
-        self.counters = {"steps": 0, "tokens": 0, "cow_copies": 0}
+        self.counters = {"steps": 0, "launched": 0, "tokens": 0, "cow_copies": 0}
         self.last_h2d_bytes = 0
         self.start_event = None                       # optional CUDA event recorded before the copy
 
@@ -124,6 +124,7 @@ class ModelRunner:
             self.abort(entries)
             raise
         self.commit(entries)
+        self.counters["launched"] += 1
         return logits[:ctx.n_rows]
 
     def patch_tokens(self, ctx: StepContext, entries: Sequence[Entry]) -> None:
