@@ -139,6 +139,13 @@ def _declare(h: ctypes.CDLL) -> None:
                                         I, P, P]
     h.prb_attention_decode.argtypes = [P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I,
                                        P, P, I, I, P, P]
+    h.prb_attention_decode_ring.argtypes = [P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F,
+                                            I, I, P, P, I, I, P, P]
+    h.prb_attention_decode_ring.restype = c_int
+    h.prb_attention_decode_ring_supports.argtypes = [I, I]
+    h.prb_attention_decode_ring_supports.restype = c_int
+    h.prb_attention_decode_ring_workspace.argtypes = [I, I, I]
+    h.prb_attention_decode_ring_workspace.restype = L
     h.prb_attention_prefill.argtypes = [P, L, P, L, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F,
                                         I, P, P]
     h.prb_attention_prefill_supports.argtypes = [I]
@@ -270,6 +277,11 @@ class Program:
                 self.handle = None
         except Exception:
             pass
+
+
+def recording() -> bool:
+    """Whether a decode program is recording (kernels it cannot hold must not be chosen)."""
+    return _RECORDER is not None
 
 
 def _no_record(what: str) -> None:
@@ -634,6 +646,45 @@ def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positi
         kv_heads, head_dim, page_size, block_table.shape[1], num_pages, float(scale),
         int(window or 0), _p(workspace), _p(counters), max_splits, split_keys, _p(status),
         _stream()), what)
+
+
+def decode_ring_supports(head_dim: int, page_size: int) -> bool:
+    return bool(lib().prb_attention_decode_ring_supports(int(head_dim), int(page_size)))
+
+
+def decode_ring_workspace(n_list: int, n_heads: int, head_dim: int) -> int:
+    """float32 elements of workspace ``attention_decode_ring`` needs for up to ``n_list`` tokens."""
+    return int(lib().prb_attention_decode_ring_workspace(int(n_list), int(n_heads), int(head_dim)))
+
+
+def attention_decode_ring(out, q, k_pages, v_pages, block_table, seq_of_token, positions,
+                          token_list, token_count, n_list, n_heads, scale, window, workspace,
+                          counters, status, new_keys: int = 1, stages: int = 0,
+                          max_context: int = 0) -> None:
+    """bfloat16 attention of single tokens over their requests' pages by persistent CTAs whose
+    warps stream keys and values through rings of shared-memory buffers; what was cached before
+    the step is requested before the kernel this one depends on has finished (head size 64).
+    ``new_keys``: how many of a token's last visible positions the step itself may have
+    written.  ``workspace``: ``decode_ring_workspace`` floats; ``counters`` int32
+    [n_list * heads], zero (left zero)."""
+    what = "attention_decode_ring"
+    _no_record(what)
+    num_pages, kv_heads, page_size, head_dim = k_pages.shape
+    for name, t in (("out", out), ("q", q)):
+        if t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != n_heads * head_dim:
+            raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
+    if k_pages.dtype != torch.bfloat16 or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise KernelArgumentError(f"{what}: the cache must be contiguous bfloat16")
+    if workspace.dtype != torch.float32 or \
+            workspace.numel() < decode_ring_workspace(n_list, n_heads, head_dim) or \
+            counters.dtype != torch.int32 or counters.numel() < n_list * n_heads:
+        raise KernelArgumentError(f"{what}: scratch too small or of the wrong type")
+    _check(lib().prb_attention_decode_ring(
+        _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(block_table),
+        _p(seq_of_token), _p(positions), _p(token_list), _p(token_count), n_list, n_heads,
+        kv_heads, head_dim, page_size, block_table.shape[1], num_pages, float(scale),
+        int(window or 0), int(new_keys), _p(workspace), _p(counters), int(stages),
+        int(max_context), _p(status), _stream()), what)
 
 
 def prefill_tile() -> int:

@@ -5,17 +5,23 @@
 // Greedy: the first maximum wins, so ties go to the lowest id, and a NaN wins over
 // every number (gpt2.clj:264-270; decoder_gpu.clj:68-70).
 //
-// Sampling: the k candidates are found in descending order (equal logits: lower id
-// first, as sampling.clj:14-29 leaves them), then one thread does the remaining
-// arithmetic in double precision and in the reference's order of operations.  Draws
-// come from a per-request 48-bit linear congruential generator with the constants of
-// java.util.Random (sampling.clj:43, 61 draws from java.util.Random(seed)); its state
-// lives in the request's state slot, so a request's draws do not depend on the batch.
+// Sampling: the k largest logits are selected in a few passes over the row, whatever k is:
+// a radix select on an order-preserving 32-bit key (three passes of 11, 11 and 10 bits with
+// shared-memory histograms) finds the key of the k-th largest logit, one more pass collects
+// everything above it and, of the logits equal to it, the lowest ids; the candidates are
+// then sorted (larger logit first, equal logits: lower id first, as sampling.clj:14-29
+// leaves them) by a bitonic sort in shared memory.  The exponentials are computed one per
+// thread in double precision; one thread then does the sums, the nucleus cut and the draw
+// in the reference's order of operations.  Draws come from a per-request 48-bit linear
+// congruential generator with the constants of java.util.Random (sampling.clj:43, 61 draws
+// from java.util.Random(seed)); its state lives in the request's state slot, so a request's
+// draws do not depend on the batch.
 #include "common.cuh"
 
 namespace {
 constexpr int SAMPLE_THREADS = 1024;
 constexpr int MAX_TOP_K = 1024;
+constexpr int HIST_COPIES = 4;        // private copies of the histogram (fewer collisions)
 
 struct Best {
     float v;
@@ -51,6 +57,18 @@ __device__ __forceinline__ Best block_best(Best b, Best* sh) {
     return r;   // identical in every thread of every warp
 }
 
+// Order-preserving key of a logit: larger logit, larger key.  NaN counts as -infinity (as in
+// the candidate search of the reference's sampler a NaN never beats a number) and -0 as +0.
+__device__ __forceinline__ unsigned sample_key(float v) {
+    if (isnan(v)) v = -INFINITY;
+    v += 0.0f;
+    const unsigned u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float sample_value(unsigned key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+
 __device__ __forceinline__ unsigned long long lcg_next(unsigned long long* s, int bits) {
     *s = (*s * 0x5DEECE66DULL + 0xBULL) & ((1ULL << 48) - 1);
     return *s >> (48 - bits);
@@ -63,8 +81,11 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
               const int* __restrict__ fresh, const int* __restrict__ slots,
               unsigned long long* __restrict__ rng_states, int n_rows) {
     __shared__ Best sh[32];
-    __shared__ int cand_id[MAX_TOP_K];
-    __shared__ float cand_v[MAX_TOP_K];
+    // histograms of the selection; afterwards the candidates (64-bit sort keys) and their
+    // exponentials
+    __shared__ __align__(16) unsigned char work[HIST_COPIES * 2048 * sizeof(unsigned)];
+    __shared__ int pick_sh[8];
+    __shared__ int warp_count[32];
     const int r = blockIdx.x;
     if (r >= n_rows) return;
     const float* row = logits + (size_t)r * row_stride;
@@ -93,41 +114,147 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
     if (k > vocab) k = vocab;
     if (k > MAX_TOP_K) k = MAX_TOP_K;
     if (k < 1) k = 1;
-    // k rounds: the best element that comes after the previous pick in (value desc, id asc)
-    float pv = 0.0f;
-    int pi = -1;
-    for (int round = 0; round < k; ++round) {
-        Best b{0.0f, -1};
+
+    // ---- the key of the k-th largest logit, most significant bits first
+    unsigned* hist = reinterpret_cast<unsigned*>(work);               // [HIST_COPIES][2048]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned prefix = 0u, decided = 0u;
+    int need = k;                        // how many of the logits under the current prefix are taken
+    unsigned equal_count = 0u;           // logits whose key equals the k-th largest's
+#pragma unroll 1
+    for (int pass = 0; pass < 3; ++pass) {
+        const int shift = pass == 0 ? 21 : pass == 1 ? 10 : 0;
+        const unsigned bins = pass == 2 ? 1024u : 2048u;
+        for (unsigned i = threadIdx.x; i < HIST_COPIES * 2048u; i += blockDim.x) hist[i] = 0u;
+        __syncthreads();
+        unsigned* mine = hist + (warp % HIST_COPIES) * 2048;
         for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            float v = row[i];
-            if (isnan(v)) v = -INFINITY;
-            if (pi >= 0 && !(v < pv || (v == pv && i > pi))) continue;
-            if (b.i < 0 || v > b.v || (v == b.v && i < b.i)) { b.v = v; b.i = i; }
+            const unsigned key = sample_key(row[i]);
+            if ((key & decided) == prefix) atomicAdd(&mine[(key >> shift) & (bins - 1u)], 1u);
         }
-        b = block_best(b, sh);
-        if (threadIdx.x == 0) { cand_id[round] = b.i; cand_v[round] = b.v; }
-        pv = b.v;
-        pi = b.i;
-        if (pi < 0) { k = round; break; }
+        __syncthreads();
+        for (unsigned i = threadIdx.x; i < bins; i += blockDim.x) {
+            unsigned c = hist[i];
+#pragma unroll
+            for (int j = 1; j < HIST_COPIES; ++j) c += hist[j * 2048 + i];
+            hist[i] = c;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            // lane l owns bins [hi - per, hi) counted from the top; find where the count of
+            // larger keys passes `need`
+            const int per = (int)bins / 32;
+            const int top = (int)bins - lane * per;             // exclusive upper bin of this lane
+            unsigned mine_sum = 0u;
+            for (int j = 1; j <= per; ++j) mine_sum += hist[top - j];
+            unsigned incl = mine_sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            const unsigned above = incl - mine_sum;             // keys in bins above this lane's
+            if (above < (unsigned)need && incl >= (unsigned)need) {
+                unsigned seen = above;
+                for (int j = 1; j <= per; ++j) {
+                    const unsigned c = hist[top - j];
+                    if (seen + c >= (unsigned)need) {
+                        pick_sh[0] = top - j;                   // the bin of the k-th largest
+                        pick_sh[1] = need - (int)seen;          // still to take inside it
+                        pick_sh[2] = (int)c;
+                        break;
+                    }
+                    seen += c;
+                }
+            }
+        }
+        __syncthreads();
+        prefix |= (unsigned)pick_sh[0] << shift;
+        decided |= (bins - 1u) << shift;
+        need = pick_sh[1];
+        equal_count = (unsigned)pick_sh[2];
+        __syncthreads();
+    }
+    const unsigned kth = prefix;                       // key of the k-th largest logit
+    const int n_greater = k - need;                    // logits strictly above it
+
+    // ---- collect: everything above, and `need` of the equal ones, lowest ids first
+    unsigned long long* cand = reinterpret_cast<unsigned long long*>(work);   // [MAX_TOP_K]
+    __syncthreads();
+    if (threadIdx.x == 0) { pick_sh[3] = 0; pick_sh[4] = 0; }
+    __syncthreads();
+    const bool all_equal_taken = equal_count == (unsigned)need;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const unsigned key = sample_key(row[i]);
+        if (key > kth) {
+            const int slot = atomicAdd(&pick_sh[3], 1);
+            cand[slot] = ((unsigned long long)key << 32) | (unsigned)(0x7fffffff - i);
+        } else if (key == kth && all_equal_taken) {
+            const int slot = n_greater + atomicAdd(&pick_sh[4], 1);
+            cand[slot] = ((unsigned long long)key << 32) | (unsigned)(0x7fffffff - i);
+        }
+    }
+    if (!all_equal_taken) {
+        // more equal logits than are wanted: the lowest ids, found in id order
+        int base = 0;
+        for (int start = 0; start < vocab && base < need; start += blockDim.x) {
+            const int i = start + threadIdx.x;
+            const bool hit = i < vocab && sample_key(row[i]) == kth;
+            const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+            if (lane == 0) warp_count[warp] = __popc(ballot);
+            __syncthreads();
+            int before = 0, total = 0;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+                const int c = warp_count[w];
+                if (w < warp) before += c;
+                total += c;
+            }
+            const int rank = base + before + __popc(ballot & ((1u << lane) - 1u));
+            if (hit && rank < need)
+                cand[n_greater + rank] = ((unsigned long long)kth << 32) | (unsigned)(0x7fffffff - i);
+            base += total;
+            __syncthreads();
+        }
+    }
+    // ---- sort: larger key first, equal keys: lower id first (both by one 64-bit compare)
+    int n2 = 1;
+    while (n2 < k) n2 <<= 1;
+    __syncthreads();
+    for (int i = k + threadIdx.x; i < n2; i += blockDim.x) cand[i] = 0ULL;     // below every key
+    __syncthreads();
+    for (int size = 2; size <= n2; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int i = threadIdx.x; i < n2 / 2; i += blockDim.x) {
+                const int lo = 2 * i - (i & (stride - 1));      // partner pairs (lo, lo + stride)
+                const int hi = lo + stride;
+                const bool descending = (lo & size) == 0;
+                const unsigned long long a = cand[lo], b2 = cand[hi];
+                if ((a < b2) == descending) { cand[lo] = b2; cand[hi] = a; }
+            }
+            __syncthreads();
+        }
+    }
+    double* e = reinterpret_cast<double*>(work + MAX_TOP_K * sizeof(unsigned long long));   // [MAX_TOP_K]
+    const double t = (double)temp;
+    {
+        const double mx = (double)sample_value((unsigned)(cand[0] >> 32)) / t;
+        for (int j = threadIdx.x; j < k; j += blockDim.x)
+            e[j] = exp((double)sample_value((unsigned)(cand[j] >> 32)) / t - mx);
     }
     __syncthreads();
     if (threadIdx.x != 0) return;
-    if (k == 0) { out[r] = 0; return; }
 
-    const double t = (double)temp;
     const double p = (double)top_p[r];
-    const double mx = (double)cand_v[0] / t;
-    // probabilities are recomputed where needed instead of stored: k <= 1024 exps
     double psum = 0.0;
-    for (int j = 0; j < k; ++j) psum += exp((double)cand_v[j] / t - mx);
+    for (int j = 0; j < k; ++j) psum += e[j];
     int cut = k;
     double c = 0.0;
     for (int j = 0; j < k; ++j) {
-        c += exp((double)cand_v[j] / t - mx) / psum;
+        c += e[j] / psum;
         if (c >= p) { cut = j + 1; break; }
     }
     double tot = 0.0;
-    for (int j = 0; j < cut; ++j) tot += exp((double)cand_v[j] / t - mx);
+    for (int j = 0; j < cut; ++j) tot += e[j];
 
     unsigned long long* state = rng_states + slots[r];
     unsigned long long s = *state;
@@ -137,10 +264,10 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
     const double u = (double)((hi << 27) + lo) * (1.0 / 9007199254740992.0);
     const double draw = u * tot;
     double acc = 0.0;
-    int pick = cand_id[cut - 1];
+    int pick = 0x7fffffff - (int)(unsigned)(cand[cut - 1] & 0xffffffffULL);
     for (int j = 0; j < cut; ++j) {
-        acc += exp((double)cand_v[j] / t - mx);
-        if (acc >= draw || j == cut - 1) { pick = cand_id[j]; break; }
+        acc += e[j];
+        if (acc >= draw || j == cut - 1) { pick = 0x7fffffff - (int)(unsigned)(cand[j] & 0xffffffffULL); break; }
     }
     out[r] = pick;
 }

@@ -9,7 +9,6 @@ Only token ids cross the host/device boundary: ids in, one int32 per sampled row
 """
 from __future__ import annotations
 
-import os
 from typing import Callable, Dict, Hashable, List, Optional, Sequence
 
 import torch
@@ -17,7 +16,8 @@ import torch
 from ..csrc import ops
 from .batch import Entry
 from .loading import LoadedModel
-from .scheduler import Plan, Request, SamplingParams, Scheduled, Scheduler, SchedulerOptions
+from ..sampling import Sampler, SamplingParams
+from .scheduler import Plan, Request, Scheduled, Scheduler, SchedulerOptions
 
 
 class Engine:
@@ -31,32 +31,9 @@ class Engine:
             raise ValueError("scheduler capacities exceed what the runtime was loaded with")
         self.scheduler = Scheduler(self.opts, lm.cache)
         self.runner = lm.runner
-        dev, n = rt.device, rt.max_requests
         # per-request sampler state lives in the request's state slot
-        self.rng_states = torch.zeros(n, dtype=torch.int64, device=dev)
-        self._rng_started: Dict[Hashable, bool] = {}
+        self.sampler = Sampler(rt.max_requests, rt.device, lm.cache.slot)
         self._tokens_dev = self.runner.tokens_out
-        def option_buffers():
-            # pinned staging and device copies of the sampler's per-row options
-            return {
-                "temperature": (torch.zeros(n, dtype=torch.float32, pin_memory=True),
-                                torch.zeros(n, dtype=torch.float32, device=dev)),
-                "top_p": (torch.zeros(n, dtype=torch.float32, pin_memory=True),
-                          torch.zeros(n, dtype=torch.float32, device=dev)),
-                "top_k": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
-                          torch.zeros(n, dtype=torch.int32, device=dev)),
-                "fresh": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
-                          torch.zeros(n, dtype=torch.int32, device=dev)),
-                "slots": (torch.zeros(n, dtype=torch.int32, pin_memory=True),
-                          torch.zeros(n, dtype=torch.int32, device=dev)),
-                "seeds": (torch.zeros(n, dtype=torch.int64, pin_memory=True),
-                          torch.zeros(n, dtype=torch.int64, device=dev)),
-            }
-        # two sets take turns: with a step in flight the set of the step before is free
-        self._option_sets = [option_buffers(), option_buffers()]
-        self._option_turn = 0
-        self._p = self._option_sets[0]
-        self.max_top_k = ops.max_top_k()
         # optional (start events, end events) lists: step ``step_index`` records its pair
         # around the device work of the step (measurement only)
         self.timing_events = None
@@ -71,15 +48,7 @@ class Engine:
                sampling: Optional[SamplingParams] = None, eos_ids: Sequence[int] = (),
                on_token: Optional[Callable[[Hashable, int], None]] = None) -> Request:
         sampling = sampling or SamplingParams()
-        if not sampling.greedy:
-            k = 40 if sampling.top_k is None else int(sampling.top_k)
-            if k < 1:
-                raise ValueError("top_k must be >= 1")
-            if min(k, self.lm.model.vocab) > self.max_top_k:
-                raise ValueError(f"top_k={k} exceeds the sampling kernel's limit of {self.max_top_k}")
-            p = 1.0 if sampling.top_p is None else float(sampling.top_p)
-            if not 0.0 < p <= 1.0:
-                raise ValueError("top_p must be in (0, 1]")
+        sampling.validate(self.lm.model.vocab, self.sampler.max_top_k)
         vocab = self.lm.model.vocab
         for t in prompt:
             if not 0 <= int(t) < vocab:
@@ -157,7 +126,7 @@ class Engine:
         self.runner.start_event = None
         ticket = None
         if samplers:
-            self._launch_choice(logits, samplers)
+            self.sampler.launch(self._tokens_dev, logits, samplers)
         if self.timing_events is not None:             # the step's device work ends here
             self.timing_events[1][self.step_index].record()
         if samplers:
@@ -174,7 +143,7 @@ class Engine:
             self.ahead["dead_rows"] += sum(1 for r in samplers if r.rid not in self.scheduler.running)
         done = self.scheduler.complete(plan, new_tokens)
         for r in done:
-            self._rng_started.pop(r.rid, None)
+            self.sampler.forget(r.rid)
         return done
 
     # ------------------------------------------------------------- preparing ahead
@@ -240,37 +209,6 @@ class Engine:
             if e.rid in self.lm.cache.requests:
                 self.lm.cache.abort(e.rid)
         self.ahead["dropped"] += 1
-
-    def _launch_choice(self, logits: torch.Tensor, requests: List[Request]) -> None:
-        """Launch the kernel that chooses a token for every row (no synchronisation)."""
-        n = len(requests)
-        out = self._tokens_dev
-        if all(r.sampling.greedy for r in requests):
-            ops.sample(out, logits, n)
-        else:
-            self._option_turn ^= 1
-            self._p = self._option_sets[self._option_turn]
-            for i, r in enumerate(requests):
-                sp = r.sampling
-                self._p["temperature"][0][i] = 0.0 if sp.greedy else float(sp.temperature)
-                self._p["top_p"][0][i] = 1.0 if sp.top_p is None else float(sp.top_p)
-                self._p["top_k"][0][i] = 40 if sp.top_k is None else int(sp.top_k)
-                started = self._rng_started.get(r.rid, False)
-                self._p["fresh"][0][i] = 0 if started else 1
-                if not started and not sp.greedy:
-                    self._rng_started[r.rid] = True
-                self._p["slots"][0][i] = self.lm.cache.slot(r.rid)
-                if sp.seed is None:           # unseeded, like java.util.Random() without a seed
-                    seed = int.from_bytes(os.urandom(6), "little")
-                else:
-                    seed = int(sp.seed)
-                self._p["seeds"][0][i] = seed
-            for host, dev in self._p.values():
-                dev[:n].copy_(host[:n], non_blocking=True)
-            ops.sample(out, logits, n, temperature=self._p["temperature"][1],
-                       top_k=self._p["top_k"][1], top_p=self._p["top_p"][1],
-                       seeds=self._p["seeds"][1], fresh=self._p["fresh"][1],
-                       slots=self._p["slots"][1], rng_states=self.rng_states)
 
     # ------------------------------------------------------------------ generate
     def run(self) -> None:

@@ -17,26 +17,12 @@ model has positions) is refused at once with an error.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Callable, Dict, Hashable, List, Optional, Sequence, Tuple
 
 from ..cache.manager import CacheError, CacheManager, OutOfPages
-
-
-@dataclass
-class SamplingParams:
-    """Options of the reference's sampler (``src/pretrained/sampling.clj:31-43``):
-    ``temperature`` <= 0 is greedy; otherwise ``top_k`` defaults to 40 and ``top_p`` to
-    1.0, and draws come from a generator seeded with ``seed``."""
-
-    temperature: float = 0.0
-    top_k: Optional[int] = None
-    top_p: Optional[float] = None
-    seed: Optional[int] = None
-
-    @property
-    def greedy(self) -> bool:
-        return self.temperature is None or self.temperature <= 0.0
+from ..sampling.sampler import SamplingParams
 
 
 @dataclass
@@ -70,6 +56,7 @@ class SchedulerOptions:
     max_lanes: int = 64
     prefill_chunk: int = 128          # the reference's default (scheduler.clj:52-55)
     minimum_prefill_tokens: int = 0
+    keep_finished: int = 4096         # finished requests remembered for their caller to fetch
 
     def validate(self) -> None:
         for name in ("max_batched_tokens", "max_lanes", "prefill_chunk"):
@@ -141,7 +128,9 @@ class Scheduler:
         self.cache = cache
         self.waiting: List[Request] = []
         self.running: Dict[Hashable, Request] = {}
-        self.finished: Dict[Hashable, Request] = {}
+        # finished requests until their caller fetches them (``finished.pop(id)``); the oldest
+        # are forgotten beyond ``keep_finished`` so that a long-running loop does not grow
+        self.finished: "OrderedDict[Hashable, Request]" = OrderedDict()
         self._arrivals = 0
         self.stats = {"iterations": 0, "scheduled_tokens": 0, "admitted": 0,
                       "deferred_admissions": 0, "finished": 0}
@@ -284,6 +273,8 @@ class Scheduler:
             self.cache.close(r.rid)
             del self.running[r.rid]
         self.finished[r.rid] = r
+        while len(self.finished) > self.opts.keep_finished:
+            self.finished.popitem(last=False)
         self.stats["finished"] += 1
         return r
 

@@ -337,6 +337,16 @@ def profile_decode_attention(spec: str) -> int:
         res[f"split{split}"] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
                                 "ctas": nreq * nh * splits,
                                 "max_diff": float((out.float() - ref.float()).abs().max())}
+    if ops.decode_ring_supports(dh, ps):
+        ws = torch.zeros(ops.decode_ring_workspace(nreq, nh, dh), device="cuda")
+        counters = torch.zeros(nreq * nh, dtype=torch.int32, device="cuda")
+        for stages in (2, 3, 4):
+            out = torch.zeros_like(q)
+            us = _graph_time_us(lambda: ops.attention_decode_ring(
+                out, q, k, v, table, seq, pos, None, None, nreq, nh, 0.125, None, ws, counters,
+                status, new_keys=4, stages=stages, max_context=-(-ctx // 256) * 256))
+            res[f"ring_stages{stages}"] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+                                           "max_diff": float((out.float() - ref.float()).abs().max())}
     print(json.dumps({"profile_decode_attention": spec, "mbytes": round(nbytes / 1e6, 2),
                       "engine_split": chosen, "status": status.tolist(), **res}))
     return 0

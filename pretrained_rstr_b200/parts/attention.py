@@ -182,8 +182,19 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
                                   n_tiles, n_head, scale, window, ctx.status)
     if singles is None or singles > 0:
         n_list = work.caps["single_tokens"] if singles is None else singles
-        split_keys, max_splits = decode_splits(n_list * n_head, ctx.max_context, group.page_size)
         cap = ctx.runtime.max_requests * AttentionWork.SINGLE_MAX_Q
+        if SETTINGS.decode_ring and not ops.recording() and \
+                ops.decode_ring_supports(head_dim, group.page_size):
+            ws = ctx.scratch("attn_ring_ws", (ops.decode_ring_workspace(cap, n_head, head_dim),),
+                             torch.float32)
+            counters = ctx.scratch_zero("attn_decode_counters", (cap * n_head,), torch.int32)
+            ops.attention_decode_ring(out, q, cache.k, cache.v, group.block_table,
+                                      ctx.seq_of_token, ctx.positions, work.arrays["single_tokens"],
+                                      work.counts["singles"], n_list, n_head, scale, window, ws,
+                                      counters, ctx.status, new_keys=AttentionWork.SINGLE_MAX_Q,
+                                      max_context=ctx.max_context)
+            return
+        split_keys, max_splits = decode_splits(n_list * n_head, ctx.max_context, group.page_size)
         # room for the shortest splits any step may choose
         splits_cap = -(-ctx.max_positions // ops.decode_split())
         ws = ctx.scratch("attn_decode_ws", (cap * n_head * splits_cap * (head_dim + 4),),

@@ -282,6 +282,89 @@ def test_attention_decode_streaming_variant_gives_the_same_bits(nh, nkv, dh, ps,
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
 
 
+RING_CASES = [
+    # heads, kv heads, page size, window
+    (12, 12, 64, None), (6, 2, 64, None), (4, 2, 16, None), (3, 1, 8, 70), (5, 5, 128, 100),
+    (2, 2, 32, None),
+]
+
+
+@pytest.mark.parametrize("nh,nkv,ps,window", RING_CASES)
+@pytest.mark.parametrize("stages", [0, 2, 3, 4])
+def test_attention_decode_ring(nh, nkv, ps, window, stages):
+    """The ring kernel (persistent CTAs, keys and values by bulk copies into per-warp rings)
+    against the plain reference: contexts from 1 to 2,000 keys (a (token, head) shared by many
+    warps, and many of them to a warp), several tokens of one request, a token list, and the
+    unused tail of every page poisoned with NaN (what an earlier owner left must not leak)."""
+    ops = _ops()
+    dh = 64
+    assert ops.decode_ring_supports(dh, ps) and not ops.decode_ring_supports(48, ps)
+    lengths, portions = [1, 70, 300, 257, 2000, 256, 33, 1025], [1, 2, 1, 4, 1, 1, 3, 1]
+    q, k, v, table, seq, pos = _paged_case(11, nh, nkv, dh, ps, lengths, portions, torch.bfloat16)
+    for b, n in enumerate(lengths):                      # rows past a request's last token
+        last = int(table[b, (n - 1) // ps])
+        k[last, :, (n - 1) % ps + 1:, :] = float("nan")
+        v[last, :, (n - 1) % ps + 1:, :] = float("nan")
+    t = q.shape[0]
+    ws = torch.full((ops.decode_ring_workspace(t, nh, dh),), float("nan"), device="cuda")
+    counters = torch.zeros(t * nh, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ref = _ref_attention(q, k, v, table, seq, pos, nh, 0.2, window)
+    for _ in range(2):                                   # twice: the counters must be left at zero
+        out = torch.full_like(q, float("nan"))
+        ops.attention_decode_ring(out, q, k, v, table, seq, pos, None, None, t, nh, 0.2, window,
+                                  ws, counters, status, new_keys=4, stages=stages, max_context=2048)
+        torch.cuda.synchronize()
+        assert status.tolist() == [0, 0, 0, 0]
+        err = (out.float() - ref).abs()
+        assert float(err.max()) <= 2e-2, f"worst token {int(err.max(dim=1).values.argmax())}"
+        assert int(counters.abs().sum()) == 0
+    # a token list picks tokens (its length on the device); the others are not touched
+    order = torch.tensor([t - 1, 0, 5, 3], dtype=torch.int32, device="cuda")
+    count = torch.tensor([3], dtype=torch.int32, device="cuda")
+    out = torch.zeros_like(q)
+    ops.attention_decode_ring(out, q, k, v, table, seq, pos, order, count, 4, nh, 0.2, window, ws,
+                              counters, status, new_keys=4, stages=stages, max_context=2048)
+    for i in (t - 1, 0, 5):
+        assert float((out[i].float() - ref[i]).abs().max()) <= 2e-2
+    assert float(out[3].abs().max()) == 0.0
+    # a position beyond the block table is recorded, not read
+    bad = pos.clone()
+    bad[0] = table.shape[1] * ps + 5
+    ops.attention_decode_ring(out, q, k, v, table, seq, bad, None, None, t, nh, 0.2, window, ws,
+                              counters, status, new_keys=4, stages=stages, max_context=2048)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 2
+
+
+def test_attention_decode_ring_sees_what_the_step_appended():
+    """The kernel asks for old keys before the kernel it depends on has finished, and for the
+    rows the step itself wrote only afterwards: a far key written by the kernel right before it
+    in the stream, at the token's own position and three before it, must be seen."""
+    ops = _ops()
+    nh, dh, ps, n = 2, 64, 64, 1000
+    q, k, v, table, seq, pos = _paged_case(4, nh, nh, dh, ps, [n], [1], torch.bfloat16)
+    ws = torch.zeros(ops.decode_ring_workspace(1, nh, dh), device="cuda")
+    counters = torch.zeros(nh, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    big = (q[0].view(nh, dh) * 4.0).clone()
+    for back in (0, 3):
+        kk, vv = k.clone(), v.clone()
+        p = n - 1 - back
+        page, off = int(table[0, p // ps]), p % ps
+        out = torch.zeros_like(q)
+        # a long kernel first, then the write, then attention: all on one stream
+        filler = torch.randn(4096, 4096, device="cuda")
+        for _ in range(3):
+            filler = filler @ filler
+        kk[page, :, off, :] = big                      # aligned with the query: huge score
+        ops.attention_decode_ring(out, q, kk, vv, table, seq, pos, None, None, 1, nh, 0.125, None,
+                                  ws, counters, status, new_keys=4, max_context=1024)
+        torch.cuda.synchronize()
+        assert status.tolist() == [0, 0, 0, 0]
+        assert float((out[0].view(nh, dh).float() - vv[page, :, off].float()).abs().max()) < 0.05, back
+
+
 def _prefill_parts(units, most):
     """Workspace of the tensor-memory prompt kernel's key parts."""
     return (torch.empty(units * most * 8192, device="cuda"),
@@ -508,6 +591,47 @@ def test_sample_kernel_greedy_ties_and_nan():
     want = logits.argmax(dim=1).tolist()
     want[1], want[2], want[3] = 77, 123, 50256
     assert out.tolist() == want
+
+
+@pytest.mark.parametrize("vocab", [50257, 1000, 37])
+def test_sample_kernel_matches_the_plain_sampler(vocab):
+    """Top-k selection (any k up to the limit, ties, NaN, rows of equal logits), temperature
+    softmax, nucleus cut and the draw: the same token as the plain sampler on the same row,
+    and the generator state left for the next draw."""
+    import plain_gpt2
+    ops = _ops()
+    g = torch.Generator(device="cpu").manual_seed(vocab)
+    rows = torch.randn(12, vocab, generator=g) * 0.7
+    rows[1, 5] = rows[1, vocab - 1] = rows[1, 17] = 2.5        # ties among the candidates
+    rows[2, 3] = float("nan")                                   # never a candidate
+    rows[3, :] = 0.25                                           # all equal: the lowest ids
+    rows[4, ::2] = -0.0                                         # -0 and +0 tie
+    rows[4, 1::2] = 0.0
+    rows[5] = torch.round(rows[5] * 4) / 4                      # many ties at the k-th value
+    rows[6, 9] = float("-inf")
+    ks = [40, 40, 40, 7, 5, 40, 40, 1, min(1024, vocab), 3, min(300, vocab), 40]
+    ps = [1.0, 1.0, 0.9, 1.0, 1.0, 0.5, 1.0, 1.0, 0.95, 0.3, 1.0, 0.999]
+    ts = [0.8, 1.0, 0.7, 1.3, 0.9, 0.8, 2.0, 0.5, 1.0, 0.8, 0.6, 1.5]
+    n = rows.shape[0]
+    logits = rows.cuda()
+    out = torch.zeros(n, dtype=torch.int32, device="cuda")
+    states = torch.zeros(n, dtype=torch.int64, device="cuda")
+    args = dict(temperature=torch.tensor(ts, device="cuda"),
+                top_k=torch.tensor(ks, dtype=torch.int32, device="cuda"),
+                top_p=torch.tensor(ps, device="cuda"),
+                seeds=torch.arange(100, 100 + n, dtype=torch.int64, device="cuda"),
+                slots=torch.arange(n, dtype=torch.int32, device="cuda"), rng_states=states)
+    rngs = [plain_gpt2.JavaRandom(100 + i) for i in range(n)]
+    for draw in range(3):                       # the second and third draw go on from the state
+        fresh = torch.full((n,), 1 if draw == 0 else 0, dtype=torch.int32, device="cuda")
+        ops.sample(out, logits, n, fresh=fresh, **args)
+        got = out.tolist()
+        for i in range(n):
+            # (the kernel's temperature is a float32, the plain sampler gets the same value)
+            t32 = float(torch.tensor(ts[i], dtype=torch.float32))
+            p32 = float(torch.tensor(ps[i], dtype=torch.float32))
+            want = plain_gpt2.sample(rows[i], t32, ks[i], p32, rngs[i])
+            assert got[i] == want, f"row {i}, draw {draw}: {got[i]} != {want}"
 
 
 def test_gemm_smallm_scatters_keys_and_values_to_the_cache():
