@@ -140,10 +140,14 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_attention_decode.argtypes = [P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I,
                                        P, P, I, I, P, P]
     h.prb_attention_decode_ring.argtypes = [P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F,
-                                            I, I, P, P, I, I, P, P]
+                                            I, I, P, P, L, P, P, I, I, P, P]
+    h.prb_attention_decode_ring_tune.argtypes = [I, I]
+    h.prb_attention_decode_ring_tune.restype = c_int
     h.prb_attention_decode_ring.restype = c_int
     h.prb_attention_decode_ring_supports.argtypes = [I, I]
     h.prb_attention_decode_ring_supports.restype = c_int
+    h.prb_attention_decode_ring_max_list.argtypes = []
+    h.prb_attention_decode_ring_max_list.restype = c_int
     h.prb_attention_decode_ring_workspace.argtypes = [I, I, I]
     h.prb_attention_decode_ring_workspace.restype = L
     h.prb_attention_prefill.argtypes = [P, L, P, L, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F,
@@ -652,6 +656,11 @@ def decode_ring_supports(head_dim: int, page_size: int) -> bool:
     return bool(lib().prb_attention_decode_ring_supports(int(head_dim), int(page_size)))
 
 
+def decode_ring_max_list() -> int:
+    """Most single tokens a launch of ``attention_decode_ring`` takes."""
+    return int(lib().prb_attention_decode_ring_max_list())
+
+
 def decode_ring_workspace(n_list: int, n_heads: int, head_dim: int) -> int:
     """float32 elements of workspace ``attention_decode_ring`` needs for up to ``n_list`` tokens."""
     return int(lib().prb_attention_decode_ring_workspace(int(n_list), int(n_heads), int(head_dim)))
@@ -660,12 +669,15 @@ def decode_ring_workspace(n_list: int, n_heads: int, head_dim: int) -> int:
 def attention_decode_ring(out, q, k_pages, v_pages, block_table, seq_of_token, positions,
                           token_list, token_count, n_list, n_heads, scale, window, workspace,
                           counters, status, new_keys: int = 1, stages: int = 0,
-                          max_context: int = 0) -> None:
+                          max_context: int = 0, kv_new=None) -> None:
     """bfloat16 attention of single tokens over their requests' pages by persistent CTAs whose
     warps stream keys and values through rings of shared-memory buffers; what was cached before
     the step is requested before the kernel this one depends on has finished (head size 64).
     ``new_keys``: how many of a token's last visible positions the step itself may have
-    written.  ``workspace``: ``decode_ring_workspace`` floats; ``counters`` int32
+    written (at most 4).  ``kv_new`` = (k, v): the step's own keys and values, row t for token t
+    ([T, kv_heads * head_dim], may be column slices of a wider tensor), as the product before
+    this kernel left them; with them no part of the kernel waits for the cache rows the step
+    appended.  ``workspace``: ``decode_ring_workspace`` floats; ``counters`` int32
     [n_list * heads], zero (left zero)."""
     what = "attention_decode_ring"
     _no_record(what)
@@ -679,12 +691,22 @@ def attention_decode_ring(out, q, k_pages, v_pages, block_table, seq_of_token, p
             workspace.numel() < decode_ring_workspace(n_list, n_heads, head_dim) or \
             counters.dtype != torch.int32 or counters.numel() < n_list * n_heads:
         raise KernelArgumentError(f"{what}: scratch too small or of the wrong type")
+    k_new = v_new = None
+    kv_stride = 0
+    if kv_new is not None:
+        k_new, v_new = kv_new
+        for name, t in (("k_new", k_new), ("v_new", v_new)):
+            if t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != kv_heads * head_dim:
+                raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
+        if k_new.stride(0) != v_new.stride(0):
+            raise KernelArgumentError(f"{what}: k_new and v_new row strides differ")
+        kv_stride = k_new.stride(0)
     _check(lib().prb_attention_decode_ring(
         _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(block_table),
         _p(seq_of_token), _p(positions), _p(token_list), _p(token_count), n_list, n_heads,
         kv_heads, head_dim, page_size, block_table.shape[1], num_pages, float(scale),
-        int(window or 0), int(new_keys), _p(workspace), _p(counters), int(stages),
-        int(max_context), _p(status), _stream()), what)
+        int(window or 0), int(new_keys), _p(k_new), _p(v_new), int(kv_stride), _p(workspace),
+        _p(counters), int(stages), int(max_context), _p(status), _stream()), what)
 
 
 def prefill_tile() -> int:

@@ -15,13 +15,17 @@
 // in the reference's order of operations.  Draws come from a per-request 48-bit linear
 // congruential generator with the constants of java.util.Random (sampling.clj:43, 61 draws
 // from java.util.Random(seed)); its state lives in the request's state slot, so a request's
-// draws do not depend on the batch.
+// draws do not depend on the batch.  A NaN or -infinity logit counts as a candidate of weight
+// zero (the reference's search skips it and leaves its candidate slot at id 0; the two differ
+// only when k exceeds the number of finite logits of a row).
 #include "common.cuh"
 
 namespace {
 constexpr int SAMPLE_THREADS = 1024;
 constexpr int MAX_TOP_K = 1024;
 constexpr int HIST_COPIES = 4;        // private copies of the histogram (fewer collisions)
+constexpr int CAND_CAP = 4096;        // candidates the fast path sorts (8 bytes each)
+static_assert(CAND_CAP * 8 >= HIST_COPIES * 2048 * 4, "the histograms share the candidates' memory");
 
 struct Best {
     float v;
@@ -69,6 +73,34 @@ __device__ __forceinline__ float sample_value(unsigned key) {
     return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
 }
 
+// Visit every logit of a row once: f(index, value).  The row's start need not be aligned
+// (rows of an odd vocabulary are not): up to three leading elements and the tail are read one
+// by one, the rest as 16-byte loads, four of them in flight per thread, because what such a
+// pass costs is the round trips to the L2, not the bytes.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ row, int vocab, F f) {
+    const int head = min(vocab, (int)((4u - (unsigned)(((uintptr_t)row >> 2) & 3u)) & 3u));
+    const int nvec = (vocab - head) >> 2;
+    const int tail0 = head + 4 * nvec;
+    if ((int)threadIdx.x < head) f((int)threadIdx.x, row[threadIdx.x]);
+    if ((int)threadIdx.x < vocab - tail0) f(tail0 + (int)threadIdx.x, row[tail0 + threadIdx.x]);
+    const float4* vec = reinterpret_cast<const float4*>(row + head);
+    const int bd = blockDim.x;
+    for (int j = threadIdx.x; j < nvec; j += 4 * bd) {
+        const int j1 = j + bd, j2 = j + 2 * bd, j3 = j + 3 * bd;
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 v0 = vec[j];
+        const float4 v1 = j1 < nvec ? vec[j1] : z;
+        const float4 v2 = j2 < nvec ? vec[j2] : z;
+        const float4 v3 = j3 < nvec ? vec[j3] : z;
+        const int b0 = head + 4 * j;
+        f(b0, v0.x); f(b0 + 1, v0.y); f(b0 + 2, v0.z); f(b0 + 3, v0.w);
+        if (j1 < nvec) { const int b = head + 4 * j1; f(b, v1.x); f(b + 1, v1.y); f(b + 2, v1.z); f(b + 3, v1.w); }
+        if (j2 < nvec) { const int b = head + 4 * j2; f(b, v2.x); f(b + 1, v2.y); f(b + 2, v2.z); f(b + 3, v2.w); }
+        if (j3 < nvec) { const int b = head + 4 * j3; f(b, v3.x); f(b + 1, v3.y); f(b + 2, v3.z); f(b + 3, v3.w); }
+    }
+}
+
 __device__ __forceinline__ unsigned long long lcg_next(unsigned long long* s, int bits) {
     *s = (*s * 0x5DEECE66DULL + 0xBULL) & ((1ULL << 48) - 1);
     return *s >> (48 - bits);
@@ -83,8 +115,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
     __shared__ Best sh[32];
     // histograms of the selection; afterwards the candidates (64-bit sort keys) and their
     // exponentials
-    __shared__ __align__(16) unsigned char work[HIST_COPIES * 2048 * sizeof(unsigned)];
-    __shared__ int pick_sh[8];
+    __shared__ __align__(16) unsigned char work[CAND_CAP * sizeof(unsigned long long) + MAX_TOP_K * sizeof(double)];
+    __shared__ int pick_sh[8];    // [0..2] radix select, [3..4] its collect counters, [5] candidates, [6] bound
     __shared__ int warp_count[32];
     const int r = blockIdx.x;
     if (r >= n_rows) return;
@@ -93,18 +125,9 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
 
     if (!(temp > 0.0f)) {
         Best b{0.0f, -1};
-        const int bd = blockDim.x;
-        for (int i = threadIdx.x; i < vocab; i += 4 * bd) {        // four loads in flight
-            const int i1 = i + bd, i2 = i + 2 * bd, i3 = i + 3 * bd;
-            const float v0 = row[i];
-            const float v1 = i1 < vocab ? row[i1] : 0.0f;
-            const float v2 = i2 < vocab ? row[i2] : 0.0f;
-            const float v3 = i3 < vocab ? row[i3] : 0.0f;
-            if (better(v0, i, b.v, b.i)) { b.v = v0; b.i = i; }
-            if (i1 < vocab && better(v1, i1, b.v, b.i)) { b.v = v1; b.i = i1; }
-            if (i2 < vocab && better(v2, i2, b.v, b.i)) { b.v = v2; b.i = i2; }
-            if (i3 < vocab && better(v3, i3, b.v, b.i)) { b.v = v3; b.i = i3; }
-        }
+        for_each_logit(row, vocab, [&](int i, float v) {
+            if (better(v, i, b.v, b.i)) { b.v = v; b.i = i; }
+        });
         b = block_best(b, sh);
         if (threadIdx.x == 0) out[r] = b.i;
         return;
@@ -115,131 +138,190 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
     if (k > MAX_TOP_K) k = MAX_TOP_K;
     if (k < 1) k = 1;
 
-    // ---- the key of the k-th largest logit, most significant bits first
-    unsigned* hist = reinterpret_cast<unsigned*>(work);               // [HIST_COPIES][2048]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    unsigned prefix = 0u, decided = 0u;
-    int need = k;                        // how many of the logits under the current prefix are taken
-    unsigned equal_count = 0u;           // logits whose key equals the k-th largest's
-#pragma unroll 1
-    for (int pass = 0; pass < 3; ++pass) {
-        const int shift = pass == 0 ? 21 : pass == 1 ? 10 : 0;
-        const unsigned bins = pass == 2 ? 1024u : 2048u;
-        for (unsigned i = threadIdx.x; i < HIST_COPIES * 2048u; i += blockDim.x) hist[i] = 0u;
+    unsigned long long* cand = reinterpret_cast<unsigned long long*>(work);   // [CAND_CAP]
+    auto sort_descending = [&](int count) {
+        // bitonic sort of cand[0, count): larger key first, equal keys: lower id first (one
+        // 64-bit compare does both); entries beyond `count` are padded below every key
+        int n2 = 1;
+        while (n2 < count) n2 <<= 1;
         __syncthreads();
-        unsigned* mine = hist + (warp % HIST_COPIES) * 2048;
-        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-            const unsigned key = sample_key(row[i]);
-            if ((key & decided) == prefix) atomicAdd(&mine[(key >> shift) & (bins - 1u)], 1u);
-        }
+        for (int i = count + threadIdx.x; i < n2; i += blockDim.x) cand[i] = 0ULL;
         __syncthreads();
-        for (unsigned i = threadIdx.x; i < bins; i += blockDim.x) {
-            unsigned c = hist[i];
-#pragma unroll
-            for (int j = 1; j < HIST_COPIES; ++j) c += hist[j * 2048 + i];
-            hist[i] = c;
-        }
-        __syncthreads();
-        if (warp == 0) {
-            // lane l owns bins [hi - per, hi) counted from the top; find where the count of
-            // larger keys passes `need`
-            const int per = (int)bins / 32;
-            const int top = (int)bins - lane * per;             // exclusive upper bin of this lane
-            unsigned mine_sum = 0u;
-            for (int j = 1; j <= per; ++j) mine_sum += hist[top - j];
-            unsigned incl = mine_sum;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const unsigned v = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += v;
+        for (int size = 2; size <= n2; size <<= 1) {
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                for (int i = threadIdx.x; i < n2 / 2; i += blockDim.x) {
+                    const int lo = 2 * i - (i & (stride - 1));      // pairs (lo, lo + stride)
+                    const int hi = lo + stride;
+                    const bool descending = (lo & size) == 0;
+                    const unsigned long long x = cand[lo], y = cand[hi];
+                    if ((x < y) == descending) { cand[lo] = y; cand[hi] = x; }
+                }
+                __syncthreads();
             }
-            const unsigned above = incl - mine_sum;             // keys in bins above this lane's
-            if (above < (unsigned)need && incl >= (unsigned)need) {
-                unsigned seen = above;
-                for (int j = 1; j <= per; ++j) {
-                    const unsigned c = hist[top - j];
-                    if (seen + c >= (unsigned)need) {
-                        pick_sh[0] = top - j;                   // the bin of the k-th largest
-                        pick_sh[1] = need - (int)seen;          // still to take inside it
-                        pick_sh[2] = (int)c;
-                        break;
+        }
+    };
+
+    // Order cand[0, count) (larger key first, equal keys: lower id first) by counting, for
+    // every entry, the entries that come before it: no barriers inside, `count` broadcast
+    // reads per entry.  The ordered entries go to `sorted` (another part of shared memory).
+    auto rank_sort = [&](int count, unsigned long long* sorted) {
+        __syncthreads();
+        for (int t = threadIdx.x; t < count; t += blockDim.x) {
+            const unsigned long long mine = cand[t];
+            int before = 0;
+            for (int j = 0; j < count; ++j) before += cand[j] > mine ? 1 : 0;
+            sorted[before] = mine;                                 // entries are distinct
+        }
+        __syncthreads();
+    };
+
+    // ---- a bound first: the k-th largest of the threads' own maxima.  At least k logits are
+    // that large, so every one of the k largest is; usually not many more are.
+    {
+        unsigned best = 0u;
+        for_each_logit(row, vocab, [&](int, float v) { best = max(best, sample_key(v)); });
+        // (made distinct by the thread's number, so that exactly one entry has each rank)
+        cand[threadIdx.x] = ((unsigned long long)best << 32) | (unsigned)(blockDim.x - 1 - threadIdx.x);
+        __syncthreads();
+        const unsigned long long mine = cand[threadIdx.x];
+        int before = 0;
+        for (int j = 0; j < (int)blockDim.x; ++j) before += cand[j] > mine ? 1 : 0;
+        if (before == k - 1) pick_sh[6] = (int)best;
+        __syncthreads();
+    }
+    const unsigned bound = (unsigned)pick_sh[6];
+    if (threadIdx.x == 0) pick_sh[5] = 0;
+    __syncthreads();
+    for_each_logit(row, vocab, [&](int i, float v) {
+        const unsigned key = sample_key(v);
+        if (key >= bound) {
+            const int slot = atomicAdd(&pick_sh[5], 1);
+            if (slot < CAND_CAP) cand[slot] = ((unsigned long long)key << 32) | (unsigned)(0x7fffffff - i);
+        }
+    });
+    __syncthreads();
+    int n_cand = pick_sh[5];
+    if (n_cand > CAND_CAP) {
+        // too many logits at or above the bound (long runs of equal logits, a large k): the
+        // exact key of the k-th largest by radix select, then exactly k candidates
+        __syncthreads();
+        // ---- the key of the k-th largest logit, most significant bits first
+        unsigned* hist = reinterpret_cast<unsigned*>(work);               // [HIST_COPIES][2048]
+        unsigned prefix = 0u, decided = 0u;
+        int need = k;                        // how many of the logits under the current prefix are taken
+        unsigned equal_count = 0u;           // logits whose key equals the k-th largest's
+    #pragma unroll 1
+        for (int pass = 0; pass < 3; ++pass) {
+            const int shift = pass == 0 ? 21 : pass == 1 ? 10 : 0;
+            const unsigned bins = pass == 2 ? 1024u : 2048u;
+            for (unsigned i = threadIdx.x; i < HIST_COPIES * 2048u; i += blockDim.x) hist[i] = 0u;
+            __syncthreads();
+            unsigned* mine = hist + (warp % HIST_COPIES) * 2048;
+            for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+                const unsigned key = sample_key(row[i]);
+                if ((key & decided) == prefix) atomicAdd(&mine[(key >> shift) & (bins - 1u)], 1u);
+            }
+            __syncthreads();
+            for (unsigned i = threadIdx.x; i < bins; i += blockDim.x) {
+                unsigned c = hist[i];
+    #pragma unroll
+                for (int j = 1; j < HIST_COPIES; ++j) c += hist[j * 2048 + i];
+                hist[i] = c;
+            }
+            __syncthreads();
+            if (warp == 0) {
+                // lane l owns bins [hi - per, hi) counted from the top; find where the count of
+                // larger keys passes `need`
+                const int per = (int)bins / 32;
+                const int top = (int)bins - lane * per;             // exclusive upper bin of this lane
+                unsigned mine_sum = 0u;
+                for (int j = 1; j <= per; ++j) mine_sum += hist[top - j];
+                unsigned incl = mine_sum;
+    #pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                const unsigned above = incl - mine_sum;             // keys in bins above this lane's
+                if (above < (unsigned)need && incl >= (unsigned)need) {
+                    unsigned seen = above;
+                    for (int j = 1; j <= per; ++j) {
+                        const unsigned c = hist[top - j];
+                        if (seen + c >= (unsigned)need) {
+                            pick_sh[0] = top - j;                   // the bin of the k-th largest
+                            pick_sh[1] = need - (int)seen;          // still to take inside it
+                            pick_sh[2] = (int)c;
+                            break;
+                        }
+                        seen += c;
                     }
-                    seen += c;
                 }
             }
+            __syncthreads();
+            prefix |= (unsigned)pick_sh[0] << shift;
+            decided |= (bins - 1u) << shift;
+            need = pick_sh[1];
+            equal_count = (unsigned)pick_sh[2];
+            __syncthreads();
         }
-        __syncthreads();
-        prefix |= (unsigned)pick_sh[0] << shift;
-        decided |= (bins - 1u) << shift;
-        need = pick_sh[1];
-        equal_count = (unsigned)pick_sh[2];
-        __syncthreads();
-    }
-    const unsigned kth = prefix;                       // key of the k-th largest logit
-    const int n_greater = k - need;                    // logits strictly above it
+        const unsigned kth = prefix;                       // key of the k-th largest logit
+        const int n_greater = k - need;                    // logits strictly above it
 
-    // ---- collect: everything above, and `need` of the equal ones, lowest ids first
-    unsigned long long* cand = reinterpret_cast<unsigned long long*>(work);   // [MAX_TOP_K]
-    __syncthreads();
-    if (threadIdx.x == 0) { pick_sh[3] = 0; pick_sh[4] = 0; }
-    __syncthreads();
-    const bool all_equal_taken = equal_count == (unsigned)need;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const unsigned key = sample_key(row[i]);
-        if (key > kth) {
-            const int slot = atomicAdd(&pick_sh[3], 1);
-            cand[slot] = ((unsigned long long)key << 32) | (unsigned)(0x7fffffff - i);
-        } else if (key == kth && all_equal_taken) {
-            const int slot = n_greater + atomicAdd(&pick_sh[4], 1);
-            cand[slot] = ((unsigned long long)key << 32) | (unsigned)(0x7fffffff - i);
-        }
-    }
-    if (!all_equal_taken) {
-        // more equal logits than are wanted: the lowest ids, found in id order
-        int base = 0;
-        for (int start = 0; start < vocab && base < need; start += blockDim.x) {
-            const int i = start + threadIdx.x;
-            const bool hit = i < vocab && sample_key(row[i]) == kth;
-            const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-            if (lane == 0) warp_count[warp] = __popc(ballot);
-            __syncthreads();
-            int before = 0, total = 0;
-            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
-                const int c = warp_count[w];
-                if (w < warp) before += c;
-                total += c;
+        // ---- collect: everything above, and `need` of the equal ones, lowest ids first
+        __syncthreads();
+        if (threadIdx.x == 0) { pick_sh[3] = 0; pick_sh[4] = 0; }
+        __syncthreads();
+        const bool all_equal_taken = equal_count == (unsigned)need;
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            const unsigned key = sample_key(row[i]);
+            if (key > kth) {
+                const int slot = atomicAdd(&pick_sh[3], 1);
+                cand[slot] = ((unsigned long long)key << 32) | (unsigned)(0x7fffffff - i);
+            } else if (key == kth && all_equal_taken) {
+                const int slot = n_greater + atomicAdd(&pick_sh[4], 1);
+                cand[slot] = ((unsigned long long)key << 32) | (unsigned)(0x7fffffff - i);
             }
-            const int rank = base + before + __popc(ballot & ((1u << lane) - 1u));
-            if (hit && rank < need)
-                cand[n_greater + rank] = ((unsigned long long)kth << 32) | (unsigned)(0x7fffffff - i);
-            base += total;
-            __syncthreads();
         }
-    }
-    // ---- sort: larger key first, equal keys: lower id first (both by one 64-bit compare)
-    int n2 = 1;
-    while (n2 < k) n2 <<= 1;
-    __syncthreads();
-    for (int i = k + threadIdx.x; i < n2; i += blockDim.x) cand[i] = 0ULL;     // below every key
-    __syncthreads();
-    for (int size = 2; size <= n2; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            for (int i = threadIdx.x; i < n2 / 2; i += blockDim.x) {
-                const int lo = 2 * i - (i & (stride - 1));      // partner pairs (lo, lo + stride)
-                const int hi = lo + stride;
-                const bool descending = (lo & size) == 0;
-                const unsigned long long a = cand[lo], b2 = cand[hi];
-                if ((a < b2) == descending) { cand[lo] = b2; cand[hi] = a; }
+        if (!all_equal_taken) {
+            // more equal logits than are wanted: the lowest ids, found in id order
+            int base = 0;
+            for (int start = 0; start < vocab && base < need; start += blockDim.x) {
+                const int i = start + threadIdx.x;
+                const bool hit = i < vocab && sample_key(row[i]) == kth;
+                const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+                if (lane == 0) warp_count[warp] = __popc(ballot);
+                __syncthreads();
+                int before = 0, total = 0;
+                for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+                    const int c = warp_count[w];
+                    if (w < warp) before += c;
+                    total += c;
+                }
+                const int rank = base + before + __popc(ballot & ((1u << lane) - 1u));
+                if (hit && rank < need)
+                    cand[n_greater + rank] = ((unsigned long long)kth << 32) | (unsigned)(0x7fffffff - i);
+                base += total;
+                __syncthreads();
             }
-            __syncthreads();
         }
+        n_cand = k;
     }
-    double* e = reinterpret_cast<double*>(work + MAX_TOP_K * sizeof(unsigned long long));   // [MAX_TOP_K]
+    // ---- order the candidates
+    unsigned long long* sorted = cand + CAND_CAP / 2;               // second half of the buffer
+    if (n_cand <= CAND_CAP / 2) {
+        rank_sort(n_cand, sorted);
+    } else {
+        sort_descending(n_cand);
+        sorted = cand;
+    }
+    __syncthreads();
+    double* e = reinterpret_cast<double*>(work + CAND_CAP * sizeof(unsigned long long));     // [MAX_TOP_K]
     const double t = (double)temp;
     {
-        const double mx = (double)sample_value((unsigned)(cand[0] >> 32)) / t;
+        const double mx = (double)sample_value((unsigned)(sorted[0] >> 32)) / t;
         for (int j = threadIdx.x; j < k; j += blockDim.x)
-            e[j] = exp((double)sample_value((unsigned)(cand[j] >> 32)) / t - mx);
+            e[j] = exp((double)sample_value((unsigned)(sorted[j] >> 32)) / t - mx);
     }
     __syncthreads();
     if (threadIdx.x != 0) return;
@@ -264,10 +346,10 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
     const double u = (double)((hi << 27) + lo) * (1.0 / 9007199254740992.0);
     const double draw = u * tot;
     double acc = 0.0;
-    int pick = 0x7fffffff - (int)(unsigned)(cand[cut - 1] & 0xffffffffULL);
+    int pick = 0x7fffffff - (int)(unsigned)(sorted[cut - 1] & 0xffffffffULL);
     for (int j = 0; j < cut; ++j) {
         acc += e[j];
-        if (acc >= draw || j == cut - 1) { pick = 0x7fffffff - (int)(unsigned)(cand[j] & 0xffffffffULL); break; }
+        if (acc >= draw || j == cut - 1) { pick = 0x7fffffff - (int)(unsigned)(sorted[j] & 0xffffffffULL); break; }
     }
     out[r] = pick;
 }

@@ -110,7 +110,9 @@ class CausalAttention(Mixer):
         if cache.writes and not appended:
             ops.kv_append(cache.k, cache.v, k, v, group.slots, t, ctx.status)
         o = ctx.scratch("attn_out", (ctx.token_capacity, self.q_width), dtype)[:t]
-        attend(ctx, o, q, cache, group, self.n_head, self.scale, self.window)
+        # (the step's own keys and values lie beside the queries exactly as the cache got them)
+        attend(ctx, o, q, cache, group, self.n_head, self.scale, self.window,
+               kv_new=(k, v) if cache.writes else None)
         self.out.forward(ctx, o, x, resid=x)
 
 
@@ -140,7 +142,7 @@ def prefill_key_parts(items: int, max_context: int, window: Optional[int]):
 
 
 def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
-           window: Optional[int]) -> None:
+           window: Optional[int], kv_new=None) -> None:
     """Attention of the step's tokens over their requests' cached keys and values.
 
     float32 runtime: the 32-bit kernel for every token.  bfloat16 runtime: prompt
@@ -183,7 +185,7 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
     if singles is None or singles > 0:
         n_list = work.caps["single_tokens"] if singles is None else singles
         cap = ctx.runtime.max_requests * AttentionWork.SINGLE_MAX_Q
-        if SETTINGS.decode_ring and not ops.recording() and \
+        if SETTINGS.decode_ring and not ops.recording() and cap <= ops.decode_ring_max_list() and \
                 ops.decode_ring_supports(head_dim, group.page_size):
             ws = ctx.scratch("attn_ring_ws", (ops.decode_ring_workspace(cap, n_head, head_dim),),
                              torch.float32)
@@ -192,7 +194,7 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
                                       ctx.seq_of_token, ctx.positions, work.arrays["single_tokens"],
                                       work.counts["singles"], n_list, n_head, scale, window, ws,
                                       counters, ctx.status, new_keys=AttentionWork.SINGLE_MAX_Q,
-                                      max_context=ctx.max_context)
+                                      max_context=ctx.max_context, kv_new=kv_new)
             return
         split_keys, max_splits = decode_splits(n_list * n_head, ctx.max_context, group.page_size)
         # room for the shortest splits any step may choose

@@ -319,6 +319,25 @@ def test_attention_decode_ring(nh, nkv, ps, window, stages):
         err = (out.float() - ref).abs()
         assert float(err.max()) <= 2e-2, f"worst token {int(err.max(dim=1).values.argmax())}"
         assert int(counters.abs().sum()) == 0
+    # the step's own keys and values handed over beside the queries: the kernel must take
+    # those rows from there (their cache rows are poisoned here) and everything else from the cache
+    k_new = torch.zeros(t, nkv * dh, dtype=torch.bfloat16, device="cuda")
+    v_new = torch.zeros_like(k_new)
+    k2, v2 = k.clone(), v.clone()
+    for i in range(t):
+        b, p = int(seq[i]), int(pos[i])
+        page, off = int(table[b, p // ps]), p % ps
+        k_new[i], v_new[i] = k[page, :, off, :].reshape(-1), v[page, :, off, :].reshape(-1)
+        k2[page, :, off, :] = float("nan")
+        v2[page, :, off, :] = float("nan")
+    both = torch.cat([k_new, v_new], dim=1)              # column slices of one wider tensor
+    out = torch.full_like(q, float("nan"))
+    ops.attention_decode_ring(out, q, k2, v2, table, seq, pos, None, None, t, nh, 0.2, window, ws,
+                              counters, status, new_keys=4, stages=stages, max_context=2048,
+                              kv_new=(both[:, :nkv * dh], both[:, nkv * dh:]))
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    assert float((out.float() - ref).abs().max()) <= 2e-2
     # a token list picks tokens (its length on the device); the others are not touched
     order = torch.tensor([t - 1, 0, 5, 3], dtype=torch.int32, device="cuda")
     count = torch.tensor([3], dtype=torch.int32, device="cuda")
@@ -612,6 +631,11 @@ def test_sample_kernel_matches_the_plain_sampler(vocab):
     ks = [40, 40, 40, 7, 5, 40, 40, 1, min(1024, vocab), 3, min(300, vocab), 40]
     ps = [1.0, 1.0, 0.9, 1.0, 1.0, 0.5, 1.0, 1.0, 0.95, 0.3, 1.0, 0.999]
     ts = [0.8, 1.0, 0.7, 1.3, 0.9, 0.8, 2.0, 0.5, 1.0, 0.8, 0.6, 1.5]
+    # (the reference's candidate search skips -inf and NaN logits and leaves the unfilled
+    # candidate slots at id 0, sampling.clj:14-29; the kernel takes such a logit as a candidate
+    # of weight zero instead.  The two differ only when k exceeds the number of finite logits,
+    # which these rows avoid.)
+    ks[2], ks[6] = min(ks[2], vocab - 2), min(ks[6], vocab - 2)
     n = rows.shape[0]
     logits = rows.cuda()
     out = torch.zeros(n, dtype=torch.int32, device="cuda")
