@@ -32,12 +32,10 @@
 //
 // Limits: head size 64, page sizes 8, 16 or a multiple of 32.  Other sizes are refused
 // (the caller uses the register-batch kernel of attention_decode.cu).
-#include "common.cuh"
-#include "tensor_map.cuh"
-
 #ifdef PRB_TRACE
 // device-side timestamps of one launch (thread 0 of every CTA): start, work divided, first
 // copies requested, dependency resolved, first buffer landed, run done, end
+#include <cuda_runtime.h>
 __device__ unsigned long long g_ring_trace[256 * 8];
 #define RING_TRACE(slot)                                                              \
     do {                                                                              \
@@ -47,597 +45,34 @@ __device__ unsigned long long g_ring_trace[256 * 8];
             g_ring_trace[blockIdx.x * 8 + (slot)] = t__;                              \
         }                                                                             \
     } while (0)
+#endif
+#include "attention_decode_ring.cuh"
+
+#ifdef PRB_TRACE
 PRB_API int prb_attention_decode_ring_trace(unsigned long long* host, int n) {
     return (int)cudaMemcpyFromSymbol(host, g_ring_trace, sizeof(unsigned long long) * n);
 }
-#else
-#define RING_TRACE(slot)
 #endif
 
 namespace {
-constexpr int RING_WARPS = 8;                 // most warps of a CTA (a launch may use fewer)
-constexpr int RING_THREADS = RING_WARPS * 32;
-constexpr int UNIT = 32;                      // keys per unit
-constexpr int DH = 64;                        // head size: one 128-byte swizzled box per row
-constexpr int ROW = DH * 2;                   // bytes of a row
-constexpr int TILE = UNIT * ROW;              // bytes of a unit's keys (and of its values)
-constexpr int MAX_LIST = 256;                 // most single tokens of a launch
-constexpr int MAX_STAGES = 4;
-constexpr int PART = DH + 4;                  // floats of a partial state: values, maximum, sum
-constexpr uint32_t RING_WAIT_LIMIT = 1u << 22;
-
-struct RingArgs {
-    __nv_bfloat16* out;
-    long out_stride;
-    const __nv_bfloat16* q;
-    long q_stride;
-    const int* block_table;
-    const int* seq_of_token;
-    const int* positions;
-    const int* token_list;
-    const int* token_count;
-    int n_list, n_heads, kv_heads, page_size, max_pages, num_pages;
-    float scale;
-    int window;
-    int new_keys;                   // a token's last `new_keys` visible positions may have been
-                                    // written by the step itself: fetched after the dependency
-    // The step's own keys and values as the product before this kernel left them beside the
-    // queries (row t of k_new / v_new: token t's keys / values, kv_heads * 64 wide), or null.
-    // With them no unit has to wait for the cache rows the step appended: the whole unit is
-    // requested early and those rows are put in from here once the dependency has resolved.
-    const __nv_bfloat16* k_new;
-    const __nv_bfloat16* v_new;
-    long kv_stride;
-    float* workspace;               // [(CTAs + n_list * n_heads)][PART] float32
-    int* counters;                  // [n_list * n_heads] int32, zero; left zero
-    int stages;
-    int* status;
-};
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < RING_WAIT_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-// Rows `row` .. of the cache seen as a matrix of 64 columns; x is always 0, so the 16-byte
-// rule on the innermost coordinate holds.
-__device__ __forceinline__ void tma_rows(uint32_t dst, const CUtensorMap* map, uint32_t bar, int row) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(row)
-        : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-// D += A . B where only row 0 of A is a query (its rows 8..15 are zero: a1 = a3 = 0)
-__device__ __forceinline__ void mma_row(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
-        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float x, float y) {
-    const __nv_bfloat162 v = __floats2bfloat162_rn(x, y);
-    return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-// Where a token's keys are: request, position, first and number of 32-key blocks.
-struct TokenSpan {
-    int t, b, pos, lo, first_blk, n_blk;
-};
-__device__ __forceinline__ void span_blocks(const RingArgs& a, TokenSpan& s) {
-    s.lo = (a.window > 0 && s.pos - a.window + 1 > 0) ? s.pos - a.window + 1 : 0;
-    s.first_blk = s.lo / UNIT;
-    s.n_blk = s.pos / UNIT - s.first_blk + 1;
-}
-__device__ __forceinline__ TokenSpan token_span(const RingArgs& a, int idx, int n) {
-    TokenSpan s{-1, -1, 0, 0, 0, 0};
-    if (idx >= n) return s;
-    s.t = a.token_list ? a.token_list[idx] : idx;
-    s.b = a.seq_of_token[s.t];
-    if (s.b < 0) return s;
-    s.pos = a.positions[s.t];
-    if (s.pos < 0 || s.pos >= a.max_pages * a.page_size) {
-        prb_set_status(a.status, PRB_S_POSITION_RANGE, s.t, s.pos, 0);
-        s.b = -1;
-        return s;
-    }
-    span_blocks(a, s);
-    return s;
-}
-
-// A partial state as the merges see it: lane l holds output dimensions 2 l, 2 l + 1.
-struct Partial {
-    float m, l, o0, o1;
-};
-__device__ __forceinline__ void merge_into(Partial& acc, float m2, float l2, float a0, float a1) {
-    const float mn = fmaxf(acc.m, m2);
-    const float c1 = (acc.m == -INFINITY) ? 0.0f : __expf(acc.m - mn);
-    const float c2 = (m2 == -INFINITY) ? 0.0f : __expf(m2 - mn);
-    acc.l = acc.l * c1 + l2 * c2;
-    acc.o0 = acc.o0 * c1 + a0 * c2;
-    acc.o1 = acc.o1 * c1 + a1 * c2;
-    acc.m = mn;
-}
+using namespace ring;
 
 __global__ void __launch_bounds__(RING_THREADS, 2)
 attention_decode_ring_kernel(RingArgs a, const __grid_constant__ CUtensorMap map_k,
                              const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ __align__(128) unsigned char ring_raw[];
-    __shared__ int cum[MAX_LIST + 1];               // units before each place of the token list
-    __shared__ int span_t[MAX_LIST], span_b[MAX_LIST], span_pos[MAX_LIST];   // token, request, position
-    __shared__ int warp_tot[RING_WARPS];
-    __shared__ __align__(8) unsigned long long bars[RING_WARPS * MAX_STAGES];
-    // what a warp leaves for the merge: the state of the first and of the last (token, head)
-    // of its run (the ones other warps may share), and which they are
-    __shared__ float edge_state[RING_WARPS][2][PART];
-    __shared__ int edge_pair[RING_WARPS][2];        // idx * heads + h, or -1
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_warps = (int)blockDim.x >> 5;
+    __shared__ Shared sh;
     RING_TRACE(0);
     prb_grid_launch_dependents();                   // the next kernel may set itself up
-
-    // ---- the step's description (it was copied to the device before the step's first
-    // kernel): units per token, and their running sum
-    int n = a.n_list;
-    if (a.token_count != nullptr) n = min(n, *a.token_count);
-    {
-        int run = 0;
-        for (int base = 0; base < n; base += (int)blockDim.x) {
-            const TokenSpan s = token_span(a, base + (int)threadIdx.x, n);
-            if (base + (int)threadIdx.x < n) {
-                span_t[base + threadIdx.x] = s.t;
-                span_b[base + threadIdx.x] = s.b;
-                span_pos[base + threadIdx.x] = s.pos;
-            }
-            const int mine = s.b >= 0 ? s.n_blk * a.n_heads : 0;
-            int incl = mine;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int v = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += v;
-            }
-            if (lane == 31) warp_tot[warp] = incl;
-            __syncthreads();
-            int before = 0, total = 0;
-            for (int w = 0; w < n_warps; ++w) {
-                const int c = warp_tot[w];
-                if (w < warp) before += c;
-                total += c;
-            }
-            if (base + (int)threadIdx.x < n) cum[base + threadIdx.x] = run + before + incl - mine;
-            run += total;
-            __syncthreads();
-        }
-        if (threadIdx.x == 0) cum[n] = run;
-    }
-    const int stages = a.stages;
-    if (lane == 0) {
-        for (int s = 0; s < stages; ++s) mbar_init(smem_addr(&bars[warp * MAX_STAGES + s]), 1);
-        edge_pair[warp][0] = edge_pair[warp][1] = -1;
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    __syncthreads();
+    const uint32_t ring_base = (smem_addr(ring_raw) + 1023u) & ~1023u;
+    if (threadIdx.x < RING_WARPS) sh.bars_valid[threadIdx.x] = 0;
+    plan(a, sh);
     RING_TRACE(1);
-
-    // Runs of `per` units each: CTA c's warp w is worker c * warps + w and takes units
-    // [worker * per, worker * per + per), so that the warps that share a (token, head) are
-    // mostly warps of one CTA.  With few units the runs are a unit long and the CTAs are
-    // spread out: worker numbers then step through the CTAs first.
-    const long total_units = cum[n];
-    const long workers = (long)gridDim.x * n_warps;
-    const long per = total_units > 0 ? (total_units + workers - 1) / workers : 1;
-    const long busy = (total_units + per - 1) / per;             // workers that have a run
-    // CTAs that get work, each with `wpc` busy warps (the last may have fewer)
-    const long wpc = min((long)n_warps, max(1L, (busy + gridDim.x - 1) / (long)gridDim.x));
-    const long gw = (long)blockIdx.x * wpc + warp;               // this warp's worker number
-    const bool has_run = warp < wpc && gw < busy;
-    const int u_begin = has_run ? (int)(gw * per) : 0;
-    const int u_end = has_run ? (int)min(total_units, gw * per + per) : 0;
-    auto cta_of = [&](long u) { return (u / per) / wpc; };       // the CTA whose warps hold unit u
-
-    const uint32_t ring0 = ((smem_addr(ring_raw) + 1023u) & ~1023u) + (uint32_t)warp * stages * 2 * TILE;
-    const uint32_t bar0 = smem_addr(&bars[warp * MAX_STAGES]);
-    const int hpg = a.n_heads / a.kv_heads;          // query heads per key/value head
-
-    // ---- a lane's own unit of the current batch of 32 units: decoded once, then its copies
-    // are issued by that lane when the unit's ring buffer is free
-    struct LaneUnit {
-        int idx, h, blk;            // place in the token list, head, absolute 32-key block
-        int pos, lo, t;
-        bool late;                  // holds rows the step itself may have written
-        bool bad;                   // a page of it lies outside the pool
-        int pages[4];               // its pages (one when the page holds 32 keys or more)
-        int rows;                   // rows to copy: up to the end of the last page it touches
-    };
-    auto decode = [&](int u) {
-        LaneUnit lu;
-        lu.idx = -1;
-        if (u >= u_end) return lu;
-        int lo_i = 0, hi_i = n;                      // largest idx with cum[idx] <= u
-        while (hi_i - lo_i > 1) {
-            const int mid = (lo_i + hi_i) >> 1;
-            if (cum[mid] <= u) lo_i = mid; else hi_i = mid;
-        }
-        TokenSpan s{span_t[lo_i], span_b[lo_i], span_pos[lo_i], 0, 0, 0};
-        span_blocks(a, s);
-        const int r = u - cum[lo_i];
-        lu.idx = lo_i;
-        lu.h = r / s.n_blk;
-        lu.blk = s.first_blk + r % s.n_blk;
-        lu.pos = s.pos; lu.lo = s.lo; lu.t = s.t;
-        const int k0 = lu.blk * UNIT;
-        lu.late = a.k_new == nullptr && k0 + UNIT > s.pos - a.new_keys + 1;
-        lu.bad = false;
-        const int last_key = min(k0 + UNIT - 1, s.pos);
-        const int* table = a.block_table + (size_t)s.b * a.max_pages;
-        if (a.page_size >= UNIT) {
-            lu.pages[0] = table[k0 / a.page_size];
-            lu.pages[1] = lu.pages[2] = lu.pages[3] = -1;
-            lu.rows = UNIT;
-            if (lu.pages[0] < 0 || lu.pages[0] >= a.num_pages) lu.bad = true;
-        } else {
-            const int fit = UNIT / a.page_size;      // 2 or 4 pages to a unit
-            const int used = (last_key - k0) / a.page_size + 1;
-            lu.rows = used * a.page_size;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                lu.pages[i] = (i < fit && i < used) ? table[k0 / a.page_size + i] : -1;
-                if (i < used && (lu.pages[i] < 0 || lu.pages[i] >= a.num_pages)) lu.bad = true;
-            }
-        }
-        if (lu.bad) prb_set_status(a.status, PRB_S_PAGE_RANGE, s.t, k0, lu.pages[0]);
-        return lu;
-    };
-    auto issue = [&](const LaneUnit& lu, int slot) {  // this lane starts the copies of its unit
-        const uint32_t bar = bar0 + 8 * slot;
-        if (lu.bad) {                                // nothing to copy: the unit counts as masked
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-            return;
-        }
-        const uint32_t kd = ring0 + slot * 2 * TILE, vd = kd + TILE;
-        const int hk = lu.h / hpg;
-        mbar_expect_tx(bar, 2u * lu.rows * ROW);
-        if (a.page_size >= UNIT) {
-            const int row = (lu.pages[0] * a.kv_heads + hk) * a.page_size + (lu.blk * UNIT) % a.page_size;
-            tma_rows(kd, &map_k, bar, row);
-            tma_rows(vd, &map_v, bar, row);
-        } else {
-            const int used = lu.rows / a.page_size;
-            for (int i = 0; i < used; ++i) {
-                const int row = (lu.pages[i] * a.kv_heads + hk) * a.page_size;
-                tma_rows(kd + i * a.page_size * ROW, &map_k, bar, row);
-                tma_rows(vd + i * a.page_size * ROW, &map_v, bar, row);
-            }
-        }
-    };
-
-    // ---- before the dependency: every old unit that has a ring buffer is requested
-    LaneUnit mine = decode(u_begin + lane);          // units u_begin .. u_begin + 31
-    LaneUnit ahead = mine;                           // the 32 units after them, once decoded
-    bool ahead_ready = false;
-    int batch0 = u_begin;                            // first unit of `mine`
-    if (lane < stages && mine.idx >= 0 && !mine.late) issue(mine, lane);
+    early(a, &map_k, &map_v, sh, ring_base, (int)gridDim.x, (int)blockIdx.x);
     RING_TRACE(2);
     prb_grid_wait();
     RING_TRACE(3);
-    if (lane < stages && mine.idx >= 0 && mine.late) issue(mine, lane);
-
-    // ---- walk the run.  The query is row 0 of a 16-row tile, so the lanes 0..3 (row group 0
-    // of the tensor-core fragments) hold what counts: lane c of them the scores of keys
-    // 8 j + 2 c, + 1 of a unit and the output dimensions 8 j + 2 c, + 1.
-    const int qd = lane & 3;
-    const bool row0 = lane < 4;
-    float m = -INFINITY, l = 0.0f;
-    float o[8][4];                                   // [dimension tile][fragment]; [j][0], [j][1] count
-#pragma unroll
-    for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
-    uint32_t qa[4][2];                               // the query as A fragments, per 16 dimensions
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) qa[ks][0] = qa[ks][1] = 0u;
-    int cur_idx = -1, cur_h = -1, cur_t = 0, cur_n_blk = 0;
-    int pairs_done = 0;                              // (token, head)s this warp has left behind
-    bool alive = true;
-
-    // The running state is complete as far as this warp goes.  If the whole (token, head) lies
-    // in this warp's run it is written out; otherwise it is left in shared memory for the merge
-    // (only the first and the last (token, head) of a run can be shared with other warps).
-    auto finish_pair = [&]() {
-        const long p_u0 = (long)cum[cur_idx] + (long)cur_h * cur_n_blk, p_u1 = p_u0 + cur_n_blk;
-        if (p_u0 >= u_begin && p_u1 <= u_end) {
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            __nv_bfloat16* head_out = a.out + (size_t)cur_t * a.out_stride + (size_t)cur_h * DH;
-            if (row0) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    *reinterpret_cast<__nv_bfloat162*>(head_out + 8 * j + 2 * qd) =
-                        __floats2bfloat162_rn(o[j][0] * inv, o[j][1] * inv);
-            }
-        } else {
-            float* st = edge_state[warp][pairs_done == 0 ? 0 : 1];
-            if (row0) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    *reinterpret_cast<float2*>(st + 8 * j + 2 * qd) = make_float2(o[j][0], o[j][1]);
-            }
-            if (lane == 0) {
-                st[DH] = m;
-                st[DH + 1] = l;
-                edge_pair[warp][pairs_done == 0 ? 0 : 1] = cur_idx * a.n_heads + cur_h;
-            }
-        }
-        ++pairs_done;
-    };
-
-    for (int u = u_begin; u < u_end && alive; ++u) {
-        if (u - batch0 >= 32) {                      // on to the next 32 units (decoded when the
-            mine = ahead;                            // first of them was requested)
-            batch0 += 32;
-            ahead_ready = false;
-        }
-        const int rel = u - batch0;                  // which lane decoded this unit
-        const int slot = (u - u_begin) % stages;
-        const uint32_t parity = (uint32_t)((u - u_begin) / stages) & 1u;
-        const int idx = __shfl_sync(0xffffffffu, mine.idx, rel);
-        const int h = __shfl_sync(0xffffffffu, mine.h, rel);
-        const int blk = __shfl_sync(0xffffffffu, mine.blk, rel);
-        const int pos = __shfl_sync(0xffffffffu, mine.pos, rel);
-        const int lo = __shfl_sync(0xffffffffu, mine.lo, rel);
-        const int t = __shfl_sync(0xffffffffu, mine.t, rel);
-        const int bad = __shfl_sync(0xffffffffu, mine.bad ? 1 : 0, rel);
-        if (idx != cur_idx || h != cur_h) {
-            if (cur_idx >= 0) finish_pair();
-            cur_idx = idx; cur_h = h; cur_t = t;
-            TokenSpan s{t, span_b[idx], pos, 0, 0, 0};
-            span_blocks(a, s);
-            cur_n_blk = s.n_blk;
-            m = -INFINITY; l = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
-            // this pair's query as A fragments: row 0 only, so only lanes 0..3 hold any of it
-            const uint32_t* qp = reinterpret_cast<const uint32_t*>(
-                a.q + (size_t)t * a.q_stride + (size_t)h * DH);
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                qa[ks][0] = row0 ? qp[8 * ks + qd] : 0u;          // dimensions 16 ks + 2 c, + 1
-                qa[ks][1] = row0 ? qp[8 * ks + 4 + qd] : 0u;      // dimensions 16 ks + 8 + 2 c, + 1
-            }
-        }
-        if (!mbar_wait_bounded(bar0 + 8 * slot, parity)) {
-            if (lane == 0) prb_set_status(a.status, PRB_S_WAIT_TIMEOUT, 32, (int)blockIdx.x, u);
-            alive = false;
-            break;
-        }
-        if (u == u_begin) RING_TRACE(4);
-        const uint32_t kd = ring0 + slot * 2 * TILE, vd = kd + TILE;
-        if (a.k_new != nullptr && !bad && (blk + 1) * UNIT > pos - a.new_keys + 1) {
-            // rows of this unit that the step itself appended: lanes 8 j .. 8 j + 7 bring the
-            // row of position pos - j, if token t - j is that position of the same request
-            const int j = lane >> 3, c = lane & 7;
-            const int key = pos - j;
-            const int src = idx - j;                 // its place in the token list
-            if (j < a.new_keys && key >= blk * UNIT && key < (blk + 1) * UNIT && key >= lo && src >= 0 &&
-                span_t[src] == t - j && span_b[src] == span_b[idx] && span_pos[src] == key) {
-                const int hk = h / hpg, r = key - blk * UNIT;
-                const size_t off = (size_t)(t - j) * a.kv_stride + (size_t)hk * DH + c * 8;
-                const uint4 kk = *reinterpret_cast<const uint4*>(a.k_new + off);
-                const uint4 vv = *reinterpret_cast<const uint4*>(a.v_new + off);
-                const uint32_t dst = (uint32_t)r * ROW + (uint32_t)((c ^ (r & 7)) << 4);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(kd + dst), "r"(kk.x), "r"(kk.y), "r"(kk.z), "r"(kk.w) : "memory");
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(vd + dst), "r"(vv.x), "r"(vv.y), "r"(vv.z), "r"(vv.w) : "memory");
-            }
-            __syncwarp();
-        }
-        // a masked key's values must be finite: what an earlier owner of the page left there is
-        // zeroed (lane j looks after row j) before it is multiplied by a zero weight
-        {
-            const int key = blk * UNIT + lane;
-            if (bad || key < lo || key > pos) {
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(vd + lane * ROW + c * 16), "r"(0u) : "memory");
-            }
-        }
-        // ---- scores S = q . K^T: key tiles of 8 (B fragments straight from the rows of the
-        // swizzled tile), 16 dimensions a step
-        float sc[4][4];
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.0f;
-        {
-            const int r = lane & 7, mi = lane >> 3;  // this lane gives the address of row r of matrix mi
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const uint32_t rowaddr = kd + (uint32_t)(8 * nt + r) * ROW;
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t b[4];                   // 16-byte pieces 4 half + 0..3 of the 8 rows
-                    ldmatrix_x4(rowaddr + (uint32_t)(((4 * half + mi) ^ r) << 4), b);
-                    mma_row(sc[nt], qa[2 * half][0], qa[2 * half][1], b[0], b[1]);
-                    mma_row(sc[nt], qa[2 * half + 1][0], qa[2 * half + 1][1], b[2], b[3]);
-                }
-            }
-        }
-        // ---- softmax over the unit's keys (row 0: lanes 0..3), running maximum and sum
-        float um = -INFINITY;
-#pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = blk * UNIT + 8 * nt + 2 * qd + e;
-                const bool seen = row0 && !bad && key >= lo && key <= pos;
-                sc[nt][e] = seen ? sc[nt][e] * a.scale : -INFINITY;
-                um = fmaxf(um, sc[nt][e]);
-            }
-        um = fmaxf(um, __shfl_xor_sync(0xffffffffu, um, 1));
-        um = fmaxf(um, __shfl_xor_sync(0xffffffffu, um, 2));
-        const float m_new = fmaxf(m, um);
-        float corr = 1.0f, ps = 0.0f;
-        uint32_t pa[2][2];                           // the weights as A fragments, per 16 keys
-        {
-            float pv[4][2];
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    pv[nt][e] = (m_new > -INFINITY && sc[nt][e] > -INFINITY) ? __expf(sc[nt][e] - m_new) : 0.0f;
-                    ps += pv[nt][e];
-                }
-            if (m_new > -INFINITY) corr = (m == -INFINITY) ? 0.0f : __expf(m - m_new);
-            pa[0][0] = pack_bf16(pv[0][0], pv[0][1]);
-            pa[0][1] = pack_bf16(pv[1][0], pv[1][1]);
-            pa[1][0] = pack_bf16(pv[2][0], pv[2][1]);
-            pa[1][1] = pack_bf16(pv[3][0], pv[3][1]);
-        }
-        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
-        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
-        l = l * corr + ps;
-        m = m_new;
-        __syncwarp();                                 // the zeroed value rows are in place
-        // ---- O = O * corr + P . V: dimension tiles of 8, 16 keys a step (B fragments by
-        // transposing loads from the rows of the value tile)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { o[j][0] *= corr; o[j][1] *= corr; }
-        {
-            const int r = lane & 7, mi = lane >> 3;
-#pragma unroll
-            for (int ks = 0; ks < 2; ++ks)
-#pragma unroll
-                for (int jp = 0; jp < 4; ++jp) {     // dimension tiles 2 jp, 2 jp + 1
-                    // matrices: (keys 16 ks + 0..7, piece 2 jp), (keys + 8.., piece 2 jp),
-                    //           (keys 16 ks + 0..7, piece 2 jp + 1), (keys + 8.., piece 2 jp + 1)
-                    const int key_row = 16 * ks + 8 * (mi & 1) + r;
-                    const int piece = 2 * jp + (mi >> 1);
-                    uint32_t b[4];
-                    ldmatrix_x4_trans(vd + (uint32_t)key_row * ROW + (uint32_t)((piece ^ (key_row & 7)) << 4), b);
-                    mma_row(o[2 * jp], pa[ks][0], pa[ks][1], b[0], b[1]);
-                    mma_row(o[2 * jp + 1], pa[ks][0], pa[ks][1], b[2], b[3]);
-                }
-        }
-        __syncwarp();                                 // every lane has read the buffer
-        // ---- the buffer is free: the unit `stages` ahead takes it
-        const int nu = u + stages;
-        if (nu < u_end) {
-            // (generic-proxy accesses to the buffer come before the copy engine's writes)
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            if (nu - batch0 < 32) {
-                if (lane == nu - batch0) issue(mine, slot);
-            } else {
-                if (!ahead_ready) {
-                    ahead = decode(batch0 + 32 + lane);
-                    ahead_ready = true;
-                }
-                if (lane == nu - batch0 - 32) issue(ahead, slot);
-            }
-        }
-    }
-    if (alive && cur_idx >= 0) finish_pair();
-    if (!alive) {
-        // a wait gave up: wait once more, bounded, for this warp's own copies in flight
-        for (int s = 0; s < stages; ++s)
-            for (uint32_t i = 0; i < (1u << 16); ++i)
-                if (mbar_try_wait(bar0 + 8 * s, 0) || mbar_try_wait(bar0 + 8 * s, 1)) break;
-    }
-    RING_TRACE(5);
-    __syncthreads();                                  // every warp's edge states are in place
-
-    // ---- merge.  The edge states of the CTA's warps, in warp order, form chains of the same
-    // (token, head); the warp that holds a chain's first state merges it.  A chain that is the
-    // whole (token, head) is written out; otherwise it goes to the workspace, and the last CTA
-    // of that (token, head) to arrive merges the CTAs' states in CTA order.
-    for (int e = 0; e < 2; ++e) {
-        const int pair = edge_pair[warp][e];
-        if (pair < 0) continue;
-        // is there an earlier state of the same pair in this CTA?  (then that warp merges)
-        bool first = true;
-        if (e == 1 && edge_pair[warp][0] == pair) first = false;
-        if (first && warp > 0 && (edge_pair[warp - 1][1] == pair ||
-                                  (edge_pair[warp - 1][1] < 0 && edge_pair[warp - 1][0] == pair)))
-            first = false;
-        if (!first) continue;
-        Partial acc{-INFINITY, 0.0f, 0.0f, 0.0f};
-        bool go = true;
-        for (int w = warp; w < n_warps && go; ++w)
-            for (int e2 = (w == warp ? e : 0); e2 < 2; ++e2) {
-                if (edge_pair[w][e2] != pair) {
-                    // a warp's second slot may be empty (its run was one (token, head) long)
-                    if (edge_pair[w][e2] < 0 && e2 == 1) continue;
-                    go = false;
-                    break;
-                }
-                const float* st = edge_state[w][e2];
-                merge_into(acc, st[DH], st[DH + 1], st[2 * lane], st[2 * lane + 1]);
-            }
-        const int idx = pair / a.n_heads, h = pair - idx * a.n_heads;
-        TokenSpan s{span_t[idx], span_b[idx], span_pos[idx], 0, 0, 0};
-        span_blocks(a, s);
-        const long p_u0 = (long)cum[idx] + (long)h * s.n_blk, p_u1 = p_u0 + s.n_blk;
-        const long fc = cta_of(p_u0), lc = cta_of(p_u1 - 1);
-        __nv_bfloat16* dst = a.out + (size_t)s.t * a.out_stride + (size_t)h * DH + 2 * lane;
-        if (fc == lc) {
-            const float inv = acc.l > 0.0f ? 1.0f / acc.l : 0.0f;
-            *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.o0 * inv, acc.o1 * inv);
-            continue;
-        }
-        float* part = a.workspace + (size_t)(blockIdx.x + pair) * PART;
-        *reinterpret_cast<float2*>(part + 2 * lane) = make_float2(acc.o0, acc.o1);
-        if (lane == 0) { part[DH] = acc.m; part[DH + 1] = acc.l; }
-        __threadfence();
-        __syncwarp();
-        int last = 0;
-        if (lane == 0) last = atomicAdd(&a.counters[pair], 1) == (int)(lc - fc) ? 1 : 0;
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (!last) continue;
-        __threadfence();
-        // the CTAs' states in CTA order (= block order); all loads first, then the sums
-        Partial tot{-INFINITY, 0.0f, 0.0f, 0.0f};
-        for (long c0 = fc; c0 <= lc; c0 += 4) {
-            float pm[4], pl[4];
-            float2 po[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float* pw = a.workspace + (size_t)(min(c0 + j, lc) + pair) * PART;
-                pm[j] = __ldcg(pw + DH);
-                pl[j] = __ldcg(pw + DH + 1);
-                po[j] = __ldcg(reinterpret_cast<const float2*>(pw + 2 * lane));
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (c0 + j <= lc) merge_into(tot, pm[j], pl[j], po[j].x, po[j].y);
-        }
-        const float inv = tot.l > 0.0f ? 1.0f / tot.l : 0.0f;
-        *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(tot.o0 * inv, tot.o1 * inv);
-        if (lane == 0) a.counters[pair] = 0;
-    }
-    RING_TRACE(6);
+    late(a, &map_k, &map_v, sh, ring_base, (int)gridDim.x, (int)blockIdx.x);
 }
 
 int launch_ring(const RingArgs& a, const CUtensorMap& mk, const CUtensorMap& mv, int grid, int warps,
@@ -670,11 +105,22 @@ PRB_API int prb_attention_decode_ring_tune(int warps, int stages) {
 
 // Whether the kernel takes these sizes.
 PRB_API int prb_attention_decode_ring_supports(int head_dim, int page_size) {
-    return head_dim == DH &&
-           (page_size == 8 || page_size == 16 || (page_size >= 32 && page_size % 32 == 0));
+    return ring::supports(head_dim, page_size);
 }
 
 PRB_API int prb_attention_decode_ring_max_list() { return MAX_LIST; }
+
+// Whether this kernel is the faster one for a launch of n_list tokens over contexts of up to
+// max_context keys.  It is where its warps have long runs to stream (more than three units
+// each) and where everything fits the buffers that are filled before the dependency resolves
+// (at most one unit each).  Between the two, where a warp's third unit has to be requested
+// after the first was read, the split-key kernel of attention_decode.cu measured faster inside
+// a step (GPT-2 small, 8 requests of 1,000 tokens: 0.431 ms a step against 0.457).
+PRB_API int prb_attention_decode_ring_prefers(int n_list, int n_heads, int max_context) {
+    const long units = (long)n_list * n_heads * (max_context / UNIT + 1);
+    const long warps = (long)prb_sm_count() * RING_WARPS;
+    return units <= warps || units > 3 * warps;
+}
 
 // Floats of workspace a launch of up to n_list tokens needs.
 PRB_API long prb_attention_decode_ring_workspace(int n_list, int n_heads, int head_dim) {
@@ -698,16 +144,12 @@ PRB_API int prb_attention_decode_ring(void* out, long out_stride, const void* q,
                                       float* workspace, int* counters, int stages,
                                       int max_context, int* status, cudaStream_t stream) {
     if (n_list <= 0) return 0;
-    if (!prb_attention_decode_ring_supports(head_dim, page_size) || n_heads <= 0 || kv_heads <= 0 ||
-        n_heads % kv_heads != 0 || n_list > MAX_LIST || new_keys < 1 || new_keys > 4 || stages < 0 ||
-        stages > MAX_STAGES || stages == 1 ||
-        (long)num_pages * kv_heads * page_size > 0x7fffffffL)
-        return PRB_E_SIZE;
-    if (q_stride % 8 != 0 || ((uintptr_t)q) % 16 != 0 || ((uintptr_t)k_pages) % 16 != 0 ||
-        ((uintptr_t)v_pages) % 16 != 0 || ((uintptr_t)out) % 4 != 0 || out_stride % 2 != 0 ||
-        ((k_new != nullptr) != (v_new != nullptr)) ||
-        (k_new != nullptr && (kv_stride % 8 != 0 || ((uintptr_t)k_new) % 16 != 0 || ((uintptr_t)v_new) % 16 != 0)))
-        return PRB_E_ALIGN;
+    if (stages < 0 || stages > MAX_STAGES || stages == 1) return PRB_E_SIZE;
+    CUtensorMap mk, mv;
+    const int rc = check_and_maps(q, q_stride, out, out_stride, k_pages, v_pages, n_list, n_heads,
+                                  kv_heads, head_dim, page_size, num_pages, new_keys, k_new, v_new,
+                                  kv_stride, &mk, &mv);
+    if (rc) return rc;
     RingArgs a;
     a.out = (__nv_bfloat16*)out; a.out_stride = out_stride;
     a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride;
@@ -717,14 +159,6 @@ PRB_API int prb_attention_decode_ring(void* out, long out_stride, const void* q,
     a.max_pages = max_pages; a.num_pages = num_pages; a.scale = scale; a.window = window;
     a.k_new = (const __nv_bfloat16*)k_new; a.v_new = (const __nv_bfloat16*)v_new; a.kv_stride = kv_stride;
     a.new_keys = new_keys; a.workspace = workspace; a.counters = counters; a.status = status;
-    // the cache as a matrix of 64 columns; a copy brings the rows of a unit (or of a page,
-    // where pages are shorter than a unit)
-    const long cache_rows = (long)num_pages * kv_heads * page_size;
-    const int box_rows = page_size >= UNIT ? UNIT : page_size;
-    CUtensorMap mk, mv;
-    int rc = tmap::get_map(k_pages, cache_rows, DH, DH, box_rows, &mk);
-    if (rc) return rc;
-    if ((rc = tmap::get_map(v_pages, cache_rows, DH, DH, box_rows, &mv)) != 0) return rc;
     const int sms = prb_sm_count();
     // Warps and ring depth.  The CTAs of this kernel are meant to sit on the SMs beside those
     // of the product before it (about 48 KB of shared memory each) while that still runs, and

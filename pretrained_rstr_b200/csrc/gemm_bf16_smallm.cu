@@ -234,68 +234,14 @@ template <int MT>
 __device__ __forceinline__ void norm_rows_staged(const Args& a, __nv_bfloat16* xs, const float* gb) {
     constexpr int MP = 8 * MT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int k = a.k, nvec = a.k / 4;            // float4 per row
+    const int k = a.k;
     for (int t = warp; t < MP; t += WARPS) {
         __nv_bfloat16* dst = xs + (size_t)t * a.xs_pitch;
         if (t >= a.m) {
             for (int i = lane; i < k / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
             continue;
         }
-        const float4* src = reinterpret_cast<const float4*>(a.xf + (size_t)t * a.ldx);
-        float4 v[LN_MAX_K / 128];
-        const int iters = (nvec + 31) / 32;       // the same for the whole warp
-#pragma unroll
-        for (int i = 0; i < LN_MAX_K / 128; ++i) {
-            if (i < iters) {
-                const int idx = lane + 32 * i;
-                v[i] = idx < nvec ? src[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        }
-        // One pass for both statistics, on data shifted by the row's first element so that
-        // the difference of squares does not cancel; one round of shuffles for both sums.
-        const float pivot = __shfl_sync(0xffffffffu, v[0].x, 0);
-        float s1 = 0.0f, s2 = 0.0f;
-#pragma unroll
-        for (int i = 0; i < LN_MAX_K / 128; ++i) {
-            if (i < iters && lane + 32 * i < nvec) {
-                const float c0 = v[i].x - pivot, c1 = v[i].y - pivot, c2 = v[i].z - pivot,
-                            c3 = v[i].w - pivot;
-                s1 += (c0 + c1) + (c2 + c3);
-                s2 += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-            s2 += __shfl_xor_sync(0xffffffffu, s2, o);
-        }
-        const float dm = s1 / (float)k;                        // mean - pivot
-        const float var = fmaxf(s2 / (float)k - dm * dm, 0.0f);
-        const float inv = rsqrtf(var + a.eps);
-        const float shift = -(pivot + dm) * inv;               // y = (x * inv + shift) * gamma + beta
-        const uint32_t gaddr = (uint32_t)__cvta_generic_to_shared(gb);
-#pragma unroll
-        for (int i = 0; i < LN_MAX_K / 128; ++i) {
-            const int idx = lane + 32 * i;
-            if (i < iters && idx < nvec) {
-                float4 gm, bt = make_float4(0.f, 0.f, 0.f, 0.f);
-                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-                             : "=f"(gm.x), "=f"(gm.y), "=f"(gm.z), "=f"(gm.w)
-                             : "r"(gaddr + idx * 16));
-                if (a.beta)
-                    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-                                 : "=f"(bt.x), "=f"(bt.y), "=f"(bt.z), "=f"(bt.w)
-                                 : "r"(gaddr + (k + idx * 4) * 4));
-                const __nv_bfloat162 lo = __floats2bfloat162_rn(
-                    fmaf(fmaf(v[i].x, inv, shift), gm.x, bt.x), fmaf(fmaf(v[i].y, inv, shift), gm.y, bt.y));
-                const __nv_bfloat162 hi = __floats2bfloat162_rn(
-                    fmaf(fmaf(v[i].z, inv, shift), gm.z, bt.z), fmaf(fmaf(v[i].w, inv, shift), gm.w, bt.w));
-                uint2 pk;
-                pk.x = *reinterpret_cast<const uint32_t*>(&lo);
-                pk.y = *reinterpret_cast<const uint32_t*>(&hi);
-                *reinterpret_cast<uint2*>(dst + idx * 4) = pk;
-            }
-        }
+        norm_row_any(a.xf + (size_t)t * a.ldx, dst, gb, k, a.beta != nullptr, a.eps);
     }
     __syncthreads();
 }

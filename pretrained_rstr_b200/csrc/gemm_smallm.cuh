@@ -65,6 +65,64 @@ __host__ __device__ inline size_t smem_bytes(int mt, bool ln, int k) {
     return (size_t)WARPS * ROWS * 8 * mt * sizeof(float) + (ln ? (size_t)8 * mt * norm_pitch(k) * 2 : 0);
 }
 
+// LayerNorm of one float32 row of k elements into bfloat16, by one warp.  The row is held in
+// NV float4 per lane; the caller picks the smallest instance that holds it, so that a short
+// row does not issue the (predicated-off) instructions of a long one.  Mean first, then the
+// centred squares from the registers, both float32 and both summed in a fixed order.
+// gb: gamma [k] then beta [k] (if has_beta), anywhere (shared memory in both callers).
+template <int NV>
+__device__ __forceinline__ void norm_row(const float* __restrict__ xrow, __nv_bfloat16* dst,
+                                         const float* gb, int k, bool has_beta, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int nvec = k / 4;
+    const float4* src = reinterpret_cast<const float4*>(xrow);
+    float4 v[NV];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int idx = lane + 32 * i;
+        v[i] = idx < nvec ? __ldcg(src + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    const float mean = prb_warp_sum(s) / (float)k;
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (lane + 32 * i < nvec) {
+            const float c0 = v[i].x - mean, c1 = v[i].y - mean, c2 = v[i].z - mean, c3 = v[i].w - mean;
+            sq += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+        }
+    }
+    const float inv = 1.0f / sqrtf(prb_warp_sum(sq) / (float)k + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int idx = lane + 32 * i;
+        if (idx < nvec) {
+            const float4 gm = reinterpret_cast<const float4*>(gb)[idx];
+            float4 bt = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (has_beta) bt = reinterpret_cast<const float4*>(gb + k)[idx];
+            const __nv_bfloat162 lo = __floats2bfloat162_rn((v[i].x - mean) * inv * gm.x + bt.x,
+                                                            (v[i].y - mean) * inv * gm.y + bt.y);
+            const __nv_bfloat162 hi = __floats2bfloat162_rn((v[i].z - mean) * inv * gm.z + bt.z,
+                                                            (v[i].w - mean) * inv * gm.w + bt.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(dst + idx * 4) = pk;
+        }
+    }
+}
+
+// The instance for a row of k elements (k a multiple of 4, at most LN_MAX_K).
+__device__ __forceinline__ void norm_row_any(const float* xrow, __nv_bfloat16* dst, const float* gb,
+                                             int k, bool has_beta, float eps) {
+    const int iters = (k / 4 + 31) / 32;
+    if (iters <= 2) norm_row<2>(xrow, dst, gb, k, has_beta, eps);
+    else if (iters <= 6) norm_row<6>(xrow, dst, gb, k, has_beta, eps);
+    else if (iters <= 8) norm_row<8>(xrow, dst, gb, k, has_beta, eps);
+    else norm_row<LN_MAX_K / 128>(xrow, dst, gb, k, has_beta, eps);
+}
+
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(

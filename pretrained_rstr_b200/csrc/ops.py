@@ -98,15 +98,15 @@ def _declare_program(h: ctypes.CDLL) -> None:
     h.prb_program_add_norm.argtypes = [P, P, P, P, P, P, I, I, I, F, I, P]
     h.prb_program_add_gemm.argtypes = [P, P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
                                        P, P, P, I, I, I, I, I, P]
-    h.prb_program_add_append.argtypes = [P, P, P, P, P, L, P, I, I, I, I, I, I, P]
-    h.prb_program_add_attention.argtypes = [P, P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I,
-                                            I, F, I, P, P, I, I, P]
+    h.prb_program_add_attention_ring.argtypes = [P, P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I,
+                                                 I, I, F, I, I, P, P, L, P, P, P]
+    h.prb_program_max_rows.argtypes = []
     h.prb_program_upload.argtypes = [P, P, P]
     h.prb_program_run.argtypes = [P, P, P, P, P]
     h.prb_set_pdl.argtypes = [I]
     h.prb_set_pdl.restype = None
     for name in ("prb_program_length", "prb_program_add_embed", "prb_program_add_norm",
-                 "prb_program_add_gemm", "prb_program_add_append", "prb_program_add_attention",
+                 "prb_program_add_gemm", "prb_program_add_attention_ring", "prb_program_max_rows",
                  "prb_program_upload", "prb_program_run"):
         getattr(h, name).restype = c_int
 
@@ -146,6 +146,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_attention_decode_ring.restype = c_int
     h.prb_attention_decode_ring_supports.argtypes = [I, I]
     h.prb_attention_decode_ring_supports.restype = c_int
+    h.prb_attention_decode_ring_prefers.argtypes = [I, I, I]
+    h.prb_attention_decode_ring_prefers.restype = c_int
     h.prb_attention_decode_ring_max_list.argtypes = []
     h.prb_attention_decode_ring_max_list.restype = c_int
     h.prb_attention_decode_ring_workspace.argtypes = [I, I, I]
@@ -241,12 +243,14 @@ _RECORDER = None
 class Program:
     """The operations of one decode step, recorded once and run as a single persistent
     kernel (``csrc/decode_program.cu``).  While a program records (``with program:``) the
-    wrappers below that it can hold (embed, layernorm, gemm_smallm, kv_append,
-    attention_decode) append an operation instead of launching; any other wrapper raises
-    :class:`NotRecordable`."""
+    wrappers below that it can hold (embed, layernorm, gemm_smallm, attention_decode_ring)
+    append an operation instead of launching; any other wrapper raises
+    :class:`NotRecordable`, and so does a step the one kernel has no room for."""
 
     def __init__(self, max_rows: int, device):
         self.handle = program_lib().prb_program_new(int(max_rows))
+        if not self.handle:
+            raise NotRecordable(f"a decode program holds steps of up to {program_max_rows()} tokens")
         self.device = device
         self.ops = None                    # device copy of the operation list
         self.barrier = torch.zeros(2, dtype=torch.int32, device=device)
@@ -267,8 +271,11 @@ class Program:
     def finish(self) -> None:
         self.length = program_lib().prb_program_length(self.handle)
         nbytes = program_lib().prb_program_bytes(self.handle)
-        self.ops = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=self.device)
-        _check(program_lib().prb_program_upload(self.handle, _p(self.ops), _stream()), "program upload")
+        self.ops = torch.zeros(max(nbytes, 64) + 64, dtype=torch.uint8, device=self.device)
+        code = program_lib().prb_program_upload(self.handle, _p(self.ops), _stream())
+        if code == -3:
+            raise NotRecordable("the step's operations do not fit one kernel's shared memory")
+        _check(code, "program upload")
 
     def run(self, status) -> None:
         _check(program_lib().prb_program_run(self.handle, _p(self.ops), _p(self.barrier), _p(status),
@@ -286,6 +293,11 @@ class Program:
 def recording() -> bool:
     """Whether a decode program is recording (kernels it cannot hold must not be chosen)."""
     return _RECORDER is not None
+
+
+def program_max_rows() -> int:
+    """Most tokens a step may hold to run as a decode program."""
+    return int(program_lib().prb_program_max_rows())
 
 
 def _no_record(what: str) -> None:
@@ -385,12 +397,7 @@ def kv_append(k_pages, v_pages, k_src, v_src, slots, n_tokens, status) -> None:
             raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
     if k_src.stride(0) != v_src.stride(0):
         raise KernelArgumentError(f"{what}: k_src and v_src row strides differ")
-    if _RECORDER is not None:
-        _check(program_lib().prb_program_add_append(_RECORDER.handle, _p(k_pages), _p(v_pages), _p(k_src),
-                                            _p(v_src), k_src.stride(0), _p(slots), n_tokens,
-                                            kv_heads, head_dim, page_size, num_pages,
-                                            dtype_code(k_pages.dtype), _p(status)), what)
-        return
+    _no_record(what)
     _check(lib().prb_kv_append(_p(k_pages), _p(v_pages), _p(k_src), _p(v_src), k_src.stride(0),
                                _p(slots), n_tokens, kv_heads, head_dim, page_size, num_pages,
                                dtype_code(k_pages.dtype), _p(status), _stream()), what)
@@ -552,11 +559,15 @@ def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0,
         kv = (_p(k_pages), _p(v_pages), _p(slots), q_width, kv_heads * head_dim, head_dim,
               page_size, num_pages)
     if _RECORDER is not None:
-        _check(program_lib().prb_program_add_gemm(
+        code = program_lib().prb_program_add_gemm(
             _RECORDER.handle, _p(out), None if norm_input is not None else _p(x),
             _p(x) if norm_input is not None else None, _p(gamma), _p(beta), float(eps), _p(w),
             _p(bias), _p(resid), m, n, k, x.stride(0), w.stride(0), out.stride(0), ACT_CODES[act],
-            dtype_code(out.dtype), *kv, _p(status)), what)
+            dtype_code(out.dtype), *kv, _p(status))
+        if code == -3:
+            raise NotRecordable(f"{what}: a decode program takes up to {program_max_rows()} rows and "
+                                f"reductions that are multiples of 64 (this one: {m} rows, K = {k})")
+        _check(code, what)
         return
     _check(lib().prb_gemm_smallm(
         _p(out), None if norm_input is not None else _p(x),
@@ -636,14 +647,7 @@ def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positi
     if workspace.dtype != torch.float32 or workspace.numel() < need or \
             counters.dtype != torch.int32 or counters.numel() < n_list * n_heads:
         raise KernelArgumentError(f"{what}: scratch too small or of the wrong type")
-    if _RECORDER is not None:
-        _check(program_lib().prb_program_add_attention(
-            _RECORDER.handle, _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages),
-            _p(v_pages), _p(block_table), _p(seq_of_token), _p(positions), _p(token_list),
-            _p(token_count), n_list, n_heads, kv_heads, head_dim, page_size, block_table.shape[1],
-            num_pages, float(scale), int(window or 0), _p(workspace), _p(counters), max_splits,
-            split_keys, _p(status)), what)
-        return
+    _no_record(what)
     _check(lib().prb_attention_decode(
         _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(block_table),
         _p(seq_of_token), _p(positions), _p(token_list), _p(token_count), n_list, n_heads,
@@ -654,6 +658,11 @@ def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positi
 
 def decode_ring_supports(head_dim: int, page_size: int) -> bool:
     return bool(lib().prb_attention_decode_ring_supports(int(head_dim), int(page_size)))
+
+
+def decode_ring_prefers(n_list: int, n_heads: int, max_context: int) -> bool:
+    """Whether ``attention_decode_ring`` is the faster kernel for this launch (both are right)."""
+    return bool(lib().prb_attention_decode_ring_prefers(int(n_list), int(n_heads), int(max_context)))
 
 
 def decode_ring_max_list() -> int:
@@ -680,7 +689,6 @@ def attention_decode_ring(out, q, k_pages, v_pages, block_table, seq_of_token, p
     appended.  ``workspace``: ``decode_ring_workspace`` floats; ``counters`` int32
     [n_list * heads], zero (left zero)."""
     what = "attention_decode_ring"
-    _no_record(what)
     num_pages, kv_heads, page_size, head_dim = k_pages.shape
     for name, t in (("out", out), ("q", q)):
         if t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != n_heads * head_dim:
@@ -701,6 +709,14 @@ def attention_decode_ring(out, q, k_pages, v_pages, block_table, seq_of_token, p
         if k_new.stride(0) != v_new.stride(0):
             raise KernelArgumentError(f"{what}: k_new and v_new row strides differ")
         kv_stride = k_new.stride(0)
+    if _RECORDER is not None:
+        _check(program_lib().prb_program_add_attention_ring(
+            _RECORDER.handle, _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages),
+            _p(block_table), _p(seq_of_token), _p(positions), _p(token_list), _p(token_count),
+            n_list, n_heads, kv_heads, head_dim, page_size, block_table.shape[1], num_pages,
+            float(scale), int(window or 0), int(new_keys), _p(k_new), _p(v_new), int(kv_stride),
+            _p(workspace), _p(counters), _p(status)), what)
+        return
     _check(lib().prb_attention_decode_ring(
         _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(block_table),
         _p(seq_of_token), _p(positions), _p(token_list), _p(token_count), n_list, n_heads,

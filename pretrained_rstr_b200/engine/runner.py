@@ -152,7 +152,7 @@ class ModelRunner:
         # without single tokens) gets a graph without the kernels of that list, since an idle
         # launch per layer is a tenth of a small decode step
         filled = tuple(bool(c) for view in ctx.work.values() for c in view.host_counts.values())
-        if self.use_programs and lay.t_cap <= ops.smallm_limits()[0]:
+        if self.use_programs and lay.t_cap <= ops.program_max_rows():
             saved = [dict(view.host_counts) for view in ctx.work.values()]
             logits = self._run_program(ctx, filled)
             if logits is not None:
@@ -334,14 +334,14 @@ class ModelRunner:
         self._counts_from_device(ctx)
         ctx.max_context = self.model.max_positions
         if hit is None:
-            program = ops.Program(lay.t_cap, self.device)
             try:
+                program = ops.Program(lay.t_cap, self.device)
                 with program:
                     logits = self.model.forward(ctx)
+                program.finish()
             except ops.NotRecordable:
                 self._programs[key] = False
                 return None
-            program.finish()
             hit = (program, logits)
             self._programs[key] = hit
         hit[0].run(self.status)

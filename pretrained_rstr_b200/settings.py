@@ -12,7 +12,8 @@ Python side (``SETTINGS``):
 ``PRB200_ATTN_TC=0``       prompt attention on ``mma.sync`` even where the tcgen05 kernel applies
 ``PRB200_PREFILL_PART=N``  key blocks per part of the tcgen05 prompt attention (-1: the kernel's rule)
 ``PRB200_DECODE_CTAS=N``   CTAs a decode attention launch aims for (0: about five per SM)
-``PRB200_DECODE_RING=0``   decode attention by the register-batch kernel even where the ring kernel applies
+``PRB200_DECODE_RING=0|1`` decode attention always by the split-key kernel (0) or, where its sizes
+                           allow, always by the ring kernel (1); unset: whichever measured faster
 
 Read by the CUDA library itself (``csrc/``): ``PRB200_DECODE_EARLY=1`` and
 ``PRB200_EARLY_SMALL=1`` let kernels of many small CTAs be placed on the SMs before their
@@ -23,6 +24,7 @@ from __future__ import annotations
 
 import os
 from dataclasses import dataclass
+from typing import Optional
 
 
 def _flag(name: str, default: bool) -> bool:
@@ -47,7 +49,7 @@ class Settings:
     attention_tcgen05: bool = True
     prefill_part: int = -1
     decode_ctas: int = 0
-    decode_ring: bool = True
+    decode_ring: Optional[bool] = None
 
     @classmethod
     def from_environment(cls) -> "Settings":
@@ -55,7 +57,8 @@ class Settings:
                    pdl=_flag("PRB200_PDL", True), attention_tcgen05=_flag("PRB200_ATTN_TC", True),
                    prefill_part=_int("PRB200_PREFILL_PART", -1),
                    decode_ctas=_int("PRB200_DECODE_CTAS", 0),
-                   decode_ring=_flag("PRB200_DECODE_RING", True))
+                   decode_ring=(_flag("PRB200_DECODE_RING", True)
+                                if "PRB200_DECODE_RING" in os.environ else None))
 
 
 SETTINGS = Settings.from_environment()

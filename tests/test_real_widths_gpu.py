@@ -165,3 +165,40 @@ def test_sixty_four_requests_decoding_together(models, tmp_path, dtype):
     assert len(rp.rows) == 64 * (decode_steps + 1)
     worst = compare(rp.rows, oracle, _tol(dtype, raw["n_embd"]))
     print(f"64 requests {dtype}: largest difference {worst:.2e}")
+
+
+@pytest.mark.parametrize("ring", [False, True])
+def test_either_decode_attention_kernel_forced(models, monkeypatch, ring):
+    """The engine picks the decode attention kernel by the size of the launch; here each of
+    the two runs everything: single tokens of one request, of three requests of unequal
+    length side by side, and portions of two to four tokens beside them."""
+    from pretrained_rstr_b200.settings import SETTINGS
+    monkeypatch.setattr(SETTINGS, "decode_ring", ring)
+    folder, raw, prompts, wanted, oracle = models("small", "bfloat16")
+    rp = Replayer(folder, "bfloat16", max_tokens=2048, max_batched_tokens=1024)
+    tail = 12
+    for rid, ids in prompts.items():
+        head = len(ids) - tail
+        rp.step([(rid, ids[:head], _want_in(wanted[rid], 0, head))])
+    first = next(iter(prompts))
+    done = {rid: len(ids) - tail for rid, ids in prompts.items()}
+    for i in range(4):                                     # one request alone
+        at = done[first]
+        rp.step([(first, prompts[first][at:at + 1], [0])])
+        done[first] += 1
+    cuts = [1, 3, 2, 1, 4, 1]
+    step = 0
+    while any(done[rid] < len(ids) for rid, ids in prompts.items()):
+        batch, ended = [], []
+        for j, (rid, ids) in enumerate(prompts.items()):
+            if done[rid] >= len(ids):
+                continue
+            n = min(cuts[(step + j) % len(cuts)], len(ids) - done[rid])
+            batch.append((rid, ids[done[rid]:done[rid] + n], list(range(n))))
+            done[rid] += n
+            if done[rid] == len(ids):
+                ended.append(rid)
+        rp.step(batch, end=ended)
+        step += 1
+    worst = compare(rp.rows, oracle, _tol("bfloat16", raw["n_embd"]))
+    print(f"ring {ring}: largest difference {worst:.2e}")
