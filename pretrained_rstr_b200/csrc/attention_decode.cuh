@@ -16,9 +16,8 @@
 // Scratch: workspace [tokens, heads, max_splits, head_dim + 4] float32 and counters
 // [tokens * heads] int32 (zero before the first launch; the kernel leaves them zero).
 //
-// The unit of work (one token, one head, one split) is a device function so that the
-// stand-alone kernel (attention_decode.cu) and the whole-step decode program
-// (decode_program.cu) run the very same code.
+// The unit of work (one token, one head, one split) is a device function of its own; the
+// kernels of attention_decode.cu call it.
 #pragma once
 #include "common.cuh"
 
@@ -65,8 +64,7 @@ __device__ __forceinline__ float dot8(const uint4& a, const float* q) {
     return s;
 }
 
-// Shared memory of one unit; the caller provides it (static in the stand-alone kernel,
-// carved from the program's shared memory in the decode program).
+// Shared memory of one unit; the caller provides it.
 template <int NW> struct Shared {
     float m[NW], l[NW];
     float o[NW][MAX_DH];

@@ -1,8 +1,7 @@
 // Decode attention by persistent CTAs whose warps stream keys and values through private
 // rings of shared-memory buffers (TMA tile copies, 128-byte swizzle, no multicast) and
-// multiply them with mma.sync: the device functions.  The stand-alone kernel
-// (attention_decode_ring.cu) and the whole-step decode program (decode_program.cu) run this
-// very code; the method is described in attention_decode_ring.cu.
+// multiply them with mma.sync: the device functions of the kernel in
+// attention_decode_ring.cu, where the method is described.
 //
 // Three phases, each called by every thread of the CTA:
 //   plan()   the step's description -> units per token and their running sum, in shared memory

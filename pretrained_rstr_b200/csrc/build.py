@@ -23,12 +23,6 @@ from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libprb200.so"
-# The whole-step decode program (an option that is off by default) takes as long to compile
-# as everything else together: it is a library of its own, built when first asked for.  It
-# links the objects whose host functions it calls.
-PROGRAM_LIB_NAME = "libprb200_program.so"
-PROGRAM_SOURCES = ["decode_program.cu"]
-PROGRAM_NEEDS = ["gemm_bf16_smallm.cu", "elementwise.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math=false",
                            "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
@@ -42,14 +36,9 @@ class BuildError(RuntimeError):
     pass
 
 
-def sources(which: str = "core") -> List[str]:
-    """Files of the core library, of the decode-program library, or ("all") of both."""
-    every = sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
-    if which == "all":
-        return every
-    if which == "program":
-        return [f for f in every if f in PROGRAM_SOURCES]
-    return [f for f in every if f not in PROGRAM_SOURCES]
+def sources() -> List[str]:
+    """The CUDA files of the library: every .cu file of this folder."""
+    return sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
 
 
 def _headers() -> List[str]:
@@ -64,11 +53,10 @@ def find_nvcc() -> str:
                      "pretrained_rstr_b200 cannot be built and there is no fallback")
 
 
-def _stamp(which: str = "core") -> str:
+def _stamp() -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    names = sources(which) + (PROGRAM_NEEDS if which == "program" else [])
-    for name in names + _headers():
+    for name in sources() + _headers():
         h.update(name.encode())
         with open(os.path.join(HERE, name), "rb") as fh:
             h.update(fh.read())
@@ -113,16 +101,13 @@ def _compile_one(nvcc: str, src: str, obj: str, verbose_ptxas: bool) -> str:
     return proc.stderr
 
 
-def build(force: bool = False, verbose_ptxas: bool = False, which: str = "core") -> str:
-    """Build if needed; returns the path of the shared library (``which``: "core", or
-    "program" for the decode-program library)."""
+def build(force: bool = False, verbose_ptxas: bool = False) -> str:
+    """Build if needed; returns the path of the shared library."""
     out_dir = build_dir()
-    if which == "program":
-        build(force=force, verbose_ptxas=verbose_ptxas, which="core")    # its objects are linked in
-    lib_name = PROGRAM_LIB_NAME if which == "program" else LIB_NAME
+    lib_name = LIB_NAME
     lib = os.path.join(out_dir, lib_name)
-    stamp_file = os.path.join(out_dir, "stamp" if which == "core" else "stamp_program")
-    stamp = _stamp(which)
+    stamp_file = os.path.join(out_dir, "stamp")
+    stamp = _stamp()
 
     def fresh() -> bool:
         if not os.path.isfile(lib) or not os.path.isfile(stamp_file):
@@ -132,14 +117,14 @@ def build(force: bool = False, verbose_ptxas: bool = False, which: str = "core")
 
     if not force and fresh():
         return lib
-    lock_path = os.path.join(out_dir, "lock" if which == "core" else "lock_program")
+    lock_path = os.path.join(out_dir, "lock")
     with open(lock_path, "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)
         try:
             if not force and fresh():
                 return lib
             nvcc = find_nvcc()
-            srcs = sources(which)
+            srcs = sources()
             _log(f"compiling {len(srcs)} CUDA files for sm_100a into {out_dir} "
                  f"(first call only)")
             t0 = time.time()
@@ -163,9 +148,7 @@ def build(force: bool = False, verbose_ptxas: bool = False, which: str = "core")
                         if verbose_ptxas and info:
                             print(info, file=sys.stderr)
                 tmp = lib + f".tmp{os.getpid()}"
-                extra = [os.path.join(out_dir, s[:-3] + ".o") for s in PROGRAM_NEEDS] \
-                    if which == "program" else []
-                cmd = [nvcc] + ARCH_FLAGS + ["-shared", "-o", tmp] + objs + extra
+                cmd = [nvcc] + ARCH_FLAGS + ["-shared", "-o", tmp] + objs
                 proc = subprocess.run(cmd, capture_output=True, text=True)
                 if proc.returncode != 0:
                     raise BuildError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
@@ -181,5 +164,4 @@ def build(force: bool = False, verbose_ptxas: bool = False, which: str = "core")
 
 
 if __name__ == "__main__":
-    for part in ("core", "program"):
-        print(build(force="--force" in sys.argv, verbose_ptxas="-v" in sys.argv, which=part))
+    print(build(force="--force" in sys.argv, verbose_ptxas="-v" in sys.argv))

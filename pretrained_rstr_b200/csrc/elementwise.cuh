@@ -1,6 +1,4 @@
-// Units of work of the memory-bound kernels as device functions, shared by the
-// stand-alone kernels (elementwise.cu) and the whole-step decode program
-// (decode_program.cu).
+// Units of work of the memory-bound kernels (elementwise.cu) as device functions.
 #pragma once
 #include "common.cuh"
 

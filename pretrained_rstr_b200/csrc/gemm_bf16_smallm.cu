@@ -539,7 +539,7 @@ PRB_API int prb_gemm_smallm_tune(int kc, int ctas_per_sm, int stages, int budget
 }
 PRB_API int prb_gemm_smallm_max_norm_width() { return LN_MAX_K; }
 
-// Argument check shared with the decode program; 0 when the kernel takes these sizes.
+// Argument check; 0 when the kernel takes these sizes.
 int prb_gemm_smallm_check(const void* x, const float* xf, const float* gamma, const float* beta,
                           const void* w, int m, int n, int k, long ldx, long ldw) {
     if (m > 64 || k <= 0 || n <= 0) return PRB_E_SIZE;

@@ -44,8 +44,28 @@ __device__ unsigned long long g_gemm_trace[256 * 8];
 PRB_API int prb_gemm_bf16_trace(unsigned long long* host, int n) {
     return (int)cudaMemcpyFromSymbol(host, g_gemm_trace, sizeof(unsigned long long) * n);
 }
+// cycles one role of a CTA spent in a kind of work: [0] producer waiting for a free stage,
+// [1] producer issuing loads, [2] MMA thread waiting for a full stage, [3] MMA thread issuing
+__device__ long long g_gemm_cycles[256 * 4];
+PRB_API int prb_gemm_bf16_cycles(long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, g_gemm_cycles, sizeof(long long) * n);
+}
+#define GC_BEGIN long long gc_t__ = clock64(), gc_a__ = 0, gc_b__ = 0
+#define GC_A do { const long long n__ = clock64(); gc_a__ += n__ - gc_t__; gc_t__ = n__; } while (0)
+#define GC_B do { const long long n__ = clock64(); gc_b__ += n__ - gc_t__; gc_t__ = n__; } while (0)
+#define GC_END(slot)                                                                  \
+    do {                                                                              \
+        if (blockIdx.x < 256) {                                                       \
+            g_gemm_cycles[blockIdx.x * 4 + (slot)] = gc_a__;                          \
+            g_gemm_cycles[blockIdx.x * 4 + (slot) + 1] = gc_b__;                      \
+        }                                                                             \
+    } while (0)
 #else
 #define GT(slot)
+#define GC_BEGIN
+#define GC_A
+#define GC_B
+#define GC_END(slot)
 #endif
 
 namespace {
@@ -57,21 +77,22 @@ constexpr int GEMM_THREADS = 320;     // producer warp, MMA warp, 8 epilogue war
 
 using namespace tc5;
 
-template <int BN> struct TileCfg {
+template <int BN, bool PAIR = false> struct TileCfg {
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile width: a multiple of 32 up to 256");
     static constexpr int A_BYTES = BM * BK * 2;
-    static constexpr int B_BYTES = BN * BK * 2;
+    // (a CTA of a pair loads its 128 rows of A and its half of the tile's rows of W)
+    static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = (176 * 1024) / STAGE_BYTES > 8 ? 8 : (176 * 1024) / STAGE_BYTES;
     // two accumulators, each at a power-of-two column offset (tensor memory is allocated in
     // powers of two)
     static constexpr int ACC_STRIDE = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
     static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
-    // per epilogue warp a 32 x 33 word staging tile (rows of the accumulator are turned into
-    // rows of the output so that global accesses are whole lines)
-    static constexpr int STG_WORDS = 32 * 33;
+    // per epilogue warp a staging tile of 32 rows x 128 bytes of finished output (after the
+    // stages, so that it is 1024-byte aligned as the 128-byte swizzle wants)
+    static constexpr int STG_BYTES = 32 * 128;
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 +
-                                   (size_t)8 * STG_WORDS * 4;
+                                   (size_t)8 * STG_BYTES;
 };
 
 
@@ -116,34 +137,70 @@ __device__ __forceinline__ float epilogue_act(float x, int act) {
     return prb_activate(x, act);
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, int rank) {
+    uint32_t raddr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(local_addr), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t local_addr, int rank) {
+    uint32_t raddr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(local_addr), "r"(rank));
+    return raddr;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
+                 : "memory");
+}
+
 // Persistent kernel: each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (tiles
 // that share a W tile are neighbours, so they run at the same time and share it in L2).
 // The producer runs ahead across tile borders; the accumulator alternates between two
 // TMEM buffers, so the epilogue of one tile overlaps the main loop of the next.
-template <int BN, typename O>
+//
+// PAIR: the two CTAs of a cluster share a 256 x BN tile (tcgen05.mma.cta_group::2).  Each
+// loads its own 128 rows of A and its own half of the tile's rows of W with plain TMA loads
+// (no multicast) that count on the even CTA's barrier; the even CTA's MMA thread issues one
+// instruction for both, whose operands are read from both CTAs' shared memory and whose
+// result lands in both CTAs' tensor memory; its commits arrive on both CTAs' barriers
+// (tcgen05.commit ... multicast::cluster).  Each CTA finishes its own 128 rows.  A CTA thus
+// takes in half the bytes of W per multiply-add: the main loop of a 128 x 128 tile is bound
+// by what one SM can take in from the L2, not by its tensor core.
+template <int BN, typename O, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                  O* __restrict__ c, const float* __restrict__ bias,
                  const float* __restrict__ resid, int m, int n, int k, long ldc, int act,
                  int* status, Scatter sc) {
-    using Cfg = TileCfg<BN>;
+    using Cfg = TileCfg<BN, PAIR>;
     extern __shared__ uint8_t smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint8_t* staging = smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES;      // [8][32][128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + (size_t)8 * Cfg::STG_BYTES);
     uint64_t* full_bar = bars;                       // [STAGES]  TMA -> MMA
     uint64_t* empty_bar = bars + Cfg::STAGES;        // [STAGES]  MMA -> TMA
     uint64_t* tfull_bar = bars + 2 * Cfg::STAGES;    // [2]       MMA -> epilogue
     uint64_t* tempty_bar = tfull_bar + 2;            // [2]       epilogue -> MMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    uint32_t* staging = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (warp == 0) GT(0);
     prb_grid_launch_dependents();     // the next kernel may set itself up while this one runs
-    const int m_tiles = (m + BM - 1) / BM, n_tiles = (n + BN - 1) / BN;
+    // A walker is a CTA, or the pair of CTAs of a cluster; it owns tiles of TM rows.
+    constexpr int TM = PAIR ? 2 * BM : BM;
+    const int rank = PAIR ? (int)(blockIdx.x & 1) : 0;              // CTA of the pair (cluster of 2 along x)
+    const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int walkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int m_tiles = (m + TM - 1) / TM, n_tiles = (n + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
     const int k_blocks = (k + BK - 1) / BK;
 
@@ -154,21 +211,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&tfull_bar[a]), 1);
-            mbar_init(smem_u32(&tempty_bar[a]), 8);      // one arrival per epilogue warp
+            // one arrival per epilogue warp (of both CTAs, on the even CTA's barrier, in a pair)
+            mbar_init(smem_u32(&tempty_bar[a]), PAIR ? 16 : 8);
         }
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                         smem_u32(tmem_slot)),
-                     "r"((uint32_t)Cfg::TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {
+            // one warp of each CTA of the pair, the same shared-memory offset in both
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(tmem_slot)),
+                         "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(tmem_slot)),
+                         "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();           // the peer's barriers exist before anything arrives on them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (warp == 0) GT(1);
@@ -177,27 +245,50 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
-        if (lane == 0) {
-            int it = 0;                               // k-blocks issued so far, over all tiles
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % Cfg::STAGES;
-                    ok = mbar_wait(smem_u32(&empty_bar[s]), ((it / Cfg::STAGES) & 1) ^ 1, failed);
-                    if (!ok) {
-                        prb_set_status(status, PRB_S_WAIT_TIMEOUT, 1, blockIdx.x, it);
-                        break;
-                    }
-                    const uint32_t fb = smem_u32(&full_bar[s]);
-                    mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-                    uint8_t* stage = tiles + (size_t)s * Cfg::STAGE_BYTES;
-                    tma_load_2d(smem_u32(stage), &map_a, fb, kb * BK, m0);
-                    tma_load_2d(smem_u32(stage + Cfg::A_BYTES), &map_w, fb, kb * BK, n0);
+        // The whole warp walks the loop and waits; one elected lane issues.  (With the loop
+        // inside "if (lane == 0)" the warp is divergent for its whole life, and the copy and
+        // MMA instructions, whose operands live in uniform registers, measured three times
+        // as slow to issue.)
+        int it = 0;                                   // k-blocks issued so far, over all tiles
+        bool ok = true;
+        GC_BEGIN;
+        for (int tile = walker; tile < total_tiles && ok; tile += walkers) {
+            const int m0 = (tile % m_tiles) * TM + rank * BM;
+            const int n0 = (tile / m_tiles) * BN + (PAIR ? rank * (BN / 2) : 0);
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % Cfg::STAGES;
+                ok = mbar_wait_warp(smem_u32(&empty_bar[s]), ((it / Cfg::STAGES) & 1) ^ 1, failed);
+                if (!ok) {
+                    if (lane == 0) prb_set_status(status, PRB_S_WAIT_TIMEOUT, 1, blockIdx.x, it);
+                    break;
                 }
+                GC_A;
+                const uint32_t fb = smem_u32(&full_bar[s]);
+                const uint32_t stage = smem_u32(tiles + (size_t)s * Cfg::STAGE_BYTES);
+                if (elect_one()) {
+                    if constexpr (PAIR) {
+                        // both CTAs' bytes count on the even CTA's barrier, which its own
+                        // producer arms for both; the odd CTA only loads
+                        if (rank == 0) mbar_expect_tx(fb, 2 * Cfg::STAGE_BYTES);
+                        tma_load_2d_pair(stage, &map_a, fb, kb * BK, m0);
+                        tma_load_2d_pair(stage + Cfg::A_BYTES, &map_w, fb, kb * BK, n0);
+                    } else {
+                        mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+                        tma_load_2d(stage, &map_a, fb, kb * BK, m0);
+                        tma_load_2d(stage + Cfg::A_BYTES, &map_w, fb, kb * BK, n0);
+                    }
+                }
+                __syncwarp();
+                GC_B;
             }
-            if (!ok) {
-                // wait (bounded) for loads still in flight before the CTA may exit
+        }
+        if (lane == 0) GC_END(0);
+        if (!ok && lane == 0) {
+            // wait (bounded) for loads still in flight before the CTA may exit (the odd
+            // CTA of a pair cannot see the barrier they count on: it gives them time)
+            if (PAIR && rank != 0) {
+                for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+            } else {
                 const int first = it > Cfg::STAGES ? it - Cfg::STAGES : 0;
                 for (int j = first; j < it; ++j) {
                     const uint32_t fb = smem_u32(&full_bar[j % Cfg::STAGES]);
@@ -206,175 +297,210 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
             }
         }
+        __syncwarp();
     } else if (warp == 1) {
         // ---------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BM, BN);
+        if (rank == 0) {
+            constexpr uint32_t idesc = make_idesc(TM, BN);
             int it = 0, local = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            GC_BEGIN;
+            for (int tile = walker; tile < total_tiles && ok; tile += walkers, ++local) {
                 const int acc = local & 1;
                 // the epilogue must have drained this accumulator (two tiles ago)
-                ok = mbar_wait(smem_u32(&tempty_bar[acc]), ((local >> 1) & 1) ^ 1, failed);
+                ok = mbar_wait_warp(smem_u32(&tempty_bar[acc]), ((local >> 1) & 1) ^ 1, failed);
                 if (!ok) {
-                    prb_set_status(status, PRB_S_WAIT_TIMEOUT, 4, blockIdx.x, local);
+                    if (lane == 0) prb_set_status(status, PRB_S_WAIT_TIMEOUT, 4, blockIdx.x, local);
                     break;
                 }
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * Cfg::ACC_STRIDE);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % Cfg::STAGES;
-                    ok = mbar_wait(smem_u32(&full_bar[s]), (it / Cfg::STAGES) & 1, failed);
+                    ok = mbar_wait_warp(smem_u32(&full_bar[s]), (it / Cfg::STAGES) & 1, failed);
                     if (!ok) {
-                        prb_set_status(status, PRB_S_WAIT_TIMEOUT, 2, blockIdx.x, it);
+                        if (lane == 0) prb_set_status(status, PRB_S_WAIT_TIMEOUT, 2, blockIdx.x, it);
                         break;
                     }
                     tcgen05_fence_after();
+                    GC_A;
                     if (it == 0) GT(2);
                     const uint32_t a_addr = smem_u32(tiles + (size_t)s * Cfg::STAGE_BYTES);
                     const uint64_t a_desc = make_smem_desc(a_addr);
                     const uint64_t b_desc = make_smem_desc(a_addr + Cfg::A_BYTES);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        // 16 elements = 32 bytes further inside the swizzle atom: +2 (16-byte units)
-                        umma_bf16(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2),
-                                  idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                            // 16 elements = 32 bytes further inside the swizzle atom: +2 (16-byte units)
+                            if constexpr (PAIR)
+                                umma_bf16_pair(d_tmem, a_desc + (uint64_t)(kk * 2),
+                                               b_desc + (uint64_t)(kk * 2), idesc,
+                                               (kb > 0 || kk > 0) ? 1u : 0u);
+                            else
+                                umma_bf16(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2),
+                                          idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                        }
+                        // frees the stage (in both CTAs of a pair) when the MMAs retire
+                        if constexpr (PAIR) umma_commit_pair(smem_u32(&empty_bar[s]));
+                        else umma_commit(smem_u32(&empty_bar[s]));
                     }
-                    umma_commit(smem_u32(&empty_bar[s]));   // frees the stage when the MMAs retire
+                    __syncwarp();
+                    GC_B;
                 }
-                if (ok) umma_commit(smem_u32(&tfull_bar[acc]));   // accumulator complete
+                if (ok && elect_one()) {                          // accumulator complete
+                    if constexpr (PAIR) umma_commit_pair(smem_u32(&tfull_bar[acc]));
+                    else umma_commit(smem_u32(&tfull_bar[acc]));
+                }
+                __syncwarp();
                 if (local == 0) GT(3);
             }
+            if (lane == 0) GC_END(2);
         }
     } else {
         // ------------------------------------------------------------ epilogue
-        // A warp reads 32 accumulator rows x 32 columns from tensor memory (one row per
-        // thread), turns them through its staging tile so that a quarter warp (float32
-        // output) or four lanes (bfloat16) own a contiguous piece of one output row, and
-        // there adds bias, applies the activation, adds the residual and stores whole lines.
-        // The bias and residual values of a chunk are requested before the chunk's
-        // accumulator is waited for, so their latency is off the path.
+        // Per chunk of 32 columns a warp reads 32 accumulator rows from tensor memory, one row
+        // per thread, and writes them as they are into its staging tile (32 rows x 128 bytes,
+        // the eight 16-byte pieces of a row XORed with the row index: no bank conflicts either
+        // way).  Then it reads the tile the other way round, four whole rows per instruction
+        // (eight lanes a row, four columns a lane): there it adds bias, applies the
+        // activation, adds the residual, converts and stores, so that every global access
+        // covers whole 128-byte (float32) or 64-byte (bfloat16) runs of a row.  A lane's four
+        // columns are the same for all rows of a chunk: its bias and residual values are
+        // requested a chunk ahead, before the accumulator is waited for.
         const int quarter = warp & 3;                       // TMEM lanes this warp may read
         const int half = (warp - 2) >> 2;                   // two warps share a quarter: even / odd chunks
+        constexpr bool F32 = sizeof(O) == 4;
+        constexpr int CH = 32;                              // columns per chunk
         const bool vec_ok = ((ldc * (long)sizeof(O)) % 16 == 0) && (((uintptr_t)c) % 16 == 0) &&
                             (((uintptr_t)bias) % 16 == 0) &&
                             (resid == nullptr ||
                              (((ldc * 4) % 16 == 0) && (((uintptr_t)resid) % 16 == 0)));
-        constexpr bool F32 = sizeof(O) == 4;
-        constexpr int ITERS = F32 ? 8 : 4;                  // passes over the staging tile
-        constexpr int RPI = 32 / ITERS;                     // rows per pass
-        constexpr int CPL = 32 / (32 / RPI);                // columns per lane: 4 or 8
-        uint32_t* stg = staging + (size_t)(warp - 2) * Cfg::STG_WORDS;
-        const int t_row = lane / (32 / RPI);                // row within a pass
-        const int t_col = (lane % (32 / RPI)) * CPL;        // first column of this lane
-        float pb[CPL];                                      // prefetched bias of the lane's columns
-        float4 pr[F32 ? ITERS : 1];                         // prefetched residual (float32 output)
-        auto prefetch = [&](int m0, int ncol) {
-            // only chunks that take the vector path are prefetched
-            if (!(vec_ok && ncol + 32 <= n)) return;
-#pragma unroll
-            for (int e = 0; e < CPL; e += 4) {
-                float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (bias) b = __ldg(reinterpret_cast<const float4*>(bias + ncol + t_col + e));
-                pb[e] = b.x; pb[e + 1] = b.y; pb[e + 2] = b.z; pb[e + 3] = b.w;
-            }
+        uint8_t* warp_stage = staging + (size_t)(warp - 2) * Cfg::STG_BYTES;
+        uint8_t* my_stage = warp_stage + (size_t)lane * 128;         // this thread's row
+        const int rd_row = lane >> 3, rd_piece = lane & 7;           // the way back: row within four, piece
+        float4 pb;                                          // prefetched bias of the lane's four columns
+        float4 pr[F32 ? 8 : 1];                             // prefetched residual (float32 output)
+        auto prefetch = [&](int row0, int ncol) {
+            // (pieces the fast path will not use, or that do not exist, read as zero)
+            const int col = ncol + rd_piece * 4;
+            const bool there = vec_ok && col + 4 <= n;
+            pb = (there && bias != nullptr) ? __ldg(reinterpret_cast<const float4*>(bias + col))
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
             if constexpr (F32) {
 #pragma unroll
-                for (int it = 0; it < ITERS; ++it) {
-                    const int rr = m0 + quarter * 32 + it * RPI + t_row;
-                    pr[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (resid && rr < m)
-                        pr[it] = *reinterpret_cast<const float4*>(resid + (size_t)rr * ldc + ncol + t_col);
+                for (int it = 0; it < 8; ++it) {
+                    const int rr = row0 + it * 4 + rd_row;
+                    pr[it] = (there && resid != nullptr && rr < m)
+                                 ? *reinterpret_cast<const float4*>(resid + (size_t)rr * ldc + col)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             }
         };
         int local = 0;
         bool ok = true;
-        if ((int)blockIdx.x < total_tiles && half * 32 < BN)
-            prefetch((blockIdx.x % m_tiles) * BM, (blockIdx.x / m_tiles) * BN + half * 32);
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
-            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+        // the accumulator is handed back on the barrier the MMA thread waits on: this CTA's,
+        // or the even CTA's of a pair
+        uint32_t tempty_addr[2] = {smem_u32(&tempty_bar[0]), smem_u32(&tempty_bar[1])};
+        if constexpr (PAIR) {
+            tempty_addr[0] = cluster_addr(tempty_addr[0], 0);
+            tempty_addr[1] = cluster_addr(tempty_addr[1], 0);
+        }
+        auto hand_back = [&](int acc) {
+            if constexpr (PAIR) mbar_arrive_cluster(tempty_addr[acc]);
+            else mbar_arrive(tempty_addr[acc]);
+        };
+        auto tile_m0 = [&](int t) { return (t % m_tiles) * TM + rank * BM; };
+        if (walker < total_tiles && half * CH < BN)
+            prefetch(tile_m0(walker) + quarter * 32, (walker / m_tiles) * BN + half * CH);
+        for (int tile = walker; tile < total_tiles && ok; tile += walkers, ++local) {
+            const int m0 = tile_m0(tile), n0 = (tile / m_tiles) * BN;
             const int acc = local & 1;
-            const int row = m0 + quarter * 32 + lane;
+            const int row0 = m0 + quarter * 32;
+            const int row = row0 + lane;
             ok = mbar_wait(smem_u32(&tfull_bar[acc]), (local >> 1) & 1, failed);
             if (!ok && lane == 0) prb_set_status(status, PRB_S_WAIT_TIMEOUT, 3, blockIdx.x, local);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             tcgen05_fence_after();
             if (warp == 2 && local == 0) GT(4);
-            if (half * 32 >= BN || n0 + half * 32 >= n) {      // nothing to read for this warp
-                if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
-                const int nt = tile + gridDim.x;
-                if (nt < total_tiles && half * 32 < BN)
-                    prefetch((nt % m_tiles) * BM, (nt / m_tiles) * BN + half * 32);
+            const int nt = tile + walkers;                  // this CTA's next tile
+            if (half * CH >= BN || n0 + half * CH >= n) {   // nothing to read for this warp
+                if (lane == 0) hand_back(acc);
+                if (nt < total_tiles && half * CH < BN)
+                    prefetch(tile_m0(nt) + quarter * 32, (nt / m_tiles) * BN + half * CH);
                 continue;
             }
+            // the cache slots of the rows this lane stores on the way back
+            int slot[(!F32) ? 8 : 1];
+            if constexpr (!F32) {
+                if (sc.kv_width != 0) {
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = row0 + it * 4 + rd_row;
+                        slot[it] = rr < m ? sc.slots[rr] : -1;
+                    }
+                }
+            }
 #pragma unroll 1
-            for (int c0 = half * 32; c0 < BN; c0 += 64) {
+            for (int c0 = half * CH; c0 < BN; c0 += 2 * CH) {
                 if (n0 + c0 >= n) break;                    // uniform across the warp
+                const int ncol = n0 + c0;
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) +
                                   (uint32_t)(acc * Cfg::ACC_STRIDE + c0), r);
-                const bool last_chunk = c0 + 64 >= BN || n0 + c0 + 64 >= n;
+                const bool last_chunk = c0 + 2 * CH >= BN || n0 + c0 + 2 * CH >= n;
                 if (last_chunk) {
                     // this warp's last read of the accumulator: hand it back before the stores
                     tcgen05_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+                    if (lane == 0) hand_back(acc);
                 }
-                const int ncol = n0 + c0;
-                const int n_valid = (n - ncol) < 32 ? (n - ncol) : 32;
-                if (vec_ok && n_valid == 32) {
+                const int n_valid = (n - ncol) < CH ? (n - ncol) : CH;
+                if (vec_ok && n_valid % 4 == 0) {
+                    __syncwarp();                        // the tile's last readers are done
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = r[j];
+                    for (int q = 0; q < 8; ++q)
+                        *reinterpret_cast<uint4*>(my_stage + ((q ^ (lane & 7)) << 4)) =
+                            make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
                     __syncwarp();
                     // what this chunk needs has been requested before; keep it and request the
                     // next chunk's (of this tile, or the first of the CTA's next tile)
-                    float b_now[CPL];
-                    float4 r_now[F32 ? ITERS : 1];
+                    const float4 b_now = pb;
+                    float4 r_now[F32 ? 8 : 1];
 #pragma unroll
-                    for (int e = 0; e < CPL; ++e) b_now[e] = pb[e];
+                    for (int it = 0; it < (F32 ? 8 : 1); ++it) r_now[it] = pr[it];
+                    if (!last_chunk) prefetch(row0, ncol + 2 * CH);
+                    else if (nt < total_tiles)
+                        prefetch(tile_m0(nt) + quarter * 32, (nt / m_tiles) * BN + half * CH);
+                    const int col = ncol + rd_piece * 4;
+                    if (rd_piece * 4 < n_valid) {
 #pragma unroll
-                    for (int it = 0; it < (F32 ? ITERS : 1); ++it) r_now[it] = pr[it];
-                    if (!last_chunk) {
-                        prefetch(m0, ncol + 64);
-                    } else {
-                        const int nt = tile + gridDim.x;
-                        if (nt < total_tiles)
-                            prefetch((nt % m_tiles) * BM, (nt / m_tiles) * BN + half * 32);
-                    }
-                    const int row_base = m0 + quarter * 32;
-#pragma unroll
-                    for (int it = 0; it < ITERS; ++it) {
-                        const int rr = it * RPI + t_row;
-                        float v[CPL];
-#pragma unroll
-                        for (int e = 0; e < CPL; ++e)
-                            v[e] = epilogue_act(__uint_as_float(stg[rr * 33 + t_col + e]) + b_now[e], act);
-                        if (row_base + rr < m) {
-                            const size_t off = (size_t)(row_base + rr) * ldc + ncol + t_col;
-                            if constexpr (F32) {
-                                if (resid) {
-                                    v[0] += r_now[it].x; v[1] += r_now[it].y;
-                                    v[2] += r_now[it].z; v[3] += r_now[it].w;
-                                }
-                                *reinterpret_cast<float4*>(reinterpret_cast<float*>(c) + off) =
-                                    make_float4(v[0], v[1], v[2], v[3]);
-                            } else {
-                                uint4 u;
-                                u.x = pack2(v[0], v[1]); u.y = pack2(v[2], v[3]);
-                                u.z = pack2(v[4], v[5]); u.w = pack2(v[6], v[7]);
-                                *reinterpret_cast<uint4*>(c + off) = u;
-                                if (sc.kv_width != 0 && ncol + t_col >= sc.q_width) {
-                                    // eight columns inside one head (head sizes are multiples of 8)
-                                    O* dst = scatter_dst<O>(sc, ncol + t_col, sc.slots[row_base + rr],
-                                                            row_base + rr, status);
-                                    if (dst) *reinterpret_cast<uint4*>(dst) = u;
+                        for (int it = 0; it < 8; ++it) {
+                            const int tr = it * 4 + rd_row;           // row of the tile
+                            const float4 a4 = *reinterpret_cast<const float4*>(
+                                warp_stage + tr * 128 + ((rd_piece ^ (tr & 7)) << 4));
+                            float v0 = epilogue_act(a4.x + b_now.x, act);
+                            float v1 = epilogue_act(a4.y + b_now.y, act);
+                            float v2 = epilogue_act(a4.z + b_now.z, act);
+                            float v3 = epilogue_act(a4.w + b_now.w, act);
+                            if (row0 + tr < m) {
+                                const size_t off = (size_t)(row0 + tr) * ldc + col;
+                                if constexpr (F32) {
+                                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(c) + off) =
+                                        make_float4(v0 + r_now[it].x, v1 + r_now[it].y,
+                                                    v2 + r_now[it].z, v3 + r_now[it].w);
+                                } else {
+                                    const uint2 u = make_uint2(pack2(v0, v1), pack2(v2, v3));
+                                    *reinterpret_cast<uint2*>(c + off) = u;
+                                    if (sc.kv_width != 0 && col >= sc.q_width) {
+                                        // four columns inside one head (head sizes are multiples of 8)
+                                        O* dst = scatter_dst<O>(sc, col, slot[it], row0 + tr, status);
+                                        if (dst) *reinterpret_cast<uint2*>(dst) = u;
+                                    }
                                 }
                             }
                         }
                     }
-                    __syncwarp();                           // the tile is reused by the next chunk
                 } else {
                     // tail columns or unaligned rows (e.g. a vocabulary that is odd): one by one
                     O* crow = c + (size_t)row * ldc + ncol;
@@ -393,13 +519,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             }
                         }
                     }
-                    if (last_chunk) {
-                        const int nt = tile + gridDim.x;
-                        if (nt < total_tiles)
-                            prefetch((nt % m_tiles) * BM, (nt / m_tiles) * BN + half * 32);
-                    } else {
-                        prefetch(m0, ncol + 64);
-                    }
+                    if (!last_chunk) prefetch(row0, ncol + 2 * CH);
+                    else if (nt < total_tiles)
+                        prefetch(tile_m0(nt) + quarter * 32, (nt / m_tiles) * BN + half * CH);
                 }
             }
             if (warp == 2 && local == 0) GT(5);
@@ -408,12 +530,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
     tcgen05_fence_before();
     __syncthreads();
+    // neither CTA of a pair leaves (or frees tensor memory) while the other may still read its
+    // shared memory, write its tensor memory or arrive on its barriers
+    if constexpr (PAIR) cluster_sync_all();
     if (warp == 0) GT(7);
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                     "r"((uint32_t)Cfg::TMEM_COLS)
-                     : "memory");
+        if constexpr (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                         "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                         "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
     }
 }
 
@@ -426,18 +556,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // values over the cluster in rank order through distributed shared memory, adds bias, applies
 // the activation, adds the residual and stores.  A second cluster barrier keeps every CTA's
 // shared memory alive until its peers have read it.
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, int rank) {
-    uint32_t raddr;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(local_addr), "r"(rank));
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
-    return v;
-}
-
 template <int BN, int S, typename O>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_splitk_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -634,7 +752,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, O* c, const float* bias
     using Cfg = TileCfg<BN>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, O>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, O, false>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)Cfg::SMEM);
         if (e != cudaSuccess) return (int)e;
@@ -643,9 +761,45 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, O* c, const float* bias
     const int sm_count = prb_sm_count();
     const long tiles = (long)((n + BN - 1) / BN) * ((m + BM - 1) / BM);
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    cudaError_t le = prb_launch_dependent(gemm_bf16_kernel<BN, O>, dim3(grid), dim3(GEMM_THREADS),
-                                          Cfg::SMEM, stream, ma, mw, c, bias, resid, m, n, k, ldc,
-                                          act, status, sc);
+    cudaError_t le = prb_launch_dependent(gemm_bf16_kernel<BN, O, false>, dim3(grid),
+                                          dim3(GEMM_THREADS), Cfg::SMEM, stream, ma, mw, c, bias,
+                                          resid, m, n, k, ldc, act, status, sc);
+    if (le != cudaSuccess) return (int)le;
+    return 0;
+}
+
+// CTA pairs on 256 x BN tiles: clusters of two CTAs, as many as tiles or as pairs of SMs.
+template <int BN, typename O>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, O* c, const float* bias,
+                const float* resid, int m, int n, int k, long ldc, int act, int* status,
+                const Scatter& sc, cudaStream_t stream) {
+    using Cfg = TileCfg<BN, true>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, O, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)Cfg::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const long tiles = (long)((n + BN - 1) / BN) * ((m + 2 * BM - 1) / (2 * BM));
+    const long pairs = prb_sm_count() / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * (tiles < pairs ? tiles : pairs)));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = prb_pdl_enabled() ? 1 : 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<BN, O, true>, ma, mw, c, bias, resid,
+                                        m, n, k, ldc, act, status, sc);
     if (le != cudaSuccess) return (int)le;
     return 0;
 }
@@ -694,7 +848,10 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
     if (k % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)a) % 16 != 0 ||
         ((uintptr_t)w) % 16 != 0)
         return PRB_E_ALIGN;
-    int split = tile_n >> 16;          // forced: tile width in the low half, cluster size above
+    // forced: tile width in the low half, cluster size of the split-K variant in bits 16 to
+    // 23, bit 24 for CTA pairs
+    int pair = (tile_n >> 24) & 1;
+    int split = (tile_n >> 16) & 0xff;
     tile_n &= 0xffff;
     if (tile_n == 0) {
         // The CTA with the most tiles sets the time.  A tile's main loop is bound by the
@@ -736,18 +893,34 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
                        (((k + BK - 1) / BK + split - 1) / split) * (split - 1) >= (k + BK - 1) / BK))
         return PRB_E_ARG;
     if (tile_n < 32 || tile_n > 256 || tile_n % 32 != 0) return PRB_E_ARG;
+    if (pair && (split != 0 || tile_n % 64 != 0)) return PRB_E_ARG;
     CUtensorMap ma, mw;
     int r = get_map(a, m, k, lda, BM, &ma);
     if (r) return r;
-    r = get_map(w, n, k, ldw, tile_n, &mw);
+    r = get_map(w, n, k, ldw, pair ? tile_n / 2 : tile_n, &mw);
     if (r) return r;
 #define PRB_GO(BN_)                                                                              \
     (out_dtype == PRB_F32                                                                        \
-         ? launch<BN_, float>(ma, mw, (float*)c, bias, resid, m, n, k, ldc, act, status, sc,     \
+         ? launch<BN_, float>(ma, mw, (float*)c, bias, resid, m, n, k, ldc, act, status, sc, \
                               stream)                                                            \
-         : launch<BN_, __nv_bfloat16>(ma, mw, (__nv_bfloat16*)c, bias, resid, m, n, k, ldc, act, \
-                                      status, sc, stream))
+         : launch<BN_, __nv_bfloat16>(ma, mw, (__nv_bfloat16*)c, bias, resid, m, n, k, ldc,  \
+                                      act, status, sc, stream))
     if (out_dtype != PRB_F32 && out_dtype != PRB_BF16) return PRB_E_DTYPE;
+#define PRB_GO_PAIR(BN_)                                                                         \
+    (out_dtype == PRB_F32                                                                        \
+         ? launch_pair<BN_, float>(ma, mw, (float*)c, bias, resid, m, n, k, ldc, act,        \
+                                   status, sc, stream)                                           \
+         : launch_pair<BN_, __nv_bfloat16>(ma, mw, (__nv_bfloat16*)c, bias, resid, m, n, k,  \
+                                           ldc, act, status, sc, stream))
+    if (pair) {
+        switch (tile_n) {
+            case 64: return PRB_GO_PAIR(64);
+            case 128: return PRB_GO_PAIR(128);
+            case 192: return PRB_GO_PAIR(192);
+            default: return PRB_GO_PAIR(256);
+        }
+    }
+#undef PRB_GO_PAIR
 #define PRB_GO_SPLIT(BN_, S_)                                                                    \
     (out_dtype == PRB_F32                                                                        \
          ? launch_splitk<BN_, S_, float>(ma, mw, (float*)c, bias, resid, m, n, k, ldc, act,      \
@@ -775,7 +948,8 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
 }  // namespace
 
 // tile_n: 0 = choose (by M, N, K and the output type), or a multiple of 32 up to 256; with a
-// cluster size of 2, 4 or 8 in bits 16 and up, the split-K variant at tile width 64 or 128.
+// cluster size of 2, 4 or 8 in bits 16 to 23, the split-K variant at tile width 64 or 128;
+// with bit 24, CTA pairs on 256-row tiles at tile width 64, 128, 192 or 256.
 PRB_API int prb_gemm_bf16(void* c, const void* a, const void* w, const float* bias,
                           const float* resid, int m, int n, int k, long lda, long ldw, long ldc,
                           int act, int out_dtype, int tile_n, int* status, cudaStream_t stream) {

@@ -16,8 +16,7 @@
 // (after the fused LayerNorm) or from global memory (L2) directly.
 // float32: statistics of the norm, accumulation, bias, activation, residual.
 //
-// The pieces are device functions so that the stand-alone kernel (gemm_bf16_smallm.cu) and
-// the whole-step decode program (decode_program.cu) run the very same code.
+// The pieces the kernels of gemm_bf16_smallm.cu are made of.
 #pragma once
 #include "common.cuh"
 

@@ -66,51 +66,6 @@ def library_path() -> str:
     return _build.build()
 
 
-_PROGRAM_LIB = None
-
-
-def program_lib() -> ctypes.CDLL:
-    """The library of the whole-step decode program; built and loaded when first asked for."""
-    global _PROGRAM_LIB
-    if _PROGRAM_LIB is None:
-        lib()                                   # the core comes first (and its objects are linked in)
-        try:
-            handle = ctypes.CDLL(_build.build(which="program"))
-        except (OSError, _build.BuildError) as exc:
-            raise ExtensionError(
-                f"the decode-program library of pretrained_rstr_b200 is not available: {exc}") from exc
-        _declare_program(handle)
-        handle.prb_set_pdl(1 if _PDL else 0)
-        _PROGRAM_LIB = handle
-    return _PROGRAM_LIB
-
-
-def _declare_program(h: ctypes.CDLL) -> None:
-    P, I, L, F = c_void_p, c_int, c_long, c_float
-    h.prb_program_new.argtypes = [I]
-    h.prb_program_new.restype = P
-    h.prb_program_free.argtypes = [P]
-    h.prb_program_free.restype = None
-    h.prb_program_length.argtypes = [P]
-    h.prb_program_bytes.argtypes = [P]
-    h.prb_program_bytes.restype = L
-    h.prb_program_add_embed.argtypes = [P, P, P, P, P, P, I, I, I, I, I, P]
-    h.prb_program_add_norm.argtypes = [P, P, P, P, P, P, I, I, I, F, I, P]
-    h.prb_program_add_gemm.argtypes = [P, P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
-                                       P, P, P, I, I, I, I, I, P]
-    h.prb_program_add_attention_ring.argtypes = [P, P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I,
-                                                 I, I, F, I, I, P, P, L, P, P, P]
-    h.prb_program_max_rows.argtypes = []
-    h.prb_program_upload.argtypes = [P, P, P]
-    h.prb_program_run.argtypes = [P, P, P, P, P]
-    h.prb_set_pdl.argtypes = [I]
-    h.prb_set_pdl.restype = None
-    for name in ("prb_program_length", "prb_program_add_embed", "prb_program_add_norm",
-                 "prb_program_add_gemm", "prb_program_add_attention_ring", "prb_program_max_rows",
-                 "prb_program_upload", "prb_program_run"):
-        getattr(h, name).restype = c_int
-
-
 def require_cuda() -> None:
     if not torch.cuda.is_available():
         raise ExtensionError("pretrained_rstr_b200 runs on a CUDA device only (sm_100a); "
@@ -232,79 +187,6 @@ def _need(t: torch.Tensor, dtype, name: str, what: str) -> None:
         raise KernelArgumentError(f"{what}: {name} must be contiguous")
 
 
-# ---------------------------------------------------------------------- programs
-class NotRecordable(RuntimeError):
-    """An operation that a decode program cannot hold was called while recording."""
-
-
-_RECORDER = None
-
-
-class Program:
-    """The operations of one decode step, recorded once and run as a single persistent
-    kernel (``csrc/decode_program.cu``).  While a program records (``with program:``) the
-    wrappers below that it can hold (embed, layernorm, gemm_smallm, attention_decode_ring)
-    append an operation instead of launching; any other wrapper raises
-    :class:`NotRecordable`, and so does a step the one kernel has no room for."""
-
-    def __init__(self, max_rows: int, device):
-        self.handle = program_lib().prb_program_new(int(max_rows))
-        if not self.handle:
-            raise NotRecordable(f"a decode program holds steps of up to {program_max_rows()} tokens")
-        self.device = device
-        self.ops = None                    # device copy of the operation list
-        self.barrier = torch.zeros(2, dtype=torch.int32, device=device)
-        self.length = 0
-
-    def __enter__(self):
-        global _RECORDER
-        if _RECORDER is not None:
-            raise RuntimeError("a program is already recording")
-        _RECORDER = self
-        return self
-
-    def __exit__(self, *exc):
-        global _RECORDER
-        _RECORDER = None
-        return False
-
-    def finish(self) -> None:
-        self.length = program_lib().prb_program_length(self.handle)
-        nbytes = program_lib().prb_program_bytes(self.handle)
-        self.ops = torch.zeros(max(nbytes, 64) + 64, dtype=torch.uint8, device=self.device)
-        code = program_lib().prb_program_upload(self.handle, _p(self.ops), _stream())
-        if code == -3:
-            raise NotRecordable("the step's operations do not fit one kernel's shared memory")
-        _check(code, "program upload")
-
-    def run(self, status) -> None:
-        _check(program_lib().prb_program_run(self.handle, _p(self.ops), _p(self.barrier), _p(status),
-                                     _stream()), "program run")
-
-    def __del__(self):
-        try:
-            if self.handle:
-                program_lib().prb_program_free(self.handle)
-                self.handle = None
-        except Exception:
-            pass
-
-
-def recording() -> bool:
-    """Whether a decode program is recording (kernels it cannot hold must not be chosen)."""
-    return _RECORDER is not None
-
-
-def program_max_rows() -> int:
-    """Most tokens a step may hold to run as a decode program."""
-    return int(program_lib().prb_program_max_rows())
-
-
-def _no_record(what: str) -> None:
-    if _RECORDER is not None:
-        raise NotRecordable(what)
-
-
 _PDL = True
 
 
@@ -313,8 +195,6 @@ def set_pdl(on: bool) -> None:
     global _PDL
     _PDL = bool(on)
     lib().prb_set_pdl(1 if on else 0)
-    if _PROGRAM_LIB is not None:
-        _PROGRAM_LIB.prb_set_pdl(1 if on else 0)
 
 
 # ------------------------------------------------------------------------ kernels
@@ -330,12 +210,6 @@ def embed(out, tokens, positions, wte, wpe, status) -> None:
         raise KernelArgumentError(f"{what}: table widths or types differ from the output's")
     if tokens.numel() < n or positions.numel() < n:
         raise KernelArgumentError(f"{what}: fewer token ids or positions than output rows")
-    if _RECORDER is not None:
-        _check(program_lib().prb_program_add_embed(_RECORDER.handle, _p(out), _p(tokens), _p(positions),
-                                           _p(wte), _p(wpe), n, width, wte.shape[0],
-                                           0 if wpe is None else wpe.shape[0],
-                                           dtype_code(wte.dtype), _p(status)), what)
-        return
     _check(lib().prb_embed(_p(out), _p(tokens), _p(positions), _p(wte), _p(wpe), n, width,
                            wte.shape[0], 0 if wpe is None else wpe.shape[0],
                            dtype_code(wte.dtype), _p(status), _stream()), what)
@@ -356,11 +230,6 @@ def layernorm(out, x, gamma, beta, eps: float, rows=None, status=None) -> None:
         raise KernelArgumentError(f"{what}: fewer input rows than output rows")
     if rows is not None:
         _need(rows, torch.int32, "rows", what)
-    if _RECORDER is not None:
-        _check(program_lib().prb_program_add_norm(_RECORDER.handle, _p(out), _p(x), _p(gamma), _p(beta),
-                                          _p(rows), n_rows, x.shape[0], width, float(eps),
-                                          dtype_code(out.dtype), _p(status)), what)
-        return
     _check(lib().prb_layernorm(_p(out), _p(x), _p(gamma), _p(beta), _p(rows), n_rows, x.shape[0],
                                width, float(eps), dtype_code(out.dtype), _p(status), _stream()),
            what)
@@ -369,7 +238,6 @@ def layernorm(out, x, gamma, beta, eps: float, rows=None, status=None) -> None:
 def bias_act(out, inp, bias, resid, act) -> None:
     """out = act(inp + bias) (+ resid), sums in float32."""
     what = "bias_act"
-    _no_record(what)
     _need(out, None, "out", what)
     _need(inp, None, "inp", what)
     m, n = inp.shape
@@ -397,7 +265,6 @@ def kv_append(k_pages, v_pages, k_src, v_src, slots, n_tokens, status) -> None:
             raise KernelArgumentError(f"{what}: {name} has the wrong type, width or inner stride")
     if k_src.stride(0) != v_src.stride(0):
         raise KernelArgumentError(f"{what}: k_src and v_src row strides differ")
-    _no_record(what)
     _check(lib().prb_kv_append(_p(k_pages), _p(v_pages), _p(k_src), _p(v_src), k_src.stride(0),
                                _p(slots), n_tokens, kv_heads, head_dim, page_size, num_pages,
                                dtype_code(k_pages.dtype), _p(status), _stream()), what)
@@ -406,7 +273,6 @@ def kv_append(k_pages, v_pages, k_src, v_src, slots, n_tokens, status) -> None:
 def copy_pages(storage, pairs, n_pairs, status) -> None:
     """storage: [pools, pages, ...] contiguous; pairs int32 [n, 2] (source, destination)."""
     what = "copy_pages"
-    _no_record(what)
     _need(storage, None, "storage", what)
     _need(pairs, torch.int32, "pairs", what)
     pools, pages = storage.shape[0], storage.shape[1]
@@ -418,7 +284,6 @@ def copy_pages(storage, pairs, n_pairs, status) -> None:
 def gemm_f32(out, a, w, bias=None, resid=None, act=None) -> None:
     """out[M,N] = act(a[M,K] . w[N,K]^T + bias) (+ resid): true 32-bit FMA."""
     what = "gemm_f32"
-    _no_record(what)
     for name, t in (("out", out), ("a", a), ("w", w)):
         if not t.is_cuda or t.dtype != torch.float32 or t.stride(1) != 1:
             raise KernelArgumentError(f"{what}: {name} must be float32 on CUDA with unit inner stride")
@@ -437,16 +302,16 @@ def gemm_f32(out, a, w, bias=None, resid=None, act=None) -> None:
 
 
 def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, status=None,
-              kv_scatter=None, split_k: int = 0) -> None:
+              kv_scatter=None, split_k: int = 0, pair: bool = False) -> None:
     """out[M,N] = act(a[M,K] . w[N,K]^T + bias) (+ resid) on the tcgen05 tensor cores:
     bfloat16 operands, float32 accumulation in tensor memory, epilogue in float32; out is
     bfloat16 or float32.  K and the row pitches of a and w must be multiples of 8.
     ``kv_scatter`` = (k_pages, v_pages, slots, q_width): the key and value columns of a fused
     QKV product also go to the paged cache (of the output's element type).  ``tile_n`` and
     ``split_k`` force a tile width and, for widths 64 and 128, a cluster of 2, 4 or 8 CTAs
-    that share a tile's reduction; left at 0 the kernel chooses."""
+    that share a tile's reduction; ``pair`` (widths 64, 128, 192, 256) forces pairs of CTAs on
+    256-row tiles (``tcgen05.mma.cta_group::2``); left at 0 the kernel chooses."""
     what = "gemm_bf16"
-    _no_record(what)
     for name, t in (("a", a), ("w", w)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(1) != 1:
             raise KernelArgumentError(f"{what}: {name} must be bfloat16 on CUDA with unit inner stride")
@@ -464,7 +329,7 @@ def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, statu
             raise KernelArgumentError(f"{what}: resid must have the output's shape and stride")
     if kv_scatter is not None:
         k_pages, v_pages, slots, q_width = kv_scatter
-        if resid is not None or tile_n or split_k:
+        if resid is not None or tile_n or split_k or pair:
             raise KernelArgumentError(f"{what}: a product that scatters takes no residual or tile width")
         if k_pages.dtype != out.dtype or v_pages.dtype != out.dtype or not k_pages.is_contiguous() \
                 or not v_pages.is_contiguous():
@@ -478,7 +343,8 @@ def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, statu
         return
     _check(lib().prb_gemm_bf16(_p(out), _p(a), _p(w), _p(bias), _p(resid), m, n, k, a.stride(0),
                                w.stride(0), out.stride(0), ACT_CODES[act], dtype_code(out.dtype),
-                               int(tile_n) | (int(split_k) << 16), _p(status), _stream()), what)
+                               int(tile_n) | (int(split_k) << 16) | (int(bool(pair)) << 24),
+                               _p(status), _stream()), what)
 
 
 def midm_supports(m: int, n: int, k: int) -> bool:
@@ -489,7 +355,6 @@ def gemm_midm(out, a, w, bias=None, resid=None, act=None, status=None) -> None:
     """out[M,N] = act(a[M,K] . w[N,K]^T + bias) (+ resid) for up to 64 rows, K a multiple of
     64: the reduction is split over a thread-block cluster (``csrc/gemm_bf16_midm.cu``)."""
     what = "gemm_midm"
-    _no_record(what)
     for name, t in (("a", a), ("w", w)):
         if not t.is_cuda or t.dtype != torch.bfloat16 or t.stride(1) != 1:
             raise KernelArgumentError(f"{what}: {name} must be bfloat16 on CUDA with unit inner stride")
@@ -558,17 +423,6 @@ def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0,
             raise KernelArgumentError(f"{what}: cache type or widths do not fit the product")
         kv = (_p(k_pages), _p(v_pages), _p(slots), q_width, kv_heads * head_dim, head_dim,
               page_size, num_pages)
-    if _RECORDER is not None:
-        code = program_lib().prb_program_add_gemm(
-            _RECORDER.handle, _p(out), None if norm_input is not None else _p(x),
-            _p(x) if norm_input is not None else None, _p(gamma), _p(beta), float(eps), _p(w),
-            _p(bias), _p(resid), m, n, k, x.stride(0), w.stride(0), out.stride(0), ACT_CODES[act],
-            dtype_code(out.dtype), *kv, _p(status))
-        if code == -3:
-            raise NotRecordable(f"{what}: a decode program takes up to {program_max_rows()} rows and "
-                                f"reductions that are multiples of 64 (this one: {m} rows, K = {k})")
-        _check(code, what)
-        return
     _check(lib().prb_gemm_smallm(
         _p(out), None if norm_input is not None else _p(x),
         _p(x) if norm_input is not None else None, _p(gamma), _p(beta), float(eps), _p(w),
@@ -581,7 +435,6 @@ def attention_generic(out, q, k_pages, v_pages, block_table, seq_of_token, posit
     """Attention of every token of the step over its request's cached keys; 32-bit
     arithmetic.  q: [T, n_heads*head_dim] (may be a column slice), out likewise."""
     what = "attention_generic"
-    _no_record(what)
     num_pages, kv_heads, page_size, head_dim = k_pages.shape
     for name, t in (("out", out), ("q", q)):
         if t.dtype != k_pages.dtype or t.stride(1) != 1 or t.shape[1] != n_heads * head_dim:
@@ -647,7 +500,6 @@ def attention_decode(out, q, k_pages, v_pages, block_table, seq_of_token, positi
     if workspace.dtype != torch.float32 or workspace.numel() < need or \
             counters.dtype != torch.int32 or counters.numel() < n_list * n_heads:
         raise KernelArgumentError(f"{what}: scratch too small or of the wrong type")
-    _no_record(what)
     _check(lib().prb_attention_decode(
         _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(block_table),
         _p(seq_of_token), _p(positions), _p(token_list), _p(token_count), n_list, n_heads,
@@ -709,14 +561,6 @@ def attention_decode_ring(out, q, k_pages, v_pages, block_table, seq_of_token, p
         if k_new.stride(0) != v_new.stride(0):
             raise KernelArgumentError(f"{what}: k_new and v_new row strides differ")
         kv_stride = k_new.stride(0)
-    if _RECORDER is not None:
-        _check(program_lib().prb_program_add_attention_ring(
-            _RECORDER.handle, _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages),
-            _p(block_table), _p(seq_of_token), _p(positions), _p(token_list), _p(token_count),
-            n_list, n_heads, kv_heads, head_dim, page_size, block_table.shape[1], num_pages,
-            float(scale), int(window or 0), int(new_keys), _p(k_new), _p(v_new), int(kv_stride),
-            _p(workspace), _p(counters), _p(status)), what)
-        return
     _check(lib().prb_attention_decode_ring(
         _p(out), out.stride(0), _p(q), q.stride(0), _p(k_pages), _p(v_pages), _p(block_table),
         _p(seq_of_token), _p(positions), _p(token_list), _p(token_count), n_list, n_heads,
@@ -747,7 +591,6 @@ def attention_prefill_tc(out, q, k_pages, v_pages, block_table, positions, tile_
     float32 [n_tiles * n_heads * max_parts * 256], zeroed int32 [n_tiles * n_heads]) is the
     workspace through which the chunks of an item are merged)."""
     what = "attention_prefill_tc"
-    _no_record(what)
     num_pages, kv_heads, page_size, head_dim = k_pages.shape
     for name, t in (("out", out), ("q", q)):
         if t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != n_heads * head_dim:
@@ -780,7 +623,6 @@ def attention_prefill(out, q, k_pages, v_pages, block_table, positions, tile_req
     """bfloat16 causal attention of prompt portions (work items of up to 128 queries, two
     CTAs of 64 each) on mma.sync tensor-core instructions; any head size in steps of 16."""
     what = "attention_prefill"
-    _no_record(what)
     num_pages, kv_heads, page_size, head_dim = k_pages.shape
     for name, t in (("out", out), ("q", q)):
         if t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != n_heads * head_dim:
@@ -798,7 +640,6 @@ def resolve_tokens(tokens, n, prev, status) -> None:
     """tokens[t] = prev[-tokens[t] - 1] wherever tokens[t] < 0 (t < n): ids that name a place
     among the tokens the sampling kernel chose last."""
     what = "resolve_tokens"
-    _no_record(what)
     _need(tokens, torch.int32, "tokens", what)
     _need(prev, torch.int32, "prev", what)
     _check(lib().prb_resolve_tokens(_p(tokens), int(n), _p(prev), prev.numel(), _p(status),
@@ -814,7 +655,6 @@ def sample(out, logits, n_rows, temperature=None, top_k=None, top_p=None, seeds=
     """out[r] = chosen token of logits[r,:] (float32).  Without ``temperature`` every row
     is greedy; otherwise rows with temperature <= 0 are greedy and the rest sample."""
     what = "sample"
-    _no_record(what)
     _need(out, torch.int32, "out", what)
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelArgumentError(f"{what}: logits must be float32 with unit inner stride")

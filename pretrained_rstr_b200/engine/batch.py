@@ -79,7 +79,6 @@ class Runtime:
     max_batched_tokens: int = 2048
     max_requests: int = 64
     use_graphs: bool = True            # replay small steps as CUDA graphs
-    use_programs: bool = False         # run decode-only steps as one persistent kernel
 
     @property
     def serving(self) -> bool:

@@ -79,7 +79,7 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0", page_size: int = 
     arch, config = read_config(folder)
     runtime = Runtime(device=device, dtype=dtype, page_size=page_size,
                       max_batched_tokens=max_batched_tokens, max_requests=max_requests,
-                      use_graphs=SETTINGS.graphs, use_programs=SETTINGS.programs)
+                      use_graphs=SETTINGS.graphs)
     store = load_weights(folder, arch.expected_tensors(config), device,
                          strip_prefixes=arch.strip_prefixes, ignorable=arch.ignorable)
     model = arch.build(config, store, runtime)

@@ -77,10 +77,6 @@ class ModelRunner:
         self.graph_max_tokens = runtime.max_batched_tokens
         self._graphs: Dict[tuple, tuple] = {}
         self._seen: Dict[tuple, int] = {}
-        # decode programs (whole steps of single tokens as one persistent kernel), same keys
-        self.use_programs = bool(runtime.use_programs) and runtime.dtype == torch.bfloat16 and \
-            getattr(model, "graph_safe", False)
-        self._programs: Dict[tuple, object] = {}
         self._pairs_host = torch.empty((runtime.max_requests, 2), dtype=torch.int32,
                                        pin_memory=True)
         self._pairs_dev = torch.zeros((runtime.max_requests, 2), dtype=torch.int32,
@@ -152,13 +148,6 @@ class ModelRunner:
         # without single tokens) gets a graph without the kernels of that list, since an idle
         # launch per layer is a tenth of a small decode step
         filled = tuple(bool(c) for view in ctx.work.values() for c in view.host_counts.values())
-        if self.use_programs and lay.t_cap <= ops.program_max_rows():
-            saved = [dict(view.host_counts) for view in ctx.work.values()]
-            logits = self._run_program(ctx, filled)
-            if logits is not None:
-                return logits
-            for view, counts in zip(ctx.work.values(), saved):
-                view.host_counts = counts
         if not self.use_graphs or lay.t_cap > self.graph_max_tokens:
             return self.model.forward(ctx)
         rows_cap = StepContext.row_capacity(max(ctx.n_rows, 1)) if ctx.n_rows else 0
@@ -318,34 +307,6 @@ class ModelRunner:
                 self.storage.copy_pages(g, self._pairs_dev, len(chunk), self.status)
                 torch.cuda.current_stream().synchronize()      # pinned pairs buffer is reused
                 self.counters["cow_copies"] += len(chunk)
-
-    def _run_program(self, ctx: StepContext, filled: tuple) -> Optional[torch.Tensor]:
-        """A step of single tokens only (decoding) as ONE persistent kernel: the model's
-        forward pass is recorded once per shape as a list of operations and from then on a
-        cooperative kernel interprets the list (``csrc/decode_program.cu``).  Returns None
-        when the model uses an operation a program cannot hold."""
-        lay = ctx.layout
-        rows_cap = StepContext.row_capacity(max(ctx.n_rows, 1)) if ctx.n_rows else 0
-        key = (lay.t_cap, lay.b_cap, rows_cap, filled)
-        hit = self._programs.get(key)
-        if hit is False:
-            return None
-        ctx.launch_tokens, ctx.launch_rows = lay.t_cap, rows_cap
-        self._counts_from_device(ctx)
-        ctx.max_context = self.model.max_positions
-        if hit is None:
-            try:
-                program = ops.Program(lay.t_cap, self.device)
-                with program:
-                    logits = self.model.forward(ctx)
-                program.finish()
-            except ops.NotRecordable:
-                self._programs[key] = False
-                return None
-            hit = (program, logits)
-            self._programs[key] = hit
-        hit[0].run(self.status)
-        return hit[1]
 
     def commit(self, entries: Sequence[Entry]) -> None:
         for e in entries:

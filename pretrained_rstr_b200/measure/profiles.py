@@ -44,6 +44,12 @@ def profile_gemm(shape: str) -> int:
             "bf16_bias_gelu_us": timeit(lambda: ops.gemm_bf16(outb, a, w, bias=bias, act="gelu_new", tile_n=tn)),
             "f32_bias_resid_us": timeit(lambda: ops.gemm_bf16(outf, a, w, bias=bias, resid=outf, tile_n=tn)),
         }
+    for tn in (64, 128, 192, 256):
+        res[f"pair{tn}"] = {
+            "bf16_plain_us": timeit(lambda: ops.gemm_bf16(outb, a, w, tile_n=tn, pair=True)),
+            "bf16_bias_gelu_us": timeit(lambda: ops.gemm_bf16(outb, a, w, bias=bias, act="gelu_new", tile_n=tn, pair=True)),
+            "f32_bias_resid_us": timeit(lambda: ops.gemm_bf16(outf, a, w, bias=bias, resid=outf, tile_n=tn, pair=True)),
+        }
     blocks = -(-k // 64)
     for tn in (64, 128):
         for sp in (2, 4, 8):

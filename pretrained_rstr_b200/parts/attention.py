@@ -186,8 +186,8 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
         n_list = work.caps["single_tokens"] if singles is None else singles
         cap = ctx.runtime.max_requests * AttentionWork.SINGLE_MAX_Q
         ring = SETTINGS.decode_ring
-        if ring is None:                 # (a whole-step program holds only the ring kernel)
-            ring = ops.recording() or ops.decode_ring_prefers(n_list, n_head, ctx.max_context)
+        if ring is None:
+            ring = ops.decode_ring_prefers(n_list, n_head, ctx.max_context)
         if ring and cap <= ops.decode_ring_max_list() and \
                 ops.decode_ring_supports(head_dim, group.page_size):
             ws = ctx.scratch("attn_ring_ws", (ops.decode_ring_workspace(cap, n_head, head_dim),),

@@ -7,7 +7,6 @@ this module is first imported.
 Python side (``SETTINGS``):
 
 ``PRB200_GRAPHS=0``        small steps are launched kernel by kernel instead of as CUDA graphs
-``PRB200_PROGRAMS=1``      decode-only steps run as one persistent kernel (off by default)
 ``PRB200_PDL=0``           no programmatic dependent launch between the kernels of a step
 ``PRB200_ATTN_TC=0``       prompt attention on ``mma.sync`` even where the tcgen05 kernel applies
 ``PRB200_PREFILL_PART=N``  key blocks per part of the tcgen05 prompt attention (-1: the kernel's rule)
@@ -44,7 +43,6 @@ def _int(name: str, default: int) -> int:
 @dataclass
 class Settings:
     graphs: bool = True
-    programs: bool = False
     pdl: bool = True
     attention_tcgen05: bool = True
     prefill_part: int = -1
@@ -53,8 +51,8 @@ class Settings:
 
     @classmethod
     def from_environment(cls) -> "Settings":
-        return cls(graphs=_flag("PRB200_GRAPHS", True), programs=_flag("PRB200_PROGRAMS", False),
-                   pdl=_flag("PRB200_PDL", True), attention_tcgen05=_flag("PRB200_ATTN_TC", True),
+        return cls(graphs=_flag("PRB200_GRAPHS", True), pdl=_flag("PRB200_PDL", True),
+                   attention_tcgen05=_flag("PRB200_ATTN_TC", True),
                    prefill_part=_int("PRB200_PREFILL_PART", -1),
                    decode_ctas=_int("PRB200_DECODE_CTAS", 0),
                    decode_ring=(_flag("PRB200_DECODE_RING", True)

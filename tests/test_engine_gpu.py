@@ -254,63 +254,35 @@ def test_trace_run_program(tmp_path, dtype):
     assert float((got7 - oracle["a"][66:70]).abs().max()) <= tol
 
 
-def _program_steps(folder, raw, programs, n_req):
-    """A prompt step of `n_req` requests, then four decode steps of all of them; the decode steps
-    run as one persistent kernel (`programs`) or kernel by kernel."""
-    lengths = [raw["n_positions"] - 5, 70, 9, 130, 33, 64, 65, 200][:n_req]
+def _decode_steps(folder, raw, graphs, n_req):
+    """A prompt step of `n_req` requests, then five decode steps of all of them, replayed as CUDA
+    graphs from the third on (`graphs`) or launched kernel by kernel."""
+    lengths = [raw["n_positions"] - 6, 70, 9, 130, 33, 64, 65, 200][:n_req]
     prompts = {f"d{i}": random_tokens(n, raw["vocab_size"], 50 + i) for i, n in enumerate(lengths)}
     rp = Replayer(folder, "bfloat16", max_tokens=sum(-(-n // 64) * 64 for n in lengths),
                   max_requests=8, max_batched_tokens=2048)
-    rp.lm.runner.use_programs = programs
-    rp.lm.runner.use_graphs = False
-    rp.step([(r, ids[:len(ids) - 4], [len(ids) - 5]) for r, ids in prompts.items()])
-    for k in range(4, 0, -1):
+    rp.lm.runner.use_graphs = graphs
+    rp.step([(r, ids[:len(ids) - 5], [len(ids) - 6]) for r, ids in prompts.items()])
+    for k in range(5, 0, -1):
         rp.step([(r, ids[len(ids) - k:len(ids) - k + 1], [0]) for r, ids in prompts.items()])
     return rp, prompts
 
 
 @pytest.mark.parametrize("n_req", [1, 3, 8])
-def test_decode_program_equals_kernel_by_kernel(folders, n_req):
-    """Decode-only steps of up to eight tokens run as one persistent kernel that interprets
-    the recorded step (weights and cached keys requested an operation ahead, a grid-wide
-    barrier between operations); the same steps launched kernel by kernel give the same
-    logits to rounding, and both match the plain implementation."""
+def test_decode_graphs_equal_kernel_by_kernel(folders, n_req):
+    """Decode steps replayed as CUDA graphs (planned with the capacities of their shape: the
+    longest context, padded rows) give the logits of the same steps launched kernel by kernel,
+    to rounding, and both match the plain implementation."""
     raw, seed = TINY["C"]
     folder = folders[("C", "bfloat16")]
     results = {}
-    for programs in (True, False):
-        rp, prompts = _program_steps(folder, raw, programs, n_req)
-        used = [v for v in rp.lm.runner._programs.values() if v]
-        assert bool(used) == programs
-        if programs:
-            assert used[0][0].length > 5 * raw["n_layer"]
+    for graphs in (True, False):
+        rp, prompts = _decode_steps(folder, raw, graphs, n_req)
+        assert bool(rp.lm.runner._graphs) == graphs
         compare(rp.rows, oracle_logits(folder, prompts), ATOL["bfloat16"])
-        results[programs] = rp.rows
+        results[graphs] = rp.rows
     for key, row in results[True].items():
         assert float((row - results[False][key]).abs().max()) <= 2e-3
-
-
-def test_decode_program_at_gpt2_small_widths(tmp_path):
-    """The same at the layer sizes the benchmark runs (width 768, 12 heads, inner width 3,072,
-    vocabulary 50,257; two layers): the products' rings, the head's 3,142 strips through four
-    buffers, the attention rings, all inside the one kernel."""
-    from helpers import bf16_atol, oracle_rows, real_width
-    raw = real_width("small")
-    folder = make_folder(str(tmp_path / "small"), raw, 2, "bfloat16")
-    rp, prompts = _program_steps(folder, raw, True, 8)
-    assert any(rp.lm.runner._programs.values())
-    wanted = {r: list(range(len(ids) - 5, len(ids))) for r, ids in prompts.items()}
-    compare(rp.rows, oracle_rows(folder, prompts, wanted), bf16_atol(raw["n_embd"]))
-
-
-def test_steps_a_program_cannot_hold_run_as_kernels(folders):
-    """A model whose sizes the one kernel does not take (head size 16, a width that is no
-    multiple of 64) is refused when the step is recorded and runs kernel by kernel."""
-    for name in ("A", "B"):
-        raw, seed = TINY[name]
-        rp, prompts = _program_steps(folders[(name, "bfloat16")], raw, True, 3)
-        assert rp.lm.runner._programs and not any(rp.lm.runner._programs.values())
-        compare(rp.rows, oracle_logits(folders[(name, "bfloat16")], prompts), ATOL["bfloat16"])
 
 
 def _run_cli(*args, stdin=None):

@@ -77,6 +77,36 @@ def test_gemm_bf16_every_tile_width(tile_n):
     assert float((out - ref).abs().max()) <= 1e-3
 
 
+@pytest.mark.parametrize("tile_n", [64, 128, 192, 256])
+@pytest.mark.parametrize("m,n,k", [(2048, 768, 768), (600, 1000, 1096), (130, 72, 136)])
+def test_gemm_bf16_cta_pairs(tile_n, m, n, k):
+    """Pairs of CTAs on 256-row tiles (one tcgen05.mma of the pair per 16 of K): both output
+    types, with bias, activation and residual, at sizes that leave ragged tiles in every
+    direction, an odd CTA with no rows at all, and more tiles than pairs of SMs."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(tile_n + m)
+    a = (torch.randn(m, k, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda", generator=g)
+    resid = torch.randn(m, n, device="cuda", generator=g)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ref = a.float() @ w.float().t() + bias
+    out = resid.clone()
+    ops.gemm_bf16(out, a, w, bias=bias, resid=out, tile_n=tile_n, pair=True, status=status)
+    assert float((out - (ref + resid)).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))
+    out16 = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(out16, a, w, bias=bias, act="gelu_new", tile_n=tile_n, pair=True, status=status)
+    want = _act("gelu_new", ref)
+    assert float((out16.float() - want).abs().max()) <= 1e-2 * max(1.0, float(want.abs().max()))
+    assert status.tolist() == [0, 0, 0, 0]
+    # one CTA per tile gives the same values: the same products summed in the same order
+    single = resid.clone()
+    ops.gemm_bf16(single, a, w, bias=bias, resid=single, tile_n=tile_n, status=status)
+    assert torch.equal(single, out)
+    with pytest.raises(ops.KernelArgumentError):
+        ops.gemm_bf16(out, a, w, tile_n=96, pair=True)
+
+
 @pytest.mark.parametrize("tile_n,split_k", [(64, 2), (64, 4), (64, 8), (128, 2), (128, 4), (128, 8)])
 @pytest.mark.parametrize("m,n,k", [(256, 768, 3072), (200, 600, 1000), (130, 72, 520)])
 def test_gemm_bf16_split_over_a_cluster(tile_n, split_k, m, n, k):
