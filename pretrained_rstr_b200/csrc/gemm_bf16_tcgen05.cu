@@ -430,14 +430,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     prefetch(tile_m0(nt) + quarter * 32, (nt / m_tiles) * BN + half * CH);
                 continue;
             }
-            // the cache slots of the rows this lane stores on the way back
-            int slot[(!F32) ? 8 : 1];
+            // where in a page array the rows this lane stores on the way back begin (element
+            // offset of head 0, dimension 0 of the token's slot; -1: no slot), worked out once
+            // per tile
+            long slot_at[(!F32) ? 8 : 1];
             if constexpr (!F32) {
                 if (sc.kv_width != 0) {
+                    const int kv_heads = sc.kv_width / sc.head_dim;
 #pragma unroll
                     for (int it = 0; it < 8; ++it) {
                         const int rr = row0 + it * 4 + rd_row;
-                        slot[it] = rr < m ? sc.slots[rr] : -1;
+                        const int slot = rr < m ? sc.slots[rr] : -1;
+                        slot_at[it] = -1;
+                        if (slot >= 0) {
+                            const int page = slot / sc.page_size, off = slot - page * sc.page_size;
+                            if (page >= sc.num_pages)
+                                prb_set_status(status, PRB_S_SLOT_RANGE, rr, slot, sc.num_pages);
+                            else
+                                slot_at[it] = ((long)page * kv_heads * sc.page_size + off) * sc.head_dim;
+                        }
                     }
                 }
             }
@@ -473,6 +484,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     else if (nt < total_tiles)
                         prefetch(tile_m0(nt) + quarter * 32, (nt / m_tiles) * BN + half * CH);
                     const int col = ncol + rd_piece * 4;
+                    // key or value columns: the page array and the offset of the lane's four
+                    // columns (inside one head: head sizes are multiples of 8) within a slot
+                    O* pages = nullptr;
+                    long head_at = 0;
+                    if constexpr (!F32) {
+                        if (sc.kv_width != 0 && col >= sc.q_width) {
+                            int cc = col - sc.q_width;
+                            pages = reinterpret_cast<O*>(cc < sc.kv_width ? sc.k_pages : sc.v_pages);
+                            if (cc >= sc.kv_width) cc -= sc.kv_width;
+                            const int h = cc / sc.head_dim;
+                            head_at = (long)h * sc.page_size * sc.head_dim + (cc - h * sc.head_dim);
+                        }
+                    }
                     if (rd_piece * 4 < n_valid) {
 #pragma unroll
                         for (int it = 0; it < 8; ++it) {
@@ -492,11 +516,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                 } else {
                                     const uint2 u = make_uint2(pack2(v0, v1), pack2(v2, v3));
                                     *reinterpret_cast<uint2*>(c + off) = u;
-                                    if (sc.kv_width != 0 && col >= sc.q_width) {
-                                        // four columns inside one head (head sizes are multiples of 8)
-                                        O* dst = scatter_dst<O>(sc, col, slot[it], row0 + tr, status);
-                                        if (dst) *reinterpret_cast<uint2*>(dst) = u;
-                                    }
+                                    if (pages != nullptr && slot_at[it] >= 0)
+                                        *reinterpret_cast<uint2*>(pages + slot_at[it] + head_at) = u;
                                 }
                             }
                         }

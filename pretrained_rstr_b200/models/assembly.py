@@ -98,7 +98,8 @@ class Model:
     # --------------------------------------------------------------------- forward
     def forward(self, ctx) -> torch.Tensor:
         """Run the step's tokens through the model; returns float32 logits [rows, vocab]
-        for ``ctx.logit_rows`` (a view of scratch memory: copy it to keep it)."""
+        for ``ctx.logit_rows`` (a view of scratch memory whose rows are padded to a multiple
+        of 32 elements: copy it to keep it)."""
         t = ctx.launch_tokens
         x = ctx.scratch("residual", (ctx.token_capacity, self.width), torch.float32)[:t]
         self.embedding.forward(ctx, self.position, x)
@@ -109,7 +110,11 @@ class Model:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=x.device)
         hn = ctx.scratch("final_normed", (ctx.row_capacity(r), self.width), self.runtime.dtype)[:r]
         self.final_norm.forward(ctx, x, hn, rows=ctx.logit_rows)
-        logits = ctx.scratch("logits", (ctx.row_capacity(r), self.vocab), torch.float32)[:r]
+        # rows 128 bytes apart at least: a vocabulary that is no multiple of 4 (GPT-2's 50,257)
+        # would otherwise put every row at an odd address, which the products' epilogues can
+        # only store element by element
+        pitch = -(-self.vocab // 32) * 32
+        logits = ctx.scratch("logits", (ctx.row_capacity(r), pitch), torch.float32)[:r, :self.vocab]
         self.head.forward(ctx, hn, logits)
         return logits
 
