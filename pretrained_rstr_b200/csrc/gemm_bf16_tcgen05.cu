@@ -908,6 +908,28 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
                 }
             }
         }
+        // Pairs of CTAs on 256-row tiles take in half the bytes of W per multiply-add, which
+        // is what bounds the main loop once every SM is loading; they cost a cluster's set-up
+        // and need enough 256-row tiles to go round.  Times in nanoseconds, fitted to
+        // measurements at K = 768 to 6,400 (a k-block of a single CTA: 190 + width, of a
+        // pair: 230 + width / 2; an epilogue: 1,900 + 14.5 a column, a quarter more with an
+        // activation): pairs win at GPT-2 XL's widths and beyond, not at GPT-2 small's.
+        if (split == 0 && kb >= 16) {
+            const double act_factor = (act == PRB_ACT_NONE) ? 1.0 : 1.25;
+            auto model = [&](long tiles, long walkers, double per_kb, double setup, int bn) {
+                const double rounds = (double)((tiles + walkers - 1) / walkers);
+                const double main_loop = kb * per_kb, epilogue = (1900.0 + 14.5 * bn) * act_factor;
+                return setup + (rounds - 1) * (main_loop > epilogue ? main_loop : epilogue) +
+                       main_loop + epilogue;
+            };
+            const double single = model(mt * ((n + tile_n - 1) / tile_n), sms, 190.0 + tile_n, 1300.0, tile_n);
+            double best_pair = single * 0.95;
+            const long mt2 = (m + 2 * BM - 1) / (2 * BM);
+            for (int bn = 256; bn >= 128; bn -= 64) {
+                const double t = model(mt2 * ((n + bn - 1) / bn), sms / 2, 230.0 + bn / 2.0, 1900.0, bn);
+                if (t < best_pair) { best_pair = t; tile_n = bn; pair = 1; }
+            }
+        }
     }
     if (split != 0 && (sc.kv_width != 0 || (split != 2 && split != 4 && split != 8) ||
                        (tile_n != 64 && tile_n != 128) ||
