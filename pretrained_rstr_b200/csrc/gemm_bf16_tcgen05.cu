@@ -25,6 +25,7 @@
 #include <cudaTypedefs.h>
 
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "common.cuh"
@@ -497,16 +498,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             head_at = (long)h * sc.page_size * sc.head_dim + (cc - h * sc.head_dim);
                         }
                     }
-                    if (rd_piece * 4 < n_valid) {
+                    // (the activation is chosen outside the loop: chosen per element, its branches
+                    // were most of the epilogue's time, a lone warp having nothing to hide them with)
+                    auto way_back = [&](auto kind) {
+                        constexpr int KIND = decltype(kind)::value;
 #pragma unroll
                         for (int it = 0; it < 8; ++it) {
                             const int tr = it * 4 + rd_row;           // row of the tile
                             const float4 a4 = *reinterpret_cast<const float4*>(
                                 warp_stage + tr * 128 + ((rd_piece ^ (tr & 7)) << 4));
-                            float v0 = epilogue_act(a4.x + b_now.x, act);
-                            float v1 = epilogue_act(a4.y + b_now.y, act);
-                            float v2 = epilogue_act(a4.z + b_now.z, act);
-                            float v3 = epilogue_act(a4.w + b_now.w, act);
+                            float v0 = a4.x + b_now.x, v1 = a4.y + b_now.y, v2 = a4.z + b_now.z,
+                                  v3 = a4.w + b_now.w;
+                            if constexpr (KIND == 1) {
+                                v0 = gelu_tanh_fast(v0); v1 = gelu_tanh_fast(v1);
+                                v2 = gelu_tanh_fast(v2); v3 = gelu_tanh_fast(v3);
+                            } else if constexpr (KIND == 2) {
+                                v0 = prb_activate(v0, act); v1 = prb_activate(v1, act);
+                                v2 = prb_activate(v2, act); v3 = prb_activate(v3, act);
+                            }
                             if (row0 + tr < m) {
                                 const size_t off = (size_t)(row0 + tr) * ldc + col;
                                 if constexpr (F32) {
@@ -521,6 +530,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                 }
                             }
                         }
+                    };
+                    if (rd_piece * 4 < n_valid) {
+                        if (act == PRB_ACT_NONE) way_back(std::integral_constant<int, 0>{});
+                        else if (act == PRB_ACT_GELU_TANH) way_back(std::integral_constant<int, 1>{});
+                        else way_back(std::integral_constant<int, 2>{});
                     }
                 } else {
                     // tail columns or unaligned rows (e.g. a vocabulary that is odd): one by one
@@ -898,12 +912,14 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
         // CTA finishes only its share of the tile's rows (constants fitted to measurements at
         // 128 to 1,024 rows, N = 768 and 1,600, K = 768 to 6,400).
         if (sc.kv_width == 0) {
-            for (int bn = 128; bn >= 64; bn -= 64) {
+            for (int bn = 256; bn >= 64; bn -= 64) {
                 const long tiles = mt * ((n + bn - 1) / bn);
-                for (int sp = 2; sp <= 8; sp *= 2) {
+                for (int sp = 2; sp <= (bn > 128 ? 2 : 8); sp *= 2) {
                     const long per = (kb + sp - 1) / sp;
                     if (tiles * sp > sms || per * (sp - 1) >= kb || per < 2) continue;
-                    const long cost = per * (128 + bn) + 400 + 700 + per_col * bn / 2;
+                    // (the partial tiles' way through shared memory grows with their width)
+                    const long exchange = bn > 128 ? 300 + 6 * bn : 700;
+                    const long cost = per * (128 + bn) + 400 + exchange + per_col * bn / 2;
                     if (cost < best) { best = cost; tile_n = bn; split = sp; }
                 }
             }
@@ -932,7 +948,7 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
         }
     }
     if (split != 0 && (sc.kv_width != 0 || (split != 2 && split != 4 && split != 8) ||
-                       (tile_n != 64 && tile_n != 128) ||
+                       (tile_n != 64 && tile_n != 128 && !(split == 2 && (tile_n == 192 || tile_n == 256))) ||
                        (((k + BK - 1) / BK + split - 1) / split) * (split - 1) >= (k + BK - 1) / BK))
         return PRB_E_ARG;
     if (tile_n < 32 || tile_n > 256 || tile_n % 32 != 0) return PRB_E_ARG;
@@ -971,6 +987,8 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
          : launch_splitk<BN_, S_, __nv_bfloat16>(ma, mw, (__nv_bfloat16*)c, bias, resid, m, n, k, \
                                                  ldc, act, status, stream))
     if (split != 0) {
+        if (tile_n == 192) return PRB_GO_SPLIT(192, 2);
+        if (tile_n == 256) return PRB_GO_SPLIT(256, 2);
         if (tile_n == 64)
             return split == 2 ? PRB_GO_SPLIT(64, 2) : split == 4 ? PRB_GO_SPLIT(64, 4) : PRB_GO_SPLIT(64, 8);
         return split == 2 ? PRB_GO_SPLIT(128, 2) : split == 4 ? PRB_GO_SPLIT(128, 4) : PRB_GO_SPLIT(128, 8);
@@ -991,7 +1009,8 @@ int gemm_bf16_entry(void* c, const void* a, const void* w, const float* bias, co
 }  // namespace
 
 // tile_n: 0 = choose (by M, N, K and the output type), or a multiple of 32 up to 256; with a
-// cluster size of 2, 4 or 8 in bits 16 to 23, the split-K variant at tile width 64 or 128;
+// cluster size of 2, 4 or 8 in bits 16 to 23, the split-K variant at tile width 64 or 128
+// (cluster size 2: also 192 and 256);
 // with bit 24, CTA pairs on 256-row tiles at tile width 64, 128, 192 or 256.
 PRB_API int prb_gemm_bf16(void* c, const void* a, const void* w, const float* bias,
                           const float* resid, int m, int n, int k, long lda, long ldw, long ldc,

@@ -51,8 +51,8 @@ def profile_gemm(shape: str) -> int:
             "f32_bias_resid_us": timeit(lambda: ops.gemm_bf16(outf, a, w, bias=bias, resid=outf, tile_n=tn, pair=True)),
         }
     blocks = -(-k // 64)
-    for tn in (64, 128):
-        for sp in (2, 4, 8):
+    for tn in (64, 128, 192, 256):
+        for sp in ((2, 4, 8) if tn <= 128 else (2,)):
             if -(-blocks // sp) * (sp - 1) >= blocks or -(-m // 128) * -(-n // tn) * sp > 148:
                 continue
             res[f"tile{tn}_split{sp}"] = {

@@ -107,7 +107,8 @@ def test_gemm_bf16_cta_pairs(tile_n, m, n, k):
         ops.gemm_bf16(out, a, w, tile_n=96, pair=True)
 
 
-@pytest.mark.parametrize("tile_n,split_k", [(64, 2), (64, 4), (64, 8), (128, 2), (128, 4), (128, 8)])
+@pytest.mark.parametrize("tile_n,split_k", [(64, 2), (64, 4), (64, 8), (128, 2), (128, 4), (128, 8),
+                                            (192, 2), (256, 2)])
 @pytest.mark.parametrize("m,n,k", [(256, 768, 3072), (200, 600, 1000), (130, 72, 520)])
 def test_gemm_bf16_split_over_a_cluster(tile_n, split_k, m, n, k):
     """The reduction of a tile split over a thread-block cluster: both output types, with
