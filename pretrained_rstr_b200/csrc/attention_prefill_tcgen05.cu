@@ -214,85 +214,99 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
-        if (lane == 0) {
-            const uint32_t qb = smem_u32(q_full);
+        // (The whole warp walks the loop and waits; one elected lane issues: inside
+        // "if (lane == 0)" the warp would be divergent for its whole life and the copy and MMA
+        // instructions, whose operands live in uniform registers, issue several times slower.)
+        const uint32_t qb = smem_u32(q_full);
+        if (elect_one()) {
             mbar_expect_tx(qb, Q_BYTES);
             tma_load_2d(smem_u32(q_s), &map_q, qb, h * DH, row0);
-            bool ok = true;
-            int j = 0;
-            for (; j < n_blocks && ok; ++j) {
-                const int st = j % STAGES;
-                ok = mbar_wait(smem_u32(&kv_empty[st]), ((j / STAGES) & 1) ^ 1, failed);
-                if (!ok) {
-                    prb_set_status(p.status, PRB_S_WAIT_TIMEOUT, 11, blockIdx.x, j);
-                    break;
-                }
-                const int key0 = (blk_first + j) * KB;
-                const int page = table[key0 / p.page_size];
-                const uint32_t fb = smem_u32(&kv_full[st]);
-                if (page < 0 || page >= p.num_pages) {
-                    // recorded; the block's buffer keeps what it held and the result of the
-                    // tile is not to be used
+        }
+        __syncwarp();
+        bool ok = true;
+        int j = 0;
+        for (; j < n_blocks && ok; ++j) {
+            const int st = j % STAGES;
+            ok = mbar_wait_warp(smem_u32(&kv_empty[st]), ((j / STAGES) & 1) ^ 1, failed);
+            if (!ok) {
+                if (lane == 0) prb_set_status(p.status, PRB_S_WAIT_TIMEOUT, 11, blockIdx.x, j);
+                break;
+            }
+            const int key0 = (blk_first + j) * KB;
+            const int page = table[key0 / p.page_size];
+            const uint32_t fb = smem_u32(&kv_full[st]);
+            if (page < 0 || page >= p.num_pages) {
+                // recorded; the block's buffer keeps what it held and the result of the
+                // tile is not to be used
+                if (lane == 0) {
                     prb_set_status(p.status, PRB_S_PAGE_RANGE, row0, key0, page);
                     mbar_arrive(fb);
-                    continue;
                 }
-                const int crow = (page * p.kv_heads + hk) * p.page_size + key0 % p.page_size;
-                mbar_expect_tx(fb, STAGE_BYTES);
-                uint8_t* stage = ring + (size_t)st * STAGE_BYTES;
-                tma_load_2d(smem_u32(stage), &map_k, fb, 0, crow);
-                tma_load_2d(smem_u32(stage + K_BYTES), &map_v, fb, 0, crow);
+                __syncwarp();
+                continue;
             }
-            if (!ok) {
-                // wait (bounded) for loads still in flight before the CTA may exit
+            const int crow = (page * p.kv_heads + hk) * p.page_size + key0 % p.page_size;
+            const uint32_t stage = smem_u32(ring + (size_t)st * STAGE_BYTES);
+            if (elect_one()) {
+                mbar_expect_tx(fb, STAGE_BYTES);
+                tma_load_2d(stage, &map_k, fb, 0, crow);
+                tma_load_2d(stage + K_BYTES, &map_v, fb, 0, crow);
+            }
+            __syncwarp();
+        }
+        if (!ok && lane == 0) {
+            // wait (bounded) for loads still in flight before the CTA may exit
+            for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+                if (mbar_try_wait(smem_u32(q_full), 0)) break;
+            const int first = j > STAGES ? j - STAGES : 0;
+            for (int jj = first; jj < j; ++jj) {
+                const uint32_t fb = smem_u32(&kv_full[jj % STAGES]);
                 for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-                    if (mbar_try_wait(smem_u32(q_full), 0)) break;
-                const int first = j > STAGES ? j - STAGES : 0;
-                for (int jj = first; jj < j; ++jj) {
-                    const uint32_t fb = smem_u32(&kv_full[jj % STAGES]);
-                    for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-                        if (mbar_try_wait(fb, (jj / STAGES) & 1)) break;
-                }
+                    if (mbar_try_wait(fb, (jj / STAGES) & 1)) break;
             }
         }
+        __syncwarp();
     } else if (warp == 1) {
         // ---------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_s = make_idesc(QT, KB);          // Q, K: both K-major
-            constexpr uint32_t idesc_o = make_idesc_b_mn(QT, DH);     // P K-major, V MN-major
-            const uint64_t q_desc = make_smem_desc(smem_u32(q_s));
-            auto issue_scores = [&](int j) {
-                const uint8_t* stage = ring + (size_t)(j % STAGES) * STAGE_BYTES;
-                const uint64_t k_desc = make_smem_desc(smem_u32(stage));
-                const uint32_t d = tmem_base + (uint32_t)((j & 1) * KB);
+        constexpr uint32_t idesc_s = make_idesc(QT, KB);          // Q, K: both K-major
+        constexpr uint32_t idesc_o = make_idesc_b_mn(QT, DH);     // P K-major, V MN-major
+        const uint64_t q_desc = make_smem_desc(smem_u32(q_s));
+        auto issue_scores = [&](int j) {
+            const uint8_t* stage = ring + (size_t)(j % STAGES) * STAGE_BYTES;
+            const uint64_t k_desc = make_smem_desc(smem_u32(stage));
+            const uint32_t d = tmem_base + (uint32_t)((j & 1) * KB);
+            if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < DH / 16; ++kk)
                     umma_bf16(d, q_desc + (uint64_t)(kk * 2), k_desc + (uint64_t)(kk * 2), idesc_s,
                               kk > 0 ? 1u : 0u);
                 umma_commit(smem_u32(&s_full[j & 1]));
-            };
-            bool ok = mbar_wait(smem_u32(q_full), 0, failed);
-            if (ok) ok = mbar_wait(smem_u32(&kv_full[0]), 0, failed);
-            if (ok) {
-                tcgen05_fence_after();
-                issue_scores(0);
             }
-            for (int j = 0; j < n_blocks && ok; ++j) {
-                if (j + 1 < n_blocks) {
-                    ok = mbar_wait(smem_u32(&kv_full[(j + 1) % STAGES]), ((j + 1) / STAGES) & 1, failed);
-                    if (!ok) break;
-                    tcgen05_fence_after();
-                    issue_scores(j + 1);
-                }
-                PF_TRACE(j, 8);
-                ok = mbar_wait(smem_u32(p_full), j & 1, failed);
+            __syncwarp();
+        };
+        bool ok = mbar_wait_warp(smem_u32(q_full), 0, failed);
+        if (ok) ok = mbar_wait_warp(smem_u32(&kv_full[0]), 0, failed);
+        if (ok) {
+            tcgen05_fence_after();
+            issue_scores(0);
+        }
+        for (int j = 0; j < n_blocks && ok; ++j) {
+            if (j + 1 < n_blocks) {
+                ok = mbar_wait_warp(smem_u32(&kv_full[(j + 1) % STAGES]), ((j + 1) / STAGES) & 1, failed);
                 if (!ok) break;
-                PF_TRACE(j, 9);
                 tcgen05_fence_after();
-                const uint8_t* stage = ring + (size_t)(j % STAGES) * STAGE_BYTES;
-                const uint32_t v_addr = smem_u32(stage + K_BYTES);
-                const uint64_t pj_desc = make_smem_desc(smem_u32(p_s + (size_t)(j & 1) * P_BYTES));
-                const uint32_t d = tmem_base + 2 * KB;
+                issue_scores(j + 1);
+            }
+            PF_TRACE(j, 8);
+            ok = mbar_wait_warp(smem_u32(p_full), j & 1, failed);
+            if (!ok) break;
+            PF_TRACE(j, 9);
+            tcgen05_fence_after();
+            const uint8_t* stage = ring + (size_t)(j % STAGES) * STAGE_BYTES;
+            const uint32_t v_addr = smem_u32(stage + K_BYTES);
+            const uint64_t pj_desc = make_smem_desc(smem_u32(p_s + (size_t)(j & 1) * P_BYTES));
+            const uint32_t d = tmem_base + 2 * KB;
+            if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < KB / 16; ++kk) {
                     // 16 keys further: two 8-row groups of 1024 bytes; O accumulates over blocks
@@ -301,10 +315,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 }
                 umma_commit(smem_u32(o_full));
                 umma_commit(smem_u32(&kv_empty[j % STAGES]));     // frees the stage
-                PF_TRACE(j, 10);
             }
-            if (!ok) prb_set_status(p.status, PRB_S_WAIT_TIMEOUT, 12, blockIdx.x, 0);
+            __syncwarp();
+            PF_TRACE(j, 10);
         }
+        if (!ok && lane == 0) prb_set_status(p.status, PRB_S_WAIT_TIMEOUT, 12, blockIdx.x, 0);
     } else {
         // ------------------------------------------------------------- softmax
         // Two threads per query row: warps 2-5 take key columns 0-31 of a block and output

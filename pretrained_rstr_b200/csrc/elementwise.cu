@@ -84,8 +84,20 @@ layernorm_warp_kernel(elementwise::NormArgs a) {
     for (int i = 0; i < 8; ++i) {
         const int idx = lane + 32 * i;
         v[i] = idx < nvec ? x4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
-        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     }
+    // gamma and beta are asked for before the statistics are reduced, not after: the row's
+    // way through the kernel is one memory round trip long instead of two
+    const float4* g4 = reinterpret_cast<const float4*>(a.gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(a.beta);
+    float4 g[8], b[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = lane + 32 * i;
+        g[i] = idx < nvec ? __ldg(g4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+        b[i] = (idx < nvec && a.beta) ? __ldg(b4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     const float mean = prb_warp_sum(s) / (float)a.width;
     float q = 0.0f;
 #pragma unroll
@@ -97,16 +109,12 @@ layernorm_warp_kernel(elementwise::NormArgs a) {
         }
     }
     const float inv = 1.0f / sqrtf(prb_warp_sum(q) / (float)a.width + a.eps);
-    const float4* g4 = reinterpret_cast<const float4*>(a.gamma);
-    const float4* b4 = reinterpret_cast<const float4*>(a.beta);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int idx = lane + 32 * i;
         if (idx < nvec) {
-            const float4 g = g4[idx];
-            const float4 b = a.beta ? b4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
-            const float y0 = (v[i].x - mean) * inv * g.x + b.x, y1 = (v[i].y - mean) * inv * g.y + b.y;
-            const float y2 = (v[i].z - mean) * inv * g.z + b.z, y3 = (v[i].w - mean) * inv * g.w + b.w;
+            const float y0 = (v[i].x - mean) * inv * g[i].x + b[i].x, y1 = (v[i].y - mean) * inv * g[i].y + b[i].y;
+            const float y2 = (v[i].z - mean) * inv * g[i].z + b[i].z, y3 = (v[i].w - mean) * inv * g[i].w + b[i].w;
             if constexpr (sizeof(O) == 4) {
                 *reinterpret_cast<float4*>(out + idx * 4) = make_float4(y0, y1, y2, y3);
             } else {

@@ -666,57 +666,62 @@ gemm_bf16_splitk_kernel(const __grid_constant__ CUtensorMap map_a,
         }
     }
     if (warp == 0) {
-        if (lane == 0) {
-            bool ok = true;
-            int it = 0;
-            for (; it < n_kb; ++it) {
-                const int s = it % Cfg::STAGES;
-                ok = mbar_wait(smem_u32(&empty_bar[s]), ((it / Cfg::STAGES) & 1) ^ 1, failed);
-                if (!ok) {
-                    prb_set_status(status, PRB_S_WAIT_TIMEOUT, 21, blockIdx.x, it);
-                    break;
-                }
-                const uint32_t fb = smem_u32(&full_bar[s]);
-                mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-                uint8_t* stage = tiles + (size_t)s * Cfg::STAGE_BYTES;
-                tma_load_2d(smem_u32(stage), &map_a, fb, (kb0 + it) * BK, m0);
-                tma_load_2d(smem_u32(stage + Cfg::A_BYTES), &map_w, fb, (kb0 + it) * BK, n0);
-            }
+        // (whole warps walk the loops, one elected lane issues: see the kernel above)
+        bool ok = true;
+        int it = 0;
+        for (; it < n_kb; ++it) {
+            const int s = it % Cfg::STAGES;
+            ok = mbar_wait_warp(smem_u32(&empty_bar[s]), ((it / Cfg::STAGES) & 1) ^ 1, failed);
             if (!ok) {
-                const int first = it > Cfg::STAGES ? it - Cfg::STAGES : 0;
-                for (int j = first; j < it; ++j) {
-                    const uint32_t fb = smem_u32(&full_bar[j % Cfg::STAGES]);
-                    for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-                        if (mbar_try_wait(fb, (j / Cfg::STAGES) & 1)) break;
-                }
+                if (lane == 0) prb_set_status(status, PRB_S_WAIT_TIMEOUT, 21, blockIdx.x, it);
+                break;
+            }
+            const uint32_t fb = smem_u32(&full_bar[s]);
+            const uint32_t stage = smem_u32(tiles + (size_t)s * Cfg::STAGE_BYTES);
+            if (elect_one()) {
+                mbar_expect_tx(fb, Cfg::STAGE_BYTES);
+                tma_load_2d(stage, &map_a, fb, (kb0 + it) * BK, m0);
+                tma_load_2d(stage + Cfg::A_BYTES, &map_w, fb, (kb0 + it) * BK, n0);
+            }
+            __syncwarp();
+        }
+        if (!ok && lane == 0) {
+            const int first = it > Cfg::STAGES ? it - Cfg::STAGES : 0;
+            for (int j = first; j < it; ++j) {
+                const uint32_t fb = smem_u32(&full_bar[j % Cfg::STAGES]);
+                for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+                    if (mbar_try_wait(fb, (j / Cfg::STAGES) & 1)) break;
             }
         }
+        __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BM, BN);
-            bool ok = true;
-            for (int it = 0; it < n_kb; ++it) {
-                const int s = it % Cfg::STAGES;
-                ok = mbar_wait(smem_u32(&full_bar[s]), (it / Cfg::STAGES) & 1, failed);
-                if (!ok) {
-                    prb_set_status(status, PRB_S_WAIT_TIMEOUT, 22, blockIdx.x, it);
-                    break;
-                }
-                tcgen05_fence_after();
-                const uint32_t a_addr = smem_u32(tiles + (size_t)s * Cfg::STAGE_BYTES);
-                const uint64_t a_desc = make_smem_desc(a_addr);
-                const uint64_t b_desc = make_smem_desc(a_addr + Cfg::A_BYTES);
+        constexpr uint32_t idesc = make_idesc(BM, BN);
+        bool ok = true;
+        for (int it = 0; it < n_kb; ++it) {
+            const int s = it % Cfg::STAGES;
+            ok = mbar_wait_warp(smem_u32(&full_bar[s]), (it / Cfg::STAGES) & 1, failed);
+            if (!ok) {
+                if (lane == 0) prb_set_status(status, PRB_S_WAIT_TIMEOUT, 22, blockIdx.x, it);
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t a_addr = smem_u32(tiles + (size_t)s * Cfg::STAGE_BYTES);
+            const uint64_t a_desc = make_smem_desc(a_addr);
+            const uint64_t b_desc = make_smem_desc(a_addr + Cfg::A_BYTES);
+            if (elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < BK / UMMA_K; ++kk)
                     umma_bf16(tmem_base, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2),
                               idesc, (it > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(smem_u32(&empty_bar[s]));
             }
-            if (ok) {
-                if (n_kb > 0) umma_commit(smem_u32(tfull_bar));
-                else mbar_arrive(smem_u32(tfull_bar));       // nothing to wait for
-            }
+            __syncwarp();
         }
+        if (ok && elect_one()) {
+            if (n_kb > 0) umma_commit(smem_u32(tfull_bar));
+            else mbar_arrive(smem_u32(tfull_bar));       // nothing to wait for
+        }
+        __syncwarp();
     } else {
         // the accumulator, one row per thread, into the partial tile
         const int quarter = warp & 3, half = (warp - 2) >> 2;
