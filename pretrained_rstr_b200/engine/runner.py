@@ -140,7 +140,7 @@ class ModelRunner:
     def _run(self, ctx: StepContext) -> torch.Tensor:
         """Run the model for a prepared step: directly, or, for small steps when graphs are
         on, as a CUDA graph of the whole step.  A graph is captured for fixed capacities
-        (tokens, requests, logits rows); rows beyond the real ones are padding that no
+        (tokens, requests, logits rows, longest context); rows beyond the real ones are padding that no
         kernel lets touch the cache.  The first step of a shape runs directly with the
         padded sizes (which also sizes all scratch memory), the second is captured."""
         lay = ctx.layout
@@ -151,10 +151,17 @@ class ModelRunner:
         if not self.use_graphs or lay.t_cap > self.graph_max_tokens:
             return self.model.forward(ctx)
         rows_cap = StepContext.row_capacity(max(ctx.n_rows, 1)) if ctx.n_rows else 0
-        key = (lay.t_cap, lay.b_cap, rows_cap, filled)
+        # the longest context the graph is planned for: the step's own bound rounded up to
+        # 256, 512, 1,024, ... (the attention kernels choose their splits, and which of them
+        # runs, by it; a graph for every length would be captured all the time)
+        reach = 256
+        while reach < ctx.max_context:
+            reach *= 2
+        reach = min(reach, self.model.max_positions)
+        key = (lay.t_cap, lay.b_cap, rows_cap, filled, reach)
         ctx.launch_tokens, ctx.launch_rows = lay.t_cap, rows_cap
         self._counts_from_device(ctx)
-        ctx.max_context = self.model.max_positions
+        ctx.max_context = reach
         hit = self._graphs.get(key)
         if hit is not None:
             hit[0].replay()
