@@ -61,7 +61,7 @@ class Linear:
         if self.runtime.dtype == torch.float32:
             ops.gemm_f32(out, _tensor(a), self.weight, self.bias, resid, act)
             return False
-        # Which kernel (measured on GPT-2 small and XL shapes, see profiles/): up to 16 rows
+        # Which kernel (measured on GPT-2 small and XL shapes): up to 16 rows
         # the weight-streaming kernel with the norm fused into it; 17 to 64 rows the cluster
         # split-K kernel for narrow outputs and long reductions, the tensor-memory kernel for
         # wide outputs (the register-streaming kernel where K is no multiple of 64); beyond
