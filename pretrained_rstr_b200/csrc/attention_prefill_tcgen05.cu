@@ -413,6 +413,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 for (int i = 0; i < HD; ++i) ob[i] = __float_as_uint(__uint_as_float(ob[i]) * corr);
                 tmem_st_32x32(lane_addr + (uint32_t)(2 * KB + half * HD), ob);
             }
+            // Keys after the tile's last query position (the rest of the request's last page)
+            // hold whatever the page's earlier owner left there.  Their weights are zero, but
+            // zero times a NaN or an infinity is a NaN: their value rows are cleared before
+            // the product reads them (whole 128-byte rows, so the swizzle does not matter).
+            const int first_stale = pos_last + 1 - (blk_first + j) * KB;    // key row within the block
+            if (ok && first_stale < KB) {
+                const uint32_t v_tile = smem_u32(ring + (size_t)(j % STAGES) * STAGE_BYTES + K_BYTES);
+                const int t = (warp - 2) * 32 + lane;
+                for (int piece = (first_stale < 0 ? 0 : first_stale) * 8 + t; piece < KB * 8; piece += 256)
+                    st_shared_v4(v_tile + (uint32_t)piece * 16, 0u, 0u, 0u, 0u);
+            }
             // 16-byte pieces of row r, swizzled with the row as TMA would have placed them
             const uint32_t p_dst = p_row + (uint32_t)((j & 1) * P_BYTES);
 #pragma unroll

@@ -454,6 +454,14 @@ def test_attention_prefill(nh, nkv, dh, ps, window, tile):
                              "parts": _prefill_parts(len(tiles) * nh, most)}))
     else:
         assert not (dh == 64 and ps % 64 == 0)
+    # what a page's earlier owner may have left after a request's last position must not
+    # reach the output: not-a-number there, in keys and in values
+    k, v = k.clone(), v.clone()
+    for b, n in enumerate(lengths):
+        if n % ps:
+            page = int(table[b, (n - 1) // ps])
+            k[page, :, n % ps:, :] = float("nan")
+            v[page, :, n % ps:, :] = float("nan")
     for name, kernel, kw in kernels:
         status = torch.zeros(4, dtype=torch.int32, device="cuda")
         out = torch.full_like(q, float("nan"))
@@ -565,6 +573,34 @@ def test_gemm_smallm_rows_do_not_depend_on_the_batch(k):
     assert torch.equal(one[0], mid[7])             # the same kernel: the same bits
     # 40 rows go to another kernel, which adds the same products in another order
     assert float((big[17] - one[0]).abs().max()) <= 2e-4 * float(big[17].abs().max())
+
+
+@pytest.mark.parametrize("k", [64, 768, 1024, 1600])
+def test_gemm_smallm_fused_norm_with_an_outlier_channel(k):
+    """A row whose first channel is thousands among values of order one (as massive
+    activations are): the fused norm's statistics are mean first, then centred squares, and
+    agree with the two-pass norm kernel followed by the plain product; a one-pass variance on
+    data shifted by the first element would cancel here."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(k)
+    m, n = 5, 96
+    x = torch.randn(m, k, device="cuda", generator=g)
+    x[:, 0] = torch.tensor([3e3, -2e3, 5e3, 1.0, 8e3], device="cuda")
+    x[2, k // 2] = -4e3
+    gamma = torch.rand(k, device="cuda", generator=g) + 0.5
+    beta = torch.randn(k, device="cuda", generator=g) * 0.1
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    fused = torch.zeros(m, n, device="cuda")
+    ops.gemm_smallm(fused, w, norm_input=x, gamma=gamma, beta=beta, eps=1e-5)
+    normed = torch.zeros(m, k, device="cuda", dtype=torch.bfloat16)
+    ops.layernorm(normed, x, gamma, beta, 1e-5)
+    apart = torch.zeros(m, n, device="cuda")
+    ops.gemm_smallm(apart, w, a=normed)
+    ref = torch.nn.functional.layer_norm(x.double(), (k,), gamma.double(), beta.double(), 1e-5)
+    ref = (ref.float().to(torch.bfloat16).float() @ w.float().t())
+    scale = max(1.0, float(ref.abs().max()))
+    assert float((fused - apart).abs().max()) <= 2e-3 * scale
+    assert float((fused - ref).abs().max()) <= 1e-2 * scale
 
 
 # ------------------------------------------------------------------------ small kernels
