@@ -46,11 +46,27 @@ __device__ unsigned long long g_pf_trace[64 * 16];
             g_pf_trace[(j) * 16 + (slot)] = t__;                                      \
         }                                                                             \
     } while (0)
+// per CTA (linear block index): start, -, first scores seen, last block done, end, key blocks, SM
+__device__ unsigned long long g_pf_cta[8192 * 8];
+#define PF_CTA(slot, value)                                                           \
+    do {                                                                              \
+        const unsigned id__ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x; \
+        if (id__ < 8192) g_pf_cta[id__ * 8 + (slot)] = (value);                        \
+    } while (0)
+__device__ __forceinline__ unsigned long long pf_now() {
+    unsigned long long t__;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));
+    return t__;
+}
+PRB_API int prb_attention_prefill_tc_cta_trace(unsigned long long* host, int n) {
+    return (int)cudaMemcpyFromSymbol(host, g_pf_cta, sizeof(unsigned long long) * n);
+}
 PRB_API int prb_attention_prefill_tc_trace(unsigned long long* host, int n) {
     return (int)cudaMemcpyFromSymbol(host, g_pf_trace, sizeof(unsigned long long) * n);
 }
 #else
 #define PF_TRACE(j, slot)
+#define PF_CTA(slot, value)
 #endif
 
 namespace {
@@ -75,6 +91,15 @@ struct Params {
     float* part_ml;                 // [...][QT][2]: maximum (log2 units) and sum of a row
     int* part_count;                // [tile * heads + head], zero before and after
     int part_blocks;                // blocks per chunk; 0: one CTA per (tile, head)
+    // Work items (optional; else a CTA's tile and chunk are its grid indices x and z): item i
+    // is tile item_tile[i] as a whole (item_part[i] < 0) or its chunk item_part[i], whose
+    // partial result goes to slot item_slot[i] of the workspace (the chunks of a tile have
+    // consecutive slots, chunk 0 first); the chunk size is read from the device.
+    const int* item_tile;
+    const int* item_part;
+    const int* item_slot;
+    const int* item_count;          // null: every CTA of the grid has an item
+    const int* part_blocks_dev;
     __nv_bfloat16* out;
     long out_stride;
     const int* block_table;
@@ -141,14 +166,39 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     prb_grid_launch_dependents();     // the next kernel may set itself up while this one runs
 
-    // the longest tiles (late query positions) first
-    const int n_items = p.tile_count != nullptr ? *p.tile_count : (int)gridDim.x;
-    if ((int)blockIdx.x >= n_items) {
-        prb_grid_wait();              // a kernel is complete only when those before it are
-        return;
+    const bool listed = p.item_tile != nullptr;
+    int item, chunk_z = (int)blockIdx.z, part_blocks = p.part_blocks, slot_base = 0;
+    bool whole = part_blocks <= 0;
+    if (listed) {
+        // the host's list: longest first, only items that have work.  The grid is (heads,
+        // items): CTAs are placed in the order of their linear index, heads fastest, so the
+        // longest items of all heads come first.
+        const int n_listed = p.item_count != nullptr ? *p.item_count : (int)gridDim.y;
+        const int li = (int)blockIdx.y;
+        if (li >= n_listed) {
+            prb_grid_wait();          // a kernel is complete only when those before it are
+            return;
+        }
+        item = p.item_tile[li];
+        chunk_z = p.item_part[li];
+        whole = chunk_z < 0;
+        part_blocks = whole ? 0 : *p.part_blocks_dev;
+        slot_base = whole ? 0 : p.item_slot[li] - chunk_z;
+        if (!whole && part_blocks <= 0) {
+            if (threadIdx.x == 0) prb_set_status(p.status, PRB_S_POSITION_RANGE, item, chunk_z, part_blocks);
+            prb_grid_wait();
+            return;
+        }
+    } else {
+        // the longest tiles (late query positions) first
+        const int n_items = p.tile_count != nullptr ? *p.tile_count : (int)gridDim.x;
+        if ((int)blockIdx.x >= n_items) {
+            prb_grid_wait();
+            return;
+        }
+        item = n_items - 1 - blockIdx.x;
     }
-    const int item = n_items - 1 - blockIdx.x;
-    const int h = blockIdx.y;
+    const int h = listed ? (int)blockIdx.x : (int)blockIdx.y;
     const int b = p.tile_req[item];
     const int row0 = p.tile_row0[item];
     const int rows = p.tile_rows[item];
@@ -164,25 +214,32 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int lo_all = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
     int blk_first = lo_all / KB, blk_last = pos_last / KB;
     int n_parts = 1;
-    if (p.part_blocks > 0) {
+    if (!whole) {
         // chunk (first chunk + z) of the tile's keys
-        const int chunk0 = blk_first / p.part_blocks;
-        n_parts = blk_last / p.part_blocks - chunk0 + 1;
-        if (n_parts > (int)gridDim.z || n_parts > MAX_PARTS) {
-            if (threadIdx.x == 0 && blockIdx.z == 0)
+        const int chunk0 = blk_first / part_blocks;
+        n_parts = blk_last / part_blocks - chunk0 + 1;
+        if ((!listed && n_parts > (int)gridDim.z) || n_parts > MAX_PARTS) {
+            if (threadIdx.x == 0 && chunk_z == 0)
                 prb_set_status(p.status, PRB_S_POSITION_RANGE, row0, pos_last, n_parts);
             prb_grid_wait();
             return;
         }
-        if ((int)blockIdx.z >= n_parts) {
+        if (chunk_z >= n_parts) {
             prb_grid_wait();
             return;
         }
-        const int lo = (chunk0 + (int)blockIdx.z) * p.part_blocks;
+        const int lo = (chunk0 + chunk_z) * part_blocks;
         if (lo > blk_first) blk_first = lo;
-        if (lo + p.part_blocks - 1 < blk_last) blk_last = lo + p.part_blocks - 1;
+        if (lo + part_blocks - 1 < blk_last) blk_last = lo + part_blocks - 1;
     }
     const int n_blocks = blk_last - blk_first + 1;
+#ifdef PRB_TRACE
+    if (threadIdx.x == 0) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        PF_CTA(0, pf_now()); PF_CTA(5, (unsigned long long)n_blocks); PF_CTA(6, (unsigned long long)smid);
+    }
+#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -346,6 +403,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
             if (warp == 2) PF_TRACE(j, 1);
+#ifdef PRB_TRACE
+            if (warp == 2 && lane == 0 && j == 0) PF_CTA(2, pf_now());
+#endif
             uint32_t sr[HC];
             if (ok) {
                 tcgen05_fence_after();
@@ -436,6 +496,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             if (lane == 0) mbar_arrive(smem_u32(p_full));
             if (warp == 2) PF_TRACE(j, 6);
         }
+#ifdef PRB_TRACE
+        if (warp == 2 && lane == 0) PF_CTA(3, pf_now());
+#endif
         // the row sum: both halves (every thread of the pair reaches this barrier)
         xmax[half * QT + r] = l_run;
         asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory");
@@ -472,8 +535,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             if (ok && row_ok) store_row(o_own, l_all > 0.0f ? 1.0f / l_all : 0.0f);
         } else {
             // this CTA's part: rows as [dim][row], so that a warp's 32 rows are one line
-            const size_t unit = (size_t)item * p.n_heads + h;
-            const size_t slot = unit * gridDim.z + blockIdx.z;
+            // listed items: the tile's chunks lie in consecutive slots from slot_base on;
+            // else (tile, head) units of gridDim.z slots each
+            const size_t unit = listed ? (size_t)slot_base * p.n_heads + h : (size_t)item * p.n_heads + h;
+            const size_t stride = listed ? (size_t)p.n_heads : 1;
+            const size_t slot = listed ? (size_t)(slot_base + chunk_z) * p.n_heads + h
+                                       : unit * gridDim.z + chunk_z;
             float* po = p.part_o + slot * (size_t)(DH * QT) + (size_t)(half * HD) * QT + r;
 #pragma unroll
             for (int i = 0; i < HD; ++i) __stcg(po + (size_t)i * QT, o_own[i]);
@@ -491,10 +558,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             asm volatile("bar.sync 5, 256;" ::: "memory");
             if (*is_last) {
                 __threadfence();
-                const size_t slot0 = unit * gridDim.z;
+                const size_t slot0 = listed ? unit : unit * gridDim.z;
                 float ms[MAX_PARTS], m_all = -INFINITY;
                 for (int s = 0; s < n_parts; ++s) {
-                    ms[s] = __ldcg(p.part_ml + (slot0 + s) * (size_t)(2 * QT) + 2 * r);
+                    ms[s] = __ldcg(p.part_ml + (slot0 + s * stride) * (size_t)(2 * QT) + 2 * r);
                     m_all = fmaxf(m_all, ms[s]);
                 }
                 float acc[HD], l_sum = 0.0f;
@@ -502,8 +569,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 for (int i = 0; i < HD; ++i) acc[i] = 0.0f;
                 for (int s = 0; s < n_parts; ++s) {          // in chunk order
                     const float wgt = ms[s] == -INFINITY ? 0.0f : fast_exp2(ms[s] - m_all);
-                    l_sum = fmaf(wgt, __ldcg(p.part_ml + (slot0 + s) * (size_t)(2 * QT) + 2 * r + 1), l_sum);
-                    const float* src = p.part_o + (slot0 + s) * (size_t)(DH * QT) + (size_t)(half * HD) * QT + r;
+                    l_sum = fmaf(wgt, __ldcg(p.part_ml + (slot0 + s * stride) * (size_t)(2 * QT) + 2 * r + 1), l_sum);
+                    const float* src = p.part_o + (slot0 + s * stride) * (size_t)(DH * QT) + (size_t)(half * HD) * QT + r;
 #pragma unroll
                     for (int i = 0; i < HD; ++i) acc[i] = fmaf(wgt, __ldcg(src + (size_t)i * QT), acc[i]);
                 }
@@ -511,6 +578,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             }
         }
         if (!ok && lane == 0) prb_set_status(p.status, PRB_S_WAIT_TIMEOUT, 13, blockIdx.x, warp);
+#ifdef PRB_TRACE
+        if (warp == 2 && lane == 0) PF_CTA(4, pf_now());
+#endif
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -544,9 +614,16 @@ PRB_API int prb_attention_prefill_tc(void* out, long out_stride, const void* q, 
                                      int n_heads, int kv_heads, int head_dim, int page_size,
                                      int max_pages, int num_pages, float scale, int window,
                                      int part_blocks, int max_parts, float* part_o,
-                                     float* part_ml, int* part_count, int* status,
-                                     cudaStream_t stream) {
+                                     float* part_ml, int* part_count, const int* item_tile,
+                                     const int* item_part, const int* item_slot,
+                                     const int* item_count, const int* part_blocks_dev,
+                                     int n_items, int* status, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
+    const bool listed = item_tile != nullptr;
+    if (listed && (n_items <= 0 || item_part == nullptr || item_slot == nullptr ||
+                   part_blocks_dev == nullptr || part_o == nullptr || part_ml == nullptr ||
+                   part_count == nullptr))
+        return PRB_E_ARG;
     if (part_blocks < 0 || (part_blocks > 0 && (max_parts < 1 || max_parts > MAX_PARTS ||
                                                 part_o == nullptr || part_ml == nullptr ||
                                                 part_count == nullptr)))
@@ -577,6 +654,8 @@ PRB_API int prb_attention_prefill_tc(void* out, long out_stride, const void* q, 
     }
     Params p;
     p.part_o = part_o; p.part_ml = part_ml; p.part_count = part_count; p.part_blocks = part_blocks;
+    p.item_tile = item_tile; p.item_part = item_part; p.item_slot = item_slot;
+    p.item_count = item_count; p.part_blocks_dev = part_blocks_dev;
     p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
     p.block_table = block_table; p.positions = positions;
     p.tile_req = tile_req; p.tile_row0 = tile_row0; p.tile_rows = tile_rows;
@@ -584,7 +663,9 @@ PRB_API int prb_attention_prefill_tc(void* out, long out_stride, const void* q, 
     p.n_heads = n_heads; p.kv_heads = kv_heads; p.page_size = page_size;
     p.max_pages = max_pages; p.num_pages = num_pages; p.scale = scale; p.window = window;
     p.status = status;
-    dim3 grid(n_tiles, n_heads, part_blocks > 0 ? max_parts : 1);
+    if (listed && n_items > 65535) return PRB_E_SIZE;
+    dim3 grid(listed ? n_heads : n_tiles, listed ? n_items : n_heads,
+              (!listed && part_blocks > 0) ? max_parts : 1);
     cudaError_t le = prb_launch_maybe_early(prb_small_ctas_early(), attention_prefill_tc_kernel, grid,
                                             dim3(THREADS), SMEM_BYTES, stream, map_q, map_k, map_v, p);
     if (le != cudaSuccess) return (int)le;

@@ -112,7 +112,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_attention_prefill_supports.argtypes = [I]
     h.prb_attention_prefill_tile.argtypes = []
     h.prb_attention_prefill_tc.argtypes = [P, L, P, L, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I,
-                                           I, F, I, I, I, P, P, P, P, P]
+                                           I, F, I, I, I, P, P, P, P, P, P, P, P, I, P, P]
     h.prb_attention_prefill_tc_supports.argtypes = [I, I]
     h.prb_attention_prefill_tc_tile.argtypes = []
     h.prb_attention_decode_split.argtypes = []
@@ -583,13 +583,19 @@ PREFILL_MAX_PARTS = 16
 
 def attention_prefill_tc(out, q, k_pages, v_pages, block_table, positions, tile_req, tile_row0,
                          tile_rows, tile_count, n_tiles, n_heads, scale, window, status,
-                         part_blocks: int = 0, max_parts: int = 1, parts=None) -> None:
+                         part_blocks: int = 0, max_parts: int = 1, parts=None, items=None) -> None:
     """bfloat16 causal attention of prompt portions on tcgen05 (head size 64, pages of a
     multiple of 64 positions): one CTA per work item of up to 128 queries and head, or, with
     ``part_blocks`` > 0, one per chunk of ``part_blocks`` * 64 keys of the item (at most
     ``max_parts`` chunks; ``parts`` = (float32 [n_tiles * n_heads * max_parts * 8192],
     float32 [n_tiles * n_heads * max_parts * 256], zeroed int32 [n_tiles * n_heads]) is the
-    workspace through which the chunks of an item are merged)."""
+    workspace through which the chunks of an item are merged).
+
+    ``items`` = (item_tile, item_part, item_slot, item_count or None, part_blocks (device
+    int32 [1]), n_items, n_slots): the CTAs' work as a list instead (item i is tile
+    ``item_tile[i]`` as a whole when ``item_part[i]`` < 0, else that chunk of it, whose
+    partial result goes to workspace slot ``item_slot[i]``; a tile's chunks have consecutive
+    slots); ``parts`` then holds ``n_slots * n_heads`` slots and counters."""
     what = "attention_prefill_tc"
     num_pages, kv_heads, page_size, head_dim = k_pages.shape
     for name, t in (("out", out), ("q", q)):
@@ -598,6 +604,24 @@ def attention_prefill_tc(out, q, k_pages, v_pages, block_table, positions, tile_
     if k_pages.dtype != torch.bfloat16 or not k_pages.is_contiguous() or not v_pages.is_contiguous():
         raise KernelArgumentError(f"{what}: the cache must be contiguous bfloat16")
     part_o = part_ml = part_count = None
+    item_tile = item_part = item_slot = item_count = part_dev = None
+    n_items = 0
+    if items is not None:
+        item_tile, item_part, item_slot, item_count, part_dev, n_items, n_slots = items
+        if part_blocks or parts is None:
+            raise KernelArgumentError(f"{what}: a work list brings its own chunk size and needs a workspace")
+        for name, t in (("item_tile", item_tile), ("item_part", item_part), ("item_slot", item_slot),
+                        ("part_blocks", part_dev)):
+            _need(t, torch.int32, name, what)
+        if min(item_tile.numel(), item_part.numel(), item_slot.numel()) < n_items:
+            raise KernelArgumentError(f"{what}: the work list is shorter than {n_items} items")
+        part_o, part_ml, part_count = parts
+        _need(part_o, torch.float32, "parts[0]", what)
+        _need(part_ml, torch.float32, "parts[1]", what)
+        _need(part_count, torch.int32, "parts[2]", what)
+        units = int(n_slots) * n_heads
+        if part_o.numel() < units * 8192 or part_ml.numel() < units * 256 or part_count.numel() < units:
+            raise KernelArgumentError(f"{what}: the workspace of the key parts is too small")
     if part_blocks:
         if parts is None or not 1 <= max_parts <= PREFILL_MAX_PARTS:
             raise KernelArgumentError(f"{what}: key parts need a workspace and 1 to "
@@ -615,7 +639,8 @@ def attention_prefill_tc(out, q, k_pages, v_pages, block_table, positions, tile_
         _p(block_table), _p(positions), _p(tile_req), _p(tile_row0), _p(tile_rows), _p(tile_count),
         n_tiles, n_heads, kv_heads, head_dim, page_size, block_table.shape[1], num_pages,
         float(scale), int(window or 0), int(part_blocks), int(max_parts), _p(part_o), _p(part_ml),
-        _p(part_count), _p(status), _stream()), what)
+        _p(part_count), _p(item_tile), _p(item_part), _p(item_slot), _p(item_count), _p(part_dev),
+        int(n_items), _p(status), _stream()), what)
 
 
 def attention_prefill(out, q, k_pages, v_pages, block_table, positions, tile_req, tile_row0,

@@ -44,9 +44,19 @@ class WorkPlanner:
         ``t_cap`` tokens and ``b_cap`` requests."""
         raise NotImplementedError
 
+    #: whether ``fill`` also wants the position of every request's first token of the step
+    wants_starts: bool = False
+    #: counter name -> (step, name of the array the counter counts): in a step that is
+    #: replayed from a CUDA graph the kernels of such a list are launched for the host's count
+    #: rounded up to a multiple of the step (the rounded count is part of the graph's key)
+    #: instead of for the array's capacity
+    launch_steps: Dict[str, Tuple[int, str]] = {}
+
     def fill(self, arrays: Dict[str, np.ndarray], lengths: Sequence[int]) -> Dict[str, int]:
         """Write the lists of a step whose requests bring ``lengths[b]`` tokens each (token
-        rows are concatenated in request order); returns the counters."""
+        rows are concatenated in request order); returns the counters.  A planner with
+        ``wants_starts`` is called as ``fill(arrays, lengths, starts)``: ``starts[b]`` is the
+        position of request b's first token of this step."""
         raise NotImplementedError
 
 
@@ -59,6 +69,8 @@ class WorkView:
     #: the counters as the host knows them; None while a step is replayed from a CUDA graph
     #: (kernels then take the capacity as their grid and the device-side counter as the bound)
     host_counts: Dict[str, Optional[int]]
+    #: for counters the planner lists in ``launch_steps``: the launch size of a replayed step
+    launch: Dict[str, int] = field(default_factory=dict)
 
 
 @dataclass
@@ -325,7 +337,8 @@ def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: L
         for name, (off, words, fill) in lay.work_arrays[planner.key].items():
             views[name] = host_np[off:off + words]
             views[name][:] = fill              # entries the planner leaves unused
-        got = planner.fill(views, lengths)
+        got = planner.fill(views, lengths, list(start_pos)) if planner.wants_starts \
+            else planner.fill(views, lengths)
         counts[planner.key] = {name: int(got[name]) for name in planner.counters}
         for name in planner.counters:
             host_np[at] = counts[planner.key][name]

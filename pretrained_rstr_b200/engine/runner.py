@@ -158,7 +158,15 @@ class ModelRunner:
         while reach < ctx.max_context:
             reach *= 2
         reach = min(reach, self.model.max_positions)
-        key = (lay.t_cap, lay.b_cap, rows_cap, filled, reach)
+        # lists whose kernels are launched for a rounded count rather than their capacity
+        bounds = []
+        for planner in self.planners:
+            view = ctx.work[planner.key]
+            for name, (step, array) in planner.launch_steps.items():
+                count = view.host_counts.get(name) or 0
+                view.launch[name] = min(view.caps[array], -(-count // step) * step)
+                bounds.append(view.launch[name])
+        key = (lay.t_cap, lay.b_cap, rows_cap, filled, reach, tuple(bounds))
         ctx.launch_tokens, ctx.launch_rows = lay.t_cap, rows_cap
         self._counts_from_device(ctx)
         ctx.max_context = reach

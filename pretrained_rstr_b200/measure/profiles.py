@@ -214,6 +214,22 @@ def profile_attention(spec: str) -> int:
                   torch.zeros(units, dtype=torch.int32, device="cuda"))
             cases.append((f"tcgen05_parts_of_{part}", ops.attention_prefill_tc,
                           {"part_blocks": part, "max_parts": most, "parts": ws}))
+    # the planner's work list: exactly the CTAs that have work, longest first, long tiles in parts
+    import numpy as np
+    from pretrained_rstr_b200.parts.attention import AttentionWork
+    planner = AttentionWork()
+    planner.note_mixer(nh, None, ops.sm_count())
+    host = {name: np.full(cap, fill, dtype=np.int32)
+            for name, (cap, fill) in planner.arrays(nseq * length, nseq).items()}
+    got = planner.fill(host, [length] * nseq, [0] * nseq)
+    dev = {name: torch.from_numpy(a).cuda() for name, a in host.items()}
+    n_slots = planner.slot_cap()
+    ws = (torch.empty(n_slots * nh * 8192, device="cuda"), torch.empty(n_slots * nh * 256, device="cuda"),
+          torch.zeros(n_slots * nh, dtype=torch.int32, device="cuda"))
+    cases.append((f"tcgen05_listed_{got['items']}_items_parts_of_{int(host['part_blocks'][0])}",
+                  ops.attention_prefill_tc,
+                  {"parts": ws, "items": (dev["item_tile"], dev["item_part"], dev["item_slot"], None,
+                                          dev["part_blocks"], got["items"], n_slots)}))
     flops = 4 * nseq * nh * dh * length * (length + 1) / 2
     res, ref = {}, None
     for name, fn, kw in cases:

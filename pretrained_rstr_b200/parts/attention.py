@@ -29,35 +29,117 @@ from .registry import register_part
 class AttentionWork(WorkPlanner):
     """How the attention kernels cut a step: portions of prompts go in tiles of up to
     ``TILE`` queries of one request to the prompt kernels; decoded tokens and portions of
-    up to ``SINGLE_MAX_Q`` tokens go token by token to the split-key decode kernel."""
+    up to ``SINGLE_MAX_Q`` tokens go token by token to the decode kernels.
+
+    For the tensor-memory prompt kernel the tiles are also listed as work ITEMS, longest
+    first: a tile as a whole, or, where that balances the step better, a tile's keys in parts
+    of ``part_blocks`` blocks of ``KEY_BLOCK`` absolute positions, a CTA each, merged by the
+    last to finish.  A tile's time goes with its number of key blocks (plus about four
+    blocks' worth of set-up), a late tile of a long prompt has many times an early one's, and
+    a launch lasts as long as its longest CTA: 2 x 1,024 tokens of GPT-2 small are 192 (tile,
+    head) CTAs of 2 to 16 blocks, 25 us a launch, where 360 CTAs of at most 6 blocks need 15.
+    The list holds exactly the CTAs that have work: CTAs that find nothing to do and leave
+    at once do not give their place on an SM to a waiting CTA until much later (measured)."""
 
     key = "causal_attention"
-    counters = ("tiles", "singles")
+    counters = ("tiles", "singles", "items")
+    wants_starts = True
+    # CTAs that find nothing to do keep a waiting CTA from its place on an SM for
+    # microseconds: a replayed step launches the items it has (rounded up), not the capacity
+    launch_steps = {"items": (8, "item_tile")}
     TILE = 128
     SINGLE_MAX_Q = 4
+    KEY_BLOCK = 64
+    MAX_PARTS = 8                       # most parts of one tile
+    MIN_PART = 4                        # blocks: a part costs about as much as four besides its own
+
+    def __init__(self):
+        self.heads = 1                  # most query heads of the mixers that use the lists
+        self.window: Optional[int] = None
+        self.sm_count = 148             # (set from the device when a mixer is built on one)
+
+    def note_mixer(self, heads: int, window: Optional[int], sm_count: Optional[int]) -> None:
+        """Called by every mixer that is built: the lists are balanced for the heads of the
+        model built last; parts are planned for one window (a mixer with another one, or
+        of a model built earlier with another one, has its chunks taken by grid index)."""
+        self.heads = int(heads)
+        self.window = window or None
+        if sm_count:
+            self.sm_count = int(sm_count)
+
+    def slot_cap(self) -> int:
+        """Most part slots (parts of split tiles) a step may use."""
+        return max(16, 4 * self.sm_count // self.heads)
 
     def arrays(self, t_cap: int, b_cap: int):
         tile_cap = t_cap // self.TILE + b_cap
+        item_cap = tile_cap + self.slot_cap()
         return {"tile_req": (tile_cap, -1), "tile_row0": (tile_cap, 0), "tile_rows": (tile_cap, 0),
-                "single_tokens": (min(t_cap, b_cap * self.SINGLE_MAX_Q), 0)}
+                "single_tokens": (min(t_cap, b_cap * self.SINGLE_MAX_Q), 0),
+                "item_tile": (item_cap, 0), "item_part": (item_cap, -1), "item_slot": (item_cap, 0),
+                "part_blocks": (1, 0)}
 
-    def fill(self, arrays: Dict[str, np.ndarray], lengths: Sequence[int]) -> Dict[str, int]:
+    def fill(self, arrays: Dict[str, np.ndarray], lengths: Sequence[int],
+             starts: Optional[Sequence[int]] = None) -> Dict[str, int]:
         treq, trow, tnum = arrays["tile_req"], arrays["tile_row0"], arrays["tile_rows"]
         sing = arrays["single_tokens"]
         n_tiles = n_sing = 0
         t = 0
+        spans = []                      # (first key block, last key block) of every tile
         for b, n in enumerate(lengths):
             if n <= self.SINGLE_MAX_Q:
                 sing[n_sing:n_sing + n] = np.arange(t, t + n, dtype=np.int32)
                 n_sing += n
             else:
                 for r0 in range(0, n, self.TILE):
+                    rows = min(self.TILE, n - r0)
                     treq[n_tiles] = b
                     trow[n_tiles] = t + r0
-                    tnum[n_tiles] = min(self.TILE, n - r0)
+                    tnum[n_tiles] = rows
+                    pos0 = (starts[b] if starts is not None else 0) + r0
+                    lo = max(0, pos0 - self.window + 1) if self.window else 0
+                    spans.append((lo // self.KEY_BLOCK, (pos0 + rows - 1) // self.KEY_BLOCK))
                     n_tiles += 1
             t += n
-        return {"tiles": n_tiles, "singles": n_sing}
+        n_items = self._items(arrays, spans) if spans and "item_tile" in arrays else 0
+        return {"tiles": n_tiles, "singles": n_sing, "items": n_items}
+
+    def _split(self, spans, blocks, part):
+        """The items for parts of ``part`` blocks: (blocks of the item, tile, part or -1, slot)."""
+        items, slots = [], 0
+        for tile in sorted(range(len(spans)), key=lambda i: -blocks[i]):
+            first, last = spans[tile]
+            n_parts = last // part - first // part + 1
+            if blocks[tile] < part + 2 or n_parts < 2 or slots + n_parts > self.slot_cap():
+                items.append((blocks[tile], tile, -1, 0))
+                continue
+            for z in range(n_parts):
+                lo = max(first, (first // part + z) * part)
+                hi = min(last, (first // part + z) * part + part - 1)
+                items.append((hi - lo + 1, tile, z, slots + z))
+            slots += n_parts
+        return items
+
+    def _items(self, arrays, spans) -> int:
+        """The tiles as work items, longest first, the long ones in parts: the smallest parts
+        (of at least ``MIN_PART`` blocks) with which all CTAs still run at once, two to an SM
+        (every part costs its CTA a set-up and a merge, so a second round of short CTAs is
+        dearer than a first round of longer ones)."""
+        itile, ipart, islot = arrays["item_tile"], arrays["item_part"], arrays["item_slot"]
+        blocks = [last - first + 1 for first, last in spans]
+        longest = max(blocks, default=0)
+        part = max(self.MIN_PART, -(-longest // self.MAX_PARTS))
+        items = self._split(spans, blocks, part)
+        while part < longest and (len(items) * self.heads > 2 * self.sm_count or len(items) > len(itile)):
+            part += 1
+            items = self._split(spans, blocks, part)
+        if len(items) > len(itile):
+            items = [(blocks[i], i, -1, 0) for i in range(len(spans))]
+        items.sort(key=lambda it: -it[0])
+        for i, (_n, tile, z, slot) in enumerate(items):
+            itile[i], ipart[i], islot[i] = tile, z, slot
+        arrays["part_blocks"][0] = part
+        return len(items)
 
 
 ATTENTION_WORK = AttentionWork()
@@ -83,6 +165,7 @@ class CausalAttention(Mixer):
         self.scale, self.window = float(scale), window
         self.runtime = runtime
         self.position = position
+        ATTENTION_WORK.note_mixer(n_head, window, ops.sm_count() if torch.cuda.is_available() else None)
 
     def kv_spec(self) -> KVSpec:
         return KVSpec(self.n_kv_head, self.head_dim, self.window)
@@ -165,19 +248,36 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
     if tiles is None or tiles > 0:
         n_tiles = work.caps["tile_req"] if tiles is None else tiles
         if SETTINGS.attention_tcgen05 and ops.prefill_tc_supports(head_dim, group.page_size):
-            # (a step that runs as a graph is planned with its capacities: the most tiles and
-            # the longest context it may have)
-            parts = None
-            part_blocks, max_parts = prefill_key_parts(n_tiles * n_head, ctx.max_context, window)
-            if part_blocks:
-                units = 1 << max(6, (n_tiles * n_head - 1).bit_length())
-                parts = (ctx.scratch("attn_part_o", (units * max_parts * 8192,), torch.float32),
-                         ctx.scratch("attn_part_ml", (units * max_parts * 256,), torch.float32),
-                         ctx.scratch_zero("attn_part_count", (units,), torch.int32))
-            ops.attention_prefill_tc(out, q, cache.k, cache.v, group.block_table, ctx.positions,
-                                     tile_req, tile_row0, tile_rows, work.counts["tiles"],
-                                     n_tiles, n_head, scale, window, ctx.status,
-                                     part_blocks=part_blocks, max_parts=max_parts, parts=parts)
+            if SETTINGS.prefill_part < 0 and "item_tile" in work.arrays and \
+                    ATTENTION_WORK.window == window:
+                # the planner's list: exactly the CTAs that have work, longest first, long
+                # tiles in parts (a step that runs as a graph is planned with its capacities)
+                items = work.host_counts["items"]
+                n_items = work.launch.get("items", work.caps["item_tile"]) if items is None else items
+                n_slots = ATTENTION_WORK.slot_cap()
+                parts = (ctx.scratch("attn_part_o", (n_slots * n_head * 8192,), torch.float32),
+                         ctx.scratch("attn_part_ml", (n_slots * n_head * 256,), torch.float32),
+                         ctx.scratch_zero("attn_part_count", (n_slots * n_head,), torch.int32))
+                ops.attention_prefill_tc(out, q, cache.k, cache.v, group.block_table, ctx.positions,
+                                         tile_req, tile_row0, tile_rows, work.counts["tiles"],
+                                         n_tiles, n_head, scale, window, ctx.status, parts=parts,
+                                         items=(work.arrays["item_tile"], work.arrays["item_part"],
+                                                work.arrays["item_slot"], work.counts["items"],
+                                                work.arrays["part_blocks"], n_items, n_slots))
+            else:
+                # (a forced chunk size, or a mixer whose heads or window the planner did not
+                # plan for: chunks by grid index)
+                parts = None
+                part_blocks, max_parts = prefill_key_parts(n_tiles * n_head, ctx.max_context, window)
+                if part_blocks:
+                    units = 1 << max(6, (n_tiles * n_head - 1).bit_length())
+                    parts = (ctx.scratch("attn_part_o2", (units * max_parts * 8192,), torch.float32),
+                             ctx.scratch("attn_part_ml2", (units * max_parts * 256,), torch.float32),
+                             ctx.scratch_zero("attn_part_count2", (units,), torch.int32))
+                ops.attention_prefill_tc(out, q, cache.k, cache.v, group.block_table, ctx.positions,
+                                         tile_req, tile_row0, tile_rows, work.counts["tiles"],
+                                         n_tiles, n_head, scale, window, ctx.status,
+                                         part_blocks=part_blocks, max_parts=max_parts, parts=parts)
         else:
             ops.attention_prefill(out, q, cache.k, cache.v, group.block_table, ctx.positions,
                                   tile_req, tile_row0, tile_rows, work.counts["tiles"],

@@ -452,6 +452,33 @@ def test_attention_prefill(nh, nkv, dh, ps, window, tile):
             kernels.append((f"tcgen05 / parts of {part}", ops.attention_prefill_tc,
                             {"part_blocks": part, "max_parts": most,
                              "parts": _prefill_parts(len(tiles) * nh, most)}))
+        if tile == 128:
+            # the planner's own list (exactly the CTAs with work, longest first, long tiles in
+            # parts): with the balance it chooses, and with small parts forced by telling it
+            # of a device with few SMs
+            import numpy as np
+            from pretrained_rstr_b200.parts.attention import AttentionWork
+            for small in (False, True):
+                planner = AttentionWork()
+                if small:
+                    planner.MIN_PART = 1
+                planner.note_mixer(nh, window, 10_000 if small else None)
+                host = {name: np.full(cap, fill, dtype=np.int32)
+                        for name, (cap, fill) in planner.arrays(sum(portions), len(portions)).items()}
+                got = planner.fill(host, portions, [n - p for n, p in zip(lengths, portions)])
+                assert got["tiles"] == len(tiles)
+                assert host["tile_row0"][:len(tiles)].tolist() == [x[1] for x in tiles]
+                dev = {name: torch.from_numpy(a).cuda() for name, a in host.items()}
+                slots = planner.slot_cap()
+                ws = (torch.full((slots * nh * 8192,), float("nan"), device="cuda"),
+                      torch.full((slots * nh * 256,), float("nan"), device="cuda"),
+                      torch.zeros(slots * nh, dtype=torch.int32, device="cuda"))
+                split = int((host["item_part"][:got["items"]] >= 0).sum())
+                assert not small or split > 0
+                kernels.append((f"tcgen05 / listed, {got['items']} items, {split} of them parts",
+                                ops.attention_prefill_tc,
+                                {"parts": ws, "items": (dev["item_tile"], dev["item_part"], dev["item_slot"],
+                                                        None, dev["part_blocks"], got["items"], slots)}))
     else:
         assert not (dh == 64 and ps % 64 == 0)
     # what a page's earlier owner may have left after a request's last position must not
