@@ -105,6 +105,7 @@ struct Scatter {
     void* v_pages;
     const int* slots;
     int q_width, kv_width, head_dim, page_size, num_pages;
+    int only_cache;                 // key and value columns go to the cache alone, not to the output
 };
 
 // Where `count` consecutive output columns starting at `col` (inside one head) of the token
@@ -397,6 +398,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
             }
         };
+        // where in a page array the rows this lane stores on the way back begin (element
+        // offset of head 0, dimension 0 of the token's slot; -1: no slot), worked out once
+        // per tile, for the next tile while this one's last chunk is on its way out
+        long slot_at[(!F32) ? 8 : 1];
+        auto find_slots = [&](int first_row) {
+            if constexpr (!F32) {
+                if (sc.kv_width != 0) {
+                    const int kv_heads = sc.kv_width / sc.head_dim;
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = first_row + it * 4 + rd_row;
+                        const int slot = rr < m ? sc.slots[rr] : -1;
+                        slot_at[it] = -1;
+                        if (slot >= 0) {
+                            const int page = slot / sc.page_size, off = slot - page * sc.page_size;
+                            if (page >= sc.num_pages)
+                                prb_set_status(status, PRB_S_SLOT_RANGE, rr, slot, sc.num_pages);
+                            else
+                                slot_at[it] = ((long)page * kv_heads * sc.page_size + off) * sc.head_dim;
+                        }
+                    }
+                }
+            }
+        };
         int local = 0;
         bool ok = true;
         // the accumulator is handed back on the barrier the MMA thread waits on: this CTA's,
@@ -411,8 +436,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             else mbar_arrive(tempty_addr[acc]);
         };
         auto tile_m0 = [&](int t) { return (t % m_tiles) * TM + rank * BM; };
-        if (walker < total_tiles && half * CH < BN)
+        if (walker < total_tiles && half * CH < BN) {
             prefetch(tile_m0(walker) + quarter * 32, (walker / m_tiles) * BN + half * CH);
+            find_slots(tile_m0(walker) + quarter * 32);
+        }
         for (int tile = walker; tile < total_tiles && ok; tile += walkers, ++local) {
             const int m0 = tile_m0(tile), n0 = (tile / m_tiles) * BN;
             const int acc = local & 1;
@@ -431,28 +458,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     prefetch(tile_m0(nt) + quarter * 32, (nt / m_tiles) * BN + half * CH);
                 continue;
             }
-            // where in a page array the rows this lane stores on the way back begin (element
-            // offset of head 0, dimension 0 of the token's slot; -1: no slot), worked out once
-            // per tile
-            long slot_at[(!F32) ? 8 : 1];
-            if constexpr (!F32) {
-                if (sc.kv_width != 0) {
-                    const int kv_heads = sc.kv_width / sc.head_dim;
-#pragma unroll
-                    for (int it = 0; it < 8; ++it) {
-                        const int rr = row0 + it * 4 + rd_row;
-                        const int slot = rr < m ? sc.slots[rr] : -1;
-                        slot_at[it] = -1;
-                        if (slot >= 0) {
-                            const int page = slot / sc.page_size, off = slot - page * sc.page_size;
-                            if (page >= sc.num_pages)
-                                prb_set_status(status, PRB_S_SLOT_RANGE, rr, slot, sc.num_pages);
-                            else
-                                slot_at[it] = ((long)page * kv_heads * sc.page_size + off) * sc.head_dim;
-                        }
-                    }
-                }
-            }
+            // (the cache rows of this tile were looked up before the accumulator was waited for)
 #pragma unroll 1
             for (int c0 = half * CH; c0 < BN; c0 += 2 * CH) {
                 if (n0 + c0 >= n) break;                    // uniform across the warp
@@ -524,7 +530,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                                     v2 + r_now[it].z, v3 + r_now[it].w);
                                 } else {
                                     const uint2 u = make_uint2(pack2(v0, v1), pack2(v2, v3));
-                                    *reinterpret_cast<uint2*>(c + off) = u;
+                                    if (pages == nullptr || !sc.only_cache)
+                                        *reinterpret_cast<uint2*>(c + off) = u;
                                     if (pages != nullptr && slot_at[it] >= 0)
                                         *reinterpret_cast<uint2*>(pages + slot_at[it] + head_at) = u;
                                 }
@@ -559,6 +566,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         prefetch(tile_m0(nt) + quarter * 32, (nt / m_tiles) * BN + half * CH);
                 }
             }
+            if (nt < total_tiles) find_slots(tile_m0(nt) + quarter * 32);
             if (warp == 2 && local == 0) GT(5);
         }
         if (warp == 2) GT(6);
@@ -1032,13 +1040,14 @@ PRB_API int prb_gemm_bf16_scatter(void* c, const void* a, const void* w, const f
                                   int n, int k, long lda, long ldw, long ldc, int act,
                                   int out_dtype, void* k_pages, void* v_pages, const int* slots,
                                   int q_width, int kv_width, int head_dim, int page_size,
-                                  int num_pages, int* status, cudaStream_t stream) {
+                                  int num_pages, int only_cache, int* status, cudaStream_t stream) {
     if (head_dim <= 0 || head_dim % 8 != 0 || kv_width <= 0 || kv_width % head_dim != 0 ||
         page_size <= 0 || q_width < 0 || q_width % 8 != 0 || q_width + 2 * kv_width != n ||
         k_pages == nullptr || v_pages == nullptr || slots == nullptr)
         return PRB_E_ARG;
     if (((uintptr_t)k_pages) % 16 != 0 || ((uintptr_t)v_pages) % 16 != 0) return PRB_E_ALIGN;
-    Scatter sc = {k_pages, v_pages, slots, q_width, kv_width, head_dim, page_size, num_pages};
+    Scatter sc = {k_pages, v_pages, slots, q_width, kv_width, head_dim, page_size, num_pages,
+                  only_cache ? 1 : 0};
     return gemm_bf16_entry(c, a, w, bias, nullptr, m, n, k, lda, ldw, ldc, act, out_dtype, 0,
                            status, sc, stream);
 }

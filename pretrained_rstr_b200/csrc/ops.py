@@ -83,7 +83,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_gemm_f32.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, P]
     h.prb_gemm_bf16.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, I, P, P]
     h.prb_gemm_bf16_scatter.argtypes = [P, P, P, P, I, I, I, L, L, L, I, I, P, P, P, I, I, I, I, I,
-                                        P, P]
+                                        I, P, P]
     h.prb_gemm_midm.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, P, P]
     h.prb_gemm_midm_supports.argtypes = [I, I, I]
     h.prb_gemm_smallm.argtypes = [P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
@@ -306,8 +306,9 @@ def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, statu
     """out[M,N] = act(a[M,K] . w[N,K]^T + bias) (+ resid) on the tcgen05 tensor cores:
     bfloat16 operands, float32 accumulation in tensor memory, epilogue in float32; out is
     bfloat16 or float32.  K and the row pitches of a and w must be multiples of 8.
-    ``kv_scatter`` = (k_pages, v_pages, slots, q_width): the key and value columns of a fused
-    QKV product also go to the paged cache (of the output's element type).  ``tile_n`` and
+    ``kv_scatter`` = (k_pages, v_pages, slots, q_width[, only_cache]): the key and value
+    columns of a fused QKV product also go to the paged cache (of the output's element type);
+    with ``only_cache`` they need not reach ``out`` at all.  ``tile_n`` and
     ``split_k`` force a tile width and, for widths 64 and 128, a cluster of 2, 4 or 8 CTAs
     that share a tile's reduction; ``pair`` (widths 64, 128, 192, 256) forces pairs of CTAs on
     256-row tiles (``tcgen05.mma.cta_group::2``); left at 0 the kernel chooses."""
@@ -328,7 +329,8 @@ def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, statu
         if resid.shape != out.shape or resid.stride(0) != out.stride(0):
             raise KernelArgumentError(f"{what}: resid must have the output's shape and stride")
     if kv_scatter is not None:
-        k_pages, v_pages, slots, q_width = kv_scatter
+        k_pages, v_pages, slots, q_width = kv_scatter[:4]
+        only_cache = bool(kv_scatter[4]) if len(kv_scatter) > 4 else False
         if resid is not None or tile_n or split_k or pair:
             raise KernelArgumentError(f"{what}: a product that scatters takes no residual or tile width")
         if k_pages.dtype != out.dtype or v_pages.dtype != out.dtype or not k_pages.is_contiguous() \
@@ -339,7 +341,8 @@ def gemm_bf16(out, a, w, bias=None, resid=None, act=None, tile_n: int = 0, statu
         _check(lib().prb_gemm_bf16_scatter(
             _p(out), _p(a), _p(w), _p(bias), m, n, k, a.stride(0), w.stride(0), out.stride(0),
             ACT_CODES[act], dtype_code(out.dtype), _p(k_pages), _p(v_pages), _p(slots), int(q_width),
-            kv_heads * head_dim, head_dim, page_size, num_pages, _p(status), _stream()), what)
+            kv_heads * head_dim, head_dim, page_size, num_pages, int(only_cache), _p(status),
+            _stream()), what)
         return
     _check(lib().prb_gemm_bf16(_p(out), _p(a), _p(w), _p(bias), _p(resid), m, n, k, a.stride(0),
                                w.stride(0), out.stride(0), ACT_CODES[act], dtype_code(out.dtype),
@@ -416,7 +419,7 @@ def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0,
             raise KernelArgumentError(f"{what}: resid must be float32 with the output's shape and stride")
     kv = (None, None, None, 0, 0, 0, 0, 0)
     if kv_scatter is not None:
-        k_pages, v_pages, slots, q_width = kv_scatter
+        k_pages, v_pages, slots, q_width = kv_scatter[:4]
         num_pages, kv_heads, page_size, head_dim = k_pages.shape
         if k_pages.dtype != out.dtype or v_pages.dtype != out.dtype or slots.dtype != torch.int32 \
                 or q_width + 2 * kv_heads * head_dim != n:

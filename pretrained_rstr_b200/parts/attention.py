@@ -182,7 +182,10 @@ class CausalAttention(Mixer):
         # keys and values to their cache slots itself.
         rotates = self.position is not None and \
             type(self.position).rotate is not PositionEncoding.rotate
-        scatter = (cache.k, cache.v, group.slots, self.q_width) \
+        # (a step without single tokens reads keys and values from the cache alone: the product
+        # need not store those columns beside the queries as well)
+        singles = ctx.work[ATTENTION_WORK.key].host_counts.get("singles")
+        scatter = (cache.k, cache.v, group.slots, self.q_width, singles == 0) \
             if cache.writes and not rotates else None
         appended = self.qkv.forward(ctx, h, qkv, kv_scatter=scatter)
         q = qkv[:, :self.q_width]

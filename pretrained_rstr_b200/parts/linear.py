@@ -55,7 +55,7 @@ class Linear:
         alias it) or the activation type.  ``a`` is a tensor, or a :class:`LazyNorm`: a
         norm that has not run yet, which the decode-time kernel computes in its prologue
         and every other kernel asks to run first.  ``kv_scatter`` = (k_pages, v_pages, slots,
-        q_width) offers the kernel the chance to write the key and value columns of a fused
+        q_width[, only_cache]) offers the kernel the chance to write the key and value columns of a fused
         QKV product straight to the cache; returns True when it did."""
         m = out.shape[0]
         if self.runtime.dtype == torch.float32:

@@ -807,6 +807,14 @@ def test_gemm_bf16_scatters_keys_and_values_to_the_cache(m, heads, kv_heads, dh,
     assert torch.equal(out1, out2) and torch.equal(k1, k2) and torch.equal(v1, v2)
     assert status.tolist() == [0, 0, 0, 0]
     assert int((k1 != 0).any(dim=-1).sum()) == (m - 1) * kv_heads
+    # keys and values to the cache alone: the same cache, the query columns as before; what
+    # lies in the output's key and value columns afterwards does not matter
+    k3, v3 = torch.zeros_like(k1), torch.zeros_like(k1)
+    out3 = torch.full_like(out1, 7.0)
+    ops.gemm_bf16(out3, a, w, bias=bias, kv_scatter=(k3, v3, slots, q_width, True), status=status)
+    torch.cuda.synchronize()
+    assert torch.equal(k3, k1) and torch.equal(v3, v1)
+    assert torch.equal(out3[:, :q_width], out1[:, :q_width])
 
 
 @pytest.mark.parametrize("m,n,k", [(64, 768, 768), (17, 768, 3072), (40, 1600, 6400), (33, 4800, 1600),
