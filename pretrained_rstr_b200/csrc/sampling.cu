@@ -183,11 +183,10 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
         for_each_logit(row, vocab, [&](int, float v) { best = max(best, sample_key(v)); });
         // (made distinct by the thread's number, so that exactly one entry has each rank)
         cand[threadIdx.x] = ((unsigned long long)best << 32) | (unsigned)(blockDim.x - 1 - threadIdx.x);
-        __syncthreads();
-        const unsigned long long mine = cand[threadIdx.x];
-        int before = 0;
-        for (int j = 0; j < (int)blockDim.x; ++j) before += cand[j] > mine ? 1 : 0;
-        if (before == k - 1) pick_sh[6] = (int)best;
+        // (ordered by a bitonic sort, 55 exchanges a thread: counting every maximum's rank
+        // against all the others was 1,024 compares a thread and half the kernel's time)
+        sort_descending((int)blockDim.x);
+        if (threadIdx.x == 0) pick_sh[6] = (int)(cand[k - 1] >> 32);
         __syncthreads();
     }
     const unsigned bound = (unsigned)pick_sh[6];
@@ -308,8 +307,10 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
         n_cand = k;
     }
     // ---- order the candidates
+    // (few candidates: by counting ranks, no barriers; many: a bitonic sort, whose work grows
+    // with n log^2 n instead of n^2)
     unsigned long long* sorted = cand + CAND_CAP / 2;               // second half of the buffer
-    if (n_cand <= CAND_CAP / 2) {
+    if (n_cand <= 256) {
         rank_sort(n_cand, sorted);
     } else {
         sort_descending(n_cand);
@@ -324,19 +325,35 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
             e[j] = exp((double)sample_value((unsigned)(sorted[j] >> 32)) / t - mx);
     }
     __syncthreads();
+    // The sums are the reference's, term by term in its order (one thread); what does not
+    // depend on the order is done by all: the quotients e / sum.  The sum of the first `cut`
+    // terms and the running sum of the draw are partial sums of the same series, so they are
+    // kept from the first loop instead of being added up again.
+    double* part = reinterpret_cast<double*>(work);      // [k] partial sums (the candidates' keys are
+    __shared__ double psum_sh;                           //      not needed any more: ids are kept below)
+    __shared__ int ids_sh[MAX_TOP_K];
+    for (int j = threadIdx.x; j < k; j += blockDim.x)
+        ids_sh[j] = 0x7fffffff - (int)(unsigned)(sorted[j] & 0xffffffffULL);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double acc0 = 0.0;
+        for (int j = 0; j < k; ++j) { acc0 += e[j]; part[j] = acc0; }
+        psum_sh = acc0;
+    }
+    __syncthreads();
+    const double psum = psum_sh;
+    for (int j = threadIdx.x; j < k; j += blockDim.x) e[j] = e[j] / psum;
+    __syncthreads();
     if (threadIdx.x != 0) return;
 
     const double p = (double)top_p[r];
-    double psum = 0.0;
-    for (int j = 0; j < k; ++j) psum += e[j];
     int cut = k;
     double c = 0.0;
     for (int j = 0; j < k; ++j) {
-        c += e[j] / psum;
+        c += e[j];
         if (c >= p) { cut = j + 1; break; }
     }
-    double tot = 0.0;
-    for (int j = 0; j < cut; ++j) tot += e[j];
+    const double tot = part[cut - 1];
 
     unsigned long long* state = rng_states + slots[r];
     unsigned long long s = *state;
@@ -345,11 +362,9 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
     *state = s;
     const double u = (double)((hi << 27) + lo) * (1.0 / 9007199254740992.0);
     const double draw = u * tot;
-    double acc = 0.0;
-    int pick = 0x7fffffff - (int)(unsigned)(sorted[cut - 1] & 0xffffffffULL);
+    int pick = ids_sh[cut - 1];
     for (int j = 0; j < cut; ++j) {
-        acc += e[j];
-        if (acc >= draw || j == cut - 1) { pick = 0x7fffffff - (int)(unsigned)(sorted[j] & 0xffffffffULL); break; }
+        if (part[j] >= draw || j == cut - 1) { pick = ids_sh[j]; break; }
     }
     out[r] = pick;
 }
