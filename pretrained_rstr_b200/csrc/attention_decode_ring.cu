@@ -111,15 +111,20 @@ PRB_API int prb_attention_decode_ring_supports(int head_dim, int page_size) {
 PRB_API int prb_attention_decode_ring_max_list() { return MAX_LIST; }
 
 // Whether this kernel is the faster one for a launch of n_list tokens over contexts of up to
-// max_context keys.  It is where its warps have long runs to stream (more than three units
-// each) and where everything fits the buffers that are filled before the dependency resolves
-// (at most one unit each).  Between the two, where a warp's third unit has to be requested
-// after the first was read, the split-key kernel of attention_decode.cu measured faster inside
-// a step (GPT-2 small, 8 requests of 1,000 tokens: 0.431 ms a step against 0.457).
+// max_context keys; the split-key kernel of attention_decode.cu is the other.  Measured inside
+// GPT-2 small's decode step (12 heads; ms a step, ring / split-key): 1 request 0.364 / 0.372
+// at context 256 and 0.366 / 0.366 at 1,000; 8 requests 0.377 / 0.372 and 0.442 / 0.427; 16
+// requests 0.496 / 0.485 (512) and 0.572 / 0.560 (1,024); 32 requests 0.673 / 0.689 and 0.806 /
+// 0.892; 48 requests 0.746 / 0.704 and 0.928 / 0.894; 64 requests 0.726 / 0.690 (256) and 1.029 /
+// 1.140 (1,000).  The ring wins where many (token, head) pairs have long contexts (its warps
+// stream long runs, the other kernel's CTAs walk a thousand keys one batch after the other)
+// and at a single request with a short context (everything it reads is requested before the
+// dependency resolves and one CTA holds a whole pair).
 PRB_API int prb_attention_decode_ring_prefers(int n_list, int n_heads, int max_context) {
-    const long units = (long)n_list * n_heads * (max_context / UNIT + 1);
-    const long warps = (long)prb_sm_count() * RING_WARPS;
-    return units <= warps || units > 3 * warps;
+    const long pairs = (long)n_list * n_heads;
+    const long sms = prb_sm_count();
+    if (pairs >= 2 * sms) return max_context > 512;
+    return pairs * 8 <= sms && max_context <= 512;
 }
 
 // Floats of workspace a launch of up to n_list tokens needs.

@@ -197,6 +197,24 @@ def set_pdl(on: bool) -> None:
     lib().prb_set_pdl(1 if on else 0)
 
 
+class plain_launch:
+    """``with plain_launch(cond):`` kernels launched inside start only when their predecessor
+    has ended (no programmatic dependent launch), if ``cond``; the setting outside is kept."""
+
+    def __init__(self, cond: bool = True):
+        self.cond = bool(cond) and _PDL
+
+    def __enter__(self):
+        if self.cond:
+            lib().prb_set_pdl(0)
+        return self
+
+    def __exit__(self, *exc):
+        if self.cond:
+            lib().prb_set_pdl(1)
+        return False
+
+
 # ------------------------------------------------------------------------ kernels
 def embed(out, tokens, positions, wte, wpe, status) -> None:
     """out[t,:] = wte[tokens[t],:] (+ wpe[positions[t],:]); out float32 [T, width]."""
