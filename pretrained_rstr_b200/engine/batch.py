@@ -52,6 +52,10 @@ class WorkPlanner:
     #: instead of for the array's capacity
     launch_steps: Dict[str, Tuple[int, str]] = {}
 
+    def absorb(self, other: "WorkPlanner") -> None:
+        """Several parts of a model may bring a planner of the same key (one per layer): the
+        model keeps the first and lets it absorb the others (what they were told to plan for)."""
+
     def fill(self, arrays: Dict[str, np.ndarray], lengths: Sequence[int]) -> Dict[str, int]:
         """Write the lists of a step whose requests bring ``lengths[b]`` tokens each (token
         rows are concatenated in request order); returns the counters.  A planner with
@@ -71,6 +75,8 @@ class WorkView:
     host_counts: Dict[str, Optional[int]]
     #: for counters the planner lists in ``launch_steps``: the launch size of a replayed step
     launch: Dict[str, int] = field(default_factory=dict)
+    #: the planner that filled the lists (what it planned for: a part may ask it)
+    planner: Optional["WorkPlanner"] = None
 
 
 @dataclass
@@ -222,8 +228,10 @@ class StepContext:
         (self.tokens, self.positions, self.seq_of_token, self.logit_rows, self.q_start,
          self.kv_len, self.state_slot, self.fresh, self.counts) = views
         # the parts' own work lists; the host-side counters are filled in by the runner
+        by_key = {planner.key: planner for planner in layout.planners}
         self.work: Dict[str, WorkView] = {
-            key: WorkView(arrays, counts, caps, {name: None for name in counts})
+            key: WorkView(arrays, counts, caps, {name: None for name in counts},
+                          planner=by_key.get(key))
             for key, (arrays, counts, caps) in layout.work_views(device_buf).items()}
         self.feedback = False               # token ids below zero name tokens chosen last
 

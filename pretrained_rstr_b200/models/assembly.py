@@ -48,8 +48,11 @@ class Model:
         self.planners = []
         for part in parts:
             for planner in getattr(part, "work_planners", lambda: [])():
-                if all(planner.key != have.key for have in self.planners):
+                kept = [have for have in self.planners if have.key == planner.key]
+                if not kept:
                     self.planners.append(planner)
+                elif kept[0] is not planner:
+                    kept[0].absorb(planner)
 
     # ---------------------------------------------------------------- cache layout
     def _derive_cache_layout(self) -> None:

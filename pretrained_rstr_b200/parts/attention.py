@@ -59,13 +59,19 @@ class AttentionWork(WorkPlanner):
         self.sm_count = 148             # (set from the device when a mixer is built on one)
 
     def note_mixer(self, heads: int, window: Optional[int], sm_count: Optional[int]) -> None:
-        """Called by every mixer that is built: the lists are balanced for the heads of the
-        model built last; parts are planned for one window (a mixer with another one, or
-        of a model built earlier with another one, has its chunks taken by grid index)."""
+        """What a mixer that uses the lists needs them planned for."""
         self.heads = int(heads)
         self.window = window or None
         if sm_count:
             self.sm_count = int(sm_count)
+
+    def absorb(self, other: "AttentionWork") -> None:
+        """The mixers of a model share one planner: the lists are balanced for the most heads
+        any of them has, and parts are planned for one window (the first mixer's; a mixer with
+        another window has its tiles' chunks taken by grid index instead)."""
+        self.heads = max(self.heads, other.heads)
+        if other.sm_count != 148:
+            self.sm_count = other.sm_count
 
     def slot_cap(self) -> int:
         """Most part slots (parts of split tiles) a step may use."""
@@ -142,9 +148,6 @@ class AttentionWork(WorkPlanner):
         return len(items)
 
 
-ATTENTION_WORK = AttentionWork()
-
-
 class CausalAttention(Mixer):
     graph_safe = True
     accepts_lazy_norm = True      # the first matrix product may compute the norm itself
@@ -165,13 +168,14 @@ class CausalAttention(Mixer):
         self.scale, self.window = float(scale), window
         self.runtime = runtime
         self.position = position
-        ATTENTION_WORK.note_mixer(n_head, window, ops.sm_count() if torch.cuda.is_available() else None)
+        self.work_plan = AttentionWork()
+        self.work_plan.note_mixer(n_head, window, ops.sm_count() if torch.cuda.is_available() else None)
 
     def kv_spec(self) -> KVSpec:
         return KVSpec(self.n_kv_head, self.head_dim, self.window)
 
     def work_planners(self):
-        return [ATTENTION_WORK]
+        return [self.work_plan]
 
     def forward(self, ctx, h, x, cache: LayerCache) -> None:
         t = x.shape[0]
@@ -184,7 +188,7 @@ class CausalAttention(Mixer):
             type(self.position).rotate is not PositionEncoding.rotate
         # (a step without single tokens reads keys and values from the cache alone: the product
         # need not store those columns beside the queries as well)
-        singles = ctx.work[ATTENTION_WORK.key].host_counts.get("singles")
+        singles = ctx.work[AttentionWork.key].host_counts.get("singles")
         scatter = (cache.k, cache.v, group.slots, self.q_width, singles == 0) \
             if cache.writes and not rotates else None
         appended = self.qkv.forward(ctx, h, qkv, kv_scatter=scatter)
@@ -251,19 +255,20 @@ def attend(ctx, out, q, cache: LayerCache, group, n_head: int, scale: float,
         ops.attention_generic(out, q, cache.k, cache.v, group.block_table, ctx.seq_of_token,
                               ctx.positions, t, n_head, scale, window, ctx.max_context, ctx.status)
         return
-    work = ctx.work[ATTENTION_WORK.key]
+    work = ctx.work[AttentionWork.key]
+    planner = work.planner
     tiles, singles = work.host_counts["tiles"], work.host_counts["singles"]
     tile_req, tile_row0, tile_rows = (work.arrays[n] for n in ("tile_req", "tile_row0", "tile_rows"))
     if tiles is None or tiles > 0:
         n_tiles = work.caps["tile_req"] if tiles is None else tiles
         if SETTINGS.attention_tcgen05 and ops.prefill_tc_supports(head_dim, group.page_size):
-            if SETTINGS.prefill_part < 0 and "item_tile" in work.arrays and \
-                    ATTENTION_WORK.window == window:
+            if SETTINGS.prefill_part < 0 and "item_tile" in work.arrays and planner is not None \
+                    and planner.window == (window or None):
                 # the planner's list: exactly the CTAs that have work, longest first, long
                 # tiles in parts (a step that runs as a graph is planned with its capacities)
                 items = work.host_counts["items"]
                 n_items = work.launch.get("items", work.caps["item_tile"]) if items is None else items
-                n_slots = ATTENTION_WORK.slot_cap()
+                n_slots = planner.slot_cap()
                 parts = (ctx.scratch("attn_part_o", (n_slots * n_head * 8192,), torch.float32),
                          ctx.scratch("attn_part_ml", (n_slots * n_head * 256,), torch.float32),
                          ctx.scratch_zero("attn_part_count", (n_slots * n_head,), torch.int32))
