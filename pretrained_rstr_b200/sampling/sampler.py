@@ -63,12 +63,20 @@ class Sampler:
         self.max_top_k = ops.max_top_k()
 
         def option_buffers():
-            def pair(dtype):
-                return (torch.zeros(rows, dtype=dtype, pin_memory=True),
-                        torch.zeros(rows, dtype=dtype, device=device))
-            return {"temperature": pair(torch.float32), "top_p": pair(torch.float32),
-                    "top_k": pair(torch.int32), "fresh": pair(torch.int32),
-                    "slots": pair(torch.int32), "seeds": pair(torch.int64)}
+            # one pinned buffer and one device buffer hold all six arrays, so that a step's
+            # options go to the device in ONE copy; numpy views for the host side (writing
+            # tensor elements one by one costs a microsecond each)
+            words = rows * (2 + 5)                       # seeds are 8 bytes, the rest 4
+            host = torch.zeros(words, dtype=torch.int32, pin_memory=True)
+            dev = torch.zeros(words, dtype=torch.int32, device=device)
+            names = ("temperature", "top_p", "top_k", "fresh", "slots")
+            dtypes = (torch.float32, torch.float32, torch.int32, torch.int32, torch.int32)
+            views = {"seeds": (host[:2 * rows].view(torch.int64).numpy(),
+                               dev[:2 * rows].view(torch.int64))}
+            for j, (name, dtype) in enumerate(zip(names, dtypes)):
+                lo = (2 + j) * rows
+                views[name] = (host[lo:lo + rows].view(dtype).numpy(), dev[lo:lo + rows].view(dtype))
+            return host, dev, views
         self._sets = [option_buffers(), option_buffers()]
         self._turn = 0
 
@@ -84,7 +92,7 @@ class Sampler:
             ops.sample(out, logits, n)
             return
         self._turn ^= 1
-        p = self._sets[self._turn]
+        host, dev, p = self._sets[self._turn]
         for i, r in enumerate(requests):
             sp = r.sampling
             p["temperature"][0][i] = 0.0 if sp.greedy else float(sp.temperature)
@@ -100,8 +108,7 @@ class Sampler:
             else:
                 seed = int(sp.seed)
             p["seeds"][0][i] = seed
-        for host, dev in p.values():
-            dev[:n].copy_(host[:n], non_blocking=True)
+        dev.copy_(host, non_blocking=True)
         ops.sample(out, logits, n, temperature=p["temperature"][1], top_k=p["top_k"][1],
                    top_p=p["top_p"][1], seeds=p["seeds"][1], fresh=p["fresh"][1],
                    slots=p["slots"][1], rng_states=self.rng_states)
