@@ -60,7 +60,9 @@ class WorkPlanner:
         """Write the lists of a step whose requests bring ``lengths[b]`` tokens each (token
         rows are concatenated in request order); returns the counters.  A planner with
         ``wants_starts`` is called as ``fill(arrays, lengths, starts)``: ``starts[b]`` is the
-        position of request b's first token of this step."""
+        position of request b's first token of this step.  Under the key "_used" it may name
+        the arrays this step needs on the device (the others hold nothing its kernels read,
+        as its counters say); arrays that are often unused belong last in ``arrays()``."""
         raise NotImplementedError
 
 
@@ -131,15 +133,18 @@ class BatchLayout:
         self.slots = [take(t_cap) for _ in range(n_groups)]
         self.first_pos = [take(b_cap) for _ in range(n_groups)]
         self.block_table = [take(b_cap * max_pages) for _ in range(n_groups)]
-        # work lists of the parts that asked for some (see WorkPlanner): arrays, and counters
-        # that live on the device too
+        # work lists of the parts that asked for some (see WorkPlanner): counters that live on
+        # the device too, then the arrays.  The arrays come last, in the planners' own order,
+        # so that a step which leaves the last ones unused need not copy them to the device
+        # (fill_host_buffer says how many words a step uses): a copy of up to a kilobyte,
+        # which a small decode step fits, measured 7 microseconds faster than a larger one.
+        n_counters = sum(len(p.counters) for p in self.planners)
+        self.counts = take(2 + n_counters)    # [tokens, requests, planners' counters ...]
         self.work_arrays: Dict[str, Dict[str, Tuple[int, int, int]]] = {}   # key -> name -> (offset, words, fill)
         for planner in self.planners:
             self.work_arrays[planner.key] = {
                 name: (take(words), words, fill)
                 for name, (words, fill) in planner.arrays(t_cap, b_cap).items()}
-        n_counters = sum(len(p.counters) for p in self.planners)
-        self.counts = take(2 + n_counters)    # [tokens, requests, planners' counters ...]
         self.work_counts: Dict[str, Dict[str, int]] = {}
         at = self.counts + 2
         for planner in self.planners:
@@ -234,6 +239,7 @@ class StepContext:
                           planner=by_key.get(key))
             for key, (arrays, counts, caps) in layout.work_views(device_buf).items()}
         self.feedback = False               # token ids below zero name tokens chosen last
+        self.used_words: Optional[int] = None      # words of the step's buffer that go to the device
 
     @property
     def dtype(self) -> torch.dtype:
@@ -287,7 +293,8 @@ def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: L
                      group_slots: List[List[List[int]]], group_tables: List[List[List[int]]],
                      group_first: List[List[int]], logit_rows: List[int]) -> Dict[str, Dict[str, int]]:
     """Write one step into the pinned host buffer.  Returns the counters of the parts' work
-    lists, by planner key and counter name."""
+    lists, by planner key and counter name, and under "_words" how many words of the buffer
+    the step uses (what lies beyond need not be copied to the device)."""
     lay = layout
     n_req = len(entries_tokens)
     t = 0
@@ -339,6 +346,8 @@ def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: L
     # the parts' work lists
     lengths = [len(toks) for toks in entries_tokens]
     counts: Dict[str, Dict[str, int]] = {}
+    n_counters = sum(len(p.counters) for p in lay.planners)
+    used_words = lay.counts + (2 + n_counters + 3) // 4 * 4       # everything up to the counters
     at = lay.counts + 2
     for planner in lay.planners:
         views = {}
@@ -348,8 +357,13 @@ def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: L
         got = planner.fill(views, lengths, list(start_pos)) if planner.wants_starts \
             else planner.fill(views, lengths)
         counts[planner.key] = {name: int(got[name]) for name in planner.counters}
+        # (arrays the planner did not write hold nothing a kernel reads: its counters say so)
+        for name in got.get("_used", views.keys()):
+            off, words, _fill = lay.work_arrays[planner.key][name]
+            used_words = max(used_words, off + words)
         for name in planner.counters:
             host_np[at] = counts[planner.key][name]
             at += 1
     host_np[lay.counts:lay.counts + 2] = (n_tok, n_req)
+    counts["_words"] = used_words
     return counts

@@ -298,6 +298,7 @@ class ModelRunner:
                           groups, self.status, self.scratch, max_context, max_q,
                           launch_tokens=total, launch_rows=len(logit_rows),
                           max_positions=self.model.max_positions)
+        ctx.used_words = work_counts.pop("_words", None)
         for key, counts in work_counts.items():
             ctx.work[key].host_counts = dict(counts)
         ctx.staging, ctx.staging_turn = staging, turn
@@ -310,9 +311,10 @@ class ModelRunner:
         layout = ctx.layout
         if self.start_event is not None:             # measurement: device work of the step begins
             self.start_event.record()
-        self._dev[:layout.size].copy_(ctx.staging[:layout.size], non_blocking=True)
+        words = ctx.used_words or layout.size
+        self._dev[:words].copy_(ctx.staging[:words], non_blocking=True)
         self._host_events[ctx.staging_turn].record()
-        self.last_h2d_bytes = layout.size * 4
+        self.last_h2d_bytes = words * 4
         for g in range(self.n_groups):
             pairs = [(src, dst) for (gg, src, dst) in ctx.copies if gg == g]
             for i in range(0, len(pairs), self._pairs_host.shape[0]):

@@ -80,10 +80,12 @@ class AttentionWork(WorkPlanner):
     def arrays(self, t_cap: int, b_cap: int):
         tile_cap = t_cap // self.TILE + b_cap
         item_cap = tile_cap + self.slot_cap()
-        return {"tile_req": (tile_cap, -1), "tile_row0": (tile_cap, 0), "tile_rows": (tile_cap, 0),
-                "single_tokens": (min(t_cap, b_cap * self.SINGLE_MAX_Q), 0),
-                "item_tile": (item_cap, 0), "item_part": (item_cap, -1), "item_slot": (item_cap, 0),
-                "part_blocks": (1, 0)}
+        # (the single tokens first: a decode step uses nothing of what follows, and what a
+        # step does not use is not copied to the device)
+        return {"single_tokens": (min(t_cap, b_cap * self.SINGLE_MAX_Q), 0),
+                "tile_req": (tile_cap, -1), "tile_row0": (tile_cap, 0), "tile_rows": (tile_cap, 0),
+                "part_blocks": (1, 0),
+                "item_tile": (item_cap, 0), "item_part": (item_cap, -1), "item_slot": (item_cap, 0)}
 
     def fill(self, arrays: Dict[str, np.ndarray], lengths: Sequence[int],
              starts: Optional[Sequence[int]] = None) -> Dict[str, int]:
@@ -108,7 +110,10 @@ class AttentionWork(WorkPlanner):
                     n_tiles += 1
             t += n
         n_items = self._items(arrays, spans) if spans and "item_tile" in arrays else 0
-        return {"tiles": n_tiles, "singles": n_sing, "items": n_items}
+        used = (["single_tokens"] if n_sing else []) + \
+            (["tile_req", "tile_row0", "tile_rows", "part_blocks", "item_tile", "item_part", "item_slot"]
+             if n_tiles else [])
+        return {"tiles": n_tiles, "singles": n_sing, "items": n_items, "_used": used}
 
     def _split(self, spans, blocks, part):
         """The items for parts of ``part`` blocks: (blocks of the item, tile, part or -1, slot)."""

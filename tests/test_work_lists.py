@@ -91,7 +91,7 @@ def test_attention_items_balance_a_long_prompt_step():
     planner = AttentionWork()
     planner.note_mixer(12, None, 148)
     arrays, got = _fill(planner, [1024, 1024], [0, 0], t_cap=2048, b_cap=8)
-    assert got == {"tiles": 16, "singles": 0, "items": 24}
+    assert {k: got[k] for k in planner.counters} == {"tiles": 16, "singles": 0, "items": 24}
     assert int(arrays["part_blocks"][0]) == 8
     assert got["items"] * 12 <= 2 * 148
     # with 25 heads the tiles alone are more than a round: nothing is split
@@ -104,8 +104,9 @@ def test_a_decode_step_plans_no_items():
     planner = AttentionWork()
     planner.note_mixer(12, None, 148)
     arrays, got = _fill(planner, [1] * 8, [900 + i for i in range(8)])
-    assert got == {"tiles": 0, "singles": 8, "items": 0}
+    assert {k: got[k] for k in planner.counters} == {"tiles": 0, "singles": 8, "items": 0}
     assert arrays["single_tokens"][:8].tolist() == list(range(8))
+    assert got["_used"] == ["single_tokens"]            # nothing else need go to the device
 
 
 class _Lists(WorkPlanner):
@@ -146,3 +147,9 @@ def test_layout_gives_planners_room_and_counters():
     assert host[off:off + 4].tolist() == [0, 2, 3, -1]
     assert counts["causal_attention"]["singles"] == 2 + 1 + 4 and counts["causal_attention"]["tiles"] == 1
     assert host[lay.work_counts["even"]["evens"]] == 3
+    # the words a step copies to the device end behind the last array it uses: here the
+    # other planner's list (it names no arrays, so all of them count)
+    assert counts["_words"] == off + 8
+    decode = fill_host_buffer(host, lay, [[1], [2], [3]], [7, 8, 9], [0, 1, 2], [False] * 3,
+                              [[[0], [1], [2]]], [[[0] * 16 for _ in range(3)]], [[0, 0, 0]], [0, 1, 2])
+    assert decode["_words"] == off + 8
