@@ -34,6 +34,8 @@ from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 
 class CacheError(RuntimeError):
     pass
@@ -128,6 +130,34 @@ class SlotAllocator:
         heapq.heappush(self._free, slot)
 
 
+class _Table(list):
+    """A block table (pages by logical index, -1 for a page given back) that keeps its
+    device form up to date: ``row``, the same pages padded with -1 to the longest table a
+    request can have.  A step copies rows; it does not rebuild them."""
+
+    __slots__ = ("row",)
+
+    def __init__(self, row: np.ndarray, pages: Sequence[int] = ()):
+        super().__init__(pages)
+        self.row = row
+        row[:] = -1
+        if len(self):
+            row[:len(self)] = self
+
+    def append(self, page: int) -> None:
+        self.row[len(self)] = page
+        super().append(page)
+
+    def pop(self) -> int:                  # the last page only
+        page = super().pop()
+        self.row[len(self)] = -1
+        return page
+
+    def __setitem__(self, index: int, page: int) -> None:
+        super().__setitem__(index, page)
+        self.row[index] = page
+
+
 @dataclass
 class _Pending:
     count: int
@@ -190,6 +220,9 @@ class CacheManager:
         self.max_positions = max_positions
         self.max_pages_per_request = -(-max_positions // page_size)
         self.requests: Dict[Hashable, _Request] = {}
+        # the block tables in their device form, by group: one row per state slot
+        self.table_rows = [np.full((num_slots, self.max_pages_per_request), -1, dtype=np.int32)
+                           for _ in self.groups]
         # Sharing full prompt pages needs every group to keep all its pages, and a model
         # without fixed-size state per request: a request that takes over shared pages skips
         # their tokens, so a part that keeps a state would never see them
@@ -253,7 +286,7 @@ class CacheManager:
             raise CacheError("no free state slot")
         slot = self.slots.allocate()
         self.requests[rid] = _Request(rid=rid, slot=slot,
-                                      tables=[[] for _ in self.groups],
+                                      tables=[_Table(rows[slot]) for rows in self.table_rows],
                                       promise=reserved)
         return slot
 
@@ -266,6 +299,8 @@ class CacheManager:
             for page in table:
                 if page >= 0:
                     self._release(gi, page)
+        for rows in self.table_rows:
+            rows[req.slot] = -1
         self.slots.release(req.slot)
         del self.requests[rid]
 
@@ -297,7 +332,7 @@ class CacheManager:
         req.fresh = False if length > 0 else True
         n_pages = -(-length // self.page_size)
         for gi in range(len(self.groups)):
-            req.tables[gi] = list(src.tables[gi][:n_pages])
+            req.tables[gi] = _Table(self.table_rows[gi][slot], src.tables[gi][:n_pages])
             for page in req.tables[gi]:
                 if page >= 0:
                     self.allocators[gi].retain(page)
@@ -468,6 +503,11 @@ class CacheManager:
     def length(self, rid: Hashable) -> int:
         return self._get(rid).length
 
+    def peek(self, rid: Hashable) -> _Request:
+        """The request's record, to read ``slot``, ``length`` and ``fresh`` from in one
+        look-up; not to be changed by the caller."""
+        return self._get(rid)
+
     def slot(self, rid: Hashable) -> int:
         return self._get(rid).slot
 
@@ -515,6 +555,18 @@ class CacheManager:
                 raise CacheError("a held page is in the free set")
             if len(free) + sum(1 for c in alloc.refcount if c) != alloc.num_pages:
                 raise CacheError("a page is lost")
+            rows = self.table_rows[gi]
+            held_slots = set()
+            for req in self.requests.values():
+                held_slots.add(req.slot)
+                table = req.tables[gi]
+                if rows[req.slot, :len(table)].tolist() != list(table) or \
+                        bool((rows[req.slot, len(table):] != -1).any()):
+                    raise CacheError(f"request {req.rid!r}: the device form of its block table "
+                                     f"differs from the table")
+            for slot in range(rows.shape[0]):
+                if slot not in held_slots and bool((rows[slot] != -1).any()):
+                    raise CacheError(f"state slot {slot} is free and its block table row is not empty")
 
     # ----------------------------------------------------------------- internals
     def _get(self, rid: Hashable) -> _Request:

@@ -80,6 +80,10 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_kv_append.argtypes = [P, P, P, P, L, P, I, I, I, I, I, I, P, P]
     h.prb_copy_pages.argtypes = [P, P, I, L, I, I, P, P]
     h.prb_resolve_tokens.argtypes = [P, I, P, I, P, P]
+    h.prb_host_device_address.argtypes = [P]
+    h.prb_host_device_address.restype = c_void_p
+    h.prb_fetch_step.argtypes = [P, P, I, I, I, P, I, P, P]
+    h.prb_publish_result.argtypes = [P, P, I, P]
     h.prb_gemm_f32.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, P]
     h.prb_gemm_bf16.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, I, P, P]
     h.prb_gemm_bf16_scatter.argtypes = [P, P, P, P, I, I, I, L, L, L, I, I, P, P, P, I, I, I, I, I,
@@ -126,7 +130,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_set_pdl.restype = None
     h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
     h.prb_sample_max_top_k.argtypes = []
-    for name in ("prb_resolve_tokens", "prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
+    for name in ("prb_resolve_tokens", "prb_fetch_step", "prb_publish_result", "prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
                  "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_bf16_scatter", "prb_gemm_midm",
                  "prb_gemm_midm_supports", "prb_gemm_smallm", "prb_gemm_smallm_max_rows",
                  "prb_gemm_smallm_max_norm_width", "prb_attention_generic", "prb_attention_decode",
@@ -690,6 +694,40 @@ def resolve_tokens(tokens, n, prev, status) -> None:
     _need(prev, torch.int32, "prev", what)
     _check(lib().prb_resolve_tokens(_p(tokens), int(n), _p(prev), prev.numel(), _p(status),
                                     _stream()), what)
+
+
+def host_device_address(host: torch.Tensor) -> int:
+    """The address under which kernels reach this pinned host tensor, or 0 if they cannot
+    (the caller then copies with the copy engine)."""
+    if host.is_cuda or not host.is_pinned():
+        return 0
+    return int(lib().prb_host_device_address(host.data_ptr()) or 0)
+
+
+def fetch_step(dev, host_address: int, words: int, tokens_at: int = 0, n_tokens: int = 0,
+               prev=None, status=None) -> None:
+    """dev[:words] = the int32 words at ``host_address`` (from :func:`host_device_address`),
+    read by a kernel; with ``prev``, token ids below zero among words
+    [tokens_at, tokens_at + n_tokens) become prev[-id - 1] on the way."""
+    what = "fetch_step"
+    _need(dev, torch.int32, "dev", what)
+    if not host_address or words > dev.numel():
+        raise KernelArgumentError(f"{what}: no host address, or {words} words do not fit")
+    if prev is not None:
+        _need(prev, torch.int32, "prev", what)
+    _check(lib().prb_fetch_step(_p(dev), host_address, int(words), int(tokens_at), int(n_tokens),
+                                _p(prev), 0 if prev is None else prev.numel(), _p(status),
+                                _stream()), what)
+
+
+def publish_result(host_address: int, dev, words: int) -> None:
+    """The int32 words dev[:words] written to pinned host memory at ``host_address`` by a
+    kernel; the host sees them once an event recorded after this call has completed."""
+    what = "publish_result"
+    _need(dev, torch.int32, "dev", what)
+    if not host_address or words > dev.numel():
+        raise KernelArgumentError(f"{what}: no host address, or {words} words do not fit")
+    _check(lib().prb_publish_result(host_address, _p(dev), int(words), _stream()), what)
 
 
 def max_top_k() -> int:

@@ -288,13 +288,25 @@ class ScratchPool:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
 
 
+_IOTA = np.arange(64, dtype=np.int32)
+
+
+def _iota(n: int) -> np.ndarray:
+    global _IOTA
+    if n > len(_IOTA):
+        _IOTA = np.arange(max(n, 2 * len(_IOTA)), dtype=np.int32)
+    return _IOTA[:n]
+
+
 def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: List[List[int]],
                      start_pos: List[int], state_slots: List[int], fresh: List[bool],
-                     group_slots: List[List[List[int]]], group_tables: List[List[List[int]]],
+                     group_slots: List[List[List[int]]], group_tables: List,
                      group_first: List[List[int]], logit_rows: List[int]) -> Dict[str, Dict[str, int]]:
-    """Write one step into the pinned host buffer.  Returns the counters of the parts' work
-    lists, by planner key and counter name, and under "_words" how many words of the buffer
-    the step uses (what lies beyond need not be copied to the device)."""
+    """Write one step into the pinned host buffer (``group_tables[g]``: the block tables of
+    the requests, as lists of pages or as an array of rows padded with -1).  Returns the
+    counters of the parts' work lists, by planner key and counter name, and under "_words"
+    how many words of the buffer the step uses (what lies beyond need not be copied to the
+    device)."""
     lay = layout
     n_req = len(entries_tokens)
     t = 0
@@ -306,17 +318,29 @@ def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: L
     kv = host_np[lay.kv_len:lay.kv_len + lay.b_cap]
     ss = host_np[lay.state_slot:lay.state_slot + lay.b_cap]
     fr = host_np[lay.fresh:lay.fresh + lay.b_cap]
-    for b, toks in enumerate(entries_tokens):
-        n = len(toks)
-        tok[t:t + n] = toks
-        pos[t:t + n] = np.arange(start_pos[b], start_pos[b] + n, dtype=np.int32)
-        seq[t:t + n] = b
-        qs[b] = t
-        kv[b] = start_pos[b] + n
-        ss[b] = state_slots[b]
-        fr[b] = 1 if fresh[b] else 0
-        t += n
-    n_tok = t
+    if all(len(toks) == 1 for toks in entries_tokens):
+        # every request brings one token (a decode step): whole arrays at once
+        n_tok = n_req
+        iota = _iota(n_req)
+        tok[:n_req] = [toks[0] for toks in entries_tokens]
+        pos[:n_req] = start_pos
+        seq[:n_req] = iota
+        qs[:n_req] = iota
+        np.add(pos[:n_req], 1, out=kv[:n_req])
+        ss[:n_req] = state_slots
+        fr[:n_req] = fresh
+    else:
+        for b, toks in enumerate(entries_tokens):
+            n = len(toks)
+            tok[t:t + n] = toks
+            pos[t:t + n] = np.arange(start_pos[b], start_pos[b] + n, dtype=np.int32)
+            seq[t:t + n] = b
+            qs[b] = t
+            kv[b] = start_pos[b] + n
+            ss[b] = state_slots[b]
+            fr[b] = 1 if fresh[b] else 0
+            t += n
+        n_tok = t
     tok[n_tok:] = 0
     pos[n_tok:] = 0
     seq[n_tok:] = -1
@@ -328,21 +352,30 @@ def fill_host_buffer(host_np: np.ndarray, layout: BatchLayout, entries_tokens: L
     rows[len(logit_rows):] = 0
     for g in range(lay.n_groups):
         sl = host_np[lay.slots[g]:lay.slots[g] + lay.t_cap]
-        t = 0
-        for b in range(n_req):
-            n = len(group_slots[g][b])
-            sl[t:t + n] = group_slots[g][b]
-            t += n
+        if n_tok == n_req:
+            sl[:n_req] = [s[0] for s in group_slots[g]]
+        else:
+            t = 0
+            for b in range(n_req):
+                n = len(group_slots[g][b])
+                sl[t:t + n] = group_slots[g][b]
+                t += n
         sl[n_tok:] = -1
         fp = host_np[lay.first_pos[g]:lay.first_pos[g] + lay.b_cap]
         fp[:n_req] = group_first[g]
         fp[n_req:] = 0
-        bt = host_np[lay.block_table[g]:lay.block_table[g] + lay.b_cap * lay.max_pages]
-        bt[:] = -1
-        bt2 = bt.reshape(lay.b_cap, lay.max_pages)
-        for b in range(n_req):
-            table = group_tables[g][b]
-            bt2[b, :len(table)] = table
+        bt2 = host_np[lay.block_table[g]:lay.block_table[g] + lay.b_cap * lay.max_pages] \
+            .reshape(lay.b_cap, lay.max_pages)
+        tables = group_tables[g]
+        if isinstance(tables, np.ndarray):          # rows in their device form already
+            bt2[:n_req, :tables.shape[1]] = tables
+            bt2[:n_req, tables.shape[1]:] = -1
+            bt2[n_req:] = -1
+        else:
+            bt2[:] = -1
+            for b in range(n_req):
+                table = tables[b]
+                bt2[b, :len(table)] = table
     # the parts' work lists
     lengths = [len(toks) for toks in entries_tokens]
     counts: Dict[str, Dict[str, int]] = {}

@@ -18,12 +18,19 @@ import torch
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage
 from ..csrc import ops
+from ..settings import SETTINGS
 from .batch import (BatchLayout, Entry, GroupView, HostBatch, Runtime, ScratchPool, StepContext,
                     fill_host_buffer)
 
 
 class StepError(RuntimeError):
     pass
+
+
+# A step whose description is at most this long is read from the pinned buffer by a kernel;
+# a longer one (a large portion of a prompt) goes through the copy engine, whose bandwidth
+# then counts for more than the hand-over it costs.
+FETCH_BY_KERNEL_WORDS = 4096
 
 
 def _bucket(n: int, floor: int, cap: int) -> int:
@@ -69,6 +76,14 @@ class ModelRunner:
                               torch.zeros_like(self.result_host).pin_memory()]
         self._result_events = [torch.cuda.Event(), torch.cuda.Event()]
         self._result_turn = 0
+        # Small steps cross the bus inside kernels that read and write the pinned buffers
+        # directly (no hand-over between copy engine and kernels on the stream); 0 where
+        # kernels cannot reach a buffer, and then the copy engine moves it.
+        by_kernel = SETTINGS.step_words_by_kernel
+        self._host_addresses = [ops.host_device_address(h) if by_kernel else 0
+                                for h in self._hosts]
+        self._result_addresses = [ops.host_device_address(h) if by_kernel else 0
+                                  for h in self._result_hosts]
         self.tokens_out = self.result[:runtime.max_requests]
         self.status = self.result[runtime.max_requests:]
         self._status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
@@ -113,8 +128,6 @@ class ModelRunner:
                 exc, self.fail_next_step = self.fail_next_step, None
                 raise exc
             self.upload(ctx)
-            if ctx.feedback:
-                ops.resolve_tokens(ctx.tokens, ctx.n_tokens, self.tokens_out, self.status)
             logits = self._run(ctx)
         except Exception:
             self.abort(entries)
@@ -215,21 +228,29 @@ class ModelRunner:
             raise StepError(f"{total} tokens in one step; the runtime takes "
                             f"{self.runtime.max_batched_tokens}")
         vocab = self.model.vocab
+        lowest = -self.runtime.max_requests if feedback else 0
         for e in entries:
-            if len(e.tokens) == 0:
+            n = len(e.tokens)
+            if n == 0:
                 raise StepError(f"request {e.rid!r}: no tokens in this step")
             for w in e.want:
-                if not 0 <= w < len(e.tokens):
+                if not 0 <= w < n:
                     raise StepError(f"request {e.rid!r}: wanted place {w} outside its "
-                                    f"{len(e.tokens)} tokens")
-            toks = np.asarray(e.tokens)
-            lowest = -self.runtime.max_requests if feedback else 0
-            if toks.dtype.kind not in "iu" or int(toks.min()) < lowest or int(toks.max()) >= vocab:
+                                    f"{n} tokens")
+            if n == 1:
+                t = e.tokens[0]
+                fine = isinstance(t, (int, np.integer)) and lowest <= t < vocab
+            else:
+                toks = np.asarray(e.tokens)
+                fine = toks.dtype.kind in "iu" and int(toks.min()) >= lowest and \
+                    int(toks.max()) < vocab
+            if not fine:
                 bad = [t for t in e.tokens if not (isinstance(t, (int, np.integer)) and 0 <= t < vocab)]
                 raise StepError(f"request {e.rid!r}: token id {bad[0] if bad else '?'} outside the "
                                 f"vocabulary of {vocab}")
-            if self.cache.length(e.rid) + len(e.tokens) > self.model.max_positions:
-                raise StepError(f"request {e.rid!r}: {self.cache.length(e.rid)}+{len(e.tokens)} "
+            held = self.cache.length(e.rid)
+            if held + n > self.model.max_positions:
+                raise StepError(f"request {e.rid!r}: {held}+{n} "
                                 f"tokens exceed the model's {self.model.max_positions} positions")
         reserved: List[Hashable] = []
         try:
@@ -254,18 +275,22 @@ class ModelRunner:
         total = sum(len(e.tokens) for e in entries)
         layout = self.layout_for(total, n_req)
         start_pos = [r.start for r in reservations]
-        state_slots = [self.cache.slot(e.rid) for e in entries]
-        fresh = [self.cache.is_fresh(e.rid) for e in entries]
+        records = [self.cache.peek(e.rid) for e in entries]
+        state_slots = [r.slot for r in records]
+        fresh = [r.fresh for r in records]
         group_slots = [[r.slots[g] for r in reservations] for g in range(self.n_groups)]
-        group_tables = [[self.cache.block_table(e.rid, g) for e in entries]
-                        for g in range(self.n_groups)]
-        group_first = [[self.cache.first_visible(e.rid, g) for e in entries]
-                       for g in range(self.n_groups)]
+        # block tables: the manager keeps them in their device form, one row per state slot
+        group_tables = [rows[state_slots] for rows in self.cache.table_rows]
+        group_first = [[0] * n_req if spec.window is None else
+                       [self.cache.first_visible(e.rid, g) for e in entries]
+                       for g, spec in enumerate(self.cache.groups)]
         logit_rows: List[int] = []
         q_start = [0]
         for e in entries:
-            logit_rows.extend(q_start[-1] + w for w in e.want)
-            q_start.append(q_start[-1] + len(e.tokens))
+            at = q_start[-1]
+            for w in e.want:
+                logit_rows.append(at + w)
+            q_start.append(at + len(e.tokens))
         turn = self._host_turn
         self._host_turn ^= 1
         self._host_events[turn].synchronize()        # the copy that last used this buffer is done
@@ -306,13 +331,22 @@ class ModelRunner:
         return ctx
 
     def upload(self, ctx: StepContext) -> None:
-        """The step's arrays go to the device in one copy; copy-on-write page copies come
-        before anything reads or writes the new pages."""
+        """The step's arrays go to the device in one piece (a kernel that reads the pinned
+        buffer for a small step, one copy for a large one), token ids that name places among
+        the tokens chosen last are put in, and copy-on-write page copies come before anything
+        reads or writes the new pages."""
         layout = ctx.layout
         if self.start_event is not None:             # measurement: device work of the step begins
             self.start_event.record()
         words = ctx.used_words or layout.size
-        self._dev[:words].copy_(ctx.staging[:words], non_blocking=True)
+        address = self._host_addresses[ctx.staging_turn]
+        if address and words <= FETCH_BY_KERNEL_WORDS:
+            ops.fetch_step(self._dev, address, words, layout.tokens, ctx.n_tokens,
+                           self.tokens_out if ctx.feedback else None, self.status)
+        else:
+            self._dev[:words].copy_(ctx.staging[:words], non_blocking=True)
+            if ctx.feedback:
+                ops.resolve_tokens(ctx.tokens, ctx.n_tokens, self.tokens_out, self.status)
         self._host_events[ctx.staging_turn].record()
         self.last_h2d_bytes = words * 4
         for g in range(self.n_groups):
@@ -348,7 +382,10 @@ class ModelRunner:
         afterwards does not delay the ticket."""
         turn = self._result_turn
         self._result_turn ^= 1
-        self._result_hosts[turn].copy_(self.result, non_blocking=True)
+        if self._result_addresses[turn]:
+            ops.publish_result(self._result_addresses[turn], self.result, self.result.numel())
+        else:
+            self._result_hosts[turn].copy_(self.result, non_blocking=True)
         self._result_events[turn].record()
         return turn
 

@@ -94,6 +94,10 @@ class AttentionWork(WorkPlanner):
         n_tiles = n_sing = 0
         t = 0
         spans = []                      # (first key block, last key block) of every tile
+        if max(lengths) == 1:           # a decode step: every token is a single one
+            n_sing = len(lengths)
+            sing[:n_sing] = np.arange(n_sing, dtype=np.int32)
+            lengths = ()
         for b, n in enumerate(lengths):
             if n <= self.SINGLE_MAX_Q:
                 sing[n_sing:n_sing + n] = np.arange(t, t + n, dtype=np.int32)

@@ -48,6 +48,7 @@ class Settings:
     prefill_part: int = -1
     decode_ctas: int = 0
     decode_ring: Optional[bool] = None
+    step_words_by_kernel: bool = True
 
     @classmethod
     def from_environment(cls) -> "Settings":
@@ -56,7 +57,8 @@ class Settings:
                    prefill_part=_int("PRB200_PREFILL_PART", -1),
                    decode_ctas=_int("PRB200_DECODE_CTAS", 0),
                    decode_ring=(_flag("PRB200_DECODE_RING", True)
-                                if "PRB200_DECODE_RING" in os.environ else None))
+                                if "PRB200_DECODE_RING" in os.environ else None),
+                   step_words_by_kernel=_flag("PRB200_STEP_WORDS_BY_KERNEL", True))
 
 
 SETTINGS = Settings.from_environment()

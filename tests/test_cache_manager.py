@@ -247,3 +247,32 @@ def test_state_keeping_models_share_no_prefix_and_fork_with_their_state():
     bare.commit("a")
     with pytest.raises(CacheError, match="no state copy"):
         bare.fork("a", "b")
+
+
+def test_block_tables_keep_their_device_form():
+    """Each table's row (padded with -1, by state slot) follows appends, copy-on-write
+    swaps, aborted reservations, pages a window has passed, forks and the request's end."""
+    groups = [GroupSpec("all", (0,), 2, 16), GroupSpec("near", (1,), 2, 16, window=20)]
+    cm = CacheManager(groups, page_size=16, num_pages=[12, 12], num_slots=3, max_positions=96)
+    sa = cm.open("a")
+    cm.reserve("a", 40)
+    assert cm.table_rows[0][sa].tolist() == cm.block_table("a", 0) + [-1] * 3
+    cm.abort("a")
+    assert cm.table_rows[0][sa].tolist() == [-1] * 6
+    cm.reserve("a", 40)
+    cm.commit("a")
+    cm.check()
+    assert cm.table_rows[1][sa].tolist()[:3] == cm.block_table("a", 1) and \
+        cm.table_rows[1][sa][0] == -1                      # the window has passed page 0
+    sb = cm.fork("a", "b")
+    assert cm.table_rows[0][sb].tolist() == cm.table_rows[0][sa].tolist()
+    cm.reserve("b", 1)                                      # copies the shared, partly filled page
+    cm.commit("b")
+    assert cm.table_rows[0][sb][2] != cm.table_rows[0][sa][2]
+    assert cm.table_rows[0][sb].tolist()[:3] == cm.block_table("b", 0)
+    cm.check()
+    cm.close("a")
+    assert cm.table_rows[0][sa].tolist() == [-1] * 6 and cm.table_rows[1][sa].tolist() == [-1] * 6
+    cm.check()
+    cm.close("b")
+    cm.check()

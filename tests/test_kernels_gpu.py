@@ -693,6 +693,48 @@ def test_kv_append_and_copy_pages():
     assert status.tolist()[0] == 3
 
 
+@pytest.mark.parametrize("words", [1, 37, 256, 1500, 4096])
+def test_step_words_cross_the_bus_inside_kernels(words):
+    """A step's description read from pinned memory by a kernel (with the ids that name
+    places among the last tokens put in on the way), and a result written back by one."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(words)
+    host = torch.randint(0, 1000, (words + 8,), dtype=torch.int32, generator=g).pin_memory()
+    address = ops.host_device_address(host)
+    assert address != 0
+    assert ops.host_device_address(torch.zeros(4, dtype=torch.int32)) == 0      # pageable
+    prev = torch.arange(100, 108, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    tokens_at, n_tokens = min(5, words - 1), min(20, words - min(5, words - 1))
+    expect = host.clone()
+    for i in range(tokens_at, tokens_at + n_tokens, 3):
+        host[i] = -(i % 8) - 1
+        expect[i] = 100 + i % 8
+    if words > 30:                       # a negative word outside the token range stays
+        host[words - 1] = -3
+        expect[words - 1] = -3
+    dev = torch.full((words + 8,), -7, dtype=torch.int32, device="cuda")
+    ops.fetch_step(dev, address, words, tokens_at, n_tokens, prev, status)
+    assert torch.equal(dev[:words].cpu(), expect[:words])
+    assert bool((dev[words:] == -7).all())
+    assert int(status[0]) == 0
+    # without the last tokens nothing is replaced
+    ops.fetch_step(dev, address, words, tokens_at, n_tokens, None, status)
+    assert torch.equal(dev[:words].cpu(), host[:words])
+    # a place beyond the last tokens is recorded, not read
+    host[tokens_at] = -9
+    ops.fetch_step(dev, address, words, tokens_at, n_tokens, prev, status)
+    torch.cuda.synchronize()
+    assert int(status[0]) != 0 and int(dev[tokens_at]) == 0
+    # and back
+    out = torch.full((words + 8,), -1, dtype=torch.int32).pin_memory()
+    n_back = min(words, 128 + 68)
+    ops.publish_result(ops.host_device_address(out), dev, n_back)
+    torch.cuda.synchronize()
+    assert torch.equal(out[:n_back], dev[:n_back].cpu())
+    assert bool((out[n_back:] == -1).all())
+
+
 def test_sample_kernel_greedy_ties_and_nan():
     ops = _ops()
     logits = torch.randn(6, 50257, device="cuda")

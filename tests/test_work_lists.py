@@ -153,3 +153,42 @@ def test_layout_gives_planners_room_and_counters():
     decode = fill_host_buffer(host, lay, [[1], [2], [3]], [7, 8, 9], [0, 1, 2], [False] * 3,
                               [[[0], [1], [2]]], [[[0] * 16 for _ in range(3)]], [[0, 0, 0]], [0, 1, 2])
     assert decode["_words"] == off + 8
+
+
+def test_a_decode_step_is_described_like_any_other():
+    """One token per request takes a shorter way through fill_host_buffer, and block tables
+    may come as rows in their device form: the words are those of the long way."""
+    lay = BatchLayout(8, 4, 2, 6, (AttentionWork(),))
+    tables = [[[3, 1, 4], [5], [9, 2]], [[7, -1, 8], [0], [6, 11]]]
+    rows = [np.full((3, 6), -1, dtype=np.int32) for _ in range(2)]
+    for g in range(2):
+        for b, table in enumerate(tables[g]):
+            rows[g][b, :len(table)] = table
+    slots = [[[3 * 16 + 2], [5 * 16 + 1], [2 * 16 + 15]], [[8 * 16 + 2], [1], [11 * 16 + 15]]]
+    args = ([[17], [4], [250]], [130, 1, 31], [2, 0, 1], [False, True, False])
+    a = np.full(lay.size, 77, dtype=np.int32)
+    b = np.full(lay.size, 77, dtype=np.int32)
+    ca = fill_host_buffer(a, lay, *args, slots, tables, [[0, 0, 0], [64, 0, 0]], [0, 1, 2])
+    cb = fill_host_buffer(b, lay, *args, slots, rows, [[0, 0, 0], [64, 0, 0]], [0, 1, 2])
+    assert ca == cb and np.array_equal(a[:ca["_words"]], b[:cb["_words"]])
+    assert a[lay.tokens:lay.tokens + 4].tolist() == [17, 4, 250, 0]
+    assert a[lay.positions:lay.positions + 4].tolist() == [130, 1, 31, 0]
+    assert a[lay.seq_of_token:lay.seq_of_token + 4].tolist() == [0, 1, 2, -1]
+    assert a[lay.q_start:lay.q_start + 5].tolist() == [0, 1, 2, 3, 3]
+    assert a[lay.kv_len:lay.kv_len + 4].tolist() == [131, 2, 32, 0]
+    assert a[lay.state_slot:lay.state_slot + 4].tolist() == [2, 0, 1, 0]
+    assert a[lay.fresh:lay.fresh + 4].tolist() == [0, 1, 0, 0]
+    assert a[lay.slots[1]:lay.slots[1] + 4].tolist() == [130, 1, 191, -1]
+    assert a[lay.first_pos[1]:lay.first_pos[1] + 4].tolist() == [64, 0, 0, 0]
+    assert a[lay.block_table[1]:lay.block_table[1] + 24].reshape(4, 6).tolist() == \
+        [[7, -1, 8, -1, -1, -1], [0, -1, -1, -1, -1, -1], [6, 11, -1, -1, -1, -1], [-1] * 6]
+    assert a[lay.counts:lay.counts + 2].tolist() == [3, 3]
+    # the same requests with two tokens for one of them go the long way
+    c = np.full(lay.size, 77, dtype=np.int32)
+    slots2 = [[[50], [81, 82], [47]], [[130], [1, 2], [191]]]
+    fill_host_buffer(c, lay, [[17], [4, 5], [250]], [130, 1, 31], [2, 0, 1], [False, True, False],
+                     slots2, rows, [[0, 0, 0], [64, 0, 0]], [0, 2, 3])
+    assert c[lay.positions:lay.positions + 5].tolist() == [130, 1, 2, 31, 0]
+    assert c[lay.kv_len:lay.kv_len + 4].tolist() == [131, 3, 32, 0]
+    assert np.array_equal(c[lay.block_table[0]:lay.block_table[0] + 24],
+                          a[lay.block_table[0]:lay.block_table[0] + 24])
