@@ -233,15 +233,34 @@ __device__ __forceinline__ void cp_async_wait_all() {
 template <int MT>
 __device__ __forceinline__ void norm_rows_staged(const Args& a, __nv_bfloat16* xs, const float* gb) {
     constexpr int MP = 8 * MT;
+    static_assert(MP % WARPS == 0 && MP / WARPS <= 2, "one or two rows per warp");
+    constexpr int R = MP / WARPS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k = a.k;
-    for (int t = warp; t < MP; t += WARPS) {
-        __nv_bfloat16* dst = xs + (size_t)t * a.xs_pitch;
-        if (t >= a.m) {
+    // rows warp, warp + 8: those beyond M are zero
+    int live = 0;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int t = warp + r * WARPS;
+        if (t < a.m) {
+            ++live;
+        } else {
+            __nv_bfloat16* dst = xs + (size_t)t * a.xs_pitch;
             for (int i = lane; i < k / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
-            continue;
         }
-        norm_row_any(a.xf + (size_t)t * a.ldx, dst, gb, k, a.beta != nullptr, a.eps);
+    }
+    if (live == R) {
+        const float* xrow[R];
+        __nv_bfloat16* dst[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            xrow[r] = a.xf + (size_t)(warp + r * WARPS) * a.ldx;
+            dst[r] = xs + (size_t)(warp + r * WARPS) * a.xs_pitch;
+        }
+        norm_rows_any<R>(xrow, dst, gb, k, a.beta != nullptr, a.eps);
+    } else if (live == 1) {                          // (rows are live from the first on)
+        norm_row_any(a.xf + (size_t)warp * a.ldx, xs + (size_t)warp * a.xs_pitch, gb, k,
+                     a.beta != nullptr, a.eps);
     }
     __syncthreads();
 }

@@ -64,35 +64,52 @@ __host__ __device__ inline size_t smem_bytes(int mt, bool ln, int k) {
     return (size_t)WARPS * ROWS * 8 * mt * sizeof(float) + (ln ? (size_t)8 * mt * norm_pitch(k) * 2 : 0);
 }
 
-// LayerNorm of one float32 row of k elements into bfloat16, by one warp.  The row is held in
-// NV float4 per lane; the caller picks the smallest instance that holds it, so that a short
-// row does not issue the (predicated-off) instructions of a long one.  Mean first, then the
-// centred squares from the registers, both float32 and both summed in a fixed order.
+// LayerNorm of R float32 rows of k elements into bfloat16, by one warp: the rows' loads are
+// all requested before the first sum, so that two rows cost one round trip to the L2, not
+// two (a CTA of eight warps norms sixteen rows in the time of eight).  A row is held in NV
+// float4 per lane; the caller picks the smallest instance that holds it, so that a short row
+// does not issue the (predicated-off) instructions of a long one.  Mean first, then the
+// centred squares from the registers, both float32 and both summed in a fixed order: a row's
+// result does not depend on R.
 // gb: gamma [k] then beta [k] (if has_beta), anywhere (shared memory in both callers).
-template <int NV>
-__device__ __forceinline__ void norm_row(const float* __restrict__ xrow, __nv_bfloat16* dst,
-                                         const float* gb, int k, bool has_beta, float eps) {
+template <int NV, int R>
+__device__ __forceinline__ void norm_rows_of_warp(const float* const (&xrow)[R],
+                                                  __nv_bfloat16* const (&dst)[R], const float* gb,
+                                                  int k, bool has_beta, float eps) {
     const int lane = threadIdx.x & 31;
     const int nvec = k / 4;
-    const float4* src = reinterpret_cast<const float4*>(xrow);
-    float4 v[NV];
-    float s = 0.0f;
+    float4 v[R][NV];
+    float s[R];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int idx = lane + 32 * i;
-        v[i] = idx < nvec ? __ldcg(src + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
-        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-    }
-    const float mean = prb_warp_sum(s) / (float)k;
-    float sq = 0.0f;
+    for (int r = 0; r < R; ++r) {
+        const float4* src = reinterpret_cast<const float4*>(xrow[r]);
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        if (lane + 32 * i < nvec) {
-            const float c0 = v[i].x - mean, c1 = v[i].y - mean, c2 = v[i].z - mean, c3 = v[i].w - mean;
-            sq += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+        for (int i = 0; i < NV; ++i) {
+            const int idx = lane + 32 * i;
+            v[r][i] = idx < nvec ? __ldcg(src + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
-    const float inv = 1.0f / sqrtf(prb_warp_sum(sq) / (float)k + eps);
+    float mean[R], inv[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        s[r] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) s[r] += (v[r][i].x + v[r][i].y) + (v[r][i].z + v[r][i].w);
+        mean[r] = prb_warp_sum(s[r]) / (float)k;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        float sq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (lane + 32 * i < nvec) {
+                const float c0 = v[r][i].x - mean[r], c1 = v[r][i].y - mean[r],
+                            c2 = v[r][i].z - mean[r], c3 = v[r][i].w - mean[r];
+                sq += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+            }
+        }
+        inv[r] = 1.0f / sqrtf(prb_warp_sum(sq) / (float)k + eps);
+    }
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int idx = lane + 32 * i;
@@ -100,26 +117,47 @@ __device__ __forceinline__ void norm_row(const float* __restrict__ xrow, __nv_bf
             const float4 gm = reinterpret_cast<const float4*>(gb)[idx];
             float4 bt = make_float4(0.f, 0.f, 0.f, 0.f);
             if (has_beta) bt = reinterpret_cast<const float4*>(gb + k)[idx];
-            const __nv_bfloat162 lo = __floats2bfloat162_rn((v[i].x - mean) * inv * gm.x + bt.x,
-                                                            (v[i].y - mean) * inv * gm.y + bt.y);
-            const __nv_bfloat162 hi = __floats2bfloat162_rn((v[i].z - mean) * inv * gm.z + bt.z,
-                                                            (v[i].w - mean) * inv * gm.w + bt.w);
-            uint2 pk;
-            pk.x = *reinterpret_cast<const uint32_t*>(&lo);
-            pk.y = *reinterpret_cast<const uint32_t*>(&hi);
-            *reinterpret_cast<uint2*>(dst + idx * 4) = pk;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const __nv_bfloat162 lo =
+                    __floats2bfloat162_rn((v[r][i].x - mean[r]) * inv[r] * gm.x + bt.x,
+                                          (v[r][i].y - mean[r]) * inv[r] * gm.y + bt.y);
+                const __nv_bfloat162 hi =
+                    __floats2bfloat162_rn((v[r][i].z - mean[r]) * inv[r] * gm.z + bt.z,
+                                          (v[r][i].w - mean[r]) * inv[r] * gm.w + bt.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(dst[r] + idx * 4) = pk;
+            }
         }
     }
 }
 
-// The instance for a row of k elements (k a multiple of 4, at most LN_MAX_K).
+// The instance for rows of k elements (k a multiple of 4, at most LN_MAX_K).  Two long rows
+// together would not fit a lane's registers: they go one after the other.
+template <int R>
+__device__ __forceinline__ void norm_rows_any(const float* const (&xrow)[R],
+                                              __nv_bfloat16* const (&dst)[R], const float* gb, int k,
+                                              bool has_beta, float eps) {
+    const int iters = (k / 4 + 31) / 32;
+    if (iters <= 2) norm_rows_of_warp<2, R>(xrow, dst, gb, k, has_beta, eps);
+    else if (iters <= 6) norm_rows_of_warp<6, R>(xrow, dst, gb, k, has_beta, eps);
+    else if (iters <= 8) norm_rows_of_warp<8, R>(xrow, dst, gb, k, has_beta, eps);
+    else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float* const one_x[1] = {xrow[r]};
+            __nv_bfloat16* const one_d[1] = {dst[r]};
+            norm_rows_of_warp<LN_MAX_K / 128, 1>(one_x, one_d, gb, k, has_beta, eps);
+        }
+    }
+}
 __device__ __forceinline__ void norm_row_any(const float* xrow, __nv_bfloat16* dst, const float* gb,
                                              int k, bool has_beta, float eps) {
-    const int iters = (k / 4 + 31) / 32;
-    if (iters <= 2) norm_row<2>(xrow, dst, gb, k, has_beta, eps);
-    else if (iters <= 6) norm_row<6>(xrow, dst, gb, k, has_beta, eps);
-    else if (iters <= 8) norm_row<8>(xrow, dst, gb, k, has_beta, eps);
-    else norm_row<LN_MAX_K / 128>(xrow, dst, gb, k, has_beta, eps);
+    const float* const one_x[1] = {xrow};
+    __nv_bfloat16* const one_d[1] = {dst};
+    norm_rows_any<1>(one_x, one_d, gb, k, has_beta, eps);
 }
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,

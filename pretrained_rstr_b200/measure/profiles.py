@@ -346,7 +346,8 @@ def profile_decode_attention(spec: str) -> int:
         chosen = decode_splits(nreq * nh, -(-ctx // 256) * 256, ps)[0]
     except Exception:
         pass
-    for split in sorted({granule, 2 * granule, 4 * granule, 8 * granule, -(-ctx // granule) * granule}):
+    for split in sorted({granule, 2 * granule, 3 * granule, 4 * granule, 8 * granule,
+                         -(-ctx // granule) * granule} | ({chosen} if chosen else set())):
         splits = -(-ctx // split)
         ws = torch.zeros(nreq * nh * splits * (dh + 4), device="cuda")
         counters = torch.zeros(nreq * nh, dtype=torch.int32, device="cuda")
