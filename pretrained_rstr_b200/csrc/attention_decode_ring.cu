@@ -112,18 +112,26 @@ PRB_API int prb_attention_decode_ring_max_list() { return MAX_LIST; }
 
 // Whether this kernel is the faster one for a launch of n_list tokens over contexts of up to
 // max_context keys; the split-key kernel of attention_decode.cu is the other.  Measured inside
-// GPT-2 small's decode step (12 heads; ms a step, ring / split-key): 1 request 0.364 / 0.372
-// at context 256 and 0.366 / 0.366 at 1,000; 8 requests 0.377 / 0.372 and 0.442 / 0.427; 16
-// requests 0.496 / 0.485 (512) and 0.572 / 0.560 (1,024); 32 requests 0.673 / 0.689 and 0.806 /
-// 0.892; 48 requests 0.746 / 0.704 and 0.928 / 0.894; 64 requests 0.726 / 0.690 (256) and 1.029 /
-// 1.140 (1,000).  The ring wins where many (token, head) pairs have long contexts (its warps
-// stream long runs, the other kernel's CTAs walk a thousand keys one batch after the other)
-// and at a single request with a short context (everything it reads is requested before the
-// dependency resolves and one CTA holds a whole pair).
+// whole decode steps (ms a step, split-key / ring; n_list is the capacity the step's graph
+// was made for, so 24 requests run as 32 and 48 as 64).  GPT-2 small, 12 heads: 1 request 0.372
+// / 0.364 at context 256 and 0.366 / 0.366 at 1,000; 8 requests 0.358 / 0.391 (500) and 0.417 /
+// 0.437 (1,000); 12 requests 0.540 / 0.524 and 16 requests 0.545 / 0.544 (1,000), 16 requests
+// 0.502 / 0.507 (320) and 0.561 / 0.541 (576); 32 requests 0.586 / 0.578 (250), 0.691 / 0.660
+// (320), 0.821 / 0.717 (576), 0.884 / 0.776 (1,000); 24 as 32: 0.709 / 0.726; 40: 0.875 / 0.859;
+// 48: 0.881 / 0.895; 56: 1.121 / 0.947; 64 requests 0.620 / 0.646 (250), 0.719 / 0.730 (320),
+// 0.899 / 0.858 (576), 1.140 / 0.992 (1,000).  Medium, 16 heads: 16 requests 1.360 / 1.305
+// (1,000); 32 requests 1.633 / 1.487 (250).  XL, 25 heads: 8 requests 2.55 / 2.75 (1,000); 16
+// requests 3.99 / 3.80 (1,000) and 2.80 / 2.83 (250).
+// The ring wins where many (token, head) pairs have long contexts (its warps stream long runs,
+// the other kernel's CTAs walk their keys one batch after the other), in the middle range at
+// every context, and at a single request with a short context (everything it reads is
+// requested before the dependency resolves and one CTA holds a whole pair).
 PRB_API int prb_attention_decode_ring_prefers(int n_list, int n_heads, int max_context) {
     const long pairs = (long)n_list * n_heads;
     const long sms = prb_sm_count();
-    if (pairs >= 2 * sms) return max_context > 512;
+    if (pairs >= 4 * sms) return max_context > 512;
+    if (pairs >= 2 * sms) return 1;
+    if (pairs >= sms) return n_list >= 16 && max_context > 512;
     return pairs * 8 <= sms && max_context <= 512;
 }
 
@@ -165,16 +173,16 @@ PRB_API int prb_attention_decode_ring(void* out, long out_stride, const void* q,
     a.k_new = (const __nv_bfloat16*)k_new; a.v_new = (const __nv_bfloat16*)v_new; a.kv_stride = kv_stride;
     a.new_keys = new_keys; a.workspace = workspace; a.counters = counters; a.status = status;
     const int sms = prb_sm_count();
-    // Warps and ring depth.  The CTAs of this kernel are meant to sit on the SMs beside those
-    // of the product before it (about 48 KB of shared memory each) while that still runs, and
-    // to leave room for the product after it: 8 warps x 2 buffers (128 KB) do, and with up to
-    // two units per warp they hold everything a warp will ever read, requested before the
+    // Warps and ring depth: 8 warps x 2 buffers (128 KB).  The CTAs of this kernel are meant
+    // to sit on the SMs beside those of the product before it (about 48 KB of shared memory
+    // each) while that still runs, and to leave room for the product after it; with up to two
+    // units per warp the buffers hold everything a warp will ever read, requested before the
     // dependency resolves (a third unit follows when the first has been read).  Longer runs
-    // stream: 8 warps x 3 buffers, most bytes in flight (and no room beside a neighbour, which
-    // a long kernel can afford).
-    const long units = (long)n_list * n_heads * ((max_context > 0 ? max_context : page_size * max_pages) / UNIT + 1);
-    auto per_warp = [&](int w) { return (units + (long)sms * w - 1) / ((long)sms * w); };
-    int warps = 8, st = per_warp(8) <= 3 ? 2 : 3;
+    // stream through the same two buffers: a third buffer per warp (most bytes in flight)
+    // measured slower alone at every size (64 requests x 12 heads at 1,000 keys: 43.9 against
+    // 42.8 us) and more so inside a step, where its 192 KB leave the next kernel no room
+    // (GPT-2 small, 64 requests: 1.021 against 0.992 ms a step; XL: 7.43 against 7.24 ms).
+    int warps = 8, st = 2;
     if (stages > 0) { st = stages; warps = (size_t)stages * 8 * 2 * TILE > 200 * 1024 ? 6 : 8; }
     if (stages == 0 && g_ring_warps > 0) { warps = g_ring_warps; st = g_ring_stages; }
     a.stages = st;

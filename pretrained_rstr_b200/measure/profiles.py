@@ -317,27 +317,33 @@ def _graph_time_us(fn, reps=10):
 def profile_decode_attention(spec: str) -> int:
     """The decode attention kernel alone: REQUESTS single tokens at context CONTEXT, HEADS
     heads of 64 ("HEADS,REQUESTS,CONTEXT"), over a paged cache with shuffled pages, by split
-    size; each a CUDA graph of 10 launches.  Bytes = the keys and values read once."""
+    size; each a CUDA graph of 10 or more launches that go round several sets of requests,
+    together larger than the L2.  Bytes = the keys and values read once."""
     import torch
     from ..csrc import ops
     nh, nreq, ctx = (int(x) for x in spec.split(","))
     dh = ps = 64
     g = torch.Generator(device="cpu").manual_seed(0)
     pages_per = -(-ctx // ps)
-    num_pages = nreq * pages_per + 3
+    nbytes = 2 * nreq * nh * ctx * dh * 2
+    # as many sets of requests as together exceed the L2, one set per launch in turn: inside
+    # a step no layer finds its keys and values in the L2 either
+    sets = max(1, -(-int(300e6) // nbytes))
+    num_pages = sets * nreq * pages_per + 3
     k = torch.randn(num_pages, nh, ps, dh, generator=g).bfloat16().cuda()
     v = torch.randn(num_pages, nh, ps, dh, generator=g).bfloat16().cuda()
     perm = torch.randperm(num_pages, generator=g).tolist()
-    table = torch.full((nreq, pages_per + 1), -1, dtype=torch.int32)
-    for b in range(nreq):
-        for i in range(pages_per):
-            table[b, i] = perm.pop()
-    table = table.cuda()
+    tables = []
+    for _ in range(sets):
+        table = torch.full((nreq, pages_per + 1), -1, dtype=torch.int32)
+        for b in range(nreq):
+            for i in range(pages_per):
+                table[b, i] = perm.pop()
+        tables.append(table.cuda())
     seq = torch.arange(nreq, dtype=torch.int32).cuda()
     pos = torch.full((nreq,), ctx - 1, dtype=torch.int32).cuda()
     q = torch.randn(nreq, nh * dh, generator=g).bfloat16().cuda()
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
-    nbytes = 2 * nreq * nh * ctx * dh * 2
     res, ref = {}, None
     granule = ops.decode_split()
     chosen = None
@@ -346,15 +352,25 @@ def profile_decode_attention(spec: str) -> int:
         chosen = decode_splits(nreq * nh, -(-ctx // 256) * 256, ps)[0]
     except Exception:
         pass
+    launches = max(10, sets)
+
+    def timed(one):
+        turn = [0]
+
+        def run():
+            one(tables[turn[0] % sets])
+            turn[0] += 1
+        return _graph_time_us(run, launches)
+
     for split in sorted({granule, 2 * granule, 3 * granule, 4 * granule, 8 * granule,
                          -(-ctx // granule) * granule} | ({chosen} if chosen else set())):
         splits = -(-ctx // split)
         ws = torch.zeros(nreq * nh * splits * (dh + 4), device="cuda")
         counters = torch.zeros(nreq * nh, dtype=torch.int32, device="cuda")
         out = torch.zeros_like(q)
-        us = _graph_time_us(lambda: ops.attention_decode(out, q, k, v, table, seq, pos, None, None,
-                                                         nreq, nh, 0.125, None, ws, counters,
-                                                         splits, status, split_keys=split))
+        us = timed(lambda table: ops.attention_decode(out, q, k, v, table, seq, pos, None, None,
+                                                      nreq, nh, 0.125, None, ws, counters,
+                                                      splits, status, split_keys=split))
         if ref is None:
             ref = out.clone()
         res[f"split{split}"] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
@@ -365,12 +381,13 @@ def profile_decode_attention(spec: str) -> int:
         counters = torch.zeros(nreq * nh, dtype=torch.int32, device="cuda")
         for stages in (2, 3, 4):
             out = torch.zeros_like(q)
-            us = _graph_time_us(lambda: ops.attention_decode_ring(
+            us = timed(lambda table: ops.attention_decode_ring(
                 out, q, k, v, table, seq, pos, None, None, nreq, nh, 0.125, None, ws, counters,
                 status, new_keys=4, stages=stages, max_context=-(-ctx // 256) * 256))
             res[f"ring_stages{stages}"] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
                                            "max_diff": float((out.float() - ref.float()).abs().max())}
     print(json.dumps({"profile_decode_attention": spec, "mbytes": round(nbytes / 1e6, 2),
+                      "sets": sets,
                       "engine_split": chosen, "status": status.tolist(), **res}))
     return 0
 

@@ -96,7 +96,7 @@ def timed_prefill(lm, n_prompts, prompt_len, vocab, warmup=3, repeats=5, seed=11
 
 def mixed_workload(engine, vocab, n_requests=64, max_new=128, shared_fraction=0.3,
                    shared_prefix=256, min_prompt=16, max_prompt=1024, seed=4,
-                   max_events=8192):
+                   max_events=4096):
     """Many requests at once through the scheduler: prompt lengths uniform in
     [min_prompt, max_prompt) from ``seed``, a fraction of them beginning with one common
     prefix (found again through the prefix index once the first of them has computed it),
@@ -115,6 +115,9 @@ def mixed_workload(engine, vocab, n_requests=64, max_new=128, shared_fraction=0.
             prompts.append(prefix + [rng.randrange(vocab) for _ in range(n - shared_prefix)])
         else:
             prompts.append([rng.randrange(vocab) for _ in range(n)])
+    # (made before the clock starts: thousands of events take milliseconds to create)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(max_events)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(max_events)]
     first_token = {}
     t_submit = time.perf_counter()
 
@@ -125,8 +128,6 @@ def mixed_workload(engine, vocab, n_requests=64, max_new=128, shared_fraction=0.
     rids = [("mixed", seed, i) for i in range(n_requests)]
     for rid, p in zip(rids, prompts):
         engine.submit(rid, p, max_new, on_token=on_token)
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(max_events)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(max_events)]
     engine.timing_events = (starts, ends)
     kinds = []
     before = dict(engine.scheduler.stats), dict(engine.lm.cache.stats), dict(engine.runner.counters)
