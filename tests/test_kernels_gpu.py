@@ -541,7 +541,9 @@ def test_attention_far_key_stands_out():
 # ------------------------------------------------------------------ decode-time product
 @pytest.mark.parametrize("m,n,k", [(1, 192, 64), (8, 2304, 768), (5, 1000, 96), (16, 320, 96),
                                    (33, 768, 3072), (64, 50257, 768), (3, 24, 1608),
-                                   (8, 100, 6400), (12, 200, 1000), (2, 50, 1600), (16, 72, 3072)])
+                                   (8, 100, 6400), (12, 200, 1000), (2, 50, 1600), (16, 72, 3072),
+                                   (13, 808, 768), (24, 2304, 768), (32, 328, 3072), (17, 100, 64),
+                                   (29, 1000, 1600)])
 @pytest.mark.parametrize("variant", ["plain_f32", "bias_gelu_bf16", "bias_resid_f32", "norm_bf16"])
 def test_gemm_smallm(m, n, k, variant):
     ops = _ops()
@@ -598,22 +600,27 @@ def test_gemm_smallm_rows_do_not_depend_on_the_batch(k):
     one = torch.zeros(1, 256, device="cuda")
     ops.gemm_smallm(one, w, a=a[17:18].contiguous())
     assert torch.equal(one[0], mid[7])             # the same kernel: the same bits
+    wide = torch.zeros(30, 256, device="cuda")     # 30 rows: the other kernel again
+    ops.gemm_smallm(wide, w, a=a[5:35].contiguous())
+    assert float((wide[12] - one[0]).abs().max()) <= 2e-4 * float(big[17].abs().max())
     # 40 rows go to another kernel, which adds the same products in another order
     assert float((big[17] - one[0]).abs().max()) <= 2e-4 * float(big[17].abs().max())
 
 
+@pytest.mark.parametrize("m", [5, 13, 16, 30])
 @pytest.mark.parametrize("k", [64, 768, 1024, 1600])
-def test_gemm_smallm_fused_norm_with_an_outlier_channel(k):
+def test_gemm_smallm_fused_norm_with_an_outlier_channel(k, m):
     """A row whose first channel is thousands among values of order one (as massive
     activations are): the fused norm's statistics are mean first, then centred squares, and
     agree with the two-pass norm kernel followed by the plain product; a one-pass variance on
     data shifted by the first element would cancel here."""
     ops = _ops()
     g = torch.Generator(device="cuda").manual_seed(k)
-    m, n = 5, 96
+    n = 96
     x = torch.randn(m, k, device="cuda", generator=g)
-    x[:, 0] = torch.tensor([3e3, -2e3, 5e3, 1.0, 8e3], device="cuda")
+    x[:, 0] = torch.tensor([3e3, -2e3, 5e3, 1.0, 8e3], device="cuda").repeat(7)[:m]
     x[2, k // 2] = -4e3
+    x[m - 1, k // 3] = 6e3
     gamma = torch.rand(k, device="cuda", generator=g) + 0.5
     beta = torch.randn(k, device="cuda", generator=g) * 0.1
     w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
@@ -819,6 +826,40 @@ def test_gemm_smallm_scatters_keys_and_values_to_the_cache():
     torch.cuda.synchronize()
     assert torch.equal(out1, out2) and torch.equal(k1, k2) and torch.equal(v1, v2)
     assert int((k1 != 0).any(dim=-1).sum()) == 6 * kv_heads and status.tolist() == [0, 0, 0, 0]
+
+
+def test_gemm_smallm_scatters_at_27_rows():
+    """The same with 27 tokens, against the tensor-memory product and the append kernel."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(4)
+    m, heads, kv_heads, dh, ps, pages, k = 27, 6, 3, 32, 16, 9, 128
+    q_width, kv_width = heads * dh, kv_heads * dh
+    n = q_width + 2 * kv_width
+    a = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.2).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda", generator=g)
+    order = torch.randperm(pages * ps, generator=torch.Generator().manual_seed(1))[:m].to(torch.int32)
+    order[3] = -1
+    slots = order.cuda()
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    k1 = torch.zeros(pages, kv_heads, ps, dh, device="cuda", dtype=torch.bfloat16)
+    v1, k2, v2 = torch.zeros_like(k1), torch.zeros_like(k1), torch.zeros_like(k1)
+    out1 = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    out2 = torch.zeros_like(out1)
+    ops.gemm_smallm(out1, w, a=a, bias=bias, kv_scatter=(k1, v1, slots, q_width), status=status)
+    ops.gemm_bf16(out2, a, w, bias)
+    ops.kv_append(k2, v2, out2[:, q_width:q_width + kv_width], out2[:, q_width + kv_width:], slots, m,
+                  status)
+    torch.cuda.synchronize()
+    ref = a.float() @ w.float().t() + bias
+    assert float((out1.float() - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+    assert float((k1.float() - k2.float()).abs().max()) <= 2e-2 * float(ref.abs().max())
+    assert int((k1 != 0).any(dim=-1).sum()) == 26 * kv_heads and status.tolist() == [0, 0, 0, 0]
+    # each cached row is the output row's own bits
+    for t in (0, 11, 26):
+        slot = int(slots[t])
+        assert torch.equal(k1[slot // ps, :, slot % ps].reshape(-1), out1[t, q_width:q_width + kv_width])
+        assert torch.equal(v1[slot // ps, :, slot % ps].reshape(-1), out1[t, q_width + kv_width:])
 
 
 @pytest.mark.parametrize("m,heads,kv_heads,dh,ps", [(200, 6, 3, 32, 16), (130, 12, 12, 64, 64), (70, 5, 1, 24, 32)])
