@@ -66,6 +66,57 @@ def profile_gemm(shape: str) -> int:
     return 0
 
 
+def profile_host(batch: int) -> int:
+    """The host's side of a decode step: the benchmark model with ONE layer (so that the
+    device is never the bound), ``batch`` requests decoding through
+    ``Engine.step(ahead=True)``; wall time a step over 300 steps, then the same under
+    cProfile (its overhead about doubles the times; the shares are what it is for)."""
+    import cProfile
+    import pstats
+    import random
+    import time
+    import torch
+    from pretrained_rstr_b200 import load_lm
+    from pretrained_rstr_b200.config import GPT2Config
+    from pretrained_rstr_b200.weights import make_random_model
+    raw = dict(SMALL)
+    raw["n_layer"] = 1
+    tmp = tempfile.mkdtemp(prefix="prb200_prof_")
+    try:
+        make_random_model(tmp, GPT2Config.from_dict(raw), seed=2, dtype=torch.bfloat16)
+        m = load_lm(tmp, gpu=True, dtype="bfloat16", max_lanes=64, max_batched_tokens=2048,
+                    prefill_chunk=1024, share_prefixes=False)
+    finally:
+        import shutil
+        shutil.rmtree(tmp, ignore_errors=True)
+    e = m.engine
+    rng = random.Random(0)
+    for i in range(batch):
+        e.submit(i, [rng.randrange(raw["vocab_size"]) for _ in range(300)], 650)
+    while any(r.phase != "decode" for r in e.scheduler.running.values()) or e.scheduler.waiting:
+        e.step()
+    for _ in range(30):
+        e.step(ahead=True)
+    e.flush()
+    torch.cuda.synchronize()
+    steps = 300
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        e.step(ahead=True)
+    e.flush()
+    torch.cuda.synchronize()
+    wall_us = (time.perf_counter() - t0) / steps * 1e6
+    prof = cProfile.Profile()
+    prof.enable()
+    for _ in range(200):
+        e.step(ahead=True)
+    e.flush()
+    prof.disable()
+    pstats.Stats(prof).sort_stats("tottime").print_stats(16)
+    print(json.dumps({"profile_host": batch, "layers": 1, "wall_us_per_step": round(wall_us, 1)}))
+    return 0
+
+
 def profile_decode(batch: int, table: bool = False) -> int:
     """Small workload for ncu: the benchmark model, ``batch`` requests of 900 prompt tokens,
     then four decode steps launched kernel by kernel (no CUDA graph)."""
