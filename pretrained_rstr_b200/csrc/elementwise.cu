@@ -296,21 +296,37 @@ __global__ void resolve_tokens_kernel(int* __restrict__ tokens, int n, const int
 // (prb_host_device_address; null if the memory cannot be reached from kernels: the caller
 // then copies).
 namespace {
-__global__ void fetch_step_kernel(int* __restrict__ dev, const int* __restrict__ host, int words,
-                                  int tokens_at, int n_tokens, const int* __restrict__ prev,
-                                  int n_prev, int* status) {
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < words; i += gridDim.x * blockDim.x) {
-        int v = host[i];
-        if (prev != nullptr && v < 0 && i >= tokens_at && i < tokens_at + n_tokens) {
-            const int k = -v - 1;
+// (at most FETCH_PER_THREAD words per thread: the host words are requested before the wait on
+// the kernel before, whose chosen ids only the replacement needs)
+constexpr int FETCH_THREADS = 256, FETCH_PER_THREAD = 4;
+__global__ void __launch_bounds__(FETCH_THREADS)
+fetch_step_kernel(int* __restrict__ dev, const int* __restrict__ host, int words,
+                  int tokens_at, int n_tokens, const int* __restrict__ prev,
+                  int n_prev, int* status) {
+    prb_grid_launch_dependents();
+    const int first = blockIdx.x * blockDim.x + threadIdx.x, stride = gridDim.x * blockDim.x;
+    int v[FETCH_PER_THREAD];
+#pragma unroll
+    for (int j = 0; j < FETCH_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        v[j] = i < words ? host[i] : 0;
+    }
+    prb_grid_wait();
+#pragma unroll
+    for (int j = 0; j < FETCH_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        if (i >= words) continue;
+        int x = v[j];
+        if (prev != nullptr && x < 0 && i >= tokens_at && i < tokens_at + n_tokens) {
+            const int k = -x - 1;
             if (k >= n_prev) {
                 prb_set_status(status, PRB_S_ROW_RANGE, i - tokens_at, k, n_prev);
-                v = 0;
+                x = 0;
             } else {
-                v = prev[k];
+                x = prev[k];
             }
         }
-        dev[i] = v;
+        dev[i] = x;
     }
 }
 __global__ void publish_result_kernel(int* __restrict__ host, const int* __restrict__ dev, int words) {
@@ -334,11 +350,17 @@ PRB_API int prb_fetch_step(int* dev, const int* host_dev_address, int words, int
                            cudaStream_t stream) {
     if (words <= 0) return 0;
     if (dev == nullptr || host_dev_address == nullptr) return PRB_E_ARG;
-    const int blocks = words > 1024 ? 8 : (words + 255) / 256;
-    fetch_step_kernel<<<blocks, 256, 0, stream>>>(dev, host_dev_address, words, tokens_at, n_tokens,
-                                                  prev, n_prev, status);
-    PRB_LAUNCH_CHECK();
-    return 0;
+    // one word per thread up to 2,048 words (8 blocks); beyond, up to FETCH_PER_THREAD words
+    // per thread over 8 blocks or as many as that needs
+    int blocks = (words + FETCH_THREADS - 1) / FETCH_THREADS;
+    if (blocks > 8) {
+        blocks = (words + FETCH_THREADS * FETCH_PER_THREAD - 1) / (FETCH_THREADS * FETCH_PER_THREAD);
+        if (blocks < 8) blocks = 8;
+    }
+    cudaError_t e = prb_launch_dependent(fetch_step_kernel, dim3(blocks), dim3(FETCH_THREADS), 0, stream,
+                                         dev, host_dev_address, words, tokens_at, n_tokens, prev,
+                                         n_prev, status);
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 PRB_API int prb_publish_result(int* host_dev_address, const int* dev, int words, cudaStream_t stream) {

@@ -128,7 +128,7 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_attention_decode_set_stream.restype = None
     h.prb_set_pdl.argtypes = [I]
     h.prb_set_pdl.restype = None
-    h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P]
+    h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P, P, I, P, P]
     h.prb_sample_max_top_k.argtypes = []
     for name in ("prb_resolve_tokens", "prb_fetch_step", "prb_publish_result", "prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
                  "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_bf16_scatter", "prb_gemm_midm",
@@ -735,10 +735,22 @@ def max_top_k() -> int:
 
 
 def sample(out, logits, n_rows, temperature=None, top_k=None, top_p=None, seeds=None, fresh=None,
-           slots=None, rng_states=None) -> None:
+           slots=None, rng_states=None, publish=None) -> None:
     """out[r] = chosen token of logits[r,:] (float32).  Without ``temperature`` every row
-    is greedy; otherwise rows with temperature <= 0 are greedy and the rest sample."""
+    is greedy; otherwise rows with temperature <= 0 are greedy and the rest sample.
+    ``publish`` = (host_address, src, words, counter): the launch's last CTA also writes the
+    int32 words src[:words] to pinned host memory at ``host_address`` (from
+    :func:`host_device_address`); ``counter`` is one int32 on the device, zero between launches."""
     what = "sample"
+    pub = (None, None, 0, None)
+    if publish is not None:
+        address, src, words, counter = publish
+        _need(src, torch.int32, "publish source", what)
+        _need(counter, torch.int32, "publish counter", what)
+        if not address or words > src.numel():
+            raise KernelArgumentError(f"{what}: no host address to publish to, or {words} words "
+                                      f"are more than the source holds")
+        pub = (int(address), _p(src), int(words), _p(counter))
     _need(out, torch.int32, "out", what)
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelArgumentError(f"{what}: logits must be float32 with unit inner stride")
@@ -752,4 +764,4 @@ def sample(out, logits, n_rows, temperature=None, top_k=None, top_p=None, seeds=
         _need(rng_states, torch.int64, "rng_states", what)
     _check(lib().prb_sample(_p(out), _p(logits), logits.stride(0), logits.shape[1],
                             _p(temperature), _p(top_k), _p(top_p), _p(seeds), _p(fresh), _p(slots),
-                            _p(rng_states), n_rows, _stream()), what)
+                            _p(rng_states), n_rows, *pub, _stream()), what)

@@ -106,12 +106,13 @@ __device__ __forceinline__ unsigned long long lcg_next(unsigned long long* s, in
     return *s >> (48 - bits);
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_stride, int vocab,
-              const float* __restrict__ temperature, const int* __restrict__ top_k,
-              const float* __restrict__ top_p, const long long* __restrict__ seeds,
-              const int* __restrict__ fresh, const int* __restrict__ slots,
-              unsigned long long* __restrict__ rng_states, int n_rows) {
+// One row: the CTA's threads come back from here at different places (thread 0 last).
+__device__ __forceinline__ void
+sample_row(int* __restrict__ out, const float* __restrict__ logits, long row_stride, int vocab,
+           const float* __restrict__ temperature, const int* __restrict__ top_k,
+           const float* __restrict__ top_p, const long long* __restrict__ seeds,
+           const int* __restrict__ fresh, const int* __restrict__ slots,
+           unsigned long long* __restrict__ rng_states, int n_rows) {
     __shared__ Best sh[32];
     // histograms of the selection; afterwards the candidates (64-bit sort keys) and their
     // exponentials
@@ -368,20 +369,62 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
     }
     out[r] = pick;
 }
+
+// Where the chosen ids go besides `out`: the last CTA of the launch to finish copies `words`
+// int32 words from `src` (the ids and, behind them, the step's status words, which every
+// earlier kernel of the stream has finished writing) to `host`, the device address of a
+// pinned host buffer, so that no kernel or copy of its own stands between a step's last
+// kernel and the host's read.  counter: one int32, zero between launches.
+struct Publish {
+    int* host;
+    const int* src;
+    int words;
+    int* counter;
+};
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_stride, int vocab,
+              const float* __restrict__ temperature, const int* __restrict__ top_k,
+              const float* __restrict__ top_p, const long long* __restrict__ seeds,
+              const int* __restrict__ fresh, const int* __restrict__ slots,
+              unsigned long long* __restrict__ rng_states, int n_rows, Publish pub) {
+    prb_grid_launch_dependents();      // the next step's description may be fetched meanwhile
+    sample_row(out, logits, row_stride, vocab, temperature, top_k, top_p, seeds, fresh, slots,
+               rng_states, n_rows);
+    if (pub.host == nullptr) return;
+    __shared__ int last_sh;
+    __syncthreads();                   // thread 0 has stored this row's id
+    if (threadIdx.x == 0) {
+        __threadfence();
+        last_sh = atomicAdd(pub.counter, 1) == (int)gridDim.x - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (!last_sh) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < pub.words; i += blockDim.x) pub.host[i] = __ldcg(pub.src + i);
+    if (threadIdx.x == 0) *pub.counter = 0;
+    __threadfence_system();
+}
 }  // namespace
 
 PRB_API int prb_sample_max_top_k() { return MAX_TOP_K; }
 
 // temperature == nullptr: every row is greedy and the remaining pointers are unused.
+// publish_host (may be null): see Publish.
 PRB_API int prb_sample(int* out, const float* logits, long row_stride, int vocab,
                        const float* temperature, const int* top_k, const float* top_p,
                        const long long* seeds, const int* fresh, const int* slots,
-                       unsigned long long* rng_states, int n_rows, cudaStream_t stream) {
+                       unsigned long long* rng_states, int n_rows, int* publish_host,
+                       const int* publish_src, int publish_words, int* publish_counter,
+                       cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (vocab <= 0) return PRB_E_SIZE;
+    Publish pub{publish_host, publish_src, publish_words, publish_counter};
+    if (publish_host != nullptr && (publish_src == nullptr || publish_counter == nullptr || publish_words <= 0))
+        return PRB_E_ARG;
     sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(out, logits, row_stride, vocab,
                                                          temperature, top_k, top_p, seeds, fresh,
-                                                         slots, rng_states, n_rows);
+                                                         slots, rng_states, n_rows, pub);
     PRB_LAUNCH_CHECK();
     return 0;
 }

@@ -126,11 +126,15 @@ class Engine:
         self.runner.start_event = None
         ticket = None
         if samplers:
-            self.sampler.launch(self._tokens_dev, logits, samplers)
+            # the kernel that chooses the tokens is the step's last: it also writes them, and
+            # the status word, to the pinned buffer the host will read
+            turn, address = self.runner.begin_result()
+            publish = (address, self.runner.result, self.runner.result.numel()) if address else None
+            self.sampler.launch(self._tokens_dev, logits, samplers, publish=publish)
         if self.timing_events is not None:             # the step's device work ends here
             self.timing_events[1][self.step_index].record()
         if samplers:
-            ticket = self.runner.queue_result()
+            ticket = self.runner.end_result(turn, published=publish is not None)
         return (plan, entries, samplers, ticket)
 
     def _finish(self, flight) -> List[Request]:

@@ -380,12 +380,25 @@ class ModelRunner:
         """Queue the copy of the sampled tokens and the status word to the host behind the
         work launched so far; returns a ticket for :meth:`wait_result`.  Work launched
         afterwards does not delay the ticket."""
+        turn, _address = self.begin_result()
+        return self.end_result(turn, published=False)
+
+    def begin_result(self):
+        """The host buffer the next result goes to: (ticket, address under which kernels
+        reach it, or 0).  A kernel that is the last of its step may write ``self.result``
+        there itself (``ops.sample(..., publish=...)``); :meth:`end_result` follows."""
         turn = self._result_turn
         self._result_turn ^= 1
-        if self._result_addresses[turn]:
-            ops.publish_result(self._result_addresses[turn], self.result, self.result.numel())
-        else:
-            self._result_hosts[turn].copy_(self.result, non_blocking=True)
+        return turn, self._result_addresses[turn]
+
+    def end_result(self, turn: int, published: bool) -> int:
+        """Second half of :meth:`queue_result`: bring the result to the host unless the
+        step's last kernel has done so, and mark the place in the stream."""
+        if not published:
+            if self._result_addresses[turn]:
+                ops.publish_result(self._result_addresses[turn], self.result, self.result.numel())
+            else:
+                self._result_hosts[turn].copy_(self.result, non_blocking=True)
         self._result_events[turn].record()
         return turn
 

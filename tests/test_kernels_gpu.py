@@ -742,6 +742,36 @@ def test_step_words_cross_the_bus_inside_kernels(words):
     assert bool((out[n_back:] == -1).all())
 
 
+@pytest.mark.parametrize("rows", [1, 5, 64])
+def test_sample_kernel_publishes_its_result(rows):
+    """The launch's last CTA writes the chosen ids and the words behind them to pinned host
+    memory; the counter it uses is zero again afterwards, launch after launch."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    result = torch.zeros(rows + 4, dtype=torch.int32, device="cuda")
+    result[rows:] = torch.tensor([0, 11, 22, 33], dtype=torch.int32)
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    host = torch.full((rows + 8,), -5, dtype=torch.int32).pin_memory()
+    address = ops.host_device_address(host)
+    for turn in range(3):
+        logits = torch.randn(rows, 1000, device="cuda", generator=g)
+        ops.sample(result[:rows], logits, rows, publish=(address, result, rows + 4, counter))
+        torch.cuda.synchronize()
+        assert host[:rows].tolist() == logits.argmax(dim=1).tolist()
+        assert host[rows:rows + 4].tolist() == [0, 11, 22, 33] and host[rows + 4:].tolist() == [-5] * 4
+        assert int(counter[0]) == 0
+    temp = torch.full((rows,), 0.7, device="cuda")
+    args = dict(temperature=temp, top_k=torch.full((rows,), 20, dtype=torch.int32, device="cuda"),
+                top_p=torch.ones(rows, device="cuda"),
+                seeds=torch.arange(rows, dtype=torch.int64, device="cuda"),
+                fresh=torch.ones(rows, dtype=torch.int32, device="cuda"),
+                slots=torch.arange(rows, dtype=torch.int32, device="cuda"),
+                rng_states=torch.zeros(rows, dtype=torch.int64, device="cuda"))
+    ops.sample(result[:rows], logits, rows, publish=(address, result, rows + 4, counter), **args)
+    torch.cuda.synchronize()
+    assert host[:rows].tolist() == result[:rows].tolist() and int(counter[0]) == 0
+
+
 def test_sample_kernel_greedy_ties_and_nan():
     ops = _ops()
     logits = torch.randn(6, 50257, device="cuda")
