@@ -331,7 +331,6 @@ fetch_step_kernel(int* __restrict__ dev, const int* __restrict__ host, int words
 }
 __global__ void publish_result_kernel(int* __restrict__ host, const int* __restrict__ dev, int words) {
     for (int i = threadIdx.x; i < words; i += blockDim.x) host[i] = dev[i];
-    __threadfence_system();
 }
 }  // namespace
 

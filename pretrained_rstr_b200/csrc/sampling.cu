@@ -403,7 +403,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, long row_
     __threadfence();
     for (int i = threadIdx.x; i < pub.words; i += blockDim.x) pub.host[i] = __ldcg(pub.src + i);
     if (threadIdx.x == 0) *pub.counter = 0;
-    __threadfence_system();
+    // (the host reads after an event recorded behind this launch has completed: the end of
+    // the kernel makes the words visible, no fence of its own is needed)
 }
 }  // namespace
 
