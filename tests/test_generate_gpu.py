@@ -163,3 +163,22 @@ def test_arrivals_cancels_and_mixed_sampling_with_steps_in_flight(folders):
     assert stats["prepared_ahead"]["used"] > 20
     m.engine.lm.cache.check()
     assert not m.engine.lm.cache.requests
+
+
+def test_step_words_through_the_copy_engine(folders, monkeypatch):
+    """Where kernels cannot reach the pinned buffers (here: switched off), the step's
+    description and its result go through the copy engine and token feedback through a kernel
+    of its own; the tokens are the same."""
+    from pretrained_rstr_b200 import generate_batch, load_lm
+    from pretrained_rstr_b200.settings import SETTINGS
+    raw, seed = TINY["A"]
+    folder = folders[("A", "float32")]
+    prompts = [random_tokens(n, raw["vocab_size"], 40 + n) for n in (3, 9, 17)]
+    by_kernel = load_lm(folder, gpu=True, dtype="float32")
+    assert all(by_kernel.engine.runner._host_addresses) and all(by_kernel.engine.runner._result_addresses)
+    want = generate_batch(by_kernel, prompts, 12)
+    monkeypatch.setattr(SETTINGS, "step_words_by_kernel", False)
+    by_copy = load_lm(folder, gpu=True, dtype="float32")
+    assert not any(by_copy.engine.runner._host_addresses) and not any(by_copy.engine.runner._result_addresses)
+    assert generate_batch(by_copy, prompts, 12) == want
+    assert by_copy.engine.ahead["used"] > 0                # steps were launched ahead (feedback)
