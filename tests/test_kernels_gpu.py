@@ -760,6 +760,27 @@ def test_sample_kernel_publishes_its_result(rows):
         assert host[:rows].tolist() == logits.argmax(dim=1).tolist()
         assert host[rows:rows + 4].tolist() == [0, 11, 22, 33] and host[rows + 4:].tolist() == [-5] * 4
         assert int(counter[0]) == 0
+    # greedy rows with a publishing target are searched in slices by several CTAs: ties go to
+    # the lowest id and a NaN wins, wherever in the row they lie; odd widths and row starts
+    for vocab in (1000, 50257, 515):
+        wide = torch.randn(rows, vocab + 3, device="cuda", generator=g)[:, 1:vocab + 1]
+        want = wide.argmax(dim=1).tolist()
+        if rows >= 5:
+            wide[0, vocab - 1] = 50.0
+            wide[0, vocab // 2] = 50.0
+            wide[0, 7] = 50.0
+            wide[1, vocab - 2] = float("nan")
+            wide[2, vocab - 2] = float("nan")
+            wide[2, vocab // 3] = float("nan")
+            wide[3, :] = float("-inf")
+            wide[4, vocab - 1] = 60.0
+            want[:5] = [7, vocab - 2, vocab // 3, 0, vocab - 1]
+        ops.sample(result[:rows], wide, rows, publish=(address, result, rows + 4, counter))
+        torch.cuda.synchronize()
+        assert host[:rows].tolist() == want and result[:rows].tolist() == want
+        alone = torch.zeros(rows, dtype=torch.int32, device="cuda")
+        ops.sample(alone, wide, rows)                   # one CTA a row: the same ids
+        assert alone.tolist() == want
     temp = torch.full((rows,), 0.7, device="cuda")
     args = dict(temperature=temp, top_k=torch.full((rows,), 20, dtype=torch.int32, device="cuda"),
                 top_p=torch.ones(rows, device="cuda"),
