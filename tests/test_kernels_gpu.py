@@ -24,7 +24,8 @@ def _act(name, u):
 
 
 GEMM_SHAPES = [(5, 192, 64), (130, 320, 96), (300, 96, 320), (1, 2304, 768), (64, 1000, 96),
-               (257, 808, 1608), (2048, 768, 3072), (7, 50257, 768)]
+               (257, 808, 1608), (2048, 768, 3072), (7, 50257, 768), (33, 3072, 768), (64, 768, 3072),
+               (17, 6400, 1600)]
 
 
 @pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
@@ -913,7 +914,8 @@ def test_gemm_smallm_scatters_at_27_rows():
         assert torch.equal(v1[slot // ps, :, slot % ps].reshape(-1), out1[t, q_width + kv_width:])
 
 
-@pytest.mark.parametrize("m,heads,kv_heads,dh,ps", [(200, 6, 3, 32, 16), (130, 12, 12, 64, 64), (70, 5, 1, 24, 32)])
+@pytest.mark.parametrize("m,heads,kv_heads,dh,ps", [(200, 6, 3, 32, 16), (130, 12, 12, 64, 64), (70, 5, 1, 24, 32),
+                                                    (40, 6, 3, 32, 16), (64, 12, 12, 64, 64)])
 def test_gemm_bf16_scatters_keys_and_values_to_the_cache(m, heads, kv_heads, dh, ps):
     """The prompt-time QKV product writes its key and value columns to the cache slots itself
     (whole 16-byte pieces, or element by element when the width is not a multiple of 32); the
