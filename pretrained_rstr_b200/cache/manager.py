@@ -135,25 +135,29 @@ class _Table(list):
     device form up to date: ``row``, the same pages padded with -1 to the longest table a
     request can have.  A step copies rows; it does not rebuild them."""
 
-    __slots__ = ("row",)
+    __slots__ = ("row", "held")
 
     def __init__(self, row: np.ndarray, pages: Sequence[int] = ()):
         super().__init__(pages)
         self.row = row
+        self.held = sum(1 for p in self if p >= 0)      # pages not given back
         row[:] = -1
         if len(self):
             row[:len(self)] = self
 
     def append(self, page: int) -> None:
         self.row[len(self)] = page
+        self.held += 1 if page >= 0 else 0
         super().append(page)
 
     def pop(self) -> int:                  # the last page only
         page = super().pop()
+        self.held -= 1 if page >= 0 else 0
         self.row[len(self)] = -1
         return page
 
     def __setitem__(self, index: int, page: int) -> None:
+        self.held += (1 if page >= 0 else 0) - (1 if self[index] >= 0 else 0)
         super().__setitem__(index, page)
         self.row[index] = page
 
@@ -189,7 +193,7 @@ class _Request:
     chain: bytes = b""                             # hash chain up to indexed_pages
 
     def held(self, group: int) -> int:
-        return sum(1 for p in self.tables[group] if p >= 0)
+        return self.tables[group].held
 
 
 def chain_hash(parent: bytes, tokens: Sequence[int]) -> bytes:
@@ -234,6 +238,11 @@ class CacheManager:
             all(g.window is None for g in self.groups)
         # chain hash -> (pages per group, tokens of that page); LRU order.
         self._index: "OrderedDict[bytes, Tuple[Tuple[int, ...], Tuple[int, ...]]]" = OrderedDict()
+        # which pages the index names, and how many of them nobody else holds (what an
+        # admission may count on besides the free pages), kept up to date where reference
+        # counts change: asking must not cost a walk over the index
+        self._indexed = [bytearray(a.num_pages) for a in self.allocators]
+        self._cached = [0] * len(self.groups)
         self.stats = {"allocated": 0, "released": 0, "window_released": 0, "cow_copies": 0,
                       "prefix_hits": 0, "evicted": 0}
 
@@ -251,11 +260,12 @@ class CacheManager:
         """Pages that could be handed out now: free ones plus those only the prefix index
         holds, minus what admissions were promised."""
         alloc = self.allocators[group]
-        cached = sum(1 for pages, _ in self._index.values()
-                     if alloc.refcount[pages[group]] == 1)
-        outstanding = sum(max(0, r.promise[group] - r.held(group))
-                          for r in self.requests.values())
-        return alloc.free_count + cached - outstanding
+        outstanding = 0
+        for r in self.requests.values():
+            short = r.promise[group] - r.tables[group].held
+            if short > 0:
+                outstanding += short
+        return alloc.free_count + self._cached[group] - outstanding
 
     # ------------------------------------------------------------------ requests
     def open(self, rid: Hashable, reserve_tokens: Optional[int] = None,
@@ -335,7 +345,7 @@ class CacheManager:
             req.tables[gi] = _Table(self.table_rows[gi][slot], src.tables[gi][:n_pages])
             for page in req.tables[gi]:
                 if page >= 0:
-                    self.allocators[gi].retain(page)
+                    self._retain(gi, page)
         req.length = length
         req.tokens = list(src.tokens[:length])
         return slot
@@ -359,7 +369,7 @@ class CacheManager:
                 break
             self._index.move_to_end(key)
             for gi, page in enumerate(hit[0]):
-                self.allocators[gi].retain(page)
+                self._retain(gi, page)
                 req.tables[gi].append(page)
             chain = key
             shared += 1
@@ -382,7 +392,8 @@ class CacheManager:
             if key not in self._index:
                 pages = tuple(req.tables[gi][i] for gi in range(len(self.groups)))
                 for gi, page in enumerate(pages):
-                    self.allocators[gi].retain(page)
+                    self._retain(gi, page)
+                    self._indexed[gi][page] = 1          # (held by the request too: not counted)
                 self._index[key] = (pages, tokens)
             else:
                 self._index.move_to_end(key)
@@ -395,6 +406,8 @@ class CacheManager:
             if all(self.allocators[gi].refcount[p] == 1 for gi, p in enumerate(pages)):
                 del self._index[key]
                 for gi, p in enumerate(pages):
+                    self._indexed[gi][p] = 0
+                    self._cached[gi] -= 1
                     self._release(gi, p)
                 self.stats["evicted"] += 1
                 return True
@@ -555,11 +568,22 @@ class CacheManager:
                 raise CacheError("a held page is in the free set")
             if len(free) + sum(1 for c in alloc.refcount if c) != alloc.num_pages:
                 raise CacheError("a page is lost")
+            named = bytearray(alloc.num_pages)
+            for pages, _ in self._index.values():
+                named[pages[gi]] = 1
+            if named != self._indexed[gi]:
+                raise CacheError(f"group {gi}: the record of indexed pages differs from the index")
+            alone = sum(1 for pages, _ in self._index.values() if alloc.refcount[pages[gi]] == 1)
+            if alone != self._cached[gi]:
+                raise CacheError(f"group {gi}: {self._cached[gi]} pages counted as held by the index "
+                                 f"alone, {alone} are")
             rows = self.table_rows[gi]
             held_slots = set()
             for req in self.requests.values():
                 held_slots.add(req.slot)
                 table = req.tables[gi]
+                if table.held != sum(1 for p in table if p >= 0):
+                    raise CacheError(f"request {req.rid!r}: held-page count differs from the table")
                 if rows[req.slot, :len(table)].tolist() != list(table) or \
                         bool((rows[req.slot, len(table):] != -1).any()):
                     raise CacheError(f"request {req.rid!r}: the device form of its block table "
@@ -590,6 +614,15 @@ class CacheManager:
         self.stats["allocated"] += 1
         return page
 
+    def _retain(self, gi: int, page: int) -> None:
+        alloc = self.allocators[gi]
+        alloc.retain(page)
+        if self._indexed[gi][page] and alloc.refcount[page] == 2:
+            self._cached[gi] -= 1                        # no longer the index's alone
+
     def _release(self, gi: int, page: int) -> None:
-        self.allocators[gi].release(page)
+        alloc = self.allocators[gi]
+        alloc.release(page)
+        if self._indexed[gi][page] and alloc.refcount[page] == 1:
+            self._cached[gi] += 1                        # only the index holds it now
         self.stats["released"] += 1
