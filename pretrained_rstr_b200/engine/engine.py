@@ -11,6 +11,7 @@ from __future__ import annotations
 
 from typing import Callable, Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..csrc import ops
@@ -50,10 +51,13 @@ class Engine:
         sampling = sampling or SamplingParams()
         sampling.validate(self.lm.model.vocab, self.sampler.max_top_k)
         vocab = self.lm.model.vocab
-        for t in prompt:
-            if not 0 <= int(t) < vocab:
-                raise ValueError(f"prompt token id {t} outside the vocabulary of {vocab}")
-        req = Request(rid=rid, prompt=[int(t) for t in prompt], max_new_tokens=int(max_new_tokens),
+        ids = np.asarray(prompt)
+        if ids.ndim != 1 or (ids.size and ids.dtype.kind not in "iu"):
+            ids = np.asarray([int(t) for t in prompt], dtype=np.int64)      # (raises on what is no integer)
+        if ids.size and (int(ids.min()) < 0 or int(ids.max()) >= vocab):
+            bad = next(int(t) for t in ids if not 0 <= int(t) < vocab)
+            raise ValueError(f"prompt token id {bad} outside the vocabulary of {vocab}")
+        req = Request(rid=rid, prompt=ids.tolist(), max_new_tokens=int(max_new_tokens),
                       sampling=sampling, eos_ids=tuple(int(e) for e in eos_ids), on_token=on_token)
         self.scheduler.submit(req)
         return req
