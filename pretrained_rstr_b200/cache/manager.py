@@ -433,13 +433,14 @@ class CacheManager:
             for gi in range(len(self.groups)):
                 table = req.tables[gi]
                 group_slots: List[int] = []
-                for pos in range(req.length, req.length + count):
+                pos, end = req.length, req.length + count
+                while pos < end:                       # page by page, not token by token
                     li, off = divmod(pos, ps)
                     if li == len(table):
                         page = self._allocate(gi, req)
                         table.append(page)
                         pending.new_pages.append((gi, li, page))
-                    elif off != 0 or pos == req.length:
+                    else:
                         page = table[li]
                         if page < 0:
                             raise CacheError("append into a released page")
@@ -450,7 +451,10 @@ class CacheManager:
                             pending.swapped.append((gi, li, page, new))
                             table[li] = new
                             self.stats["cow_copies"] += 1
-                    group_slots.append(table[li] * ps + off)
+                    n = min(ps - off, end - pos)
+                    first = table[li] * ps + off
+                    group_slots.extend(range(first, first + n))
+                    pos += n
                 slots.append(group_slots)
         except Exception:
             req.pending = pending
@@ -471,7 +475,7 @@ class CacheManager:
             if len(tokens) != req.pending.count:
                 raise CacheError("commit: token count differs from the reservation")
             if len(req.tokens) == req.length:
-                req.tokens.extend(int(t) for t in tokens)
+                req.tokens.extend(tokens if type(tokens) is list else [int(t) for t in tokens])
         req.length += req.pending.count
         req.pending = None
         req.fresh = False
