@@ -363,7 +363,7 @@ class ModelRunner:
         for e in entries:
             # ids that are not known on the host yet are not recorded (such pages are not
             # offered for sharing)
-            known = all(t >= 0 for t in e.tokens)
+            known = min(e.tokens) >= 0
             self.cache.commit(e.rid, list(e.tokens) if known else None)
 
     def abort(self, entries: Sequence[Entry]) -> None:
