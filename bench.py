@@ -73,6 +73,12 @@ def load_bench_model(size: str, layers, max_tokens=None, prefill_chunk=1024, sha
 
 def run_mixed(args) -> int:
     """The mixed workload: one JSON line."""
+    # Every kernel instance is loaded when the library is (the driver's default loads an
+    # instance at its first launch, a stall of milliseconds that a server meets once per
+    # instance and this short run would meet inside its timed pass: 17.9 k to 21.4 k generated
+    # tokens/s from run to run at GPT-2 medium sizes without this, 20.6 k to 21.4 k with it).
+    # Must be set before the process's first CUDA call.
+    os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
     from pretrained_rstr_b200.measure.workloads import mixed_workload
     raw = dict(SIZES[args.size])
     per_request = -(-raw["n_positions"] // 64) * 64
@@ -96,7 +102,8 @@ def run_mixed(args) -> int:
                    "n_inner": raw["n_inner"], "vocab_size": raw["vocab_size"],
                    "requests": args.requests, "prompts": "uniform [16, 1024)", "prefill_chunk": 512,
                    "shared_prefix": 256, "shared_fraction": 0.3, "max_new": args.max_new,
-                   "pool_fraction": args.pool_fraction, "page_size": 64},
+                   "pool_fraction": args.pool_fraction, "page_size": 64,
+                   "module_loading": os.environ.get("CUDA_MODULE_LOADING", "")},
         **res, "clocks": clocks.summary()}))
     return 0
 
