@@ -130,6 +130,8 @@ def _declare(h: ctypes.CDLL) -> None:
     h.prb_set_pdl.restype = None
     h.prb_sample.argtypes = [P, P, L, I, P, P, P, P, P, P, P, I, P, P, I, P, P]
     h.prb_sample_max_top_k.argtypes = []
+    h.prb_sample_workspace_words.argtypes = []
+    h.prb_sample_workspace_words.restype = c_int
     for name in ("prb_resolve_tokens", "prb_fetch_step", "prb_publish_result", "prb_embed", "prb_layernorm", "prb_bias_act", "prb_kv_append", "prb_copy_pages",
                  "prb_gemm_f32", "prb_gemm_bf16", "prb_gemm_bf16_scatter", "prb_gemm_midm",
                  "prb_gemm_midm_supports", "prb_gemm_smallm", "prb_gemm_smallm_max_rows",
@@ -734,23 +736,33 @@ def max_top_k() -> int:
     return lib().prb_sample_max_top_k()
 
 
+def sample_workspace_words() -> int:
+    return lib().prb_sample_workspace_words()
+
+
 def sample(out, logits, n_rows, temperature=None, top_k=None, top_p=None, seeds=None, fresh=None,
-           slots=None, rng_states=None, publish=None) -> None:
+           slots=None, rng_states=None, publish=None, workspace=None) -> None:
     """out[r] = chosen token of logits[r,:] (float32).  Without ``temperature`` every row
     is greedy; otherwise rows with temperature <= 0 are greedy and the rest sample.
-    ``publish`` = (host_address, src, words, counter): the launch's last CTA also writes the
-    int32 words src[:words] to pinned host memory at ``host_address`` (from
-    :func:`host_device_address`); ``counter`` is one int32 on the device, zero between launches."""
+    ``workspace``: :func:`sample_workspace_words` int32 words on the device, zero at first and
+    then left to the kernels (one per stream of calls); with it a launch of up to 64 greedy
+    rows gives every row to several CTAs.  ``publish`` = (host_address, src, words), with a
+    workspace: the launch's last CTA also writes the int32 words src[:words] to pinned host
+    memory at ``host_address`` (from :func:`host_device_address`)."""
     what = "sample"
-    pub = (None, None, 0, None)
+    if workspace is not None:
+        _need(workspace, torch.int32, "workspace", what)
+        if workspace.numel() < sample_workspace_words() or not workspace.is_contiguous():
+            raise KernelArgumentError(f"{what}: the workspace needs {sample_workspace_words()} "
+                                      f"contiguous int32 words")
+    pub = (None, None, 0)
     if publish is not None:
-        address, src, words, counter = publish
+        address, src, words = publish
         _need(src, torch.int32, "publish source", what)
-        _need(counter, torch.int32, "publish counter", what)
-        if not address or words > src.numel():
-            raise KernelArgumentError(f"{what}: no host address to publish to, or {words} words "
-                                      f"are more than the source holds")
-        pub = (int(address), _p(src), int(words), _p(counter))
+        if workspace is None or not address or words > src.numel():
+            raise KernelArgumentError(f"{what}: publishing needs a workspace and a host address, "
+                                      f"and {words} words the source holds")
+        pub = (int(address), _p(src), int(words))
     _need(out, torch.int32, "out", what)
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelArgumentError(f"{what}: logits must be float32 with unit inner stride")
@@ -764,4 +776,5 @@ def sample(out, logits, n_rows, temperature=None, top_k=None, top_p=None, seeds=
         _need(rng_states, torch.int64, "rng_states", what)
     _check(lib().prb_sample(_p(out), _p(logits), logits.stride(0), logits.shape[1],
                             _p(temperature), _p(top_k), _p(top_p), _p(seeds), _p(fresh), _p(slots),
-                            _p(rng_states), n_rows, *pub, _stream()), what)
+                            _p(rng_states), n_rows, *pub, _p(workspace), _stream()), what)
+

@@ -464,5 +464,11 @@ def profile_sample(spec: str) -> int:
         res[f"sampled_top_p_{p}_us"] = round(_graph_time_us(
             lambda: ops.sample(out, logits, rows, temperature=temp, top_k=top_k, top_p=top_p,
                                seeds=seeds, fresh=fresh, slots=slots, rng_states=states)), 2)
+    if rows <= 64:
+        # with a workspace every greedy row goes to several CTAs (what the engine's sampler runs)
+        ws = torch.zeros(ops.sample_workspace_words(), dtype=torch.int32, device="cuda")
+        res["several_ctas_greedy_us"] = round(_graph_time_us(
+            lambda: ops.sample(out, logits, rows, workspace=ws)), 2)
+
     print(json.dumps({"profile_sample": spec, "mbytes": round(rows * vocab * 4 / 1e6, 2), **res}))
     return 0

@@ -59,7 +59,8 @@ class Sampler:
         self.rows = rows
         self.slot_of = slot_of                         # request id -> state slot
         self.rng_states = torch.zeros(rows, dtype=torch.int64, device=device)
-        self._publish_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        # scratch of the launches that give a row to several CTAs (and their counter)
+        self._workspace = torch.zeros(ops.sample_workspace_words(), dtype=torch.int32, device=device)
         self.started: Dict[Hashable, bool] = {}
         self.max_top_k = ops.max_top_k()
 
@@ -92,10 +93,8 @@ class Sampler:
         ``requests[i]``); nothing synchronises.  ``publish`` = (host address, source, words):
         the kernel also writes these words (the chosen ids among them) to pinned host memory."""
         n = len(requests)
-        if publish is not None:
-            publish = (*publish, self._publish_counter)
         if all(r.sampling.greedy for r in requests):
-            ops.sample(out, logits, n, publish=publish)
+            ops.sample(out, logits, n, publish=publish, workspace=self._workspace)
             return
         self._turn ^= 1
         host, dev, p = self._sets[self._turn]
@@ -124,4 +123,5 @@ class Sampler:
             self._sent[self._turn] = now
         ops.sample(out, logits, n, temperature=p["temperature"][1], top_k=p["top_k"][1],
                    top_p=p["top_p"][1], seeds=p["seeds"][1], fresh=p["fresh"][1],
-                   slots=p["slots"][1], rng_states=self.rng_states, publish=publish)
+                   slots=p["slots"][1], rng_states=self.rng_states, publish=publish,
+                   workspace=self._workspace)

@@ -751,12 +751,13 @@ def test_sample_kernel_publishes_its_result(rows):
     g = torch.Generator(device="cuda").manual_seed(rows)
     result = torch.zeros(rows + 4, dtype=torch.int32, device="cuda")
     result[rows:] = torch.tensor([0, 11, 22, 33], dtype=torch.int32)
-    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    workspace = torch.zeros(ops.sample_workspace_words(), dtype=torch.int32, device="cuda")
+    counter = workspace[:1]
     host = torch.full((rows + 8,), -5, dtype=torch.int32).pin_memory()
     address = ops.host_device_address(host)
     for turn in range(3):
         logits = torch.randn(rows, 1000, device="cuda", generator=g)
-        ops.sample(result[:rows], logits, rows, publish=(address, result, rows + 4, counter))
+        ops.sample(result[:rows], logits, rows, publish=(address, result, rows + 4), workspace=workspace)
         torch.cuda.synchronize()
         assert host[:rows].tolist() == logits.argmax(dim=1).tolist()
         assert host[rows:rows + 4].tolist() == [0, 11, 22, 33] and host[rows + 4:].tolist() == [-5] * 4
@@ -776,7 +777,7 @@ def test_sample_kernel_publishes_its_result(rows):
             wide[3, :] = float("-inf")
             wide[4, vocab - 1] = 60.0
             want[:5] = [7, vocab - 2, vocab // 3, 0, vocab - 1]
-        ops.sample(result[:rows], wide, rows, publish=(address, result, rows + 4, counter))
+        ops.sample(result[:rows], wide, rows, publish=(address, result, rows + 4), workspace=workspace)
         torch.cuda.synchronize()
         assert host[:rows].tolist() == want and result[:rows].tolist() == want
         alone = torch.zeros(rows, dtype=torch.int32, device="cuda")
@@ -789,9 +790,15 @@ def test_sample_kernel_publishes_its_result(rows):
                 fresh=torch.ones(rows, dtype=torch.int32, device="cuda"),
                 slots=torch.arange(rows, dtype=torch.int32, device="cuda"),
                 rng_states=torch.zeros(rows, dtype=torch.int64, device="cuda"))
-    ops.sample(result[:rows], logits, rows, publish=(address, result, rows + 4, counter), **args)
+    ops.sample(result[:rows], logits, rows, publish=(address, result, rows + 4), workspace=workspace, **args)
     torch.cuda.synchronize()
     assert host[:rows].tolist() == result[:rows].tolist() and int(counter[0]) == 0
+    assert int(workspace[:4].abs().sum()) == 0             # the launch's counter is back at zero
+    # the same rows by one CTA each choose the same tokens
+    args["rng_states"] = torch.zeros(rows, dtype=torch.int64, device="cuda")
+    alone = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    ops.sample(alone, logits, rows, **args)
+    assert alone.tolist() == result[:rows].tolist()
 
 
 def test_sample_kernel_greedy_ties_and_nan():
@@ -807,8 +814,9 @@ def test_sample_kernel_greedy_ties_and_nan():
     assert out.tolist() == want
 
 
+@pytest.mark.parametrize("several", [False, True])
 @pytest.mark.parametrize("vocab", [50257, 1000, 37])
-def test_sample_kernel_matches_the_plain_sampler(vocab):
+def test_sample_kernel_matches_the_plain_sampler(vocab, several):
     """Top-k selection (any k up to the limit, ties, NaN, rows of equal logits), temperature
     softmax, nucleus cut and the draw: the same token as the plain sampler on the same row,
     and the generator state left for the next draw."""
@@ -840,6 +848,8 @@ def test_sample_kernel_matches_the_plain_sampler(vocab):
                 top_p=torch.tensor(ps, device="cuda"),
                 seeds=torch.arange(100, 100 + n, dtype=torch.int64, device="cuda"),
                 slots=torch.arange(n, dtype=torch.int32, device="cuda"), rng_states=states)
+    if several:       # (a workspace changes nothing for rows that sample)
+        args["workspace"] = torch.zeros(ops.sample_workspace_words(), dtype=torch.int32, device="cuda")
     rngs = [plain_gpt2.JavaRandom(100 + i) for i in range(n)]
     for draw in range(3):                       # the second and third draw go on from the state
         fresh = torch.full((n,), 1 if draw == 0 else 0, dtype=torch.int32, device="cuda")
