@@ -237,30 +237,27 @@ __device__ __forceinline__ void norm_rows_staged(const Args& a, __nv_bfloat16* x
     constexpr int R = MP / WARPS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k = a.k;
-    // rows warp, warp + 8: those beyond M are zero
+    // rows warp, warp + 8: those beyond M (or gathered from outside the input) are zero
+    const float* xrow[R];
+    __nv_bfloat16* dst[R];
     int live = 0;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int t = warp + r * WARPS;
-        if (t < a.m) {
+        dst[r] = xs + (size_t)t * a.xs_pitch;
+        xrow[r] = t < a.m ? norm_source(a, t) : nullptr;
+        if (xrow[r] != nullptr) {
             ++live;
         } else {
-            __nv_bfloat16* dst = xs + (size_t)t * a.xs_pitch;
-            for (int i = lane; i < k / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
+            for (int i = lane; i < k / 2; i += 32) reinterpret_cast<uint32_t*>(dst[r])[i] = 0u;
         }
     }
     if (live == R) {
-        const float* xrow[R];
-        __nv_bfloat16* dst[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            xrow[r] = a.xf + (size_t)(warp + r * WARPS) * a.ldx;
-            dst[r] = xs + (size_t)(warp + r * WARPS) * a.xs_pitch;
-        }
         norm_rows_any<R>(xrow, dst, gb, k, a.beta != nullptr, a.eps);
-    } else if (live == 1) {                          // (rows are live from the first on)
-        norm_row_any(a.xf + (size_t)warp * a.ldx, xs + (size_t)warp * a.xs_pitch, gb, k,
-                     a.beta != nullptr, a.eps);
+    } else if (live > 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+            if (xrow[r] != nullptr) norm_row_any(xrow[r], dst[r], gb, k, a.beta != nullptr, a.eps);
     }
     __syncthreads();
 }
@@ -575,11 +572,13 @@ int prb_gemm_smallm_check(const void* x, const float* xf, const float* gamma, co
     return 0;
 }
 
-// x: bfloat16 [M,K] (xf null), or xf: float32 [M,K] to be LayerNorm-ed first with gamma, beta
-// (may be null) and eps.  m <= 64, k % 8 == 0, pitches multiples of 8 (4 for xf).
+// x: bfloat16 [M,K] (xf null), or xf: float32 rows to be LayerNorm-ed first with gamma, beta
+// (may be null) and eps: row t of the product from row xf_rows[t] of xf's xf_rows_in rows
+// (xf_rows null: from row t).  m <= 64, k % 8 == 0, pitches multiples of 8 (4 for xf).
 // kv_width > 0: the product is a fused QKV projection and its key and value columns are
 // also written to the paged cache at slots[token] (the cache has the output's element type).
-PRB_API int prb_gemm_smallm(void* out, const void* x, const float* xf, const float* gamma,
+PRB_API int prb_gemm_smallm(void* out, const void* x, const float* xf, const int* xf_rows,
+                            int xf_rows_in, const float* gamma,
                             const float* beta, float eps, const void* w, const float* bias,
                             const float* resid, int m, int n, int k, long ldx, long ldw, long ldc,
                             int act, int out_dtype, void* k_pages, void* v_pages,
@@ -592,6 +591,8 @@ PRB_API int prb_gemm_smallm(void* out, const void* x, const float* xf, const flo
     a.out = out;
     a.x = (const __nv_bfloat16*)x;
     a.xf = xf;
+    a.xf_rows = xf != nullptr ? xf_rows : nullptr;
+    a.xf_rows_in = xf_rows_in;
     a.gamma = gamma;
     a.beta = beta;
     a.eps = eps;

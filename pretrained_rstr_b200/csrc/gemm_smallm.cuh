@@ -31,7 +31,9 @@ constexpr int PF = 4;               // k-steps of weights in flight per warp
 struct Args {
     void* out;
     const __nv_bfloat16* x;         // bfloat16 [M,K], or null when xf is given
-    const float* xf;                // float32 [M,K] to be normalised first, or null
+    const float* xf;                // float32 rows to be normalised first, or null
+    const int* xf_rows;             // which row of xf output row t is made of (null: row t)
+    int xf_rows_in;                 // rows xf holds (the gathered indices are checked against it)
     const float* gamma;
     const float* beta;
     float eps;
@@ -54,6 +56,18 @@ struct Args {
 struct Prefetch {
     uint4 wa[PF], wb[PF];
 };
+
+// The float32 row that output row t is normalised from; null (and recorded in the status
+// word) when a gathered index lies outside xf.  The same answer in every lane of a warp.
+__device__ __forceinline__ const float* norm_source(const Args& a, int t) {
+    if (a.xf_rows == nullptr) return a.xf + (size_t)t * a.ldx;
+    const int src = a.xf_rows[t];
+    if (src < 0 || src >= a.xf_rows_in) {
+        if ((threadIdx.x & 31) == 0) prb_set_status(a.status, PRB_S_ROW_RANGE, t, src, a.xf_rows_in);
+        return nullptr;
+    }
+    return a.xf + (size_t)src * a.ldx;
+}
 
 // row pitch of the normalised activations: words per row = 16 mod 32 (conflict-free reads)
 __host__ __device__ inline int norm_pitch(int k) {
@@ -203,11 +217,12 @@ __device__ __forceinline__ void norm_rows(const Args& a, __nv_bfloat16* xs) {
     const int k = a.k, nvec = a.k / 4;            // float4 per row
     for (int t = warp; t < MP; t += WARPS) {
         __nv_bfloat16* dst = xs + (size_t)t * a.xs_pitch;
-        if (t >= a.m) {
+        const float* xrow = t < a.m ? norm_source(a, t) : nullptr;
+        if (xrow == nullptr) {
             for (int i = lane; i < k / 2; i += 32) reinterpret_cast<uint32_t*>(dst)[i] = 0u;
             continue;
         }
-        const float4* src = reinterpret_cast<const float4*>(a.xf + (size_t)t * a.ldx);
+        const float4* src = reinterpret_cast<const float4*>(xrow);
         float4 v[LN_MAX_K / 128];
         float s = 0.0f;
 #pragma unroll

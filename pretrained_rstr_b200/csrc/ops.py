@@ -90,7 +90,7 @@ def _declare(h: ctypes.CDLL) -> None:
                                         I, P, P]
     h.prb_gemm_midm.argtypes = [P, P, P, P, P, I, I, I, L, L, L, I, I, P, P]
     h.prb_gemm_midm_supports.argtypes = [I, I, I]
-    h.prb_gemm_smallm.argtypes = [P, P, P, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
+    h.prb_gemm_smallm.argtypes = [P, P, P, P, I, P, P, F, P, P, P, I, I, I, L, L, L, I, I,
                                   P, P, P, I, I, I, I, I, P, P]
     h.prb_gemm_smallm_max_rows.argtypes = []
     h.prb_gemm_smallm_max_norm_width.argtypes = []
@@ -412,10 +412,12 @@ def smallm_limits():
 
 
 def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0, bias=None,
-                resid=None, act=None, kv_scatter=None, status=None) -> None:
+                resid=None, act=None, kv_scatter=None, status=None, norm_rows=None) -> None:
     """out[M,N] = act(X . w[N,K]^T + bias) (+ resid) for M <= 64 rows, weights streamed once.
     X is ``a`` (bfloat16 [M,K]) or LayerNorm(``norm_input``) (float32 [M,K]) with ``gamma``,
-    ``beta`` and ``eps``, the norm fused into the kernel.  ``kv_scatter`` = (k_pages, v_pages,
+    ``beta`` and ``eps``, the norm fused into the kernel; with ``norm_rows`` (int32 [M]) row t
+    of X is the norm of row norm_rows[t] of ``norm_input`` (an index outside it gives a zero
+    row and is recorded in ``status``).  ``kv_scatter`` = (k_pages, v_pages,
     slots, q_width): the product is a fused QKV projection; its key and value columns are also
     written to the paged cache (same element type as ``out``) at each token's slot."""
     what = "gemm_smallm"
@@ -434,7 +436,14 @@ def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0,
         if x is None or x.dtype != torch.bfloat16 or x.stride(1) != 1:
             raise KernelArgumentError(f"{what}: a must be bfloat16 with unit inner stride")
     m = out.shape[0]
-    if x.shape[0] < m or x.shape[1] != k or out.shape[1] != n or out.stride(1) != 1:
+    if norm_rows is not None:
+        if norm_input is None:
+            raise KernelArgumentError(f"{what}: norm_rows gathers rows of norm_input")
+        _need(norm_rows, torch.int32, "norm_rows", what)
+        if norm_rows.numel() < m:
+            raise KernelArgumentError(f"{what}: {m} output rows, {norm_rows.numel()} row indices")
+    if (norm_rows is None and x.shape[0] < m) or x.shape[1] != k or out.shape[1] != n or \
+            out.stride(1) != 1:
         raise KernelArgumentError(f"{what}: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     if bias is not None:
         _need(bias, torch.float32, "bias", what)
@@ -452,7 +461,8 @@ def gemm_smallm(out, w, a=None, norm_input=None, gamma=None, beta=None, eps=0.0,
               page_size, num_pages)
     _check(lib().prb_gemm_smallm(
         _p(out), None if norm_input is not None else _p(x),
-        _p(x) if norm_input is not None else None, _p(gamma), _p(beta), float(eps), _p(w),
+        _p(x) if norm_input is not None else None, _p(norm_rows),
+        x.shape[0] if norm_input is not None else 0, _p(gamma), _p(beta), float(eps), _p(w),
         _p(bias), _p(resid), m, n, k, x.stride(0), w.stride(0), out.stride(0), ACT_CODES[act],
         dtype_code(out.dtype), *kv, _p(status), _stream()), what)
 

@@ -21,6 +21,7 @@ import torch
 from ..cache.manager import GroupSpec
 from ..parts import build_part, part_factory
 from ..parts.interfaces import LayerCache, StateSpec
+from ..parts.linear import LazyNorm
 
 
 class Model:
@@ -112,13 +113,17 @@ class Model:
         if r == 0:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=x.device)
         hn = ctx.scratch("final_normed", (ctx.row_capacity(r), self.width), self.runtime.dtype)[:r]
-        self.final_norm.forward(ctx, x, hn, rows=ctx.logit_rows)
+        # (a head that can norm its few rows itself does: the norm then is no kernel of its own)
+        lazy = getattr(self.head, "accepts_lazy_norm", False)
+        h_in = LazyNorm(ctx, self.final_norm, x, hn, rows=ctx.logit_rows) if lazy else hn
+        if not lazy:
+            self.final_norm.forward(ctx, x, hn, rows=ctx.logit_rows)
         # rows 128 bytes apart at least: a vocabulary that is no multiple of 4 (GPT-2's 50,257)
         # would otherwise put every row at an odd address, which the products' epilogues can
         # only store element by element
         pitch = -(-self.vocab // 32) * 32
         logits = ctx.scratch("logits", (ctx.row_capacity(r), pitch), torch.float32)[:r, :self.vocab]
-        self.head.forward(ctx, hn, logits)
+        self.head.forward(ctx, h_in, logits)
         return logits
 
 

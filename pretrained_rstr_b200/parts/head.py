@@ -11,6 +11,7 @@ from .registry import register_part
 
 class TiedHead(Head):
     graph_safe = True
+    accepts_lazy_norm = True        # ``h`` may be a LazyNorm: few rows are normed inside the product
     def __init__(self, table: torch.Tensor, vocab: int, width: int, runtime):
         if tuple(table.shape) != (vocab, width):
             raise ValueError(f"tied_head: table is {list(table.shape)}, expected [{vocab}, {width}]")

@@ -101,6 +101,9 @@ class Embedding:
 
 
 class Head:
+    """``accepts_lazy_norm`` (optional, False): the head takes the final norm as a ``LazyNorm``
+    (of the wanted rows of the residual stream) and may compute it inside its product."""
+
     def forward(self, ctx, h: torch.Tensor, logits: torch.Tensor) -> None:
         """logits[r] = h[r] . W^T, float32 [R, vocab]."""
         raise NotImplementedError

@@ -79,7 +79,8 @@ class Linear:
             if m <= 16 and isinstance(a, LazyNorm) and a.fusable and self.n_in <= max_norm:
                 ops.gemm_smallm(out, self.weight, norm_input=a.x, gamma=a.norm.gamma,
                                 beta=a.norm.beta, eps=a.norm.eps, bias=self.bias, resid=resid,
-                                act=act, kv_scatter=kv_scatter, status=ctx.status)
+                                act=act, kv_scatter=kv_scatter, status=ctx.status,
+                                norm_rows=a.rows)
             else:
                 ops.gemm_smallm(out, self.weight, a=_tensor(a), bias=self.bias, resid=resid,
                                 act=act, kv_scatter=kv_scatter, status=ctx.status)
@@ -93,12 +94,13 @@ class Linear:
 
 
 class LazyNorm:
-    """A norm of ``x`` that runs when its result is first needed.  A consumer that can
-    compute the norm itself (``fusable``: a plain layer norm) reads ``x`` and ``norm``
-    instead and the norm never runs as a kernel of its own."""
+    """A norm of ``x`` (of its rows ``rows``, if given: an int32 tensor of row indices) that
+    runs when its result is first needed.  A consumer that can compute the norm itself
+    (``fusable``: a plain layer norm) reads ``x``, ``rows`` and ``norm`` instead and the norm
+    never runs as a kernel of its own."""
 
-    def __init__(self, ctx, norm, x: torch.Tensor, out: torch.Tensor):
-        self.ctx, self.norm, self.x, self._out = ctx, norm, x, out
+    def __init__(self, ctx, norm, x: torch.Tensor, out: torch.Tensor, rows=None):
+        self.ctx, self.norm, self.x, self._out, self.rows = ctx, norm, x, out, rows
         self._done = False
         self.fusable = all(hasattr(norm, f) for f in ("gamma", "beta", "eps")) and \
             getattr(norm, "kind", "") == "layer_norm"
@@ -106,7 +108,10 @@ class LazyNorm:
 
     def tensor(self) -> torch.Tensor:
         if not self._done:
-            self.norm.forward(self.ctx, self.x, self._out)
+            if self.rows is None:
+                self.norm.forward(self.ctx, self.x, self._out)
+            else:
+                self.norm.forward(self.ctx, self.x, self._out, rows=self.rows)
             self._done = True
         return self._out
 

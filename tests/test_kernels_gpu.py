@@ -863,6 +863,37 @@ def test_sample_kernel_matches_the_plain_sampler(vocab, several):
             assert got[i] == want, f"row {i}, draw {draw}: {got[i]} != {want}"
 
 
+@pytest.mark.parametrize("m", [1, 8, 13])
+def test_gemm_smallm_fused_norm_of_gathered_rows(m):
+    """The fused norm may take its rows from anywhere in the input (the wanted rows of a
+    step before the head): the same bits as the norm of those rows placed in order; an index
+    outside the input gives a zero row and is recorded."""
+    ops = _ops()
+    g = torch.Generator(device="cuda").manual_seed(m)
+    k, n, t = 768, 1000, 40
+    x = torch.randn(t, k, device="cuda", generator=g)
+    gamma = torch.rand(k, device="cuda", generator=g) + 0.5
+    beta = torch.randn(k, device="cuda", generator=g) * 0.1
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    rows = torch.randperm(t, generator=torch.Generator().manual_seed(m))[:m].to(torch.int32).cuda()
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    gathered = torch.zeros(m, n, device="cuda")
+    ops.gemm_smallm(gathered, w, norm_input=x, gamma=gamma, beta=beta, eps=1e-5, norm_rows=rows,
+                    status=status)
+    in_order = torch.zeros(m, n, device="cuda")
+    ops.gemm_smallm(in_order, w, norm_input=x[rows.long()].contiguous(), gamma=gamma, beta=beta, eps=1e-5)
+    assert torch.equal(gathered, in_order) and status.tolist() == [0, 0, 0, 0]
+    ref = torch.nn.functional.layer_norm(x[rows.long()].double(), (k,), gamma.double(), beta.double(), 1e-5)
+    ref = ref.float().to(torch.bfloat16).float() @ w.float().t()
+    assert float((gathered - ref).abs().max()) <= 1e-2 * float(ref.abs().max())
+    rows[m - 1] = t                                      # one index outside the input
+    ops.gemm_smallm(gathered, w, norm_input=x, gamma=gamma, beta=beta, eps=1e-5, norm_rows=rows,
+                    status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] != 0 and float(gathered[m - 1].abs().max()) == 0.0
+    assert torch.equal(gathered[:m - 1], in_order[:m - 1])
+
+
 def test_gemm_smallm_scatters_keys_and_values_to_the_cache():
     """The decode-time QKV product writes its key and value columns to the cache slots
     itself; the result equals the product followed by the append kernel."""
