@@ -182,3 +182,18 @@ def test_step_words_through_the_copy_engine(folders, monkeypatch):
     assert not any(by_copy.engine.runner._host_addresses) and not any(by_copy.engine.runner._result_addresses)
     assert generate_batch(by_copy, prompts, 12) == want
     assert by_copy.engine.ahead["used"] > 0                # steps were launched ahead (feedback)
+
+
+def test_more_lanes_than_the_several_cta_token_choice_takes(folders):
+    """100 requests through 128 lanes (steps of up to 100 rows: one CTA a row chooses and
+    publishes) give what they give through 8 lanes, greedy and sampled."""
+    from pretrained_rstr_b200 import generate_batch, load_lm
+    raw, seed = TINY["A"]
+    folder = folders[("A", "float32")]
+    few = load_lm(folder, gpu=True, dtype="float32", max_lanes=8)
+    many = load_lm(folder, gpu=True, dtype="float32", max_lanes=128, max_batched_tokens=1024)
+    prompts = [random_tokens(3 + i % 17, raw["vocab_size"], 100 + i) for i in range(100)]
+    assert generate_batch(many, prompts, 10) == generate_batch(few, prompts, 10)
+    assert many.engine.ahead["used"] > 0
+    sampling = {"temperature": 0.8, "top_k": 20, "seed": 3}
+    assert generate_batch(many, prompts, 10, sampling) == generate_batch(few, prompts, 10, sampling)
