@@ -382,6 +382,23 @@ class CacheManager:
             req.fresh = False
         return req.length
 
+    def page_keys(self, prompt: Sequence[int]) -> List[bytes]:
+        """The chained hashes under which the prompt's full pages would be found in the prefix
+        index, in order (none where nothing is shared; never the page that holds the prompt's
+        last token, which is always computed)."""
+        if not self.share_prefixes:
+            return []
+        ps = self.page_size
+        keys: List[bytes] = []
+        chain = b""
+        while (len(keys) + 1) * ps < len(prompt):
+            chain = chain_hash(chain, tuple(prompt[len(keys) * ps:(len(keys) + 1) * ps]))
+            keys.append(chain)
+        return keys
+
+    def is_indexed(self, key: bytes) -> bool:
+        return key in self._index
+
     def _offer_full_pages(self, req: _Request) -> None:
         ps = self.page_size
         while (req.indexed_pages + 1) * ps <= req.length and \

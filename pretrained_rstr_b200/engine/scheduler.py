@@ -40,6 +40,7 @@ class Request:
     output: List[int] = field(default_factory=list)
     finish_reason: Optional[str] = None
     cancelled: bool = False
+    page_keys: Optional[List[bytes]] = None     # prefix-index keys of the prompt's full pages
 
     @property
     def tokens(self) -> List[int]:
@@ -133,7 +134,9 @@ class Scheduler:
         self.finished: "OrderedDict[Hashable, Request]" = OrderedDict()
         self._arrivals = 0
         self.stats = {"iterations": 0, "scheduled_tokens": 0, "admitted": 0,
-                      "deferred_admissions": 0, "finished": 0}
+                      "deferred_admissions": 0, "finished": 0, "prefix_waits": 0}
+        # prefix-index key of a page -> the running request that will compute it first
+        self._producing: Dict[bytes, Hashable] = {}
 
     # ------------------------------------------------------------------ submit
     def submit(self, request: Request) -> None:
@@ -177,26 +180,53 @@ class Scheduler:
     # ------------------------------------------------------------------- admit
     def admit(self) -> List[Request]:
         """Move waiting requests into the running set, in arrival order, while a lane is
-        free and their pages can be promised.  Stops at the first that does not fit."""
+        free and their pages can be promised.  Stops at the first that does not fit.  A
+        request whose prompt begins with pages that a running request is computing right now
+        (the same tokens, not yet in the prefix index) is passed over until those pages are
+        there: requests that arrive together with a common prefix then compute it once."""
         admitted: List[Request] = []
         for r in [w for w in self.waiting if w.cancelled]:
             self.waiting.remove(r)
             self._finish(r, "cancelled", opened=False)
-        while self.waiting and len(self.running) < self.opts.max_lanes:
-            r = self.waiting[0]
+        at = 0
+        while at < len(self.waiting) and len(self.running) < self.opts.max_lanes:
+            r = self.waiting[at]
+            if self._awaits_prefix(r):
+                self.stats["prefix_waits"] += 1
+                at += 1
+                continue
             try:
                 self.cache.open(r.rid, reserve_tokens=self._reserve_tokens(r),
                                 longest_step=self.opts.prefill_chunk)
             except OutOfPages:
                 self.stats["deferred_admissions"] += 1
                 break
-            self.waiting.pop(0)
+            self.waiting.pop(at)
             r.computed = self.cache.match_prefix(r.rid, r.prompt)
             r.phase = "prefill"
             self.running[r.rid] = r
+            for key in r.page_keys or ():
+                if not self.cache.is_indexed(key):
+                    self._producing.setdefault(key, r.rid)
             admitted.append(r)
             self.stats["admitted"] += 1
         return admitted
+
+    def _awaits_prefix(self, r: Request) -> bool:
+        """Whether the first page of ``r``'s prompt that the prefix index does not hold is one
+        a running request is about to compute (it still prefills and has not passed it)."""
+        if r.page_keys is None:
+            r.page_keys = self.cache.page_keys(r.prompt)
+        for i, key in enumerate(r.page_keys):
+            if self.cache.is_indexed(key):
+                continue
+            owner = self.running.get(self._producing.get(key))
+            if owner is None or owner.cancelled or owner.phase != "prefill" or \
+                    owner.computed >= (i + 1) * self.cache.page_size:
+                self._producing.pop(key, None)          # nobody (any more): compute it yourself
+                return False
+            return True
+        return False
 
     # -------------------------------------------------------------------- plan
     def next_plan(self) -> Plan:

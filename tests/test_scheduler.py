@@ -132,3 +132,51 @@ def test_cancel_between_steps():
 def test_sampling_params_defaults():
     assert SamplingParams().greedy and SamplingParams(temperature=0.0).greedy
     assert not SamplingParams(temperature=0.8).greedy
+
+
+def test_requests_that_arrive_together_compute_a_common_prefix_once():
+    """Three requests with the same first two pages arrive at once: the first computes them,
+    the others are passed over until the pages are in the prefix index and then take them
+    from there; a fourth with another prompt does not wait behind them."""
+    cache = CacheManager([FULL], 8, 64, 8, 128, share_prefixes=True)
+    sched = Scheduler(SchedulerOptions(max_batched_tokens=64, max_lanes=8, prefill_chunk=8), cache)
+    prefix = list(range(100, 116))                      # two full pages
+    prompts = {"a": prefix + [1, 2, 3], "b": prefix + [4, 5, 6, 7, 8], "c": prefix + [9],
+               "d": list(range(200, 212))}
+    for rid, p in prompts.items():
+        sched.submit(Request(rid=rid, prompt=p, max_new_tokens=2))
+    computed = {rid: 0 for rid in prompts}
+    admitted_at = {}
+    step = 0
+    while not sched.idle:
+        step += 1
+        assert step < 100
+        plan = sched.next_plan()
+        for rid in sched.running:
+            admitted_at.setdefault(rid, step)
+        for item in plan.scheduled:
+            toks = sched.step_tokens(item)
+            cache.reserve(item.rid, len(toks))
+            cache.commit(item.rid, toks)
+            if item.phase == "prefill":
+                computed[item.rid] += len(toks)
+        sched.complete(plan, {s.rid: 7 for s in plan.scheduled if sched.wants_logits(s)})
+    # a and d start at once; b and c wait for a's two pages and then compute only their own tails
+    assert admitted_at["a"] == 1 and admitted_at["d"] == 1
+    assert admitted_at["b"] == admitted_at["c"] == 3
+    assert computed == {"a": 19, "b": 5, "c": 1, "d": 12}
+    assert cache.stats["prefix_hits"] == 4 and sched.stats["prefix_waits"] > 0
+    cache.check()
+
+
+def test_a_prefix_is_not_waited_for_when_its_producer_goes_away():
+    cache = CacheManager([FULL], 8, 64, 8, 128, share_prefixes=True)
+    sched = Scheduler(SchedulerOptions(max_batched_tokens=64, max_lanes=8, prefill_chunk=8), cache)
+    prefix = list(range(100, 116))
+    sched.submit(Request(rid="a", prompt=prefix + [1, 2, 3], max_new_tokens=2))
+    sched.submit(Request(rid="b", prompt=prefix + [4], max_new_tokens=2))
+    sched.next_plan()
+    assert set(sched.running) == {"a"} and [r.rid for r in sched.waiting] == ["b"]
+    sched.cancel("a")
+    sched.next_plan()                                   # a ends; nobody computes the prefix now
+    assert set(sched.running) == {"b"} and sched.running["b"].computed == 0
